@@ -1,0 +1,328 @@
+"""LLMEngine: the public, in-process API of the inference engine.
+
+``add_request`` queues a tokenised prompt, ``step`` runs one continuous-batching iteration (schedule ->
+forward -> sample -> emit) and returns the requests that produced tokens, ``generate`` drives steps
+until a list of prompts has finished.  The HTTP server wraps an engine in a single scheduler thread
+that owns the CUDA context (reference: ``crates/spark-server/src/scheduler/mod.rs:262`` ``run``,
+``crates/spark-model/src/engine.rs:26`` ``generate``).
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, Hashable, List, Optional, Sequence as Seq
+
+import torch
+
+from .config import EngineConfig, ModelConfig
+from .kv import BlockPool, RadixCache, SlotPool
+from .models import CacheStore, DecoderLM, ForwardBatch
+from .runner import ModelRunner
+from .sampling import Sampler, SamplingParams
+from .sched import FinishReason, ScheduledSeq, Scheduler, SchedulerOutput, SeqStatus, Sequence
+from .sched.spec import SpecController
+from .utils.metrics import EngineStats
+
+
+@dataclass
+class RequestOutput:
+    request_id: str
+    new_tokens: List[int]
+    output_tokens: List[int]
+    finished: bool
+    finish_reason: Optional[str] = None
+    prompt_tokens: int = 0
+    cached_tokens: int = 0
+    ttft_s: Optional[float] = None
+    decode_time_s: Optional[float] = None
+    logprobs: Optional[List[Any]] = None
+    accepted_prediction_tokens: int = 0
+
+
+class RequestRejected(ValueError):
+    pass
+
+
+class LLMEngine:
+    def __init__(self, model: DecoderLM, cfg: Optional[EngineConfig] = None):
+        self.model = model
+        self.cfg = cfg or EngineConfig()
+        self.mcfg: ModelConfig = model.cfg
+        dev = model.device
+        self.hybrid = self.mcfg.family == "hybrid" and len(model.gdn_layers()) > 0
+        self.kv_dtype = self._resolve_kv_dtype()
+        num_blocks = self.cfg.num_kv_blocks or self._profile_num_blocks()
+        n_active = self.cfg.max_num_seqs if self.hybrid else 0
+        n_snap = self.cfg.ssm_cache_slots if (self.hybrid and self.cfg.enable_prefix_caching) else 0
+        self.cache: CacheStore = model.alloc_cache(num_blocks, self.cfg.block_size, self.kv_dtype, n_active + n_snap)
+        self.pool = BlockPool(num_blocks, self.cfg.block_size)
+        self.state_pool = SlotPool(n_active) if self.hybrid else None
+        self.snapshot_base = n_active
+        self.radix = RadixCache(self.pool, snapshot_slots=n_snap) if self.cfg.enable_prefix_caching else None
+        self.scheduler = Scheduler(self.cfg, self.pool, self.radix, self.state_pool, self.hybrid)
+        self.sampler = Sampler(self.mcfg.vocab_size, self.mcfg.eos_ids())
+        self.runner = ModelRunner(model, self.cache, self.cfg)
+        self.spec = SpecController(self, self.cfg) if (self.cfg.speculative and model.mtp is not None
+                                                         and self.cfg.num_drafts > 0) else None
+        self.stats = EngineStats()
+        self._seqs: Dict[str, Sequence] = {}
+        self._ids = itertools.count()
+        self._stop_checkers: Dict[str, Callable[[Sequence], bool]] = {}
+
+    # ------------------------------------------------------------------ sizing
+    def _resolve_kv_dtype(self) -> torch.dtype:
+        want = self.cfg.kv_cache_dtype
+        if want == "auto":
+            want = self.mcfg.quant.kv_cache_dtype
+        if want == "fp8":
+            return torch.float8_e4m3fn
+        if want == "bf16":
+            return torch.bfloat16
+        return self.model.dtype
+
+    def _profile_num_blocks(self) -> int:
+        per_block = max(1, self.model.kv_bytes_per_block(self.cfg.block_size, self.kv_dtype))
+        if self.model.device.type == "cuda":
+            free, total = torch.cuda.mem_get_info(self.model.device)
+            budget = int(total * self.cfg.gpu_memory_utilization) - (total - free)
+            # keep headroom for activations of the largest prefill chunk and the graph pools
+            budget -= self.runner_activation_reserve()
+            n = max(16, budget // per_block)
+        else:
+            n = 4096
+        cap = (self.cfg.max_seq_len // self.cfg.block_size + 1) * self.cfg.max_num_seqs
+        return int(min(n, cap))
+
+    def runner_activation_reserve(self) -> int:
+        c = self.mcfg
+        widest = max(c.q_size + 2 * c.kv_size, 2 * max(c.intermediate_size, c.moe_intermediate_size * max(1, c.num_experts_per_tok)),
+                     c.hidden_size)
+        tp = max(1, self.model.pctx.tp_size)
+        act = self.cfg.max_prefill_tokens * (widest // tp + 4 * c.hidden_size) * 2 * 3
+        logits = self.cfg.max_num_seqs * c.vocab_size * 6
+        return int(act + logits + (2 << 30))
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt_tokens: Seq[int], sampling: Optional[SamplingParams] = None,
+                    request_id: Optional[str] = None, namespace: Hashable = 0, priority: int = 0,
+                    timeout_s: Optional[float] = None, grammar: Any = None,
+                    logits_processors: Optional[List[Callable]] = None, disable_spec: bool = False,
+                    stop_checker: Optional[Callable[[Sequence], bool]] = None, adapter_slot: int = 0) -> str:
+        sampling = sampling or SamplingParams()
+        sampling.validate()
+        rid = request_id or f"req-{next(self._ids)}"
+        prompt = [int(t) for t in prompt_tokens]
+        if not prompt:
+            raise RequestRejected("empty prompt")
+        if any(t < 0 or t >= self.mcfg.vocab_size for t in prompt):
+            raise RequestRejected("token id out of range")
+        total = len(prompt) + sampling.max_tokens
+        if len(prompt) >= self.cfg.max_seq_len:
+            raise RequestRejected(f"prompt of {len(prompt)} tokens exceeds max_seq_len {self.cfg.max_seq_len}")
+        if total > self.cfg.max_seq_len:
+            sampling.max_tokens = self.cfg.max_seq_len - len(prompt)
+        if self.pool.blocks_for_tokens(len(prompt) + 1) > self.pool.num_blocks:
+            raise RequestRejected("prompt does not fit in the KV cache")
+        t_out = timeout_s if timeout_s is not None else (self.cfg.request_timeout_s or None)
+        seq = Sequence(rid, prompt, sampling, namespace=(adapter_slot, namespace), priority=priority,
+                       deadline=(time.monotonic() + t_out) if t_out else None, grammar=grammar,
+                       logits_processors=list(logits_processors or []), disable_spec=disable_spec,
+                       adapter_slot=adapter_slot)
+        self._seqs[rid] = seq
+        if stop_checker is not None:
+            self._stop_checkers[rid] = stop_checker
+        self.scheduler.add(seq)
+        self.stats.requests_total += 1
+        return rid
+
+    def abort(self, request_id: str) -> bool:
+        s = self.scheduler.abort(request_id)
+        self._seqs.pop(request_id, None)
+        self._stop_checkers.pop(request_id, None)
+        return s is not None
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_work()
+
+    # ------------------------------------------------------------------ one step
+    @torch.inference_mode()
+    def step(self) -> List[RequestOutput]:
+        t0 = time.monotonic()
+        sched = self.scheduler
+        out = sched.schedule()
+        results: List[RequestOutput] = []
+        for s in sched.finished_queue:      # deadline expiries
+            results.append(self._make_output(s, []))
+            self._seqs.pop(s.request_id, None)
+        sched.finished_queue.clear()
+        if out.empty:
+            return results
+        for snap_slot, seq_slot in out.restored_snapshots:
+            self.runner.copy_state(self.snapshot_base + snap_slot, seq_slot)
+        use_spec = self.spec is not None and self.spec.active()
+        batch = self.runner.build_batch(out, self.snapshot_base)
+        hidden = self.runner.forward(batch)
+        # rows that need logits
+        rows, row_owner = [], []
+        qsl = 0
+        for idx, it in enumerate(out.items):
+            if it.sample:
+                if it.verify_drafts:
+                    rows.extend(range(qsl, qsl + it.num_tokens))
+                    row_owner.extend([idx] * it.num_tokens)
+                else:
+                    rows.append(qsl + it.num_tokens - 1)
+                    row_owner.append(idx)
+            qsl += it.num_tokens
+        sampled: Dict[int, List[int]] = {}
+        lps: Dict[int, list] = {}
+        if rows:
+            logits = self.runner.logits(hidden, rows)
+            seqs_rows = [out.items[i].seq for i in row_owner]
+            so = self.sampler(logits, seqs_rows) if not any(out.items[i].verify_drafts for i in set(row_owner)) \
+                else self._sample_verify_rows(logits, out, row_owner)
+            for j, i in enumerate(row_owner):
+                sampled.setdefault(i, []).append(so.tokens[j])
+                if so.logprobs is not None and so.logprobs[j] is not None:
+                    lps.setdefault(i, []).append(so.logprobs[j])
+        now = time.monotonic()
+        accepted_rows: List[int] = []
+        qsl = 0
+        for idx, it in enumerate(out.items):
+            seq = it.seq
+            new_tokens: List[int] = []
+            if it.verify_drafts:
+                targets = sampled[idx]
+                n_acc = 0
+                while n_acc < it.verify_drafts and seq.drafts[n_acc] == targets[n_acc]:
+                    n_acc += 1
+                new_tokens = targets[:n_acc + 1]
+                seq.spec_proposed += it.verify_drafts
+                seq.spec_accepted += n_acc
+                self.stats.spec_proposed += it.verify_drafts
+                self.stats.spec_accepted += n_acc
+                sched.on_chunk_computed(it, n_acc + 1)
+                accepted_rows.append(n_acc + 1)
+                seq.drafts = []
+            else:
+                sched.on_chunk_computed(it)
+                accepted_rows.append(it.num_tokens)
+                if it.sample:
+                    new_tokens = sampled[idx]
+            if new_tokens:
+                kept = self._append_tokens(seq, new_tokens, now, lps.get(idx))
+                if seq.status == SeqStatus.PREFILL and not seq.finished:
+                    sched.promote(seq)
+                results.append(self._make_output(seq, kept))
+                if seq.finished:
+                    self._seqs.pop(seq.request_id, None)
+                    self._stop_checkers.pop(seq.request_id, None)
+            qsl += it.num_tokens
+        if batch.spec_verify:
+            self.model.commit_spec(accepted_rows, self.cache)
+            for it in out.items:
+                if not it.seq.finished:
+                    sched.trim_blocks(it.seq)
+        if use_spec:
+            self.spec.after_step(out, batch, hidden, sampled, accepted_rows)
+        dt = time.monotonic() - t0
+        self.stats.on_step(dt, out, sum(len(r.new_tokens) for r in results))
+        if self.spec is not None:
+            self.spec.gate.record(batch.spec_verify, dt, sum(len(r.new_tokens) for r in results))
+        return results
+
+    def _sample_verify_rows(self, logits, out: SchedulerOutput, row_owner: List[int]):
+        """Sample every verify row with the uniform of the output position it would emit at, so that
+        accepted tokens equal what plain decoding would have drawn."""
+        from .sampling import SamplerOutput
+        seqs, offs = [], []
+        seen: Dict[int, int] = {}
+        for i in row_owner:
+            k = seen.get(i, 0)
+            seen[i] = k + 1
+            seqs.append(_RowView(out.items[i].seq, k))
+        so = self.sampler(logits, seqs)
+        return so
+
+    def _append_tokens(self, seq: Sequence, toks: List[int], now: float, lps: Optional[list]) -> List[int]:
+        """Append sampled tokens, stopping at EOS / stop ids / max_tokens.  Returns the tokens kept."""
+        p = seq.sampling
+        kept: List[int] = []
+        eos = set() if p.ignore_eos else set(self.mcfg.eos_ids())
+        stop_ids = set(p.stop_token_ids)
+        checker = self._stop_checkers.get(seq.request_id)
+        for j, t in enumerate(toks):
+            if seq.first_token_time is None:
+                seq.first_token_time = now
+                self.stats.on_first_token(now - seq.arrival)
+            seq.output_tokens.append(int(t))
+            kept.append(int(t))
+            if lps is not None and j < len(lps):
+                seq.logprobs.append(lps[j])
+            reason = None
+            if seq.num_output_tokens >= p.min_tokens and (t in eos or t in stop_ids):
+                reason = FinishReason.STOP
+            elif checker is not None and checker(seq):
+                reason = FinishReason.STOP
+            elif seq.num_output_tokens >= p.max_tokens or seq.num_tokens >= self.cfg.max_seq_len:
+                reason = FinishReason.LENGTH
+            if reason is not None:
+                self.scheduler.finish(seq, reason)
+                self.stats.requests_finished += 1
+                break
+        self.stats.generation_tokens += len(kept)
+        return kept
+
+    def _make_output(self, seq: Sequence, new_tokens: List[int]) -> RequestOutput:
+        ttft = (seq.first_token_time - seq.arrival) if seq.first_token_time else None
+        dec = (seq.finish_time - seq.first_token_time) if (seq.finish_time and seq.first_token_time) else None
+        return RequestOutput(seq.request_id, new_tokens, list(seq.output_tokens), seq.finished,
+                             seq.finish_reason.value if seq.finish_reason else None, len(seq.prompt_tokens),
+                             seq.num_cached_tokens, ttft, dec, list(seq.logprobs) if seq.logprobs else None,
+                             seq.spec_accepted)
+
+    # ------------------------------------------------------------------ convenience
+    def generate(self, prompts: Seq[Seq[int]], sampling: Optional[SamplingParams] = None,
+                 samplings: Optional[Seq[SamplingParams]] = None) -> List[RequestOutput]:
+        """Run the prompts to completion; results come back in prompt order."""
+        import copy
+        ids = []
+        for i, p in enumerate(prompts):
+            sp = copy.deepcopy(samplings[i] if samplings is not None else (sampling or SamplingParams()))
+            ids.append(self.add_request(p, sp))
+        done: Dict[str, RequestOutput] = {}
+        while self.has_unfinished():
+            for r in self.step():
+                if r.finished:
+                    done[r.request_id] = r
+        return [done[i] for i in ids]
+
+    def snapshot(self) -> Dict[str, Any]:
+        s = self.scheduler.snapshot()
+        s.update(self.stats.as_dict())
+        if self.radix is not None:
+            st = self.radix.stats
+            s.update({"prefix_lookups": st.lookups, "prefix_hits": st.hits, "prefix_hit_tokens": st.hit_tokens,
+                      "prefix_nodes": self.radix.num_nodes})
+        if self.spec is not None:
+            s["spec_mode"] = self.spec.gate.mode
+        return s
+
+
+class _RowView:
+    """Presents verify row ``k`` of a sequence to the sampler as if ``k`` more tokens were already out."""
+
+    def __init__(self, seq: Sequence, k: int):
+        self._seq, self._k = seq, k
+
+    def __getattr__(self, name):
+        return getattr(self._seq, name)
+
+    @property
+    def num_output_tokens(self) -> int:
+        return self._seq.num_output_tokens + self._k
+
+    @property
+    def output_tokens(self) -> List[int]:
+        return self._seq.output_tokens + self._seq.drafts[:self._k]

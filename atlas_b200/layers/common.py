@@ -1,0 +1,74 @@
+"""Shared layer plumbing: parallel context, weight construction and TP slicing.
+
+TP slicing happens on the high-precision tensor *before* quantization, so every rank quantizes its
+own shard (reference: ``crates/spark-model/src/tp_shard.rs:37-120``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+import torch
+
+from ..ops import LinearWeight
+
+
+@dataclass
+class ParallelCtx:
+    tp_rank: int = 0
+    tp_size: int = 1
+    ep_rank: int = 0
+    ep_size: int = 1
+    comm: Any = None        # parallel.comm.CommBackend over the TP group
+    ep_comm: Any = None     # CommBackend over the EP group (may alias ``comm``)
+
+    @property
+    def is_tp(self) -> bool:
+        return self.tp_size > 1
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        if self.tp_size > 1 and self.comm is not None:
+            return self.comm.all_reduce(t)
+        return t
+
+    def ep_all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        c = self.ep_comm if self.ep_comm is not None else self.comm
+        if self.ep_size > 1 and c is not None:
+            return c.all_reduce(t)
+        return t
+
+
+def shard_rows(w: torch.Tensor, rank: int, size: int) -> torch.Tensor:
+    """Column-parallel slice (output features)."""
+    if size == 1:
+        return w
+    n = w.shape[0]
+    assert n % size == 0, f"rows {n} not divisible by tp {size}"
+    s = n // size
+    return w[rank * s:(rank + 1) * s]
+
+
+def shard_cols(w: torch.Tensor, rank: int, size: int) -> torch.Tensor:
+    """Row-parallel slice (input features)."""
+    if size == 1:
+        return w
+    k = w.shape[1]
+    assert k % size == 0, f"cols {k} not divisible by tp {size}"
+    s = k // size
+    return w[:, rank * s:(rank + 1) * s]
+
+
+def randn_weight(gen: torch.Generator, n: int, k: int, std: float, dtype, device) -> torch.Tensor:
+    """N(0, std) weight drawn on the generator's device, moved to ``device``."""
+    w = torch.randn(n, k, generator=gen, dtype=torch.float32, device=gen.device) * std
+    return w.to(device=device, dtype=dtype)
+
+
+def make_weight(w: torch.Tensor, kind: str, bias: Optional[torch.Tensor] = None) -> LinearWeight:
+    """Wrap (and quantize, if asked) a high-precision ``[N,K]`` tensor."""
+    n, k = w.shape
+    if kind == "fp8_block" and (k % 128 != 0):
+        kind = "dense"
+    if kind == "nvfp4" and (k % 16 != 0):
+        kind = "dense"
+    return LinearWeight.from_dense(w, kind, bias)

@@ -1,0 +1,46 @@
+"""SwiGLU feed-forward: fused gate|up GEMM -> SiLU*mul (+FP8 quant) -> row-parallel down GEMM.
+
+Under tensor parallelism gate/up are column-parallel and down is row-parallel with its reduction
+fused into the GEMM epilogue.  (The reference replicates dense FFN weights across TP ranks,
+``crates/spark-model/src/layers/dense_ffn*``; sharding them is this engine's choice.)
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..config import ModelConfig
+from ..ops import Act, LinearWeight
+from .common import ParallelCtx, make_weight, randn_weight, shard_cols, shard_rows
+
+
+class DenseMLP:
+    def __init__(self, cfg: ModelConfig, pctx: ParallelCtx, quant_kind: str, intermediate: Optional[int] = None,
+                 shard: bool = True):
+        self.cfg, self.pctx, self.quant_kind = cfg, pctx, quant_kind
+        self.inter = intermediate or cfg.intermediate_size
+        self.shard = shard and pctx.tp_size > 1 and self.inter % (pctx.tp_size * 128) == 0
+        self.gate_up: Optional[LinearWeight] = None
+        self.down: Optional[LinearWeight] = None
+
+    def load(self, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> None:
+        tp, r = (self.pctx.tp_size, self.pctx.tp_rank) if self.shard else (1, 0)
+        gu = torch.cat([shard_rows(gate, r, tp), shard_rows(up, r, tp)], 0)
+        self.gate_up = make_weight(gu, self.quant_kind)
+        self.down = make_weight(shard_cols(down, r, tp).contiguous(), self.quant_kind)
+
+    def init_random(self, gen, std, dtype, device) -> None:
+        h = self.cfg.hidden_size
+        self.load(randn_weight(gen, self.inter, h, std, dtype, device),
+                  randn_weight(gen, self.inter, h, std, dtype, device),
+                  randn_weight(gen, h, self.inter, std, dtype, device))
+
+    def forward(self, act: Act, reduce: bool = True) -> torch.Tensor:
+        gu = ops.linear(act, self.gate_up)
+        a = ops.silu_mul_act(gu, want_fp8=self.down.kind == "fp8_block")
+        y = ops.linear(a, self.down)
+        if self.shard and reduce:
+            y = self.pctx.all_reduce(y)
+        return y

@@ -1,0 +1,218 @@
+"""Generic decoder-only LM assembled from the layer blocks.
+
+One class covers the dense (Llama/Mistral/Qwen2/Qwen3), MoE (Qwen3-MoE) and hybrid
+(Qwen3-Next: Gated DeltaNet + gated attention + MoE + MTP head) families; ``ModelConfig`` decides
+the mixer and FFN kind of every layer.
+
+Reference parity: ``crates/spark-model/src/model/`` (``TransformerModel``), the decode program in
+``model/trait_impl/decode_a2.rs`` and the chunked prefill program in ``model/trait_impl/prefill_b.rs``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from .. import ops
+from ..config import ModelConfig
+from ..layers import Attention, DenseMLP, GatedDeltaNet, MoE, ParallelCtx
+from ..layers.common import make_weight, randn_weight, shard_rows
+from ..ops import Act, LinearWeight, reference as ref
+from .batch import ForwardBatch
+
+_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16,
+           "torch.float32": torch.float32, "torch.bfloat16": torch.bfloat16, "torch.float16": torch.float16}
+
+
+def torch_dtype(name: str) -> torch.dtype:
+    return _DTYPES.get(str(name), torch.bfloat16)
+
+
+def quant_kinds(cfg: ModelConfig) -> Tuple[str, str]:
+    """(kind for dense projections, kind for MoE expert stacks)."""
+    m = cfg.quant.method
+    if m == "fp8_block":
+        return "fp8_block", "fp8_block"
+    if m == "nvfp4":
+        return ("dense" if cfg.quant.experts_only else "nvfp4"), "nvfp4"
+    return "dense", "dense"
+
+
+@dataclass
+class CacheStore:
+    """Device memory the model reads/writes across steps: paged KV per attention layer and the
+    recurrent-state slot pool per GDN layer."""
+    kv: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)
+    kv_scales: Dict[int, Tuple[float, float]] = field(default_factory=dict)
+    states: Dict[int, dict] = field(default_factory=dict)
+    block_size: int = 16
+    num_blocks: int = 0
+
+    def layer_kv(self, i: int):
+        k, v = self.kv[i]
+        ks, vs = self.kv_scales.get(i, (1.0, 1.0))
+        return k, v, ks, vs
+
+
+class DecoderLayer:
+    def __init__(self, cfg: ModelConfig, idx: int, pctx: ParallelCtx, ep_mode: str = "auto",
+                 force_attention: bool = False):
+        self.cfg, self.idx = cfg, idx
+        dense_kind, expert_kind = quant_kinds(cfg)
+        self.kind = "attention" if force_attention else cfg.layer_kind(idx)
+        self.mixer = Attention(cfg, idx, pctx, dense_kind) if self.kind == "attention" else GatedDeltaNet(cfg, idx, pctx, dense_kind)
+        self.is_moe = (cfg.num_experts > 0) if force_attention else cfg.is_moe_layer(idx)
+        self.ffn = MoE(cfg, pctx, expert_kind, dense_kind, ep_mode) if self.is_moe else DenseMLP(cfg, pctx, dense_kind)
+        self.input_norm: Optional[torch.Tensor] = None
+        self.post_norm: Optional[torch.Tensor] = None
+
+    def init_random(self, gen, std, dtype, device):
+        base = 0.0 if self.cfg.norm_plus_one else 1.0
+        self.input_norm = torch.full((self.cfg.hidden_size,), base, dtype=dtype, device=device)
+        self.post_norm = torch.full((self.cfg.hidden_size,), base, dtype=dtype, device=device)
+        self.mixer.init_random(gen, std, dtype, device)
+        self.ffn.init_random(gen, std, dtype, device)
+
+    def _mixer_fp8(self) -> bool:
+        w = self.mixer.qkv if self.kind == "attention" else self.mixer.in_proj
+        return w.kind == "fp8_block"
+
+    def _ffn_fp8(self) -> bool:
+        return (not self.is_moe) and self.ffn.gate_up.kind == "fp8_block"
+
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor], batch: ForwardBatch, cache: CacheStore,
+                rope_cache: torch.Tensor):
+        cfg = self.cfg
+        if residual is None:
+            act, _ = ops.rmsnorm_act(x, self.input_norm, cfg.rms_norm_eps, None, cfg.norm_plus_one, self._mixer_fp8())
+            residual = x
+        else:
+            act, residual = ops.rmsnorm_act(x, self.input_norm, cfg.rms_norm_eps, residual, cfg.norm_plus_one, self._mixer_fp8())
+        if self.kind == "attention":
+            h = self.mixer.forward(act, batch, cache.layer_kv(self.idx), rope_cache)
+        else:
+            h = self.mixer.forward(act, batch, cache.states[self.idx])
+        act, residual = ops.rmsnorm_act(h, self.post_norm, cfg.rms_norm_eps, residual, cfg.norm_plus_one, self._ffn_fp8())
+        h = self.ffn.forward(act)
+        return h, residual
+
+
+class DecoderLM:
+    def __init__(self, cfg: ModelConfig, pctx: Optional[ParallelCtx] = None, device="cpu", ep_mode: str = "auto",
+                 with_mtp: Optional[bool] = None):
+        self.cfg = cfg
+        self.pctx = pctx or ParallelCtx()
+        self.device = torch.device(device)
+        self.dtype = torch_dtype(cfg.dtype)
+        self.layers = [DecoderLayer(cfg, i, self.pctx, ep_mode) for i in range(cfg.num_hidden_layers)]
+        self.embed: Optional[torch.Tensor] = None
+        self.final_norm: Optional[torch.Tensor] = None
+        self.lm_head: Optional[LinearWeight] = None          # vocab-parallel slice under TP
+        self.rope_cache: Optional[torch.Tensor] = None
+        self.mtp = None
+        if (with_mtp if with_mtp is not None else cfg.mtp_num_layers > 0):
+            from .mtp import MTPHead
+            self.mtp = MTPHead(cfg, self.pctx, ep_mode)
+        tp = self.pctx.tp_size
+        self.vocab_parallel = tp > 1 and cfg.vocab_size % tp == 0
+
+    # ------------------------------------------------------------------ weights
+    def init_random(self, seed: int = 0, std: float = 0.02, max_pos: Optional[int] = None) -> "DecoderLM":
+        cfg, dev, dt = self.cfg, self.device, self.dtype
+        gen_dev = "cuda" if dev.type == "cuda" else "cpu"
+        gen = torch.Generator(device=gen_dev)
+        gen.manual_seed(seed)
+        self.embed = randn_weight(gen, cfg.vocab_size, cfg.hidden_size, std, dt, dev)
+        for layer in self.layers:
+            layer.init_random(gen, std, dt, dev)
+        base = 0.0 if cfg.norm_plus_one else 1.0
+        self.final_norm = torch.full((cfg.hidden_size,), base, dtype=dt, device=dev)
+        head = self.embed if cfg.tie_word_embeddings else randn_weight(gen, cfg.vocab_size, cfg.hidden_size, std, dt, dev)
+        self.set_lm_head(head)
+        if self.mtp is not None:
+            self.mtp.init_random(gen, std, dt, dev)
+        self.finalize(max_pos)
+        return self
+
+    def set_lm_head(self, head: torch.Tensor) -> None:
+        if self.vocab_parallel:
+            head = shard_rows(head, self.pctx.tp_rank, self.pctx.tp_size).contiguous()
+        self.lm_head = LinearWeight("dense", head)
+
+    def finalize(self, max_pos: Optional[int] = None) -> None:
+        cfg = self.cfg
+        mp = max_pos or cfg.max_position_embeddings
+        self.rope_cache = ref.build_rope_cache(cfg.rotary_dim, mp, cfg.rope_theta, cfg.rope_scaling, self.device)
+
+    # ------------------------------------------------------------------ cache allocation
+    def attention_layers(self) -> List[int]:
+        return [l.idx for l in self.layers if l.kind == "attention"]
+
+    def gdn_layers(self) -> List[int]:
+        return [l.idx for l in self.layers if l.kind == "gdn"]
+
+    def kv_bytes_per_block(self, block_size: int, kv_dtype: torch.dtype) -> int:
+        n_attn = len(self.attention_layers()) + (1 if self.mtp is not None else 0)
+        hkv = self.layers[self.attention_layers()[0]].mixer.hkv if n_attn else 0
+        return 2 * n_attn * block_size * hkv * self.cfg.head_dim * kv_dtype.itemsize
+
+    def alloc_cache(self, num_blocks: int, block_size: int, kv_dtype: torch.dtype, state_slots: int = 0) -> CacheStore:
+        store = CacheStore(block_size=block_size, num_blocks=num_blocks)
+        for l in self.layers:
+            if l.kind == "attention":
+                shape = (num_blocks, block_size, l.mixer.hkv, self.cfg.head_dim)
+                store.kv[l.idx] = (torch.zeros(shape, dtype=kv_dtype, device=self.device),
+                                   torch.zeros(shape, dtype=kv_dtype, device=self.device))
+                store.kv_scales[l.idx] = (1.0, 1.0)
+            else:
+                store.states[l.idx] = l.mixer.alloc_state(max(1, state_slots), self.device, self.dtype)
+        if self.mtp is not None:
+            self.mtp.alloc_cache(store, num_blocks, block_size, kv_dtype, self.device)
+        return store
+
+    # ------------------------------------------------------------------ forward
+    def embed_tokens(self, ids: torch.Tensor) -> torch.Tensor:
+        return self.embed[ids.long()]
+
+    @torch.inference_mode()
+    def forward(self, batch: ForwardBatch, cache: CacheStore) -> torch.Tensor:
+        """Returns the final-normed hidden states ``[T,H]`` of every row."""
+        x = batch.inputs_embeds if batch.inputs_embeds is not None else self.embed_tokens(batch.input_ids)
+        residual = None
+        for layer in self.layers:
+            x, residual = layer.forward(x, residual, batch, cache, self.rope_cache)
+        self.last_prenorm = (x, residual)
+        y, _ = ops.rmsnorm(x, self.final_norm, self.cfg.rms_norm_eps, residual, self.cfg.norm_plus_one)
+        return y
+
+    @torch.inference_mode()
+    def compute_logits(self, hidden: torch.Tensor, indices: Optional[torch.Tensor] = None) -> torch.Tensor:
+        h = hidden if indices is None else hidden[indices]
+        logits = ops.linear(h, self.lm_head)
+        if self.vocab_parallel and self.pctx.comm is not None:
+            logits = self.pctx.comm.all_gather(logits, dim=-1)
+        return logits
+
+    def commit_spec(self, accepted_rows: List[int], cache: CacheStore) -> None:
+        """After speculative verification: fold the accepted rows into every GDN layer's state."""
+        for l in self.layers:
+            if l.kind == "gdn":
+                l.mixer.commit(accepted_rows, cache.states[l.idx])
+
+    # ------------------------------------------------------------------ oracle
+    @torch.inference_mode()
+    def forward_dense_reference(self, token_ids: List[int]) -> torch.Tensor:
+        """Plain eager forward of ONE sequence without any paging (logits of every position).
+
+        Used by tests as the "plain eager forward" that the paged/batched engine must match.
+        """
+        n = len(token_ids)
+        bs = 16
+        nblk = (n + bs - 1) // bs
+        kv_dtype = self.dtype
+        tmp = self.alloc_cache(nblk, bs, kv_dtype, state_slots=1)
+        fb = ForwardBatch.build([list(token_ids)], [0], [list(range(nblk))], bs, device=self.device,
+                                state_slots=[0], has_state=[False], all_logits=True)
+        h = self.forward(fb, tmp)
+        return self.compute_logits(h)

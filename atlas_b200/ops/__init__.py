@@ -1,0 +1,193 @@
+"""Op front-end: every call goes to the sm_100a kernel library when the tensors live on a GPU and to
+the plain-PyTorch restatement (``ops.reference``) otherwise.
+
+On a machine with a GPU the kernel library is mandatory: importing this package there without a
+built ``libatlas_b200_kernels.so`` raises instead of silently running eager PyTorch.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Tuple
+
+import torch
+
+from .. import quant as Q
+from . import reference as ref
+
+_cuda = None
+
+
+def cuda_ops():
+    """The ctypes binding module for the kernel library (loaded on first GPU use)."""
+    global _cuda
+    if _cuda is None:
+        from . import cuda as _c
+        _c.load()
+        _cuda = _c
+    return _cuda
+
+
+# ----------------------------------------------------------------------------- weights / activations
+@dataclass
+class LinearWeight:
+    """One (possibly quantized) ``[N,K]`` projection.
+
+    kind ``dense``: ``weight [N,K]`` in the model dtype.
+    kind ``fp8_block``: ``weight [N,K]`` e4m3, ``scale [ceil(N/128), ceil(K/128)]`` fp32.
+    kind ``nvfp4``: ``weight [N,K/2]`` packed E2M1, ``scale [N,K/16]`` e4m3, ``gscale [1]`` fp32.
+    """
+    kind: str
+    weight: torch.Tensor
+    scale: Optional[torch.Tensor] = None
+    gscale: Optional[torch.Tensor] = None
+    bias: Optional[torch.Tensor] = None
+    _dense_cache: Optional[torch.Tensor] = None
+
+    @property
+    def out_features(self) -> int:
+        return self.weight.shape[0]
+
+    @property
+    def in_features(self) -> int:
+        return self.weight.shape[1] * (2 if self.kind == "nvfp4" else 1)
+
+    def dequantized(self) -> torch.Tensor:
+        if self.kind == "dense":
+            return self.weight
+        if self.kind == "fp8_block":
+            return Q.dequantize_fp8_block(self.weight, self.scale)
+        return Q.dequantize_nvfp4(self.weight, self.scale, self.gscale)
+
+    @staticmethod
+    def from_dense(w: torch.Tensor, kind: str, bias=None) -> "LinearWeight":
+        if kind in ("dense", "none"):
+            return LinearWeight("dense", w.contiguous(), bias=bias)
+        if kind == "fp8_block":
+            q, s = Q.quantize_fp8_block(w)
+            return LinearWeight("fp8_block", q, s, bias=bias)
+        if kind == "nvfp4":
+            p, s, g = Q.quantize_nvfp4(w)
+            return LinearWeight("nvfp4", p, s, g, bias=bias)
+        raise ValueError(kind)
+
+
+@dataclass
+class Act:
+    """Activation handle: plain ``x [T,K]`` and/or its FP8 group-quantized form ``(q, s)``."""
+    x: Optional[torch.Tensor] = None
+    q: Optional[torch.Tensor] = None
+    s: Optional[torch.Tensor] = None
+
+    def plain(self) -> torch.Tensor:
+        if self.x is None:
+            self.x = (self.q.float().view(self.q.shape[0], -1, 128) * self.s[..., None]).view(self.q.shape).to(torch.bfloat16)
+        return self.x
+
+    def fp8(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        if self.q is None:
+            self.q, self.s = quant_fp8(self.x)
+        return self.q, self.s
+
+
+# ----------------------------------------------------------------------------- elementwise / norm
+def quant_fp8(x: torch.Tensor, group: int = 128):
+    if x.is_cuda:
+        return cuda_ops().quant_fp8(x, group)
+    return Q.per_token_group_quant_fp8(x, group)
+
+
+def rmsnorm(x, w, eps, residual=None, plus_one=False):
+    if x.is_cuda:
+        return cuda_ops().rmsnorm(x, w, eps, residual, plus_one, quant=False)
+    return ref.rmsnorm(x, w, eps, residual, plus_one)
+
+
+def rmsnorm_act(x, w, eps, residual=None, plus_one=False, want_fp8=False) -> Tuple[Act, Optional[torch.Tensor]]:
+    """Residual add + RMSNorm, emitting FP8 group-quantized activations when the consumer is an FP8 GEMM."""
+    if want_fp8 and x.shape[-1] % 128 == 0:
+        if x.is_cuda:
+            q, s, r = cuda_ops().rmsnorm(x, w, eps, residual, plus_one, quant=True)
+        else:
+            q, s, r = ref.rmsnorm_quant_fp8(x, w, eps, residual, plus_one)
+        return Act(q=q, s=s), r
+    y, r = rmsnorm(x, w, eps, residual, plus_one)
+    return Act(x=y), r
+
+
+def silu_mul_act(gate_up: torch.Tensor, want_fp8=False) -> Act:
+    inter = gate_up.shape[-1] // 2
+    if want_fp8 and inter % 128 == 0:
+        if gate_up.is_cuda:
+            q, s = cuda_ops().silu_mul(gate_up, quant=True)
+        else:
+            q, s = ref.silu_mul_quant_fp8(gate_up)
+        return Act(q=q, s=s)
+    if gate_up.is_cuda:
+        return Act(x=cuda_ops().silu_mul(gate_up, quant=False))
+    return Act(x=ref.silu_mul(gate_up))
+
+
+# ----------------------------------------------------------------------------- GEMM
+def linear(a, w: LinearWeight, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``y = a @ W^T (+ bias)``; ``a`` is a tensor or an :class:`Act`."""
+    act = a if isinstance(a, Act) else Act(x=a)
+    dev_cuda = (act.x if act.x is not None else act.q).is_cuda
+    if w.kind == "fp8_block":
+        q, s = act.fp8()
+        if dev_cuda:
+            y = cuda_ops().gemm_fp8_block(q, s, w.weight, w.scale, out=out)
+        else:
+            y = Q.fp8_block_gemm_ref(q, s, w.weight, w.scale, out_dtype=torch.bfloat16)
+    elif w.kind == "nvfp4":
+        x = act.plain()
+        if dev_cuda:
+            y = cuda_ops().gemm_nvfp4(x, w.weight, w.scale, w.gscale, out=out)
+        else:
+            y = (x.float() @ w.dequantized().t()).to(x.dtype)
+    else:
+        x = act.plain()
+        if dev_cuda and x.dtype == torch.bfloat16:
+            y = cuda_ops().gemm_bf16(x, w.weight, out=out)
+        else:
+            y = torch.nn.functional.linear(x, w.weight)
+    if w.bias is not None:
+        y = y + w.bias
+    return y
+
+
+# ----------------------------------------------------------------------------- attention
+def qk_norm_rope_kv_write(q, k, v, positions, rope_cache, rotary_dim, k_cache, v_cache, slot_mapping,
+                          k_scale=1.0, v_scale=1.0, q_norm_w=None, k_norm_w=None, eps=1e-6, norm_plus_one=False):
+    if q.is_cuda:
+        return cuda_ops().qk_norm_rope_kv_write(q, k, v, positions, rope_cache, rotary_dim, k_cache, v_cache,
+                                                slot_mapping, k_scale, v_scale, q_norm_w, k_norm_w, eps, norm_plus_one)
+    return ref.qk_norm_rope_kv_write(q, k, v, positions, rope_cache, rotary_dim, k_cache, v_cache, slot_mapping,
+                                     k_scale, v_scale, q_norm_w, k_norm_w, eps, norm_plus_one)
+
+
+def paged_attention(q, k_cache, v_cache, batch, scale, k_scale=1.0, v_scale=1.0, sliding_window=None) -> torch.Tensor:
+    """Attention of the step's query rows over the paged cache. ``batch`` is a ``ForwardBatch``."""
+    if q.is_cuda:
+        return cuda_ops().paged_attention(q, k_cache, v_cache, batch, scale, k_scale, v_scale, sliding_window)
+    return ref.paged_attention(q, k_cache, v_cache, batch.block_tables, batch.seq_lens, batch.query_start_loc,
+                               scale, k_scale, v_scale, sliding_window)
+
+
+# ----------------------------------------------------------------------------- MoE
+def moe_route(logits, top_k, norm_topk, scoring="softmax"):
+    if logits.is_cuda:
+        return cuda_ops().moe_route(logits, top_k, norm_topk, scoring)
+    return ref.moe_route(logits, top_k, norm_topk, scoring)
+
+
+# ----------------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    if logits.is_cuda:
+        return cuda_ops().argmax(logits)
+    return ref.argmax_first(logits)
+
+
+def sample(logits, temperature, top_k, top_p, min_p, uniform):
+    if logits.is_cuda:
+        return cuda_ops().sample(logits, temperature, top_k, top_p, min_p, uniform)
+    return ref.sample(logits, temperature, top_k, top_p, min_p, uniform)

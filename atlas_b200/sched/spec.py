@@ -1,0 +1,159 @@
+"""Speculative decoding control: MTP proposal chain, acceptance bookkeeping and the throughput gate.
+
+Per step, after the target model has run and tokens were sampled:
+
+1. the MTP head consumes ``(target hidden at p, token at p+1)`` for every row the step kept, which
+   keeps the head's own KV layer in lock-step with the target's;
+2. for sequences that just emitted a token the head's last row gives draft ``d1``; ``d2..dK`` come from
+   a chain of single-row head steps fed with the head's own hidden;
+3. the next engine step verifies ``[last, d1..dK]`` as K+1 query rows; a draft is accepted while it
+   equals the token the target samples at that row (so emitted tokens are exactly the target's).
+
+The gate arbitrates between speculative and plain decoding by measured emitted tokens per second,
+re-measuring the losing mode periodically.
+
+Reference parity: ``crates/spark-server/src/scheduler/mtp_step.rs``, ``mtp_gate.rs`` (MeasureDecode /
+MeasureVerify arbitration), ``crates/spark-model/src/speculative.rs:327`` (``DraftProposer``),
+``layers/mtp_head/propose_chain.rs``.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import ops
+from ..config import EngineConfig
+from ..models import ForwardBatch
+from .sequence import SchedulerOutput, SeqStatus
+
+
+class MtpGate:
+    """Throughput arbitration between speculative and plain decode."""
+
+    def __init__(self, enabled: bool = True, window: int = 32, remeasure_every: int = 512, probe_steps: int = 16):
+        self.enabled = enabled
+        self.window, self.remeasure_every, self.probe_steps = window, remeasure_every, probe_steps
+        self.mode = "spec"                       # spec | plain
+        self.tps = {"spec": 0.0, "plain": 0.0}
+        self._acc = {"spec": [0.0, 0], "plain": [0.0, 0]}   # [seconds, tokens]
+        self._steps_in_mode = 0
+        self._probing: Optional[str] = "spec" if enabled else None
+        self._since_measure = 0
+
+    def use_spec(self) -> bool:
+        if not self.enabled:
+            return True
+        return (self._probing or self.mode) == "spec"
+
+    def record(self, was_spec: bool, seconds: float, tokens: int) -> None:
+        if not self.enabled or tokens <= 0:
+            return
+        key = "spec" if was_spec else "plain"
+        acc = self._acc[key]
+        acc[0] += seconds
+        acc[1] += tokens
+        self._steps_in_mode += 1
+        self._since_measure += 1
+        if self._probing is not None and self._steps_in_mode >= self.probe_steps:
+            sec, tok = self._acc[self._probing]
+            if sec > 0:
+                self.tps[self._probing] = tok / sec
+            self._acc[self._probing] = [0.0, 0]
+            self._steps_in_mode = 0
+            if self._probing == "spec" and self.tps["plain"] == 0.0:
+                self._probing = "plain"
+            else:
+                self._probing = None
+                self.mode = "spec" if self.tps["spec"] >= self.tps["plain"] else "plain"
+                self._since_measure = 0
+        elif self._probing is None and self._since_measure >= self.remeasure_every:
+            self._probing = "plain" if self.mode == "spec" else "spec"
+            self._steps_in_mode = 0
+            self._acc[self._probing] = [0.0, 0]
+
+
+class SpecController:
+    def __init__(self, engine, cfg: EngineConfig):
+        self.engine = engine
+        self.cfg = cfg
+        self.k = cfg.num_drafts
+        self.gate = MtpGate(enabled=cfg.mtp_gate)
+
+    def active(self) -> bool:
+        return True
+
+    # ------------------------------------------------------------------ after each target step
+    @torch.inference_mode()
+    def after_step(self, out: SchedulerOutput, batch: ForwardBatch, hidden: torch.Tensor,
+                   sampled: Dict[int, List[int]], kept_rows: List[int]) -> None:
+        eng = self.engine
+        model, mtp, runner = eng.model, eng.model.mtp, eng.runner
+        bs = eng.cfg.block_size
+        rows: List[int] = []
+        toks: List[List[int]] = []
+        ctxs: List[int] = []
+        tables: List[List[int]] = []
+        owners: List[int] = []
+        propose: List[bool] = []
+        r0 = 0
+        for idx, it in enumerate(out.items):
+            seq = it.seq
+            m = kept_rows[idx]
+            n_in = it.num_tokens
+            if seq.finished or m <= 0:
+                r0 += n_in
+                continue
+            all_toks = seq.all_tokens
+            nxt = all_toks[it.start + 1:it.start + m + 1]        # token at p+1 for each kept row p
+            if len(nxt) < m:
+                r0 += n_in
+                continue
+            rows.extend(range(r0, r0 + m))
+            toks.append(nxt)
+            ctxs.append(it.start)
+            tables.append(seq.blocks)
+            owners.append(idx)
+            propose.append(bool(it.sample) and seq.status == SeqStatus.RUNNING and not seq.disable_spec)
+            r0 += n_in
+        if not rows:
+            return
+        fb = ForwardBatch.build(toks, ctxs, tables, bs, device=model.device)
+        fb.num_decodes = 0          # positions are arbitrary chunks; use the general attention path
+        ridx = torch.tensor(rows, dtype=torch.long, device=hidden.device)
+        h_prev = hidden[ridx]
+        emb = model.embed_tokens(fb.input_ids)
+        mh = mtp.forward(fb, emb, h_prev, eng.cache, model.rope_cache)
+        last_rows = (fb.query_start_loc[1:] - 1).long()
+        want = [i for i, p in enumerate(propose) if p]
+        if not want or not self.gate.use_spec():
+            return
+        sel = last_rows[torch.tensor(want, device=last_rows.device)]
+        cur_h = mh[sel]
+        drafts: List[List[int]] = [[] for _ in want]
+        seqs = [out.items[owners[i]].seq for i in want]
+        d = ops.argmax(model.compute_logits(cur_h)).tolist()
+        for j, t in enumerate(d):
+            drafts[j].append(int(t))
+        alive = list(range(len(want)))
+        for step in range(1, self.k):
+            # chain: position p+step, inputs (head hidden, previous draft)
+            ok = [j for j in alive if eng.scheduler._ensure_blocks(seqs[j], seqs[j].num_computed + step)]
+            if not ok:
+                break
+            alive = ok
+            t_in = [[drafts[j][-1]] for j in alive]
+            c_in = [seqs[j].num_computed + step - 1 for j in alive]
+            fbc = ForwardBatch.build(t_in, c_in, [seqs[j].blocks for j in alive], bs, device=model.device)
+            fbc.num_decodes = 0
+            hsel = cur_h[torch.tensor(alive, device=cur_h.device)] if len(alive) != cur_h.shape[0] else cur_h
+            mh2 = mtp.forward(fbc, model.embed_tokens(fbc.input_ids), hsel, eng.cache, model.rope_cache)
+            d = ops.argmax(model.compute_logits(mh2)).tolist()
+            nh = cur_h.clone()
+            for jj, j in enumerate(alive):
+                drafts[j].append(int(d[jj]))
+                nh[j] = mh2[jj]
+            cur_h = nh
+        for j, s in enumerate(seqs):
+            room = s.sampling.max_tokens - s.num_output_tokens - 1
+            s.drafts = drafts[j][:max(0, min(self.k, room))]
