@@ -1,0 +1,424 @@
+// Paged attention over the FP8 KV cache.
+//
+//   decode  : one CTA per (kv head, k-split, sequence).  The G = Hq/Hkv query heads that share the kv head are
+//             packed into the M rows of the tensor-core tile (GQA packing), the CTA's four warps take alternating
+//             16-token pages of the split's range, keep online-softmax state in registers and are merged through
+//             shared memory; splits are merged by a second tiny kernel (flash-decoding).
+//   prefill : one warp per 16 query rows of one head; loops causally over the sequence's pages.
+//
+// K pages are [block_size, D] row-major per head, V pages are stored transposed [D, block_size] (see
+// elementwise.cu).  FP8 bytes are widened to f16 in registers (cvt.f16x2.e4m3x2) and fed to
+// mma.sync.m16n8k16; the head-dim (for QK^T) and token (for PV) indices are permuted so that every thread reads
+// contiguous 16/4-byte pieces and the C fragment of QK^T is directly the A fragment of PV:
+//   * QK^T k-index: thread c = lane%4 owns dims [c*D/4, (c+1)*D/4); k-step ks uses its bytes ks*4..ks*4+3.
+//   * token <-> n-column inside a 16-token page: tile i (0/1), column j  <->  token (j/2)*4 + 2*i + j%2,
+//     so a thread's four P values of a row are tokens c*4 .. c*4+3, exactly one 32-bit word of a V^T row.
+// The FP8 K scale is folded into the query scaling, the V scale into the final normalisation (hoisted out of the
+// loop like the reference's paged_decode_attn_fp8.cu:42-48).
+//
+// Reference ops replaced: kernels/gb10/common/paged_decode_attn*.cu (SIMT), inferspark_prefill_paged_fp8.cu.
+#include "common.cuh"
+#include "host_api.h"
+
+namespace atlas {
+
+struct AttnParams {
+  const __nv_bfloat16* q; long long ldq;       // [T, Hq, D], token stride ldq
+  __nv_bfloat16* out; long long ldo;           // [T, Hq, D]
+  const uint8_t* k_cache; const uint8_t* v_cache;
+  const int* block_tables; int bt_ld;
+  const int* seq_lens; const int* query_start_loc;
+  int seq_base;                                 // index of the first sequence this launch covers
+  float qk_scale_log2;                          // softmax scale * k_scale * log2(e)
+  float v_scale;
+  int Hq, Hkv, block_size, window;
+  // decode
+  int num_splits;
+  float* part_o;                                // [B, Hq, splits, D]
+  float* part_ml;                               // [B, Hq, splits, 2]
+  // prefill
+  const int* tile_seq; const int* tile_q0; int num_tiles;
+};
+
+ATLAS_DEVICE void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+ATLAS_DEVICE uint32_t fp8x2_to_f16x2(uint16_t v) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(r) : "h"(v));
+  return r;
+}
+ATLAS_DEVICE uint32_t pack_f16x2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int D, bool PREFILL>
+__global__ void __launch_bounds__(128)
+paged_attn_kernel(const AttnParams p) {
+  constexpr int KS = D / 16;            // k-steps of QK^T
+  constexpr int NT = D / 8;             // n-tiles of PV
+  constexpr int DQ = D / 4;             // dims owned by one thread of a quad
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = lane & 3, rq = lane >> 2;
+  const int G = p.Hq / p.Hkv;
+
+  int b, kvh, q_row0, q_len, L, qhead = 0, tile_q0 = 0, split = 0;
+  if (PREFILL) {
+    const int tile = blockIdx.x * 4 + warp;
+    if (tile >= p.num_tiles) return;
+    b = p.tile_seq[tile];
+    tile_q0 = p.tile_q0[tile];
+    qhead = blockIdx.y;
+    kvh = qhead / G;
+  } else {
+    b = p.seq_base + blockIdx.z;
+    kvh = blockIdx.x;
+    split = blockIdx.y;
+  }
+  L = p.seq_lens[b];
+  q_row0 = p.query_start_loc[b];
+  q_len = p.query_start_loc[b + 1] - q_row0;
+
+  // ---- query fragments (scaled, f16)
+  uint32_t qf[KS][4];
+  {
+    const __nv_bfloat16* qrow[2] = {nullptr, nullptr};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = rq + 8 * h;
+      if (PREFILL) {
+        if (tile_q0 + r < q_len) qrow[h] = p.q + (long long)(q_row0 + tile_q0 + r) * p.ldq + qhead * D;
+      } else {
+        if (r < G) qrow[h] = p.q + (long long)q_row0 * p.ldq + (kvh * G + r) * D;
+      }
+    }
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (qrow[h]) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(qrow[h] + c * DQ + ks * 4);
+          const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+          const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+          v[0] = __low2float(lo) * p.qk_scale_log2; v[1] = __high2float(lo) * p.qk_scale_log2;
+          v[2] = __low2float(hi) * p.qk_scale_log2; v[3] = __high2float(hi) * p.qk_scale_log2;
+        }
+        qf[ks][h] = pack_f16x2(v[0], v[1]);         // a0 / a1 : k = c*2 + {0,1}
+        qf[ks][2 + h] = pack_f16x2(v[2], v[3]);     // a2 / a3 : k = c*2 + 8 + {0,1}
+      }
+    }
+  }
+
+  // ---- page range
+  const int n_pages = (L + 15) >> 4;
+  int pg_begin, pg_end, pg_step;
+  int qpos[2];                                       // absolute position of this thread's two rows (causal bound)
+  if (PREFILL) {
+    const int first_pos = L - q_len + tile_q0;
+    qpos[0] = first_pos + rq;
+    qpos[1] = first_pos + rq + 8;
+    const int last_pos = min(L - 1, first_pos + 15);
+    pg_begin = 0;
+    if (p.window > 0) pg_begin = max(0, first_pos - p.window + 1) >> 4;
+    pg_end = (last_pos >> 4) + 1;
+    pg_step = 1;
+  } else {
+    qpos[0] = qpos[1] = L - 1;
+    const int per_split = (n_pages + p.num_splits - 1) / p.num_splits;
+    int lo = split * per_split;
+    if (p.window > 0) lo = max(lo, max(0, L - p.window) >> 4);
+    pg_begin = lo + warp;
+    pg_end = min(n_pages, (split + 1) * per_split);
+    pg_step = 4;
+  }
+
+  float o[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+  const int* bt = p.block_tables + (long long)b * p.bt_ld;
+  const int bs = p.block_size;
+
+  for (int pg = pg_begin; pg < pg_end; pg += pg_step) {
+    const int tok0 = pg << 4;
+    const int blk = bt[tok0 / bs];
+    const int off = tok0 % bs;
+    const uint8_t* kpage = p.k_cache + (((long long)blk * p.Hkv + kvh) * bs + off) * D;
+    const uint8_t* vpage = p.v_cache + ((long long)blk * p.Hkv + kvh) * (long long)D * bs + off;
+
+    // ---- S = Q K^T for the 16 tokens of this page
+    float s[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+      const int tok_in_page = (rq >> 1) * 4 + 2 * i + (rq & 1);
+      const uint4* krow = reinterpret_cast<const uint4*>(kpage + tok_in_page * D + c * DQ);
+#pragma unroll
+      for (int v4 = 0; v4 < DQ / 16; ++v4) {
+        const uint4 raw = __ldg(krow + v4);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+          const uint32_t b0 = fp8x2_to_f16x2((uint16_t)(w[wi] & 0xFFFFu));
+          const uint32_t b1 = fp8x2_to_f16x2((uint16_t)(w[wi] >> 16));
+          mma_f16(s[i], qf[v4 * 4 + wi], b0, b1);
+        }
+      }
+    }
+    // ---- mask + online softmax.  s[i][j] (row rq) and s[i][2+j] (row rq+8) belong to token tok0 + c*4 + 2i + j.
+    float mx[2] = {m_run[0], m_run[1]};
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int tok = tok0 + c * 4 + 2 * i + j;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          bool ok = tok <= qpos[h] && tok < L;
+          if (p.window > 0) ok = ok && tok > qpos[h] - p.window;
+          float& sv = s[i][2 * h + j];
+          sv = ok ? sv : -INFINITY;
+          mx[h] = fmaxf(mx[h], sv);
+        }
+      }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+    }
+    float alpha[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      alpha[h] = (mx[h] == -INFINITY) ? 1.f : exp2f(m_run[h] - mx[h]);
+      m_run[h] = mx[h];
+      l_run[h] *= alpha[h];
+    }
+    uint32_t pf[4];
+    {
+      float pv[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int h = e >> 1;
+          const float x = (mx[h] == -INFINITY) ? 0.f : exp2f(s[i][e] - mx[h]);
+          pv[i][e] = x;
+          l_run[h] += x;
+        }
+      pf[0] = pack_f16x2(pv[0][0], pv[0][1]);
+      pf[1] = pack_f16x2(pv[0][2], pv[0][3]);
+      pf[2] = pack_f16x2(pv[1][0], pv[1][1]);
+      pf[3] = pack_f16x2(pv[1][2], pv[1][3]);
+    }
+    // tokens past the sequence end may hold stale bytes: zero them so 0 * garbage cannot produce NaN
+    uint32_t vmask = 0xFFFFFFFFu;
+    {
+      const int first = tok0 + c * 4;
+      if (first + 3 >= L) {
+        vmask = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (first + j < L) vmask |= 0xFFu << (8 * j);
+      }
+    }
+    // ---- O = alpha * O + P V
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      const uint32_t word = __ldg(reinterpret_cast<const uint32_t*>(vpage + (long long)(j * 8 + rq) * bs + c * 4)) & vmask;
+      const uint32_t b0 = fp8x2_to_f16x2((uint16_t)(word & 0xFFFFu));
+      const uint32_t b1 = fp8x2_to_f16x2((uint16_t)(word >> 16));
+      o[j][0] *= alpha[0]; o[j][1] *= alpha[0];
+      o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+      mma_f16(o[j], pf, b0, b1);
+    }
+  }
+  // quad-reduce the row sums
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+
+  if (PREFILL) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = rq + 8 * h;
+      if (tile_q0 + r >= q_len) continue;
+      const float inv = l_run[h] > 0.f ? p.v_scale / l_run[h] : 0.f;
+      __nv_bfloat16* orow = p.out + (long long)(q_row0 + tile_q0 + r) * p.ldo + qhead * D;
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+        *reinterpret_cast<__nv_bfloat162*>(orow + j * 8 + c * 2) =
+            __floats2bfloat162_rn(o[j][2 * h] * inv, o[j][2 * h + 1] * inv);
+    }
+    return;
+  } else {
+    // ---- merge the four warps through shared memory
+    extern __shared__ float sm[];
+    float* sm_m = sm;                    // [4][16]
+    float* sm_l = sm + 64;               // [4][16]
+    float* sm_o = sm + 128;              // [4][16][D]
+    if (c == 0) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        sm_m[warp * 16 + rq + 8 * h] = m_run[h];
+        sm_l[warp * 16 + rq + 8 * h] = l_run[h];
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = rq + 8 * h;
+      if (r < G) {
+        float* dst = sm_o + ((warp * 16 + r) * D);
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          dst[j * 8 + c * 2] = o[j][2 * h];
+          dst[j * 8 + c * 2 + 1] = o[j][2 * h + 1];
+        }
+      }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * D; idx += 128) {
+      const int r = idx / D, d = idx % D;
+      float m = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) m = fmaxf(m, sm_m[w * 16 + r]);
+      float acc = 0.f, l = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float mw = sm_m[w * 16 + r];
+        const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
+        acc += f * sm_o[(w * 16 + r) * D + d];
+        l += f * sm_l[w * 16 + r];
+      }
+      const int head = kvh * G + r;
+      if (p.num_splits == 1) {
+        const float inv = l > 0.f ? p.v_scale / l : 0.f;
+        p.out[(long long)q_row0 * p.ldo + head * D + d] = __float2bfloat16_rn(acc * inv);
+      } else {
+        const long long pi = ((long long)(b - p.seq_base) * p.Hq + head) * p.num_splits + split;
+        p.part_o[pi * D + d] = acc;
+        if (d == 0) {
+          p.part_ml[pi * 2] = m;
+          p.part_ml[pi * 2 + 1] = l;
+        }
+      }
+    }
+  }
+}
+
+// Merge split partials: grid (Hq, B), D threads.
+__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                  __nv_bfloat16* out, long long ldo, const int* query_start_loc, int seq_base, int Hq,
+                                  int D, int splits, float v_scale) {
+  const int head = blockIdx.x, bi = blockIdx.y, d = threadIdx.x;
+  const long long base = ((long long)bi * Hq + head) * splits;
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
+  float acc = 0.f, l = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = part_ml[(base + s) * 2];
+    const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
+    acc += f * part_o[(base + s) * D + d];
+    l += f * part_ml[(base + s) * 2 + 1];
+  }
+  const float inv = l > 0.f ? v_scale / l : 0.f;
+  const int row = query_start_loc[seq_base + bi];
+  out[(long long)row * ldo + head * D + d] = __float2bfloat16_rn(acc * inv);
+}
+
+template <int D>
+static int launch_decode(const AttnParams& p, int B, cudaStream_t st) {
+  const int smem = (128 + 4 * 16 * D) * sizeof(float);
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(paged_attn_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return -20;
+    attr = true;
+  }
+  dim3 grid(p.Hkv, p.num_splits, B);
+  paged_attn_kernel<D, false><<<grid, 128, smem, st>>>(p);
+  if (cudaGetLastError() != cudaSuccess) return -21;
+  if (p.num_splits > 1) {
+    dim3 g2(p.Hq, B);
+    attn_merge_kernel<<<g2, D, 0, st>>>(p.part_o, p.part_ml, p.out, p.ldo, p.query_start_loc, p.seq_base, p.Hq, D,
+                                        p.num_splits, p.v_scale);
+    if (cudaGetLastError() != cudaSuccess) return -22;
+  }
+  return 0;
+}
+
+template <int D>
+static int launch_prefill(const AttnParams& p, cudaStream_t st) {
+  dim3 grid((p.num_tiles + 3) / 4, p.Hq);
+  paged_attn_kernel<D, true><<<grid, 128, 0, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+}  // namespace atlas
+
+using namespace atlas;
+
+static int fill_common(AttnParams& p, const void* q, long long ldq, void* out, long long ldo, const void* k_cache,
+                       const void* v_cache, const int* block_tables, int bt_ld, const int* seq_lens,
+                       const int* query_start_loc, int seq_base, float scale, float k_scale, float v_scale, int Hq,
+                       int Hkv, int D, int block_size, int window) {
+  if (Hq % Hkv || Hq / Hkv > 16 || block_size % 16 || (D != 64 && D != 128 && D != 256)) return -1;
+  if (ldq % 4 || ldo % 2) return -2;
+  p.q = reinterpret_cast<const __nv_bfloat16*>(q); p.ldq = ldq;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ldo = ldo;
+  p.k_cache = reinterpret_cast<const uint8_t*>(k_cache); p.v_cache = reinterpret_cast<const uint8_t*>(v_cache);
+  p.block_tables = block_tables; p.bt_ld = bt_ld; p.seq_lens = seq_lens; p.query_start_loc = query_start_loc;
+  p.seq_base = seq_base;
+  p.qk_scale_log2 = scale * k_scale * 1.4426950408889634f;
+  p.v_scale = v_scale;
+  p.Hq = Hq; p.Hkv = Hkv; p.block_size = block_size; p.window = window;
+  p.num_splits = 1; p.part_o = nullptr; p.part_ml = nullptr; p.tile_seq = nullptr; p.tile_q0 = nullptr; p.num_tiles = 0;
+  return 0;
+}
+
+// Decode attention for sequences [seq_base, seq_base+B), one query row each.  With num_splits > 1 the caller
+// provides scratch: part_o [B*Hq*splits*D] floats and part_ml [B*Hq*splits*2] floats.
+extern "C" int atlas_attn_decode(const void* q, long long ldq, void* out, long long ldo, const void* k_cache,
+                                 const void* v_cache, const int* block_tables, int bt_ld, const int* seq_lens,
+                                 const int* query_start_loc, int seq_base, int B, float scale, float k_scale,
+                                 float v_scale, int Hq, int Hkv, int D, int block_size, int window, int num_splits,
+                                 float* part_o, float* part_ml, void* stream) {
+  if (B <= 0) return 0;
+  AttnParams p;
+  int rc = fill_common(p, q, ldq, out, ldo, k_cache, v_cache, block_tables, bt_ld, seq_lens, query_start_loc, seq_base,
+                       scale, k_scale, v_scale, Hq, Hkv, D, block_size, window);
+  if (rc) return rc;
+  p.num_splits = num_splits < 1 ? 1 : num_splits;
+  if (p.num_splits > 1 && (!part_o || !part_ml)) return -3;
+  p.part_o = part_o; p.part_ml = part_ml;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (D == 64) return launch_decode<64>(p, B, st);
+  if (D == 128) return launch_decode<128>(p, B, st);
+  return launch_decode<256>(p, B, st);
+}
+
+// Prefill / verify attention: `num_tiles` 16-row query tiles described by (sequence index, first query row of the
+// tile inside the sequence's chunk).
+extern "C" int atlas_attn_prefill(const void* q, long long ldq, void* out, long long ldo, const void* k_cache,
+                                  const void* v_cache, const int* block_tables, int bt_ld, const int* seq_lens,
+                                  const int* query_start_loc, const int* tile_seq, const int* tile_q0, int num_tiles,
+                                  float scale, float k_scale, float v_scale, int Hq, int Hkv, int D, int block_size,
+                                  int window, void* stream) {
+  if (num_tiles <= 0) return 0;
+  AttnParams p;
+  int rc = fill_common(p, q, ldq, out, ldo, k_cache, v_cache, block_tables, bt_ld, seq_lens, query_start_loc, 0, scale,
+                       k_scale, v_scale, Hq, Hkv, D, block_size, window);
+  if (rc) return rc;
+  p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.num_tiles = num_tiles;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (D == 64) return launch_prefill<64>(p, st);
+  if (D == 128) return launch_prefill<128>(p, st);
+  return launch_prefill<256>(p, st);
+}

@@ -1,0 +1,393 @@
+// Bandwidth-bound fused ops around the GEMMs (all 16-byte vectorised, one pass over the data):
+//   * residual add + RMSNorm (+ per-token 128-group FP8 quantisation feeding the block-scaled GEMM)
+//   * SiLU(gate) * up (+ FP8 group quantisation)
+//   * stand-alone per-token-group FP8 quantisation
+//   * per-head q/k RMSNorm + rotary embedding + FP8 quantisation + paged KV-cache write
+//   * gated RMSNorm of the Gated-DeltaNet output
+//
+// FP8 activation scales are written "k-group major": scale[(k/128) * scale_ld + token], so that the GEMM
+// epilogue's per-row scale reads are coalesced.
+//
+// Paged KV layout written here (and read by attention.cu):
+//   K: [num_blocks, Hkv, block_size, D]      one page of one head is a contiguous [block_size, D] tile
+//   V: [num_blocks, Hkv, D, block_size]      transposed inside the page: tokens are the contiguous axis, which is
+//                                            the K-major operand layout for P*V on the tensor cores
+// Reference ops replaced: kernels/gb10/common/{rms_norm,moe_silu_mul,per_token_group_quant_fp8,rope,
+// reshape_and_cache,fused_k_norm_rope_cache}.cu.
+#include "common.cuh"
+#include "host_api.h"
+
+namespace atlas {
+
+constexpr float kFp8Max = 448.f;
+
+struct __align__(16) bf16x8 {
+  __nv_bfloat162 v[4];
+};
+
+ATLAS_DEVICE void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  bf16x8 r = *reinterpret_cast<const bf16x8*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(r.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+ATLAS_DEVICE void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  bf16x8 r;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) r.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  *reinterpret_cast<bf16x8*>(p) = r;
+}
+// 8 floats -> 8 e4m3 bytes with a common scale (IEEE x / scale, so codes match a host restatement), packed
+ATLAS_DEVICE uint2 quant8(const float (&f)[8], float scale) {
+  uint32_t w[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint32_t acc = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc |= (uint32_t)f32_to_fp8_e4m3(__fdiv_rn(f[h * 4 + i], scale)) << (8 * i);
+    w[h] = acc;
+  }
+  return make_uint2(w[0], w[1]);
+}
+// max |x| over the 16 consecutive lanes that hold one 128-element group
+ATLAS_DEVICE float group16_absmax(float v) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+template <int kMaxIters>
+__global__ void __launch_bounds__(1024)
+rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* residual, long long ldr,
+               const __nv_bfloat16* __restrict__ w, __nv_bfloat16* res_out, long long ldro, __nv_bfloat16* y,
+               long long ldy, uint8_t* q, long long ldq, float* scale, long long scale_ld, int H, float eps,
+               int plus_one) {
+  const int t = blockIdx.x;
+  const int tid = threadIdx.x;
+  float vals[kMaxIters][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < kMaxIters; ++it) {
+    const int e = (it * blockDim.x + tid) * 8;
+    if (e < H) {
+      load8(x + t * ldx + e, vals[it]);
+      if (residual) {
+        float r[8];
+        load8(residual + t * ldr + e, r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) vals[it][i] += r[i];
+        if (res_out) {
+          store8(res_out + t * ldro + e, vals[it]);
+          // normalise what was stored (the rounded residual stream), like the unfused sequence would
+#pragma unroll
+          for (int i = 0; i < 8; ++i) vals[it][i] = __bfloat162float(__float2bfloat16_rn(vals[it][i]));
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += vals[it][i] * vals[it][i];
+    }
+  }
+  __shared__ float red[32];
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  if (tid < 32) {
+    float v = tid < (blockDim.x >> 5) ? red[tid] : 0.f;
+    v = warp_sum(v);
+    if (tid == 0) red[0] = v;
+  }
+  __syncthreads();
+  const float rstd = rsqrtf(red[0] / (float)H + eps);
+#pragma unroll
+  for (int it = 0; it < kMaxIters; ++it) {
+    const int e = (it * blockDim.x + tid) * 8;
+    const bool live = e < H;
+    float o[8];
+    float amax = 0.f;
+    if (live) {
+      float wv[8];
+      load8(w + e, wv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float ww = plus_one ? wv[i] + 1.f : wv[i];
+        o[i] = __bfloat162float(__float2bfloat16_rn(vals[it][i] * rstd * ww));   // same rounding as the bf16 output
+        amax = fmaxf(amax, fabsf(o[i]));
+      }
+    }
+    if (q) {
+      amax = group16_absmax(amax);
+      if (live) {
+        const float sc = fmaxf(amax, 1e-10f) / kFp8Max;
+        *reinterpret_cast<uint2*>(q + t * ldq + e) = quant8(o, sc);
+        if ((tid & 15) == 0) scale[(long long)(e >> 7) * scale_ld + t] = sc;
+      }
+    } else if (live) {
+      store8(y + t * ldy + e, o);
+    }
+  }
+}
+
+// gate_up [T, 2I] -> silu(gate) * up, bf16 or fp8+scale
+__global__ void __launch_bounds__(256)
+silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, long long ld, int I, __nv_bfloat16* y, long long ldy, uint8_t* q,
+                long long ldq, float* scale, long long scale_ld) {
+  const int t = blockIdx.y;
+  const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  const bool live = e < I;
+  float o[8];
+  float amax = 0.f;
+  if (live) {
+    float g[8], u[8];
+    load8(gu + t * ld + e, g);
+    load8(gu + t * ld + I + e, u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float s = g[i] / (1.f + __expf(-g[i]));
+      o[i] = __bfloat162float(__float2bfloat16_rn(s * u[i]));
+      amax = fmaxf(amax, fabsf(o[i]));
+    }
+  }
+  if (q) {
+    amax = group16_absmax(amax);
+    if (live) {
+      const float sc = fmaxf(amax, 1e-10f) / kFp8Max;
+      *reinterpret_cast<uint2*>(q + t * ldq + e) = quant8(o, sc);
+      if ((threadIdx.x & 15) == 0) scale[(long long)(e >> 7) * scale_ld + t] = sc;
+    }
+  } else if (live) {
+    store8(y + t * ldy + e, o);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int K, uint8_t* q, long long ldq, float* scale,
+                 long long scale_ld) {
+  const int t = blockIdx.y;
+  const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  const bool live = e < K;
+  float o[8];
+  float amax = 0.f;
+  if (live) {
+    load8(x + t * ld + e, o);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(o[i]));
+  }
+  amax = group16_absmax(amax);
+  if (live) {
+    const float sc = fmaxf(amax, 1e-10f) / kFp8Max;
+    *reinterpret_cast<uint2*>(q + t * ldq + e) = quant8(o, sc);
+    if ((threadIdx.x & 15) == 0) scale[(long long)(e >> 7) * scale_ld + t] = sc;
+  }
+}
+
+// One warp per (token, head): heads [0,Hq) are q (norm + rope, in place), [Hq,Hq+Hkv) are k (norm + rope + cache
+// write), [Hq+Hkv, Hq+2Hkv) are v (cache write).  D <= 512, D % 64 == 0.
+struct RopeKvParams {
+  __nv_bfloat16* q; long long ldq;
+  const __nv_bfloat16* k; long long ldk;
+  const __nv_bfloat16* v; long long ldv;
+  const int* positions;
+  const float* rope;      // [max_pos, rotary_dim]: cos half then sin half
+  const __nv_bfloat16* q_norm_w;
+  const __nv_bfloat16* k_norm_w;
+  void* k_cache; void* v_cache;
+  const int* slot_mapping;
+  int T, Hq, Hkv, D, rotary_dim, block_size, kv_fp8, plus_one;
+  float eps, inv_k_scale, inv_v_scale;
+};
+
+__global__ void __launch_bounds__(128)
+rope_kv_write_kernel(const RopeKvParams p) {
+  extern __shared__ float sm_rope[];          // [4 warps][D]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * 4 + warp;
+  const int heads = p.Hq + 2 * p.Hkv;
+  if (unit >= (long long)p.T * heads) return;
+  const int t = (int)(unit / heads);
+  const int h = (int)(unit % heads);
+  float* buf = sm_rope + warp * p.D;
+  const int D = p.D;
+  const bool is_q = h < p.Hq;
+  const bool is_k = !is_q && h < p.Hq + p.Hkv;
+  const int hh = is_q ? h : (is_k ? h - p.Hq : h - p.Hq - p.Hkv);
+  const __nv_bfloat16* src = is_q ? p.q + t * p.ldq + hh * D : (is_k ? p.k + t * p.ldk + hh * D : p.v + t * p.ldv + hh * D);
+  const int slot = p.slot_mapping[t];
+  if (!is_q && slot < 0) return;
+  float ss = 0.f;
+  for (int e = lane * 2; e < D; e += 64) {
+    float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + e));
+    buf[e] = f.x;
+    buf[e + 1] = f.y;
+    ss += f.x * f.x + f.y * f.y;
+  }
+  const __nv_bfloat16* nw = is_q ? p.q_norm_w : (is_k ? p.k_norm_w : nullptr);
+  if (nw) {
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)D + p.eps);
+    for (int e = lane * 2; e < D; e += 64) {
+      float2 wv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(nw + e));
+      if (p.plus_one) { wv.x += 1.f; wv.y += 1.f; }
+      // round like the unfused op chain would (norm output is bf16)
+      buf[e] = __bfloat162float(__float2bfloat16_rn(buf[e] * rstd * wv.x));
+      buf[e + 1] = __bfloat162float(__float2bfloat16_rn(buf[e + 1] * rstd * wv.y));
+    }
+  }
+  __syncwarp();
+  const int half = p.rotary_dim >> 1;
+  const float* cs = p.rope + (long long)p.positions[t] * p.rotary_dim;
+  long long kbase = 0, vbase = 0;
+  int tok_in_blk = 0;
+  if (!is_q) {
+    const int blk = slot / p.block_size;
+    tok_in_blk = slot % p.block_size;
+    kbase = (((long long)blk * p.Hkv + hh) * p.block_size + tok_in_blk) * D;          // K: [blk][head][tok][d]
+    vbase = ((long long)blk * p.Hkv + hh) * (long long)D * p.block_size + tok_in_blk;  // V: [blk][head][d][tok]
+  }
+  for (int e = lane * 2; e < D; e += 64) {
+    float o[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int d = e + i;
+      float val = buf[d];
+      if (!(!is_q && !is_k) && d < p.rotary_dim) {
+        if (d < half) val = buf[d] * cs[d] - buf[d + half] * cs[half + d];
+        else          val = buf[d] * cs[d - half] + buf[d - half] * cs[d];
+      }
+      o[i] = val;
+    }
+    if (is_q) {
+      *reinterpret_cast<__nv_bfloat162*>(p.q + t * p.ldq + hh * D + e) = __floats2bfloat162_rn(o[0], o[1]);
+    } else if (is_k) {
+      if (p.kv_fp8) {
+        uint16_t pk = (uint16_t)f32_to_fp8_e4m3(o[0] * p.inv_k_scale) | ((uint16_t)f32_to_fp8_e4m3(o[1] * p.inv_k_scale) << 8);
+        *reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(p.k_cache) + kbase + e) = pk;
+      } else {
+        *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(p.k_cache) + kbase + e) =
+            __floats2bfloat162_rn(o[0], o[1]);
+      }
+    } else {
+      if (p.kv_fp8) {
+        uint8_t* vc = reinterpret_cast<uint8_t*>(p.v_cache) + vbase;
+        vc[(long long)e * p.block_size] = f32_to_fp8_e4m3(o[0] * p.inv_v_scale);
+        vc[(long long)(e + 1) * p.block_size] = f32_to_fp8_e4m3(o[1] * p.inv_v_scale);
+      } else {
+        __nv_bfloat16* vc = reinterpret_cast<__nv_bfloat16*>(p.v_cache) + vbase;
+        vc[(long long)e * p.block_size] = __float2bfloat16_rn(o[0]);
+        vc[(long long)(e + 1) * p.block_size] = __float2bfloat16_rn(o[1]);
+      }
+    }
+  }
+}
+
+// y = rmsnorm(x) * w * silu(z), one warp per (token, head); x,z [T, H, D] with token strides
+__global__ void __launch_bounds__(128)
+gated_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ z,
+                     long long ldz, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* y, long long ldy, int T, int H,
+                     int D, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * 4 + warp;
+  if (unit >= (long long)T * H) return;
+  const int t = (int)(unit / H), h = (int)(unit % H);
+  const __nv_bfloat16* xr = x + t * ldx + h * D;
+  const __nv_bfloat16* zr = z + t * ldz + h * D;
+  float ss = 0.f;
+  for (int e = lane * 2; e < D; e += 64) {
+    float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xr + e));
+    ss += f.x * f.x + f.y * f.y;
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / (float)D + eps);
+  for (int e = lane * 2; e < D; e += 64) {
+    float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xr + e));
+    float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(zr + e));
+    float2 wv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + e));
+    const float a = f.x * rstd * wv.x * (g.x / (1.f + __expf(-g.x)));
+    const float b = f.y * rstd * wv.y * (g.y / (1.f + __expf(-g.y)));
+    *reinterpret_cast<__nv_bfloat162*>(y + t * ldy + h * D + e) = __floats2bfloat162_rn(a, b);
+  }
+}
+
+}  // namespace atlas
+
+using namespace atlas;
+
+extern "C" int atlas_rmsnorm(const void* x, long long ldx, const void* residual, long long ldr, const void* w,
+                             void* res_out, long long ldro, void* y, long long ldy, void* q, long long ldq,
+                             float* scale, long long scale_ld, int T, int H, float eps, int plus_one, void* stream) {
+  if (T <= 0) return 0;
+  if (H % 8 || (q && H % 128)) return -1;
+  int threads = ((H / 8 + 31) / 32) * 32;
+  int iters = 1;
+  while (threads > 1024) { iters *= 2; threads = (((H / 8 + iters - 1) / iters + 31) / 32) * 32; }
+  if (q && threads % 16) return -2;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  auto X = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto R = reinterpret_cast<const __nv_bfloat16*>(residual);
+  auto W = reinterpret_cast<const __nv_bfloat16*>(w);
+  auto RO = reinterpret_cast<__nv_bfloat16*>(res_out);
+  auto Y = reinterpret_cast<__nv_bfloat16*>(y);
+  auto Qp = reinterpret_cast<uint8_t*>(q);
+  if (iters == 1) rmsnorm_kernel<1><<<T, threads, 0, st>>>(X, ldx, R, ldr, W, RO, ldro, Y, ldy, Qp, ldq, scale, scale_ld, H, eps, plus_one);
+  else if (iters == 2) rmsnorm_kernel<2><<<T, threads, 0, st>>>(X, ldx, R, ldr, W, RO, ldro, Y, ldy, Qp, ldq, scale, scale_ld, H, eps, plus_one);
+  else if (iters == 4) rmsnorm_kernel<4><<<T, threads, 0, st>>>(X, ldx, R, ldr, W, RO, ldro, Y, ldy, Qp, ldq, scale, scale_ld, H, eps, plus_one);
+  else return -3;
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+extern "C" int atlas_silu_mul(const void* gu, long long ld, int T, int I, void* y, long long ldy, void* q,
+                              long long ldq, float* scale, long long scale_ld, void* stream) {
+  if (T <= 0) return 0;
+  if (I % 8 || (q && I % 128)) return -1;
+  dim3 grid((I / 8 + 255) / 256, T);
+  silu_mul_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(gu), ld, I, reinterpret_cast<__nv_bfloat16*>(y), ldy,
+      reinterpret_cast<uint8_t*>(q), ldq, scale, scale_ld);
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+extern "C" int atlas_quant_fp8(const void* x, long long ld, int T, int K, void* q, long long ldq, float* scale,
+                               long long scale_ld, void* stream) {
+  if (T <= 0) return 0;
+  if (K % 128) return -1;
+  dim3 grid((K / 8 + 255) / 256, T);
+  quant_fp8_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), ld, K, reinterpret_cast<uint8_t*>(q), ldq, scale, scale_ld);
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+extern "C" int atlas_rope_kv_write(void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv,
+                                   const int* positions, const float* rope, const void* q_norm_w,
+                                   const void* k_norm_w, void* k_cache, void* v_cache, const int* slot_mapping, int T,
+                                   int Hq, int Hkv, int D, int rotary_dim, int block_size, int kv_fp8, int plus_one,
+                                   float eps, float k_scale, float v_scale, void* stream) {
+  if (T <= 0) return 0;
+  if (D % 64 || D > 512 || rotary_dim > D || rotary_dim % 2) return -1;
+  RopeKvParams p;
+  p.q = reinterpret_cast<__nv_bfloat16*>(q); p.ldq = ldq;
+  p.k = reinterpret_cast<const __nv_bfloat16*>(k); p.ldk = ldk;
+  p.v = reinterpret_cast<const __nv_bfloat16*>(v); p.ldv = ldv;
+  p.positions = positions; p.rope = rope;
+  p.q_norm_w = reinterpret_cast<const __nv_bfloat16*>(q_norm_w);
+  p.k_norm_w = reinterpret_cast<const __nv_bfloat16*>(k_norm_w);
+  p.k_cache = k_cache; p.v_cache = v_cache; p.slot_mapping = slot_mapping;
+  p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.rotary_dim = rotary_dim; p.block_size = block_size;
+  p.kv_fp8 = kv_fp8; p.plus_one = plus_one; p.eps = eps; p.inv_k_scale = 1.f / k_scale; p.inv_v_scale = 1.f / v_scale;
+  const long long units = (long long)T * (Hq + 2 * Hkv);
+  const int grid = (int)((units + 3) / 4);
+  rope_kv_write_kernel<<<grid, 128, 4 * D * sizeof(float), reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+extern "C" int atlas_gated_rmsnorm(const void* x, long long ldx, const void* z, long long ldz, const void* w, void* y,
+                                   long long ldy, int T, int H, int D, float eps, void* stream) {
+  if (T <= 0) return 0;
+  if (D % 64) return -1;
+  const long long units = (long long)T * H;
+  gated_rmsnorm_kernel<<<(int)((units + 3) / 4), 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), ldx, reinterpret_cast<const __nv_bfloat16*>(z), ldz,
+      reinterpret_cast<const __nv_bfloat16*>(w), reinterpret_cast<__nv_bfloat16*>(y), ldy, T, H, D, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}

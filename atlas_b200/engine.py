@@ -66,6 +66,8 @@ class LLMEngine:
         self.spec = SpecController(self, self.cfg) if (self.cfg.speculative and model.mtp is not None
                                                          and self.cfg.num_drafts > 0) else None
         self.stats = EngineStats()
+        self.time_device = False          # accumulate CUDA-event time of each step's GPU work
+        self.device_time_ms = 0.0
         self._seqs: Dict[str, Sequence] = {}
         self._ids = itertools.count()
         self._stop_checkers: Dict[str, Callable[[Sequence], bool]] = {}
@@ -75,8 +77,8 @@ class LLMEngine:
         want = self.cfg.kv_cache_dtype
         if want == "auto":
             want = self.mcfg.quant.kv_cache_dtype
-        if want == "fp8":
-            return torch.float8_e4m3fn
+        if want == "fp8" or (want == "auto" and self.model.device.type == "cuda"):
+            return torch.float8_e4m3fn      # the GPU attention kernels are FP8-KV only
         if want == "bf16":
             return torch.bfloat16
         return self.model.dtype
@@ -162,6 +164,10 @@ class LLMEngine:
             self.runner.copy_state(self.snapshot_base + snap_slot, seq_slot)
         use_spec = self.spec is not None and self.spec.active()
         batch = self.runner.build_batch(out, self.snapshot_base)
+        ev = None
+        if self.time_device and self.model.device.type == "cuda":
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            ev[0].record()
         hidden = self.runner.forward(batch)
         # rows that need logits
         rows, row_owner = [], []
@@ -186,6 +192,10 @@ class LLMEngine:
                 sampled.setdefault(i, []).append(so.tokens[j])
                 if so.logprobs is not None and so.logprobs[j] is not None:
                     lps.setdefault(i, []).append(so.logprobs[j])
+        if ev is not None:
+            ev[1].record()
+            ev[1].synchronize()
+            self.device_time_ms += ev[0].elapsed_time(ev[1])
         now = time.monotonic()
         accepted_rows: List[int] = []
         qsl = 0

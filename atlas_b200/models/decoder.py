@@ -25,6 +25,15 @@ _DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torc
            "torch.float32": torch.float32, "torch.bfloat16": torch.bfloat16, "torch.float16": torch.float16}
 
 
+def alloc_kv(num_blocks: int, block_size: int, hkv: int, d: int, dtype, device):
+    """Paged K and V pools as logical ``[num_blocks, block_size, Hkv, D]`` tensors (the GPU pools are views
+    of the kernels' physical layout)."""
+    if torch.device(device).type == "cuda":
+        return ops.cuda_ops().alloc_kv_cache(num_blocks, block_size, hkv, d, dtype, device)
+    shape = (num_blocks, block_size, hkv, d)
+    return torch.zeros(shape, dtype=dtype, device=device), torch.zeros(shape, dtype=dtype, device=device)
+
+
 def torch_dtype(name: str) -> torch.dtype:
     return _DTYPES.get(str(name), torch.bfloat16)
 
@@ -161,9 +170,7 @@ class DecoderLM:
         store = CacheStore(block_size=block_size, num_blocks=num_blocks)
         for l in self.layers:
             if l.kind == "attention":
-                shape = (num_blocks, block_size, l.mixer.hkv, self.cfg.head_dim)
-                store.kv[l.idx] = (torch.zeros(shape, dtype=kv_dtype, device=self.device),
-                                   torch.zeros(shape, dtype=kv_dtype, device=self.device))
+                store.kv[l.idx] = alloc_kv(num_blocks, block_size, l.mixer.hkv, self.cfg.head_dim, kv_dtype, self.device)
                 store.kv_scales[l.idx] = (1.0, 1.0)
             else:
                 store.states[l.idx] = l.mixer.alloc_state(max(1, state_slots), self.device, self.dtype)

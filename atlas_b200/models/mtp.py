@@ -41,9 +41,8 @@ class MTPHead:
         self.layer.init_random(gen, std, dtype, device)
 
     def alloc_cache(self, store, num_blocks, block_size, kv_dtype, device) -> None:
-        shape = (num_blocks, block_size, self.layer.mixer.hkv, self.cfg.head_dim)
-        store.kv[self.layer_idx] = (torch.zeros(shape, dtype=kv_dtype, device=device),
-                                    torch.zeros(shape, dtype=kv_dtype, device=device))
+        from .decoder import alloc_kv
+        store.kv[self.layer_idx] = alloc_kv(num_blocks, block_size, self.layer.mixer.hkv, self.cfg.head_dim, kv_dtype, device)
         store.kv_scales[self.layer_idx] = (1.0, 1.0)
 
     @torch.inference_mode()

@@ -1,0 +1,382 @@
+"""ctypes binding of the sm_100a kernel library (``atlas_b200/_C/libatlas_b200_kernels.so``).
+
+Every wrapper here launches hand-written kernels on the current CUDA stream; nothing falls back to eager
+PyTorch.  A missing library raises at load time.  ``launch_count`` counts kernel-launching calls so that
+benchmarks can report how many of this library's kernels ran inside a timed region.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Dict, Optional, Tuple
+
+import torch
+
+_LIB = None
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(os.path.dirname(_HERE), "_C", "libatlas_b200_kernels.so")
+
+launch_count = 0
+_status_ptr: Dict[int, int] = {}
+_num_sms: Dict[int, int] = {}
+_scratch: Dict[Tuple[int, str], torch.Tensor] = {}
+
+FP8 = torch.float8_e4m3fn
+_vp, _ll, _i, _f = C.c_void_p, C.c_longlong, C.c_int, C.c_float
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def load() -> None:
+    global _LIB
+    if _LIB is not None:
+        return
+    if not os.path.exists(LIB_PATH):
+        raise KernelError(f"{LIB_PATH} is missing: run `python -m atlas_b200.build` (the GPU path has no eager fallback)")
+    lib = C.CDLL(LIB_PATH)
+    lib.atlas_status_ptr.restype = C.c_void_p
+    lib.atlas_read_status.restype = C.c_ulonglong
+    lib.atlas_gemm.argtypes = [_i, _vp, _vp, _vp, _vp, _ll, _ll, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _vp, _i, _vp, _vp]
+    lib.atlas_rmsnorm.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _ll, _i, _i, _f, _i, _vp]
+    lib.atlas_silu_mul.argtypes = [_vp, _ll, _i, _i, _vp, _ll, _vp, _ll, _vp, _ll, _vp]
+    lib.atlas_quant_fp8.argtypes = [_vp, _ll, _i, _i, _vp, _ll, _vp, _ll, _vp]
+    lib.atlas_rope_kv_write.argtypes = [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
+                                        _i, _i, _i, _i, _f, _f, _f, _vp]
+    lib.atlas_gated_rmsnorm.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _ll, _i, _i, _i, _f, _vp]
+    lib.atlas_attn_decode.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _f, _f, _f, _i, _i, _i,
+                                      _i, _i, _i, _vp, _vp, _vp]
+    lib.atlas_attn_prefill.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _f, _f, _f, _i,
+                                       _i, _i, _i, _i, _vp]
+    lib.atlas_argmax.argtypes = [_vp, _ll, _i, _i, _i, _vp, _vp]
+    lib.atlas_sample.argtypes = [_vp, _ll, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]
+    lib.atlas_spec_accept.argtypes = [_vp, _vp, _i, _i, _vp, _vp]
+    _LIB = lib
+    _bind_optional(lib)
+
+
+def _bind_optional(lib) -> None:
+    """Entry points of translation units that may be added later (MoE, GDN, comm)."""
+    from . import cuda_ext
+    cuda_ext.bind(lib)
+
+
+def lib():
+    load()
+    return _LIB
+
+
+def _dev(t: torch.Tensor) -> int:
+    d = t.device.index
+    d = torch.cuda.current_device() if d is None else d
+    if d not in _status_ptr:
+        rc = lib().atlas_init(d)
+        if rc != 0:
+            raise KernelError(f"atlas_init({d}) failed: {rc}")
+        _status_ptr[d] = lib().atlas_status_ptr(d)
+        _num_sms[d] = lib().atlas_num_sms(d)
+    return d
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(rc: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
+    if rc != 0:
+        raise KernelError(f"{what} failed with code {rc}")
+
+
+def check_status(device: Optional[int] = None, clear: bool = True) -> int:
+    """Synchronise and read the device status word (0 = no bounded wait ever gave up)."""
+    d = torch.cuda.current_device() if device is None else device
+    if d not in _status_ptr:
+        return 0
+    return int(lib().atlas_read_status(d, 1 if clear else 0))
+
+
+def scratch(name: str, nbytes: int, device) -> torch.Tensor:
+    """Per-device persistent scratch (grown on demand, never shrunk): stable addresses for CUDA graphs."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), name)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _scale_buf(T: int, kb: int, device) -> torch.Tensor:
+    """Activation scales, k-group major: logical ``[T, kb]`` with strides ``(1, T)``."""
+    return torch.empty(kb, T, dtype=torch.float32, device=device).t()
+
+
+# ----------------------------------------------------------------------------- elementwise
+def quant_fp8(x: torch.Tensor, group: int = 128):
+    assert group == 128 and x.dim() == 2 and x.dtype == torch.bfloat16 and x.stride(1) == 1
+    T, K = x.shape
+    _dev(x)
+    q = torch.empty(T, K, dtype=FP8, device=x.device)
+    s = _scale_buf(T, K // 128, x.device)
+    _check(lib().atlas_quant_fp8(x.data_ptr(), x.stride(0), T, K, q.data_ptr(), K, s.data_ptr(), s.stride(1), _stream()),
+           "quant_fp8")
+    return q, s
+
+
+def rmsnorm(x, w, eps, residual=None, plus_one=False, quant=False):
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+    T, H = x.shape
+    _dev(x)
+    res_out = torch.empty(T, H, dtype=x.dtype, device=x.device) if residual is not None else None
+    y = q = s = None
+    if quant:
+        q = torch.empty(T, H, dtype=FP8, device=x.device)
+        s = _scale_buf(T, H // 128, x.device)
+    else:
+        y = torch.empty(T, H, dtype=x.dtype, device=x.device)
+    _check(lib().atlas_rmsnorm(x.data_ptr(), x.stride(0), _ptr(residual), residual.stride(0) if residual is not None else 0,
+                               w.data_ptr(), _ptr(res_out), H, _ptr(y), H, _ptr(q), H, _ptr(s), s.stride(1) if s is not None else 0,
+                               T, H, float(eps), 1 if plus_one else 0, _stream()), "rmsnorm")
+    if quant:
+        return q, s, res_out
+    return y, res_out
+
+
+def silu_mul(gate_up: torch.Tensor, quant=False):
+    assert gate_up.dtype == torch.bfloat16 and gate_up.stride(1) == 1
+    T, I2 = gate_up.shape
+    I = I2 // 2
+    _dev(gate_up)
+    if quant:
+        q = torch.empty(T, I, dtype=FP8, device=gate_up.device)
+        s = _scale_buf(T, I // 128, gate_up.device)
+        _check(lib().atlas_silu_mul(gate_up.data_ptr(), gate_up.stride(0), T, I, None, 0, q.data_ptr(), I, s.data_ptr(),
+                                    s.stride(1), _stream()), "silu_mul")
+        return q, s
+    y = torch.empty(T, I, dtype=gate_up.dtype, device=gate_up.device)
+    _check(lib().atlas_silu_mul(gate_up.data_ptr(), gate_up.stride(0), T, I, y.data_ptr(), I, None, 0, None, 0, _stream()),
+           "silu_mul")
+    return y
+
+
+def gated_rmsnorm(x, z, w, eps):
+    T, H, D = x.shape
+    _dev(x)
+    assert x.stride(2) == 1 and z.stride(2) == 1 and x.stride(1) == D and z.stride(1) == D
+    y = torch.empty(T, H, D, dtype=x.dtype, device=x.device)
+    _check(lib().atlas_gated_rmsnorm(x.data_ptr(), x.stride(0), z.data_ptr(), z.stride(0), w.data_ptr(), y.data_ptr(),
+                                     H * D, T, H, D, float(eps), _stream()), "gated_rmsnorm")
+    return y
+
+
+# ----------------------------------------------------------------------------- GEMM
+_GEMM_WS_BYTES = 64 << 20
+_FORCE_BLOCK_N = int(os.environ.get("ATLAS_GEMM_BLOCK_N", "0"))
+_FORCE_SPLITS = int(os.environ.get("ATLAS_GEMM_SPLITS", "0"))
+
+
+def gemm_plan(M: int, N: int, K: int, kind: int, sms: int) -> Tuple[int, int]:
+    """(block_n, k-splits) for a problem: fill the SMs first with tiles, then with K splits."""
+    k_blocks = (K + (128 if kind == 1 else 64) - 1) // (128 if kind == 1 else 64)
+    m_tiles = (M + 127) // 128
+    if _FORCE_BLOCK_N:
+        bn = _FORCE_BLOCK_N
+    elif m_tiles * ((N + 255) // 256) >= 2 * sms and N % 256 == 0:
+        bn = 256
+    elif m_tiles * ((N + 127) // 128) >= sms:
+        bn = 128
+    else:
+        bn = 64 if N >= 64 * 8 else 64
+    tiles = m_tiles * ((N + bn - 1) // bn)
+    splits = 1
+    if _FORCE_SPLITS:
+        splits = _FORCE_SPLITS
+    elif tiles * 2 <= sms and k_blocks >= 8:
+        splits = max(1, min(sms // tiles, k_blocks // 4, 16))
+    while splits > 1 and splits * M * N * 4 > _GEMM_WS_BYTES:
+        splits -= 1
+    return bn, splits
+
+
+def _gemm(kind: int, a: torch.Tensor, b: torch.Tensor, a_scale, b_scale, out: Optional[torch.Tensor]) -> torch.Tensor:
+    M, K = a.shape
+    N = b.shape[0]
+    d = _dev(a)
+    assert a.stride(1) == 1 and b.stride(1) == 1 and b.shape[1] == K
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    assert out.stride(1) == 1 and out.dtype == torch.bfloat16
+    sms = _num_sms[d]
+    bn, splits = gemm_plan(M, N, K, kind, sms)
+    ws = cnt = None
+    if splits > 1:
+        ws = scratch("gemm_ws", _GEMM_WS_BYTES, a.device)
+        cnt = scratch("gemm_counters", 1 << 18, a.device)
+    sa_m = sa_k = 0
+    if kind == 1:
+        sa_m, sa_k = a_scale.stride(0), a_scale.stride(1)
+        assert b_scale.is_contiguous() and b_scale.dtype == torch.float32 and a_scale.dtype == torch.float32
+    _check(lib().atlas_gemm(kind, a.data_ptr(), b.data_ptr(), out.data_ptr(), _ptr(a_scale), sa_m, sa_k, _ptr(b_scale),
+                            b_scale.shape[1] if b_scale is not None else 0, M, N, K, a.stride(0), b.stride(0),
+                            out.stride(0), bn, splits, _ptr(ws), _ptr(cnt), sms, _status_ptr[d], _stream()), "gemm")
+    return out
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out=None) -> torch.Tensor:
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    if x.stride(1) != 1 or (x.stride(0) * 2) % 16 or x.data_ptr() % 16:
+        x = x.contiguous()
+    return _gemm(0, x, w, None, None, out)
+
+
+def gemm_fp8_block(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor, out=None) -> torch.Tensor:
+    assert xq.dtype == FP8 and wq.dtype == FP8
+    return _gemm(1, xq, wq, xs, ws, out)
+
+
+def gemm_nvfp4(x, packed, bscale, gscale, out=None):
+    from . import cuda_ext
+    return cuda_ext.gemm_nvfp4(x, packed, bscale, gscale, out)
+
+
+# ----------------------------------------------------------------------------- KV cache + attention
+def alloc_kv_cache(num_blocks: int, block_size: int, hkv: int, d: int, dtype, device):
+    """Physical layout K ``[nb, Hkv, bs, D]``, V ``[nb, Hkv, D, bs]``; both returned as logical
+    ``[nb, bs, Hkv, D]`` views so indexing code is layout-agnostic."""
+    k = torch.zeros(num_blocks, hkv, block_size, d, dtype=dtype, device=device).permute(0, 2, 1, 3)
+    v = torch.zeros(num_blocks, hkv, d, block_size, dtype=dtype, device=device).permute(0, 3, 1, 2)
+    return k, v
+
+
+def _kv_layout_ok(k_cache: torch.Tensor, v_cache: torch.Tensor) -> None:
+    nb, bs, hkv, d = k_cache.shape
+    if k_cache.stride() != (hkv * bs * d, d, bs * d, 1) or v_cache.stride() != (hkv * bs * d, 1, d * bs, bs):
+        raise KernelError("KV cache is not in the kernel layout (allocate it with ops.cuda.alloc_kv_cache)")
+    if k_cache.dtype != FP8:
+        raise KernelError("the GPU attention kernels read an FP8 (e4m3) KV cache")
+
+
+def qk_norm_rope_kv_write(q, k, v, positions, rope_cache, rotary_dim, k_cache, v_cache, slot_mapping, k_scale, v_scale,
+                          q_norm_w, k_norm_w, eps, norm_plus_one):
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    _dev(q)
+    _kv_layout_ok(k_cache, v_cache)
+    assert q.stride(2) == 1 and q.stride(1) == D and k.stride(1) == D and v.stride(1) == D
+    assert positions.dtype == torch.int32 and slot_mapping.dtype == torch.int32 and rope_cache.dtype == torch.float32
+    bs = k_cache.shape[1]
+    _check(lib().atlas_rope_kv_write(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+                                     positions.data_ptr(), rope_cache.data_ptr(), _ptr(q_norm_w), _ptr(k_norm_w),
+                                     k_cache.data_ptr(), v_cache.data_ptr(), slot_mapping.data_ptr(), T, Hq, Hkv, D,
+                                     rotary_dim, bs, 1, 1 if norm_plus_one else 0, float(eps), float(k_scale),
+                                     float(v_scale), _stream()), "rope_kv_write")
+    return q
+
+
+def decode_splits(B: int, hkv: int, max_seq_len: int, sms: int) -> int:
+    ctas = B * hkv
+    if ctas >= 2 * sms:
+        return 1
+    pages = (max_seq_len + 15) // 16
+    return int(max(1, min((2 * sms + ctas - 1) // ctas, (pages + 7) // 8, 64)))
+
+
+def paged_attention(q, k_cache, v_cache, batch, scale, k_scale, v_scale, sliding_window):
+    T, Hq, D = q.shape
+    nb, bs, Hkv, _ = k_cache.shape
+    d = _dev(q)
+    _kv_layout_ok(k_cache, v_cache)
+    out = torch.empty(T, Hq, D, dtype=q.dtype, device=q.device)
+    bt = batch.block_tables
+    window = int(sliding_window or 0)
+    nd = batch.num_decodes
+    st = _stream()
+    if nd > 0:
+        splits = decode_splits(nd, Hkv, batch.max_seq_len, _num_sms[d])
+        po = pml = None
+        if splits > 1:
+            po = scratch("attn_part_o", nd * Hq * splits * D * 4, q.device)
+            pml = scratch("attn_part_ml", nd * Hq * splits * 2 * 4, q.device)
+        _check(lib().atlas_attn_decode(q.data_ptr(), q.stride(0), out.data_ptr(), Hq * D, k_cache.data_ptr(),
+                                       v_cache.data_ptr(), bt.data_ptr(), bt.stride(0), batch.seq_lens.data_ptr(),
+                                       batch.query_start_loc.data_ptr(), 0, nd, float(scale), float(k_scale),
+                                       float(v_scale), Hq, Hkv, D, bs, window, splits, _ptr(po), _ptr(pml), st),
+               "attn_decode")
+    if batch.num_seqs > nd:
+        tiles = getattr(batch, "_attn_tiles", None)
+        if tiles is None:
+            ts, tq = [], []
+            for i in range(nd, batch.num_seqs):
+                for q0 in range(0, batch.query_lens_host[i], 16):
+                    ts.append(i)
+                    tq.append(q0)
+            host = torch.tensor([ts, tq], dtype=torch.int32).pin_memory()
+            tiles = (host.to(q.device, non_blocking=True), len(ts))
+            batch._attn_tiles = tiles
+        tdev, n_tiles = tiles
+        _check(lib().atlas_attn_prefill(q.data_ptr(), q.stride(0), out.data_ptr(), Hq * D, k_cache.data_ptr(),
+                                        v_cache.data_ptr(), bt.data_ptr(), bt.stride(0), batch.seq_lens.data_ptr(),
+                                        batch.query_start_loc.data_ptr(), tdev[0].data_ptr(), tdev[1].data_ptr(),
+                                        n_tiles, float(scale), float(k_scale), float(v_scale), Hq, Hkv, D, bs, window,
+                                        st), "attn_prefill")
+    return out
+
+
+# ----------------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    B, V = logits.shape
+    _dev(logits)
+    assert logits.stride(1) == 1 and logits.dtype in (torch.bfloat16, torch.float32)
+    out = torch.empty(B, dtype=torch.int64, device=logits.device)
+    _check(lib().atlas_argmax(logits.data_ptr(), logits.stride(0), B, V, 1 if logits.dtype == torch.bfloat16 else 0,
+                              out.data_ptr(), _stream()), "argmax")
+    return out
+
+
+def sample(logits, temperature, top_k, top_p, min_p, uniform):
+    B, V = logits.shape
+    _dev(logits)
+    if logits.dtype not in (torch.bfloat16, torch.float32):
+        logits = logits.float()
+    out = torch.empty(B, dtype=torch.int64, device=logits.device)
+    _check(lib().atlas_sample(logits.data_ptr(), logits.stride(0), B, V, 1 if logits.dtype == torch.bfloat16 else 0,
+                              temperature.float().contiguous().data_ptr(), top_k.to(torch.int32).contiguous().data_ptr(),
+                              top_p.float().contiguous().data_ptr(), min_p.float().contiguous().data_ptr(),
+                              uniform.float().contiguous().data_ptr(), out.data_ptr(), _stream()), "sample")
+    return out
+
+
+def spec_accept(draft: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
+    B, K = draft.shape
+    _dev(draft)
+    out = torch.empty(B, dtype=torch.int32, device=draft.device)
+    _check(lib().atlas_spec_accept(draft.contiguous().data_ptr(), target.contiguous().data_ptr(), B, K, out.data_ptr(),
+                                   _stream()), "spec_accept")
+    return out
+
+
+# ----------------------------------------------------------------------------- MoE / GDN (cuda_ext)
+def moe_route(logits, top_k, norm_topk, scoring):
+    from . import cuda_ext
+    return cuda_ext.moe_route(logits, top_k, norm_topk, scoring)
+
+
+def moe_forward(x, topk_w, topk_ids, experts, e_lo, pctx, ep_mode):
+    from . import cuda_ext
+    return cuda_ext.moe_forward(x, topk_w, topk_ids, experts, e_lo, pctx, ep_mode)
+
+
+def gdn_forward(layer, mixed, a, b, batch, state, commit):
+    from . import cuda_ext
+    return cuda_ext.gdn_forward(layer, mixed, a, b, batch, state, commit)
+
+
+def gdn_commit(layer, mixed, a, b, qlens, slots, has_state, state, num_accepted_rows):
+    from . import cuda_ext
+    return cuda_ext.gdn_commit(layer, mixed, a, b, qlens, slots, has_state, state, num_accepted_rows)

@@ -142,14 +142,13 @@ def qk_norm_rope_kv_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos
     nb, bs, hkv, d = k_cache.shape
     valid = slot_mapping >= 0
     slots = slot_mapping[valid].long()
-    kc = k_cache.view(nb * bs, hkv, d)
-    vc = v_cache.view(nb * bs, hkv, d)
+    blk, off = slots // bs, slots % bs          # index the logical dims: the cache may be a permuted view
     if k_cache.dtype == FP8:
-        kc[slots] = (k[valid].float() / k_scale).clamp(-FP8_MAX, FP8_MAX).to(FP8)
-        vc[slots] = (v[valid].float() / v_scale).clamp(-FP8_MAX, FP8_MAX).to(FP8)
+        k_cache[blk, off] = (k[valid].float() / k_scale).clamp(-FP8_MAX, FP8_MAX).to(FP8)
+        v_cache[blk, off] = (v[valid].float() / v_scale).clamp(-FP8_MAX, FP8_MAX).to(FP8)
     else:
-        kc[slots] = k[valid].to(k_cache.dtype)
-        vc[slots] = v[valid].to(v_cache.dtype)
+        k_cache[blk, off] = k[valid].to(k_cache.dtype)
+        v_cache[blk, off] = v[valid].to(v_cache.dtype)
     return q
 
 

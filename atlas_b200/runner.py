@@ -123,6 +123,11 @@ class ModelRunner:
             return self._forward_graph(batch)
         return self.model.forward(batch, self.cache)
 
+    def kernels_per_graph(self) -> int:
+        """Kernel launches inside one captured decode step (what one replay stands for)."""
+        ks = [g.num_kernels for g in self.graphs.values() if g.num_kernels]
+        return int(sum(ks) / len(ks)) if ks else 0
+
     def logits(self, hidden: torch.Tensor, rows: List[int]) -> torch.Tensor:
         if len(rows) == hidden.shape[0] and rows == list(range(len(rows))):
             return self.model.compute_logits(hidden)
@@ -160,6 +165,7 @@ class _DecodeGraph:
         self.qsl = torch.arange(padded + 1, dtype=torch.int32, device=dev)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.out: Optional[torch.Tensor] = None
+        self.num_kernels = 0
 
     def _batch(self, max_seq_len: int) -> ForwardBatch:
         return ForwardBatch(input_ids=self.ids, positions=self.pos, slot_mapping=self.slots, block_tables=self.tables,
@@ -192,8 +198,11 @@ class _DecodeGraph:
                     r.model.forward(fb, r.cache)
             torch.cuda.current_stream().wait_stream(s)
             self.graph = torch.cuda.CUDAGraph()
+            from .ops import cuda as K
+            n0 = K.launch_count
             with torch.cuda.graph(self.graph):
                 self.out = r.model.forward(fb, r.cache)
+            self.num_kernels = K.launch_count - n0
             self._load(b)
         self.graph.replay()
         r.graph_replays += 1

@@ -1,0 +1,193 @@
+#!/usr/bin/env python
+"""Headline benchmark: aggregate output tokens/s of a wave of concurrent requests (the reference's
+concurrency-sweep metric) on a Llama-3-8B-shaped FP8 block-scaled decoder with an FP8 KV cache.
+
+One *step* is one full wave: ``--concurrency`` requests of ``--isl`` random input tokens each generate
+``--osl`` tokens (EOS ignored) through ``LLMEngine`` (continuous batching, chunked prefill, paged KV).
+``--gpus N`` runs tensor-parallel over N GPUs (launch with torchrun for N > 1).
+
+Prints one JSON line.  ``value`` is output tokens / CUDA-event time of the steps' GPU work;
+``e2e.value`` is output tokens / wall time of the same waves through the public API, including every step's
+pinned-host -> device input copies and the device -> host read of the sampled tokens.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+BASELINE_TOK_S = None   # the reference publishes no number for this config on any hardware
+
+
+def _clock_sampler(gpu_index: int):
+    q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    try:
+        return subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                 "-i", str(gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+    except Exception:
+        return None
+
+
+def _clock_summary(proc):
+    if proc is None:
+        return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+    proc.terminate()
+    try:
+        out, _ = proc.communicate(timeout=5)
+    except Exception:
+        proc.kill()
+        out = ""
+    sm, mx, reasons = [], [], set()
+    names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    for line in out.splitlines():
+        f = [x.strip() for x in line.split(",")]
+        if len(f) < 9:
+            continue
+        try:
+            sm.append(float(f[1]))
+            mx.append(float(f[2]))
+        except ValueError:
+            continue
+        for n, v in zip(names, f[5:9]):
+            if v.lower().startswith("active"):
+                reasons.add(n)
+    if not sm:
+        return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+    busy = sorted(sm)[len(sm) // 4:]       # drop the idle tail of samples
+    return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="atlas_b200", choices=["atlas_b200", "reference"])
+    ap.add_argument("--model", default="llama3-8b")
+    ap.add_argument("--concurrency", type=int, default=128)
+    ap.add_argument("--isl", type=int, default=1024)
+    ap.add_argument("--osl", type=int, default=256)
+    ap.add_argument("--block-size", type=int, default=16)
+    ap.add_argument("--max-prefill-tokens", type=int, default=8192)
+    ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (marks the result invalid)")
+    ap.add_argument("--no-graphs", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "refused by a safety check: pip install of /root/reference was denied; the reference is a Rust "
+                          "workspace (no setup.py/pyproject.toml, needs cargo which the image lacks)"}))
+        return 0
+
+    import torch
+    from atlas_b200.config import PRESETS, EngineConfig
+    from atlas_b200.engine import LLMEngine
+    from atlas_b200.models import build_model
+    from atlas_b200.parallel import init_distributed
+    from atlas_b200.sampling import SamplingParams
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if args.gpus > 1:
+            print(f"bench.py: --gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})", file=sys.stderr)
+            return 2
+    topo, pctx, device = init_distributed(tp_size=world)
+    rank = topo.rank
+    from atlas_b200.ops import cuda as K
+
+    mcfg = PRESETS[args.model]()
+    if args.layers:
+        mcfg.num_hidden_layers = args.layers
+    max_len = args.isl + args.osl + 16
+    mcfg.max_position_embeddings = max(4096, max_len)
+    model = build_model(mcfg, pctx, device=device).init_random(0, max_pos=max_len + 16)
+    blocks_per_seq = (max_len + args.block_size - 1) // args.block_size + 1
+    ecfg = EngineConfig(max_seq_len=max_len, block_size=args.block_size, max_num_seqs=max(args.concurrency, 1),
+                        max_batch_size=max(args.concurrency, 1), max_prefill_tokens=args.max_prefill_tokens,
+                        num_kv_blocks=blocks_per_seq * args.concurrency + 64, enable_prefix_caching=False,
+                        use_cuda_graphs=not args.no_graphs, tp_size=world)
+    eng = LLMEngine(model, ecfg)
+    eng.time_device = True
+    sp = SamplingParams(max_tokens=args.osl, temperature=0.0, ignore_eos=True)
+    gen = torch.Generator().manual_seed(1234)
+
+    def wave():
+        prompts = [torch.randint(0, mcfg.vocab_size, (args.isl,), generator=gen).tolist() for _ in range(args.concurrency)]
+        outs = eng.generate(prompts, sp)
+        return sum(len(o.output_tokens) for o in outs), [o.ttft_s for o in outs]
+
+    def sync_all():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        wave()
+    sync_all()
+    st = K.check_status()
+    if st:
+        print(f"bench.py: device status word {st:#x} after warm-up", file=sys.stderr)
+        return 3
+    sampler = _clock_sampler(torch.cuda.current_device()) if rank == 0 else None
+    eng.device_time_ms = 0.0
+    launches0, replays0 = K.launch_count, eng.runner.graph_replays
+    h2d0 = eng.runner.h2d_bytes
+    steps0 = eng.stats.steps
+    sync_all()
+    t0 = time.perf_counter()
+    tokens = 0
+    ttfts = []
+    for _ in range(args.steps):
+        n, tt = wave()
+        tokens += n
+        ttfts += [t for t in tt if t is not None]
+    sync_all()
+    wall = time.perf_counter() - t0
+    clocks = _clock_summary(sampler) if rank == 0 else None
+    dev_s = eng.device_time_ms / 1e3
+    t = torch.tensor([wall, dev_s], dtype=torch.float64, device=device)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    wall, dev_s = float(t[0]), float(t[1])
+    eng_steps = eng.stats.steps - steps0
+    launches = (K.launch_count - launches0) + (eng.runner.graph_replays - replays0) * eng.runner.kernels_per_graph()
+    if rank == 0:
+        value = tokens / dev_s if dev_s > 0 else 0.0
+        e2e = tokens / wall
+        line = {
+            "metric": "aggregate output tok/s (concurrency wave, ISL/OSL)", "value": round(value, 2), "unit": "tok/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(wall * 1e3 / args.steps, 3), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": (value / BASELINE_TOK_S) if BASELINE_TOK_S else None, "dtype": "fp8-e4m3 weights (128x128 scales) + fp8 KV, bf16 activations",
+            "data": "synthetic: uniform-random token ids, random-init N(0,0.02) weights quantized to fp8 block-scaled",
+            "config": {"model": args.model + ("" if not args.layers else f"-TRUNCATED-{args.layers}L-INVALID"),
+                       "global_batch": args.concurrency, "seq_len": args.isl + args.osl, "isl": args.isl, "osl": args.osl,
+                       "parallelism": f"tp{world}", "l2": "inputs larger than L2 (8 GB weights + KV stream every step)",
+                       "step": "one wave of `global_batch` concurrent requests, prefill + decode",
+                       "engine_steps_per_wave": eng_steps / max(1, args.steps), "cuda_graphs": not args.no_graphs},
+            "clocks": clocks,
+            "e2e": {"value": round(e2e, 2), "unit": "tok/s",
+                    "h2d_bytes_per_step": int((eng.runner.h2d_bytes - h2d0) / max(1, eng_steps)),
+                    "d2h_bytes_per_step": int(8 * tokens / max(1, eng_steps)),
+                    "note": "per engine step; every step copies token ids / positions / slots / block tables from pinned host memory and reads the sampled token ids back"},
+            "gpu_launches": int(launches),
+            "ttft_p50_ms": round(statistics.median(ttfts) * 1e3, 2) if ttfts else None,
+            "tpot_ms": round((wall / args.steps) * 1e3 / args.osl, 3),
+            "impl": "atlas_b200",
+        }
+        print(json.dumps(line))
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
