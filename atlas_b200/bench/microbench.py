@@ -1,0 +1,242 @@
+"""Kernel micro-benchmarks with roofline fractions.
+
+``python -m atlas_b200.bench.microbench [--model llama3-8b] [--out FILE]`` times every hot kernel on the
+shapes the named model produces (decode batch and prefill chunk), with CUDA events on the launching
+stream, three warm-up runs, an L2 flush (a 256 MiB write) between timed runs, and prints achieved GB/s /
+TFLOP/s and the fraction of the measured peaks (``MEASURED_PEAKS.json`` next to the repository root when
+present, else the documented fallback figures).
+
+Reference counterpart: the kernel micro-benchmark table of ``book/src/operations/benchmarks.md:67-102``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+from typing import Callable, Dict, List, Optional
+
+import torch
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def load_peaks() -> Dict[str, float]:
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    d = dict(FALLBACK_PEAKS)
+    d["source"] = "fallback"
+    return d
+
+
+class Timer:
+    def __init__(self, device="cuda", use_graph: bool = True):
+        self.use_graph = use_graph
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    def time(self, fn: Callable[[], None], iters: int = 7, warmup: int = 3) -> float:
+        """Median milliseconds of ``fn`` with a cold L2.  ``fn`` is captured into a CUDA graph first so that
+        host-side launch cost (Python, descriptor lookup, allocator) is not part of the number."""
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        if self.use_graph:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            fn = g.replay
+            fn()
+            torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            self.flush.fill_(1)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            s.record()
+            fn()
+            e.record()
+            e.synchronize()
+            ts.append(s.elapsed_time(e))
+        return statistics.median(ts)
+
+
+def run(model: str = "llama3-8b", decode_batch: int = 128, ctx: int = 1152, chunk: int = 8192,
+        only: Optional[str] = None) -> List[dict]:
+    from atlas_b200 import quant as Q
+    from atlas_b200.config import PRESETS
+    from atlas_b200.models.batch import ForwardBatch
+    from atlas_b200.ops import cuda as K
+    from atlas_b200.ops import reference as ref
+    K.load()
+    cfg = PRESETS[model]()
+    peaks = load_peaks()
+    dev = "cuda"
+    T = Timer(dev)
+    rows: List[dict] = []
+
+    def add(name, ms, bytes_=0, flops=0, note=""):
+        r = {"kernel": name, "ms": round(ms, 4), "note": note}
+        if bytes_:
+            gbs = bytes_ / ms / 1e6
+            r["GB/s"] = round(gbs, 1)
+            r["frac_hbm"] = round(gbs / peaks["hbm_gbs"], 3)
+        if flops:
+            tf = flops / ms / 1e9
+            r["TFLOP/s"] = round(tf, 1)
+            r["frac_bf16_peak"] = round(tf / peaks["bf16_tflops"], 3)
+        rows.append(r)
+        print(json.dumps(r), flush=True)
+
+    H, I = cfg.hidden_size, cfg.intermediate_size
+    qkv_n = cfg.q_size + 2 * cfg.kv_size
+    gemms = [("qkv", qkv_n, H), ("o", H, cfg.q_size), ("gate_up", 2 * I, H), ("down", H, I)]
+    if not only or "gemm" in only:
+        for M in (decode_batch, chunk):
+            x = torch.randn(M, max(H, I), device=dev).bfloat16()
+            for name, N, Kd in gemms:
+                w = torch.randn(N, Kd, device=dev) * 0.02
+                wq, ws = Q.quantize_fp8_block(w)
+                del w
+                xq, xs = K.quant_fp8(x[:, :Kd].contiguous())
+                out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+                ms = T.time(lambda: K.gemm_fp8_block(xq, xs, wq, ws, out=out))
+                bn, sp = K.gemm_plan(M, N, Kd, 1, 148)
+                add(f"gemm_fp8 {name} M={M} N={N} K={Kd}", ms, bytes_=N * Kd + M * Kd + 2 * M * N, flops=2 * M * N * Kd,
+                    note=f"block_n={bn} splits={sp}")
+                del wq, ws
+        # lm_head bf16
+        M = decode_batch
+        w = (torch.randn(cfg.vocab_size, H, device=dev) * 0.02).bfloat16()
+        x = torch.randn(M, H, device=dev).bfloat16()
+        out = torch.empty(M, cfg.vocab_size, dtype=torch.bfloat16, device=dev)
+        ms = T.time(lambda: K.gemm_bf16(x, w, out=out))
+        add(f"gemm_bf16 lm_head M={M} N={cfg.vocab_size} K={H}", ms, bytes_=2 * cfg.vocab_size * H + 2 * M * cfg.vocab_size,
+            flops=2 * M * cfg.vocab_size * H)
+        M = 4096
+        x = torch.randn(M, H, device=dev).bfloat16()
+        w2 = w[:8192]
+        out = torch.empty(M, 8192, dtype=torch.bfloat16, device=dev)
+        ms = T.time(lambda: K.gemm_bf16(x, w2, out=out))
+        add(f"gemm_bf16 M={M} N=8192 K={H}", ms, flops=2 * M * 8192 * H, bytes_=2 * (M * H + 8192 * H + M * 8192))
+        del w, w2
+
+    if only and only.startswith("one:"):
+        # one FP8 GEMM shape, few launches, no graph: the case to put under a profiler.  only = "one:<name>:<M>"
+        _, name, m_s = only.split(":")
+        M = int(m_s)
+        N, Kd = {n: (a, b) for n, a, b in gemms}[name]
+        x = torch.randn(M, Kd, device=dev).bfloat16()
+        wq, ws = Q.quantize_fp8_block(torch.randn(N, Kd, device=dev) * 0.02)
+        xq, xs = K.quant_fp8(x)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        T.use_graph = False
+        ms = T.time(lambda: K.gemm_fp8_block(xq, xs, wq, ws, out=out), iters=3, warmup=2)
+        bn, sp = K.gemm_plan(M, N, Kd, 1, 148)
+        add(f"gemm_fp8 {name} M={M} N={N} K={Kd}", ms, bytes_=N * Kd + M * Kd + 2 * M * N, flops=2 * M * N * Kd,
+            note=f"block_n={bn} splits={sp} (eager launch)")
+        return rows
+
+    if only and "sweep" in only:
+        # tile / split-K sweep for the decode-size FP8 GEMMs
+        for M in (decode_batch,):
+            x = torch.randn(M, max(H, I), device=dev).bfloat16()
+            for name, N, Kd in gemms:
+                w = torch.randn(N, Kd, device=dev) * 0.02
+                wq, ws = Q.quantize_fp8_block(w)
+                del w
+                xq, xs = K.quant_fp8(x[:, :Kd].contiguous())
+                out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+                for bn in (64, 128):
+                    for sp in (1, 2, 4, 8):
+                        K._FORCE_BLOCK_N, K._FORCE_SPLITS = bn, sp
+                        ms = T.time(lambda: K.gemm_fp8_block(xq, xs, wq, ws, out=out), iters=5)
+                        add(f"sweep gemm_fp8 {name} M={M} N={N} K={Kd} bn={bn} splits={sp}", ms,
+                            bytes_=N * Kd + M * Kd + 2 * M * N)
+                K._FORCE_BLOCK_N = K._FORCE_SPLITS = 0
+                del wq, ws
+
+    if not only or "elt" in only:
+        for M in (decode_batch, chunk):
+            x = torch.randn(M, H, device=dev).bfloat16()
+            r = torch.randn(M, H, device=dev).bfloat16()
+            wn = torch.ones(H, device=dev).bfloat16()
+            ms = T.time(lambda: K.rmsnorm(x, wn, 1e-5, r, False, quant=True))
+            add(f"residual_rmsnorm_quant T={M} H={H}", ms, bytes_=M * H * (2 + 2 + 2 + 1))
+            gu = torch.randn(M, 2 * I, device=dev).bfloat16()
+            ms = T.time(lambda: K.silu_mul(gu, quant=True))
+            add(f"silu_mul_quant T={M} I={I}", ms, bytes_=M * I * (4 + 1))
+
+    if not only or "attn" in only:
+        bs = 16
+        Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        B = decode_batch
+        nblk = (ctx + bs - 1) // bs
+        nb = B * nblk + 8
+        kc, vc = K.alloc_kv_cache(nb, bs, Hkv, D, torch.float8_e4m3fn, dev)
+        kc.copy_((torch.randn(nb, bs, Hkv, D, device=dev) * 0.5).to(torch.float8_e4m3fn))
+        vc.copy_((torch.randn(nb, bs, Hkv, D, device=dev) * 0.5).to(torch.float8_e4m3fn))
+        perm = torch.randperm(nb - 8).tolist()
+        tables = [perm[i * nblk:(i + 1) * nblk] for i in range(B)]
+        fb = ForwardBatch.build([[0]] * B, [ctx - 1] * B, tables, bs, device=dev)
+        q = (torch.randn(B, Hq, D, device=dev) * 0.5).bfloat16()
+        ms = T.time(lambda: K.paged_attention(q, kc, vc, fb, D ** -0.5, 1.0, 1.0, None))
+        add(f"attn_decode B={B} ctx={ctx} Hq={Hq} Hkv={Hkv} D={D}", ms, bytes_=2 * B * ctx * Hkv * D,
+            flops=4 * B * ctx * Hq * D)
+        # rope + kv write at decode
+        qkv = torch.randn(B, (Hq + 2 * Hkv) * D, device=dev).bfloat16()
+        rope = ref.build_rope_cache(D, 4096, 5e5, None, dev)
+        qv = qkv[:, :Hq * D].view(B, Hq, D)
+        kv_ = qkv[:, Hq * D:(Hq + Hkv) * D].view(B, Hkv, D)
+        vv = qkv[:, (Hq + Hkv) * D:].view(B, Hkv, D)
+        ms = T.time(lambda: K.qk_norm_rope_kv_write(qv, kv_, vv, fb.positions, rope, D, kc, vc, fb.slot_mapping, 1.0, 1.0,
+                                                    None, None, 1e-6, False))
+        add(f"rope_kv_write T={B}", ms, bytes_=B * (Hq + 2 * Hkv) * D * 2 * 2)
+        # prefill: chunk tokens as sequences of 1024
+        n_seq = max(1, chunk // 1024)
+        L = 1024
+        nblk = L // bs
+        tables = [perm[i * nblk:(i + 1) * nblk] for i in range(n_seq)]
+        fbp = ForwardBatch.build([[0] * L] * n_seq, [0] * n_seq, tables, bs, device=dev)
+        qp = (torch.randn(n_seq * L, Hq, D, device=dev) * 0.5).bfloat16()
+        ms = T.time(lambda: K.paged_attention(qp, kc, vc, fbp, D ** -0.5, 1.0, 1.0, None), iters=5)
+        add(f"attn_prefill seqs={n_seq} len={L} Hq={Hq} Hkv={Hkv} D={D}", ms, flops=4 * n_seq * Hq * D * L * L // 2)
+        qkvp = torch.randn(n_seq * L, (Hq + 2 * Hkv) * D, device=dev).bfloat16()
+        qv = qkvp[:, :Hq * D].view(-1, Hq, D)
+        kv_ = qkvp[:, Hq * D:(Hq + Hkv) * D].view(-1, Hkv, D)
+        vv = qkvp[:, (Hq + Hkv) * D:].view(-1, Hkv, D)
+        ms = T.time(lambda: K.qk_norm_rope_kv_write(qv, kv_, vv, fbp.positions, rope, D, kc, vc, fbp.slot_mapping, 1.0, 1.0,
+                                                    None, None, 1e-6, False))
+        add(f"rope_kv_write T={n_seq * L}", ms, bytes_=n_seq * L * (Hq + 2 * Hkv) * D * 2 * 2)
+
+    if not only or "sample" in only:
+        lg = torch.randn(decode_batch, cfg.vocab_size, device=dev).bfloat16()
+        ms = T.time(lambda: K.argmax(lg))
+        add(f"argmax B={decode_batch} V={cfg.vocab_size}", ms, bytes_=2 * decode_batch * cfg.vocab_size)
+    st = K.check_status()
+    if st:
+        print(f"device status word {st:#x}", file=sys.stderr)
+    return rows
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="llama3-8b")
+    ap.add_argument("--batch", type=int, default=128)
+    ap.add_argument("--ctx", type=int, default=1152)
+    ap.add_argument("--chunk", type=int, default=8192)
+    ap.add_argument("--only", default=None)
+    ap.add_argument("--out", default=None)
+    a = ap.parse_args()
+    rows = run(a.model, a.batch, a.ctx, a.chunk, a.only)
+    if a.out:
+        with open(a.out, "w") as f:
+            json.dump({"peaks": load_peaks(), "rows": rows}, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()

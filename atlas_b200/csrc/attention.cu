@@ -313,6 +313,268 @@ paged_attn_kernel(const AttnParams p) {
   }
 }
 
+// ----------------------------------------------------------------------------- decode (bulk-copy pipeline)
+// One CTA per (kv head, k-split, sequence): warp 4 streams whole KV blocks of that head (K block and V^T block are
+// each one contiguous region) into a shared-memory ring with cp.async.bulk + mbarriers; warps 0..3 take the
+// blocks round-robin and keep online-softmax state in registers.
+//
+// The tensor-core tiles are oriented with TOKENS on the M dimension and the (up to 8) query heads that share the
+// kv head on N:   S^T[16 tok x 8 heads] = K[16 x D] * Q^T[D x 8],   O^T[D x 8 heads] += V^T[D x 16 tok] * P^T[16 x 8].
+// K and V^T are the A operands (FP8 bytes widened pairwise to f16), Q^T lives in registers as B fragments, and
+// P^T is obtained from the S^T accumulator with two movmatrix transposes.  Token <-> row mapping inside a
+// 16-token page: row r <-> token (r%8/2)*4 + 2*(r/8) + r%2, which makes every thread's fragment bytes contiguous.
+constexpr int kDecodeThreads = 160;
+constexpr int kBtSmemEntries = 1024;
+
+ATLAS_DEVICE void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+// four e4m3 bytes -> two f16x2 registers (bytes 0,1 and bytes 2,3)
+ATLAS_DEVICE void fp8x4_to_f16x2x2(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, l;\n\tcvt.rn.f16x2.e4m3x2 %1, h;\n\t}\n"
+      : "=r"(lo), "=r"(hi)
+      : "r"(w));
+}
+ATLAS_DEVICE uint32_t movmatrix_trans(uint32_t v) {
+  uint32_t r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(r) : "r"(v));
+  return r;
+}
+
+template <int D, int BS>       // BS: block size known at compile time (0 = runtime)
+__global__ void __launch_bounds__(kDecodeThreads)
+attn_decode_kernel(const AttnParams p, int stages, status_t* status) {
+  constexpr int KS = D / 16, MT = D / 16, DQ = D / 4;
+  extern __shared__ __align__(128) uint8_t dsm[];
+  const int bs = BS ? BS : p.block_size;
+  const int stage_bytes = 2 * bs * D;
+  uint64_t* full = reinterpret_cast<uint64_t*>(dsm);
+  uint64_t* empty = full + stages;
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(empty + stages);
+  int* bt_sm = reinterpret_cast<int*>(dsm + 512);
+  uint8_t* ring = dsm + 512 + kBtSmemEntries * 4;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = lane & 3, rq = lane >> 2;
+  const int G = p.Hq / p.Hkv;
+  const int b = p.seq_base + blockIdx.z, kvh = blockIdx.x, split = blockIdx.y;
+  const int L = p.seq_lens[b];
+  const int q_row0 = p.query_start_loc[b];
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  const int n_blocks = (L + bs - 1) / bs;
+  const int per_split = (n_blocks + p.num_splits - 1) / p.num_splits;
+  int blk_lo = split * per_split;
+  const int blk_hi = min(n_blocks, (split + 1) * per_split);
+  if (p.window > 0) blk_lo = max(blk_lo, max(0, L - p.window) / bs);
+  const int n_mine = max(0, blk_hi - blk_lo);
+  const int* bt = p.block_tables + (long long)b * p.bt_ld + blk_lo;
+  for (int i = threadIdx.x; i < min(n_mine, kBtSmemEntries); i += kDecodeThreads) bt_sm[i] = bt[i];
+  __syncthreads();
+
+  // per-thread state: heads c*2, c*2+1 (n columns), dims mt*16 + rq (+8)
+  float o[MT][4];
+#pragma unroll
+  for (int j = 0; j < MT; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+
+  if (warp == 4) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int i = 0; i < n_mine && ok; ++i) {
+        const int st = i % stages;
+        if (!mbar_wait(&empty[st], ((i / stages) & 1) ^ 1u, abort_flag, status, 0x400)) { ok = false; break; }
+        const int blk = i < kBtSmemEntries ? bt_sm[i] : bt[i];
+        const long long off = ((long long)blk * p.Hkv + kvh) * (long long)bs * D;
+        uint8_t* dst = ring + (size_t)st * stage_bytes;
+        mbar_expect_tx(&full[st], stage_bytes);
+        bulk_g2s(dst, p.k_cache + off, bs * D, &full[st]);
+        bulk_g2s(dst + bs * D, p.v_cache + off, bs * D, &full[st]);
+      }
+      if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+  } else {
+    // ---- Q^T as B fragments: b0 = (k = c*2+{0,1}, n = rq) , b1 = (k = c*2+8+{0,1}, n = rq); n = head in group.
+    // dim permutation: MMA k index kk of k-step ks <-> dim c'*DQ + ks*4 + ..., matching the K bytes a thread reads.
+    uint32_t qb[KS][2];
+    {
+      const __nv_bfloat16* qrow = rq < G ? p.q + (long long)q_row0 * p.ldq + (kvh * G + rq) * D : nullptr;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (qrow) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(qrow + c * DQ + ks * 4);
+          const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+          const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+          v[0] = __low2float(lo) * p.qk_scale_log2; v[1] = __high2float(lo) * p.qk_scale_log2;
+          v[2] = __low2float(hi) * p.qk_scale_log2; v[3] = __high2float(hi) * p.qk_scale_log2;
+        }
+        qb[ks][0] = pack_f16x2(v[0], v[1]);
+        qb[ks][1] = pack_f16x2(v[2], v[3]);
+      }
+    }
+    const int win_lo = p.window > 0 ? L - 1 - p.window : -1;  // tokens <= win_lo are outside the window
+    // this thread's two token rows inside a page
+    const int tok_r0 = (rq >> 1) * 4 + (rq & 1);
+    const int tok_r1 = tok_r0 + 2;
+    bool ok = true;
+    for (int i = warp; i < n_mine && ok; i += 4) {
+      const int st = i % stages;
+      if (!mbar_wait(&full[st], (i / stages) & 1u, abort_flag, status, 0x401)) { ok = false; break; }
+      const uint8_t* kblk = ring + (size_t)st * stage_bytes;
+      const uint8_t* vblk = kblk + bs * D;
+      const int blk_tok0 = (blk_lo + i) * bs;
+#pragma unroll 1
+      for (int sub = 0; sub * 16 < bs; ++sub) {
+        const int tok0 = blk_tok0 + sub * 16;
+        if (tok0 >= L) break;
+        // ---- S^T = K Q^T : rows = tokens (tok_r0 -> row rq, tok_r1 -> row rq+8), cols = heads
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint4* k0 = reinterpret_cast<const uint4*>(kblk + (sub * 16 + tok_r0) * D + c * DQ);
+        const uint4* k1 = reinterpret_cast<const uint4*>(kblk + (sub * 16 + tok_r1) * D + c * DQ);
+#pragma unroll
+        for (int v4 = 0; v4 < DQ / 16; ++v4) {
+          const uint4 ra = k0[v4], rb = k1[v4];
+          const uint32_t wa[4] = {ra.x, ra.y, ra.z, ra.w};
+          const uint32_t wb[4] = {rb.x, rb.y, rb.z, rb.w};
+#pragma unroll
+          for (int wi = 0; wi < 4; ++wi) {
+            uint32_t a[4];
+            fp8x4_to_f16x2x2(wa[wi], a[0], a[2]);      // row rq   : k lo / k hi
+            fp8x4_to_f16x2x2(wb[wi], a[1], a[3]);      // row rq+8
+            mma_f16(s, a, qb[v4 * 4 + wi][0], qb[v4 * 4 + wi][1]);
+          }
+        }
+        // ---- mask (token validity is per row), online softmax per head column
+        const bool in0 = (tok0 + tok_r0) < L && (tok0 + tok_r0) > win_lo;
+        const bool in1 = (tok0 + tok_r1) < L && (tok0 + tok_r1) > win_lo;
+        s[0] = in0 ? s[0] : -INFINITY; s[1] = in0 ? s[1] : -INFINITY;
+        s[2] = in1 ? s[2] : -INFINITY; s[3] = in1 ? s[3] : -INFINITY;
+        float mx[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 4));
+          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 8));
+          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 16));
+          mx[h] = fmaxf(mx[h], m_run[h]);
+        }
+        float alpha[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          alpha[h] = (mx[h] == -INFINITY) ? 1.f : exp2f(m_run[h] - mx[h]);
+          m_run[h] = mx[h];
+        }
+        float pv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int h = e & 1;
+          pv[e] = (mx[h] == -INFINITY) ? 0.f : exp2f(s[e] - mx[h]);
+        }
+        l_run[0] = l_run[0] * alpha[0] + pv[0] + pv[2];
+        l_run[1] = l_run[1] * alpha[1] + pv[1] + pv[3];
+        // P^T as the B operand of the PV product: transpose the two 8x8 (token x head) blocks
+        const uint32_t pb0 = movmatrix_trans(pack_f16x2(pv[0], pv[1]));
+        const uint32_t pb1 = movmatrix_trans(pack_f16x2(pv[2], pv[3]));
+        // after the transpose this thread holds head rq, tokens c*4+{0,1} (pb0) and c*4+{2,3} (pb1)
+        uint32_t vmask = 0xFFFFFFFFu;
+        {
+          const int first = tok0 + c * 4;
+          if (first + 3 >= L) {
+            vmask = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (first + j < L) vmask |= 0xFFu << (8 * j);
+          }
+        }
+        // rescale only when some head's running max moved (the accumulator's columns are heads c*2, c*2+1)
+        const bool rescale = __any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f);
+        // ---- O^T += V^T P^T : rows = dims, k = tokens
+        const uint8_t* vsub = vblk + sub * 16 + c * 4;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(vsub + (mt * 16 + rq) * bs) & vmask;
+          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(vsub + (mt * 16 + rq + 8) * bs) & vmask;
+          uint32_t a[4];
+          fp8x4_to_f16x2x2(w0, a[0], a[2]);
+          fp8x4_to_f16x2x2(w1, a[1], a[3]);
+          if (rescale) {
+            o[mt][0] *= alpha[0]; o[mt][1] *= alpha[1];
+            o[mt][2] *= alpha[0]; o[mt][3] *= alpha[1];
+          }
+          mma_f16(o[mt], a, pb0, pb1);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[st]);
+    }
+    // column (head) sums live split across the 8 row-lanes
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 4);
+      l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 8);
+      l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 16);
+    }
+  }
+
+  // ---- merge the four consumer warps (the ring is dead now; reuse it)
+  __syncthreads();
+  float* sm_m = reinterpret_cast<float*>(ring);          // [4][8]
+  float* sm_l = sm_m + 32;                               // [4][8]
+  float* sm_o = sm_m + 64;                               // [4][8][D]
+  if (warp < 4) {
+    if (rq == 0) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        sm_m[warp * 8 + c * 2 + h] = m_run[h];
+        sm_l[warp * 8 + c * 2 + h] = l_run[h];
+      }
+    }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int head = c * 2 + (e & 1);
+        const int dim = mt * 16 + rq + 8 * (e >> 1);
+        if (head < G) sm_o[(warp * 8 + head) * D + dim] = o[mt][e];
+      }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += kDecodeThreads) {
+    const int r = idx / D, d = idx % D;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, sm_m[w * 8 + r]);
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = sm_m[w * 8 + r];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
+      acc += f * sm_o[(w * 8 + r) * D + d];
+      l += f * sm_l[w * 8 + r];
+    }
+    const int head = kvh * G + r;
+    if (p.num_splits == 1) {
+      const float inv = l > 0.f ? p.v_scale / l : 0.f;
+      p.out[(long long)q_row0 * p.ldo + head * D + d] = __float2bfloat16_rn(acc * inv);
+    } else {
+      const long long pi = ((long long)(b - p.seq_base) * p.Hq + head) * p.num_splits + split;
+      p.part_o[pi * D + d] = acc;
+      if (d == 0) {
+        p.part_ml[pi * 2] = m;
+        p.part_ml[pi * 2 + 1] = l;
+      }
+    }
+  }
+}
+
 // Merge split partials: grid (Hq, B), D threads.
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   __nv_bfloat16* out, long long ldo, const int* query_start_loc, int seq_base, int Hq,
@@ -333,17 +595,23 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
   out[(long long)row * ldo + head * D + d] = __float2bfloat16_rn(acc * inv);
 }
 
-template <int D>
-static int launch_decode(const AttnParams& p, int B, cudaStream_t st) {
-  const int smem = (128 + 4 * 16 * D) * sizeof(float);
-  static bool attr = false;
-  if (!attr) {
-    if (cudaFuncSetAttribute(paged_attn_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+template <int D, int BS>
+static int launch_decode_bs(const AttnParams& p, int B, status_t* status, cudaStream_t st) {
+  const int stage_bytes = 2 * p.block_size * D;
+  int stages = (32 * 1024) / stage_bytes;
+  stages = stages > 16 ? 16 : (stages < 4 ? 4 : stages);
+  stages = (stages / 4) * 4;                       // block i -> stage i % stages -> warp i % 4
+  const int merge_bytes = (64 + 4 * 8 * D) * (int)sizeof(float);
+  const int ring_bytes = stages * stage_bytes > merge_bytes ? stages * stage_bytes : merge_bytes;
+  const int smem = 512 + kBtSmemEntries * 4 + ring_bytes;
+  static int attr_smem = 0;
+  if (smem > attr_smem) {
+    if (cudaFuncSetAttribute(attn_decode_kernel<D, BS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return -20;
-    attr = true;
+    attr_smem = smem;
   }
   dim3 grid(p.Hkv, p.num_splits, B);
-  paged_attn_kernel<D, false><<<grid, 128, smem, st>>>(p);
+  attn_decode_kernel<D, BS><<<grid, kDecodeThreads, smem, st>>>(p, stages, status);
   if (cudaGetLastError() != cudaSuccess) return -21;
   if (p.num_splits > 1) {
     dim3 g2(p.Hq, B);
@@ -352,6 +620,11 @@ static int launch_decode(const AttnParams& p, int B, cudaStream_t st) {
     if (cudaGetLastError() != cudaSuccess) return -22;
   }
   return 0;
+}
+template <int D>
+static int launch_decode(const AttnParams& p, int B, status_t* status, cudaStream_t st) {
+  if (p.block_size == 16) return launch_decode_bs<D, 16>(p, B, status, st);
+  return launch_decode_bs<D, 0>(p, B, status, st);
 }
 
 template <int D>
@@ -369,7 +642,7 @@ static int fill_common(AttnParams& p, const void* q, long long ldq, void* out, l
                        const void* v_cache, const int* block_tables, int bt_ld, const int* seq_lens,
                        const int* query_start_loc, int seq_base, float scale, float k_scale, float v_scale, int Hq,
                        int Hkv, int D, int block_size, int window) {
-  if (Hq % Hkv || Hq / Hkv > 16 || block_size % 16 || (D != 64 && D != 128 && D != 256)) return -1;
+  if (Hq % Hkv || block_size % 16 || (D != 64 && D != 128 && D != 256)) return -1;
   if (ldq % 4 || ldo % 2) return -2;
   p.q = reinterpret_cast<const __nv_bfloat16*>(q); p.ldq = ldq;
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ldo = ldo;
@@ -389,7 +662,7 @@ extern "C" int atlas_attn_decode(const void* q, long long ldq, void* out, long l
                                  const void* v_cache, const int* block_tables, int bt_ld, const int* seq_lens,
                                  const int* query_start_loc, int seq_base, int B, float scale, float k_scale,
                                  float v_scale, int Hq, int Hkv, int D, int block_size, int window, int num_splits,
-                                 float* part_o, float* part_ml, void* stream) {
+                                 float* part_o, float* part_ml, unsigned long long* status, void* stream) {
   if (B <= 0) return 0;
   AttnParams p;
   int rc = fill_common(p, q, ldq, out, ldo, k_cache, v_cache, block_tables, bt_ld, seq_lens, query_start_loc, seq_base,
@@ -399,9 +672,11 @@ extern "C" int atlas_attn_decode(const void* q, long long ldq, void* out, long l
   if (p.num_splits > 1 && (!part_o || !part_ml)) return -3;
   p.part_o = part_o; p.part_ml = part_ml;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (D == 64) return launch_decode<64>(p, B, st);
-  if (D == 128) return launch_decode<128>(p, B, st);
-  return launch_decode<256>(p, B, st);
+  if (p.block_size * D * 2 > 96 * 1024) return -4;
+  if (Hq / Hkv > 8) return -5;        // one n-tile of heads per kv head
+  if (D == 64) return launch_decode<64>(p, B, status, st);
+  if (D == 128) return launch_decode<128>(p, B, status, st);
+  return launch_decode<256>(p, B, status, st);
 }
 
 // Prefill / verify attention: `num_tiles` 16-row query tiles described by (sequence index, first query row of the

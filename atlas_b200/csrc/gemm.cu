@@ -8,9 +8,9 @@
 //           kernels/gb10/common/fp8_gemm_t_blockscaled.cu:15-17, which does it with mma.sync).
 //
 // Roles (320 threads, one CTA per SM, static round-robin over work items):
-//   warp 0      TMA producer: 128B-swizzled A/B tiles into a multi-stage shared-memory ring
-//   warp 1      TMEM owner + single-thread tcgen05.mma issuer, two TMEM accumulator buffers
-//   warps 2..9  epilogue: tcgen05.ld, scale folding, bf16 conversion, global stores, split-K reduction
+//   warp 0       TMA producer: 128B-swizzled A/B tiles into a multi-stage shared-memory ring
+//   warp 1       TMEM owner + single-thread tcgen05.mma issuer, ring of up to four TMEM accumulator buffers
+//   warps 2..9   epilogue: tcgen05.ld, scale folding, bf16 conversion, global stores, split-K reduction
 //
 // Split-K: a work item is (k-split, n-tile, m-tile).  Partials go to an fp32 workspace; the CTA that finishes
 // a tile last (ticket counter) sums the partials in split order, so results do not depend on timing.
@@ -25,7 +25,8 @@ namespace atlas {
 constexpr int kBlockM = 128;
 constexpr int kRowBytes = 128;            // one swizzle row = one BLOCK_K slice
 constexpr int kEpiWarps = 8;
-constexpr int kGemmThreads = 32 * (2 + kEpiWarps);
+constexpr int kCtrlWarps = 2;            // warp 0: TMA producer, warp 1: MMA issuer
+constexpr int kGemmThreads = 32 * (kCtrlWarps + kEpiWarps);
 
 template <int BLOCK_N>
 struct GemmCfg {
@@ -33,9 +34,13 @@ struct GemmCfg {
   static constexpr int kBBytes = BLOCK_N * kRowBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = BLOCK_N == 256 ? 4 : (BLOCK_N == 128 ? 6 : 8);
-  static constexpr int kTmemCols = 2 * BLOCK_N < 32 ? 32 : 2 * BLOCK_N;
+  static constexpr int kAccStages = (512 / BLOCK_N) < 4 ? (512 / BLOCK_N) : 4;   // TMEM accumulator ring depth
+  static constexpr int kTmemCols = kAccStages * BLOCK_N;
   static constexpr int kHalf = BLOCK_N / 2;             // columns per epilogue thread
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 512 /*barriers*/;
+  static constexpr int kScaleRingBytes = kStages * kBlockM * 4;   // per stage: 128 activation scales (fp32)
+  static constexpr int kBScaleMax = 512;                          // k-groups of one split kept in shared memory
+  static constexpr int kBScaleBytes = 2 * 2 * kBScaleMax * 4;     // double-buffered over tiles, two 128-column groups
+  static constexpr int kSmemBytes = kStages * kStageBytes + kScaleRingBytes + kBScaleBytes + 1024 /*align*/ + 512 /*barriers*/;
 };
 
 struct GemmParams {
@@ -46,7 +51,7 @@ struct GemmParams {
   int* counters;
   status_t* status;
   long long ldc;
-  long long sa_m, sa_k;     // a_scale strides (elements) over rows / k-groups
+  long long sa_k;           // a_scale is k-group major: scale(m, g) = a_scale[g * sa_k + m]; sa_k % 4 == 0, rows padded to 128
   int M, N, K;
   int k_blocks;             // number of 128-byte K slices
   int splits, kb_per_split;
@@ -54,6 +59,13 @@ struct GemmParams {
   int b_scale_ld;           // k-groups per row of b_scale
   int vec_ok;               // 16-byte stores into C are legal
 };
+
+ATLAS_DEVICE void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
 
 template <int BLOCK_N, bool FP8>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -67,12 +79,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
+  float* sc_ring = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes);        // [kStages][128]
+  float* bs_smem = sc_ring + kStages * kBlockM;                                         // [2][kBScaleMax]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + Cfg::kScaleRingBytes + Cfg::kBScaleBytes);
   uint64_t* full = bars;
   uint64_t* empty = bars + kStages;
   uint64_t* acc_full = bars + 2 * kStages;
-  uint64_t* acc_empty = acc_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  constexpr int kAcc = Cfg::kAccStages;
+  uint64_t* acc_empty = acc_full + kAcc;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kAcc);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile int* ticket_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
@@ -82,9 +97,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
+      mbar_init(&empty[s], FP8 ? 1 + kEpiWarps : 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kAcc; ++b) {
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], kEpiWarps);
     }
@@ -121,7 +136,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 0x100)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
-          mbar_expect_tx(&full[stage], Cfg::kStageBytes);
+          mbar_expect_tx(&full[stage], Cfg::kStageBytes + (FP8 ? kBlockM * 4 : 0));
+          if (FP8)
+            bulk_g2s(sc_ring + stage * kBlockM, p.a_scale + (long long)kb * p.sa_k + m_tile * kBlockM, kBlockM * 4,
+                     &full[stage]);
           tma_load_2d(sa, &tmap_a, &full[stage], kb * kElemsPerRow, m_tile * kBlockM);
           tma_load_2d(sa + Cfg::kABytes, &tmap_b, &full[stage], kb * kElemsPerRow, n_tile * BLOCK_N);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -142,14 +160,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
         if (!FP8) {
-          const uint32_t buf = acc_iter & 1u, aph = (acc_iter >> 1) & 1u;
+          const uint32_t buf = acc_iter % kAcc, aph = (acc_iter / kAcc) & 1u;
           if (!mbar_wait(&acc_empty[buf], aph ^ 1u, abort_flag, p.status, 0x200)) { ok = false; break; }
           tc_fence_after();
         }
         for (int kb = kb0; kb < kb1; ++kb) {
-          uint32_t buf = acc_iter & 1u;
+          const uint32_t buf = acc_iter % kAcc;
           if (FP8) {
-            const uint32_t aph = (acc_iter >> 1) & 1u;
+            const uint32_t aph = (acc_iter / kAcc) & 1u;
             if (!mbar_wait(&acc_empty[buf], aph ^ 1u, abort_flag, p.status, 0x201)) { ok = false; break; }
           }
           if (!mbar_wait(&full[stage], phase, abort_flag, p.status, 0x202)) { ok = false; break; }
@@ -169,18 +187,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        if (!FP8) { umma_commit(&acc_full[acc_iter & 1u]); ++acc_iter; }
+        if (!FP8) { umma_commit(&acc_full[acc_iter % kAcc]); ++acc_iter; }
       }
     }
-  } else {
+  } else if (warp >= kCtrlWarps) {
     // ------------------------------------------------------------------ epilogue (8 warps)
-    const int e = warp - 2;
+    const int e = warp - kCtrlWarps;
     const int lane_group = warp & 3;                 // TMEM lanes this warp may touch: [32*lane_group, +32)
     const int half = e >> 2;                         // which half of the tile's columns
     const int row_in_tile = lane_group * 32 + lane;
     const uint32_t t_lane = (uint32_t)(lane_group * 32) << 16;
-    const int epi_tid = threadIdx.x - 64;
+    const int epi_tid = threadIdx.x - 32 * kCtrlWarps;
     uint32_t acc_iter = 0;
+    uint32_t tile_iter = 0;
+    uint32_t e_stage = 0, e_phase = 0;       // mirrors the producer's ring position (fp8 path reads the scale slot)
     bool ok = true;
     float acc[HALF];
     // This loop never exits early: the split-K path below uses named barriers that need all eight warps.
@@ -194,37 +214,62 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
       const int m = m_tile * kBlockM + row_in_tile;
       const int n_base = n_tile * BLOCK_N + half * HALF;
+      // Weight scales of this tile's k range -> shared memory (one row per 128-column group of the tile).  The
+      // buffer alternates between tiles so that the single barrier below also protects the previous tile's readers.
+      // Every epilogue warp runs this for every item, whatever `ok` says.
+      float* bs_buf = bs_smem + (tile_iter & 1u) * 2 * Cfg::kBScaleMax;
+      ++tile_iter;
+      if (FP8) {
+        const int nkb = kb1 - kb0;
+        constexpr int kRows = BLOCK_N > 128 ? 2 : 1;
+        for (int i = epi_tid; i < kRows * nkb; i += 32 * kEpiWarps) {
+          const int r = i / nkb, g = i - r * nkb;
+          const int nb = (n_tile * BLOCK_N) / 128 + r;
+          bs_buf[r * Cfg::kBScaleMax + g] = (nb * 128 < p.N) ? __ldg(p.b_scale + (size_t)nb * p.b_scale_ld + kb0 + g) : 0.f;
+        }
+        asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
+      }
       if (!ok) {
         // fall through to the write-out barriers without touching TMEM
       } else if (FP8) {
 #pragma unroll
         for (int i = 0; i < HALF; ++i) acc[i] = 0.f;
-        const float* bs = p.b_scale + (size_t)(n_base / 128) * p.b_scale_ld;
-        const bool row_ok = m < p.M;
-        const bool col_ok = n_base < p.N;
-        float s_next = (row_ok && col_ok && kb0 < kb1) ? p.a_scale[m * p.sa_m + kb0 * p.sa_k] * __ldg(bs + kb0) : 0.f;
+        const float* bs_row = bs_buf + ((BLOCK_N > 128 && half) ? Cfg::kBScaleMax : 0);
         for (int kb = kb0; kb < kb1; ++kb) {
-          const float s = s_next;
-          if (kb + 1 < kb1 && row_ok && col_ok) s_next = p.a_scale[m * p.sa_m + (kb + 1) * p.sa_k] * __ldg(bs + kb + 1);
-          const uint32_t buf = acc_iter & 1u, aph = (acc_iter >> 1) & 1u;
+          const uint32_t buf = acc_iter % kAcc, aph = (acc_iter / kAcc) & 1u;
           if (!mbar_wait(&acc_full[buf], aph, abort_flag, p.status, 0x300)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t taddr = tmem_base + t_lane + buf * BLOCK_N + half * HALF;
-#pragma unroll
-          for (int c = 0; c < HALF / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(taddr + c * 32, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), s, acc[c * 32 + i]);
-          }
-          tc_fence_before();
+          // the MMAs of this k-group are done, so its stage has landed: take the row scale and free the stage
+          if (!mbar_wait(&full[e_stage], e_phase, abort_flag, p.status, 0x302)) { ok = false; break; }
+          const float s = sc_ring[e_stage * kBlockM + row_in_tile] * bs_row[kb - kb0];
           __syncwarp();
-          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          if (lane == 0) mbar_arrive(&empty[e_stage]);
+          if (++e_stage == kStages) { e_stage = 0; e_phase ^= 1u; }
+          const uint32_t taddr = tmem_base + t_lane + buf * BLOCK_N + half * HALF;
+          // Pull the partial tile into registers with back-to-back tcgen05.ld, hand the TMEM buffer back to the
+          // MMA issuer as soon as the loads have landed, and only then fold the scales in.
+          constexpr int kChunk = HALF < 64 ? HALF : 64;
+#pragma unroll
+          for (int c0 = 0; c0 < HALF; c0 += kChunk) {
+            uint32_t r[kChunk / 32][32];
+#pragma unroll
+            for (int c = 0; c < kChunk / 32; ++c) tmem_ld_32x32b_x32(taddr + c0 + c * 32, r[c]);
+            tmem_ld_wait();
+            if (c0 + kChunk >= HALF) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            }
+#pragma unroll
+            for (int c = 0; c < kChunk / 32; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                acc[c0 + c * 32 + i] = fmaf(__uint_as_float(r[c][i]), s, acc[c0 + c * 32 + i]);
+          }
           ++acc_iter;
         }
       } else {
-        const uint32_t buf = acc_iter & 1u, aph = (acc_iter >> 1) & 1u;
+        const uint32_t buf = acc_iter % kAcc, aph = (acc_iter / kAcc) & 1u;
         if (mbar_wait(&acc_full[buf], aph, abort_flag, p.status, 0x301)) {
           tc_fence_after();
           const uint32_t taddr = tmem_base + t_lane + buf * BLOCK_N + half * HALF;
@@ -246,59 +291,63 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
 
       // ---- write out
-      if (p.splits == 1) {
-        if (ok && m < p.M) {
-          __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * p.ldc;
+      bool do_store = ok;
+      if (p.splits > 1) {
+        // fp32 partials go to the workspace in fragment order (float4 index j4, then epilogue thread), so every
+        // store and load below is a fully coalesced 512-byte warp access; the CTA that takes the last ticket of
+        // the tile sums the partials in split order.
+        float4* ws4 = reinterpret_cast<float4*>(p.workspace);
+        const size_t tiles = (size_t)p.m_tiles * p.n_tiles;
+        const size_t tile_id = (size_t)n_tile * p.m_tiles + m_tile;
+        constexpr size_t kFrag4 = (size_t)(32 * kEpiWarps) * (HALF / 4);
+        if (ok) {
+          float4* dst = ws4 + ((size_t)split * tiles + tile_id) * kFrag4 + epi_tid;
 #pragma unroll
-          for (int j = 0; j < HALF; j += 8) {
-            const int n = n_base + j;
-            if (p.vec_ok && n + 8 <= p.N) {
-              uint4 v;
-              v.x = pack_bf16x2(acc[j + 0], acc[j + 1]);
-              v.y = pack_bf16x2(acc[j + 2], acc[j + 3]);
-              v.z = pack_bf16x2(acc[j + 4], acc[j + 5]);
-              v.w = pack_bf16x2(acc[j + 6], acc[j + 7]);
-              *reinterpret_cast<uint4*>(crow + n) = v;
-            } else {
-#pragma unroll
-              for (int i = 0; i < 8; ++i)
-                if (n + i < p.N) crow[n + i] = __float2bfloat16_rn(acc[j + i]);
-            }
-          }
-        }
-      } else {
-        // fp32 partial -> workspace[split][m][n], then ticket; last arriver reduces in split order
-        const size_t plane = (size_t)p.M * p.N;
-        if (ok && m < p.M) {
-          float* wrow = p.workspace + (size_t)split * plane + (size_t)m * p.N;
-#pragma unroll
-          for (int j = 0; j < HALF; ++j)
-            if (n_base + j < p.N) wrow[n_base + j] = acc[j];
+          for (int j4 = 0; j4 < HALF / 4; ++j4)
+            dst[(size_t)j4 * (32 * kEpiWarps)] = make_float4(acc[4 * j4], acc[4 * j4 + 1], acc[4 * j4 + 2], acc[4 * j4 + 3]);
         }
         __threadfence();
         asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
-        const int tile_id = n_tile * p.m_tiles + m_tile;
         if (epi_tid == 0) *ticket_slot = atomicAdd(&p.counters[tile_id], 1);
         asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
         const int ticket = *ticket_slot;
+        do_store = ok && ticket == p.splits - 1;
         if (ticket == p.splits - 1) {
           __threadfence();
-          if (ok && m < p.M) {
-            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * p.ldc;
-#pragma unroll 4
-            for (int j = 0; j < HALF; ++j) {
-              const int n = n_base + j;
-              if (n < p.N) {
-                float s = 0.f;
-                for (int sp = 0; sp < p.splits; ++sp)
-                  s += __ldcg(p.workspace + (size_t)sp * plane + (size_t)m * p.N + n);
-                crow[n] = __float2bfloat16_rn(s);
+          if (ok) {
+#pragma unroll
+            for (int i = 0; i < HALF; ++i) acc[i] = 0.f;
+            for (int sp = 0; sp < p.splits; ++sp) {
+              const float4* src = ws4 + ((size_t)sp * tiles + tile_id) * kFrag4 + epi_tid;
+#pragma unroll
+              for (int j4 = 0; j4 < HALF / 4; ++j4) {
+                const float4 v = __ldcg(src + (size_t)j4 * (32 * kEpiWarps));
+                acc[4 * j4] += v.x; acc[4 * j4 + 1] += v.y; acc[4 * j4 + 2] += v.z; acc[4 * j4 + 3] += v.w;
               }
             }
           }
           if (epi_tid == 0) p.counters[tile_id] = 0;     // ready for the next launch
         }
         asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
+      }
+      if (do_store && m < p.M) {
+        __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * p.ldc;
+#pragma unroll
+        for (int j = 0; j < HALF; j += 8) {
+          const int n = n_base + j;
+          if (p.vec_ok && n + 8 <= p.N) {
+            uint4 v;
+            v.x = pack_bf16x2(acc[j + 0], acc[j + 1]);
+            v.y = pack_bf16x2(acc[j + 2], acc[j + 3]);
+            v.z = pack_bf16x2(acc[j + 4], acc[j + 5]);
+            v.w = pack_bf16x2(acc[j + 6], acc[j + 7]);
+            *reinterpret_cast<uint4*>(crow + n) = v;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (n + i < p.N) crow[n + i] = __float2bfloat16_rn(acc[j + i]);
+          }
+        }
       }
     }
   }
@@ -390,8 +439,10 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
 
 using namespace atlas;
 
-// kind: 0 = bf16, 1 = fp8 block-scaled.  Strides are in elements.  `workspace` needs splits*M*N floats and
-// `counters` m_tiles*n_tiles zero-initialised ints when splits > 1.  Returns 0 or a negative error code.
+// kind: 0 = bf16, 1 = fp8 block-scaled.  Strides are in elements.  For kind 1, a_scale is k-group major
+// (scale(m, g) = a_scale[g * sa_k + m]) with sa_k a multiple of 4 and at least m_tiles*128, so that a 128-row
+// slice is one aligned bulk copy.  With splits > 1, `workspace` needs splits*m_tiles*n_tiles*128*block_n floats and
+// `counters` m_tiles*n_tiles zero-initialised ints.  Returns 0 or a negative error code.
 extern "C" int atlas_gemm(int kind, const void* A, const void* B, void* C, const float* a_scale, long long sa_m,
                           long long sa_k, const float* b_scale, int b_scale_ld, int M, int N, int K, long long lda,
                           long long ldb, long long ldc, int block_n, int splits, float* workspace, int* counters,
@@ -410,7 +461,7 @@ extern "C" int atlas_gemm(int kind, const void* A, const void* B, void* C, const
   if (rc) return rc;
   GemmParams p;
   p.C = C; p.a_scale = a_scale; p.b_scale = b_scale; p.workspace = workspace; p.counters = counters;
-  p.status = status; p.ldc = ldc; p.sa_m = sa_m; p.sa_k = sa_k; p.M = M; p.N = N; p.K = K;
+  p.status = status; p.ldc = ldc; p.sa_k = sa_k; p.M = M; p.N = N; p.K = K;
   p.k_blocks = (K + elems_per_row - 1) / elems_per_row;
   if (splits < 1) splits = 1;
   if (splits > p.k_blocks) splits = p.k_blocks;
@@ -419,6 +470,11 @@ extern "C" int atlas_gemm(int kind, const void* A, const void* B, void* C, const
   if (p.splits > 1 && (!workspace || !counters)) return -5;
   p.m_tiles = (M + kBlockM - 1) / kBlockM;
   p.n_tiles = (N + block_n - 1) / block_n;
+  if (kind == 1) {
+    if (sa_m != 1 || (sa_k % 4) || sa_k < (long long)p.m_tiles * kBlockM) return -6;
+    if ((reinterpret_cast<uintptr_t>(a_scale) & 15)) return -7;
+    if (p.kb_per_split > 512) return -8;
+  }
   p.b_scale_ld = b_scale_ld;
   p.vec_ok = ((ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
   const long long items = (long long)p.m_tiles * p.n_tiles * p.splits;

@@ -46,7 +46,7 @@ def load() -> None:
                                         _i, _i, _i, _i, _f, _f, _f, _vp]
     lib.atlas_gated_rmsnorm.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _ll, _i, _i, _i, _f, _vp]
     lib.atlas_attn_decode.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _f, _f, _f, _i, _i, _i,
-                                      _i, _i, _i, _vp, _vp, _vp]
+                                      _i, _i, _i, _vp, _vp, _vp, _vp]
     lib.atlas_attn_prefill.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _f, _f, _f, _i,
                                        _i, _i, _i, _i, _vp]
     lib.atlas_argmax.argtypes = [_vp, _ll, _i, _i, _i, _vp, _vp]
@@ -113,8 +113,10 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 
 
 def _scale_buf(T: int, kb: int, device) -> torch.Tensor:
-    """Activation scales, k-group major: logical ``[T, kb]`` with strides ``(1, T)``."""
-    return torch.empty(kb, T, dtype=torch.float32, device=device).t()
+    """Activation scales, k-group major: logical ``[T, kb]`` with strides ``(1, T_pad)``; rows are padded to a
+    multiple of 128 tokens so the GEMM can fetch a tile's 128 scales with one aligned bulk copy."""
+    tp = (T + 127) // 128 * 128
+    return torch.empty(kb, tp, dtype=torch.float32, device=device)[:, :T].t()
 
 
 # ----------------------------------------------------------------------------- elementwise
@@ -187,8 +189,8 @@ def gemm_plan(M: int, N: int, K: int, kind: int, sms: int) -> Tuple[int, int]:
     m_tiles = (M + 127) // 128
     if _FORCE_BLOCK_N:
         bn = _FORCE_BLOCK_N
-    elif m_tiles * ((N + 255) // 256) >= 2 * sms and N % 256 == 0:
-        bn = 256
+    elif kind == 0 and m_tiles * ((N + 255) // 256) >= 2 * sms and N % 256 == 0:
+        bn = 256          # bf16 accumulates in TMEM; the fp8 path folds scales in registers and prefers 128
     elif m_tiles * ((N + 127) // 128) >= sms:
         bn = 128
     else:
@@ -199,7 +201,7 @@ def gemm_plan(M: int, N: int, K: int, kind: int, sms: int) -> Tuple[int, int]:
         splits = _FORCE_SPLITS
     elif tiles * 2 <= sms and k_blocks >= 8:
         splits = max(1, min(sms // tiles, k_blocks // 4, 16))
-    while splits > 1 and splits * M * N * 4 > _GEMM_WS_BYTES:
+    while splits > 1 and splits * m_tiles * 128 * ((N + bn - 1) // bn) * bn * 4 > _GEMM_WS_BYTES:
         splits -= 1
     return bn, splits
 
@@ -220,6 +222,11 @@ def _gemm(kind: int, a: torch.Tensor, b: torch.Tensor, a_scale, b_scale, out: Op
         cnt = scratch("gemm_counters", 1 << 18, a.device)
     sa_m = sa_k = 0
     if kind == 1:
+        kb = a_scale.shape[1]
+        if a_scale.stride(0) != 1 or a_scale.stride(1) % 4 or a_scale.stride(1) < (M + 127) // 128 * 128 or a_scale.data_ptr() % 16:
+            fixed = _scale_buf(M, kb, a.device)
+            fixed.copy_(a_scale)
+            a_scale = fixed
         sa_m, sa_k = a_scale.stride(0), a_scale.stride(1)
         assert b_scale.is_contiguous() and b_scale.dtype == torch.float32 and a_scale.dtype == torch.float32
     _check(lib().atlas_gemm(kind, a.data_ptr(), b.data_ptr(), out.data_ptr(), _ptr(a_scale), sa_m, sa_k, _ptr(b_scale),
@@ -306,7 +313,7 @@ def paged_attention(q, k_cache, v_cache, batch, scale, k_scale, v_scale, sliding
         _check(lib().atlas_attn_decode(q.data_ptr(), q.stride(0), out.data_ptr(), Hq * D, k_cache.data_ptr(),
                                        v_cache.data_ptr(), bt.data_ptr(), bt.stride(0), batch.seq_lens.data_ptr(),
                                        batch.query_start_loc.data_ptr(), 0, nd, float(scale), float(k_scale),
-                                       float(v_scale), Hq, Hkv, D, bs, window, splits, _ptr(po), _ptr(pml), st),
+                                       float(v_scale), Hq, Hkv, D, bs, window, splits, _ptr(po), _ptr(pml), _status_ptr[d], st),
                "attn_decode")
     if batch.num_seqs > nd:
         tiles = getattr(batch, "_attn_tiles", None)
