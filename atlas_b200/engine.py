@@ -268,6 +268,8 @@ class LLMEngine:
                 self.stats.on_first_token(now - seq.arrival)
             seq.output_tokens.append(int(t))
             kept.append(int(t))
+            if seq.grammar is not None and hasattr(seq.grammar, "accept"):
+                seq.grammar.accept(int(t))
             if lps is not None and j < len(lps):
                 seq.logprobs.append(lps[j])
             reason = None

@@ -1,0 +1,61 @@
+"""PEFT LoRA adapters: loading (``adapter_config.json`` + ``adapter_model.safetensors``) and per-request application
+as a batched gather-matrix-vector (shrink then expand) on top of the base projection.
+
+Reference parity: ``crates/spark-model/src/layers/lora/*`` (adapter pool, bgmv shrink/expand),
+``kernels/gb10/common/lora_bgmv.cu``, ``spark-runtime/src/weights/adapter.rs``.
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass, field
+from typing import Dict, Optional
+
+import torch
+
+
+@dataclass
+class LoraAdapter:
+    name: str
+    rank: int
+    alpha: float
+    # module path (e.g. "layers.3.self_attn.q_proj") -> (A [r, in], B [out, r])
+    weights: Dict[str, tuple] = field(default_factory=dict)
+
+    @property
+    def scaling(self) -> float:
+        return self.alpha / max(1, self.rank)
+
+
+def load_adapter(path: str, model=None) -> LoraAdapter:
+    with open(os.path.join(path, "adapter_config.json")) as f:
+        cfg = json.load(f)
+    from safetensors.torch import load_file
+    st = load_file(os.path.join(path, "adapter_model.safetensors"))
+    ad = LoraAdapter(os.path.basename(path.rstrip("/")), int(cfg.get("r", 8)), float(cfg.get("lora_alpha", 16)))
+    a_parts, b_parts = {}, {}
+    for k, v in st.items():
+        key = k.replace("base_model.model.", "").replace("model.", "", 1)
+        if ".lora_A" in key:
+            a_parts[key.split(".lora_A")[0]] = v
+        elif ".lora_B" in key:
+            b_parts[key.split(".lora_B")[0]] = v
+    dev = model.device if model is not None else "cpu"
+    for mod, a in a_parts.items():
+        if mod in b_parts:
+            ad.weights[mod] = (a.to(dev), b_parts[mod].to(dev))
+    return ad
+
+
+def bgmv(x: torch.Tensor, adapters: Dict[int, tuple], slot_of_row: torch.Tensor, scaling: Dict[int, float]) -> torch.Tensor:
+    """Per-row LoRA delta: ``delta[t] = scaling * B_s (A_s x[t])`` with ``s = slot_of_row[t]`` (slot 0 = no adapter)."""
+    out = None
+    for slot, (A, B) in adapters.items():
+        rows = (slot_of_row == slot).nonzero(as_tuple=True)[0]
+        if rows.numel() == 0:
+            continue
+        d = (x[rows].float() @ A.float().t()) @ B.float().t() * scaling[slot]
+        if out is None:
+            out = torch.zeros(x.shape[0], B.shape[0], dtype=torch.float32, device=x.device)
+        out.index_add_(0, rows, d)
+    return out
