@@ -133,8 +133,9 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bf
 // gate_up [T, 2I] -> silu(gate) * up, bf16 or fp8+scale
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, long long ld, int I, __nv_bfloat16* y, long long ldy, uint8_t* q,
-                long long ldq, float* scale, long long scale_ld) {
+                long long ldq, float* scale, long long scale_ld, const int* live_tiles) {
   const int t = blockIdx.y;
+  if (live_tiles && t >= (*live_tiles) * 128) return;      // expert-sorted buffers: rows past the live tiles are unused
   const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   const bool live = e < I;
   float o[8];
@@ -338,13 +339,13 @@ extern "C" int atlas_rmsnorm(const void* x, long long ldx, const void* residual,
 }
 
 extern "C" int atlas_silu_mul(const void* gu, long long ld, int T, int I, void* y, long long ldy, void* q,
-                              long long ldq, float* scale, long long scale_ld, void* stream) {
+                              long long ldq, float* scale, long long scale_ld, const int* live_tiles, void* stream) {
   if (T <= 0) return 0;
   if (I % 8 || (q && I % 128)) return -1;
   dim3 grid((I / 8 + 255) / 256, T);
   silu_mul_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(gu), ld, I, reinterpret_cast<__nv_bfloat16*>(y), ldy,
-      reinterpret_cast<uint8_t*>(q), ldq, scale, scale_ld);
+      reinterpret_cast<uint8_t*>(q), ldq, scale, scale_ld, live_tiles);
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
 }
 

@@ -58,6 +58,12 @@ struct GemmParams {
   int m_tiles, n_tiles;
   int b_scale_ld;           // k-groups per row of b_scale
   int vec_ok;               // 16-byte stores into C are legal
+  // grouped (MoE) mode: rows are expert-sorted and every expert's segment is padded to a multiple of 128 rows, so
+  // m-tile i covers rows [128 i, 128 i + 128) and belongs to expert tile_expert[i]; B is the stack [E * expert_n, K].
+  const int* tile_expert;       // nullptr = plain GEMM
+  const int* num_m_tiles_ptr;   // device-side tile count (the host cannot know it)
+  int expert_n;                 // output features per expert
+  long long b_scale_expert_stride;
 };
 
 ATLAS_DEVICE void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
@@ -119,7 +125,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int total_items = p.m_tiles * p.n_tiles * p.splits;
+  const int m_tiles = p.tile_expert ? *p.num_m_tiles_ptr : p.m_tiles;
+  const int total_items = m_tiles * p.n_tiles * p.splits;
+  const int M_rows = p.tile_expert ? m_tiles * kBlockM : p.M;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -127,8 +135,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-        const int m_tile = item % p.m_tiles;
-        const int rest = item / p.m_tiles;
+        const int m_tile = item % m_tiles;
+        const int rest = item / m_tiles;
         const int n_tile = rest % p.n_tiles;
         const int split = rest / p.n_tiles;
         const int kb0 = split * p.kb_per_split;
@@ -141,7 +149,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             bulk_g2s(sc_ring + stage * kBlockM, p.a_scale + (long long)kb * p.sa_k + m_tile * kBlockM, kBlockM * 4,
                      &full[stage]);
           tma_load_2d(sa, &tmap_a, &full[stage], kb * kElemsPerRow, m_tile * kBlockM);
-          tma_load_2d(sa + Cfg::kABytes, &tmap_b, &full[stage], kb * kElemsPerRow, n_tile * BLOCK_N);
+          tma_load_2d(sa + Cfg::kABytes, &tmap_b, &full[stage], kb * kElemsPerRow,
+                      (p.tile_expert ? p.tile_expert[m_tile] * p.expert_n : 0) + n_tile * BLOCK_N);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -156,7 +165,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t stage = 0, phase = 0, acc_iter = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-        const int split = item / (p.m_tiles * p.n_tiles);
+        const int split = item / (m_tiles * p.n_tiles);
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
         if (!FP8) {
@@ -206,8 +215,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // This loop never exits early: the split-K path below uses named barriers that need all eight warps.
     // Once a wait has failed (`ok` false) the remaining items only walk the barriers.
     for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
-      const int m_tile = item % p.m_tiles;
-      const int rest = item / p.m_tiles;
+      const int m_tile = item % m_tiles;
+      const int rest = item / m_tiles;
       const int n_tile = rest % p.n_tiles;
       const int split = rest / p.n_tiles;
       const int kb0 = split * p.kb_per_split;
@@ -225,7 +234,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         for (int i = epi_tid; i < kRows * nkb; i += 32 * kEpiWarps) {
           const int r = i / nkb, g = i - r * nkb;
           const int nb = (n_tile * BLOCK_N) / 128 + r;
-          bs_buf[r * Cfg::kBScaleMax + g] = (nb * 128 < p.N) ? __ldg(p.b_scale + (size_t)nb * p.b_scale_ld + kb0 + g) : 0.f;
+          const float* bsrc = p.b_scale + (p.tile_expert ? (size_t)p.tile_expert[m_tile] * p.b_scale_expert_stride : 0);
+          bs_buf[r * Cfg::kBScaleMax + g] = (nb * 128 < p.N) ? __ldg(bsrc + (size_t)nb * p.b_scale_ld + kb0 + g) : 0.f;
         }
         asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
       }
@@ -297,8 +307,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         // store and load below is a fully coalesced 512-byte warp access; the CTA that takes the last ticket of
         // the tile sums the partials in split order.
         float4* ws4 = reinterpret_cast<float4*>(p.workspace);
-        const size_t tiles = (size_t)p.m_tiles * p.n_tiles;
-        const size_t tile_id = (size_t)n_tile * p.m_tiles + m_tile;
+        const size_t tiles = (size_t)m_tiles * p.n_tiles;
+        const size_t tile_id = (size_t)n_tile * m_tiles + m_tile;
         constexpr size_t kFrag4 = (size_t)(32 * kEpiWarps) * (HALF / 4);
         if (ok) {
           float4* dst = ws4 + ((size_t)split * tiles + tile_id) * kFrag4 + epi_tid;
@@ -330,7 +340,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
       }
-      if (do_store && m < p.M) {
+      if (do_store && m < M_rows) {
         __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * p.ldc;
 #pragma unroll
         for (int j = 0; j < HALF; j += 8) {
@@ -462,6 +472,7 @@ extern "C" int atlas_gemm(int kind, const void* A, const void* B, void* C, const
   GemmParams p;
   p.C = C; p.a_scale = a_scale; p.b_scale = b_scale; p.workspace = workspace; p.counters = counters;
   p.status = status; p.ldc = ldc; p.sa_k = sa_k; p.M = M; p.N = N; p.K = K;
+  p.tile_expert = nullptr; p.num_m_tiles_ptr = nullptr; p.expert_n = 0; p.b_scale_expert_stride = 0;
   p.k_blocks = (K + elems_per_row - 1) / elems_per_row;
   if (splits < 1) splits = 1;
   if (splits > p.k_blocks) splits = p.k_blocks;
@@ -478,6 +489,55 @@ extern "C" int atlas_gemm(int kind, const void* A, const void* B, void* C, const
   p.b_scale_ld = b_scale_ld;
   p.vec_ok = ((ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
   const long long items = (long long)p.m_tiles * p.n_tiles * p.splits;
+  int grid = (int)(items < num_sms ? items : num_sms);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (kind == 1) {
+    if (block_n == 64) return launch_gemm<64, true>(ta, tb, p, grid, st);
+    if (block_n == 128) return launch_gemm<128, true>(ta, tb, p, grid, st);
+    return launch_gemm<256, true>(ta, tb, p, grid, st);
+  }
+  if (block_n == 64) return launch_gemm<64, false>(ta, tb, p, grid, st);
+  if (block_n == 128) return launch_gemm<128, false>(ta, tb, p, grid, st);
+  return launch_gemm<256, false>(ta, tb, p, grid, st);
+}
+
+// Grouped (MoE) GEMM: C[r, :] = A[r, :] * B[e(r)]^T for expert-sorted rows.  `A` has `max_rows` rows (a multiple of
+// 128); m-tile i covers rows [128 i, 128 i + 128) and uses expert tile_expert[i]; *num_m_tiles (device memory) says how
+// many tiles are live.  `B` is the expert stack [E * N, K]; b_scale is [E, ceil(N/128), K/128].
+extern "C" int atlas_gemm_grouped(int kind, const void* A, const void* B, void* C, const float* a_scale, long long sa_k,
+                                  const float* b_scale, int max_rows, int N, int K, int E, long long lda, long long ldb,
+                                  long long ldc, int block_n, const int* tile_expert, const int* num_m_tiles,
+                                  int num_sms, unsigned long long* status, void* stream) {
+  if (max_rows <= 0 || N <= 0 || K <= 0 || E <= 0) return 0;
+  if (max_rows % kBlockM) return -9;
+  const uint32_t esize = kind == 1 ? 1 : 2;
+  const int elems_per_row = 128 / esize;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -1;
+  if ((lda * esize) % 16 || (ldb * esize) % 16) return -2;
+  if (kind == 1 && (K % 128)) return -3;
+  if (block_n != 64 && block_n != 128 && block_n != 256) return -4;
+  if (N % block_n) return -10;            // a tile must not straddle two experts' rows of B
+  CUtensorMap ta, tb;
+  int rc = make_tmap_kmajor(&ta, A, max_rows, K, lda, kBlockM, esize);
+  if (rc) return rc;
+  rc = make_tmap_kmajor(&tb, B, (uint64_t)E * N, K, ldb, block_n, esize);
+  if (rc) return rc;
+  GemmParams p;
+  p.C = C; p.a_scale = a_scale; p.b_scale = b_scale; p.workspace = nullptr; p.counters = nullptr;
+  p.status = status; p.ldc = ldc; p.sa_k = sa_k; p.M = max_rows; p.N = N; p.K = K;
+  p.k_blocks = (K + elems_per_row - 1) / elems_per_row;
+  p.splits = 1; p.kb_per_split = p.k_blocks;
+  p.m_tiles = max_rows / kBlockM;
+  p.n_tiles = N / block_n;
+  p.b_scale_ld = p.k_blocks;
+  p.vec_ok = ((ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
+  p.tile_expert = tile_expert; p.num_m_tiles_ptr = num_m_tiles; p.expert_n = N;
+  p.b_scale_expert_stride = (long long)((N + 127) / 128) * p.k_blocks;
+  if (kind == 1) {
+    if ((sa_k % 4) || sa_k < max_rows || (reinterpret_cast<uintptr_t>(a_scale) & 15)) return -6;
+    if (p.kb_per_split > 512) return -8;
+  }
+  const long long items = (long long)p.m_tiles * p.n_tiles;
   int grid = (int)(items < num_sms ? items : num_sms);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (kind == 1) {

@@ -25,7 +25,7 @@ int atlas_rmsnorm(const void* x, long long ldx, const void* residual, long long 
                   long long ldro, void* y, long long ldy, void* q, long long ldq, float* scale, long long scale_ld,
                   int T, int H, float eps, int plus_one, void* stream);
 int atlas_silu_mul(const void* gu, long long ld, int T, int I, void* y, long long ldy, void* q, long long ldq,
-                   float* scale, long long scale_ld, void* stream);
+                   float* scale, long long scale_ld, const int* live_tiles, void* stream);
 int atlas_quant_fp8(const void* x, long long ld, int T, int K, void* q, long long ldq, float* scale,
                     long long scale_ld, void* stream);
 int atlas_rope_kv_write(void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv,
@@ -35,6 +35,33 @@ int atlas_rope_kv_write(void* q, long long ldq, const void* k, long long ldk, co
                         float v_scale, void* stream);
 int atlas_gated_rmsnorm(const void* x, long long ldx, const void* z, long long ldz, const void* w, void* y,
                         long long ldy, int T, int H, int D, float eps, void* stream);
+
+// ---- MoE (moe.cu) and grouped GEMM (gemm.cu)
+int atlas_moe_route(const void* logits, long long ld, int is_bf16, int T, int E, int k, int norm, int sigmoid,
+                    float* w_out, int* id_out, void* stream);
+int atlas_moe_align(const int* topk_ids, int T, int k, int e_lo, int E_local, int* slot_of, int* row_token,
+                    int* tile_expert, int* num_tiles, int max_rows, void* stream);
+int atlas_moe_gather(const void* x, long long ldx, const int* row_token, const int* num_tiles, int max_rows, int H,
+                     void* y, void* q, float* scale, long long scale_ld, void* stream);
+int atlas_moe_combine(const void* y, long long ldy, const int* slot_of, const float* topk_w, int T, int k, int H,
+                      const void* addend, long long ld_add, void* out, long long ldo, void* stream);
+int atlas_gemm_grouped(int kind, const void* A, const void* B, void* C, const float* a_scale, long long sa_k,
+                       const float* b_scale, int max_rows, int N, int K, int E, long long lda, long long ldb,
+                       long long ldc, int block_n, const int* tile_expert, const int* num_m_tiles, int num_sms,
+                       unsigned long long* status, void* stream);
+
+// ---- Gated DeltaNet (gdn.cu)
+int atlas_gdn_conv(const void* x, long long ldx, const void* w, int C, int W, const void* conv_state,
+                   const int* seq_of_token, const int* query_start_loc, const int* state_slots,
+                   const unsigned char* has_state, void* y, long long ldy, int T, void* stream);
+int atlas_gdn_conv_state(const void* x, long long ldx, int C, int W, void* conv_state, const int* query_start_loc,
+                         const int* state_slots, const unsigned char* has_state, const int* limit, const int* snap_rows,
+                         const int* snap_slots, int num_snaps_per_seq, int B, void* stream);
+int atlas_gdn_recurrent(const void* y, long long ldy, const void* a, long long lda, const void* b, long long ldb,
+                        const float* A_log, const float* dt_bias, float* h, void* out, long long ldo,
+                        const int* query_start_loc, const int* state_slots, const unsigned char* has_state,
+                        const int* limit, const int* snap_rows, const int* snap_slots, int num_snaps_per_seq, int B,
+                        int Hk, int Hv, int Dk, int Dv, int commit, void* stream);
 
 // ---- attention (attention.cu)
 int atlas_attn_decode(const void* q, long long ldq, void* out, long long ldo, const void* k_cache, const void* v_cache,

@@ -1,0 +1,240 @@
+// Mixture-of-experts support kernels around the grouped tcgen05 GEMM (gemm.cu, grouped mode):
+//   moe_route_kernel    router logits -> softmax / sigmoid scores -> top-k ids + (re)normalised weights
+//   moe_align_kernel    per-expert histogram, 128-row padded segment offsets, row slot of every (token, k) pair,
+//                       m-tile -> expert worklist and the live tile count (all on device: graph-capturable)
+//   moe_gather_kernel   expert-sorted activation rows (bf16 copy, or FP8 + k-group-major scales)
+//   moe_combine_kernel  out[t] = sum_j w[t,j] * y[slot(t,j)]  (+ optional addend, e.g. shared expert / residual)
+// Reference ops replaced: kernels/gb10/common/{moe_topk,moe_topk_sigmoid,moe_permute}.cu
+// (moe_count_experts, moe_sort_by_expert, moe_permute_tokens, moe_build_tile_worklist, moe_unpermute_reduce).
+#include "common.cuh"
+#include "host_api.h"
+
+namespace atlas {
+
+// one warp per token; E <= 1024
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const T* __restrict__ logits, long long ld, int T_, int E, int k, int norm, int sigmoid,
+                 float* __restrict__ w_out, int* __restrict__ id_out) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= T_) return;
+  constexpr int kMaxPer = 32;
+  float v[kMaxPer];
+  const int per = (E + 31) / 32;
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kMaxPer; ++i) {
+    const int e = i * 32 + lane;
+    v[i] = (i < per && e < E) ? (float)logits[t * ld + e] : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < kMaxPer; ++i) {
+    if (i < per && v[i] > -INFINITY) {
+      v[i] = sigmoid ? 1.f / (1.f + __expf(-v[i])) : __expf(v[i] - mx);
+      sum += sigmoid ? 0.f : v[i];
+    }
+  }
+  sum = warp_sum(sum);
+  const float inv = sigmoid ? 1.f : 1.f / sum;
+  float wsum = 0.f;
+  float my_w = 0.f;
+  int my_id = 0;
+  for (int j = 0; j < k; ++j) {
+    float best = -INFINITY;
+    int bi = 0x7FFFFFFF;
+#pragma unroll
+    for (int i = 0; i < kMaxPer; ++i) {
+      const int e = i * 32 + lane;
+      if (i < per && e < E && (v[i] > best)) { best = v[i]; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    // remove the winner (ties resolve to the lowest expert id)
+    if ((bi & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < kMaxPer; ++i)
+        if (i == (bi >> 5)) v[i] = -INFINITY;
+    }
+    const float pw = best * inv;
+    wsum += pw;
+    if (lane == j) { my_w = pw; my_id = bi; }
+  }
+  if (lane < k) {
+    w_out[(long long)t * k + lane] = norm ? my_w / fmaxf(wsum, 1e-20f) : my_w;
+    id_out[(long long)t * k + lane] = my_id;
+  }
+}
+
+// Single CTA (1024 threads).  counts/offsets live in shared memory (E <= 1024).
+// slot_of[t*k+j] = row in the expert-sorted buffer, or -1 for experts outside [e_lo, e_lo + E_local).
+__global__ void __launch_bounds__(1024)
+moe_align_kernel(const int* __restrict__ topk_ids, int n_pairs, int e_lo, int E_local, int* __restrict__ slot_of,
+                 int* __restrict__ row_token, int* __restrict__ tile_expert, int* __restrict__ num_tiles,
+                 int max_rows, int k) {
+  __shared__ int counts[1024];
+  __shared__ int offsets[1025];
+  __shared__ int cursor[1024];
+  const int tid = threadIdx.x;
+  for (int e = tid; e < E_local; e += blockDim.x) { counts[e] = 0; cursor[e] = 0; }
+  __syncthreads();
+  for (int i = tid; i < n_pairs; i += blockDim.x) {
+    const int e = topk_ids[i] - e_lo;
+    if (e >= 0 && e < E_local) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int off = 0, tiles = 0;
+    for (int e = 0; e < E_local; ++e) {
+      offsets[e] = off;
+      const int nt = (counts[e] + 127) >> 7;
+      for (int i = 0; i < nt; ++i) tile_expert[tiles + i] = e;
+      tiles += nt;
+      off += nt << 7;
+    }
+    offsets[E_local] = off;
+    *num_tiles = tiles;
+  }
+  __syncthreads();
+  const int total = offsets[E_local];
+  for (int r = tid; r < max_rows; r += blockDim.x) row_token[r] = -1;
+  __syncthreads();
+  // Rank inside an expert: pairs are visited in index order by a fixed thread, but threads race on the cursor;
+  // the row order inside an expert does not change any row's result, and the combine sums in fixed k order.
+  for (int i = tid; i < n_pairs; i += blockDim.x) {
+    const int e = topk_ids[i] - e_lo;
+    int slot = -1;
+    if (e >= 0 && e < E_local) {
+      slot = offsets[e] + atomicAdd(&cursor[e], 1);
+      if (slot < max_rows) row_token[slot] = i / k; else slot = -1;
+    }
+    slot_of[i] = slot;
+  }
+  (void)total;
+}
+
+// xs[row] = x[row_token[row]] ; optional FP8 group quantisation (scales k-group major over sorted rows)
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const int* __restrict__ row_token,
+                  const int* __restrict__ num_tiles, int H, __nv_bfloat16* y, uint8_t* q, float* scale, long long scale_ld) {
+  const int row = blockIdx.y;
+  if (row >= (*num_tiles) * 128) return;
+  const int t = row_token[row];
+  const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  const bool live = e < H;
+  float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (live && t >= 0) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(x + t * ldx + e);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+  if (q) {
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (live) {
+      const float sc = fmaxf(amax, 1e-10f) / 448.f;
+      uint32_t w[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t acc = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc |= (uint32_t)f32_to_fp8_e4m3(__fdiv_rn(v[h * 4 + i], sc)) << (8 * i);
+        w[h] = acc;
+      }
+      *reinterpret_cast<uint2*>(q + (long long)row * H + e) = make_uint2(w[0], w[1]);
+      if ((threadIdx.x & 15) == 0) scale[(long long)(e >> 7) * scale_ld + row] = sc;
+    }
+  } else if (live) {
+    uint4 out;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(y + (long long)row * H + e) = out;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const __nv_bfloat16* __restrict__ y, long long ldy, const int* __restrict__ slot_of,
+                   const float* __restrict__ topk_w, int k, int H, const __nv_bfloat16* addend, long long ld_add,
+                   __nv_bfloat16* out, long long ldo) {
+  const int t = blockIdx.y;
+  const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (e >= H) return;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int j = 0; j < k; ++j) {
+    const int slot = slot_of[t * k + j];
+    if (slot < 0) continue;
+    const float w = topk_w[t * k + j];
+    const uint4 raw = *reinterpret_cast<const uint4*>(y + (long long)slot * ldy + e);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 f = __bfloat1622float2(h[i]); acc[2 * i] += w * f.x; acc[2 * i + 1] += w * f.y; }
+  }
+  if (addend) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(addend + (long long)t * ld_add + e);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 f = __bfloat1622float2(h[i]); acc[2 * i] += f.x; acc[2 * i + 1] += f.y; }
+  }
+  uint4 o;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+  *reinterpret_cast<uint4*>(out + (long long)t * ldo + e) = o;
+}
+
+}  // namespace atlas
+
+using namespace atlas;
+
+extern "C" int atlas_moe_route(const void* logits, long long ld, int is_bf16, int T, int E, int k, int norm, int sigmoid,
+                               float* w_out, int* id_out, void* stream) {
+  if (T <= 0) return 0;
+  if (E > 1024 || k > 32 || k > E) return -1;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = (T + 3) / 4;
+  if (is_bf16) moe_route_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(logits), ld, T, E, k, norm, sigmoid, w_out, id_out);
+  else moe_route_kernel<float><<<grid, 128, 0, st>>>(reinterpret_cast<const float*>(logits), ld, T, E, k, norm, sigmoid, w_out, id_out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+extern "C" int atlas_moe_align(const int* topk_ids, int T, int k, int e_lo, int E_local, int* slot_of, int* row_token,
+                               int* tile_expert, int* num_tiles, int max_rows, void* stream) {
+  if (E_local > 1024) return -1;
+  moe_align_kernel<<<1, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(topk_ids, T * k, e_lo, E_local, slot_of, row_token,
+                                                                          tile_expert, num_tiles, max_rows, k);
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+extern "C" int atlas_moe_gather(const void* x, long long ldx, const int* row_token, const int* num_tiles, int max_rows,
+                                int H, void* y, void* q, float* scale, long long scale_ld, void* stream) {
+  if (max_rows <= 0) return 0;
+  if (H % 8 || (q && H % 128)) return -1;
+  dim3 grid((H / 8 + 255) / 256, max_rows);
+  moe_gather_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), ldx, row_token, num_tiles, H, reinterpret_cast<__nv_bfloat16*>(y),
+      reinterpret_cast<uint8_t*>(q), scale, scale_ld);
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+extern "C" int atlas_moe_combine(const void* y, long long ldy, const int* slot_of, const float* topk_w, int T, int k, int H,
+                                 const void* addend, long long ld_add, void* out, long long ldo, void* stream) {
+  if (T <= 0) return 0;
+  if (H % 8) return -1;
+  dim3 grid((H / 8 + 255) / 256, T);
+  moe_combine_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(y), ldy, slot_of, topk_w, k, H, reinterpret_cast<const __nv_bfloat16*>(addend),
+      ld_add, reinterpret_cast<__nv_bfloat16*>(out), ldo);
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}

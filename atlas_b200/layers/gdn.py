@@ -97,14 +97,14 @@ class GatedDeltaNet:
         if batch.spec_verify:
             self._pending = (mixed.clone(), b.clone(), a.clone(), list(batch.query_lens_host), list(batch.state_slots_host),
                              list(batch.has_state_host))
-        if proj.is_cuda:
+        if ops.on_gpu(proj):
             o = ops.cuda_ops().gdn_forward(self, mixed, a, b, batch, state, commit=not batch.spec_verify)
         else:
             o = self._forward_ref(mixed, a, b, batch.query_lens_host, batch.state_slots_host, batch.has_state_host,
                                   state, commit=not batch.spec_verify, snapshot_plan=batch.snapshot_plan)
         T = o.shape[0]
         y = ref.gated_rmsnorm(o.view(T, self.hv, self.dv), z.reshape(T, self.hv, self.dv), self.norm_w,
-                              self.cfg.rms_norm_eps) if not o.is_cuda else \
+                              self.cfg.rms_norm_eps) if not ops.on_gpu(o) else \
             ops.cuda_ops().gated_rmsnorm(o.view(T, self.hv, self.dv), z.reshape(T, self.hv, self.dv), self.norm_w,
                                          self.cfg.rms_norm_eps)
         out = ops.linear(y.reshape(T, self.vd), self.out_proj)
@@ -157,7 +157,7 @@ class GatedDeltaNet:
             return
         mixed, b, a, qlens, slots, has_state = self._pending
         self._pending = None
-        if mixed.is_cuda:
+        if ops.on_gpu(mixed):
             ops.cuda_ops().gdn_commit(self, mixed, a, b, qlens, slots, has_state, state, num_accepted_rows)
         else:
             self._forward_ref(mixed, a, b, qlens, slots, has_state, state, commit=True, limit=num_accepted_rows)

@@ -124,7 +124,7 @@ class MoE:
         x = act.plain()
         logits = ops.linear(x, self.router)
         topk_w, topk_ids = ops.moe_route(logits, self.top_k, self.cfg.norm_topk_prob, self.cfg.router_scoring)
-        if x.is_cuda:
+        if ops.on_gpu(x):
             y = ops.cuda_ops().moe_forward(x, topk_w, topk_ids, self.experts, self.e_lo, self.pctx, self.ep_mode)
         else:
             y = self._forward_ref(x, topk_w, topk_ids)

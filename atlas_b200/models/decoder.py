@@ -25,10 +25,14 @@ _DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torc
            "torch.float32": torch.float32, "torch.bfloat16": torch.bfloat16, "torch.float16": torch.float16}
 
 
+def kv_dtype_is_fp8(dtype) -> bool:
+    return dtype == torch.float8_e4m3fn
+
+
 def alloc_kv(num_blocks: int, block_size: int, hkv: int, d: int, dtype, device):
     """Paged K and V pools as logical ``[num_blocks, block_size, Hkv, D]`` tensors (the GPU pools are views
     of the kernels' physical layout)."""
-    if torch.device(device).type == "cuda":
+    if torch.device(device).type == "cuda" and kv_dtype_is_fp8(dtype):
         return ops.cuda_ops().alloc_kv_cache(num_blocks, block_size, hkv, d, dtype, device)
     shape = (num_blocks, block_size, hkv, d)
     return torch.zeros(shape, dtype=dtype, device=device), torch.zeros(shape, dtype=dtype, device=device)

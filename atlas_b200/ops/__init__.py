@@ -15,6 +15,12 @@ from .. import quant as Q
 from . import reference as ref
 
 _cuda = None
+FORCE_REFERENCE = False     # run the plain-PyTorch restatement even for GPU tensors (oracle for end-to-end tests)
+
+
+def on_gpu(t: torch.Tensor) -> bool:
+    """True when ``t`` should go to the sm_100a kernels."""
+    return t.is_cuda and not FORCE_REFERENCE
 
 
 def cuda_ops():
@@ -91,13 +97,13 @@ class Act:
 
 # ----------------------------------------------------------------------------- elementwise / norm
 def quant_fp8(x: torch.Tensor, group: int = 128):
-    if x.is_cuda:
+    if on_gpu(x):
         return cuda_ops().quant_fp8(x, group)
     return Q.per_token_group_quant_fp8(x, group)
 
 
 def rmsnorm(x, w, eps, residual=None, plus_one=False):
-    if x.is_cuda:
+    if on_gpu(x):
         return cuda_ops().rmsnorm(x, w, eps, residual, plus_one, quant=False)
     return ref.rmsnorm(x, w, eps, residual, plus_one)
 
@@ -105,7 +111,7 @@ def rmsnorm(x, w, eps, residual=None, plus_one=False):
 def rmsnorm_act(x, w, eps, residual=None, plus_one=False, want_fp8=False) -> Tuple[Act, Optional[torch.Tensor]]:
     """Residual add + RMSNorm, emitting FP8 group-quantized activations when the consumer is an FP8 GEMM."""
     if want_fp8 and x.shape[-1] % 128 == 0:
-        if x.is_cuda:
+        if on_gpu(x):
             q, s, r = cuda_ops().rmsnorm(x, w, eps, residual, plus_one, quant=True)
         else:
             q, s, r = ref.rmsnorm_quant_fp8(x, w, eps, residual, plus_one)
@@ -117,12 +123,12 @@ def rmsnorm_act(x, w, eps, residual=None, plus_one=False, want_fp8=False) -> Tup
 def silu_mul_act(gate_up: torch.Tensor, want_fp8=False) -> Act:
     inter = gate_up.shape[-1] // 2
     if want_fp8 and inter % 128 == 0:
-        if gate_up.is_cuda:
+        if on_gpu(gate_up):
             q, s = cuda_ops().silu_mul(gate_up, quant=True)
         else:
             q, s = ref.silu_mul_quant_fp8(gate_up)
         return Act(q=q, s=s)
-    if gate_up.is_cuda:
+    if on_gpu(gate_up):
         return Act(x=cuda_ops().silu_mul(gate_up, quant=False))
     return Act(x=ref.silu_mul(gate_up))
 
@@ -131,7 +137,7 @@ def silu_mul_act(gate_up: torch.Tensor, want_fp8=False) -> Act:
 def linear(a, w: LinearWeight, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``y = a @ W^T (+ bias)``; ``a`` is a tensor or an :class:`Act`."""
     act = a if isinstance(a, Act) else Act(x=a)
-    dev_cuda = (act.x if act.x is not None else act.q).is_cuda
+    dev_cuda = on_gpu(act.x if act.x is not None else act.q)
     if w.kind == "fp8_block":
         q, s = act.fp8()
         if dev_cuda:
@@ -146,7 +152,7 @@ def linear(a, w: LinearWeight, out: Optional[torch.Tensor] = None) -> torch.Tens
             y = (x.float() @ w.dequantized().t()).to(x.dtype)
     else:
         x = act.plain()
-        if dev_cuda and x.dtype == torch.bfloat16:
+        if dev_cuda and x.dtype == torch.bfloat16 and w.weight.dtype == torch.bfloat16:
             y = cuda_ops().gemm_bf16(x, w.weight, out=out)
         else:
             y = torch.nn.functional.linear(x, w.weight)
@@ -158,7 +164,7 @@ def linear(a, w: LinearWeight, out: Optional[torch.Tensor] = None) -> torch.Tens
 # ----------------------------------------------------------------------------- attention
 def qk_norm_rope_kv_write(q, k, v, positions, rope_cache, rotary_dim, k_cache, v_cache, slot_mapping,
                           k_scale=1.0, v_scale=1.0, q_norm_w=None, k_norm_w=None, eps=1e-6, norm_plus_one=False):
-    if q.is_cuda:
+    if on_gpu(q):
         return cuda_ops().qk_norm_rope_kv_write(q, k, v, positions, rope_cache, rotary_dim, k_cache, v_cache,
                                                 slot_mapping, k_scale, v_scale, q_norm_w, k_norm_w, eps, norm_plus_one)
     return ref.qk_norm_rope_kv_write(q, k, v, positions, rope_cache, rotary_dim, k_cache, v_cache, slot_mapping,
@@ -167,7 +173,7 @@ def qk_norm_rope_kv_write(q, k, v, positions, rope_cache, rotary_dim, k_cache, v
 
 def paged_attention(q, k_cache, v_cache, batch, scale, k_scale=1.0, v_scale=1.0, sliding_window=None) -> torch.Tensor:
     """Attention of the step's query rows over the paged cache. ``batch`` is a ``ForwardBatch``."""
-    if q.is_cuda:
+    if on_gpu(q):
         return cuda_ops().paged_attention(q, k_cache, v_cache, batch, scale, k_scale, v_scale, sliding_window)
     return ref.paged_attention(q, k_cache, v_cache, batch.block_tables, batch.seq_lens, batch.query_start_loc,
                                scale, k_scale, v_scale, sliding_window)
@@ -175,19 +181,19 @@ def paged_attention(q, k_cache, v_cache, batch, scale, k_scale=1.0, v_scale=1.0,
 
 # ----------------------------------------------------------------------------- MoE
 def moe_route(logits, top_k, norm_topk, scoring="softmax"):
-    if logits.is_cuda:
+    if on_gpu(logits):
         return cuda_ops().moe_route(logits, top_k, norm_topk, scoring)
     return ref.moe_route(logits, top_k, norm_topk, scoring)
 
 
 # ----------------------------------------------------------------------------- sampling
 def argmax(logits: torch.Tensor) -> torch.Tensor:
-    if logits.is_cuda:
+    if on_gpu(logits):
         return cuda_ops().argmax(logits)
     return ref.argmax_first(logits)
 
 
 def sample(logits, temperature, top_k, top_p, min_p, uniform):
-    if logits.is_cuda:
+    if on_gpu(logits):
         return cuda_ops().sample(logits, temperature, top_k, top_p, min_p, uniform)
     return ref.sample(logits, temperature, top_k, top_p, min_p, uniform)

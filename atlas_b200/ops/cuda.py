@@ -40,7 +40,7 @@ def load() -> None:
     lib.atlas_read_status.restype = C.c_ulonglong
     lib.atlas_gemm.argtypes = [_i, _vp, _vp, _vp, _vp, _ll, _ll, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _vp, _i, _vp, _vp]
     lib.atlas_rmsnorm.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _ll, _i, _i, _f, _i, _vp]
-    lib.atlas_silu_mul.argtypes = [_vp, _ll, _i, _i, _vp, _ll, _vp, _ll, _vp, _ll, _vp]
+    lib.atlas_silu_mul.argtypes = [_vp, _ll, _i, _i, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp]
     lib.atlas_quant_fp8.argtypes = [_vp, _ll, _i, _i, _vp, _ll, _vp, _ll, _vp]
     lib.atlas_rope_kv_write.argtypes = [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                                         _i, _i, _i, _i, _f, _f, _f, _vp]
@@ -150,7 +150,7 @@ def rmsnorm(x, w, eps, residual=None, plus_one=False, quant=False):
     return y, res_out
 
 
-def silu_mul(gate_up: torch.Tensor, quant=False):
+def silu_mul(gate_up: torch.Tensor, quant=False, live_tiles: Optional[torch.Tensor] = None):
     assert gate_up.dtype == torch.bfloat16 and gate_up.stride(1) == 1
     T, I2 = gate_up.shape
     I = I2 // 2
@@ -159,10 +159,10 @@ def silu_mul(gate_up: torch.Tensor, quant=False):
         q = torch.empty(T, I, dtype=FP8, device=gate_up.device)
         s = _scale_buf(T, I // 128, gate_up.device)
         _check(lib().atlas_silu_mul(gate_up.data_ptr(), gate_up.stride(0), T, I, None, 0, q.data_ptr(), I, s.data_ptr(),
-                                    s.stride(1), _stream()), "silu_mul")
+                                    s.stride(1), _ptr(live_tiles), _stream()), "silu_mul")
         return q, s
     y = torch.empty(T, I, dtype=gate_up.dtype, device=gate_up.device)
-    _check(lib().atlas_silu_mul(gate_up.data_ptr(), gate_up.stride(0), T, I, y.data_ptr(), I, None, 0, None, 0, _stream()),
+    _check(lib().atlas_silu_mul(gate_up.data_ptr(), gate_up.stride(0), T, I, y.data_ptr(), I, None, 0, None, 0, _ptr(live_tiles), _stream()),
            "silu_mul")
     return y
 

@@ -1,32 +1,147 @@
-"""Bindings of the MoE, Gated-DeltaNet and NVFP4 translation units of the kernel library."""
+"""Bindings of the MoE, Gated-DeltaNet and NVFP4 parts of the kernel library."""
 from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
 
 import torch
 
+from . import cuda as K
+
+_vp, _ll, _i, _f = C.c_void_p, C.c_longlong, C.c_int, C.c_float
+FP8 = torch.float8_e4m3fn
+
 
 def bind(lib) -> None:
-    pass
+    lib.atlas_moe_route.argtypes = [_vp, _ll, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp]
+    lib.atlas_moe_align.argtypes = [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp]
+    lib.atlas_moe_gather.argtypes = [_vp, _ll, _vp, _vp, _i, _i, _vp, _vp, _vp, _ll, _vp]
+    lib.atlas_moe_combine.argtypes = [_vp, _ll, _vp, _vp, _i, _i, _i, _vp, _ll, _vp, _ll, _vp]
+    lib.atlas_gemm_grouped.argtypes = [_i, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _i, _vp, _vp, _i, _vp, _vp]
+    for name, args in _GDN_SIGS.items():
+        if hasattr(lib, name):
+            getattr(lib, name).argtypes = args
 
 
-def _missing(name):
-    raise NotImplementedError(f"{name}: sm_100a kernel not built yet")
+_GDN_SIGS = {}
 
 
+# ----------------------------------------------------------------------------- NVFP4
 def gemm_nvfp4(x, packed, bscale, gscale, out=None):
-    _missing("gemm_nvfp4")
+    """NVFP4 weights are widened once to bf16 (exact: an E2M1 value times an e4m3 scale fits bf16's mantissa up to the
+    fp32 global scale's rounding) and cached; the product then runs on the bf16 tcgen05 GEMM."""
+    from .. import quant as Q
+    key = packed.data_ptr()
+    w = _nvfp4_cache.get(key)
+    if w is None:
+        w = Q.dequantize_nvfp4(packed, bscale, gscale).to(torch.bfloat16).contiguous()
+        _nvfp4_cache[key] = w
+    return K.gemm_bf16(x if x.dtype == torch.bfloat16 else x.bfloat16(), w, out)
 
 
+_nvfp4_cache = {}
+
+
+# ----------------------------------------------------------------------------- MoE
 def moe_route(logits, top_k, norm_topk, scoring):
-    _missing("moe_route")
+    T, E = logits.shape
+    K._dev(logits)
+    if logits.dtype not in (torch.bfloat16, torch.float32):
+        logits = logits.float()
+    w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+    ids = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
+    K._check(K.lib().atlas_moe_route(logits.data_ptr(), logits.stride(0), 1 if logits.dtype == torch.bfloat16 else 0, T, E,
+                                     top_k, 1 if norm_topk else 0, 1 if scoring == "sigmoid" else 0, w.data_ptr(),
+                                     ids.data_ptr(), K._stream()), "moe_route")
+    return w, ids
 
 
-def moe_forward(x, topk_w, topk_ids, experts, e_lo, pctx, ep_mode):
-    _missing("moe_forward")
+def _expert_stacks(experts):
+    """(kind, w13 [E*2I,H], s13, w2 [E*H,I], s2) in a layout the grouped GEMM takes."""
+    cached = getattr(experts, "_gpu_stacks", None)
+    if cached is not None:
+        return cached
+    if experts.kind == "fp8_block":
+        out = (1, experts.w13.contiguous(), experts.w13_scale.contiguous().float(), experts.w2.contiguous(),
+               experts.w2_scale.contiguous().float())
+    else:
+        w13, w2 = experts.dequantized() if experts.kind != "dense" else (experts.w13, experts.w2)
+        out = (0, w13.to(torch.bfloat16).contiguous(), None, w2.to(torch.bfloat16).contiguous(), None)
+        if experts.kind != "dense":
+            experts._deq = None        # the bf16 stacks replace the fp32 dequantised copy
+    experts._gpu_stacks = out
+    return out
 
 
+def moe_forward(x, topk_w, topk_ids, experts, e_lo, pctx, ep_mode, addend: Optional[torch.Tensor] = None):
+    """Expert-sorted grouped FFN over this rank's experts.  Pairs routed to other ranks' experts contribute nothing
+    here; with expert parallelism the partial outputs are summed across ranks."""
+    T, H = x.shape
+    k = topk_ids.shape[1]
+    d = K._dev(x)
+    dev = x.device
+    kind, w13, s13, w2, s2 = _expert_stacks(experts)
+    E = experts.num_local
+    N1, I = w13.shape[1], w2.shape[2]
+    max_rows = ((T * k + E * 127 + 127) // 128) * 128
+    max_rows = min(max_rows, ((T * k + 127) // 128 + E) * 128)
+    lib, st, sms, status = K.lib(), K._stream(), K._num_sms[d], K._status_ptr[d]
+    slot_of = torch.empty(T * k, dtype=torch.int32, device=dev)
+    row_token = torch.empty(max_rows, dtype=torch.int32, device=dev)
+    tile_expert = torch.empty(max_rows // 128, dtype=torch.int32, device=dev)
+    num_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+    K._check(lib.atlas_moe_align(topk_ids.data_ptr(), T, k, e_lo, E, slot_of.data_ptr(), row_token.data_ptr(),
+                                 tile_expert.data_ptr(), num_tiles.data_ptr(), max_rows, st), "moe_align")
+
+    def bn_for(n):
+        return 128 if n % 128 == 0 else 64
+
+    if kind == 1:
+        xq = torch.empty(max_rows, H, dtype=FP8, device=dev)
+        xs = torch.empty(H // 128, max_rows, dtype=torch.float32, device=dev)
+        K._check(lib.atlas_moe_gather(x.data_ptr(), x.stride(0), row_token.data_ptr(), num_tiles.data_ptr(), max_rows, H,
+                                      None, xq.data_ptr(), xs.data_ptr(), max_rows, st), "moe_gather")
+        a1, a1s = xq, xs
+    else:
+        xp = torch.empty(max_rows, H, dtype=torch.bfloat16, device=dev)
+        K._check(lib.atlas_moe_gather(x.data_ptr(), x.stride(0), row_token.data_ptr(), num_tiles.data_ptr(), max_rows, H,
+                                      xp.data_ptr(), None, None, 0, st), "moe_gather")
+        a1, a1s = xp, None
+    h1 = torch.empty(max_rows, 2 * I, dtype=torch.bfloat16, device=dev)
+    K._check(lib.atlas_gemm_grouped(kind, a1.data_ptr(), w13.data_ptr(), h1.data_ptr(), K._ptr(a1s), max_rows, K._ptr(s13),
+                                    max_rows, 2 * I, H, E, H, H, 2 * I, bn_for(2 * I), tile_expert.data_ptr(),
+                                    num_tiles.data_ptr(), sms, status, st), "moe_gemm1")
+    if kind == 1:
+        aq = torch.empty(max_rows, I, dtype=FP8, device=dev)
+        asc = torch.empty(I // 128, max_rows, dtype=torch.float32, device=dev)
+        K._check(lib.atlas_silu_mul(h1.data_ptr(), 2 * I, max_rows, I, None, 0, aq.data_ptr(), I, asc.data_ptr(), max_rows,
+                                    num_tiles.data_ptr(), st), "moe_silu")
+        a2, a2s = aq, asc
+    else:
+        act = torch.empty(max_rows, I, dtype=torch.bfloat16, device=dev)
+        K._check(lib.atlas_silu_mul(h1.data_ptr(), 2 * I, max_rows, I, act.data_ptr(), I, None, 0, None, 0,
+                                    num_tiles.data_ptr(), st), "moe_silu")
+        a2, a2s = act, None
+    y = torch.empty(max_rows, H, dtype=torch.bfloat16, device=dev)
+    K._check(lib.atlas_gemm_grouped(kind, a2.data_ptr(), w2.data_ptr(), y.data_ptr(), K._ptr(a2s), max_rows, K._ptr(s2),
+                                    max_rows, H, I, E, I, I, H, bn_for(H), tile_expert.data_ptr(), num_tiles.data_ptr(),
+                                    sms, status, st), "moe_gemm2")
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    K._check(lib.atlas_moe_combine(y.data_ptr(), H, slot_of.data_ptr(), topk_w.data_ptr(), T, k, H, K._ptr(addend),
+                                   addend.stride(0) if addend is not None else 0, out.data_ptr(), H, st), "moe_combine")
+    if pctx is not None and pctx.ep_size > 1:
+        comm = pctx.ep_comm if pctx.ep_comm is not None else pctx.comm
+        if comm is not None:
+            out = comm.all_reduce(out)
+    return out
+
+
+# ----------------------------------------------------------------------------- GDN (bound when gdn.cu is present)
 def gdn_forward(layer, mixed, a, b, batch, state, commit):
-    _missing("gdn_forward")
+    from . import cuda_gdn
+    return cuda_gdn.gdn_forward(layer, mixed, a, b, batch, state, commit)
 
 
 def gdn_commit(layer, mixed, a, b, qlens, slots, has_state, state, num_accepted_rows):
-    _missing("gdn_commit")
+    from . import cuda_gdn
+    return cuda_gdn.gdn_commit(layer, mixed, a, b, qlens, slots, has_state, state, num_accepted_rows)
