@@ -118,6 +118,15 @@ ATLAS_DEVICE void tma_load_3d(void* smem_dst, const CUtensorMap* desc, uint64_t*
       "r"(c2)
       : "memory");
 }
+// L2 prefetch of a tile (no shared memory, no completion tracking): pulls HBM data towards L2 ahead of the load.
+ATLAS_DEVICE void tma_prefetch_l2_2d(const CUtensorMap* desc, int32_t c0, int32_t c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];\n" ::"l"(reinterpret_cast<uint64_t>(desc)),
+               "r"(c0), "r"(c1)
+               : "memory");
+}
+ATLAS_DEVICE void bulk_prefetch_l2(const void* gptr, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(reinterpret_cast<uint64_t>(gptr)), "r"(bytes) : "memory");
+}
 // 2-D tiled store shared -> global (bulk async group).
 ATLAS_DEVICE void tma_store_2d(const CUtensorMap* desc, const void* smem_src, int32_t c0, int32_t c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];\n" ::"l"(
