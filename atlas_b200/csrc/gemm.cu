@@ -60,6 +60,14 @@ struct GemmParams {
   int vec_ok;               // 16-byte stores into C are legal
   // grouped (MoE) mode: rows are expert-sorted and every expert's segment is padded to a multiple of 128 rows, so
   // m-tile i covers rows [128 i, 128 i + 128) and belongs to expert tile_expert[i]; B is the stack [E * expert_n, K].
+  // fused all-reduce (row-parallel GEMM): peers' symmetric areas, see the FUSE_AR path of the kernel
+  uint8_t* ar_data[8];
+  uint32_t* ar_flags[8];
+  unsigned int* ar_state;       // [0] epoch of the last finished call, [1] CTAs finished in this call
+  long long ar_max_cycles;
+  size_t ar_part_src_stride;    // bytes between two source ranks' partial regions
+  size_t ar_result_off;         // byte offset of the [M, N] bf16 result inside the area
+  int ar_rank, ar_world, ar_max_tiles;
   const int* tile_expert;       // nullptr = plain GEMM
   const int* num_m_tiles_ptr;   // device-side tile count (the host cannot know it)
   int expert_n;                 // output features per expert
@@ -73,7 +81,32 @@ ATLAS_DEVICE void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uin
                : "memory");
 }
 
-template <int BLOCK_N, bool FP8>
+ATLAS_DEVICE void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
+ATLAS_DEVICE uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+ATLAS_DEVICE bool wait_flag_eq(const uint32_t* p, uint32_t want, status_t* status, uint32_t site, long long max_cycles) {
+  const long long t0 = clock64();
+  while (ld_acquire_sys_u32(p) != want) {
+    if (clock64() - t0 > max_cycles) { report_status(status, kFlagTimeout, site); return false; }
+    __nanosleep(32);
+  }
+  return true;
+}
+
+// FUSE_AR: the GEMM is one rank's share of a row-parallel (K-sharded) projection.  Tile t belongs to rank t % world.
+//   GEMM phase   the epilogue stores its bf16 partial tile into the OWNER's partial region [this rank][t / world]
+//                (peer stores over NVLink) and raises part_flag[t][this rank] at the owner.
+//   reduce phase for each tile it owns a rank waits for all ranks' flags, sums the partials in rank order and stores
+//                the finished tile into EVERY rank's result area, then raises final_flag[t] everywhere.
+//   drain        a rank leaves the kernel once it has seen final_flag of every tile, so the next kernel in the stream
+//                finds the whole [M, N] result in its own memory.
+// Transfers therefore overlap the math tile by tile; flags carry the call's epoch, so nothing is ever reset.
+template <int BLOCK_N, bool FP8, bool FUSE_AR = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmParams p) {
@@ -128,6 +161,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const int m_tiles = p.tile_expert ? *p.num_m_tiles_ptr : p.m_tiles;
   const int total_items = m_tiles * p.n_tiles * p.splits;
   const int M_rows = p.tile_expert ? m_tiles * kBlockM : p.M;
+  const uint32_t ar_epoch = FUSE_AR ? p.ar_state[0] + 1u : 0u;
+  uint32_t* const part_flags = FUSE_AR ? p.ar_flags[p.ar_rank] : nullptr;                       // [tile][src]
+  (void)part_flags;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -340,7 +376,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
       }
-      if (do_store && m < M_rows) {
+      if (FUSE_AR) {
+        const int tile_id = n_tile * m_tiles + m_tile;
+        const int owner = tile_id % p.ar_world;
+        if (ok && m < M_rows) {
+          uint8_t* tile_base = p.ar_data[owner] + (size_t)p.ar_rank * p.ar_part_src_stride +
+                               (size_t)(tile_id / p.ar_world) * (kBlockM * BLOCK_N * 2);
+          uint4* dst = reinterpret_cast<uint4*>(tile_base + ((size_t)row_in_tile * BLOCK_N + half * HALF) * 2);
+#pragma unroll
+          for (int j = 0; j < HALF; j += 8) {
+            uint4 v;
+            v.x = pack_bf16x2(acc[j + 0], acc[j + 1]);
+            v.y = pack_bf16x2(acc[j + 2], acc[j + 3]);
+            v.z = pack_bf16x2(acc[j + 4], acc[j + 5]);
+            v.w = pack_bf16x2(acc[j + 6], acc[j + 7]);
+            dst[j / 8] = v;
+          }
+        }
+        __threadfence_system();
+        asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
+        if (epi_tid == 0)
+          st_release_sys_u32(p.ar_flags[owner] + (size_t)tile_id * 8 + p.ar_rank, ar_epoch);
+      } else if (do_store && m < M_rows) {
         __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * p.ldc;
 #pragma unroll
         for (int j = 0; j < HALF; j += 8) {
@@ -357,6 +414,64 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             for (int i = 0; i < 8; ++i)
               if (n + i < p.N) crow[n + i] = __float2bfloat16_rn(acc[j + i]);
           }
+        }
+      }
+    }
+    if (FUSE_AR) {
+      const int n_tiles_all = m_tiles * p.n_tiles;
+      uint32_t* my_flags = p.ar_flags[p.ar_rank];
+      uint32_t* final_base_off = nullptr;
+      (void)final_base_off;
+      const size_t final_off = (size_t)p.ar_max_tiles * 8;          // final flags follow the [tile][src] flags
+      constexpr int kVecPerRow = BLOCK_N / 8;
+      // ---- reduce phase: owned tiles rank + world * j, shared round-robin among this rank's CTAs
+      for (int j = blockIdx.x; p.ar_rank + p.ar_world * j < n_tiles_all; j += gridDim.x) {
+        const int tile_id = p.ar_rank + p.ar_world * j;
+        if (epi_tid < p.ar_world) {
+          if (!wait_flag_eq(my_flags + (size_t)tile_id * 8 + epi_tid, ar_epoch, p.status, 0x600, p.ar_max_cycles))
+            *abort_flag = 1u;
+        }
+        asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
+        const bool good = *abort_flag == 0u;
+        const int m0 = (tile_id % m_tiles) * kBlockM, n0 = (tile_id / m_tiles) * BLOCK_N;
+        if (good) {
+          for (int v = epi_tid; v < kBlockM * kVecPerRow; v += 32 * kEpiWarps) {
+            const int r = v / kVecPerRow, c8 = v % kVecPerRow;
+            const int gm = m0 + r, gn = n0 + c8 * 8;
+            if (gm >= M_rows || gn >= p.N) continue;
+            float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int src = 0; src < p.ar_world; ++src) {      // fixed order: identical bits on every rank
+              const uint4 raw = *reinterpret_cast<const uint4*>(
+                  p.ar_data[p.ar_rank] + (size_t)src * p.ar_part_src_stride + (size_t)j * (kBlockM * BLOCK_N * 2) +
+                  ((size_t)r * BLOCK_N + c8 * 8) * 2);
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); sum[2 * i] += f.x; sum[2 * i + 1] += f.y; }
+            }
+            uint4 o;
+            o.x = pack_bf16x2(sum[0], sum[1]); o.y = pack_bf16x2(sum[2], sum[3]);
+            o.z = pack_bf16x2(sum[4], sum[5]); o.w = pack_bf16x2(sum[6], sum[7]);
+            for (int dst = 0; dst < p.ar_world; ++dst)
+              *reinterpret_cast<uint4*>(p.ar_data[dst] + p.ar_result_off + ((size_t)gm * p.N + gn) * 2) = o;
+          }
+        }
+        __threadfence_system();
+        asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
+        if (epi_tid < p.ar_world) st_release_sys_u32(p.ar_flags[epi_tid] + final_off + tile_id, ar_epoch);
+      }
+      // ---- drain: see every tile's final flag before leaving
+      for (int t = blockIdx.x * (32 * kEpiWarps) + epi_tid; t < n_tiles_all; t += gridDim.x * (32 * kEpiWarps)) {
+        if (*abort_flag) break;
+        if (!wait_flag_eq(my_flags + final_off + t, ar_epoch, p.status, 0x601, p.ar_max_cycles)) *abort_flag = 1u;
+      }
+      asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
+      if (epi_tid == 0) {
+        __threadfence();
+        const unsigned int done = atomicAdd(&p.ar_state[1], 1u);
+        if (done == gridDim.x - 1) {
+          p.ar_state[1] = 0;
+          __threadfence();
+          p.ar_state[0] = ar_epoch;
         }
       }
     }
@@ -431,11 +546,11 @@ static int make_tmap_kmajor(CUtensorMap* out, const void* ptr, uint64_t rows, ui
   return 0;
 }
 
-template <int BLOCK_N, bool FP8>
+template <int BLOCK_N, bool FP8, bool FUSE_AR = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
   using Cfg = GemmCfg<BLOCK_N>;
   static bool attr_done = false;
-  auto kern = gemm_tcgen05_kernel<BLOCK_N, FP8>;
+  auto kern = gemm_tcgen05_kernel<BLOCK_N, FP8, FUSE_AR>;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return -20;
@@ -473,6 +588,7 @@ extern "C" int atlas_gemm(int kind, const void* A, const void* B, void* C, const
   p.C = C; p.a_scale = a_scale; p.b_scale = b_scale; p.workspace = workspace; p.counters = counters;
   p.status = status; p.ldc = ldc; p.sa_k = sa_k; p.M = M; p.N = N; p.K = K;
   p.tile_expert = nullptr; p.num_m_tiles_ptr = nullptr; p.expert_n = 0; p.b_scale_expert_stride = 0;
+  p.ar_state = nullptr; p.ar_world = 1; p.ar_rank = 0;
   p.k_blocks = (K + elems_per_row - 1) / elems_per_row;
   if (splits < 1) splits = 1;
   if (splits > p.k_blocks) splits = p.k_blocks;
@@ -532,6 +648,7 @@ extern "C" int atlas_gemm_grouped(int kind, const void* A, const void* B, void* 
   p.b_scale_ld = p.k_blocks;
   p.vec_ok = ((ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
   p.tile_expert = tile_expert; p.num_m_tiles_ptr = num_m_tiles; p.expert_n = N;
+  p.ar_state = nullptr; p.ar_world = 1; p.ar_rank = 0;
   p.b_scale_expert_stride = (long long)((N + 127) / 128) * p.k_blocks;
   if (kind == 1) {
     if ((sa_k % 4) || sa_k < max_rows || (reinterpret_cast<uintptr_t>(a_scale) & 15)) return -6;
@@ -548,4 +665,63 @@ extern "C" int atlas_gemm_grouped(int kind, const void* A, const void* B, void* 
   if (block_n == 64) return launch_gemm<64, false>(ta, tb, p, grid, st);
   if (block_n == 128) return launch_gemm<128, false>(ta, tb, p, grid, st);
   return launch_gemm<256, false>(ta, tb, p, grid, st);
+}
+
+// Row-parallel GEMM fused with its all-reduce.  Every rank calls this with its K-shard of A and B; the summed [M, N]
+// bf16 result appears at `result_off` inside every rank's fused area (`data[rank] + result_off`, row-major, ld = N).
+// Area layout: [world partial regions of part_src_stride bytes][result M*N*2 bytes]; flags: [max_tiles][8] partial
+// flags followed by [max_tiles] final flags (uint32).  The grid is the same on every rank by construction.
+extern "C" int atlas_gemm_allreduce(int kind, const void* A, const void* B, const float* a_scale, long long sa_k,
+                                    const float* b_scale, int b_scale_ld, int M, int N, int K, long long lda,
+                                    long long ldb, int block_n, void* const* data, void* const* flags, int rank,
+                                    int world, unsigned int* state, size_t area_bytes, int max_tiles, size_t* result_off_out,
+                                    int num_sms, long long max_cycles, unsigned long long* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const uint32_t esize = kind == 1 ? 1 : 2;
+  const int elems_per_row = 128 / esize;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -1;
+  if ((lda * esize) % 16 || (ldb * esize) % 16) return -2;
+  if (kind == 1 && (K % 128)) return -3;
+  if (block_n != 64 && block_n != 128) return -4;
+  if (N % 8 || world < 1 || world > 8) return -5;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_kmajor(&ta, A, M, K, lda, kBlockM, esize);
+  if (rc) return rc;
+  rc = make_tmap_kmajor(&tb, B, N, K, ldb, block_n, esize);
+  if (rc) return rc;
+  GemmParams p;
+  p.C = nullptr; p.a_scale = a_scale; p.b_scale = b_scale; p.workspace = nullptr; p.counters = nullptr;
+  p.status = status; p.ldc = N; p.sa_k = sa_k; p.M = M; p.N = N; p.K = K;
+  p.k_blocks = (K + elems_per_row - 1) / elems_per_row;
+  p.splits = 1; p.kb_per_split = p.k_blocks;
+  p.m_tiles = (M + kBlockM - 1) / kBlockM;
+  p.n_tiles = (N + block_n - 1) / block_n;
+  p.b_scale_ld = b_scale_ld;
+  p.vec_ok = 1;
+  p.tile_expert = nullptr; p.num_m_tiles_ptr = nullptr; p.expert_n = 0; p.b_scale_expert_stride = 0;
+  if (kind == 1) {
+    if ((sa_k % 4) || sa_k < (long long)p.m_tiles * kBlockM || (reinterpret_cast<uintptr_t>(a_scale) & 15)) return -6;
+    if (p.kb_per_split > 512) return -8;
+  }
+  const int tiles = p.m_tiles * p.n_tiles;
+  if (tiles > max_tiles) return -11;
+  const size_t tile_bytes = (size_t)kBlockM * block_n * 2;
+  p.ar_part_src_stride = (size_t)((tiles + world - 1) / world) * tile_bytes;
+  p.ar_result_off = ((size_t)world * p.ar_part_src_stride + 255) & ~(size_t)255;
+  if (p.ar_result_off + (size_t)M * N * 2 > area_bytes) return -12;
+  for (int i = 0; i < 8; ++i) {
+    p.ar_data[i] = i < world ? reinterpret_cast<uint8_t*>(data[i]) : nullptr;
+    p.ar_flags[i] = i < world ? reinterpret_cast<uint32_t*>(flags[i]) : nullptr;
+  }
+  p.ar_state = state; p.ar_rank = rank; p.ar_world = world; p.ar_max_tiles = max_tiles;
+  p.ar_max_cycles = max_cycles > 0 ? max_cycles : 2000ll * 1000ll * 1000ll;
+  if (result_off_out) *result_off_out = p.ar_result_off;
+  int grid = tiles < num_sms ? tiles : num_sms;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (kind == 1) {
+    if (block_n == 64) return launch_gemm<64, true, true>(ta, tb, p, grid, st);
+    return launch_gemm<128, true, true>(ta, tb, p, grid, st);
+  }
+  if (block_n == 64) return launch_gemm<64, false, true>(ta, tb, p, grid, st);
+  return launch_gemm<128, false, true>(ta, tb, p, grid, st);
 }

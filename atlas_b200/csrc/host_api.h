@@ -2,6 +2,7 @@
 // element strides and a CUDA stream handle, launches asynchronously and returns 0 or a negative error code.
 // The Python binding (atlas_b200/ops/cuda.py) calls these through ctypes.
 #pragma once
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -62,6 +63,19 @@ int atlas_gdn_recurrent(const void* y, long long ldy, const void* a, long long l
                         const int* query_start_loc, const int* state_slots, const unsigned char* has_state,
                         const int* limit, const int* snap_rows, const int* snap_slots, int num_snaps_per_seq, int B,
                         int Hk, int Hv, int Dk, int Dv, int commit, void* stream);
+
+// ---- peer-memory collectives (comm.cu)
+int atlas_symm_alloc(size_t bytes, void** ptr);
+int atlas_symm_free(void* ptr);
+int atlas_ipc_export(void* ptr, void* handle64);
+int atlas_ipc_open(const void* handle64, void** ptr);
+int atlas_ipc_close(void* ptr);
+int atlas_allreduce_bf16(int kind, void* const* data, void* const* flags, int rank, int world, const void* in, void* out,
+                         size_t n_bytes, size_t slot_bytes, unsigned int* state, int blocks, unsigned long long* status,
+                         long long max_cycles, void* stream);
+int atlas_alltoall_rows(void* const* data, void* const* flags, int rank, int world, const void* in, const int* send_off,
+                        void* out, int* recv_off, int row_bytes, int region_rows, size_t slot_bytes, unsigned int* state,
+                        int blocks, unsigned long long* status, long long max_cycles, void* stream);
 
 // ---- attention (attention.cu)
 int atlas_attn_decode(const void* q, long long ldq, void* out, long long ldo, const void* k_cache, const void* v_cache,

@@ -93,5 +93,4 @@ class Attention:
         if self.gated:
             gate = qkv[:, nq + 2 * nkv:]
             out = (out.float() * torch.sigmoid(gate.float())).to(out.dtype)
-        y = ops.linear(out, self.o)
-        return self.pctx.all_reduce(y)
+        return self.pctx.row_parallel_linear(out, self.o)

@@ -31,6 +31,19 @@ class ParallelCtx:
             return self.comm.all_reduce(t)
         return t
 
+    def row_parallel_linear(self, act, w) -> torch.Tensor:
+        """Row-parallel projection: GEMM on this rank's K-shard, summed over the TP group.  With a peer-memory
+        backend the reduction runs inside the GEMM kernel; otherwise GEMM then all-reduce."""
+        from .. import ops
+        if self.tp_size > 1 and self.comm is not None and hasattr(self.comm, "gemm_allreduce"):
+            a = act if isinstance(act, ops.Act) else ops.Act(x=act)
+            probe = a.x if a.x is not None else a.q
+            if ops.on_gpu(probe):
+                y = self.comm.gemm_allreduce(a, w)
+                if y is not None:
+                    return y
+        return self.all_reduce(ops.linear(act, w))
+
     def ep_all_reduce(self, t: torch.Tensor) -> torch.Tensor:
         c = self.ep_comm if self.ep_comm is not None else self.comm
         if self.ep_size > 1 and c is not None:

@@ -107,8 +107,7 @@ class GatedDeltaNet:
                               self.cfg.rms_norm_eps) if not ops.on_gpu(o) else \
             ops.cuda_ops().gated_rmsnorm(o.view(T, self.hv, self.dv), z.reshape(T, self.hv, self.dv), self.norm_w,
                                          self.cfg.rms_norm_eps)
-        out = ops.linear(y.reshape(T, self.vd), self.out_proj)
-        return self.pctx.all_reduce(out)
+        return self.pctx.row_parallel_linear(y.reshape(T, self.vd), self.out_proj)
 
     def _forward_ref(self, mixed, a, b, qlens: List[int], slots: List[int], has_state: List[bool], state: dict,
                      commit: bool, limit: Optional[List[int]] = None, snapshot_plan: Optional[dict] = None) -> torch.Tensor:

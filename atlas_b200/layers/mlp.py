@@ -40,7 +40,6 @@ class DenseMLP:
     def forward(self, act: Act, reduce: bool = True) -> torch.Tensor:
         gu = ops.linear(act, self.gate_up)
         a = ops.silu_mul_act(gu, want_fp8=self.down.kind == "fp8_block")
-        y = ops.linear(a, self.down)
         if self.shard and reduce:
-            y = self.pctx.all_reduce(y)
-        return y
+            return self.pctx.row_parallel_linear(a, self.down)
+        return ops.linear(a, self.down)

@@ -1,0 +1,164 @@
+"""Multi-GPU self-test and collective benchmark, run as one process per GPU:
+
+    python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 --master-port 29541 \
+        -m atlas_b200.parallel.selftest [--bench] [--engine]
+
+Checks (each against NCCL / a single-rank computation): peer-memory all-reduce (one-shot and two-shot), all-to-all of
+rows, the fused row-parallel GEMM + all-reduce (bf16 and FP8 block-scaled), and optionally a tensor-parallel engine run.
+``--bench`` times all-reduce over message sizes with CUDA events (max over ranks) against NCCL.
+Rank 0 prints one JSON line per check.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import torch
+
+
+def _max_over_ranks(ms: float, dist, device) -> float:
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0])
+
+
+def _time(fn, iters=20, warmup=5):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    e.synchronize()
+    return s.elapsed_time(e) / iters
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--bench", action="store_true")
+    ap.add_argument("--engine", action="store_true")
+    args = ap.parse_args()
+    import torch.distributed as dist
+    from atlas_b200 import quant as Q
+    from atlas_b200.ops import Act, LinearWeight
+    from atlas_b200.ops import cuda as K
+    from atlas_b200.parallel import init_distributed
+    from atlas_b200.parallel.symm import SymmBackend
+    topo, pctx, device = init_distributed()
+    rank, world = topo.rank, topo.world_size
+    base = pctx.comm
+    symm = SymmBackend(base, device)
+    ok_all = True
+
+    def report(name, ok, **kw):
+        nonlocal ok_all
+        flag = torch.tensor([1 if ok else 0], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        ok_all &= bool(flag.item())
+        if rank == 0:
+            print(json.dumps({"check": name, "ok": bool(flag.item()), "world": world, **kw}), flush=True)
+
+    # ---- all-reduce
+    for n in (8, 4096, 128 * 4096, 3 * 1024 * 1024 + 8, 16 * 1024 * 1024):
+        torch.manual_seed(100 + rank)
+        x = torch.randn(n, device=device).bfloat16()
+        want = x.clone()
+        dist.all_reduce(want)
+        got = symm.all_reduce(x.clone())
+        torch.cuda.synchronize()
+        err = (got.float() - want.float()).abs().max().item()
+        tol = 0.05 * world
+        report(f"allreduce_p2p n={n}", err <= tol and K.check_status() == 0, max_err=err)
+    # ---- all-to-all rows
+    torch.manual_seed(7 + rank)
+    counts = [(rank + d) % 3 + 1 for d in range(world)]
+    rows = torch.randn(sum(counts), 64, device=device).bfloat16()
+    off = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=device)
+    got, recv_off = symm.all_to_all_rows(rows, off, max_recv_rows=8)
+    parts = [rows[int(off[d]):int(off[d + 1])] for d in range(world)]
+    want = torch.cat(base.all_to_all(parts))
+    torch.cuda.synchronize()
+    n_recv = int(recv_off[-1])
+    report("alltoall_rows", n_recv == want.shape[0] and torch.equal(got[:n_recv], want) and K.check_status() == 0)
+    # ---- fused GEMM + all-reduce
+    for kind in ("dense", "fp8_block"):
+        for (M, N, Kfull) in ((128, 1024, 2048), (37, 512, 1024), (1000, 2048, 4096)):
+            torch.manual_seed(11)
+            xf = (torch.randn(M, Kfull, device=device) * 0.5).bfloat16()
+            wf = torch.randn(N, Kfull, device=device) * 0.05
+            ks = Kfull // world
+            xs = xf[:, rank * ks:(rank + 1) * ks].contiguous()
+            w = LinearWeight.from_dense(wf[:, rank * ks:(rank + 1) * ks].contiguous().bfloat16() if kind == "dense"
+                                        else wf[:, rank * ks:(rank + 1) * ks].contiguous(), kind)
+            act = Act(x=xs)
+            y = symm.gemm_allreduce(act, w)
+            ref = K.gemm_bf16(xs, w.weight) if kind == "dense" else K.gemm_fp8_block(*act.fp8(), w.weight, w.scale)
+            ref = ref.float()
+            dist.all_reduce(ref)
+            torch.cuda.synchronize()
+            st = K.check_status()
+            rel = float((y.float() - ref).pow(2).mean().sqrt() / ref.pow(2).mean().sqrt())
+            report(f"gemm_allreduce {kind} M={M} N={N} K={Kfull}", y is not None and rel < 2e-2 and st == 0, rel_rms=rel, status=st)
+    if args.bench:
+        for nbytes in (8 << 10, 64 << 10, 256 << 10, 1 << 20, 4 << 20, 16 << 20, 64 << 20):
+            x = torch.randn(nbytes // 2, device=device).bfloat16()
+            t_p2p = _max_over_ranks(_time(lambda: symm.all_reduce(x)), dist, device)
+            t_nccl = _max_over_ranks(_time(lambda: dist.all_reduce(x)), dist, device)
+            if rank == 0:
+                bus = 2 * (world - 1) / world * nbytes
+                print(json.dumps({"bench": "allreduce", "bytes": nbytes, "p2p_us": round(t_p2p * 1e3, 2), "nccl_us": round(t_nccl * 1e3, 2),
+                                  "p2p_busbw_GBs": round(bus / t_p2p / 1e6, 1), "nccl_busbw_GBs": round(bus / t_nccl / 1e6, 1)}), flush=True)
+        # fused row-parallel GEMM vs GEMM + NCCL all-reduce (o_proj / down_proj shapes of an 8B model)
+        for (M, N, Kfull, tag) in ((128, 4096, 4096, "o_proj decode"), (128, 4096, 14336, "down decode"),
+                                   (8192, 4096, 4096, "o_proj prefill"), (8192, 4096, 14336, "down prefill")):
+            ks = (Kfull // world) // 128 * 128
+            xs = torch.randn(M, ks, device=device).bfloat16()
+            w = LinearWeight.from_dense(torch.randn(N, ks, device=device) * 0.05, "fp8_block")
+            act = Act(x=xs)
+            act.fp8()
+            t_f = _max_over_ranks(_time(lambda: symm.gemm_allreduce(act, w), iters=10), dist, device)
+
+            def unfused():
+                y = K.gemm_fp8_block(act.q, act.s, w.weight, w.scale)
+                dist.all_reduce(y)
+            t_u = _max_over_ranks(_time(unfused, iters=10), dist, device)
+            t_g = _max_over_ranks(_time(lambda: K.gemm_fp8_block(act.q, act.s, w.weight, w.scale), iters=10), dist, device)
+            if rank == 0:
+                flops = 2.0 * M * N * ks
+                nv_bytes = 2.0 * (world - 1) / world * M * N * 2
+                roof_us = max(flops / 1640.6e12, nv_bytes / 770e9) * 1e6
+                print(json.dumps({"bench": "gemm_allreduce", "shape": tag, "M": M, "N": N, "K_per_rank": ks,
+                                  "fused_us": round(t_f * 1e3, 1), "gemm_plus_nccl_us": round(t_u * 1e3, 1),
+                                  "gemm_only_us": round(t_g * 1e3, 1), "roofline_us": round(roof_us, 1),
+                                  "frac_of_roofline": round(roof_us / (t_f * 1e3), 3)}), flush=True)
+    if args.engine:
+        from atlas_b200.config import EngineConfig, ModelConfig, QuantConfig
+        from atlas_b200.engine import LLMEngine
+        from atlas_b200.layers import ParallelCtx
+        from atlas_b200.models import build_model
+        from atlas_b200.sampling import SamplingParams
+        cfg = ModelConfig(model_type="llama", family="dense", vocab_size=4096, hidden_size=1024, intermediate_size=2048,
+                          num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=8, head_dim=128, rope_theta=5e5,
+                          max_position_embeddings=2048, quant=QuantConfig(method="fp8_block", kv_cache_dtype="fp8"))
+        g = torch.Generator().manual_seed(5)
+        prompts = [torch.randint(0, 4096, (40 + 3 * i,), generator=g).tolist() for i in range(4)]
+        outs = {}
+        for name, comm in (("nccl", base), ("p2p", symm)):
+            p2 = ParallelCtx(topo.tp_rank, topo.tp_size, 0, 1, comm, None)
+            model = build_model(cfg, p2, device=device).init_random(0)
+            eng = LLMEngine(model, EngineConfig(num_kv_blocks=128, max_num_seqs=8, max_seq_len=512, use_cuda_graphs=(name == "p2p")))
+            outs[name] = [o.output_tokens for o in eng.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))]
+            torch.cuda.synchronize()
+        same = sum(a == b for a, b in zip(outs["nccl"], outs["p2p"]))
+        report("engine tp nccl vs p2p", same >= 3 and K.check_status() == 0, identical=same, fused_calls=symm.calls["gemm_allreduce"])
+    dist.barrier()
+    symm.close()
+    dist.destroy_process_group()
+    return 0 if ok_all else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())
