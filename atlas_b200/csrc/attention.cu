@@ -19,6 +19,7 @@
 // Reference ops replaced: kernels/gb10/common/paged_decode_attn*.cu (SIMT), inferspark_prefill_paged_fp8.cu.
 #include "common.cuh"
 #include "host_api.h"
+#include "no_alloc_api.h"
 
 namespace atlas {
 
@@ -696,4 +697,46 @@ extern "C" int atlas_attn_prefill(const void* q, long long ldq, void* out, long 
   if (D == 64) return launch_prefill<64>(p, st);
   if (D == 128) return launch_prefill<128>(p, st);
   return launch_prefill<256>(p, st);
+}
+
+// ================================================================================ allocation-free decode attention
+// Split-K scratch (per-split partial outputs and softmax statistics) for callers that may not allocate device
+// memory.  The array is part of the library image: every GPU that loads the library carries these 16 MiB until the
+// process exits.
+static __device__ __align__(256) float g_noalloc_decode_scratch[ATLAS_NOALLOC_DECODE_SCRATCH_FLOATS];
+
+// Device address of the array above for each device, resolved the first time that device is used.  (In host code the
+// array's name only stands for the symbol; the address a kernel can dereference comes from cudaGetSymbolAddress.)
+static float* g_noalloc_scratch_ptr[16] = {nullptr};
+
+extern "C" int atlas_attn_decode_noalloc(const void* q, long long ldq, void* out, long long ldo, const void* k_cache,
+                                         const void* v_cache, const int* block_tables, int bt_ld, const int* seq_lens,
+                                         const int* query_start_loc, int B, float scale, float k_scale, float v_scale,
+                                         int Hq, int Hkv, int D, int block_size, int window, int num_splits,
+                                         unsigned long long* status, void* stream) {
+  if (B <= 0) return 0;
+  if (num_splits < 1) num_splits = 1;
+  const long long need = (long long)B * Hq * num_splits * (D + 2);
+  if (need > (long long)ATLAS_NOALLOC_DECODE_SCRATCH_FLOATS) return ATLAS_NOALLOC_ERR_TOO_LARGE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return ATLAS_NOALLOC_ERR_DEVICE;
+  if (!g_noalloc_scratch_ptr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_decode_scratch) != cudaSuccess || !p) return ATLAS_NOALLOC_ERR_SYMBOL;
+    g_noalloc_scratch_ptr[dev] = reinterpret_cast<float*>(p);
+  }
+  float* part_o = g_noalloc_scratch_ptr[dev];
+  float* part_ml = part_o + (long long)B * Hq * num_splits * D;
+  AttnParams p;
+  int rc = fill_common(p, q, ldq, out, ldo, k_cache, v_cache, block_tables, bt_ld, seq_lens, query_start_loc, 0, scale,
+                       k_scale, v_scale, Hq, Hkv, D, block_size, window);
+  if (rc) return rc;
+  if (p.block_size * D * 2 > 96 * 1024) return -4;
+  if (Hq / Hkv > 8) return -5;
+  p.num_splits = num_splits;
+  p.part_o = part_o; p.part_ml = part_ml;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (D == 64) return launch_decode<64>(p, B, status, st);
+  if (D == 128) return launch_decode<128>(p, B, status, st);
+  return launch_decode<256>(p, B, status, st);
 }
