@@ -21,6 +21,8 @@ from .comm import CommBackend, CommError, TorchDistBackend
 
 _vp, _i, _ll, _sz = C.c_void_p, C.c_int, C.c_longlong, C.c_size_t
 ONESHOT_MAX_BYTES = 2 << 20
+P2P_MAX_BYTES = 4 << 20          # above this NCCL's ring/tree is faster than the two-shot kernel (measured at 2 ranks)
+FUSED_MAX_OUT_BYTES = 2 << 20    # the fused GEMM+all-reduce pays off for decode-size outputs
 
 
 class SymmBackend(CommBackend):
@@ -128,7 +130,7 @@ class SymmBackend(CommBackend):
             return self.base.all_reduce(t)
         if nbytes <= min(ONESHOT_MAX_BYTES, self.slot_bytes):
             kind = 0
-        elif 2 * nbytes <= self.slot_bytes:
+        elif 2 * nbytes <= self.slot_bytes and nbytes <= P2P_MAX_BYTES:
             kind = 1
         else:
             self.calls["fallback"] += 1
@@ -179,7 +181,7 @@ class SymmBackend(CommBackend):
             return None
         M, Kd = a.shape
         N = b.shape[0]
-        if N % 8 or a.stride(1) != 1:
+        if N % 8 or a.stride(1) != 1 or M * N * 2 > FUSED_MAX_OUT_BYTES:
             return None
         sms = K._num_sms[self.dev_index]
         bn = 128 if ((M + 127) // 128) * ((N + 127) // 128) >= sms else 64
