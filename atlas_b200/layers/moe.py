@@ -30,7 +30,7 @@ class ExpertWeights:
     """Stacked local experts. ``w13 [E,2I,H]`` (gate rows then up rows), ``w2 [E,H,I]``.
 
     kind ``dense`` keeps the model dtype; ``fp8_block`` adds ``*_scale [E, ceil(N/128), ceil(K/128)]``;
-    ``nvfp4`` stores packed nibbles ``[E,N,K/2]``, e4m3 ``*_scale [E,N,K/16]`` and fp32 ``*_gscale [E]``.
+    ``nvfp4`` stores packed nibbles ``[E,N,K/2]``, e4m3 ``*_scale [E,N,K/16]`` and fp32 ``*_gscale [E]`` (or ``[E,N]``, one per output row).
     """
     kind: str
     w13: torch.Tensor

@@ -1,0 +1,90 @@
+"""Checkpoint directory reader: safetensors shards (+index), lazy tensor access, quantised-tensor assembly.
+
+Reads go through ``safetensors.safe_open`` (mmap).  ``FastReader`` (native, ``csrc/runtime/direct_io.cpp``) is used
+for whole-shard streaming with O_DIRECT when the runtime library is built and ``ATLAS_FAST_LOAD=1``.
+
+Reference parity: ``crates/spark-runtime/src/weights/loader.rs`` (``WeightStore``), ``fast_weights/*`` (O_DIRECT
+pipelined loader), ``spark-model/src/weight_map/nvfp4_detect.rs``.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Dict, Iterable, List, Optional
+
+import torch
+
+from .qtensor import QTensor
+
+
+class Checkpoint:
+    def __init__(self, path: str):
+        self.path = path
+        self._where: Dict[str, str] = {}
+        self._open: Dict[str, object] = {}
+        idx = os.path.join(path, "model.safetensors.index.json")
+        if os.path.exists(idx):
+            with open(idx) as f:
+                self._where = dict(json.load(f)["weight_map"])
+        else:
+            from safetensors import safe_open
+            for fn in sorted(os.listdir(path)):
+                if fn.endswith(".safetensors"):
+                    with safe_open(os.path.join(path, fn), framework="pt") as f:
+                        for k in f.keys():
+                            self._where[k] = fn
+        if not self._where:
+            raise FileNotFoundError(f"no safetensors weights under {path}")
+
+    def keys(self) -> Iterable[str]:
+        return self._where.keys()
+
+    def has(self, name: str) -> bool:
+        return name in self._where
+
+    def _file(self, fn: str):
+        f = self._open.get(fn)
+        if f is None:
+            from safetensors import safe_open
+            f = safe_open(os.path.join(self.path, fn), framework="pt")
+            self._open[fn] = f
+        return f
+
+    def get(self, name: str) -> torch.Tensor:
+        return self._file(self._where[name]).get_tensor(name)
+
+    def maybe(self, name: str) -> Optional[torch.Tensor]:
+        return self.get(name) if name in self._where else None
+
+    # ------------------------------------------------------------------ quantised linear weights
+    def linear(self, prefix: str) -> QTensor:
+        """``prefix`` without ``.weight``.  Recognises FP8 block scales (``weight_scale_inv``), ModelOpt NVFP4
+        (``weight`` uint8 + ``weight_scale`` e4m3 + ``weight_scale_2``) and compressed-tensors NVFP4
+        (``weight_packed`` + ``weight_scale`` + ``weight_global_scale``)."""
+        w = self.maybe(prefix + ".weight")
+        if w is None and self.has(prefix + ".weight_packed"):
+            packed = self.get(prefix + ".weight_packed")
+            g = self.get(prefix + ".weight_global_scale").float().reshape(-1)
+            # compressed-tensors stores the reciprocal convention: value = e2m1 * scale / global
+            return QTensor("nvfp4", packed.view(torch.uint8), self.get(prefix + ".weight_scale").view(torch.float8_e4m3fn),
+                           (1.0 / g).reshape(1))
+        if w is None:
+            raise KeyError(prefix + ".weight")
+        if w.dtype == torch.float8_e4m3fn:
+            s = self.maybe(prefix + ".weight_scale_inv")
+            if s is None:
+                s = self.maybe(prefix + ".weight_scale")
+            if s is None:
+                raise KeyError(f"{prefix}: fp8 weight without a scale tensor")
+            s = s.float()
+            if s.dim() < 2:      # per-tensor scale -> broadcast to the block grid
+                n, k = w.shape
+                s = s.reshape(1, 1).expand((n + 127) // 128, (k + 127) // 128).contiguous()
+            return QTensor("fp8_block", w, s)
+        if w.dtype == torch.uint8 and self.has(prefix + ".weight_scale_2"):
+            return QTensor("nvfp4", w, self.get(prefix + ".weight_scale").view(torch.float8_e4m3fn),
+                           self.get(prefix + ".weight_scale_2").float().reshape(1))
+        return QTensor("dense", w)
+
+    def close(self) -> None:
+        self._open.clear()

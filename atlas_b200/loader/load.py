@@ -1,0 +1,188 @@
+"""HF checkpoint -> model: weight names of the supported families, fusion (QKV, gate|up, GDN in-projection
+de-interleave), tensor / expert parallel sharding and quantised-format pass-through.
+
+Sharding happens on the checkpoint tensors (quantised ones are sliced together with their scales, high-precision
+ones are sliced first and quantised afterwards when the configuration asks for it).
+
+Reference parity: ``crates/spark-model/src/weight_loader/{qwen3,qwen35,qwen35_dense,mistral}.rs``,
+``weight_map/*``, ``tp_shard.rs``, ``factory.rs:68`` (``loader_for_config``).
+"""
+from __future__ import annotations
+
+import os
+from typing import List, Optional
+
+import torch
+
+from ..config import ModelConfig
+from ..layers import ParallelCtx
+from ..layers.moe import ExpertWeights
+from ..models import DecoderLM, build_model
+from ..models.decoder import quant_kinds
+from ..ops import LinearWeight
+from .checkpoint import Checkpoint
+from .qtensor import QTensor, as_q, cat_rows, to_linear
+
+
+def load_model(path: str, pctx: Optional[ParallelCtx] = None, device="cpu", dtype: Optional[str] = None,
+               max_pos: Optional[int] = None, with_mtp: Optional[bool] = None) -> DecoderLM:
+    cfg = ModelConfig.from_pretrained(path)
+    if dtype:
+        cfg.dtype = dtype
+    model = build_model(cfg, pctx, device=device, with_mtp=with_mtp)
+    load_weights(model, Checkpoint(path))
+    model.finalize(max_pos)
+    return model
+
+
+def _vec(ck: Checkpoint, name: str, model: DecoderLM, dtype=None) -> Optional[torch.Tensor]:
+    t = ck.maybe(name)
+    return None if t is None else t.to(device=model.device, dtype=dtype or model.dtype).contiguous()
+
+
+def _lin(q: QTensor, kind: str, model: DecoderLM, bias=None) -> LinearWeight:
+    return to_linear(q.to(model.device), kind, model.dtype, bias)
+
+
+def _load_attention(ck, pre, mixer, model, kind) -> None:
+    cfg, tp, r = mixer.cfg, mixer.pctx.tp_size, mixer.pctx.tp_rank
+    d = mixer.d
+    q, k, v, o = (ck.linear(f"{pre}.{n}_proj") for n in "qkvo")
+    if mixer.gated:
+        heads = range(r * mixer.hq, (r + 1) * mixer.hq)
+        qp = cat_rows([q.rows(h * 2 * d, h * 2 * d + d) for h in heads])
+        gp = cat_rows([q.rows(h * 2 * d + d, (h + 1) * 2 * d) for h in heads])
+    else:
+        qp, gp = q.rows(r * mixer.hq * d, (r + 1) * mixer.hq * d), None
+    kv0 = ((r // mixer.kv_rep) * mixer.hkv) * d if tp > 1 else 0
+    kp, vp = k.rows(kv0, kv0 + mixer.hkv * d), v.rows(kv0, kv0 + mixer.hkv * d)
+    bias = None
+    if ck.has(f"{pre}.q_proj.bias"):
+        bq, bk, bv = (ck.get(f"{pre}.{n}_proj.bias") for n in "qkv")
+        bias = torch.cat([bq[r * mixer.hq * d:(r + 1) * mixer.hq * d], bk[kv0:kv0 + mixer.hkv * d],
+                          bv[kv0:kv0 + mixer.hkv * d]]).to(device=model.device, dtype=model.dtype)
+    parts = [qp, kp, vp] + ([gp] if gp is not None else [])
+    mixer.qkv = _lin(cat_rows(parts), kind, model, bias)
+    mixer.o = _lin(o.cols(r * mixer.hq * d, (r + 1) * mixer.hq * d), kind, model)
+    mixer.q_norm = _vec(ck, f"{pre}.q_norm.weight", model)
+    mixer.k_norm = _vec(ck, f"{pre}.k_norm.weight", model)
+
+
+def _load_mlp(ck, pre, mlp, model, kind) -> None:
+    tp, r = (mlp.pctx.tp_size, mlp.pctx.tp_rank) if mlp.shard else (1, 0)
+    g, u, dn = (ck.linear(f"{pre}.{n}_proj") for n in ("gate", "up", "down"))
+    s = mlp.inter // tp
+    mlp.gate_up = _lin(cat_rows([g.rows(r * s, (r + 1) * s), u.rows(r * s, (r + 1) * s)]), kind, model)
+    mlp.down = _lin(dn.cols(r * s, (r + 1) * s), kind, model)
+
+
+def _stack_gscale(parts: List[QTensor]) -> torch.Tensor:
+    """``[E]`` when every expert has one global scale, ``[E,N]`` when fused rows carry their own."""
+    if all(p.gscale.numel() == 1 for p in parts):
+        return torch.cat([p.gscale.float().reshape(1) for p in parts])
+    return torch.stack([p.gscale.float().reshape(-1).expand(p.weight.shape[0]) for p in parts])
+
+
+def _stack_experts(parts13: List[QTensor], parts2: List[QTensor], want_kind: str, model) -> ExpertWeights:
+    kinds = {p.kind for p in parts13 + parts2}
+    dev = model.device
+    if kinds == {"fp8_block"}:
+        return ExpertWeights("fp8_block", torch.stack([p.weight for p in parts13]).to(dev), torch.stack([p.weight for p in parts2]).to(dev),
+                             torch.stack([p.scale.float() for p in parts13]).to(dev), torch.stack([p.scale.float() for p in parts2]).to(dev))
+    if kinds == {"nvfp4"}:
+        return ExpertWeights("nvfp4", torch.stack([p.weight for p in parts13]).to(dev), torch.stack([p.weight for p in parts2]).to(dev),
+                             torch.stack([p.scale for p in parts13]).to(dev), torch.stack([p.scale for p in parts2]).to(dev),
+                             _stack_gscale(parts13).to(dev), _stack_gscale(parts2).to(dev))
+    w13 = torch.stack([p.dequant().to(model.dtype) for p in parts13]).to(dev)
+    w2 = torch.stack([p.dequant().to(model.dtype) for p in parts2]).to(dev)
+    return ExpertWeights.from_dense(w13, w2, want_kind)
+
+
+def _load_moe(ck, pre, moe, model, dense_kind, expert_kind) -> None:
+    router = ck.get(f"{pre}.gate.weight")
+    moe.router = LinearWeight("dense", router.to(device=model.device, dtype=model.dtype).contiguous())
+    p13, p2 = [], []
+    for e in range(moe.e_lo, moe.e_hi):
+        g, u, dn = (ck.linear(f"{pre}.experts.{e}.{n}_proj") for n in ("gate", "up", "down"))
+        p13.append(cat_rows([g, u]))
+        p2.append(as_q(dn))
+    moe.experts = _stack_experts(p13, p2, expert_kind, model)
+    if moe.shared is not None:
+        _load_mlp(ck, f"{pre}.shared_expert", moe.shared, model, dense_kind)
+        sg = ck.maybe(f"{pre}.shared_expert_gate.weight")
+        moe.shared_gate = None if sg is None else sg.to(device=model.device, dtype=model.dtype)
+
+
+def _load_gdn(ck, pre, mixer, model, kind) -> None:
+    """The qkvz / ba projections may be quantised; the row regrouping is done on QTensors (128-aligned segments stay
+    quantised, the tiny b/a rows fall back to high precision inside ``cat_rows`` if needed)."""
+    cfg, tp, r = mixer.cfg, mixer.pctx.tp_size, mixer.pctx.tp_rank
+    HK, HV, dk, dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, mixer.dk, mixer.dv
+    rep = HV // HK
+    qkvz, ba = ck.linear(f"{pre}.in_proj_qkvz"), ck.linear(f"{pre}.in_proj_ba")
+    grp = 2 * dk + 2 * rep * dv
+    heads = range(r * mixer.hk, (r + 1) * mixer.hk)
+    seg = lambda lo, hi: [qkvz.rows(h * grp + lo, h * grp + hi) for h in heads]
+    qs, ks = seg(0, dk), seg(dk, 2 * dk)
+    vs, zs = seg(2 * dk, 2 * dk + rep * dv), seg(2 * dk + rep * dv, grp)
+    bs = [ba.rows(h * 2 * rep, h * 2 * rep + rep) for h in heads]
+    as_ = [ba.rows(h * 2 * rep + rep, (h + 1) * 2 * rep) for h in heads]
+    main = cat_rows(qs + ks + vs + zs)
+    tail = cat_rows(bs + as_)
+    if main.kind == "fp8_block" and main.weight.shape[0] % 128 == 0 and tail.kind == "fp8_block":
+        fused = cat_rows([main, tail])
+    elif main.kind == tail.kind == "dense":
+        fused = cat_rows([main, tail])
+    else:
+        fused = QTensor("dense", torch.cat([main.dequant().float(), tail.dequant().float()], 0))
+    mixer.in_proj = _lin(fused, kind, model)
+    cw = ck.get(f"{pre}.conv1d.weight")
+    cw = cw.reshape(cw.shape[0], -1)
+    KD, VD = HK * dk, HV * dv
+    sk, sv = slice(r * mixer.kd, (r + 1) * mixer.kd), slice(r * mixer.vd, (r + 1) * mixer.vd)
+    mixer.conv_w = torch.cat([cw[:KD][sk], cw[KD:2 * KD][sk], cw[2 * KD:2 * KD + VD][sv]], 0).to(device=model.device, dtype=model.dtype).contiguous()
+    hv = slice(r * mixer.hv, (r + 1) * mixer.hv)
+    mixer.dt_bias = ck.get(f"{pre}.dt_bias")[hv].float().to(model.device).contiguous()
+    mixer.A_log = ck.get(f"{pre}.A_log")[hv].float().to(model.device).contiguous()
+    mixer.norm_w = _vec(ck, f"{pre}.norm.weight", model)
+    mixer.out_proj = _lin(ck.linear(f"{pre}.out_proj").cols(r * mixer.vd, (r + 1) * mixer.vd), kind, model)
+
+
+def _load_layer(ck, pre, layer, model, dense_kind, expert_kind) -> None:
+    layer.input_norm = _vec(ck, f"{pre}.input_layernorm.weight", model)
+    layer.post_norm = _vec(ck, f"{pre}.post_attention_layernorm.weight", model)
+    if layer.kind == "attention":
+        _load_attention(ck, f"{pre}.self_attn", layer.mixer, model, dense_kind)
+    else:
+        _load_gdn(ck, f"{pre}.linear_attn", layer.mixer, model, dense_kind)
+    if layer.is_moe:
+        _load_moe(ck, f"{pre}.mlp", layer.ffn, model, dense_kind, expert_kind)
+    else:
+        _load_mlp(ck, f"{pre}.mlp", layer.ffn, model, dense_kind)
+
+
+def load_weights(model: DecoderLM, ck: Checkpoint) -> None:
+    cfg = model.cfg
+    dense_kind, expert_kind = quant_kinds(cfg)
+    if any(k.endswith((".weight_scale_inv", ".weight_scale", ".weight_packed")) for k in ck.keys()):
+        # a pre-quantised checkpoint: what it left in high precision (its ignore list) stays in high precision
+        dense_kind = expert_kind = "dense"
+    root = "model" if any(k.startswith("model.layers.") for k in ck.keys()) else "model.language_model"
+    model.embed = ck.get(f"{root}.embed_tokens.weight").to(device=model.device, dtype=model.dtype)
+    for i, layer in enumerate(model.layers):
+        _load_layer(ck, f"{root}.layers.{i}", layer, model, dense_kind, expert_kind)
+    model.final_norm = _vec(ck, f"{root}.norm.weight", model)
+    head = ck.maybe("lm_head.weight")
+    if head is None or cfg.tie_word_embeddings:
+        head = model.embed
+    model.set_lm_head(head.to(device=model.device, dtype=model.dtype))
+    if model.mtp is not None and ck.has("mtp.fc.weight"):
+        m = model.mtp
+        m.fc = LinearWeight("dense", ck.get("mtp.fc.weight").to(device=model.device, dtype=model.dtype).contiguous())
+        m.norm_e = _vec(ck, "mtp.pre_fc_norm_embedding.weight", model)
+        m.norm_h = _vec(ck, "mtp.pre_fc_norm_hidden.weight", model)
+        m.final_norm = _vec(ck, "mtp.norm.weight", model)
+        _load_layer(ck, "mtp.layers.0", m.layer, model, dense_kind, expert_kind)
+    elif model.mtp is not None:
+        model.mtp = None          # the checkpoint ships no draft head
+    ck.close()

@@ -40,7 +40,7 @@ class LinearWeight:
 
     kind ``dense``: ``weight [N,K]`` in the model dtype.
     kind ``fp8_block``: ``weight [N,K]`` e4m3, ``scale [ceil(N/128), ceil(K/128)]`` fp32.
-    kind ``nvfp4``: ``weight [N,K/2]`` packed E2M1, ``scale [N,K/16]`` e4m3, ``gscale [1]`` fp32.
+    kind ``nvfp4``: ``weight [N,K/2]`` packed E2M1, ``scale [N,K/16]`` e4m3, ``gscale`` fp32, ``[1]`` or one per output row ``[N]``.
     """
     kind: str
     weight: torch.Tensor
@@ -83,10 +83,15 @@ class Act:
     x: Optional[torch.Tensor] = None
     q: Optional[torch.Tensor] = None
     s: Optional[torch.Tensor] = None
+    dtype: Optional[torch.dtype] = None      # dtype of the tensor the quantised form was made from
+
+    @property
+    def out_dtype(self) -> torch.dtype:
+        return self.x.dtype if self.x is not None else (self.dtype or torch.bfloat16)
 
     def plain(self) -> torch.Tensor:
         if self.x is None:
-            self.x = (self.q.float().view(self.q.shape[0], -1, 128) * self.s[..., None]).view(self.q.shape).to(torch.bfloat16)
+            self.x = (self.q.float().view(self.q.shape[0], -1, 128) * self.s[..., None]).view(self.q.shape).to(self.out_dtype)
         return self.x
 
     def fp8(self) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -115,7 +120,7 @@ def rmsnorm_act(x, w, eps, residual=None, plus_one=False, want_fp8=False) -> Tup
             q, s, r = cuda_ops().rmsnorm(x, w, eps, residual, plus_one, quant=True)
         else:
             q, s, r = ref.rmsnorm_quant_fp8(x, w, eps, residual, plus_one)
-        return Act(q=q, s=s), r
+        return Act(q=q, s=s, dtype=x.dtype), r
     y, r = rmsnorm(x, w, eps, residual, plus_one)
     return Act(x=y), r
 
@@ -127,7 +132,7 @@ def silu_mul_act(gate_up: torch.Tensor, want_fp8=False) -> Act:
             q, s = cuda_ops().silu_mul(gate_up, quant=True)
         else:
             q, s = ref.silu_mul_quant_fp8(gate_up)
-        return Act(q=q, s=s)
+        return Act(q=q, s=s, dtype=gate_up.dtype)
     if on_gpu(gate_up):
         return Act(x=cuda_ops().silu_mul(gate_up, quant=False))
     return Act(x=ref.silu_mul(gate_up))
@@ -143,7 +148,7 @@ def linear(a, w: LinearWeight, out: Optional[torch.Tensor] = None) -> torch.Tens
         if dev_cuda:
             y = cuda_ops().gemm_fp8_block(q, s, w.weight, w.scale, out=out)
         else:
-            y = Q.fp8_block_gemm_ref(q, s, w.weight, w.scale, out_dtype=torch.bfloat16)
+            y = Q.fp8_block_gemm_ref(q, s, w.weight, w.scale, out_dtype=act.out_dtype)
     elif w.kind == "nvfp4":
         x = act.plain()
         if dev_cuda:

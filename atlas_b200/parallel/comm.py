@@ -169,6 +169,29 @@ class FakeWorld:
                 del self._slots[seq_no], self._done[seq_no]
             return [vals[r] for r in range(self.world_size)]
 
+    def comm(self, rank: int) -> "FakeComm":
+        return FakeComm(self, rank)
+
+    def run(self, fn, timeout_s: float = 120.0) -> list:
+        """Run ``fn(rank)`` on one thread per rank; returns the results in rank order, re-raising the first error."""
+        out, err = [None] * self.world_size, [None] * self.world_size
+
+        def body(r):
+            try:
+                out[r] = fn(r)
+            except BaseException as e:      # noqa: BLE001 - reported to the caller below
+                err[r] = e
+
+        ts = [threading.Thread(target=body, args=(r,), daemon=True) for r in range(self.world_size)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join(timeout_s)
+        for e in err:
+            if e is not None:
+                raise e
+        return out
+
 
 class FakeComm(CommBackend):
     name = "fake"

@@ -120,7 +120,9 @@ def dequantize_nvfp4(packed: torch.Tensor, bscale: torch.Tensor, gscale: torch.T
     lo = lut[(packed & 0xF).long()]
     hi = lut[(packed >> 4).long()]
     vals = torch.stack([lo, hi], dim=-1).view(N, K)
-    s = (bscale.float() * gscale.float().reshape(-1)[0]).repeat_interleave(group, 1)
+    g = gscale.float().reshape(-1)                       # one global scale, or one per output row (fused projections)
+    g = g[0] if g.numel() == 1 else g[:, None]
+    s = (bscale.float() * g).repeat_interleave(group, 1)
     return vals * s
 
 

@@ -78,6 +78,8 @@ def main():
     ap.add_argument("--max-prefill-tokens", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (marks the result invalid)")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"],
+                    help="tensor-parallel collectives: this engine's peer-memory kernels (default) or the NCCL baseline")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -101,6 +103,11 @@ def main():
     topo, pctx, device = init_distributed(tp_size=world)
     rank = topo.rank
     from atlas_b200.ops import cuda as K
+    symm = None
+    if world > 1 and args.comm == "p2p":
+        from atlas_b200.parallel.symm import SymmBackend
+        symm = SymmBackend(pctx.comm, device)
+        pctx.comm = symm
 
     mcfg = PRESETS[args.model]()
     if args.layers:
@@ -169,7 +176,7 @@ def main():
             "data": "synthetic: uniform-random token ids, random-init N(0,0.02) weights quantized to fp8 block-scaled",
             "config": {"model": args.model + ("" if not args.layers else f"-TRUNCATED-{args.layers}L-INVALID"),
                        "global_batch": args.concurrency, "seq_len": args.isl + args.osl, "isl": args.isl, "osl": args.osl,
-                       "parallelism": f"tp{world}", "l2": "inputs larger than L2 (8 GB weights + KV stream every step)",
+                       "parallelism": f"tp{world}", "collectives": (args.comm if world > 1 else "none"), "l2": "inputs larger than L2 (8 GB weights + KV stream every step)",
                        "step": "one wave of `global_batch` concurrent requests, prefill + decode",
                        "engine_steps_per_wave": eng_steps / max(1, args.steps), "cuda_graphs": not args.no_graphs},
             "clocks": clocks,
@@ -185,6 +192,8 @@ def main():
         print(json.dumps(line))
     if world > 1:
         torch.distributed.barrier()
+        if symm is not None:
+            symm.close()
         torch.distributed.destroy_process_group()
     return 0
 

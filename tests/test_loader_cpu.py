@@ -1,0 +1,189 @@
+"""Checkpoint loader parity: a tiny random HF model saved with ``save_pretrained`` and read back through the loader
+must give the same logits as the ``transformers`` implementation (fp32, CPU), for every supported family, with and
+without tensor / expert parallel sharding, and for pre-quantised (FP8 block scale, NVFP4) checkpoints."""
+import json
+import os
+
+import pytest
+import torch
+
+from atlas_b200 import quant as Q
+from atlas_b200.config import ModelConfig
+from atlas_b200.layers import ParallelCtx
+from atlas_b200.loader import Checkpoint, QTensor, load_model
+from atlas_b200.loader.qtensor import cat_rows
+from atlas_b200.parallel.comm import FakeWorld
+
+transformers = pytest.importorskip("transformers")
+
+
+def _hf(kind: str):
+    torch.manual_seed(0)
+    common = dict(vocab_size=512, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                  head_dim=64, max_position_embeddings=256, rms_norm_eps=1e-6, tie_word_embeddings=False)
+    if kind == "llama":
+        cfg = transformers.LlamaConfig(intermediate_size=512, rope_theta=10000.0, **common)
+        m = transformers.LlamaForCausalLM(cfg)
+    elif kind == "qwen2":
+        cfg = transformers.Qwen2Config(intermediate_size=512, **{k: v for k, v in common.items() if k != "head_dim"})
+        m = transformers.Qwen2ForCausalLM(cfg)
+    elif kind == "qwen3":
+        cfg = transformers.Qwen3Config(intermediate_size=512, **common)
+        m = transformers.Qwen3ForCausalLM(cfg)
+    elif kind == "qwen3_moe":
+        cfg = transformers.Qwen3MoeConfig(intermediate_size=512, moe_intermediate_size=128, num_experts=8, num_experts_per_tok=2,
+                                          norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[], **common)
+        m = transformers.Qwen3MoeForCausalLM(cfg)
+    elif kind == "qwen3_next":
+        cfg = transformers.Qwen3NextConfig(intermediate_size=512, moe_intermediate_size=128, shared_expert_intermediate_size=128,
+                                           num_experts=8, num_experts_per_tok=2, norm_topk_prob=True, decoder_sparse_step=1,
+                                           mlp_only_layers=[], linear_num_key_heads=2, linear_num_value_heads=4,
+                                           linear_key_head_dim=64, linear_value_head_dim=64, linear_conv_kernel_dim=4,
+                                           partial_rotary_factor=0.25, layer_types=["linear_attention", "full_attention"],
+                                           **common)
+        m = transformers.Qwen3NextForCausalLM(cfg)
+    else:
+        raise ValueError(kind)
+    m = m.float().eval()
+    with torch.no_grad():                      # make norms / biases non-trivial
+        for n, p in m.named_parameters():
+            if n.endswith("norm.weight") or n.endswith("layernorm.weight"):
+                p.add_(torch.randn_like(p) * 0.1)
+            elif n.endswith(".bias"):
+                p.copy_(torch.randn_like(p) * 0.1)
+    return m
+
+
+def _save(m, path):
+    m.save_pretrained(path, safe_serialization=True)
+    return str(path)
+
+
+def _ours_logits(model, toks):
+    return model.forward_dense_reference(toks)
+
+
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "qwen3", "qwen3_moe", "qwen3_next"])
+def test_logits_match_transformers(kind, tmp_path):
+    hf = _hf(kind)
+    path = _save(hf, tmp_path)
+    toks = torch.randint(0, 512, (24,), generator=torch.Generator().manual_seed(3)).tolist()
+    with torch.no_grad():
+        want = hf(torch.tensor([toks])).logits[0]
+    model = load_model(path, dtype="float32", with_mtp=False)
+    got = _ours_logits(model, toks)
+    torch.testing.assert_close(got, want, atol=2e-4, rtol=1e-3)
+
+
+@pytest.mark.parametrize("kind", ["qwen3", "qwen3_next"])
+def test_sharded_load_matches_full(kind, tmp_path):
+    """TP=2 (dense) / TP=2+EP=2 (hybrid MoE): the ranks, run in lock-step over the in-process fake communicator,
+    reproduce the single-rank logits."""
+    hf = _hf(kind)
+    path = _save(hf, tmp_path)
+    toks = torch.randint(0, 512, (12,), generator=torch.Generator().manual_seed(4)).tolist()
+    full = _ours_logits(load_model(path, dtype="float32", with_mtp=False), toks)
+    world = FakeWorld(2, timeout_s=60.0)
+
+    def rank_fn(r):
+        comm = world.comm(r)
+        pctx = ParallelCtx(tp_rank=r, tp_size=2, ep_rank=r, ep_size=2, comm=comm, ep_comm=comm)
+        model = load_model(path, pctx, dtype="float32", with_mtp=False)
+        return _ours_logits(model, toks)
+
+    outs = world.run(rank_fn)
+    for o in outs:
+        torch.testing.assert_close(o, full, atol=2e-4, rtol=1e-3)
+
+
+def _requantise_checkpoint(src, dst, fmt):
+    """Rewrite every 2-D projection weight of a saved checkpoint in a quantised on-disk format."""
+    from safetensors.torch import load_file, save_file
+    os.makedirs(dst, exist_ok=True)
+    tensors = load_file(os.path.join(src, "model.safetensors"))
+    out = {}
+    for name, t in tensors.items():
+        is_proj = name.endswith("_proj.weight") and t.dim() == 2 and t.shape[1] % 128 == 0 and t.shape[0] % 128 == 0
+        if not is_proj:
+            out[name] = t
+            continue
+        base = name[:-len(".weight")]
+        if fmt == "fp8":
+            q, s = Q.quantize_fp8_block(t.float())
+            out[name], out[base + ".weight_scale_inv"] = q, s
+        elif fmt == "modelopt":
+            p, s, g = Q.quantize_nvfp4(t.float())
+            out[name], out[base + ".weight_scale"], out[base + ".weight_scale_2"] = p, s, g.reshape(())
+        else:   # compressed-tensors
+            p, s, g = Q.quantize_nvfp4(t.float())
+            out[base + ".weight_packed"], out[base + ".weight_scale"] = p, s
+            out[base + ".weight_global_scale"] = (1.0 / g).reshape(1)
+    save_file({k: v.contiguous() for k, v in out.items()}, os.path.join(dst, "model.safetensors"))
+    cfg = json.load(open(os.path.join(src, "config.json")))
+    if fmt == "fp8":
+        cfg["quantization_config"] = {"quant_method": "fp8", "fmt": "e4m3", "weight_block_size": [128, 128]}
+    elif fmt == "modelopt":
+        cfg["quantization_config"] = {"quant_method": "modelopt", "quant_algo": "NVFP4"}
+    else:
+        cfg["quantization_config"] = {"quant_method": "compressed-tensors", "format": "nvfp4-pack-quantized"}
+    json.dump(cfg, open(os.path.join(dst, "config.json"), "w"))
+    return dst
+
+
+@pytest.mark.parametrize("kind,fmt", [("qwen3", "fp8"), ("qwen3", "modelopt"), ("qwen3", "compressed"),
+                                      ("qwen3_moe", "modelopt"), ("qwen3_next", "modelopt")])
+def test_prequantised_checkpoint_roundtrip(kind, fmt, tmp_path):
+    """A pre-quantised checkpoint keeps its codes and scales bit-for-bit through slicing / fusing, and its logits
+    match the dequantised weights run through ``transformers``."""
+    hf = _hf(kind)
+    src = _save(hf, tmp_path / "src")
+    dst = _requantise_checkpoint(src, str(tmp_path / fmt), fmt)
+    model = load_model(dst, dtype="float32", with_mtp=False)
+    want_kind = "fp8_block" if fmt == "fp8" else "nvfp4"
+    if kind == "qwen3":
+        assert model.layers[0].mixer.qkv.kind == want_kind and model.layers[0].ffn.down.kind == want_kind
+    else:
+        assert model.layers[0].ffn.experts.kind == want_kind
+    # oracle: transformers on a checkpoint holding the dequantised weights
+    from safetensors.torch import load_file, save_file
+    ck = Checkpoint(dst)
+    deq = str(tmp_path / "deq")
+    os.makedirs(deq)
+    dense = {}
+    for name, t in load_file(os.path.join(src, "model.safetensors")).items():
+        dense[name] = ck.linear(name[:-len(".weight")]).dequant().float().contiguous() if name.endswith("_proj.weight") else t
+    save_file(dense, os.path.join(deq, "model.safetensors"))
+    with open(os.path.join(src, "config.json")) as f, open(os.path.join(deq, "config.json"), "w") as g:
+        g.write(f.read())
+    hf = transformers.AutoModelForCausalLM.from_pretrained(deq, torch_dtype=torch.float32).eval()
+    toks = torch.randint(0, 512, (16,), generator=torch.Generator().manual_seed(5)).tolist()
+    with torch.no_grad():
+        want = hf(torch.tensor([toks])).logits[0]
+    got = _ours_logits(model, toks)
+    # activations are quantised per 128 on the fp8 path; NVFP4 weights run against full-precision activations
+    tol = dict(atol=0.08, rtol=0.05) if fmt == "fp8" else dict(atol=2e-4, rtol=1e-3)
+    torch.testing.assert_close(got, want, **tol)
+
+
+def test_qtensor_slices_are_exact():
+    w = torch.randn(512, 384)
+    q, s = Q.quantize_fp8_block(w)
+    qt = QTensor("fp8_block", q, s)
+    full = qt.dequant()
+    torch.testing.assert_close(qt.rows(128, 384).dequant(), full[128:384], atol=0, rtol=0)
+    torch.testing.assert_close(qt.cols(128, 256).dequant(), full[:, 128:256], atol=0, rtol=0)
+    torch.testing.assert_close(qt.rows(64, 96).dequant(), full[64:96], atol=0, rtol=0)
+    torch.testing.assert_close(cat_rows([qt.rows(0, 128), qt.rows(256, 512)]).dequant(),
+                               torch.cat([full[:128], full[256:]]), atol=0, rtol=0)
+    p, sc, g = Q.quantize_nvfp4(w)
+    nt = QTensor("nvfp4", p, sc, g)
+    nfull = nt.dequant()
+    torch.testing.assert_close(nt.rows(10, 70).dequant(), nfull[10:70], atol=0, rtol=0)
+    torch.testing.assert_close(nt.cols(32, 160).dequant(), nfull[:, 32:160], atol=0, rtol=0)
+
+
+def test_model_config_from_hf_dir(tmp_path):
+    path = _save(_hf("qwen3_next"), tmp_path)
+    cfg = ModelConfig.from_pretrained(path)
+    assert cfg.model_type == "qwen3_next" and cfg.layer_kind(0) == "gdn" and cfg.layer_kind(1) == "attention"
+    assert cfg.num_experts == 8 and cfg.shared_expert_intermediate_size == 128 and cfg.attn_output_gate
