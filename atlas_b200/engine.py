@@ -66,7 +66,9 @@ class LLMEngine:
         self.spec = SpecController(self, self.cfg) if (self.cfg.speculative and model.mtp is not None
                                                          and self.cfg.num_drafts > 0) else None
         self.stats = EngineStats()
+        self.control = None               # parallel.worker.StepControl when several processes serve one model
         self.time_device = False          # accumulate CUDA-event time of each step's GPU work
+        self.device_phase_ms: Dict[str, list] = {}     # phase -> [ms, steps] (steps with any multi-token item count as prefill)
         self.device_time_ms = 0.0
         self._seqs: Dict[str, Sequence] = {}
         self._ids = itertools.count()
@@ -150,15 +152,22 @@ class LLMEngine:
     # ------------------------------------------------------------------ one step
     @torch.inference_mode()
     def step(self) -> List[RequestOutput]:
+        """One scheduler tick.  With a multi-process ``control`` attached the leader's clock, request events and
+        sampling verdict are imposed on the followers (see ``parallel/worker.py``); otherwise everything is local."""
         t0 = time.monotonic()
         sched = self.scheduler
-        out = sched.schedule()
+        ctl = self.control
+        follower = ctl is not None and not ctl.is_leader
+        now_plan = ctl.begin_step(self) if ctl is not None else None
+        out = sched.schedule(now=now_plan, expire=ctl is None)
         results: List[RequestOutput] = []
         for s in sched.finished_queue:      # deadline expiries
             results.append(self._make_output(s, []))
             self._seqs.pop(s.request_id, None)
         sched.finished_queue.clear()
         if out.empty:
+            if ctl is not None:
+                ctl.finish_step(None if follower else _EMPTY_VERDICT())
             return results
         for snap_slot, seq_slot in out.restored_snapshots:
             self.runner.copy_state(self.snapshot_base + snap_slot, seq_slot)
@@ -184,21 +193,57 @@ class LLMEngine:
         sampled: Dict[int, List[int]] = {}
         lps: Dict[int, list] = {}
         if rows:
-            logits = self.runner.logits(hidden, rows)
-            seqs_rows = [out.items[i].seq for i in row_owner]
-            so = self.sampler(logits, seqs_rows) if not any(out.items[i].verify_drafts for i in set(row_owner)) \
-                else self._sample_verify_rows(logits, out, row_owner)
-            for j, i in enumerate(row_owner):
-                sampled.setdefault(i, []).append(so.tokens[j])
-                if so.logprobs is not None and so.logprobs[j] is not None:
-                    lps.setdefault(i, []).append(so.logprobs[j])
+            logits = self.runner.logits(hidden, rows)       # every rank: the vocab-parallel gather is a collective
+            if not follower:
+                seqs_rows = [out.items[i].seq for i in row_owner]
+                so = self.sampler(logits, seqs_rows) if not any(out.items[i].verify_drafts for i in set(row_owner)) \
+                    else self._sample_verify_rows(logits, out, row_owner)
+                for j, i in enumerate(row_owner):
+                    sampled.setdefault(i, []).append(so.tokens[j])
+                    if so.logprobs is not None and so.logprobs[j] is not None:
+                        lps.setdefault(i, []).append(so.logprobs[j])
         if ev is not None:
             ev[1].record()
             ev[1].synchronize()
-            self.device_time_ms += ev[0].elapsed_time(ev[1])
+            ms = ev[0].elapsed_time(ev[1])
+            self.device_time_ms += ms
+            kind = "decode" if all(it.num_tokens == 1 for it in out.items) else "prefill"
+            d = self.device_phase_ms.setdefault(kind, [0.0, 0])
+            d[0] += ms
+            d[1] += 1
         now = time.monotonic()
+        dt_gate: Optional[float] = None
+        if follower:
+            verdict = ctl.finish_step(None)
+            accepted_rows = self._apply_verdict(out, verdict.records, now)
+            dt_gate = verdict.dt
+        else:
+            accepted_rows, records = self._apply_sampled(out, sampled, lps, now, results)
+            if ctl is not None:
+                dt_gate = time.monotonic() - t0
+                ctl.finish_step(_make_verdict(records, dt_gate))
+        if batch.spec_verify:
+            self.model.commit_spec(accepted_rows, self.cache)
+            for it in out.items:
+                if not it.seq.finished:
+                    sched.trim_blocks(it.seq)
+        if use_spec:
+            self.spec.after_step(out, batch, hidden, sampled, accepted_rows)
+        dt = time.monotonic() - t0
+        n_new = sum(len(r.new_tokens) for r in results)
+        self.stats.on_step(dt, out, n_new)
+        if self.spec is not None:
+            n_gate = n_new if not follower else sum(len(v[1]) for v in verdict.records.values())
+            self.spec.gate.record(batch.spec_verify, dt if dt_gate is None else dt_gate, n_gate)
+        return results
+
+    def _apply_sampled(self, out: SchedulerOutput, sampled: Dict[int, List[int]], lps: Dict[int, list], now: float,
+                       results: List[RequestOutput]):
+        """Authoritative post-processing: draft acceptance, appends, stop conditions.  Returns the rows kept per
+        item and the per-item records a follower needs to replay the same state changes."""
+        sched = self.scheduler
         accepted_rows: List[int] = []
-        qsl = 0
+        records: Dict[int, tuple] = {}
         for idx, it in enumerate(out.items):
             seq = it.seq
             new_tokens: List[int] = []
@@ -220,6 +265,7 @@ class LLMEngine:
                 accepted_rows.append(it.num_tokens)
                 if it.sample:
                     new_tokens = sampled[idx]
+            kept: List[int] = []
             if new_tokens:
                 kept = self._append_tokens(seq, new_tokens, now, lps.get(idx))
                 if seq.status == SeqStatus.PREFILL and not seq.finished:
@@ -228,19 +274,33 @@ class LLMEngine:
                 if seq.finished:
                     self._seqs.pop(seq.request_id, None)
                     self._stop_checkers.pop(seq.request_id, None)
-            qsl += it.num_tokens
-        if batch.spec_verify:
-            self.model.commit_spec(accepted_rows, self.cache)
-            for it in out.items:
-                if not it.seq.finished:
-                    sched.trim_blocks(it.seq)
-        if use_spec:
-            self.spec.after_step(out, batch, hidden, sampled, accepted_rows)
-        dt = time.monotonic() - t0
-        self.stats.on_step(dt, out, sum(len(r.new_tokens) for r in results))
-        if self.spec is not None:
-            self.spec.gate.record(batch.spec_verify, dt, sum(len(r.new_tokens) for r in results))
-        return results
+            records[idx] = (accepted_rows[-1], kept, seq.finish_reason.value if seq.finished else None)
+        return accepted_rows, records
+
+    def _apply_verdict(self, out: SchedulerOutput, records: Dict[int, tuple], now: float) -> List[int]:
+        """Follower replay of the leader's verdict (no sampling, no stop logic of its own)."""
+        sched = self.scheduler
+        accepted_rows: List[int] = []
+        for idx, it in enumerate(out.items):
+            seq = it.seq
+            rows_kept, kept, fin = records[idx]
+            if it.verify_drafts:
+                sched.on_chunk_computed(it, rows_kept)
+                seq.drafts = []
+            else:
+                sched.on_chunk_computed(it)
+            accepted_rows.append(rows_kept)
+            if kept:
+                if seq.first_token_time is None:
+                    seq.first_token_time = now
+                seq.output_tokens.extend(int(t) for t in kept)
+                self.stats.generation_tokens += len(kept)
+            if fin is not None:
+                sched.finish(seq, FinishReason(fin))
+                self._seqs.pop(seq.request_id, None)
+            elif kept and seq.status == SeqStatus.PREFILL:
+                sched.promote(seq)
+        return accepted_rows
 
     def _sample_verify_rows(self, logits, out: SchedulerOutput, row_owner: List[int]):
         """Sample every verify row with the uniform of the output position it would emit at, so that
@@ -338,3 +398,12 @@ class _RowView:
     @property
     def output_tokens(self) -> List[int]:
         return self._seq.output_tokens + self._seq.drafts[:self._k]
+
+
+def _make_verdict(records, dt):
+    from .parallel.worker import StepVerdict
+    return StepVerdict(records, dt)
+
+
+def _EMPTY_VERDICT():
+    return _make_verdict({}, 0.0)

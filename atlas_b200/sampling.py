@@ -53,6 +53,16 @@ class SamplingParams:
     prompt_logprobs: bool = False
     n: int = 1
 
+    def to_dict(self) -> dict:
+        from dataclasses import asdict
+        return asdict(self)
+
+    @staticmethod
+    def from_dict(d: dict) -> "SamplingParams":
+        d = dict(d)
+        d["logit_bias"] = {int(k): float(v) for k, v in (d.get("logit_bias") or {}).items()}
+        return SamplingParams(**d)
+
     @property
     def greedy(self) -> bool:
         return self.temperature <= 0.0

@@ -40,7 +40,7 @@ class Scheduler:
         self.finished_queue: List[Sequence] = []
         self.num_preemptions = 0
         self.snapshot_interval = max(self.bs, (cfg.ssm_checkpoint_interval + self.bs - 1) // self.bs * self.bs)
-        self._last_decode_time = time.monotonic()
+        self._last_decode_time: Optional[float] = None
 
     # ------------------------------------------------------------------ queue ops
     def add(self, seq: Sequence) -> None:
@@ -149,11 +149,16 @@ class Scheduler:
         return True
 
     # ------------------------------------------------------------------ planning
-    def schedule(self) -> SchedulerOutput:
+    def schedule(self, now: Optional[float] = None, expire: bool = True) -> SchedulerOutput:
+        """``now`` / ``expire=False`` let a multi-process leader impose its clock and its expiry decisions on the
+        follower replicas so that every rank plans the same step."""
         out = SchedulerOutput()
         cfg = self.cfg
-        now = time.monotonic()
-        self._expire_deadlines(now)
+        now = time.monotonic() if now is None else now
+        if expire:
+            self._expire_deadlines(now)
+        if self._last_decode_time is None:
+            self._last_decode_time = now
 
         # 1. decodes (+ draft rows)
         decode_items: List[ScheduledSeq] = []
@@ -255,6 +260,12 @@ class Scheduler:
             slot = self.radix.attach_snapshot(nodes[-1])
             if slot is not None:
                 out.snapshot_requests.append((item_index, p - lo, slot))
+
+    def expire(self, now: float) -> List[Sequence]:
+        """Expire deadlines now; returns the sequences that timed out (they are also queued as finished)."""
+        n0 = len(self.finished_queue)
+        self._expire_deadlines(now)
+        return self.finished_queue[n0:]
 
     def _expire_deadlines(self, now: float) -> None:
         for q in (self.waiting, self.prefilling, self.running):

@@ -84,3 +84,8 @@ class FaultLatch:
 
 
 FAULT_LATCH = FaultLatch()
+
+
+def latch(reason: str) -> None:
+    """Trip the process-wide latch (non-GPU fatal conditions, e.g. a dead control plane, use this too)."""
+    FAULT_LATCH.trip(reason)

@@ -144,6 +144,7 @@ def main():
         return 3
     sampler = _clock_sampler(torch.cuda.current_device()) if rank == 0 else None
     eng.device_time_ms = 0.0
+    eng.device_phase_ms = {}
     launches0, replays0 = K.launch_count, eng.runner.graph_replays
     h2d0 = eng.runner.h2d_bytes
     steps0 = eng.stats.steps
@@ -187,6 +188,7 @@ def main():
             "gpu_launches": int(launches),
             "ttft_p50_ms": round(statistics.median(ttfts) * 1e3, 2) if ttfts else None,
             "tpot_ms": round((wall / args.steps) * 1e3 / args.osl, 3),
+            "device_phase_ms": {k: {"ms": round(v[0], 1), "engine_steps": v[1]} for k, v in eng.device_phase_ms.items()},
             "impl": "atlas_b200",
         }
         print(json.dumps(line))
