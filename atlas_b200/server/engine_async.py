@@ -135,6 +135,9 @@ class AsyncEngine:
         while not self._stop.is_set():
             self._drain_inbox()
             if not eng.has_unfinished():
+                idle = getattr(eng, "idle", None)      # multi-process leader: heartbeat to the follower ranks
+                if idle is not None:
+                    idle()
                 self._wake.wait(self.idle_sleep_s * 10)
                 self._wake.clear()
                 continue
