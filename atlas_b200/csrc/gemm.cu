@@ -24,9 +24,12 @@ namespace atlas {
 
 constexpr int kBlockM = 128;
 constexpr int kRowBytes = 128;            // one swizzle row = one BLOCK_K slice
-constexpr int kEpiWarps = 8;
 constexpr int kCtrlWarps = 2;            // warp 0: TMA producer, warp 1: MMA issuer
-constexpr int kGemmThreads = 32 * (kCtrlWarps + kEpiWarps);
+// Epilogue warps: eight (two per TMEM lane quadrant) except for the 256-wide FP8 tile, whose per-k-group fold keeps the
+// whole accumulator in registers: sixteen warps of 64 columns each stay under the register budget where eight warps of
+// 128 columns spill.
+__host__ __device__ constexpr int epi_warps(int block_n, bool fp8) { return (fp8 && block_n == 256) ? 16 : 8; }
+__host__ __device__ constexpr int gemm_threads(int block_n, bool fp8) { return 32 * (kCtrlWarps + epi_warps(block_n, fp8)); }
 
 template <int BLOCK_N>
 struct GemmCfg {
@@ -36,8 +39,11 @@ struct GemmCfg {
   static constexpr int kStages = BLOCK_N == 256 ? 4 : (BLOCK_N == 128 ? 6 : 8);
   static constexpr int kAccStages = (512 / BLOCK_N) < 4 ? (512 / BLOCK_N) : 4;   // TMEM accumulator ring depth
   static constexpr int kTmemCols = kAccStages * BLOCK_N;
-  static constexpr int kHalf = BLOCK_N / 2;             // columns per epilogue thread
-  static constexpr int kScaleRingBytes = kStages * kBlockM * 4;   // per stage: 128 activation scales (fp32)
+  // Activation scales travel in their own ring, deeper than the tile ring: the producer runs at most kStages k-groups
+  // ahead of the tensor cores and those at most kAccStages ahead of the epilogue, so a slot is never overwritten
+  // before the epilogue has read it and the tile stages can be recycled as soon as their MMAs retire.
+  static constexpr int kScaleSlots = kStages + kAccStages + 1;
+  static constexpr int kScaleRingBytes = kScaleSlots * kBlockM * 4;   // per slot: 128 activation scales (fp32)
   static constexpr int kBScaleMax = 512;                          // k-groups of one split kept in shared memory
   static constexpr int kBScaleBytes = 2 * 2 * kBScaleMax * 4;     // double-buffered over tiles, two 128-column groups
   static constexpr int kSmemBytes = kStages * kStageBytes + kScaleRingBytes + kBScaleBytes + 1024 /*align*/ + 512 /*barriers*/;
@@ -107,26 +113,30 @@ ATLAS_DEVICE bool wait_flag_eq(const uint32_t* p, uint32_t want, status_t* statu
 //                finds the whole [M, N] result in its own memory.
 // Transfers therefore overlap the math tile by tile; flags carry the call's epoch, so nothing is ever reset.
 template <int BLOCK_N, bool FP8, bool FUSE_AR = false>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(gemm_threads(BLOCK_N, FP8), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmParams p) {
   using Cfg = GemmCfg<BLOCK_N>;
   constexpr int kStages = Cfg::kStages;
-  constexpr int HALF = Cfg::kHalf;
+  constexpr int kEpiWarps = epi_warps(BLOCK_N, FP8);
+  constexpr int kParts = kEpiWarps / 4;                 // column slices of a tile, one per warp of a lane quadrant
+  constexpr int HALF = BLOCK_N / kParts;                // columns per epilogue thread
   constexpr int kElemsPerRow = FP8 ? 128 : 64;          // BLOCK_K in elements
   constexpr uint32_t kIdesc = make_idesc(kBlockM, BLOCK_N, FP8 ? 0u : 1u);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* sc_ring = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes);        // [kStages][128]
-  float* bs_smem = sc_ring + kStages * kBlockM;                                         // [2][kBScaleMax]
+  constexpr int kScaleSlots = Cfg::kScaleSlots;
+  float* sc_ring = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes);        // [kScaleSlots][128]
+  float* bs_smem = sc_ring + kScaleSlots * kBlockM;                                     // [2][kBScaleMax]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + Cfg::kScaleRingBytes + Cfg::kBScaleBytes);
   uint64_t* full = bars;
   uint64_t* empty = bars + kStages;
   uint64_t* acc_full = bars + 2 * kStages;
   constexpr int kAcc = Cfg::kAccStages;
   uint64_t* acc_empty = acc_full + kAcc;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kAcc);
+  uint64_t* sc_full = acc_empty + kAcc;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sc_full + kScaleSlots);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile int* ticket_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
@@ -136,8 +146,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], FP8 ? 1 + kEpiWarps : 1);
+      mbar_init(&empty[s], 1);
     }
+    for (int s = 0; s < kScaleSlots; ++s) mbar_init(&sc_full[s], 1);
     for (int b = 0; b < kAcc; ++b) {
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], kEpiWarps);
@@ -168,7 +179,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      uint32_t stage = 0, phase = 0;
+      uint32_t stage = 0, phase = 0, sc_slot = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
         const int m_tile = item % m_tiles;
@@ -180,10 +191,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 0x100)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
-          mbar_expect_tx(&full[stage], Cfg::kStageBytes + (FP8 ? kBlockM * 4 : 0));
-          if (FP8)
-            bulk_g2s(sc_ring + stage * kBlockM, p.a_scale + (long long)kb * p.sa_k + m_tile * kBlockM, kBlockM * 4,
-                     &full[stage]);
+          mbar_expect_tx(&full[stage], Cfg::kStageBytes);
+          if (FP8) {
+            mbar_expect_tx(&sc_full[sc_slot], kBlockM * 4);
+            bulk_g2s(sc_ring + sc_slot * kBlockM, p.a_scale + (long long)kb * p.sa_k + m_tile * kBlockM, kBlockM * 4,
+                     &sc_full[sc_slot]);
+            if (++sc_slot == kScaleSlots) sc_slot = 0;
+          }
           tma_load_2d(sa, &tmap_a, &full[stage], kb * kElemsPerRow, m_tile * kBlockM);
           tma_load_2d(sa + Cfg::kABytes, &tmap_b, &full[stage], kb * kElemsPerRow,
                       (p.tile_expert ? p.tile_expert[m_tile] * p.expert_n : 0) + n_tile * BLOCK_N);
@@ -236,16 +250,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
     }
   } else if (warp >= kCtrlWarps) {
-    // ------------------------------------------------------------------ epilogue (8 warps)
+    // ------------------------------------------------------------------ epilogue
     const int e = warp - kCtrlWarps;
     const int lane_group = warp & 3;                 // TMEM lanes this warp may touch: [32*lane_group, +32)
-    const int half = e >> 2;                         // which half of the tile's columns
+    const int half = e >> 2;                         // which column slice of the tile
     const int row_in_tile = lane_group * 32 + lane;
     const uint32_t t_lane = (uint32_t)(lane_group * 32) << 16;
     const int epi_tid = threadIdx.x - 32 * kCtrlWarps;
     uint32_t acc_iter = 0;
     uint32_t tile_iter = 0;
-    uint32_t e_stage = 0, e_phase = 0;       // mirrors the producer's ring position (fp8 path reads the scale slot)
+    uint32_t sc_slot = 0, sc_phase = 0;      // mirrors the producer's position in the activation-scale ring
     bool ok = true;
     float acc[HALF];
     // This loop never exits early: the split-K path below uses named barriers that need all eight warps.
@@ -280,21 +294,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       } else if (FP8) {
 #pragma unroll
         for (int i = 0; i < HALF; ++i) acc[i] = 0.f;
-        const float* bs_row = bs_buf + ((BLOCK_N > 128 && half) ? Cfg::kBScaleMax : 0);
+        const float* bs_row = bs_buf + ((half * HALF) / 128) * Cfg::kBScaleMax;
         for (int kb = kb0; kb < kb1; ++kb) {
           const uint32_t buf = acc_iter % kAcc, aph = (acc_iter / kAcc) & 1u;
           if (!mbar_wait(&acc_full[buf], aph, abort_flag, p.status, 0x300)) { ok = false; break; }
           tc_fence_after();
-          // the MMAs of this k-group are done, so its stage has landed: take the row scale and free the stage
-          if (!mbar_wait(&full[e_stage], e_phase, abort_flag, p.status, 0x302)) { ok = false; break; }
-          const float s = sc_ring[e_stage * kBlockM + row_in_tile] * bs_row[kb - kb0];
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&empty[e_stage]);
-          if (++e_stage == kStages) { e_stage = 0; e_phase ^= 1u; }
+          if (!mbar_wait(&sc_full[sc_slot], sc_phase, abort_flag, p.status, 0x302)) { ok = false; break; }
+          const float s = sc_ring[sc_slot * kBlockM + row_in_tile] * bs_row[kb - kb0];
+          if (++sc_slot == kScaleSlots) { sc_slot = 0; sc_phase ^= 1u; }
           const uint32_t taddr = tmem_base + t_lane + buf * BLOCK_N + half * HALF;
           // Pull the partial tile into registers with back-to-back tcgen05.ld, hand the TMEM buffer back to the
           // MMA issuer as soon as the loads have landed, and only then fold the scales in.
-          constexpr int kChunk = HALF < 64 ? HALF : 64;
+          constexpr int kChunk = (HALF < 64 || kEpiWarps > 8) ? 32 : 64;
 #pragma unroll
           for (int c0 = 0; c0 < HALF; c0 += kChunk) {
             uint32_t r[kChunk / 32][32];
@@ -556,7 +567,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
     if (e != cudaSuccess) return -20;
     attr_done = true;
   }
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ta, tb, p);
+  kern<<<grid, gemm_threads(BLOCK_N, FP8), Cfg::kSmemBytes, st>>>(ta, tb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
