@@ -196,6 +196,9 @@ def cmd_serve(argv: List[str]) -> int:
             pctx.comm = symm
             if pctx.ep_comm is not None and topo.overlapping:
                 pctx.ep_comm = symm
+    if args.profile:
+        from .utils.trace import TRACER
+        TRACER.enable(True)
     if args.check_kernels and device.type == "cuda":
         from .utils.selfcheck import kernel_selftest
         kernel_selftest(device)

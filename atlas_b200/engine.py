@@ -23,6 +23,7 @@ from .sampling import Sampler, SamplingParams
 from .sched import FinishReason, ScheduledSeq, Scheduler, SchedulerOutput, SeqStatus, Sequence
 from .sched.spec import SpecController
 from .utils.metrics import EngineStats
+from .utils.trace import phase
 
 
 @dataclass
@@ -159,7 +160,8 @@ class LLMEngine:
         ctl = self.control
         follower = ctl is not None and not ctl.is_leader
         now_plan = ctl.begin_step(self) if ctl is not None else None
-        out = sched.schedule(now=now_plan, expire=ctl is None)
+        with phase("schedule"):
+            out = sched.schedule(now=now_plan, expire=ctl is None)
         results: List[RequestOutput] = []
         for s in sched.finished_queue:      # deadline expiries
             results.append(self._make_output(s, []))
@@ -172,12 +174,14 @@ class LLMEngine:
         for snap_slot, seq_slot in out.restored_snapshots:
             self.runner.copy_state(self.snapshot_base + snap_slot, seq_slot)
         use_spec = self.spec is not None and self.spec.active()
-        batch = self.runner.build_batch(out, self.snapshot_base)
+        with phase("build_batch"):
+            batch = self.runner.build_batch(out, self.snapshot_base)
         ev = None
         if self.time_device and self.model.device.type == "cuda":
             ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             ev[0].record()
-        hidden = self.runner.forward(batch)
+        with phase("forward", tokens=batch.num_tokens if hasattr(batch, "num_tokens") else 0):
+            hidden = self.runner.forward(batch)
         # rows that need logits
         rows, row_owner = [], []
         qsl = 0
@@ -193,7 +197,8 @@ class LLMEngine:
         sampled: Dict[int, List[int]] = {}
         lps: Dict[int, list] = {}
         if rows:
-            logits = self.runner.logits(hidden, rows)       # every rank: the vocab-parallel gather is a collective
+            with phase("logits"):
+                logits = self.runner.logits(hidden, rows)       # every rank: the vocab-parallel gather is a collective
             if not follower:
                 seqs_rows = [out.items[i].seq for i in row_owner]
                 so = self.sampler(logits, seqs_rows) if not any(out.items[i].verify_drafts for i in set(row_owner)) \
@@ -218,7 +223,8 @@ class LLMEngine:
             accepted_rows = self._apply_verdict(out, verdict.records, now)
             dt_gate = verdict.dt
         else:
-            accepted_rows, records = self._apply_sampled(out, sampled, lps, now, results)
+            with phase("apply"):
+                accepted_rows, records = self._apply_sampled(out, sampled, lps, now, results)
             if ctl is not None:
                 dt_gate = time.monotonic() - t0
                 ctl.finish_step(_make_verdict(records, dt_gate))

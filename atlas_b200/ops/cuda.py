@@ -12,6 +12,8 @@ from typing import Dict, Optional, Tuple
 
 import torch
 
+from ..utils.trace import TRACER as _TRACER
+
 _LIB = None
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(os.path.dirname(_HERE), "_C", "libatlas_b200_kernels.so")
@@ -86,6 +88,8 @@ def _stream() -> int:
 def _check(rc: int, what: str) -> None:
     global launch_count
     launch_count += 1
+    if _TRACER.enabled:
+        _TRACER.launch(what)
     if rc != 0:
         raise KernelError(f"{what} failed with code {rc}")
 

@@ -14,6 +14,7 @@ import time
 import uuid
 from typing import Any, AsyncIterator, Dict, List, Optional
 
+from ..utils.trace import TRACER
 from fastapi import FastAPI, Request
 from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
@@ -302,6 +303,7 @@ def create_app(state: ServerState) -> FastAPI:
             req.logprobs, req.top_logprobs = True, int(body["logprobs"])
         S.gen.prepare(req)
         cid = "cmpl-" + uuid.uuid4().hex[:24]
+        want_ids = bool(body.get("return_token_ids"))
         created, model = int(time.time()), body.get("model") or S.model_name
 
         def lp_legacy(entries):
@@ -318,10 +320,11 @@ def create_app(state: ServerState) -> FastAPI:
                     if d.error:
                         yield _sse({"error": {"message": d.error, "type": "server_error"}})
                         break
-                    if d.content or d.reasoning or d.finish_reason:
+                    if d.content or d.reasoning or d.finish_reason or (want_ids and d.token_ids):
                         yield _sse({"id": cid, "object": "text_completion", "created": created, "model": model,
                                     "choices": [{"index": 0, "text": d.reasoning + d.content, "finish_reason": d.finish_reason,
-                                                 "logprobs": lp_legacy(d.logprobs) if req.logprobs else None}],
+                                                 "logprobs": lp_legacy(d.logprobs) if req.logprobs else None,
+                                                 **({"token_ids": d.token_ids} if want_ids and d.token_ids else {})}],
                                     **({"usage": d.usage} if d.usage else {})})
                 yield b"data: [DONE]\n\n"
             return StreamingResponse(sse(), media_type="text/event-stream")
@@ -330,13 +333,14 @@ def create_app(state: ServerState) -> FastAPI:
             return _err(500, o.error, "server_error")
         return JSONResponse({"id": cid, "object": "text_completion", "created": created, "model": model,
                              "choices": [{"index": 0, "text": o.reasoning + o.content, "finish_reason": o.finish_reason,
-                                          "logprobs": lp_legacy(o.logprobs) if req.logprobs else None}],
+                                          "logprobs": lp_legacy(o.logprobs) if req.logprobs else None,
+                                          **({"token_ids": o.token_ids} if want_ids else {})}],
                              "usage": o.usage})
 
     # ------------------------------------------------------------------ models / tokenize
     def model_card():
         return {"id": S.model_name, "object": "model", "created": S.created, "owned_by": "atlas-b200",
-                "max_model_len": S.engine.engine.cfg.max_seq_len}
+                "max_model_len": S.engine.engine.cfg.max_seq_len, "vocab_size": S.engine.engine.mcfg.vocab_size}
 
     @app.get("/v1/models")
     async def models():
@@ -457,7 +461,12 @@ def create_app(state: ServerState) -> FastAPI:
         import dataclasses
         return {"model": S.model_name, "engine": dataclasses.asdict(e.cfg), "scheduler": e.snapshot(),
                 "tool_call_parser": S.tool_parser_name, "grammar_backend": S.grammar.backend if S.grammar else None,
-                "kv_cache_dtype": str(e.kv_dtype), "num_kv_blocks": e.pool.num_blocks}
+                "kv_cache_dtype": str(e.kv_dtype), "num_kv_blocks": e.pool.num_blocks,
+                "serve_plan": S.args.get("serve_plan"), "trace": TRACER.summary()}
+
+    @app.get("/trace")
+    async def trace_dump():
+        return TRACER.chrome_trace()
 
     for stub in ("/v1/embeddings", "/v1/batches", "/v1/files", "/v1/audio/speech", "/v1/audio/transcriptions",
                  "/v1/audio/translations", "/v1/images/generations", "/v1/images/edits", "/v1/moderations",
