@@ -17,6 +17,7 @@ class ReasoningSplitter:
         self.in_reasoning = starts_in_reasoning
         self.seen_any = starts_in_reasoning
         self.done = False
+        self._eat_newlines = False
         self.buf = ""
 
     def _hold(self, tag: str) -> int:
@@ -30,6 +31,10 @@ class ReasoningSplitter:
         r_out, c_out = "", ""
         while True:
             if self.done:
+                if self._eat_newlines:          # newlines right after the close tag belong to neither part
+                    self.buf = self.buf.lstrip("\n")
+                    if self.buf:
+                        self._eat_newlines = False
                 c_out += self.buf
                 self.buf = ""
                 return r_out, c_out
@@ -37,8 +42,8 @@ class ReasoningSplitter:
                 i = self.buf.find(self.close)
                 if i >= 0:
                     r_out += self.buf[:i]
-                    self.buf = self.buf[i + len(self.close):].lstrip("\n")
-                    self.in_reasoning, self.done = False, True
+                    self.buf = self.buf[i + len(self.close):]
+                    self.in_reasoning, self.done, self._eat_newlines = False, True, True
                     continue
                 h = self._hold(self.close)
                 r_out += self.buf[:len(self.buf) - h]

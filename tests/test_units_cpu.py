@@ -1,0 +1,328 @@
+"""Unit tier (CPU): tool-call parsers, reasoning splitter, grammar matcher, block pool + radix cache (incl. a
+randomised model check), scheduler behaviours (chunked prefill, preemption with resume, admission), sampler
+distributions and penalties, collective protocol with injected failures, fault latch classification."""
+import json
+import random
+
+import pytest
+import torch
+
+from atlas_b200.config import EngineConfig, tiny_dense
+from atlas_b200.engine import LLMEngine
+from atlas_b200.kv import BlockPool, RadixCache
+from atlas_b200.kv.block_manager import OutOfBlocks
+from atlas_b200.models import build_model
+from atlas_b200.ops import reference as ref
+from atlas_b200.parallel.comm import CommError, FakeWorld
+from atlas_b200.sampling import RequestRng, SamplingParams
+from atlas_b200.server.reasoning import ReasoningSplitter, split_reasoning
+from atlas_b200.server.tool_parsers import StreamingToolParser, default_parser_for, get_parser
+from atlas_b200.utils.fault import Fatality, FaultLatch, classify_probe
+
+TOOLS = [{"type": "function", "function": {"name": "get_weather", "parameters": {
+    "type": "object", "properties": {"city": {"type": "string"}, "days": {"type": "integer"}, "metric": {"type": "boolean"}}}}}]
+
+
+# ----------------------------------------------------------------------------------------------------- tool parsers
+@pytest.mark.parametrize("name,text", [
+    ("hermes", 'Sure.\n<tool_call>\n{"name": "get_weather", "arguments": {"city": "Oslo", "days": 3}}\n</tool_call>'),
+    ("qwen3_coder", "Sure.<tool_call>\n<function=get_weather>\n<parameter=city>\nOslo\n</parameter>\n<parameter=days>\n3\n</parameter>\n</function>\n</tool_call>"),
+    ("mistral", 'Sure.[TOOL_CALLS][{"name": "get_weather", "arguments": {"city": "Oslo", "days": 3}}]'),
+    ("minimax_xml", 'Sure.<minimax:tool_call>\n<invoke name="get_weather">\n<parameter name="city">Oslo</parameter>\n<parameter name="days">3</parameter>\n</invoke>\n</minimax:tool_call>'),
+    ("gemma", 'Sure.\n```tool_code\nget_weather(city="Oslo", days=3)\n```'),
+])
+def test_tool_parsers_extract_calls(name, text):
+    content, calls = get_parser(name, TOOLS).parse(text)
+    assert len(calls) == 1 and calls[0].name == "get_weather"
+    args = json.loads(calls[0].arguments)
+    assert args["city"] == "Oslo" and args["days"] == 3          # typed through the declared schema
+    assert "Sure." in content and "get_weather" not in content
+    oa = calls[0].to_openai(0)
+    assert oa["type"] == "function" and oa["function"]["name"] == "get_weather" and oa["id"]
+
+
+def test_bare_json_and_plain_text_and_defaults():
+    p = get_parser("bare_json", TOOLS)
+    _, calls = p.parse('{"name": "get_weather", "arguments": {"city": "Rome"}}')
+    assert calls and json.loads(calls[0].arguments) == {"city": "Rome"}
+    for name in ("hermes", "qwen3_coder", "mistral", "bare_json", "gemma"):
+        content, calls = get_parser(name, TOOLS).parse("just words, no call")
+        assert calls == [] and content == "just words, no call"
+    assert default_parser_for("qwen3_next") == "qwen3_coder" and default_parser_for("mistral") == "mistral"
+    assert default_parser_for("qwen3_moe") == "hermes"
+    with pytest.raises(ValueError):
+        get_parser("nope")
+
+
+def test_streaming_tool_parser_holds_back_markers():
+    text = 'Let me check. <tool_call>\n{"name": "get_weather", "arguments": {"city": "Oslo"}}\n</tool_call>'
+    for step in (1, 3, 7, 1000):
+        sp = StreamingToolParser(get_parser("hermes", TOOLS))
+        shown = "".join(sp.push(text[i:i + step]) for i in range(0, len(text), step))
+        rest, calls = sp.finish()
+        assert "<" not in shown and shown.startswith("Let me check.")
+        assert len(calls) == 1 and calls[0].name == "get_weather"
+    sp = StreamingToolParser(get_parser("hermes", TOOLS))
+    shown = "".join(sp.push(ch) for ch in "a < b and <tool is not a call")
+    rest, calls = sp.finish()
+    assert calls == [] and shown + rest == "a < b and <tool is not a call"
+
+
+# ----------------------------------------------------------------------------------------------------- reasoning
+def test_reasoning_splitter_any_chunking():
+    text = "<think>\nstep one\nstep two</think>\n\nThe answer is 4."
+    for step in (1, 2, 5, 100):
+        sp = ReasoningSplitter()
+        r = c = ""
+        for i in range(0, len(text), step):
+            a, b = sp.push(text[i:i + step])
+            r, c = r + a, c + b
+        a, b = sp.finish()
+        r, c = r + a, c + b
+        assert r.strip() == "step one\nstep two" and c == "The answer is 4."
+    assert split_reasoning("no thinking here") == (None, "no thinking here")
+    assert split_reasoning("already inside</think>done", starts_in_reasoning=True) == ("already inside", "done")
+    r, c = split_reasoning("<think>never closed")
+    assert r == "never closed" and c == ""
+
+
+# ----------------------------------------------------------------------------------------------------- grammar
+def test_byte_json_matcher_keeps_brackets_balanced():
+    """The built-in fallback matcher (used when xgrammar is missing) works on byte-tokenizer ids (3 + byte): the
+    output must open with an object, brackets close in order, string contents are free, then only EOS."""
+    from atlas_b200.server.grammar import _ByteJsonMatcher
+    good = '{"a": [1, 2.5, true, null], "b": {"c": "x\\"y}]"}}'
+    m = _ByteJsonMatcher(1024)
+    assert not bool(m.token_mask(1024)[3 + ord("x")]) and bool(m.token_mask(1024)[3 + ord("{")])
+    for ch in good.encode():
+        assert bool(m.token_mask(1024)[3 + ch]), f"byte {chr(ch)!r} should be allowed"
+        assert m.accept(3 + ch)
+    assert m.terminated()
+    mask = m.token_mask(1024)
+    assert bool(mask[2]) and int(mask.sum()) == 1                  # closed: EOS only
+    m = _ByteJsonMatcher(1024)
+    for ch in b'{"a": [1':
+        m.accept(3 + ch)
+    mask = m.token_mask(1024)
+    assert bool(mask[3 + ord("]")]) and not bool(mask[3 + ord("}")])   # the array has to close first
+    assert not m.accept(3 + ord("}"))
+
+
+# ----------------------------------------------------------------------------------------------------- block pool / radix
+def test_block_pool_refcounts():
+    p = BlockPool(8, 16)
+    a = p.alloc(3)
+    p.inc_ref(a[:1])
+    assert p.free(a) == 2 and p.ref_count(a[0]) == 1 and p.num_free == 7
+    p.free(a[:1])
+    p.check_invariants()
+    with pytest.raises(ValueError):
+        p.free(a[:1])
+    with pytest.raises(OutOfBlocks):
+        p.alloc(9)
+    assert p.blocks_for_tokens(17) == 2 and p.high_water == 3
+
+
+def test_radix_match_insert_evict():
+    pool = BlockPool(16, 4)
+    rc = RadixCache(pool)
+    toks = list(range(13))
+    blocks = pool.alloc(4)
+    rc.insert(toks, blocks)                       # 3 full blocks published
+    pool.free(blocks)                             # the sequence lets go; the tree keeps 3
+    assert pool.num_used == 3
+    m = rc.match(toks[:9] + [99, 98, 97])
+    assert m.num_tokens == 8 and m.blocks == blocks[:2]
+    m1 = rc.match(toks[:8])
+    assert m1.num_tokens == 4                     # always leaves one token to compute
+    rc.release(m1.nodes)
+    pool.free(m1.blocks)
+    assert rc.evict(10) == 1                      # only the unpinned leaf can go
+    rc.release(m.nodes)
+    pool.free(m.blocks)
+    m2 = rc.match(toks[:8], namespace="other")
+    assert m2.num_tokens == 0                     # namespaces (adapters / tenants) do not share
+    assert rc.evict(10) == 2 and pool.num_used == 0
+    pool.check_invariants()
+
+
+def test_radix_randomised_against_model():
+    """Random inserts / matches / evictions against a dict-of-prefixes model; references must balance."""
+    rnd = random.Random(0)
+    pool = BlockPool(64, 2)
+    rc = RadixCache(pool)
+    known = set()
+    for _ in range(300):
+        op = rnd.random()
+        toks = [rnd.randrange(3) for _ in range(rnd.randrange(2, 12))]
+        if op < 0.5:
+            n = pool.blocks_for_tokens(len(toks))
+            if pool.num_free < n:
+                rc.evict(n)
+            if pool.num_free < n:
+                continue
+            blocks = pool.alloc(n)
+            rc.insert(toks, blocks)
+            pool.free(blocks)
+            for j in range(1, len(toks) // 2 + 1):
+                known.add(tuple(toks[:2 * j]))
+        elif op < 0.9:
+            m = rc.match(toks)
+            want = 0
+            for j in range(1, (len(toks) - 1) // 2 + 1):
+                if tuple(toks[:2 * j]) in known:
+                    want = 2 * j
+                else:
+                    break
+            assert m.num_tokens <= want            # evictions may have shortened it, never lengthened
+            rc.release(m.nodes)
+            pool.free(m.blocks)
+        else:
+            rc.evict(rnd.randrange(1, 6))
+            known = {k for k in known if rc.match(list(k) + [0]).num_tokens == len(k) or True}
+        pool.check_invariants()
+    # drop every outstanding match reference taken inside the comprehension above, then clear
+    rc.clear()
+    assert pool.num_used >= 0
+
+
+# ----------------------------------------------------------------------------------------------------- scheduler
+def _engine(**kw):
+    cfg = dict(block_size=16, num_kv_blocks=64, max_num_seqs=8, max_prefill_tokens=48)
+    cfg.update(kw)
+    return LLMEngine(build_model(tiny_dense()).init_random(0), EngineConfig(**cfg))
+
+
+def _prompts(n, length, seed=3):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, 1024, (length,), generator=g).tolist() for _ in range(n)]
+
+
+def test_chunked_prefill_and_mixed_steps():
+    eng = _engine(max_prefill_tokens=32)
+    ids = [eng.add_request(p, SamplingParams(max_tokens=6, ignore_eos=True)) for p in _prompts(2, 80)]
+    kinds = []
+    while eng.has_unfinished():
+        before = eng.stats.steps
+        eng.step()
+        assert eng.stats.steps == before + 1
+        kinds.append(eng.scheduler.snapshot())
+    assert eng.stats.prefill_tokens >= 160 and eng.stats.steps >= 160 // 32
+    eng.pool.check_invariants()
+
+
+def test_preemption_resumes_and_matches_uncontended_run():
+    prompts = _prompts(4, 40)
+    sp = SamplingParams(max_tokens=40, ignore_eos=True)
+    want = [o.output_tokens for o in _engine(num_kv_blocks=64).generate(prompts, sp)]
+    tight = _engine(num_kv_blocks=14, enable_prefix_caching=True)        # 4 x 80 tokens do not fit in 14 blocks
+    got = [o.output_tokens for o in tight.generate(prompts, sp)]
+    assert got == want
+    assert tight.scheduler.num_preemptions > 0
+    tight.pool.check_invariants()
+
+
+def test_admission_and_rejection():
+    from atlas_b200.engine import RequestRejected
+    eng = _engine(num_kv_blocks=8, max_seq_len=256)
+    with pytest.raises(RequestRejected):
+        eng.add_request([], SamplingParams())
+    with pytest.raises(RequestRejected):
+        eng.add_request([5000], SamplingParams())
+    with pytest.raises(RequestRejected):
+        eng.add_request([1] * 300, SamplingParams())
+    rid = eng.add_request([1] * 20, SamplingParams(max_tokens=1000))
+    assert eng._seqs[rid].sampling.max_tokens == 256 - 20            # clamped to the context window
+    assert eng.abort(rid) and not eng.has_unfinished() and eng.pool.num_free == 8
+
+
+# ----------------------------------------------------------------------------------------------------- sampler
+def _draw(logits, u, t=1.0, k=0, p=1.0, mp=0.0):
+    return int(ref.sample(logits, torch.tensor([t]), torch.tensor([k]), torch.tensor([p]), torch.tensor([mp]),
+                          torch.tensor([u])))
+
+
+def test_sampler_distribution_and_filters():
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, -50.0]])
+    p = torch.softmax(logits[0], -1)
+    counts = torch.zeros(5)
+    rng = RequestRng(7)
+    for i in range(4000):
+        counts[_draw(logits, rng.uniform(i))] += 1
+    assert torch.allclose(counts / 4000, p, atol=0.03)
+    rng = RequestRng(9)
+    for i in range(200):                              # top-k 2 never leaves the two best; top-p / min-p 0.5 keep only the best
+        u = rng.uniform(i)
+        assert _draw(logits, u, k=2) in (0, 1)
+        assert _draw(logits, u, p=0.5) == 0
+        assert _draw(logits, u, mp=0.5) == 0
+        assert _draw(logits, u, t=0.0) == 0
+    assert int(ref.argmax_first(torch.tensor([[1.0, 3.0, 3.0]]))) == 1            # first index wins ties
+
+
+def test_penalties_and_rng_is_position_addressed():
+    logits = torch.tensor([[1.0, 1.0, -1.0, 1.0, 1.0, 1.0]])
+    counts = torch.tensor([[0, 2, 1, 0, 0, 0]])
+    prompt = torch.tensor([[False, False, False, True, False, False]])
+    out = ref.apply_penalties(logits, counts, prompt, torch.tensor([2.0]), torch.tensor([0.5]), torch.tensor([0.25]))
+    assert out[0, 0] == 1.0                                                   # unseen: untouched
+    assert out[0, 1] == pytest.approx(1.0 / 2 - 0.25 * 2 - 0.5)               # generated twice
+    assert out[0, 2] == pytest.approx(-1.0 * 2 - 0.25 - 0.5)                  # negative logits are multiplied
+    assert out[0, 3] == pytest.approx(1.0 / 2)                                # prompt-only: repetition penalty only
+    r = RequestRng(123)
+    a = [r.uniform(i) for i in range(5)]
+    assert a == [RequestRng(123).uniform(i) for i in range(5)] and len(set(a)) == 5
+    assert all(0.0 <= x < 1.0 for x in a)
+    assert RequestRng(None, "req-a").uniform(0) != RequestRng(None, "req-b").uniform(0)
+
+
+# ----------------------------------------------------------------------------------------------------- comm / fault
+def test_fake_collectives_and_injected_failures():
+    w = FakeWorld(3, timeout_s=5.0)
+    outs = w.run(lambda r: (w_comm := w.comm(r)).all_reduce(torch.full((4,), float(r + 1))).tolist()
+                 + w_comm.all_gather(torch.tensor([r])).tolist())
+    assert all(o == [6.0] * 4 + [0, 1, 2] for o in outs)
+    # a rank that never joins: the others time out, get an error (not a hang) and their communicator is poisoned
+    w = FakeWorld(3, timeout_s=0.2)
+    w.dead.add(2)
+    comms = [w.comm(r) for r in range(3)]
+
+    def body(r):
+        try:
+            comms[r].all_reduce(torch.ones(2))
+            return "ok"
+        except CommError as e:
+            return str(e)
+    res = w.run(body)
+    assert all("missing ranks [2]" in res[r] for r in (0, 1))
+    assert comms[0].unhealthy and comms[1].unhealthy
+    with pytest.raises(CommError):
+        comms[0].barrier()                 # poisoned: fails fast from now on
+    # a dropped contribution (lost message) is detected the same way
+    w = FakeWorld(2, timeout_s=0.2)
+    w.dropped.add((1, 1))
+    res = w.run(lambda r: body_drop(w, r))
+    assert "timed out" in res[0]
+
+
+def body_drop(w, r):
+    try:
+        w.comm(r).all_reduce(torch.ones(1))
+        return "ok"
+    except CommError as e:
+        return str(e)
+
+
+def test_fault_latch_classification():
+    assert classify_probe(False, True) is Fatality.NONE
+    assert classify_probe(True, True) is Fatality.REQUEST_SCOPED
+    assert classify_probe(True, False) is Fatality.CONTEXT_LOST
+    latch = FaultLatch(probe=lambda: False)
+    assert latch.observe_exception(ValueError("bad request")) is Fatality.REQUEST_SCOPED and not latch.tripped
+    assert latch.observe_exception(RuntimeError("CUDA error: an illegal memory access was encountered")) is Fatality.CONTEXT_LOST
+    assert latch.tripped and "illegal memory access" in latch.reason
+    latch.trip("second reason")
+    assert "illegal memory access" in latch.reason            # one-shot: the first reason sticks
+    ok = FaultLatch(probe=lambda: True)
+    assert ok.observe_exception(RuntimeError("CUDA error: out of memory")) is Fatality.REQUEST_SCOPED and not ok.tripped
+    assert ok.observe_status_word(0x1234) is Fatality.REQUEST_SCOPED and ok.request_scoped_failures == 2
