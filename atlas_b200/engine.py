@@ -9,6 +9,7 @@ that owns the CUDA context (reference: ``crates/spark-server/src/scheduler/mod.r
 from __future__ import annotations
 
 import itertools
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Any, Callable, Dict, Hashable, List, Optional, Sequence as Seq
@@ -57,7 +58,11 @@ class LLMEngine:
         n_active = self.cfg.max_num_seqs if self.hybrid else 0
         n_snap = self.cfg.ssm_cache_slots if (self.hybrid and self.cfg.enable_prefix_caching) else 0
         self.cache: CacheStore = model.alloc_cache(num_blocks, self.cfg.block_size, self.kv_dtype, n_active + n_snap)
-        self.pool = BlockPool(num_blocks, self.cfg.block_size)
+        if os.environ.get("ATLAS_NATIVE_RUNTIME", "0") not in ("0", "", "false"):
+            from .runtime_native import NativeBlockPool          # C++ pool, same interface
+            self.pool = NativeBlockPool(num_blocks, self.cfg.block_size)
+        else:
+            self.pool = BlockPool(num_blocks, self.cfg.block_size)
         self.state_pool = SlotPool(n_active) if self.hybrid else None
         self.snapshot_base = n_active
         self.radix = RadixCache(self.pool, snapshot_slots=n_snap) if self.cfg.enable_prefix_caching else None

@@ -187,3 +187,16 @@ def test_model_config_from_hf_dir(tmp_path):
     cfg = ModelConfig.from_pretrained(path)
     assert cfg.model_type == "qwen3_next" and cfg.layer_kind(0) == "gdn" and cfg.layer_kind(1) == "attention"
     assert cfg.num_experts == 8 and cfg.shared_expert_intermediate_size == 128 and cfg.attn_output_gate
+
+
+def test_fast_loader_gives_identical_tensors(tmp_path, monkeypatch):
+    path = _save(_hf("qwen3"), tmp_path)
+    slow = Checkpoint(path)
+    monkeypatch.setenv("ATLAS_FAST_LOAD", "1")
+    fast = Checkpoint(path)
+    assert fast._fast and set(fast.keys()) == set(slow.keys())
+    for k in slow.keys():
+        a, b = slow.get(k), fast.get(k)
+        assert a.dtype == b.dtype and a.shape == b.shape and torch.equal(a, b)
+    m = load_model(path, dtype="float32", with_mtp=False)
+    assert m.layers[0].mixer.qkv.weight.shape[1] == 256
