@@ -125,6 +125,19 @@ def run(model: str = "llama3-8b", decode_batch: int = 128, ctx: int = 1152, chun
         add(f"gemm_bf16 M={M} N=8192 K={H}", ms, flops=2 * M * 8192 * H, bytes_=2 * (M * H + 8192 * H + M * 8192))
         del w, w2
 
+    if not only or "nvfp4" in only:
+        # NVFP4 weight-only GEMM: packed weights (0.5 B) + block scales (1/16 B) per weight are the HBM traffic
+        for M in (decode_batch, chunk):
+            x = torch.randn(M, max(H, I), device=dev).bfloat16()
+            for name, N, Kd in gemms:
+                pk, bs, gs = Q.quantize_nvfp4(torch.randn(N, Kd, device=dev) * 0.02)
+                xa = x[:, :Kd].contiguous()
+                out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+                ms = T.time(lambda: K.gemm_nvfp4(xa, pk, bs, gs, out=out))
+                add(f"gemm_nvfp4_w4a16 {name} M={M} N={N} K={Kd}", ms, bytes_=N * Kd * 9 // 16 + 2 * M * Kd + 2 * M * N,
+                    flops=2 * M * N * Kd)
+                del pk, bs, gs
+
     if only and only.startswith("one:"):
         # one FP8 GEMM shape, few launches, no graph: the case to put under a profiler.  only = "one:<name>:<M>"
         _, name, m_s = only.split(":")

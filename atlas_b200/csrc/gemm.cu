@@ -19,6 +19,7 @@
 
 #include "common.cuh"
 #include "host_api.h"
+#include "tmap.h"
 
 namespace atlas {
 
@@ -517,9 +518,10 @@ static EncodeTiledFn get_encode_fn() {
 struct TmapKey {
   const void* ptr;
   uint64_t rows, cols, ld;
-  uint32_t box_rows, esize;
+  uint32_t box_rows, esize, box_bytes;
   bool operator==(const TmapKey& o) const {
-    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows && esize == o.esize;
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows && esize == o.esize &&
+           box_bytes == o.box_bytes;
   }
 };
 struct TmapKeyHash {
@@ -527,18 +529,18 @@ struct TmapKeyHash {
     size_t h = reinterpret_cast<size_t>(k.ptr);
     h ^= k.rows * 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
     h ^= k.cols * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
-    h ^= (k.ld + k.box_rows * 131 + k.esize) * 0x165667B19E3779F9ull + (h << 6) + (h >> 2);
+    h ^= (k.ld + k.box_rows * 131 + k.esize + k.box_bytes * 7919) * 0x165667B19E3779F9ull + (h << 6) + (h >> 2);
     return h;
   }
 };
 
 // Row-major [rows, cols] matrix with leading dimension `ld` (elements), tiles of box_rows x 128 bytes,
 // 128-byte swizzle.  Cached: weights never move and graph-captured activations live at fixed addresses.
-static int make_tmap_kmajor(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
-                            uint32_t box_rows, uint32_t esize) {
+int make_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                 uint32_t esize, uint32_t box_bytes, bool swizzle128) {
   static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
   static std::mutex mu;
-  TmapKey key{ptr, rows, cols, ld, box_rows, esize};
+  TmapKey key{ptr, rows, cols, ld, box_rows, esize, box_bytes | (swizzle128 ? 0x80000000u : 0u)};
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) { *out = it->second; return 0; }
@@ -546,15 +548,21 @@ static int make_tmap_kmajor(CUtensorMap* out, const void* ptr, uint64_t rows, ui
   if (!enc) return -10;
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {ld * esize};
-  cuuint32_t box[2] = {128u / esize, box_rows};
+  cuuint32_t box[2] = {box_bytes / esize, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUtensorMapDataType dt = esize == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUresult r = enc(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return -11;
   if (cache.size() > 8192) cache.clear();
   cache.emplace(key, *out);
   return 0;
+}
+
+static int make_tmap_kmajor(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
+                            uint32_t box_rows, uint32_t esize) {
+  return make_tmap_2d(out, ptr, rows, cols, ld, box_rows, esize, 128u, true);
 }
 
 template <int BLOCK_N, bool FP8, bool FUSE_AR = false>

@@ -18,6 +18,8 @@ def bind(lib) -> None:
     lib.atlas_moe_gather.argtypes = [_vp, _ll, _vp, _vp, _i, _i, _vp, _vp, _vp, _ll, _vp]
     lib.atlas_moe_combine.argtypes = [_vp, _ll, _vp, _vp, _i, _i, _i, _vp, _ll, _vp, _ll, _vp]
     lib.atlas_gemm_grouped.argtypes = [_i, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _i, _vp, _vp, _i, _vp, _vp]
+    lib.atlas_gemm_w4a16.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _i, _vp, _vp]
+    lib.atlas_gemm_w4a16_grouped.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _vp, _vp, _i, _vp, _vp]
     for name, args in _GDN_SIGS.items():
         if hasattr(lib, name):
             getattr(lib, name).argtypes = args
@@ -27,16 +29,51 @@ _GDN_SIGS = {}
 
 
 # ----------------------------------------------------------------------------- NVFP4
+def _row_gscale(gscale: torch.Tensor, rows: int) -> torch.Tensor:
+    """The kernel takes one fp32 global scale per weight row; a checkpoint's scalar (or per-expert) scale is expanded
+    once and cached with the tensor."""
+    cached = _gs_cache.get(gscale.data_ptr())
+    if cached is not None and cached.numel() == rows:
+        return cached
+    g = gscale.float().reshape(-1)
+    if g.numel() == 1:
+        g = g.expand(rows)
+    elif g.numel() != rows:
+        g = g.repeat_interleave(rows // g.numel())
+    g = g.contiguous()
+    _gs_cache[gscale.data_ptr()] = g
+    return g
+
+
+_gs_cache = {}
+
+
 def gemm_nvfp4(x, packed, bscale, gscale, out=None):
-    """NVFP4 weights are widened once to bf16 (exact: an E2M1 value times an e4m3 scale fits bf16's mantissa up to the
-    fp32 global scale's rounding) and cached; the product then runs on the bf16 tcgen05 GEMM."""
-    from .. import quant as Q
-    key = packed.data_ptr()
-    w = _nvfp4_cache.get(key)
-    if w is None:
-        w = Q.dequantize_nvfp4(packed, bscale, gscale).to(torch.bfloat16).contiguous()
-        _nvfp4_cache[key] = w
-    return K.gemm_bf16(x if x.dtype == torch.bfloat16 else x.bfloat16(), w, out)
+    """``x [M,K]`` bf16 times NVFP4 weights (packed ``[N,K/2]``, e4m3 ``[N,K/16]``, global scale): the weights stay
+    packed in HBM and are widened to bf16 inside the kernel, tile by tile, on their way to the tensor cores."""
+    M, Kd = x.shape
+    N = packed.shape[0]
+    if Kd % 64 != 0:                    # not a whole number of 64-wide slices: widen once and use the bf16 GEMM
+        from .. import quant as Q
+        w = _nvfp4_cache.get(packed.data_ptr())
+        if w is None:
+            w = _nvfp4_cache[packed.data_ptr()] = Q.dequantize_nvfp4(packed, bscale, gscale).to(torch.bfloat16).contiguous()
+        return K.gemm_bf16(x if x.dtype == torch.bfloat16 else x.bfloat16(), w, out)
+    d = K._dev(x)
+    if x.dtype != torch.bfloat16:
+        x = x.bfloat16()
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    bs = bscale.view(torch.uint8)
+    gs = _row_gscale(gscale, N)
+    sms = K._num_sms[d]
+    tiles_m = (M + 127) // 128
+    bn = 128 if (N % 128 == 0 and tiles_m * (N // 128) >= sms) else 64
+    K._check(K.lib().atlas_gemm_w4a16(x.data_ptr(), packed.data_ptr(), bs.data_ptr(), gs.data_ptr(), out.data_ptr(), M, N, Kd,
+                                      x.stride(0), out.stride(0), bn, sms, K._status_ptr[d], K._stream()), "gemm_w4a16")
+    return out
 
 
 _nvfp4_cache = {}
@@ -64,6 +101,10 @@ def _expert_stacks(experts):
     if experts.kind == "fp8_block":
         out = (1, experts.w13.contiguous(), experts.w13_scale.contiguous().float(), experts.w2.contiguous(),
                experts.w2_scale.contiguous().float())
+    elif experts.kind == "nvfp4" and experts.w13.shape[2] % 32 == 0 and experts.w2.shape[2] % 32 == 0:
+        E, n1, n2 = experts.num_local, experts.w13.shape[1], experts.w2.shape[1]
+        out = (2, experts.w13.contiguous(), (experts.w13_scale.contiguous().view(torch.uint8), _row_gscale(experts.w13_gscale, E * n1)),
+               experts.w2.contiguous(), (experts.w2_scale.contiguous().view(torch.uint8), _row_gscale(experts.w2_gscale, E * n2)))
     else:
         w13, w2 = experts.dequantized() if experts.kind != "dense" else (experts.w13, experts.w2)
         out = (0, w13.to(torch.bfloat16).contiguous(), None, w2.to(torch.bfloat16).contiguous(), None)
@@ -82,7 +123,7 @@ def moe_forward(x, topk_w, topk_ids, experts, e_lo, pctx, ep_mode, addend: Optio
     dev = x.device
     kind, w13, s13, w2, s2 = _expert_stacks(experts)
     E = experts.num_local
-    N1, I = w13.shape[1], w2.shape[2]
+    N1, I = w13.shape[1], (w2.shape[2] * 2 if kind == 2 else w2.shape[2])
     max_rows = ((T * k + E * 127 + 127) // 128) * 128
     max_rows = min(max_rows, ((T * k + 127) // 128 + E) * 128)
     lib, st, sms, status = K.lib(), K._stream(), K._num_sms[d], K._status_ptr[d]
@@ -108,9 +149,14 @@ def moe_forward(x, topk_w, topk_ids, experts, e_lo, pctx, ep_mode, addend: Optio
                                       xp.data_ptr(), None, None, 0, st), "moe_gather")
         a1, a1s = xp, None
     h1 = torch.empty(max_rows, 2 * I, dtype=torch.bfloat16, device=dev)
-    K._check(lib.atlas_gemm_grouped(kind, a1.data_ptr(), w13.data_ptr(), h1.data_ptr(), K._ptr(a1s), max_rows, K._ptr(s13),
-                                    max_rows, 2 * I, H, E, H, H, 2 * I, bn_for(2 * I), tile_expert.data_ptr(),
-                                    num_tiles.data_ptr(), sms, status, st), "moe_gemm1")
+    if kind == 2:
+        K._check(lib.atlas_gemm_w4a16_grouped(a1.data_ptr(), w13.data_ptr(), s13[0].data_ptr(), s13[1].data_ptr(), h1.data_ptr(),
+                                              max_rows, 2 * I, H, E, H, 2 * I, bn_for(2 * I), tile_expert.data_ptr(),
+                                              num_tiles.data_ptr(), sms, status, st), "moe_gemm1_w4")
+    else:
+        K._check(lib.atlas_gemm_grouped(kind, a1.data_ptr(), w13.data_ptr(), h1.data_ptr(), K._ptr(a1s), max_rows, K._ptr(s13),
+                                        max_rows, 2 * I, H, E, H, H, 2 * I, bn_for(2 * I), tile_expert.data_ptr(),
+                                        num_tiles.data_ptr(), sms, status, st), "moe_gemm1")
     if kind == 1:
         aq = torch.empty(max_rows, I, dtype=FP8, device=dev)
         asc = torch.empty(I // 128, max_rows, dtype=torch.float32, device=dev)
@@ -123,9 +169,14 @@ def moe_forward(x, topk_w, topk_ids, experts, e_lo, pctx, ep_mode, addend: Optio
                                     num_tiles.data_ptr(), st), "moe_silu")
         a2, a2s = act, None
     y = torch.empty(max_rows, H, dtype=torch.bfloat16, device=dev)
-    K._check(lib.atlas_gemm_grouped(kind, a2.data_ptr(), w2.data_ptr(), y.data_ptr(), K._ptr(a2s), max_rows, K._ptr(s2),
-                                    max_rows, H, I, E, I, I, H, bn_for(H), tile_expert.data_ptr(), num_tiles.data_ptr(),
-                                    sms, status, st), "moe_gemm2")
+    if kind == 2:
+        K._check(lib.atlas_gemm_w4a16_grouped(a2.data_ptr(), w2.data_ptr(), s2[0].data_ptr(), s2[1].data_ptr(), y.data_ptr(),
+                                              max_rows, H, I, E, I, H, bn_for(H), tile_expert.data_ptr(), num_tiles.data_ptr(),
+                                              sms, status, st), "moe_gemm2_w4")
+    else:
+        K._check(lib.atlas_gemm_grouped(kind, a2.data_ptr(), w2.data_ptr(), y.data_ptr(), K._ptr(a2s), max_rows, K._ptr(s2),
+                                        max_rows, H, I, E, I, I, H, bn_for(H), tile_expert.data_ptr(), num_tiles.data_ptr(),
+                                        sms, status, st), "moe_gemm2")
     out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
     K._check(lib.atlas_moe_combine(y.data_ptr(), H, slot_of.data_ptr(), topk_w.data_ptr(), T, k, H, K._ptr(addend),
                                    addend.stride(0) if addend is not None else 0, out.data_ptr(), H, st), "moe_combine")

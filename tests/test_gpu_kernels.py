@@ -66,6 +66,26 @@ def test_gemm_fp8_block(K, M, N, K_):
     assert _rel_rms(out, want) < 5e-3
 
 
+@pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (5, 512, 256), (300, 640, 1024), (130, 200, 448), (1024, 4096, 4096)])
+def test_gemm_nvfp4_w4a16(K, M, N, K_):
+    """Packed E2M1 weights + e4m3 block scales + fp32 global scale, widened inside the kernel, against the fp32 product
+    with the dequantised weights (the widening itself is exact, so only bf16 activations / output rounding remain)."""
+    torch.manual_seed(3)
+    x = torch.randn(M, K_, device=DEV).bfloat16()
+    w = torch.randn(N, K_, device=DEV) * 0.05
+    packed, bs, gs = Q.quantize_nvfp4(w)
+    out = K.gemm_nvfp4(x, packed, bs, gs)
+    want = x.float() @ Q.dequantize_nvfp4(packed, bs, gs).t()
+    _status_ok(K)
+    assert _rel_rms(out, want) < 6e-3
+    # one global scale per output row (fused projections quantised separately)
+    gs_rows = (torch.rand(N, device=DEV) + 0.5) * gs.float().reshape(-1)[0]
+    out2 = K.gemm_nvfp4(x, packed, bs, gs_rows)
+    want2 = x.float() @ Q.dequantize_nvfp4(packed, bs, gs_rows).t()
+    _status_ok(K)
+    assert _rel_rms(out2, want2) < 6e-3
+
+
 @pytest.mark.parametrize("bn,splits", [(64, 1), (64, 4), (128, 1), (128, 3), (256, 1), (256, 2)])
 def test_gemm_tile_and_split_variants(K, monkeypatch, bn, splits):
     monkeypatch.setattr(K, "_FORCE_BLOCK_N", bn)

@@ -36,7 +36,7 @@ def test_moe_route(K, scoring, norm):
     torch.testing.assert_close(w.sort(-1).values, wr.sort(-1).values, atol=1e-5, rtol=1e-4)
 
 
-@pytest.mark.parametrize("kind", ["dense", "fp8_block"])
+@pytest.mark.parametrize("kind", ["dense", "fp8_block", "nvfp4"])
 @pytest.mark.parametrize("T", [5, 300])
 def test_moe_forward(K, kind, T):
     torch.manual_seed(1)
@@ -47,6 +47,9 @@ def test_moe_forward(K, kind, T):
     x = torch.randn(T, H, device=DEV).bfloat16()
     tw, ti = ref.moe_route(torch.randn(T, E, device=DEV), k, True)
     out = K.moe_forward(x, tw.contiguous(), ti.contiguous(), ex, 0, None, "auto")
+    if kind == "nvfp4":
+        from atlas_b200.ops import cuda_ext
+        assert cuda_ext._expert_stacks(ex)[0] == 2          # packed weights go to the W4A16 kernel, not a widened copy
     d13, d2 = ex.dequantized()
     want = ref.moe_experts(x, d13, d2, tw, ti, 0)
     torch.cuda.synchronize()
