@@ -46,6 +46,19 @@ int atlas_moe_gather(const void* x, long long ldx, const int* row_token, const i
                      void* y, void* q, float* scale, long long scale_ld, void* stream);
 int atlas_moe_combine(const void* y, long long ldy, const int* slot_of, const float* topk_w, int T, int k, int H,
                       const void* addend, long long ld_add, void* out, long long ldo, void* stream);
+int atlas_moe_dispatch_prep(const int* topk_ids, int pairs, int experts_per_rank, int world, int* send_off, int* pos,
+                            void* stream);
+int atlas_moe_dispatch_pack(const void* x, long long ldx, const int* topk_ids, const int* pos, int T, int k, int H,
+                            void* send, int row_bytes, void* stream);
+int atlas_moe_recv_ids(const void* recv, int row_bytes, int H, const int* recv_off, int world, int cap_rows, int* ids,
+                       void* stream);
+int atlas_gemm_w4a16(const void* A, const void* packed, const void* bscale, const float* gscale, void* C, int M, int N,
+                     int K, long long lda, long long ldc, int block_n, int num_sms, unsigned long long* status,
+                     void* stream);
+int atlas_gemm_w4a16_grouped(const void* A, const void* packed, const void* bscale, const float* gscale, void* C,
+                             int max_rows, int N, int K, int E, long long lda, long long ldc, int block_n,
+                             const int* tile_expert, const int* num_m_tiles, int num_sms, unsigned long long* status,
+                             void* stream);
 int atlas_gemm_grouped(int kind, const void* A, const void* B, void* C, const float* a_scale, long long sa_k,
                        const float* b_scale, int max_rows, int N, int K, int E, long long lda, long long ldb,
                        long long ldc, int block_n, const int* tile_expert, const int* num_m_tiles, int num_sms,

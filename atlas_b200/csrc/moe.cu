@@ -194,6 +194,55 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ y, long long ldy, const int
   *reinterpret_cast<uint4*>(out + (long long)t * ldo + e) = o;
 }
 
+// ---------------------------------------------------------------------------- expert-parallel dispatch
+// Rank r owns experts [r * experts_per_rank, (r + 1) * experts_per_rank).  One block: histogram of destination ranks
+// over all (token, k) pairs, prefix sums -> send_off[world + 1], and the position of every pair inside its
+// destination's segment (pos[pair]).  Positions come from shared-memory cursors, so the order inside a segment is
+// arbitrary; nothing downstream depends on it (results are summed per token in k order).
+__global__ void __launch_bounds__(1024)
+moe_dispatch_prep_kernel(const int* __restrict__ topk_ids, int pairs, int experts_per_rank, int world,
+                         int* __restrict__ send_off, int* __restrict__ pos) {
+  __shared__ int cnt[8], cursor[8];
+  if (threadIdx.x < 8) cnt[threadIdx.x] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int d = min(max(topk_ids[p] / experts_per_rank, 0), world - 1);
+    atomicAdd(&cnt[d], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int off = 0;
+    for (int d = 0; d < world; ++d) { send_off[d] = off; cursor[d] = off; off += cnt[d]; }
+    send_off[world] = off;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int d = min(max(topk_ids[p] / experts_per_rank, 0), world - 1);
+    pos[p] = atomicAdd(&cursor[d], 1);
+  }
+}
+
+// send row layout: H bf16 activations followed by a 16-byte trailer {expert id, 0, 0, 0}
+__global__ void __launch_bounds__(256)
+moe_dispatch_pack_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const int* __restrict__ topk_ids,
+                         const int* __restrict__ pos, int k, int H, uint8_t* __restrict__ send, int row_bytes) {
+  const int pair = blockIdx.x;
+  const int t = pair / k;
+  uint8_t* dst = send + (size_t)pos[pair] * row_bytes;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (long long)t * ldx);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = src[i];
+  if (threadIdx.x == 0) *reinterpret_cast<int4*>(dst + (size_t)H * 2) = make_int4(topk_ids[pair], 0, 0, 0);
+}
+
+// expert ids of the received rows; rows past the live count (recv_off[world]) get -1 so that they take no work
+__global__ void __launch_bounds__(256)
+moe_recv_ids_kernel(const uint8_t* __restrict__ recv, int row_bytes, int H, const int* __restrict__ recv_off, int world,
+                    int cap_rows, int* __restrict__ ids) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= cap_rows) return;
+  ids[r] = r < recv_off[world] ? *reinterpret_cast<const int*>(recv + (size_t)r * row_bytes + (size_t)H * 2) : -1;
+}
+
 }  // namespace atlas
 
 using namespace atlas;
@@ -236,5 +285,31 @@ extern "C" int atlas_moe_combine(const void* y, long long ldy, const int* slot_o
   moe_combine_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(y), ldy, slot_of, topk_w, k, H, reinterpret_cast<const __nv_bfloat16*>(addend),
       ld_add, reinterpret_cast<__nv_bfloat16*>(out), ldo);
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+// Expert-parallel dispatch helpers (see the kernels above).  `pairs` = T * k.
+extern "C" int atlas_moe_dispatch_prep(const int* topk_ids, int pairs, int experts_per_rank, int world, int* send_off,
+                                       int* pos, void* stream) {
+  if (world < 1 || world > 8 || experts_per_rank < 1) return -1;
+  moe_dispatch_prep_kernel<<<1, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(topk_ids, pairs, experts_per_rank, world,
+                                                                                   send_off, pos);
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+extern "C" int atlas_moe_dispatch_pack(const void* x, long long ldx, const int* topk_ids, const int* pos, int T, int k, int H,
+                                       void* send, int row_bytes, void* stream) {
+  if (H % 8 || row_bytes < H * 2 + 16 || row_bytes % 16) return -1;
+  if (T * k == 0) return 0;
+  moe_dispatch_pack_kernel<<<T * k, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), ldx, topk_ids, pos, k, H, reinterpret_cast<uint8_t*>(send), row_bytes);
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+extern "C" int atlas_moe_recv_ids(const void* recv, int row_bytes, int H, const int* recv_off, int world, int cap_rows, int* ids,
+                                  void* stream) {
+  if (cap_rows <= 0) return 0;
+  moe_recv_ids_kernel<<<(cap_rows + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint8_t*>(recv), row_bytes, H, recv_off, world, cap_rows, ids);
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
 }

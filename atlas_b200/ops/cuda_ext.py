@@ -18,6 +18,9 @@ def bind(lib) -> None:
     lib.atlas_moe_gather.argtypes = [_vp, _ll, _vp, _vp, _i, _i, _vp, _vp, _vp, _ll, _vp]
     lib.atlas_moe_combine.argtypes = [_vp, _ll, _vp, _vp, _i, _i, _i, _vp, _ll, _vp, _ll, _vp]
     lib.atlas_gemm_grouped.argtypes = [_i, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _i, _vp, _vp, _i, _vp, _vp]
+    lib.atlas_moe_dispatch_prep.argtypes = [_vp, _i, _i, _i, _vp, _vp, _vp]
+    lib.atlas_moe_dispatch_pack.argtypes = [_vp, _ll, _vp, _vp, _i, _i, _i, _vp, _i, _vp]
+    lib.atlas_moe_recv_ids.argtypes = [_vp, _i, _i, _vp, _i, _i, _vp, _vp]
     lib.atlas_gemm_w4a16.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _i, _vp, _vp]
     lib.atlas_gemm_w4a16_grouped.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _i, _vp, _vp, _i, _vp, _vp]
     for name, args in _GDN_SIGS.items():
@@ -116,7 +119,86 @@ def _expert_stacks(experts):
 
 def moe_forward(x, topk_w, topk_ids, experts, e_lo, pctx, ep_mode, addend: Optional[torch.Tensor] = None):
     """Expert-sorted grouped FFN over this rank's experts.  Pairs routed to other ranks' experts contribute nothing
-    here; with expert parallelism the partial outputs are summed across ranks."""
+    here; with expert parallelism the partial outputs are summed across ranks (``allreduce`` mode, the default while
+    activations are replicated across the group) or the rows travel to their experts and back (``alltoall`` mode)."""
+    if ep_mode == "alltoall" and pctx is not None and pctx.ep_size > 1:
+        comm = pctx.ep_comm if pctx.ep_comm is not None else pctx.comm
+        if hasattr(comm, "all_to_all_rows"):
+            out = _moe_forward_alltoall(x, topk_w, topk_ids, experts, e_lo, pctx, comm, addend)
+            if out is not None:
+                return out
+    out = _moe_local(x, topk_w, topk_ids, experts, e_lo, addend)
+    if pctx is not None and pctx.ep_size > 1:
+        comm = pctx.ep_comm if pctx.ep_comm is not None else pctx.comm
+        if comm is not None:
+            out = comm.all_reduce(out)
+    return out
+
+
+def _moe_forward_alltoall(x, topk_w, topk_ids, experts, e_lo, pctx, comm, addend):
+    """Dispatch / combine over peer memory.  Activations are replicated across the group, so rank r dispatches only its
+    slice of the tokens: every (token, expert) pair is computed exactly once, on the rank that owns the expert.
+
+    1. destination rank of every pair, segment offsets and positions (one kernel), rows packed with their expert id;
+    2. all-to-all #1 (peer stores, device-side counts): rows arrive grouped by source rank;
+    3. grouped expert FFN over the received rows (each row is one pair, weight 1);
+    4. all-to-all #2 with the received offsets as send offsets: results return in the order they were sent;
+    5. weighted sum over k (router probabilities) + addend at the source, then the token slices are put together.
+    Returns None when the rows do not fit the symmetric slot (the caller falls back to the all-reduce form)."""
+    T, H = x.shape
+    k = topk_ids.shape[1]
+    W, r = pctx.ep_size, pctx.ep_rank
+    d = K._dev(x)
+    dev = x.device
+    lib, st = K.lib(), K._stream()
+    per = (T + W - 1) // W
+    t0, t1 = min(T, r * per), min(T, (r + 1) * per)
+    Ts = t1 - t0
+    pairs_cap = per * k                              # same on every rank: region capacity per source
+    row_bytes = H * 2 + 16
+    if (16 + pairs_cap * row_bytes) * W > comm.slot_bytes or H % 8:
+        return None
+    e_per_rank = experts.num_local
+    ids = topk_ids[t0:t1].contiguous()
+    w = topk_w[t0:t1].contiguous()
+    send_off = torch.empty(W + 1, dtype=torch.int32, device=dev)
+    pos = torch.empty(max(1, Ts * k), dtype=torch.int32, device=dev)
+    K._check(lib.atlas_moe_dispatch_prep(ids.data_ptr(), Ts * k, e_per_rank, W, send_off.data_ptr(), pos.data_ptr(), st),
+             "moe_dispatch_prep")
+    send = torch.empty(max(1, Ts * k), row_bytes // 2, dtype=torch.bfloat16, device=dev)
+    xs = x[t0:t1]
+    if Ts:
+        K._check(lib.atlas_moe_dispatch_pack(xs.data_ptr(), x.stride(0), ids.data_ptr(), pos.data_ptr(), Ts, k, H,
+                                             send.data_ptr(), row_bytes, st), "moe_dispatch_pack")
+    recv, recv_off = comm.all_to_all_rows(send, send_off, pairs_cap)
+    cap = pairs_cap * W
+    rid = torch.empty(cap, 1, dtype=torch.int32, device=dev)
+    K._check(lib.atlas_moe_recv_ids(recv.data_ptr(), row_bytes, H, recv_off.data_ptr(), W, cap, rid.data_ptr(), st),
+             "moe_recv_ids")
+    ones = _ones(cap, dev)
+    y_rows = _moe_local(recv[:, :H], ones, rid, experts, e_lo, None)          # [cap, H]; dead rows are zero
+    back, _ = comm.all_to_all_rows(y_rows, recv_off, pairs_cap)
+    out = torch.zeros(T, H, dtype=torch.bfloat16, device=dev)
+    if Ts:
+        ad = addend[t0:t1] if addend is not None else None
+        K._check(lib.atlas_moe_combine(back.data_ptr(), H, pos.data_ptr(), w.data_ptr(), Ts, k, H, K._ptr(ad),
+                                       addend.stride(0) if addend is not None else 0, out[t0:t1].data_ptr(), H, st),
+                 "moe_combine_ep")
+    return comm.all_reduce(out)             # slices are disjoint: the sum just places them
+
+
+_ones_cache = {}
+
+
+def _ones(n: int, dev) -> torch.Tensor:
+    t = _ones_cache.get((n, dev))
+    if t is None:
+        t = _ones_cache[(n, dev)] = torch.ones(n, 1, dtype=torch.float32, device=dev)
+    return t
+
+
+def _moe_local(x, topk_w, topk_ids, experts, e_lo, addend: Optional[torch.Tensor] = None):
+    """Local experts only: align -> gather (+quant) -> grouped GEMM -> SiLU*mul -> grouped GEMM -> weighted combine."""
     T, H = x.shape
     k = topk_ids.shape[1]
     d = K._dev(x)
@@ -180,10 +262,6 @@ def moe_forward(x, topk_w, topk_ids, experts, e_lo, pctx, ep_mode, addend: Optio
     out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
     K._check(lib.atlas_moe_combine(y.data_ptr(), H, slot_of.data_ptr(), topk_w.data_ptr(), T, k, H, K._ptr(addend),
                                    addend.stride(0) if addend is not None else 0, out.data_ptr(), H, st), "moe_combine")
-    if pctx is not None and pctx.ep_size > 1:
-        comm = pctx.ep_comm if pctx.ep_comm is not None else pctx.comm
-        if comm is not None:
-            out = comm.all_reduce(out)
     return out
 
 
