@@ -51,6 +51,8 @@ def load() -> None:
                                       _i, _i, _i, _vp, _vp, _vp, _vp]
     lib.atlas_attn_prefill.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _f, _f, _f, _i,
                                        _i, _i, _i, _i, _vp]
+    lib.atlas_attn_prefill_tc.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _f, _f, _f,
+                                          _i, _i, _i, _i, _i, _vp, _vp]
     lib.atlas_argmax.argtypes = [_vp, _ll, _i, _i, _i, _vp, _vp]
     lib.atlas_sample.argtypes = [_vp, _ll, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]
     lib.atlas_spec_accept.argtypes = [_vp, _vp, _i, _i, _vp, _vp]
@@ -319,6 +321,28 @@ def paged_attention(q, k_cache, v_cache, batch, scale, k_scale, v_scale, sliding
                                        batch.query_start_loc.data_ptr(), 0, nd, float(scale), float(k_scale),
                                        float(v_scale), Hq, Hkv, D, bs, window, splits, _ptr(po), _ptr(pml), _status_ptr[d], st),
                "attn_decode")
+    if batch.num_seqs > nd and _tc_prefill_ok(q, Hq, Hkv, D, bs, window, k_cache):
+        # tensor-core (tcgen05) chunk attention: tiles of 128 / G query tokens, all G heads of a kv head per tile
+        tok = 128 // (Hq // Hkv)
+        tiles = getattr(batch, "_attn_tiles_tc", None)
+        if tiles is None or tiles[2] != tok:
+            ts, tq = [], []
+            for i in range(nd, batch.num_seqs):
+                for q0 in range(0, batch.query_lens_host[i], tok):
+                    ts.append(i)
+                    tq.append(q0)
+            host = torch.tensor([ts, tq], dtype=torch.int32).pin_memory()
+            tiles = (host.to(q.device, non_blocking=True), len(ts), tok)
+            batch._attn_tiles_tc = tiles
+        tdev, n_tiles, _ = tiles
+        rc = lib().atlas_attn_prefill_tc(q.data_ptr(), q.stride(0), out.data_ptr(), Hq * D, k_cache.data_ptr(),
+                                         v_cache.data_ptr(), bt.data_ptr(), bt.stride(0), batch.seq_lens.data_ptr(),
+                                         batch.query_start_loc.data_ptr(), tdev[0].data_ptr(), tdev[1].data_ptr(), n_tiles,
+                                         T, float(scale), float(k_scale), float(v_scale), Hq, Hkv, D, bs, window,
+                                         _status_ptr[d], st)
+        if rc != 1:
+            _check(rc, "attn_prefill_tc")
+            return out
     if batch.num_seqs > nd:
         tiles = getattr(batch, "_attn_tiles", None)
         if tiles is None:
@@ -337,6 +361,14 @@ def paged_attention(q, k_cache, v_cache, batch, scale, k_scale, v_scale, sliding
                                         n_tiles, float(scale), float(k_scale), float(v_scale), Hq, Hkv, D, bs, window,
                                         st), "attn_prefill")
     return out
+
+
+_TC_PREFILL = os.environ.get("ATLAS_ATTN_TC", "1") not in ("0", "false")
+
+
+def _tc_prefill_ok(q, Hq, Hkv, D, bs, window, k_cache) -> bool:
+    return (_TC_PREFILL and D == 128 and bs == 16 and not window and Hq % Hkv == 0 and (Hq // Hkv) in (1, 2, 4, 8)
+            and q.dtype == torch.bfloat16 and k_cache.dtype == torch.float8_e4m3fn)
 
 
 # ----------------------------------------------------------------------------- sampling

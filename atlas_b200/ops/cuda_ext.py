@@ -34,17 +34,21 @@ _GDN_SIGS = {}
 # ----------------------------------------------------------------------------- NVFP4
 def _row_gscale(gscale: torch.Tensor, rows: int) -> torch.Tensor:
     """The kernel takes one fp32 global scale per weight row; a checkpoint's scalar (or per-expert) scale is expanded
-    once and cached with the tensor."""
-    cached = _gs_cache.get(gscale.data_ptr())
-    if cached is not None and cached.numel() == rows:
-        return cached
+    once and cached.  The cache entry keeps the source tensor alive, so its address cannot be handed to another tensor
+    while the entry exists."""
+    key = (gscale.data_ptr(), rows)
+    hit = _gs_cache.get(key)
+    if hit is not None and hit[0] is gscale:
+        return hit[1]
     g = gscale.float().reshape(-1)
     if g.numel() == 1:
         g = g.expand(rows)
     elif g.numel() != rows:
         g = g.repeat_interleave(rows // g.numel())
     g = g.contiguous()
-    _gs_cache[gscale.data_ptr()] = g
+    if len(_gs_cache) > 8192:
+        _gs_cache.clear()
+    _gs_cache[key] = (gscale, g)
     return g
 
 
@@ -58,9 +62,10 @@ def gemm_nvfp4(x, packed, bscale, gscale, out=None):
     N = packed.shape[0]
     if Kd % 64 != 0:                    # not a whole number of 64-wide slices: widen once and use the bf16 GEMM
         from .. import quant as Q
-        w = _nvfp4_cache.get(packed.data_ptr())
-        if w is None:
-            w = _nvfp4_cache[packed.data_ptr()] = Q.dequantize_nvfp4(packed, bscale, gscale).to(torch.bfloat16).contiguous()
+        hit = _nvfp4_cache.get(packed.data_ptr())
+        if hit is None or hit[0] is not packed:
+            hit = _nvfp4_cache[packed.data_ptr()] = (packed, Q.dequantize_nvfp4(packed, bscale, gscale).to(torch.bfloat16).contiguous())
+        w = hit[1]
         return K.gemm_bf16(x if x.dtype == torch.bfloat16 else x.bfloat16(), w, out)
     d = K._dev(x)
     if x.dtype != torch.bfloat16:

@@ -215,6 +215,20 @@ def test_attention_prefill_and_mixed(K, D, Hq, Hkv):
     torch.testing.assert_close(out.float(), want.float(), atol=3e-2, rtol=5e-2)
 
 
+@pytest.mark.parametrize("Hq,Hkv", [(8, 2), (32, 8), (4, 4), (16, 2), (8, 4)])
+def test_attention_prefill_tcgen05(K, Hq, Hkv, monkeypatch):
+    """Chunk attention on the tcgen05 path (head_dim 128, 16-token pages, FP8 cache): several GQA group sizes, chunks
+    that start inside a context, span many KV tiles and end inside a page; it must agree with the fp32 oracle and with
+    the general kernel."""
+    qlens, ctxs = [300, 1, 37, 513, 128], [0, 90, 1000, 77, 256]
+    out, want = _attention_case(K, 128, Hq, Hkv, qlens=qlens, ctxs=ctxs)
+    assert _rel_rms(out, want) < 2e-2
+    torch.testing.assert_close(out.float(), want.float(), atol=3e-2, rtol=5e-2)
+    monkeypatch.setattr(K, "_TC_PREFILL", False)
+    old, _ = _attention_case(K, 128, Hq, Hkv, qlens=qlens, ctxs=ctxs)
+    assert _rel_rms(out, old) < 2e-2
+
+
 def test_attention_sliding_window_and_big_pages(K):
     out, want = _attention_case(K, 128, 8, 2, qlens=[1, 1, 50], ctxs=[300, 40, 90], bs=64, window=64)
     assert _rel_rms(out, want) < 2e-2
