@@ -73,6 +73,7 @@ class LLMEngine:
                                                          and self.cfg.num_drafts > 0) else None
         self.stats = EngineStats()
         self.control = None               # parallel.worker.StepControl when several processes serve one model
+        self._eos_set = frozenset(self.mcfg.eos_ids())
         self.time_device = False          # accumulate CUDA-event time of each step's GPU work
         self.device_phase_ms: Dict[str, list] = {}     # phase -> [ms, steps] (steps with any multi-token item count as prefill)
         self.device_time_ms = 0.0
@@ -330,9 +331,9 @@ class LLMEngine:
         """Append sampled tokens, stopping at EOS / stop ids / max_tokens.  Returns the tokens kept."""
         p = seq.sampling
         kept: List[int] = []
-        eos = set() if p.ignore_eos else set(self.mcfg.eos_ids())
-        stop_ids = set(p.stop_token_ids)
-        checker = self._stop_checkers.get(seq.request_id)
+        eos = _EMPTY if p.ignore_eos else self._eos_set
+        stop_ids = p.stop_token_ids if len(p.stop_token_ids) < 4 else set(p.stop_token_ids)
+        checker = self._stop_checkers.get(seq.request_id) if self._stop_checkers else None
         for j, t in enumerate(toks):
             if seq.first_token_time is None:
                 seq.first_token_time = now
@@ -360,9 +361,10 @@ class LLMEngine:
     def _make_output(self, seq: Sequence, new_tokens: List[int]) -> RequestOutput:
         ttft = (seq.first_token_time - seq.arrival) if seq.first_token_time else None
         dec = (seq.finish_time - seq.first_token_time) if (seq.finish_time and seq.first_token_time) else None
-        return RequestOutput(seq.request_id, new_tokens, list(seq.output_tokens), seq.finished,
+        # output_tokens / logprobs are the sequence's own lists (not copies: a copy per step per request is quadratic)
+        return RequestOutput(seq.request_id, new_tokens, seq.output_tokens, seq.finished,
                              seq.finish_reason.value if seq.finish_reason else None, len(seq.prompt_tokens),
-                             seq.num_cached_tokens, ttft, dec, list(seq.logprobs) if seq.logprobs else None,
+                             seq.num_cached_tokens, ttft, dec, seq.logprobs if seq.logprobs else None,
                              seq.spec_accepted)
 
     # ------------------------------------------------------------------ convenience
@@ -409,6 +411,9 @@ class _RowView:
     @property
     def output_tokens(self) -> List[int]:
         return self._seq.output_tokens + self._seq.drafts[:self._k]
+
+
+_EMPTY = frozenset()
 
 
 def _make_verdict(records, dt):

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Tuple
 
+import numpy as np
 import torch
 
 from .config import EngineConfig
@@ -40,67 +41,97 @@ class ModelRunner:
         self._pin: Dict[str, torch.Tensor] = {}
 
     # ------------------------------------------------------------------ batch assembly
-    def _stage(self, name: str, data: List[int], dtype: torch.dtype) -> torch.Tensor:
-        """Host list -> device tensor through a reusable pinned buffer (one async H2D copy)."""
-        n = len(data)
+    def _stage(self, name: str, data, dtype: torch.dtype) -> torch.Tensor:
+        """Host list / numpy array -> device tensor through a reusable pinned buffer (one async H2D copy)."""
+        src = torch.from_numpy(data) if isinstance(data, np.ndarray) else torch.tensor(data, dtype=dtype)
+        if src.dtype != dtype:
+            src = src.to(dtype)
+        n = src.numel()
         if not self.on_gpu:
-            return torch.tensor(data, dtype=dtype)
+            return src.reshape(-1)
         buf = self._pin.get(name)
         if buf is None or buf.numel() < n or buf.dtype != dtype:
             cap = max(1024, 1 << (max(n, 1) - 1).bit_length())
             buf = torch.empty(cap, dtype=dtype, pin_memory=True)
             self._pin[name] = buf
         host = buf[:n]
-        host.copy_(torch.tensor(data, dtype=dtype))
-        self.h2d_bytes += host.numel() * host.element_size()
+        host.copy_(src.reshape(-1))
+        self.h2d_bytes += n * host.element_size()
         return host.to(self.device, non_blocking=True)
+
+    @staticmethod
+    def _blocks_np(seq) -> np.ndarray:
+        """Block table of a sequence as a cached int32 array (rebuilt only when the list changed length)."""
+        cached = getattr(seq, "_blocks_cache", None)
+        blocks = seq.blocks
+        if cached is None or cached[0] != len(blocks) or cached[2] is not blocks:
+            cached = (len(blocks), np.asarray(blocks, dtype=np.int32), blocks)
+            seq._blocks_cache = cached
+        elif len(blocks) and cached[1][-1] != blocks[-1]:
+            cached = (len(blocks), np.asarray(blocks, dtype=np.int32), blocks)
+            seq._blocks_cache = cached
+        return cached[1]
 
     def build_batch(self, out: SchedulerOutput, snapshot_base: int = 0) -> ForwardBatch:
         bs = self.bs
-        ids: List[int] = []
-        pos: List[int] = []
-        slots: List[int] = []
-        qsl = [0]
-        sl: List[int] = []
-        qlens: List[int] = []
-        tables: List[List[int]] = []
-        state_slots: List[int] = []
-        has_state: List[bool] = []
-        num_dec = 0
+        items = out.items
+        B = len(items)
+        tabs = [self._blocks_np(it.seq) for it in items]
+        maxb = max(t.shape[0] for t in tabs)
+        table = np.zeros((B, maxb), dtype=np.int32)
+        for i, t in enumerate(tabs):
+            table[i, :t.shape[0]] = t
+        state_slots = [it.seq.state_slot if it.seq.state_slot is not None else 0 for it in items]
+        has_state = [it.seq.has_state for it in items]
         spec_verify = False
-        for it in out.items:
-            seq = it.seq
-            if it.verify_drafts:
-                toks = [seq.all_tokens[it.start]] + list(seq.drafts[:it.verify_drafts])
-                spec_verify = True
-            else:
-                toks = seq.all_tokens[it.start:it.start + it.num_tokens]
-            if it.is_decode:
-                num_dec += 1
-            blocks = seq.blocks
-            for j, t in enumerate(toks):
-                p = it.start + j
-                ids.append(t)
-                pos.append(p)
-                slots.append(blocks[p // bs] * bs + p % bs)
-            qsl.append(qsl[-1] + len(toks))
-            sl.append(it.start + len(toks))
-            qlens.append(len(toks))
-            tables.append(blocks)
-            state_slots.append(seq.state_slot if seq.state_slot is not None else 0)
-            has_state.append(seq.has_state)
-        B = len(out.items)
-        maxb = max(len(t) for t in tables)
-        flat_tables: List[int] = []
-        for t in tables:
-            flat_tables.extend(t)
-            flat_tables.extend([0] * (maxb - len(t)))
+        if all(it.num_tokens == 1 and not it.verify_drafts for it in items):
+            # every row is one token of one sequence (decode, or a one-token chunk): vectorised
+            starts = np.fromiter((it.start for it in items), dtype=np.int64, count=B)
+            ids = np.fromiter((it.seq.token_at(it.start) for it in items), dtype=np.int64, count=B)
+            pos = starts.astype(np.int32)
+            blk = table[np.arange(B), starts // bs]
+            slots = (blk.astype(np.int64) * bs + starts % bs).astype(np.int32)
+            qsl = np.arange(B + 1, dtype=np.int32)
+            sl_np = (starts + 1).astype(np.int32)
+            sl = sl_np.tolist()
+            qlens = [1] * B
+            num_dec = sum(1 for it in items if it.is_decode)
+        else:
+            ids_l: List[int] = []
+            pos_l: List[int] = []
+            slots_l: List[int] = []
+            qsl_l = [0]
+            sl = []
+            qlens = []
+            num_dec = 0
+            for i, it in enumerate(items):
+                seq = it.seq
+                if it.verify_drafts:
+                    toks = [seq.token_at(it.start)] + list(seq.drafts[:it.verify_drafts])
+                    spec_verify = True
+                else:
+                    toks = seq.tokens_range(it.start, it.start + it.num_tokens)
+                if it.is_decode:
+                    num_dec += 1
+                n = len(toks)
+                p = np.arange(it.start, it.start + n, dtype=np.int64)
+                ids_l.extend(toks)
+                pos_l.append(p)
+                slots_l.append(tabs[i][p // bs].astype(np.int64) * bs + p % bs)
+                qsl_l.append(qsl_l[-1] + n)
+                sl.append(it.start + n)
+                qlens.append(n)
+            ids = np.asarray(ids_l, dtype=np.int64)
+            pos = np.concatenate(pos_l).astype(np.int32)
+            slots = np.concatenate(slots_l).astype(np.int32)
+            qsl = np.asarray(qsl_l, dtype=np.int32)
+            sl_np = np.asarray(sl, dtype=np.int32)
         fb = ForwardBatch(
             input_ids=self._stage("ids", ids, torch.int64),
             positions=self._stage("pos", pos, torch.int32),
             slot_mapping=self._stage("slots", slots, torch.int32),
-            block_tables=self._stage("tables", flat_tables, torch.int32).view(B, maxb),
-            seq_lens=self._stage("sl", sl, torch.int32),
+            block_tables=self._stage("tables", table, torch.int32).view(B, maxb),
+            seq_lens=self._stage("sl", sl_np, torch.int32),
             query_start_loc=self._stage("qsl", qsl, torch.int32),
             num_decodes=num_dec, max_query_len=max(qlens), max_seq_len=max(sl),
             seq_lens_host=sl, query_lens_host=qlens, spec_verify=spec_verify,

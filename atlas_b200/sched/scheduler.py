@@ -304,6 +304,7 @@ class Scheduler:
         if len(seq.blocks) > keep:
             extra = seq.blocks[keep:]
             del seq.blocks[keep:]
+            seq._blocks_cache = None        # the runner's array view of the table is stale now
             self.pool.free(extra)
 
     def snapshot(self) -> Dict[str, int]:

@@ -68,6 +68,19 @@ class Sequence:
     def all_tokens(self) -> List[int]:
         return self.prompt_tokens + self.output_tokens
 
+    def token_at(self, pos: int) -> int:
+        n = len(self.prompt_tokens)
+        return self.prompt_tokens[pos] if pos < n else self.output_tokens[pos - n]
+
+    def tokens_range(self, lo: int, hi: int) -> List[int]:
+        """``all_tokens[lo:hi]`` without building the concatenated list."""
+        n = len(self.prompt_tokens)
+        if hi <= n:
+            return self.prompt_tokens[lo:hi]
+        if lo >= n:
+            return self.output_tokens[lo - n:hi - n]
+        return self.prompt_tokens[lo:] + self.output_tokens[:hi - n]
+
     @property
     def num_tokens(self) -> int:
         return len(self.prompt_tokens) + len(self.output_tokens)
