@@ -163,6 +163,210 @@ gdn_recurrent_kernel(const GdnParams p) {
   }
 }
 
+
+// ---------------------------------------------------------------------------- chunked form (prefill)
+// The same recurrence evaluated 64 tokens at a time on the tensor cores (TF32 mma.sync, fp32 state and accumulation).
+// With G_i the running sum of the log-decays inside the chunk and h0 the state at its start:
+//   (I + A) D = B,   A_ij = beta_i e^{G_i - G_j} (k_i . k_j)  (j < i),   B_i = beta_i (v_i - e^{G_i} h0^T k_i)
+//   o_i = e^{G_i} h0^T q_i + sum_{j <= i} e^{G_i - G_j} (q_i . k_j) D_j
+//   h   = e^{G_C} h0 + sum_j e^{G_C - G_j} k_j (x) D_j
+// so one chunk is six small matrix products plus a 64-step forward substitution in which every thread owns one value
+// column (no synchronisation inside the solve).  One CTA per (value head, sequence) walks its chunks in order; the
+// state stays in shared memory between chunks.  Decays are differences of non-positive running sums, so every
+// exponential is <= 1.  Reference ops replaced: gated_delta_rule_fla.cu / gated_delta_rule_chunk*.cu (WY chunk form).
+constexpr int kGC = 64;          // chunk length
+constexpr int kGLd = 132;        // leading dimension of the [.][128] fp32 tiles (padding spreads banks)
+constexpr int kGLdS = 68;        // leading dimension of the [64][64] tiles
+
+ATLAS_DEVICE uint32_t to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(r) : "f"(x));
+  return r;
+}
+ATLAS_DEVICE void mma_tf32(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+// c (16 x 8 tile at m0, n0) += A[m0.., 0..K) * B[0..K, n0..); a_at(m, k) and b_at(k, n) read fp32 from shared memory
+template <typename FA, typename FB>
+ATLAS_DEVICE void warp_tile_tf32(float (&c)[4], int m0, int n0, int K, FA a_at, FB b_at, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  for (int k0 = 0; k0 < K; k0 += 8) {
+    uint32_t a[4] = {to_tf32(a_at(m0 + g, k0 + t)), to_tf32(a_at(m0 + g + 8, k0 + t)), to_tf32(a_at(m0 + g, k0 + t + 4)),
+                     to_tf32(a_at(m0 + g + 8, k0 + t + 4))};
+    uint32_t b[2] = {to_tf32(b_at(k0 + t, n0 + g)), to_tf32(b_at(k0 + t + 4, n0 + g))};
+    mma_tf32(c, a, b);
+  }
+}
+
+__global__ void __launch_bounds__(256, 1)
+gdn_chunk_kernel(const GdnParams p) {
+  constexpr int DK = 128, DV = 128;
+  extern __shared__ float gsm[];
+  float* sh = gsm;                          // state [DK][kGLd]
+  float* sK = sh + DK * kGLd;               // [64][kGLd]
+  float* sQ = sK + kGC * kGLd;
+  float* sV = sQ + kGC * kGLd;              // v, then B, then D (in place)
+  float* sA = sV + kGC * kGLd;              // [64][kGLdS]
+  float* sP = sA + kGC * kGLdS;
+  float* sG = sP + kGC * kGLdS;             // running log-decay [64]
+  float* sBeta = sG + kGC;                  // [64]
+  float* sE = sBeta + kGC;                  // e^{G_i}
+  float* sW = sE + kGC;                     // e^{G_C - G_i}
+  const int hv = blockIdx.x, bseq = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int hk = hv / (p.Hv / p.Hk);
+  const int q0 = p.query_start_loc[bseq];
+  const int n = p.query_start_loc[bseq + 1] - q0;
+  if (n <= 0) return;
+  const long long slot = p.state_slots[bseq];
+  float* hs = p.h + ((slot * p.Hv + hv) * (long long)DK) * DV;
+  const bool live = p.has_state[bseq] != 0;
+  for (int i = tid; i < DK * DV; i += 256) sh[(i >> 7) * kGLd + (i & 127)] = live ? hs[i] : 0.f;
+  const float neg_a = -__expf(p.A_log[hv]);
+  const float dtb = p.dt_bias[hv];
+  const int kd = p.Hk * DK;
+  const int snaps = p.num_snaps_per_seq;
+  __syncthreads();
+
+  for (int c0 = 0; c0 < n; c0 += kGC) {
+    const int rows = min(kGC, n - c0);
+    // ---- 1. rows of the chunk: q, k L2-normalised (q also scaled), v; gates
+    for (int i = warp; i < kGC; i += 8) {
+      float q[4] = {0.f, 0.f, 0.f, 0.f}, k[4] = {0.f, 0.f, 0.f, 0.f}, v[4] = {0.f, 0.f, 0.f, 0.f};
+      if (i < rows) {
+        const __nv_bfloat16* row = p.y + (long long)(q0 + c0 + i) * p.ldy;
+        const uint2 rq = *reinterpret_cast<const uint2*>(row + hk * DK + lane * 4);
+        const uint2 rk = *reinterpret_cast<const uint2*>(row + kd + hk * DK + lane * 4);
+        const uint2 rv = *reinterpret_cast<const uint2*>(row + 2 * kd + hv * DV + lane * 4);
+        const __nv_bfloat162* hq = reinterpret_cast<const __nv_bfloat162*>(&rq);
+        const __nv_bfloat162* hkk = reinterpret_cast<const __nv_bfloat162*>(&rk);
+        const __nv_bfloat162* hvv = reinterpret_cast<const __nv_bfloat162*>(&rv);
+        for (int e = 0; e < 2; ++e) {
+          float2 f = __bfloat1622float2(hq[e]); q[2 * e] = f.x; q[2 * e + 1] = f.y;
+          f = __bfloat1622float2(hkk[e]); k[2 * e] = f.x; k[2 * e + 1] = f.y;
+          f = __bfloat1622float2(hvv[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y;
+        }
+      }
+      const float qs = warp_sum(q[0] * q[0] + q[1] * q[1] + q[2] * q[2] + q[3] * q[3]);
+      const float ks = warp_sum(k[0] * k[0] + k[1] * k[1] + k[2] * k[2] + k[3] * k[3]);
+      const float qn = rsqrtf(qs + 1e-6f) * p.scale, kn = rsqrtf(ks + 1e-6f);
+      for (int e = 0; e < 4; ++e) {
+        sQ[i * kGLd + lane * 4 + e] = q[e] * qn;
+        sK[i * kGLd + lane * 4 + e] = k[e] * kn;
+        sV[i * kGLd + lane * 4 + e] = v[e];
+      }
+      if (lane == 0) {
+        float gi = 0.f, bi = 0.f;
+        if (i < rows) {
+          const long long tt = q0 + c0 + i;
+          const float av = __bfloat162float(p.a[tt * p.lda + hv]) + dtb;
+          const float sp = av > 20.f ? av : log1pf(__expf(av));
+          gi = neg_a * sp;
+          bi = 1.f / (1.f + __expf(-__bfloat162float(p.b[tt * p.ldb + hv])));
+        }
+        sG[i] = gi;
+        sBeta[i] = bi;
+      }
+    }
+    __syncthreads();
+    if (warp == 0) {            // inclusive running sum of the 64 log-decays (two per lane)
+      float a0 = sG[lane], a1 = sG[lane + 32];
+      for (int o = 1; o < 32; o <<= 1) {
+        const float u0 = __shfl_up_sync(0xffffffffu, a0, o), u1 = __shfl_up_sync(0xffffffffu, a1, o);
+        if (lane >= o) { a0 += u0; a1 += u1; }
+      }
+      const float tot0 = __shfl_sync(0xffffffffu, a0, 31);
+      sG[lane] = a0;
+      sG[lane + 32] = a1 + tot0;
+      const float gl = __shfl_sync(0xffffffffu, a1 + tot0, 31);
+      sE[lane] = __expf(a0); sE[lane + 32] = __expf(a1 + tot0);
+      sW[lane] = __expf(gl - a0); sW[lane + 32] = __expf(gl - a1 - tot0);
+    }
+    __syncthreads();
+    // ---- 2. B = beta (v - e^G (K h0)); A and P from K K^T and Q K^T
+    for (int tile = warp; tile < 64; tile += 8) {
+      const int m0 = (tile >> 4) * 16, n0 = (tile & 15) * 8;
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      warp_tile_tf32(c, m0, n0, DK, [&](int m, int k) { return sK[m * kGLd + k]; }, [&](int k, int nn) { return sh[k * kGLd + nn]; }, lane);
+      for (int e = 0; e < 4; ++e) {
+        const int i = m0 + g + (e >> 1) * 8, j = n0 + 2 * t4 + (e & 1);
+        sV[i * kGLd + j] = sBeta[i] * (sV[i * kGLd + j] - sE[i] * c[e]);
+      }
+    }
+    for (int tile = warp; tile < 64; tile += 8) {
+      const bool is_q = tile >= 32;
+      const int tl = tile & 31;
+      const int m0 = (tl >> 3) * 16, n0 = (tl & 7) * 8;
+      const float* src = is_q ? sQ : sK;
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      warp_tile_tf32(c, m0, n0, DK, [&](int m, int k) { return src[m * kGLd + k]; }, [&](int k, int nn) { return sK[nn * kGLd + k]; }, lane);
+      for (int e = 0; e < 4; ++e) {
+        const int i = m0 + g + (e >> 1) * 8, j = n0 + 2 * t4 + (e & 1);
+        const float dec = __expf(sG[i] - sG[j]);
+        if (is_q) sP[i * kGLdS + j] = (j <= i) ? dec * c[e] : 0.f;
+        else      sA[i * kGLdS + j] = (j < i) ? sBeta[i] * dec * c[e] : 0.f;
+      }
+    }
+    __syncthreads();
+    // ---- 3. forward substitution (I + A) D = B, one value column per thread
+    if (tid < DV) {
+      float d[kGC];
+#pragma unroll
+      for (int i = 0; i < kGC; ++i) {
+        float acc = sV[i * kGLd + tid];
+#pragma unroll
+        for (int j = 0; j < i; ++j) acc = fmaf(-sA[i * kGLdS + j], d[j], acc);
+        d[i] = acc;
+      }
+#pragma unroll
+      for (int i = 0; i < kGC; ++i) sV[i * kGLd + tid] = d[i];
+    }
+    __syncthreads();
+    // ---- 4. o = e^G (Q h0) + P D
+    for (int tile = warp; tile < 64; tile += 8) {
+      const int m0 = (tile >> 4) * 16, n0 = (tile & 15) * 8;
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      warp_tile_tf32(c, m0, n0, DK, [&](int m, int k) { return sQ[m * kGLd + k]; }, [&](int k, int nn) { return sh[k * kGLd + nn]; }, lane);
+      const float e0 = sE[m0 + g], e1 = sE[m0 + g + 8];
+      c[0] *= e0; c[1] *= e0; c[2] *= e1; c[3] *= e1;
+      warp_tile_tf32(c, m0, n0, kGC, [&](int m, int k) { return sP[m * kGLdS + k]; }, [&](int k, int nn) { return sV[k * kGLd + nn]; }, lane);
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        const int i = m0 + g + hlf * 8;
+        if (i < rows) {
+          __nv_bfloat162 o2 = __floats2bfloat162_rn(c[2 * hlf], c[2 * hlf + 1]);
+          *reinterpret_cast<__nv_bfloat162*>(p.out + (long long)(q0 + c0 + i) * p.ldo + hv * DV + n0 + 2 * t4) = o2;
+        }
+      }
+    }
+    __syncthreads();
+    // ---- 5. h = e^{G_C} h0 + sum_j e^{G_C - G_j} k_j (x) D_j
+    {
+      const float gC = sE[kGC - 1];
+      for (int tile = warp; tile < 128; tile += 8) {
+        const int m0 = (tile >> 4) * 16, n0 = (tile & 15) * 8;
+        float c[4];
+        for (int e = 0; e < 4; ++e) c[e] = sh[(m0 + g + (e >> 1) * 8) * kGLd + n0 + 2 * t4 + (e & 1)] * gC;
+        warp_tile_tf32(c, m0, n0, kGC, [&](int m, int k) { return sK[k * kGLd + m] * sW[k]; },
+                       [&](int k, int nn) { return sV[k * kGLd + nn]; }, lane);
+        for (int e = 0; e < 4; ++e) sh[(m0 + g + (e >> 1) * 8) * kGLd + n0 + 2 * t4 + (e & 1)] = c[e];
+      }
+    }
+    __syncthreads();
+    for (int s = 0; s < snaps; ++s) {
+      if (p.snap_rows[bseq * snaps + s] == c0 + rows) {
+        float* dst = p.h + (((long long)p.snap_slots[bseq * snaps + s] * p.Hv + hv) * (long long)DK) * DV;
+        for (int i = tid; i < DK * DV; i += 256) dst[i] = sh[(i >> 7) * kGLd + (i & 127)];
+      }
+    }
+  }
+  if (p.commit)
+    for (int i = tid; i < DK * DV; i += 256) hs[i] = sh[(i >> 7) * kGLd + (i & 127)];
+}
+
 }  // namespace atlas
 
 using namespace atlas;
@@ -216,4 +420,34 @@ extern "C" int atlas_gdn_recurrent(const void* y, long long ldy, const void* a, 
   else if (Dk == 32) gdn_recurrent_kernel<32><<<grid, threads, 0, st>>>(p);
   else return -2;
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+// Chunked (64-token) evaluation of the same recurrence for prefill-sized chunks: Dk = Dv = 128, whole sequences (no row
+// limit); snapshot rows must be multiples of 64 or the chunk's end.  Same state layout and arguments as
+// atlas_gdn_recurrent.
+extern "C" int atlas_gdn_chunked(const void* y, long long ldy, const void* a, long long lda, const void* b, long long ldb,
+                                 const float* A_log, const float* dt_bias, float* h, void* out, long long ldo,
+                                 const int* query_start_loc, const int* state_slots, const unsigned char* has_state,
+                                 const int* snap_rows, const int* snap_slots, int num_snaps_per_seq, int B, int Hk, int Hv,
+                                 int Dk, int Dv, int commit, void* stream) {
+  if (B <= 0) return 0;
+  if (Dk != 128 || Dv != 128 || Hv % Hk || (ldy % 4) || (ldo % 2)) return 1;       // caller falls back to the recurrence
+  GdnParams p;
+  p.y = reinterpret_cast<const __nv_bfloat16*>(y); p.ldy = ldy;
+  p.a = reinterpret_cast<const __nv_bfloat16*>(a); p.lda = lda;
+  p.b = reinterpret_cast<const __nv_bfloat16*>(b); p.ldb = ldb;
+  p.A_log = A_log; p.dt_bias = dt_bias; p.h = h;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ldo = ldo;
+  p.query_start_loc = query_start_loc; p.state_slots = state_slots; p.has_state = has_state; p.limit = nullptr;
+  p.snap_rows = snap_rows; p.snap_slots = snap_slots; p.num_snaps_per_seq = num_snaps_per_seq;
+  p.Hk = Hk; p.Hv = Hv; p.Dv = Dv; p.commit = commit; p.scale = 1.f / sqrtf((float)Dk);
+  constexpr int kSmem = (128 * kGLd + 3 * kGC * kGLd + 2 * kGC * kGLdS + 4 * kGC) * 4;
+  static bool attr_done = false;
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return -20;
+    attr_done = true;
+  }
+  dim3 grid(Hv, B);
+  gdn_chunk_kernel<<<grid, 256, kSmem, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }

@@ -10,6 +10,8 @@ from . import cuda as K
 
 _vp, _ll, _i = C.c_void_p, C.c_longlong, C.c_int
 _bound = False
+USE_CHUNKED = True          # tests switch this off to compare the two kernels
+CHUNK_MIN_ROWS = 32
 
 
 def _lib():
@@ -20,6 +22,8 @@ def _lib():
         lib.atlas_gdn_conv_state.argtypes = [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp]
         lib.atlas_gdn_recurrent.argtypes = [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp,
                                             _vp, _i, _i, _i, _i, _i, _i, _i, _vp]
+        lib.atlas_gdn_chunked.argtypes = [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _i,
+                                          _i, _i, _i, _i, _i, _i, _vp]
         _bound = True
     return lib
 
@@ -52,6 +56,9 @@ class _Meta:
         self.limit = dev[o:o + B] if limit is not None else None
         self.has = torch.tensor([1 if h else 0 for h in has_state], dtype=torch.uint8).pin_memory().to(device, non_blocking=True)
         self.B, self.T, self.snaps = B, len(seq_of), snaps
+        # the chunked (64-token, tensor-core) kernel takes prefill-sized steps whose snapshots fall on chunk boundaries
+        self.chunk_ok = (limit is None and max(qlens, default=0) >= CHUNK_MIN_ROWS and
+                         all(r % 64 == 0 or r == qlens[i] for i, lst in (snapshot_plan or {}).items() for r, _ in lst))
 
 
 def _run(layer, mixed, a, b, meta: _Meta, state, commit: bool):
@@ -66,11 +73,21 @@ def _run(layer, mixed, a, b, meta: _Meta, state, commit: bool):
     K._check(lib.atlas_gdn_conv(mixed.data_ptr(), mixed.stride(0), cw.data_ptr(), Cc, layer.W, conv.data_ptr(),
                                 meta.seq_of.data_ptr(), meta.qsl.data_ptr(), meta.slots.data_ptr(), meta.has.data_ptr(),
                                 y.data_ptr(), Cc, T, st), "gdn_conv")
-    K._check(lib.atlas_gdn_recurrent(y.data_ptr(), Cc, a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0),
-                                     layer.A_log.data_ptr(), layer.dt_bias.data_ptr(), h.data_ptr(), out.data_ptr(),
-                                     layer.hv * layer.dv, meta.qsl.data_ptr(), meta.slots.data_ptr(), meta.has.data_ptr(),
-                                     K._ptr(meta.limit), meta.snap_rows.data_ptr(), meta.snap_slots.data_ptr(), meta.snaps,
-                                     meta.B, layer.hk, layer.hv, layer.dk, layer.dv, 1 if commit else 0, st), "gdn_recurrent")
+    rc = 1
+    if USE_CHUNKED and meta.chunk_ok and commit and layer.dk == 128 and layer.dv == 128:
+        rc = lib.atlas_gdn_chunked(y.data_ptr(), Cc, a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0),
+                                   layer.A_log.data_ptr(), layer.dt_bias.data_ptr(), h.data_ptr(), out.data_ptr(),
+                                   layer.hv * layer.dv, meta.qsl.data_ptr(), meta.slots.data_ptr(), meta.has.data_ptr(),
+                                   meta.snap_rows.data_ptr(), meta.snap_slots.data_ptr(), meta.snaps, meta.B, layer.hk,
+                                   layer.hv, layer.dk, layer.dv, 1, st)
+        if rc != 1:
+            K._check(rc, "gdn_chunked")
+    if rc == 1:
+      K._check(lib.atlas_gdn_recurrent(y.data_ptr(), Cc, a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0),
+                                       layer.A_log.data_ptr(), layer.dt_bias.data_ptr(), h.data_ptr(), out.data_ptr(),
+                                       layer.hv * layer.dv, meta.qsl.data_ptr(), meta.slots.data_ptr(), meta.has.data_ptr(),
+                                       K._ptr(meta.limit), meta.snap_rows.data_ptr(), meta.snap_slots.data_ptr(), meta.snaps,
+                                       meta.B, layer.hk, layer.hv, layer.dk, layer.dv, 1 if commit else 0, st), "gdn_recurrent")
     if commit:
         K._check(lib.atlas_gdn_conv_state(mixed.data_ptr(), mixed.stride(0), Cc, layer.W, conv.data_ptr(), meta.qsl.data_ptr(),
                                           meta.slots.data_ptr(), meta.has.data_ptr(), K._ptr(meta.limit),

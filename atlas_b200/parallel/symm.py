@@ -22,6 +22,7 @@ from .comm import CommBackend, CommError, TorchDistBackend
 _vp, _i, _ll, _sz = C.c_void_p, C.c_int, C.c_longlong, C.c_size_t
 ONESHOT_MAX_BYTES = 2 << 20
 P2P_MAX_BYTES = 4 << 20          # above this NCCL's ring/tree is faster than the two-shot kernel (measured at 2 ranks)
+FUSED_DECODE_MAX_K = 4096
 FUSED_MAX_OUT_BYTES = 2 << 20    # the fused GEMM+all-reduce pays off for decode-size outputs
 
 
@@ -182,6 +183,10 @@ class SymmBackend(CommBackend):
         M, Kd = a.shape
         N = b.shape[0]
         if N % 8 or a.stride(1) != 1 or M * N * 2 > FUSED_MAX_OUT_BYTES:
+            return None
+        if M <= 128 and Kd > FUSED_DECODE_MAX_K:
+            # decode-size rows with a long K: the fused kernel has no split-K, so it runs on N/64 CTAs only; the split-K
+            # GEMM followed by the one-shot all-reduce is faster there (2 x B200, 128 x 4096 x 7168: 46 us vs 59 us)
             return None
         sms = K._num_sms[self.dev_index]
         bn = 128 if ((M + 127) // 128) * ((N + 127) // 128) >= sms else 64

@@ -88,6 +88,8 @@ def main():
                           "workspace (no setup.py/pyproject.toml, needs cargo which the image lacks)"}))
         return 0
 
+    # NCCL's own banner / debug lines must not land on stdout next to the JSON line
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     import torch
     from atlas_b200.config import PRESETS, EngineConfig
     from atlas_b200.engine import LLMEngine
