@@ -43,6 +43,9 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--no-prefix-caching", dest="enable_prefix_caching", action="store_false")
     s.add_argument("--speculative", action="store_true")
     s.add_argument("--num-drafts", type=int, default=0)
+    s.add_argument("--ngram-speculative", action="store_true", help="prompt-lookup drafts (no draft model)")
+    s.add_argument("--ngram-max", type=int, default=4)
+    s.add_argument("--ngram-min", type=int, default=2)
     s.add_argument("--mtp-gate", action="store_true", default=None)
     s.add_argument("--no-mtp-gate", dest="mtp_gate", action="store_false")
     s.add_argument("--ssm-cache-slots", type=int, default=16)
@@ -119,7 +122,9 @@ def _engine_config(args, mcfg):
                         num_kv_blocks=args.num_kv_blocks, max_num_seqs=args.max_num_seqs, max_batch_size=args.max_batch_size,
                         max_prefill_tokens=args.max_prefill_tokens, scheduling_policy=args.scheduling_policy,
                         tbt_deadline_ms=args.tbt_deadline_ms, enable_prefix_caching=prefix,
-                        speculative=args.speculative, num_drafts=args.num_drafts or (1 if args.speculative else 0),
+                        speculative=args.speculative,
+                        num_drafts=args.num_drafts or (1 if args.speculative else (3 if args.ngram_speculative else 0)),
+                        ngram_speculative=args.ngram_speculative, ngram_max=args.ngram_max, ngram_min=args.ngram_min,
                         mtp_gate=True if args.mtp_gate is None else args.mtp_gate, ssm_cache_slots=args.ssm_cache_slots,
                         ssm_checkpoint_interval=args.ssm_checkpoint_interval, swap_space_gb=args.swap_space_gb,
                         use_cuda_graphs=not args.no_cuda_graphs, tp_size=max(1, args.tp_size), ep_size=max(1, args.ep_size),

@@ -359,6 +359,9 @@ class EngineConfig:
     speculative: bool = False
     num_drafts: int = 0
     mtp_gate: bool = True
+    ngram_speculative: bool = False           # prompt-lookup drafts (no draft model); uses num_drafts
+    ngram_max: int = 4
+    ngram_min: int = 2
     ssm_cache_slots: int = 16
     ssm_checkpoint_interval: int = 256
     swap_space_gb: float = 0.0

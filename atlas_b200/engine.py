@@ -71,6 +71,9 @@ class LLMEngine:
         self.runner = ModelRunner(model, self.cache, self.cfg)
         self.spec = SpecController(self, self.cfg) if (self.cfg.speculative and model.mtp is not None
                                                          and self.cfg.num_drafts > 0) else None
+        if self.spec is None and self.cfg.ngram_speculative and self.cfg.num_drafts > 0:
+            from .sched.spec import NgramSpecController
+            self.spec = NgramSpecController(self, self.cfg)     # draft-model-free: works for every architecture
         self.stats = EngineStats()
         self.control = None               # parallel.worker.StepControl when several processes serve one model
         self._eos_set = frozenset(self.mcfg.eos_ids())

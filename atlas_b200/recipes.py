@@ -22,6 +22,7 @@ SCHEMA: Dict[str, tuple] = {
     "scheduling_policy": ("--scheduling-policy", "value"), "tbt_deadline_ms": ("--tbt-deadline-ms", "value"),
     "enable_prefix_caching": ("--enable-prefix-caching", "switch"), "speculative": ("--speculative", "switch"),
     "num_drafts": ("--num-drafts", "value"), "mtp_gate": ("--mtp-gate", "switch"),
+    "ngram_speculative": ("--ngram-speculative", "switch"),
     "tp_size": ("--tp-size", "value"), "ep_size": ("--ep-size", "value"),
     "ssm_cache_slots": ("--ssm-cache-slots", "value"), "ssm_checkpoint_interval": ("--ssm-checkpoint-interval", "value"),
     "tool_call_parser": ("--tool-call-parser", "value"), "disable_thinking": ("--disable-thinking", "switch"),

@@ -157,3 +157,63 @@ class SpecController:
         for j, s in enumerate(seqs):
             room = s.sampling.max_tokens - s.num_output_tokens - 1
             s.drafts = drafts[j][:max(0, min(self.k, room))]
+
+
+class NgramSpecController:
+    """Draft tokens by prompt lookup: find the longest recent n-gram (``ngram_max`` .. ``ngram_min`` tokens ending at
+    the sequence's last token) that occurred earlier in the prompt or the output and propose the tokens that followed it.
+    No draft model is involved, so it works for every architecture; verification, acceptance (match against the target's
+    own samples), write-on-accept state handling and the throughput gate are the ones the MTP path uses.
+
+    The index (n-gram -> position after its latest earlier occurrence) is kept per sequence and extended by the tokens
+    appended since the last step.  Reference parity: ``crates/spark-server/src/ngram.rs`` (prompt-lookup proposer),
+    ``scheduler/spec_step.rs`` (n-gram / self-speculative step), ``scheduler/copy_draft/``.
+    """
+
+    def __init__(self, engine, cfg: EngineConfig):
+        self.engine, self.cfg = engine, cfg
+        self.k = max(1, cfg.num_drafts)
+        self.n_max, self.n_min = max(1, cfg.ngram_max), max(1, min(cfg.ngram_min, cfg.ngram_max))
+        self.gate = MtpGate(enabled=cfg.mtp_gate)
+        self.proposed_steps = 0
+
+    def active(self) -> bool:
+        return True
+
+    def _index(self, seq):
+        st = getattr(seq, "_ngram_state", None)
+        if st is None:
+            st = seq._ngram_state = {"upto": 0, "maps": {n: {} for n in range(self.n_min, self.n_max + 1)}}
+        return st
+
+    def propose(self, seq) -> List[int]:
+        total = seq.num_tokens
+        st = self._index(seq)
+        tok = seq.token_at
+        # index every n-gram that ENDS before the last token, so a lookup never matches itself
+        for end in range(max(st["upto"], self.n_min), total):          # gram = tokens[end-n:end]; what follows starts at `end`
+            for n, mp in st["maps"].items():
+                if end - n >= 0:
+                    mp[tuple(tok(i) for i in range(end - n, end))] = end
+        st["upto"] = max(st["upto"], total)
+        for n in range(self.n_max, self.n_min - 1, -1):
+            if total < n:
+                continue
+            pos = st["maps"][n].get(tuple(tok(i) for i in range(total - n, total)))
+            if pos is not None and pos < total:
+                return [tok(i) for i in range(pos, min(pos + self.k, total))]
+        return []
+
+    def after_step(self, out: SchedulerOutput, batch: ForwardBatch, hidden, sampled, kept_rows) -> None:
+        if not self.gate.use_spec():
+            return
+        any_draft = False
+        for it in out.items:
+            seq = it.seq
+            if seq.finished or seq.status != SeqStatus.RUNNING or seq.disable_spec or not it.sample:
+                continue
+            room = seq.sampling.max_tokens - seq.num_output_tokens - 1
+            drafts = self.propose(seq)[:max(0, min(self.k, room))]
+            seq.drafts = drafts
+            any_draft |= bool(drafts)
+        self.proposed_steps += 1 if any_draft else 0

@@ -88,8 +88,11 @@ def main():
                           "workspace (no setup.py/pyproject.toml, needs cargo which the image lacks)"}))
         return 0
 
-    # NCCL's own banner / debug lines must not land on stdout next to the JSON line
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+    # Libraries (NCCL's version banner among them) print to file descriptor 1 on their own; the contract is ONE JSON
+    # line on stdout, so everything else is sent to stderr and the result line is written to the saved descriptor.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     import torch
     from atlas_b200.config import PRESETS, EngineConfig
     from atlas_b200.engine import LLMEngine
@@ -193,7 +196,8 @@ def main():
             "device_phase_ms": {k: {"ms": round(v[0], 1), "engine_steps": v[1]} for k, v in eng.device_phase_ms.items()},
             "impl": "atlas_b200",
         }
-        print(json.dumps(line))
+        sys.stdout.flush()
+        os.write(real_stdout, (json.dumps(line) + "\n").encode())
     if world > 1:
         torch.distributed.barrier()
         if symm is not None:
