@@ -134,9 +134,9 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bf
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, long long ld, int I, __nv_bfloat16* y, long long ldy, uint8_t* q,
                 long long ldq, float* scale, long long scale_ld, const int* live_tiles) {
-  const int t = blockIdx.y;
+  const int t = blockIdx.x;           // rows on grid.x: row counts can exceed the 65535 limit of grid.y
   if (live_tiles && t >= (*live_tiles) * 128) return;      // expert-sorted buffers: rows past the live tiles are unused
-  const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  const int e = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   const bool live = e < I;
   float o[8];
   float amax = 0.f;
@@ -166,8 +166,8 @@ silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, long long ld, int I, __nv_
 __global__ void __launch_bounds__(256)
 quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int K, uint8_t* q, long long ldq, float* scale,
                  long long scale_ld) {
-  const int t = blockIdx.y;
-  const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  const int t = blockIdx.x;           // rows on grid.x: row counts can exceed the 65535 limit of grid.y
+  const int e = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   const bool live = e < K;
   float o[8];
   float amax = 0.f;
@@ -342,7 +342,7 @@ extern "C" int atlas_silu_mul(const void* gu, long long ld, int T, int I, void* 
                               long long ldq, float* scale, long long scale_ld, const int* live_tiles, void* stream) {
   if (T <= 0) return 0;
   if (I % 8 || (q && I % 128)) return -1;
-  dim3 grid((I / 8 + 255) / 256, T);
+  dim3 grid(T, (I / 8 + 255) / 256);
   silu_mul_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(gu), ld, I, reinterpret_cast<__nv_bfloat16*>(y), ldy,
       reinterpret_cast<uint8_t*>(q), ldq, scale, scale_ld, live_tiles);
@@ -353,7 +353,7 @@ extern "C" int atlas_quant_fp8(const void* x, long long ld, int T, int K, void* 
                                long long scale_ld, void* stream) {
   if (T <= 0) return 0;
   if (K % 128) return -1;
-  dim3 grid((K / 8 + 255) / 256, T);
+  dim3 grid(T, (K / 8 + 255) / 256);
   quant_fp8_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), ld, K, reinterpret_cast<uint8_t*>(q), ldq, scale, scale_ld);
   return cudaGetLastError() == cudaSuccess ? 0 : -20;

@@ -20,8 +20,8 @@ gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_b
                 const __nv_bfloat16* __restrict__ conv_state, const int* __restrict__ seq_of_token,
                 const int* __restrict__ query_start_loc, const int* __restrict__ state_slots,
                 const unsigned char* __restrict__ has_state, __nv_bfloat16* y, long long ldy, int T) {
-  const int t = blockIdx.y;
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int t = blockIdx.x;           // rows on grid.x (no 65535 limit)
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C || t >= T) return;
   const int b = seq_of_token[t];
   const int q0 = query_start_loc[b];
@@ -232,8 +232,12 @@ gdn_chunk_kernel(const GdnParams p) {
   const int snaps = p.num_snaps_per_seq;
   __syncthreads();
 
-  for (int c0 = 0; c0 < n; c0 += kGC) {
-    const int rows = min(kGC, n - c0);
+  for (int c0 = 0; c0 < n;) {
+    int rows = min(kGC, n - c0);
+    for (int s = 0; s < snaps; ++s) {          // a snapshot inside the chunk ends it there (any row may be a snapshot row)
+      const int r = p.snap_rows[bseq * snaps + s];
+      if (r > c0 && r < c0 + rows) rows = r - c0;
+    }
     // ---- 1. rows of the chunk: q, k L2-normalised (q also scaled), v; gates
     for (int i = warp; i < kGC; i += 8) {
       float q[4] = {0.f, 0.f, 0.f, 0.f}, k[4] = {0.f, 0.f, 0.f, 0.f}, v[4] = {0.f, 0.f, 0.f, 0.f};
@@ -362,6 +366,7 @@ gdn_chunk_kernel(const GdnParams p) {
         for (int i = tid; i < DK * DV; i += 256) dst[i] = sh[(i >> 7) * kGLd + (i & 127)];
       }
     }
+    c0 += rows;
   }
   if (p.commit)
     for (int i = tid; i < DK * DV; i += 256) hs[i] = sh[(i >> 7) * kGLd + (i & 127)];
@@ -376,7 +381,7 @@ extern "C" int atlas_gdn_conv(const void* x, long long ldx, const void* w, int C
                               const unsigned char* has_state, void* y, long long ldy, int T, void* stream) {
   if (T <= 0) return 0;
   if (W < 2 || W > 8) return -1;
-  dim3 grid((C + 255) / 256, T);
+  dim3 grid(T, (C + 255) / 256);
   gdn_conv_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), ldx, reinterpret_cast<const __nv_bfloat16*>(w), C, W,
       reinterpret_cast<const __nv_bfloat16*>(conv_state), seq_of_token, query_start_loc, state_slots, has_state,
@@ -423,7 +428,7 @@ extern "C" int atlas_gdn_recurrent(const void* y, long long ldy, const void* a, 
 }
 
 // Chunked (64-token) evaluation of the same recurrence for prefill-sized chunks: Dk = Dv = 128, whole sequences (no row
-// limit); snapshot rows must be multiples of 64 or the chunk's end.  Same state layout and arguments as
+// limit); a snapshot row inside a chunk simply ends that chunk early.  Same state layout and arguments as
 // atlas_gdn_recurrent.
 extern "C" int atlas_gdn_chunked(const void* y, long long ldy, const void* a, long long lda, const void* b, long long ldb,
                                  const float* A_log, const float* dt_bias, float* h, void* out, long long ldo,

@@ -124,10 +124,10 @@ moe_align_kernel(const int* __restrict__ topk_ids, int n_pairs, int e_lo, int E_
 __global__ void __launch_bounds__(256)
 moe_gather_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const int* __restrict__ row_token,
                   const int* __restrict__ num_tiles, int H, __nv_bfloat16* y, uint8_t* q, float* scale, long long scale_ld) {
-  const int row = blockIdx.y;
+  const int row = blockIdx.x;         // rows on grid.x: row counts can exceed the 65535 limit of grid.y
   if (row >= (*num_tiles) * 128) return;
   const int t = row_token[row];
-  const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  const int e = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   const bool live = e < H;
   float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   if (live && t >= 0) {
@@ -168,8 +168,8 @@ __global__ void __launch_bounds__(256)
 moe_combine_kernel(const __nv_bfloat16* __restrict__ y, long long ldy, const int* __restrict__ slot_of,
                    const float* __restrict__ topk_w, int k, int H, const __nv_bfloat16* addend, long long ld_add,
                    __nv_bfloat16* out, long long ldo) {
-  const int t = blockIdx.y;
-  const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  const int t = blockIdx.x;
+  const int e = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   if (e >= H) return;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   for (int j = 0; j < k; ++j) {
@@ -270,7 +270,7 @@ extern "C" int atlas_moe_gather(const void* x, long long ldx, const int* row_tok
                                 int H, void* y, void* q, float* scale, long long scale_ld, void* stream) {
   if (max_rows <= 0) return 0;
   if (H % 8 || (q && H % 128)) return -1;
-  dim3 grid((H / 8 + 255) / 256, max_rows);
+  dim3 grid(max_rows, (H / 8 + 255) / 256);
   moe_gather_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), ldx, row_token, num_tiles, H, reinterpret_cast<__nv_bfloat16*>(y),
       reinterpret_cast<uint8_t*>(q), scale, scale_ld);
@@ -281,7 +281,7 @@ extern "C" int atlas_moe_combine(const void* y, long long ldy, const int* slot_o
                                  const void* addend, long long ld_add, void* out, long long ldo, void* stream) {
   if (T <= 0) return 0;
   if (H % 8) return -1;
-  dim3 grid((H / 8 + 255) / 256, T);
+  dim3 grid(T, (H / 8 + 255) / 256);
   moe_combine_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(y), ldy, slot_of, topk_w, k, H, reinterpret_cast<const __nv_bfloat16*>(addend),
       ld_add, reinterpret_cast<__nv_bfloat16*>(out), ldo);

@@ -56,9 +56,8 @@ class _Meta:
         self.limit = dev[o:o + B] if limit is not None else None
         self.has = torch.tensor([1 if h else 0 for h in has_state], dtype=torch.uint8).pin_memory().to(device, non_blocking=True)
         self.B, self.T, self.snaps = B, len(seq_of), snaps
-        # the chunked (64-token, tensor-core) kernel takes prefill-sized steps whose snapshots fall on chunk boundaries
-        self.chunk_ok = (limit is None and max(qlens, default=0) >= CHUNK_MIN_ROWS and
-                         all(r % 64 == 0 or r == qlens[i] for i, lst in (snapshot_plan or {}).items() for r, _ in lst))
+        # the chunked (64-token, tensor-core) kernel takes prefill-sized steps (a snapshot row just ends a chunk early)
+        self.chunk_ok = limit is None and max(qlens, default=0) >= CHUNK_MIN_ROWS
 
 
 def _run(layer, mixed, a, b, meta: _Meta, state, commit: bool):

@@ -78,6 +78,10 @@ def main():
     ap.add_argument("--max-prefill-tokens", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (marks the result invalid)")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--speculative", action="store_true", help="MTP speculative decoding (models with a draft head)")
+    ap.add_argument("--num-drafts", type=int, default=3)
+    ap.add_argument("--prefix-cache", action="store_true")
+    ap.add_argument("--shared-prefix", type=int, default=0, help="every second prompt starts with the same N tokens")
     ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"],
                     help="tensor-parallel collectives: this engine's peer-memory kernels (default) or the NCCL baseline")
     args = ap.parse_args()
@@ -123,7 +127,9 @@ def main():
     blocks_per_seq = (max_len + args.block_size - 1) // args.block_size + 1
     ecfg = EngineConfig(max_seq_len=max_len, block_size=args.block_size, max_num_seqs=max(args.concurrency, 1),
                         max_batch_size=max(args.concurrency, 1), max_prefill_tokens=args.max_prefill_tokens,
-                        num_kv_blocks=blocks_per_seq * args.concurrency + 64, enable_prefix_caching=False,
+                        num_kv_blocks=blocks_per_seq * args.concurrency + 64, enable_prefix_caching=args.prefix_cache,
+                        speculative=args.speculative, num_drafts=args.num_drafts if args.speculative else 0,
+                        ssm_cache_slots=max(16, args.concurrency + 8),
                         use_cuda_graphs=not args.no_graphs, tp_size=world)
     eng = LLMEngine(model, ecfg)
     eng.time_device = True
@@ -132,6 +138,10 @@ def main():
 
     def wave():
         prompts = [torch.randint(0, mcfg.vocab_size, (args.isl,), generator=gen).tolist() for _ in range(args.concurrency)]
+        if args.shared_prefix:
+            shared = torch.randint(0, mcfg.vocab_size, (args.shared_prefix,), generator=gen).tolist()
+            for i in range(0, len(prompts), 2):
+                prompts[i][:args.shared_prefix] = shared
         outs = eng.generate(prompts, sp)
         return sum(len(o.output_tokens) for o in outs), [o.ttft_s for o in outs]
 
@@ -171,6 +181,11 @@ def main():
     wall, dev_s = float(t[0]), float(t[1])
     eng_steps = eng.stats.steps - steps0
     launches = (K.launch_count - launches0) + (eng.runner.graph_replays - replays0) * eng.runner.kernels_per_graph()
+    qm = mcfg.quant.method
+    dtype_desc = {"fp8_block": "fp8-e4m3 weights (128x128 scales) + fp8 KV, bf16 activations",
+                  "nvfp4": "nvfp4 weights (e2m1, e4m3 scale per 16, fp32 global)" + (" for experts, bf16 elsewhere" if mcfg.quant.experts_only else "") + " + fp8 KV, bf16 activations",
+                  }.get(qm, "bf16 weights + fp8 KV")
+    quant_desc = {"fp8_block": " quantized to fp8 block-scaled", "nvfp4": " quantized to nvfp4"}.get(qm, "")
     if rank == 0:
         value = tokens / dev_s if dev_s > 0 else 0.0
         e2e = tokens / wall
@@ -178,13 +193,16 @@ def main():
             "metric": "aggregate output tok/s (concurrency wave, ISL/OSL)", "value": round(value, 2), "unit": "tok/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(wall * 1e3 / args.steps, 3), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": (value / BASELINE_TOK_S) if BASELINE_TOK_S else None, "dtype": "fp8-e4m3 weights (128x128 scales) + fp8 KV, bf16 activations",
-            "data": "synthetic: uniform-random token ids, random-init N(0,0.02) weights quantized to fp8 block-scaled",
+            "vs_baseline": (value / BASELINE_TOK_S) if BASELINE_TOK_S else None, "dtype": dtype_desc,
+            "data": "synthetic: uniform-random token ids, random-init N(0,0.02) weights" + quant_desc,
             "config": {"model": args.model + ("" if not args.layers else f"-TRUNCATED-{args.layers}L-INVALID"),
                        "global_batch": args.concurrency, "seq_len": args.isl + args.osl, "isl": args.isl, "osl": args.osl,
                        "parallelism": f"tp{world}", "collectives": (args.comm if world > 1 else "none"), "l2": "inputs larger than L2 (8 GB weights + KV stream every step)",
                        "step": "one wave of `global_batch` concurrent requests, prefill + decode",
-                       "engine_steps_per_wave": eng_steps / max(1, args.steps), "cuda_graphs": not args.no_graphs},
+                       "engine_steps_per_wave": eng_steps / max(1, args.steps), "cuda_graphs": not args.no_graphs,
+                       "speculative": bool(args.speculative), "prefix_cache": bool(args.prefix_cache),
+                       "spec_accept_rate": (eng.stats.spec_accepted / eng.stats.spec_proposed) if eng.stats.spec_proposed else None,
+                       "prefix_hit_tokens": (eng.radix.stats.hit_tokens if eng.radix is not None else 0)},
             "clocks": clocks,
             "e2e": {"value": round(e2e, 2), "unit": "tok/s",
                     "h2d_bytes_per_step": int((eng.runner.h2d_bytes - h2d0) / max(1, eng_steps)),

@@ -125,7 +125,7 @@ def test_gdn_chunked_matches_recurrence(K):
     a = torch.randn(T, layer.hv, device=DEV).bfloat16()
     b = torch.randn(T, layer.hv, device=DEV).bfloat16()
     tables = [list(range(16))] * 4
-    plan = {0: [(64, 4), (128, 5)], 3: [(130, 6)]}
+    plan = {0: [(64, 4), (144, 5)], 3: [(130, 6)]}          # 144: a snapshot row inside a chunk
 
     def run(chunked):
         cuda_gdn.USE_CHUNKED = chunked
