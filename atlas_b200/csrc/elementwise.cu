@@ -40,15 +40,17 @@ ATLAS_DEVICE void store8(__nv_bfloat16* p, const float (&f)[8]) {
   for (int i = 0; i < 4; ++i) r.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
   *reinterpret_cast<bf16x8*>(p) = r;
 }
-// 8 floats -> 8 e4m3 bytes with a common scale (IEEE x / scale, so codes match a host restatement), packed
+// 8 floats -> 8 e4m3 bytes with a common scale, packed.  The scale's reciprocal is formed once (IEEE) and multiplied in;
+// against x / scale this moves a value by at most one fp32 ulp before the e4m3 rounding, i.e. an occasional code on a
+// rounding boundary differs by one step.  Conversions go two at a time (cvt.rn.satfinite.e4m3x2.f32).
 ATLAS_DEVICE uint2 quant8(const float (&f)[8], float scale) {
+  const float inv = __frcp_rn(scale);
   uint32_t w[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    uint32_t acc = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc |= (uint32_t)f32_to_fp8_e4m3(__fdiv_rn(f[h * 4 + i], scale)) << (8 * i);
-    w[h] = acc;
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(f[h * 4 + 0] * inv, f[h * 4 + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(f[h * 4 + 2] * inv, f[h * 4 + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+    w[h] = lo | (hi << 16);
   }
   return make_uint2(w[0], w[1]);
 }
@@ -146,7 +148,7 @@ silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, long long ld, int I, __nv_
     load8(gu + t * ld + I + e, u);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float s = g[i] / (1.f + __expf(-g[i]));
+      const float s = __fdividef(g[i], 1.f + __expf(-g[i]));
       o[i] = __bfloat162float(__float2bfloat16_rn(s * u[i]));
       amax = fmaxf(amax, fabsf(o[i]));
     }
