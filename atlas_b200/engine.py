@@ -163,7 +163,7 @@ class LLMEngine:
     @torch.inference_mode()
     def step(self) -> List[RequestOutput]:
         """One scheduler tick.  With a multi-process ``control`` attached the leader's clock, request events and
-        sampling verdict are imposed on the followers (see ``parallel/worker.py``); otherwise everything is local."""
+        sampling outcome are imposed on the followers (see ``parallel/worker.py``); otherwise everything is local."""
         t0 = time.monotonic()
         sched = self.scheduler
         ctl = self.control
@@ -178,7 +178,7 @@ class LLMEngine:
         sched.finished_queue.clear()
         if out.empty:
             if ctl is not None:
-                ctl.finish_step(None if follower else _EMPTY_VERDICT())
+                ctl.finish_step(None if follower else _empty_outcome())
             return results
         for snap_slot, seq_slot in out.restored_snapshots:
             self.runner.copy_state(self.snapshot_base + snap_slot, seq_slot)
@@ -228,15 +228,15 @@ class LLMEngine:
         now = time.monotonic()
         dt_gate: Optional[float] = None
         if follower:
-            verdict = ctl.finish_step(None)
-            accepted_rows = self._apply_verdict(out, verdict.records, now)
-            dt_gate = verdict.dt
+            outcome = ctl.finish_step(None)
+            accepted_rows = self._apply_outcome(out, outcome.records, now)
+            dt_gate = outcome.dt
         else:
             with phase("apply"):
                 accepted_rows, records = self._apply_sampled(out, sampled, lps, now, results)
             if ctl is not None:
                 dt_gate = time.monotonic() - t0
-                ctl.finish_step(_make_verdict(records, dt_gate))
+                ctl.finish_step(_make_outcome(records, dt_gate))
         if batch.spec_verify:
             self.model.commit_spec(accepted_rows, self.cache)
             for it in out.items:
@@ -248,7 +248,7 @@ class LLMEngine:
         n_new = sum(len(r.new_tokens) for r in results)
         self.stats.on_step(dt, out, n_new)
         if self.spec is not None:
-            n_gate = n_new if not follower else sum(len(v[1]) for v in verdict.records.values())
+            n_gate = n_new if not follower else sum(len(v[1]) for v in outcome.records.values())
             self.spec.gate.record(batch.spec_verify, dt if dt_gate is None else dt_gate, n_gate)
         return results
 
@@ -292,8 +292,8 @@ class LLMEngine:
             records[idx] = (accepted_rows[-1], kept, seq.finish_reason.value if seq.finished else None)
         return accepted_rows, records
 
-    def _apply_verdict(self, out: SchedulerOutput, records: Dict[int, tuple], now: float) -> List[int]:
-        """Follower replay of the leader's verdict (no sampling, no stop logic of its own)."""
+    def _apply_outcome(self, out: SchedulerOutput, records: Dict[int, tuple], now: float) -> List[int]:
+        """Follower replay of the leader's outcome (no sampling, no stop logic of its own)."""
         sched = self.scheduler
         accepted_rows: List[int] = []
         for idx, it in enumerate(out.items):
@@ -419,10 +419,10 @@ class _RowView:
 _EMPTY = frozenset()
 
 
-def _make_verdict(records, dt):
-    from .parallel.worker import StepVerdict
-    return StepVerdict(records, dt)
+def _make_outcome(records, dt):
+    from .parallel.worker import StepOutcome
+    return StepOutcome(records, dt)
 
 
-def _EMPTY_VERDICT():
-    return _make_verdict({}, 0.0)
+def _empty_outcome():
+    return _make_outcome({}, 0.0)

@@ -10,7 +10,7 @@ independent of the GPU collectives:
   previous step and its monotonic clock; followers apply the events and schedule with the same ``now``.  All ranks now
   build the same batch and launch the same kernels and collectives.
 * ``finish_step``: only the leader samples (grammar masks, logit processors, stop strings live there); it broadcasts
-  ``StepVerdict(records, dt)`` — per scheduled item the rows kept, tokens appended and the finish reason — and the
+  ``StepOutcome(records, dt)`` — per scheduled item the rows kept, tokens appended and the finish reason — and the
   followers replay that onto their sequences.  ``dt`` feeds the speculative throughput gate identically everywhere.
 
 While idle the leader sends a heartbeat plan every ``heartbeat_s`` so that a follower's bounded wait only expires when
@@ -45,7 +45,7 @@ class StepPlan:
 
 
 @dataclass
-class StepVerdict:
+class StepOutcome:
     records: Dict[int, Tuple[int, List[int], Optional[str]]] = field(default_factory=dict)   # item -> (rows kept, tokens, finish)
     dt: float = 0.0
 
@@ -118,8 +118,8 @@ class StepControl:
         if self.is_leader:
             self._bcast(StepPlan(shutdown=True))
 
-    def finish_step(self, verdict: Optional[StepVerdict]) -> StepVerdict:
-        return self._bcast(verdict if self.is_leader else None)
+    def finish_step(self, outcome: Optional[StepOutcome]) -> StepOutcome:
+        return self._bcast(outcome if self.is_leader else None)
 
     # ------------------------------------------------------------------ follower side
     @staticmethod

@@ -88,7 +88,7 @@ def main():
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
-                          "refused by a safety check: pip install of /root/reference was denied; the reference is a Rust "
+                          "refused by a safety check: pip install of the reference checkout was denied; the reference is a Rust "
                           "workspace (no setup.py/pyproject.toml, needs cargo which the image lacks)"}))
         return 0
 

@@ -84,7 +84,7 @@ def test_leader_and_followers_match_single_process(mk):
 
 
 def test_leader_only_decisions_are_replayed():
-    """A stop checker (host-side, leader only), an abort and a timeout all reach the followers as verdicts/events."""
+    """A stop checker (host-side, leader only), an abort and a timeout all reach the followers as outcomes / events."""
     prompts = _prompts(3)
 
     def leader(de):
