@@ -16,6 +16,7 @@ import torch
 from .. import ops
 from ..config import ModelConfig
 from ..ops import Act, LinearWeight
+from ..lora import add_delta
 from .common import ParallelCtx, make_weight, randn_weight, shard_cols, shard_rows
 
 
@@ -35,6 +36,7 @@ class Attention:
         self.o: Optional[LinearWeight] = None
         self.q_norm: Optional[torch.Tensor] = None
         self.k_norm: Optional[torch.Tensor] = None
+        self.lora = None                    # lora.LoraSet shared by the model's layers
 
     # ------------------------------------------------------------------ weights
     def _kv_slice(self, w: torch.Tensor) -> torch.Tensor:
@@ -82,6 +84,11 @@ class Attention:
         qkv = ops.linear(act, self.qkv)
         T = qkv.shape[0]
         nq, nkv = self.hq * self.d, self.hkv * self.d
+        if self.lora is not None and batch.adapter_rows is not None:
+            xin, pre = act.plain(), f"layers.{self.layer_idx}.self_attn."
+            add_delta(qkv, self.lora, pre + "q_proj", xin, batch, 0, nq)
+            add_delta(qkv, self.lora, pre + "k_proj", xin, batch, nq, nkv)
+            add_delta(qkv, self.lora, pre + "v_proj", xin, batch, nq + nkv, nkv)
         q = qkv[:, :nq].view(T, self.hq, self.d)
         k = qkv[:, nq:nq + nkv].view(T, self.hkv, self.d)
         v = qkv[:, nq + nkv:nq + 2 * nkv].view(T, self.hkv, self.d)
@@ -93,4 +100,9 @@ class Attention:
         if self.gated:
             gate = qkv[:, nq + 2 * nkv:]
             out = (out.float() * torch.sigmoid(gate.float())).to(out.dtype)
-        return self.pctx.row_parallel_linear(out, self.o)
+        y = self.pctx.row_parallel_linear(out, self.o)
+        if self.lora is not None and batch.adapter_rows is not None:
+            if y._base is not None:
+                y = y.clone()               # the fused path returns a view of its reduction area
+            add_delta(y, self.lora, f"layers.{self.layer_idx}.self_attn.o_proj", out, batch)
+        return y

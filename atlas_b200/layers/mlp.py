@@ -13,6 +13,7 @@ import torch
 from .. import ops
 from ..config import ModelConfig
 from ..ops import Act, LinearWeight
+from ..lora import add_delta
 from .common import ParallelCtx, make_weight, randn_weight, shard_cols, shard_rows
 
 
@@ -24,6 +25,8 @@ class DenseMLP:
         self.shard = shard and pctx.tp_size > 1 and self.inter % (pctx.tp_size * 128) == 0
         self.gate_up: Optional[LinearWeight] = None
         self.down: Optional[LinearWeight] = None
+        self.lora = None                    # lora.LoraSet shared by the model's layers
+        self.lora_prefix = ""               # e.g. "layers.3.mlp."
 
     def load(self, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> None:
         tp, r = (self.pctx.tp_size, self.pctx.tp_rank) if self.shard else (1, 0)
@@ -37,9 +40,20 @@ class DenseMLP:
                   randn_weight(gen, self.inter, h, std, dtype, device),
                   randn_weight(gen, h, self.inter, std, dtype, device))
 
-    def forward(self, act: Act, reduce: bool = True) -> torch.Tensor:
+    def forward(self, act: Act, reduce: bool = True, batch=None) -> torch.Tensor:
         gu = ops.linear(act, self.gate_up)
-        a = ops.silu_mul_act(gu, want_fp8=self.down.kind == "fp8_block")
+        use_lora = self.lora is not None and batch is not None and batch.adapter_rows is not None and self.lora_prefix
+        if use_lora:
+            xin, half = act.plain(), gu.shape[1] // 2
+            add_delta(gu, self.lora, self.lora_prefix + "gate_proj", xin, batch, 0, half)
+            add_delta(gu, self.lora, self.lora_prefix + "up_proj", xin, batch, half, half)
+        a = ops.silu_mul_act(gu, want_fp8=self.down.kind == "fp8_block" and not use_lora)
         if self.shard and reduce:
-            return self.pctx.row_parallel_linear(a, self.down)
-        return ops.linear(a, self.down)
+            y = self.pctx.row_parallel_linear(a, self.down)
+        else:
+            y = ops.linear(a, self.down)
+        if use_lora:
+            if y._base is not None:
+                y = y.clone()
+            add_delta(y, self.lora, self.lora_prefix + "down_proj", a.plain(), batch)
+        return y

@@ -59,3 +59,57 @@ def bgmv(x: torch.Tensor, adapters: Dict[int, tuple], slot_of_row: torch.Tensor,
             out = torch.zeros(x.shape[0], B.shape[0], dtype=torch.float32, device=x.device)
         out.index_add_(0, rows, d)
     return out
+
+
+class LoraSet:
+    """Adapters resident on the device, addressed by slot (0 = base model).  ``delta(module, x, rows)`` gives the
+    low-rank update of one projection for a batch whose rows may belong to different adapters (or none).
+
+    Supported targets are the dense projections of attention and the SwiGLU FFN (``q/k/v/o_proj``,
+    ``gate/up/down_proj``) on an unsharded model (tensor parallel size 1)."""
+
+    def __init__(self, max_slots: int = 8):
+        self.max_slots = max_slots
+        self.slots: Dict[int, LoraAdapter] = {}
+        self.by_name: Dict[str, int] = {}
+
+    def register(self, adapter: LoraAdapter) -> int:
+        if adapter.name in self.by_name:
+            slot = self.by_name[adapter.name]
+        else:
+            free = [s for s in range(1, self.max_slots + 1) if s not in self.slots]
+            if not free:
+                raise RuntimeError(f"all {self.max_slots} adapter slots are in use")
+            slot = free[0]
+        self.slots[slot], self.by_name[adapter.name] = adapter, slot
+        return slot
+
+    def unregister(self, name: str) -> None:
+        slot = self.by_name.pop(name, None)
+        if slot is not None:
+            self.slots.pop(slot, None)
+
+    def slot_of(self, name: Optional[str]) -> int:
+        return self.by_name.get(name, 0) if name else 0
+
+    def delta(self, module: str, x: torch.Tensor, slot_of_row: torch.Tensor) -> Optional[torch.Tensor]:
+        ads, sc = {}, {}
+        for slot, ad in self.slots.items():
+            w = ad.weights.get(module)
+            if w is not None:
+                ads[slot], sc[slot] = w, ad.scaling
+        if not ads:
+            return None
+        return bgmv(x, ads, slot_of_row, sc)
+
+
+def add_delta(y: torch.Tensor, lora: Optional["LoraSet"], module: str, x: torch.Tensor, batch, col0: int = 0,
+              cols: Optional[int] = None) -> None:
+    """``y[:, col0:col0+cols] += delta`` in place when the batch carries adapter rows and an adapter targets ``module``."""
+    rows = getattr(batch, "adapter_rows", None)
+    if lora is None or rows is None:
+        return
+    d = lora.delta(module, x, rows)
+    if d is not None:
+        n = d.shape[1] if cols is None else cols
+        y[:, col0:col0 + n] += d.to(y.dtype)

@@ -40,6 +40,8 @@ class ForwardBatch:
     snapshot_plan: Dict[int, List[Tuple[int, int]]] = field(default_factory=dict)
     # optional precomputed input embeddings (MTP head / multimodal rows)
     inputs_embeds: Optional[torch.Tensor] = None
+    # LoRA: adapter slot of every row (0 = base model); None when no row of the step uses an adapter
+    adapter_rows: Optional[torch.Tensor] = None
 
     @property
     def num_tokens(self) -> int:

@@ -107,7 +107,7 @@ class DecoderLayer:
         else:
             h = self.mixer.forward(act, batch, cache.states[self.idx])
         act, residual = ops.rmsnorm_act(h, self.post_norm, cfg.rms_norm_eps, residual, cfg.norm_plus_one, self._ffn_fp8())
-        h = self.ffn.forward(act)
+        h = self.ffn.forward(act) if self.is_moe else self.ffn.forward(act, batch=batch)
         return h, residual
 
 
@@ -147,6 +147,20 @@ class DecoderLM:
             self.mtp.init_random(gen, std, dt, dev)
         self.finalize(max_pos)
         return self
+
+    def enable_lora(self, max_slots: int = 8):
+        """Attach one adapter set to the attention and dense-FFN projections of every layer (tensor parallel size 1)."""
+        from ..lora import LoraSet
+        if self.pctx.tp_size > 1:
+            raise RuntimeError("LoRA adapters are applied on unsharded projections only (tp_size 1)")
+        if getattr(self, "lora", None) is None:
+            self.lora = LoraSet(max_slots)
+            for l in self.layers:
+                if l.kind == "attention":
+                    l.mixer.lora = self.lora
+                if not l.is_moe:
+                    l.ffn.lora, l.ffn.lora_prefix = self.lora, f"layers.{l.idx}.mlp."
+        return self.lora
 
     def set_lm_head(self, head: torch.Tensor) -> None:
         if self.vocab_parallel:

@@ -136,6 +136,9 @@ class ModelRunner:
             num_decodes=num_dec, max_query_len=max(qlens), max_seq_len=max(sl),
             seq_lens_host=sl, query_lens_host=qlens, spec_verify=spec_verify,
         )
+        if any(it.seq.adapter_slot for it in items):
+            fb.adapter_rows = self._stage("adapter_rows", np.repeat(np.asarray([it.seq.adapter_slot for it in items], dtype=np.int64),
+                                                                    np.asarray(qlens)), torch.int64)
         if self.model.gdn_layers():
             fb.state_slots = self._stage("state_slots", state_slots, torch.int32)
             fb.state_slots_host, fb.has_state_host = state_slots, has_state
@@ -146,7 +149,7 @@ class ModelRunner:
     # ------------------------------------------------------------------ execution
     def _can_graph(self, batch: ForwardBatch) -> bool:
         return (self.on_gpu and self.cfg.use_cuda_graphs and batch.num_seqs > 0
-                and batch.num_decodes == batch.num_seqs and not batch.spec_verify
+                and batch.num_decodes == batch.num_seqs and not batch.spec_verify and batch.adapter_rows is None
                 and getattr(self.model, "graph_safe", True) and not self.model.gdn_layers())
 
     def forward(self, batch: ForwardBatch) -> torch.Tensor:

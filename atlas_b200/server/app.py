@@ -425,6 +425,8 @@ def create_app(state: ServerState) -> FastAPI:
         from ..lora import load_adapter
         try:
             S.adapters[name] = load_adapter(path, S.engine.engine.model) if path else S.adapters[name]
+            S.adapters[name].name = name
+            S.engine.engine.model.enable_lora().register(S.adapters[name])      # resident from now on, addressed by slot
         except KeyError:
             return _err(404, f"adapter '{name}' is not loaded and no path was given", "not_found_error")
         except Exception as e:

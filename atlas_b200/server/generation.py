@@ -187,7 +187,12 @@ class Generator:
         n_out = 0
         t0 = time.monotonic()
         ttft = None
-        gen_iter = s.engine.generate(toks, sp, request_id="req-" + req.request_id, namespace=ns, grammar=_GrammarAdapter(grammar) if grammar else None,
+        lora = getattr(s.engine.engine.model, "lora", None)
+        adapter_slot = lora.slot_of(req.adapter or s.active_adapter) if lora is not None else 0
+        if req.adapter and not adapter_slot:
+            raise ValueError(f"adapter '{req.adapter}' is not loaded")
+        gen_iter = s.engine.generate(toks, sp, request_id="req-" + req.request_id, namespace=ns, adapter_slot=adapter_slot,
+                                     grammar=_GrammarAdapter(grammar) if grammar else None,
                                      logits_processors=procs, timeout_s=req.timeout_s, disable_spec=req.disable_spec)
         final = None
         if req.echo and prompt_text:
