@@ -313,6 +313,49 @@ gated_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
   }
 }
 
+
+// Per-row LoRA update ("batched gather matrix-vector"): y[t, col0 + n] += scaling_s * sum_r B_s[n, r] * (A_s[r, :] . x[t, :])
+// with s = slot[t] (0 = no adapter: the row is left alone).  One CTA per row: warps take the r dot products of the
+// shrink step round-robin, then every thread expands a strided set of output columns.
+// Reference op replaced: kernels/gb10/common/lora_bgmv.cu (shrink / expand pair).
+struct LoraParams {
+  const __nv_bfloat16* A[8];     // [rank, K] per slot (index 0 unused)
+  const __nv_bfloat16* B[8];     // [N, rank] per slot
+  int rank[8];
+  float scaling[8];
+};
+
+__global__ void __launch_bounds__(256)
+lora_bgmv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const long long* __restrict__ slot, const LoraParams lp,
+                 __nv_bfloat16* y, long long ldy, int col0, int K, int N) {
+  __shared__ float tvec[64];
+  const int t = blockIdx.x;
+  const int s = (int)slot[t];
+  if (s <= 0 || s >= 8 || lp.A[s] == nullptr) return;
+  const int rank = lp.rank[s];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const __nv_bfloat16* xr = x + t * ldx;
+  for (int r = warp; r < rank; r += 8) {
+    const __nv_bfloat16* ar = lp.A[s] + (long long)r * K;
+    float acc = 0.f;
+    for (int k = lane * 2; k < K; k += 64) {
+      const float2 xv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xr + k));
+      const float2 av = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(ar + k));
+      acc += xv.x * av.x + xv.y * av.y;
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) tvec[r] = acc * lp.scaling[s];
+  }
+  __syncthreads();
+  for (int n = threadIdx.x; n < N; n += 256) {
+    const __nv_bfloat16* br = lp.B[s] + (long long)n * rank;
+    float acc = 0.f;
+    for (int r = 0; r < rank; ++r) acc += __bfloat162float(br[r]) * tvec[r];
+    __nv_bfloat16* dst = y + t * ldy + col0 + n;
+    *dst = __float2bfloat16_rn(__bfloat162float(*dst) + acc);
+  }
+}
+
 }  // namespace atlas
 
 using namespace atlas;
@@ -392,5 +435,25 @@ extern "C" int atlas_gated_rmsnorm(const void* x, long long ldx, const void* z, 
   gated_rmsnorm_kernel<<<(int)((units + 3) / 4), 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), ldx, reinterpret_cast<const __nv_bfloat16*>(z), ldz,
       reinterpret_cast<const __nv_bfloat16*>(w), reinterpret_cast<__nv_bfloat16*>(y), ldy, T, H, D, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+// LoRA update of y[:, col0 : col0 + N] in place; slot [T] int64 per row, per-slot A [rank,K] / B [N,rank] bf16 device
+// pointers (arrays of 8, index 0 ignored), ranks <= 64, K even.
+extern "C" int atlas_lora_bgmv(const void* x, long long ldx, const long long* slot, const void* const* A, const void* const* B,
+                               const int* rank, const float* scaling, void* y, long long ldy, int col0, int T, int K, int N,
+                               void* stream) {
+  if (T <= 0 || N <= 0) return 0;
+  if (K % 2) return -1;
+  LoraParams lp;
+  for (int i = 0; i < 8; ++i) {
+    lp.A[i] = reinterpret_cast<const __nv_bfloat16*>(A[i]);
+    lp.B[i] = reinterpret_cast<const __nv_bfloat16*>(B[i]);
+    lp.rank[i] = rank[i];
+    lp.scaling[i] = scaling[i];
+    if (rank[i] > 64) return -2;
+  }
+  lora_bgmv_kernel<<<T, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), ldx, slot, lp, reinterpret_cast<__nv_bfloat16*>(y), ldy, col0, K, N);
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
 }

@@ -109,6 +109,13 @@ def add_delta(y: torch.Tensor, lora: Optional["LoraSet"], module: str, x: torch.
     rows = getattr(batch, "adapter_rows", None)
     if lora is None or rows is None:
         return
+    if x.is_cuda and y.dtype == torch.bfloat16:
+        ads = {s: ad.weights[module] for s, ad in lora.slots.items() if module in ad.weights}
+        if ads:
+            from .ops import cuda as K
+            n = next(iter(ads.values()))[1].shape[0] if cols is None else cols
+            K.lora_bgmv(x, rows, ads, {s: lora.slots[s].scaling for s in ads}, y, col0, n)
+        return
     d = lora.delta(module, x, rows)
     if d is not None:
         n = d.shape[1] if cols is None else cols

@@ -363,6 +363,39 @@ def paged_attention(q, k_cache, v_cache, batch, scale, k_scale, v_scale, sliding
     return out
 
 
+def lora_bgmv(x: torch.Tensor, slot_of_row: torch.Tensor, adapters: dict, scaling: dict, y: torch.Tensor, col0: int, n: int) -> None:
+    """``y[:, col0:col0+n] += scaling_s * B_s (A_s x)`` per row with the row's adapter slot (in place, bf16)."""
+    d = _dev(x)
+    L = lib()
+    if not getattr(L, "_lora_bound", False):
+        L.atlas_lora_bgmv.argtypes = [_vp, _ll, _vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_i), C.POINTER(_f), _vp, _ll, _i,
+                                      _i, _i, _i, _vp]
+        L._lora_bound = True
+    A, B = (_vp * 8)(), (_vp * 8)()
+    rk, sc = (_i * 8)(), (_f * 8)()
+    keep = []
+    for slot, (a, b) in adapters.items():
+        if not (0 < slot < 8):
+            continue
+        a16, b16 = _bf16_cached(a), _bf16_cached(b)
+        keep += [a16, b16]
+        A[slot], B[slot], rk[slot], sc[slot] = a16.data_ptr(), b16.data_ptr(), a16.shape[0], float(scaling[slot])
+    if x.dtype != torch.bfloat16 or x.stride(1) != 1:
+        x = x.bfloat16().contiguous()
+    _check(L.atlas_lora_bgmv(x.data_ptr(), x.stride(0), slot_of_row.data_ptr(), A, B, rk, sc, y.data_ptr(), y.stride(0), col0,
+                             x.shape[0], x.shape[1], n, _stream()), "lora_bgmv")
+
+
+_bf16_cache: dict = {}
+
+
+def _bf16_cached(t: torch.Tensor) -> torch.Tensor:
+    hit = _bf16_cache.get(t.data_ptr())
+    if hit is None or hit[0] is not t:
+        hit = _bf16_cache[t.data_ptr()] = (t, t.to(torch.bfloat16).contiguous())
+    return hit[1]
+
+
 _TC_PREFILL = os.environ.get("ATLAS_ATTN_TC", "1") not in ("0", "false")
 
 

@@ -288,3 +288,25 @@ def test_spec_accept(K):
     d = torch.tensor([[1, 2, 3], [4, 5, 6], [7, 8, 9]], device=DEV)
     t = torch.tensor([[1, 2, 3, 0], [4, 0, 6, 1], [0, 8, 9, 2]], device=DEV)
     assert K.spec_accept(d, t).tolist() == [3, 1, 0]
+
+
+def test_lora_bgmv(K):
+    """Per-row adapter update kernel against the fp32 restatement, rows of three kinds (no adapter, slot 1, slot 3)."""
+    from atlas_b200.lora import bgmv
+    torch.manual_seed(11)
+    T, Kd, N = 37, 512, 640
+    x = torch.randn(T, Kd, device=DEV).bfloat16()
+    slots = torch.tensor([0, 1, 3] * 12 + [1], device=DEV, dtype=torch.int64)
+    ads = {1: (torch.randn(8, Kd, device=DEV) * 0.1, torch.randn(N, 8, device=DEV) * 0.1),
+           3: (torch.randn(16, Kd, device=DEV) * 0.1, torch.randn(N, 16, device=DEV) * 0.1)}
+    sc = {1: 2.0, 3: 0.5}
+    y0 = torch.randn(T, 1024, device=DEV).bfloat16()
+    y = y0.clone()
+    K.lora_bgmv(x, slots, ads, sc, y, 128, N)
+    ads16 = {s: (a.bfloat16(), b.bfloat16()) for s, (a, b) in ads.items()}
+    want = y0.float()
+    want[:, 128:128 + N] += bgmv(x, ads16, slots, sc)
+    _status_ok(K)
+    assert torch.equal(y[:, :128], y0[:, :128]) and torch.equal(y[:, 128 + N:], y0[:, 128 + N:])
+    assert torch.equal(y[slots == 0], y0[slots == 0])
+    torch.testing.assert_close(y.float(), want, atol=3e-2, rtol=2e-2)
