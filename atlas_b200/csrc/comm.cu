@@ -39,24 +39,26 @@ ATLAS_DEVICE uint32_t ld_acquire_sys(const uint32_t* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-// Wait until *p == want (flags only ever take the value of the epoch that wrote them). Bounded.
+// Wait until *p has reached epoch `want`. Bounded.
 ATLAS_DEVICE bool wait_flag(const uint32_t* p, uint32_t want, status_t* status, uint32_t site, long long max_cycles) {
   const long long t0 = clock64();
-  while (ld_acquire_sys(p) != want) {
+  while ((int32_t)(ld_acquire_sys(p) - want) < 0) {      // epochs only grow; a peer one call ahead also ends the wait
     if (clock64() - t0 > max_cycles) {
       report_status(status, kFlagTimeout, site);
       return false;
     }
-    __nanosleep(64);
+    __nanosleep(20);
   }
   return true;
 }
 
 // Block-level barrier with all peers for `phase` (0/1) of this call: data stores of the whole block are made visible
 // system-wide first.  Returns false when a peer did not arrive in time.
+// Ordering: the block's data stores happen-before the bar.sync, and the flag stores are system-scope releases issued
+// after it, so they are cumulative over the whole block's stores; one fence per signalling lane instead of one per
+// thread (a system fence by all 512 threads cost ~10 us per barrier).
 ATLAS_DEVICE bool peer_barrier(const SymmCtx& c, int phase, uint32_t epoch, status_t* status, long long max_cycles,
                                volatile int* ok_slot) {
-  __threadfence_system();
   __syncthreads();
   const int t = threadIdx.x;
   if (t < c.world) st_release_sys(c.flags[t] + ((size_t)phase * kMaxCommBlocks + blockIdx.x) * kMaxRanks + c.rank, epoch);
@@ -190,7 +192,6 @@ alltoall_rows_kernel(const SymmCtx c, const uint4* __restrict__ in, const int* _
   }
   // every block must see every other block's stores of every peer: all blocks signal, block b waits for block b
   // of each peer, and rows were strided over blocks, so wait for ALL blocks' flags of each peer instead
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x < c.world)
     st_release_sys(c.flags[threadIdx.x] + ((size_t)0 * kMaxCommBlocks + blockIdx.x) * kMaxRanks + c.rank, epoch);

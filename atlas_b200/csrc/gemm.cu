@@ -75,6 +75,8 @@ struct GemmParams {
   size_t ar_part_src_stride;    // bytes between two source ranks' partial regions
   size_t ar_result_off;         // byte offset of the [M, N] bf16 result inside the area
   int ar_rank, ar_world, ar_max_tiles;
+  int ar_mode;                  // 0 = two-shot (owner reduces, result pushed back), 1 = one-shot (partials pushed to all)
+  size_t ar_parity_stride;      // one-shot: bytes between the two epoch-parity halves of the partial area
   const int* tile_expert;       // nullptr = plain GEMM
   const int* num_m_tiles_ptr;   // device-side tile count (the host cannot know it)
   int expert_n;                 // output features per expert
@@ -98,9 +100,10 @@ ATLAS_DEVICE uint32_t ld_acquire_sys_u32(const uint32_t* p) {
 }
 ATLAS_DEVICE bool wait_flag_eq(const uint32_t* p, uint32_t want, status_t* status, uint32_t site, long long max_cycles) {
   const long long t0 = clock64();
-  while (ld_acquire_sys_u32(p) != want) {
+  // epochs only grow: a peer that is already one call ahead has written want + 1, which also ends the wait
+  while ((int32_t)(ld_acquire_sys_u32(p) - want) < 0) {
     if (clock64() - t0 > max_cycles) { report_status(status, kFlagTimeout, site); return false; }
-    __nanosleep(32);
+    __nanosleep(20);
   }
   return true;
 }
@@ -388,7 +391,67 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
       }
-      if (FUSE_AR) {
+      bool store_now = do_store;
+      if (FUSE_AR && p.ar_mode == 1) {
+        // ---- one-shot: this tile's bf16 partial goes to every peer (fragment order: 16-byte vector jv of epilogue
+        // thread r sits at vector index jv * 128 + r, so a warp's store covers 512 contiguous bytes), one flag per
+        // (tile, source) follows, and the same threads then add the peers' partials, which arrive in this rank's own
+        // memory, to their registers in rank order (identical bits on every rank) and store C locally.
+        const int tile_id = n_tile * m_tiles + m_tile;
+        const int n_tiles_all = m_tiles * p.n_tiles;
+        constexpr int kVec = HALF / 8;
+        constexpr size_t kTileBytes = (size_t)kBlockM * BLOCK_N * 2;
+        const size_t par_off = (size_t)(ar_epoch & 1u) * p.ar_parity_stride;
+        const size_t one_flags = (size_t)p.ar_max_tiles * 9;
+        const size_t frag = (size_t)(half * kVec) * kBlockM + row_in_tile;
+        const bool live = do_store && m < M_rows;
+        uint4 mine[kVec];
+        if (live) {
+#pragma unroll
+          for (int jv = 0; jv < kVec; ++jv) {
+            mine[jv].x = pack_bf16x2(acc[8 * jv + 0], acc[8 * jv + 1]);
+            mine[jv].y = pack_bf16x2(acc[8 * jv + 2], acc[8 * jv + 3]);
+            mine[jv].z = pack_bf16x2(acc[8 * jv + 4], acc[8 * jv + 5]);
+            mine[jv].w = pack_bf16x2(acc[8 * jv + 6], acc[8 * jv + 7]);
+          }
+          for (int dst = 0; dst < p.ar_world; ++dst) {
+            if (dst == p.ar_rank) continue;
+            uint4* d = reinterpret_cast<uint4*>(p.ar_data[dst] + par_off +
+                                                ((size_t)p.ar_rank * n_tiles_all + tile_id) * kTileBytes) + frag;
+#pragma unroll
+            for (int jv = 0; jv < kVec; ++jv) d[(size_t)jv * kBlockM] = mine[jv];
+          }
+        }
+        asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
+        if (do_store && epi_tid < p.ar_world && epi_tid != p.ar_rank) {
+          st_release_sys_u32(p.ar_flags[epi_tid] + one_flags + (size_t)tile_id * 8 + p.ar_rank, ar_epoch);
+          if (!wait_flag_eq(p.ar_flags[p.ar_rank] + one_flags + (size_t)tile_id * 8 + epi_tid, ar_epoch, p.status, 0x610,
+                            p.ar_max_cycles))
+            *abort_flag = 1u;
+        }
+        asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
+        store_now = do_store && *abort_flag == 0u;
+        if (live && store_now) {
+#pragma unroll
+          for (int i = 0; i < HALF; ++i) acc[i] = 0.f;
+          for (int src = 0; src < p.ar_world; ++src) {
+            const uint4* sp = reinterpret_cast<const uint4*>(p.ar_data[p.ar_rank] + par_off +
+                                                             ((size_t)src * n_tiles_all + tile_id) * kTileBytes) + frag;
+#pragma unroll
+            for (int jv = 0; jv < kVec; ++jv) {
+              const uint4 raw = src == p.ar_rank ? mine[jv] : __ldcg(sp + (size_t)jv * kBlockM);
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(h[i]);
+                acc[8 * jv + 2 * i] += f.x;
+                acc[8 * jv + 2 * i + 1] += f.y;
+              }
+            }
+          }
+        }
+      } else if (FUSE_AR) {
+        store_now = false;
         const int tile_id = n_tile * m_tiles + m_tile;
         const int owner = tile_id % p.ar_world;
         if (ok && m < M_rows) {
@@ -405,11 +468,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             dst[j / 8] = v;
           }
         }
-        __threadfence_system();
+        // the release store below is cumulative over the epilogue warps' stores ordered before it by the barrier
         asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
         if (epi_tid == 0)
           st_release_sys_u32(p.ar_flags[owner] + (size_t)tile_id * 8 + p.ar_rank, ar_epoch);
-      } else if (do_store && m < M_rows) {
+      }
+      if (store_now && m < M_rows) {
         __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * p.ldc;
 #pragma unroll
         for (int j = 0; j < HALF; j += 8) {
@@ -429,7 +493,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
       }
     }
-    if (FUSE_AR) {
+    if (FUSE_AR && p.ar_mode == 1) {
+      // nothing to drain: partial areas alternate with the epoch parity, and a rank can only be one call ahead
+      asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
+      if (epi_tid == 0) {
+        __threadfence();
+        const unsigned int done = atomicAdd(&p.ar_state[1], 1u);
+        if (done == gridDim.x - 1) {
+          p.ar_state[1] = 0;
+          __threadfence();
+          p.ar_state[0] = ar_epoch;
+        }
+      }
+    } else if (FUSE_AR) {
       const int n_tiles_all = m_tiles * p.n_tiles;
       uint32_t* my_flags = p.ar_flags[p.ar_rank];
       uint32_t* final_base_off = nullptr;
@@ -467,7 +543,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               *reinterpret_cast<uint4*>(p.ar_data[dst] + p.ar_result_off + ((size_t)gm * p.N + gn) * 2) = o;
           }
         }
-        __threadfence_system();
         asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
         if (epi_tid < p.ar_world) st_release_sys_u32(p.ar_flags[epi_tid] + final_off + tile_id, ar_epoch);
       }
@@ -607,7 +682,7 @@ extern "C" int atlas_gemm(int kind, const void* A, const void* B, void* C, const
   p.C = C; p.a_scale = a_scale; p.b_scale = b_scale; p.workspace = workspace; p.counters = counters;
   p.status = status; p.ldc = ldc; p.sa_k = sa_k; p.M = M; p.N = N; p.K = K;
   p.tile_expert = nullptr; p.num_m_tiles_ptr = nullptr; p.expert_n = 0; p.b_scale_expert_stride = 0;
-  p.ar_state = nullptr; p.ar_world = 1; p.ar_rank = 0;
+  p.ar_state = nullptr; p.ar_world = 1; p.ar_rank = 0; p.ar_mode = 0; p.ar_parity_stride = 0;
   p.k_blocks = (K + elems_per_row - 1) / elems_per_row;
   if (splits < 1) splits = 1;
   if (splits > p.k_blocks) splits = p.k_blocks;
@@ -667,7 +742,7 @@ extern "C" int atlas_gemm_grouped(int kind, const void* A, const void* B, void* 
   p.b_scale_ld = p.k_blocks;
   p.vec_ok = ((ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
   p.tile_expert = tile_expert; p.num_m_tiles_ptr = num_m_tiles; p.expert_n = N;
-  p.ar_state = nullptr; p.ar_world = 1; p.ar_rank = 0;
+  p.ar_state = nullptr; p.ar_world = 1; p.ar_rank = 0; p.ar_mode = 0; p.ar_parity_stride = 0;
   p.b_scale_expert_stride = (long long)((N + 127) / 128) * p.k_blocks;
   if (kind == 1) {
     if ((sa_k % 4) || sa_k < max_rows || (reinterpret_cast<uintptr_t>(a_scale) & 15)) return -6;
@@ -686,15 +761,21 @@ extern "C" int atlas_gemm_grouped(int kind, const void* A, const void* B, void* 
   return launch_gemm<256, false>(ta, tb, p, grid, st);
 }
 
-// Row-parallel GEMM fused with its all-reduce.  Every rank calls this with its K-shard of A and B; the summed [M, N]
-// bf16 result appears at `result_off` inside every rank's fused area (`data[rank] + result_off`, row-major, ld = N).
-// Area layout: [world partial regions of part_src_stride bytes][result M*N*2 bytes]; flags: [max_tiles][8] partial
-// flags followed by [max_tiles] final flags (uint32).  The grid is the same on every rank by construction.
+// Row-parallel GEMM fused with its all-reduce.  Every rank calls this with its K-shard of A and B.
+//   mode 0 (two-shot): tile t is reduced by rank t % world and the sum is pushed to everyone; the [M, N] bf16 result
+//     appears at `*result_off_out` inside every rank's fused area (row-major, ld = N).  Uses the upper half of the area:
+//     [world partial regions of part_src_stride bytes][result]; flags [max_tiles][8] partial + [max_tiles] final.
+//   mode 1 (one-shot): every rank pushes each partial tile to all peers and sums all partials itself into `C` (a plain
+//     local tensor).  One flag exchange instead of two; (world - 1) x the NVLink bytes, so meant for small outputs.
+//     Uses the lower half of the area, split into two epoch-parity quarters of [world][tiles] tiles; flags
+//     [max_tiles][8] at word offset 9 * max_tiles.  K may be split (`splits`, `workspace`, `counters` as in atlas_gemm).
+// The grid is the same on every rank by construction.
 extern "C" int atlas_gemm_allreduce(int kind, const void* A, const void* B, const float* a_scale, long long sa_k,
                                     const float* b_scale, int b_scale_ld, int M, int N, int K, long long lda,
                                     long long ldb, int block_n, void* const* data, void* const* flags, int rank,
                                     int world, unsigned int* state, size_t area_bytes, int max_tiles, size_t* result_off_out,
-                                    int num_sms, long long max_cycles, unsigned long long* status, void* stream) {
+                                    int num_sms, long long max_cycles, unsigned long long* status, void* stream, int mode,
+                                    void* C, long long ldc, int splits, float* workspace, int* counters) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const uint32_t esize = kind == 1 ? 1 : 2;
   const int elems_per_row = 128 / esize;
@@ -703,6 +784,7 @@ extern "C" int atlas_gemm_allreduce(int kind, const void* A, const void* B, cons
   if (kind == 1 && (K % 128)) return -3;
   if (block_n != 64 && block_n != 128) return -4;
   if (N % 8 || world < 1 || world > 8) return -5;
+  if (mode != 0 && mode != 1) return -13;
   CUtensorMap ta, tb;
   int rc = make_tmap_kmajor(&ta, A, M, K, lda, kBlockM, esize);
   if (rc) return rc;
@@ -713,10 +795,19 @@ extern "C" int atlas_gemm_allreduce(int kind, const void* A, const void* B, cons
   p.status = status; p.ldc = N; p.sa_k = sa_k; p.M = M; p.N = N; p.K = K;
   p.k_blocks = (K + elems_per_row - 1) / elems_per_row;
   p.splits = 1; p.kb_per_split = p.k_blocks;
+  if (mode == 1) {
+    if (!C) return -14;
+    if (splits < 1) splits = 1;
+    if (splits > p.k_blocks) splits = p.k_blocks;
+    p.kb_per_split = (p.k_blocks + splits - 1) / splits;
+    p.splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
+    if (p.splits > 1 && (!workspace || !counters)) return -5;
+    p.C = C; p.ldc = ldc; p.workspace = workspace; p.counters = counters;
+  }
   p.m_tiles = (M + kBlockM - 1) / kBlockM;
   p.n_tiles = (N + block_n - 1) / block_n;
   p.b_scale_ld = b_scale_ld;
-  p.vec_ok = 1;
+  p.vec_ok = mode == 1 ? (((ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0) : 1;
   p.tile_expert = nullptr; p.num_m_tiles_ptr = nullptr; p.expert_n = 0; p.b_scale_expert_stride = 0;
   if (kind == 1) {
     if ((sa_k % 4) || sa_k < (long long)p.m_tiles * kBlockM || (reinterpret_cast<uintptr_t>(a_scale) & 15)) return -6;
@@ -725,17 +816,31 @@ extern "C" int atlas_gemm_allreduce(int kind, const void* A, const void* B, cons
   const int tiles = p.m_tiles * p.n_tiles;
   if (tiles > max_tiles) return -11;
   const size_t tile_bytes = (size_t)kBlockM * block_n * 2;
-  p.ar_part_src_stride = (size_t)((tiles + world - 1) / world) * tile_bytes;
-  p.ar_result_off = ((size_t)world * p.ar_part_src_stride + 255) & ~(size_t)255;
-  if (p.ar_result_off + (size_t)M * N * 2 > area_bytes) return -12;
+  const size_t half_area = (area_bytes / 2) & ~(size_t)255;
+  size_t base_off = 0;
+  p.ar_mode = mode;
+  p.ar_parity_stride = 0;
+  p.ar_part_src_stride = 0;
+  p.ar_result_off = 0;
+  if (mode == 0) {
+    base_off = half_area;
+    p.ar_part_src_stride = (size_t)((tiles + world - 1) / world) * tile_bytes;
+    p.ar_result_off = ((size_t)world * p.ar_part_src_stride + 255) & ~(size_t)255;
+    if (p.ar_result_off + (size_t)M * N * 2 > half_area) return -12;
+    if (result_off_out) *result_off_out = base_off + p.ar_result_off;
+  } else {
+    p.ar_parity_stride = (half_area / 2) & ~(size_t)255;
+    if ((size_t)world * tiles * tile_bytes > p.ar_parity_stride) return -12;
+    if (result_off_out) *result_off_out = 0;
+  }
   for (int i = 0; i < 8; ++i) {
-    p.ar_data[i] = i < world ? reinterpret_cast<uint8_t*>(data[i]) : nullptr;
+    p.ar_data[i] = i < world ? reinterpret_cast<uint8_t*>(data[i]) + base_off : nullptr;
     p.ar_flags[i] = i < world ? reinterpret_cast<uint32_t*>(flags[i]) : nullptr;
   }
   p.ar_state = state; p.ar_rank = rank; p.ar_world = world; p.ar_max_tiles = max_tiles;
   p.ar_max_cycles = max_cycles > 0 ? max_cycles : 2000ll * 1000ll * 1000ll;
-  if (result_off_out) *result_off_out = p.ar_result_off;
-  int grid = tiles < num_sms ? tiles : num_sms;
+  const long long items = (long long)tiles * p.splits;
+  int grid = (int)(items < num_sms ? items : num_sms);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (kind == 1) {
     if (block_n == 64) return launch_gemm<64, true, true>(ta, tb, p, grid, st);

@@ -36,6 +36,31 @@ def _time(fn, iters=20, warmup=5):
     return s.elapsed_time(e) / iters
 
 
+def _time_graph(fn, iters=20, replays=4):
+    """Device time per call with the host out of the picture: ``iters`` calls captured into one CUDA graph, the graph
+    replayed ``replays`` times, the last replay timed."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        for _ in range(iters):
+            fn()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(replays - 1):
+        g.replay()
+    torch.cuda.synchronize()
+    s.record()
+    g.replay()
+    e.record()
+    e.synchronize()
+    return s.elapsed_time(e) / iters
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--bench", action="store_true")
@@ -151,9 +176,12 @@ def main() -> int:
             x = torch.randn(nbytes // 2, device=device).bfloat16()
             t_p2p = _max_over_ranks(_time(lambda: symm.all_reduce(x)), dist, device)
             t_nccl = _max_over_ranks(_time(lambda: dist.all_reduce(x)), dist, device)
+            g_p2p = _max_over_ranks(_time_graph(lambda: symm.all_reduce(x)), dist, device)
+            g_nccl = _max_over_ranks(_time_graph(lambda: dist.all_reduce(x)), dist, device)
             if rank == 0:
                 bus = 2 * (world - 1) / world * nbytes
                 print(json.dumps({"bench": "allreduce", "bytes": nbytes, "p2p_us": round(t_p2p * 1e3, 2), "nccl_us": round(t_nccl * 1e3, 2),
+                                  "graph_p2p_us": round(g_p2p * 1e3, 2), "graph_nccl_us": round(g_nccl * 1e3, 2),
                                   "p2p_busbw_GBs": round(bus / t_p2p / 1e6, 1), "nccl_busbw_GBs": round(bus / t_nccl / 1e6, 1)}), flush=True)
         # fused row-parallel GEMM vs GEMM + NCCL all-reduce (o_proj / down_proj shapes of an 8B model)
         for (M, N, Kfull, tag) in ((128, 4096, 4096, "o_proj decode"), (128, 4096, 14336, "down decode"),
@@ -163,6 +191,10 @@ def main() -> int:
             w = LinearWeight.from_dense(torch.randn(N, ks, device=device) * 0.05, "fp8_block")
             act = Act(x=xs)
             act.fp8()
+            if symm.gemm_allreduce(act, w) is None:
+                if rank == 0:
+                    print(json.dumps({"bench": "gemm_allreduce", "shape": tag, "skipped": "not fused by policy"}), flush=True)
+                continue
             t_f = _max_over_ranks(_time(lambda: symm.gemm_allreduce(act, w), iters=10), dist, device)
 
             def unfused():
@@ -170,12 +202,15 @@ def main() -> int:
                 dist.all_reduce(y)
             t_u = _max_over_ranks(_time(unfused, iters=10), dist, device)
             t_g = _max_over_ranks(_time(lambda: K.gemm_fp8_block(act.q, act.s, w.weight, w.scale), iters=10), dist, device)
+            g_f = _max_over_ranks(_time_graph(lambda: symm.gemm_allreduce(act, w), iters=10), dist, device)
+            g_g = _max_over_ranks(_time_graph(lambda: K.gemm_fp8_block(act.q, act.s, w.weight, w.scale), iters=10), dist, device)
             if rank == 0:
                 flops = 2.0 * M * N * ks
                 nv_bytes = 2.0 * (world - 1) / world * M * N * 2
                 roof_us = max(flops / 1640.6e12, nv_bytes / 770e9) * 1e6
                 print(json.dumps({"bench": "gemm_allreduce", "shape": tag, "M": M, "N": N, "K_per_rank": ks,
-                                  "fused_us": round(t_f * 1e3, 1), "gemm_plus_nccl_us": round(t_u * 1e3, 1),
+                                  "fused_us": round(t_f * 1e3, 1), "graph_fused_us": round(g_f * 1e3, 1),
+                                  "graph_gemm_only_us": round(g_g * 1e3, 1), "gemm_plus_nccl_us": round(t_u * 1e3, 1),
                                   "gemm_only_us": round(t_g * 1e3, 1), "roofline_us": round(roof_us, 1),
                                   "frac_of_roofline": round(roof_us / (t_f * 1e3), 3)}), flush=True)
     if args.engine:

@@ -12,6 +12,8 @@ and :meth:`check` poisons the communicator (same contract as ``poison_on_error``
 """
 from __future__ import annotations
 
+import os
+
 import ctypes as C
 from typing import List, Optional
 
@@ -24,6 +26,8 @@ ONESHOT_MAX_BYTES = 2 << 20
 P2P_MAX_BYTES = 4 << 20          # above this NCCL's ring/tree is faster than the two-shot kernel (measured at 2 ranks)
 FUSED_DECODE_MAX_K = 4096
 FUSED_MAX_OUT_BYTES = 2 << 20    # the fused GEMM+all-reduce pays off for decode-size outputs
+# one-shot form of the fused kernel (partials pushed to every peer) while the pushed bytes per rank stay below this
+FUSED_ONESHOT_MAX_PUSH_BYTES = int(os.environ.get("ATLAS_FUSED_ONESHOT_MAX", str(8 << 20)))
 
 
 class SymmBackend(CommBackend):
@@ -70,7 +74,7 @@ class SymmBackend(CommBackend):
         self.fused_bytes = int(fused_bytes)
         self.max_tiles = 16384
         self._fdata = self._alloc(self.fused_bytes)
-        self._fflags = self._alloc((self.max_tiles * 9) * 4)
+        self._fflags = self._alloc((self.max_tiles * 17) * 4)
         self.fstate = torch.zeros(4, dtype=torch.int32, device=device)
         fh = [None] * self.world_size
         base.dist.all_gather_object(fh, (self._export(self._fdata), self._export(self._fflags)), group=base.group)
@@ -81,9 +85,10 @@ class SymmBackend(CommBackend):
         self.fdata_arr = (_vp * 8)(*(fd + [None] * (8 - len(fd))))
         self.fflag_arr = (_vp * 8)(*(ff + [None] * (8 - len(ff))))
         lib.atlas_gemm_allreduce.argtypes = [_i, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _ll, _ll, _i, C.POINTER(_vp),
-                                             C.POINTER(_vp), _i, _i, _vp, _sz, _i, C.POINTER(_sz), _i, _ll, _vp, _vp]
+                                             C.POINTER(_vp), _i, _i, _vp, _sz, _i, C.POINTER(_sz), _i, _ll, _vp, _vp,
+                                             _i, _vp, _ll, _i, _vp, _vp]
         base.barrier()
-        self.calls = {"oneshot": 0, "twoshot": 0, "alltoall": 0, "fallback": 0, "gemm_allreduce": 0}
+        self.calls = {"oneshot": 0, "twoshot": 0, "alltoall": 0, "fallback": 0, "gemm_allreduce": 0, "gemm_allreduce_oneshot": 0}
 
     # ------------------------------------------------------------------ IPC plumbing
     def _alloc(self, nbytes: int) -> int:
@@ -138,8 +143,9 @@ class SymmBackend(CommBackend):
             return self.base.all_reduce(t)
         self.calls["oneshot" if kind == 0 else "twoshot"] += 1
         K = self.K
+        blocks = max(1, min(self.blocks, nbytes // 16384))       # every block pays one flag exchange per peer
         rc = self.lib.atlas_allreduce_bf16(kind, self.data_arr, self.flag_arr, self.rank, self.world_size, t.data_ptr(),
-                                           t.data_ptr(), nbytes, self.slot_bytes, self.state.data_ptr(), self.blocks,
+                                           t.data_ptr(), nbytes, self.slot_bytes, self.state.data_ptr(), blocks,
                                            K._status_ptr[self.dev_index], self.wait_cycles, K._stream())
         K._check(rc, "allreduce_p2p")
         return t
@@ -184,14 +190,28 @@ class SymmBackend(CommBackend):
         N = b.shape[0]
         if N % 8 or a.stride(1) != 1 or M * N * 2 > FUSED_MAX_OUT_BYTES:
             return None
-        if M <= 128 and Kd > FUSED_DECODE_MAX_K:
-            # decode-size rows with a long K: the fused kernel has no split-K, so it runs on N/64 CTAs only; the split-K
-            # GEMM followed by the one-shot all-reduce is faster there (2 x B200, 128 x 4096 x 7168: 46 us vs 59 us)
-            return None
         sms = K._num_sms[self.dev_index]
-        bn = 128 if ((M + 127) // 128) * ((N + 127) // 128) >= sms else 64
-        tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
-        need = ((tiles + self.world_size - 1) // self.world_size) * 128 * bn * 2 * self.world_size + 256 + M * N * 2
+        oneshot = M * N * 2 * (self.world_size - 1) <= FUSED_ONESHOT_MAX_PUSH_BYTES
+        ws = cnt = out = None
+        splits = 1
+        if oneshot:
+            # every rank pushes its partial tiles to all peers and sums locally: one flag exchange, K may be split
+            bn, splits = K.gemm_plan(M, N, Kd, kind, sms)
+            bn = min(bn, 128)
+            tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
+            need = 4 * self.world_size * tiles * 128 * bn * 2 + 1024
+            if splits > 1:
+                ws = K.scratch("gemm_ws", K._GEMM_WS_BYTES, a.device)
+                cnt = K.scratch("gemm_counters", 1 << 18, a.device)
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+        else:
+            if M <= 128 and Kd > FUSED_DECODE_MAX_K:
+                # decode-size rows with a long K and an output too large for the one-shot form: the two-shot kernel has
+                # no split-K, so it would run on N/64 CTAs only; split-K GEMM + all-reduce is faster there
+                return None
+            bn = 128 if ((M + 127) // 128) * ((N + 127) // 128) >= sms else 64
+            tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
+            need = 2 * (((tiles + self.world_size - 1) // self.world_size) * 128 * bn * 2 * self.world_size + 256 + M * N * 2) + 512
         if tiles > self.max_tiles or need > self.fused_bytes:
             return None
         off = _sz(0)
@@ -200,9 +220,13 @@ class SymmBackend(CommBackend):
                                            b_scale.shape[1] if b_scale is not None else 0, M, N, Kd, a.stride(0), b.stride(0),
                                            bn, self.fdata_arr, self.fflag_arr, self.rank, self.world_size,
                                            self.fstate.data_ptr(), self.fused_bytes, self.max_tiles, C.byref(off), sms,
-                                           self.wait_cycles, K._status_ptr[self.dev_index], K._stream())
+                                           self.wait_cycles, K._status_ptr[self.dev_index], K._stream(),
+                                           1 if oneshot else 0, K._ptr(out), N, splits, K._ptr(ws), K._ptr(cnt))
         K._check(rc, "gemm_allreduce")
         self.calls["gemm_allreduce"] += 1
+        if oneshot:
+            self.calls["gemm_allreduce_oneshot"] += 1
+            return out
         return _device_view(self._fdata + off.value, (M, N), torch.bfloat16, self.device)
 
     # everything else: the bootstrap backend
