@@ -362,14 +362,15 @@ attn_decode_kernel(const AttnParams p, int stages, status_t* status) {
   const int c = lane & 3, rq = lane >> 2;
   const int G = p.Hq / p.Hkv;
   const int b = p.seq_base + blockIdx.z, kvh = blockIdx.x, split = blockIdx.y;
-  const int L = p.seq_lens[b];
-  const int q_row0 = p.query_start_loc[b];
-
+  chain_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     *abort_flag = 0;
     mbar_fence_init();
   }
+  chain_wait();                       // everything above is on-chip; global memory is only touched from here on
+  const int L = p.seq_lens[b];
+  const int q_row0 = p.query_start_loc[b];
   const int n_blocks = (L + bs - 1) / bs;
   const int per_split = (n_blocks + p.num_splits - 1) / p.num_splits;
   int blk_lo = split * per_split;
@@ -582,6 +583,8 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
                                   int D, int splits, float v_scale) {
   const int head = blockIdx.x, bi = blockIdx.y, d = threadIdx.x;
   const long long base = ((long long)bi * Hq + head) * splits;
+  chain_trigger();
+  chain_wait();
   float m = -INFINITY;
   for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
   float acc = 0.f, l = 0.f;
@@ -612,13 +615,12 @@ static int launch_decode_bs(const AttnParams& p, int B, status_t* status, cudaSt
     attr_smem = smem;
   }
   dim3 grid(p.Hkv, p.num_splits, B);
-  attn_decode_kernel<D, BS><<<grid, kDecodeThreads, smem, st>>>(p, stages, status);
-  if (cudaGetLastError() != cudaSuccess) return -21;
+  if (launch_chain(attn_decode_kernel<D, BS>, grid, dim3(kDecodeThreads), (size_t)smem, st, p, stages, status) != cudaSuccess) return -21;
   if (p.num_splits > 1) {
     dim3 g2(p.Hq, B);
-    attn_merge_kernel<<<g2, D, 0, st>>>(p.part_o, p.part_ml, p.out, p.ldo, p.query_start_loc, p.seq_base, p.Hq, D,
-                                        p.num_splits, p.v_scale);
-    if (cudaGetLastError() != cudaSuccess) return -22;
+    if (launch_chain(attn_merge_kernel, g2, dim3(D), 0, st, p.part_o, p.part_ml, p.out, p.ldo, p.query_start_loc, p.seq_base,
+                     p.Hq, D, p.num_splits, p.v_scale) != cudaSuccess)
+      return -22;
   }
   return 0;
 }

@@ -11,6 +11,7 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
+#include <cstdlib>
 #include <stdint.h>
 
 #define ATLAS_DEVICE __device__ __forceinline__
@@ -247,6 +248,39 @@ ATLAS_DEVICE float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
+}
+
+
+// ----------------------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with launch_chain() may start while its predecessor in the stream is still running: its on-chip
+// prologue (barrier init, TMEM allocation, descriptor prefetch) and the launch latency overlap the predecessor's tail.
+// chain_wait() blocks until the predecessor grid has completed and its memory operations are visible, so every global
+// memory access of such a kernel comes after it; chain_trigger() lets the next kernel in the stream start launching.
+// A kernel launched the ordinary way is unaffected by either instruction.
+ATLAS_DEVICE void chain_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+ATLAS_DEVICE void chain_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+inline bool chain_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("ATLAS_PDL");
+    return e == nullptr || e[0] != '0';
+  }();
+  return on;
+}
+
+template <typename... P, typename... A>
+inline cudaError_t launch_chain(void (*kern)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = chain_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<P>(args)...);
 }
 
 }  // namespace atlas

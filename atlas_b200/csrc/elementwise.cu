@@ -67,6 +67,8 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bf
                const __nv_bfloat16* __restrict__ w, __nv_bfloat16* res_out, long long ldro, __nv_bfloat16* y,
                long long ldy, uint8_t* q, long long ldq, float* scale, long long scale_ld, int H, float eps,
                int plus_one) {
+  chain_trigger();
+  chain_wait();
   const int t = blockIdx.x;
   const int tid = threadIdx.x;
   float vals[kMaxIters][8];
@@ -136,6 +138,8 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bf
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, long long ld, int I, __nv_bfloat16* y, long long ldy, uint8_t* q,
                 long long ldq, float* scale, long long scale_ld, const int* live_tiles) {
+  chain_trigger();
+  chain_wait();
   const int t = blockIdx.x;           // rows on grid.x: row counts can exceed the 65535 limit of grid.y
   if (live_tiles && t >= (*live_tiles) * 128) return;      // expert-sorted buffers: rows past the live tiles are unused
   const int e = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
@@ -168,6 +172,8 @@ silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, long long ld, int I, __nv_
 __global__ void __launch_bounds__(256)
 quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int K, uint8_t* q, long long ldq, float* scale,
                  long long scale_ld) {
+  chain_trigger();
+  chain_wait();
   const int t = blockIdx.x;           // rows on grid.x: row counts can exceed the 65535 limit of grid.y
   const int e = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   const bool live = e < K;
@@ -205,6 +211,8 @@ struct RopeKvParams {
 __global__ void __launch_bounds__(128)
 rope_kv_write_kernel(const RopeKvParams p) {
   extern __shared__ float sm_rope[];          // [4 warps][D]
+  chain_trigger();
+  chain_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long unit = (long long)blockIdx.x * 4 + warp;
   const int heads = p.Hq + 2 * p.Hkv;
@@ -376,9 +384,9 @@ extern "C" int atlas_rmsnorm(const void* x, long long ldx, const void* residual,
   auto RO = reinterpret_cast<__nv_bfloat16*>(res_out);
   auto Y = reinterpret_cast<__nv_bfloat16*>(y);
   auto Qp = reinterpret_cast<uint8_t*>(q);
-  if (iters == 1) rmsnorm_kernel<1><<<T, threads, 0, st>>>(X, ldx, R, ldr, W, RO, ldro, Y, ldy, Qp, ldq, scale, scale_ld, H, eps, plus_one);
-  else if (iters == 2) rmsnorm_kernel<2><<<T, threads, 0, st>>>(X, ldx, R, ldr, W, RO, ldro, Y, ldy, Qp, ldq, scale, scale_ld, H, eps, plus_one);
-  else if (iters == 4) rmsnorm_kernel<4><<<T, threads, 0, st>>>(X, ldx, R, ldr, W, RO, ldro, Y, ldy, Qp, ldq, scale, scale_ld, H, eps, plus_one);
+  if (iters == 1) launch_chain(rmsnorm_kernel<1>, dim3(T), dim3(threads), 0, st, X, ldx, R, ldr, W, RO, ldro, Y, ldy, Qp, ldq, scale, scale_ld, H, eps, plus_one);
+  else if (iters == 2) launch_chain(rmsnorm_kernel<2>, dim3(T), dim3(threads), 0, st, X, ldx, R, ldr, W, RO, ldro, Y, ldy, Qp, ldq, scale, scale_ld, H, eps, plus_one);
+  else if (iters == 4) launch_chain(rmsnorm_kernel<4>, dim3(T), dim3(threads), 0, st, X, ldx, R, ldr, W, RO, ldro, Y, ldy, Qp, ldq, scale, scale_ld, H, eps, plus_one);
   else return -3;
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
 }
@@ -388,7 +396,7 @@ extern "C" int atlas_silu_mul(const void* gu, long long ld, int T, int I, void* 
   if (T <= 0) return 0;
   if (I % 8 || (q && I % 128)) return -1;
   dim3 grid(T, (I / 8 + 255) / 256);
-  silu_mul_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_chain(silu_mul_kernel, grid, dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
       reinterpret_cast<const __nv_bfloat16*>(gu), ld, I, reinterpret_cast<__nv_bfloat16*>(y), ldy,
       reinterpret_cast<uint8_t*>(q), ldq, scale, scale_ld, live_tiles);
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
@@ -399,7 +407,7 @@ extern "C" int atlas_quant_fp8(const void* x, long long ld, int T, int K, void* 
   if (T <= 0) return 0;
   if (K % 128) return -1;
   dim3 grid(T, (K / 8 + 255) / 256);
-  quant_fp8_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_chain(quant_fp8_kernel, grid, dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
       reinterpret_cast<const __nv_bfloat16*>(x), ld, K, reinterpret_cast<uint8_t*>(q), ldq, scale, scale_ld);
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
 }
@@ -423,7 +431,7 @@ extern "C" int atlas_rope_kv_write(void* q, long long ldq, const void* k, long l
   p.kv_fp8 = kv_fp8; p.plus_one = plus_one; p.eps = eps; p.inv_k_scale = 1.f / k_scale; p.inv_v_scale = 1.f / v_scale;
   const long long units = (long long)T * (Hq + 2 * Hkv);
   const int grid = (int)((units + 3) / 4);
-  rope_kv_write_kernel<<<grid, 128, 4 * D * sizeof(float), reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  launch_chain(rope_kv_write_kernel, dim3(grid), dim3(128), 4 * D * sizeof(float), reinterpret_cast<cudaStream_t>(stream), p);
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
 }
 

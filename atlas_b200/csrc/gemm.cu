@@ -75,6 +75,7 @@ struct GemmParams {
   size_t ar_part_src_stride;    // bytes between two source ranks' partial regions
   size_t ar_result_off;         // byte offset of the [M, N] bf16 result inside the area
   int ar_rank, ar_world, ar_max_tiles;
+  int prefetch_b;               // k-slices of B to request into L2 ahead of the tile ring (0 = off)
   int ar_mode;                  // 0 = two-shot (owner reduces, result pushed back), 1 = one-shot (partials pushed to all)
   size_t ar_parity_stride;      // one-shot: bytes between the two epoch-parity halves of the partial area
   const int* tile_expert;       // nullptr = plain GEMM
@@ -164,14 +165,40 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     tmem_alloc(tmem_slot, Cfg::kTmemCols);
     tmem_relinquish();
   }
+  // Weight tiles do not depend on the previous kernel in the stream, so the producer asks for the first ones (L2 only)
+  // before waiting for that kernel: their HBM latency overlaps its tail.  `pf_*` is a cursor over this CTA's
+  // (item, k-slice) sequence that stays p.prefetch_b slices ahead of the ring's loads.
+  int pf_item = blockIdx.x, pf_kb = 0, pf_kb1 = 0, pf_row = 0, pf_ahead = 0;
+  const bool pf_on = p.prefetch_b > 0 && p.tile_expert == nullptr;
+  const int pf_total = p.m_tiles * p.n_tiles * p.splits;
+  auto pf_enter = [&]() {
+    if (pf_item < pf_total) {
+      const int rest = pf_item / p.m_tiles;
+      const int split = rest / p.n_tiles;
+      pf_row = (rest % p.n_tiles) * BLOCK_N;
+      pf_kb = split * p.kb_per_split;
+      pf_kb1 = min(p.k_blocks, pf_kb + p.kb_per_split);
+    }
+  };
+  auto pf_step = [&]() {            // request one slice and advance the cursor
+    if (pf_item >= pf_total) return;
+    tma_prefetch_l2_2d(&tmap_b, pf_kb * kElemsPerRow, pf_row);
+    if (++pf_kb >= pf_kb1) { pf_item += gridDim.x; pf_enter(); }
+  };
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (pf_on) {
+      pf_enter();
+      for (; pf_ahead < p.prefetch_b; ++pf_ahead) pf_step();
+    }
   }
+  chain_trigger();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  chain_wait();                         // barriers, TMEM and descriptors are set up; global memory from here on
 
   const int m_tiles = p.tile_expert ? *p.num_m_tiles_ptr : p.m_tiles;
   const int total_items = m_tiles * p.n_tiles * p.splits;
@@ -205,6 +232,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           tma_load_2d(sa, &tmap_a, &full[stage], kb * kElemsPerRow, m_tile * kBlockM);
           tma_load_2d(sa + Cfg::kABytes, &tmap_b, &full[stage], kb * kElemsPerRow,
                       (p.tile_expert ? p.tile_expert[m_tile] * p.expert_n : 0) + n_tile * BLOCK_N);
+          if (pf_on) pf_step();
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -650,8 +678,17 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
     if (e != cudaSuccess) return -20;
     attr_done = true;
   }
-  kern<<<grid, gemm_threads(BLOCK_N, FP8), Cfg::kSmemBytes, st>>>(ta, tb, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+  return launch_chain(kern, dim3(grid), dim3(gemm_threads(BLOCK_N, FP8)), (size_t)Cfg::kSmemBytes, st, ta, tb, p) == cudaSuccess ? 0 : -21;
+}
+
+// k-slices of weights requested into L2 ahead of the tile ring for decode-size GEMMs (ATLAS_GEMM_PREFETCH, 0 = off)
+static int prefetch_depth() {
+  static const int d = [] {
+    const char* e = getenv("ATLAS_GEMM_PREFETCH");
+    const int v = e ? atoi(e) : 0;   // off: on B200 the extra requests compete with the ring for TMA throughput (slower)
+    return v < 0 ? 0 : (v > 64 ? 64 : v);
+  }();
+  return d;
 }
 
 }  // namespace atlas
@@ -682,7 +719,7 @@ extern "C" int atlas_gemm(int kind, const void* A, const void* B, void* C, const
   p.C = C; p.a_scale = a_scale; p.b_scale = b_scale; p.workspace = workspace; p.counters = counters;
   p.status = status; p.ldc = ldc; p.sa_k = sa_k; p.M = M; p.N = N; p.K = K;
   p.tile_expert = nullptr; p.num_m_tiles_ptr = nullptr; p.expert_n = 0; p.b_scale_expert_stride = 0;
-  p.ar_state = nullptr; p.ar_world = 1; p.ar_rank = 0; p.ar_mode = 0; p.ar_parity_stride = 0;
+  p.ar_state = nullptr; p.ar_world = 1; p.ar_rank = 0; p.ar_mode = 0; p.ar_parity_stride = 0; p.prefetch_b = 0;
   p.k_blocks = (K + elems_per_row - 1) / elems_per_row;
   if (splits < 1) splits = 1;
   if (splits > p.k_blocks) splits = p.k_blocks;
@@ -700,6 +737,7 @@ extern "C" int atlas_gemm(int kind, const void* A, const void* B, void* C, const
   p.vec_ok = ((ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
   const long long items = (long long)p.m_tiles * p.n_tiles * p.splits;
   int grid = (int)(items < num_sms ? items : num_sms);
+  p.prefetch_b = p.m_tiles <= 2 ? prefetch_depth() : 0;      // weights read once from HBM: run ahead of the ring in L2
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (kind == 1) {
     if (block_n == 64) return launch_gemm<64, true>(ta, tb, p, grid, st);
@@ -742,7 +780,7 @@ extern "C" int atlas_gemm_grouped(int kind, const void* A, const void* B, void* 
   p.b_scale_ld = p.k_blocks;
   p.vec_ok = ((ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
   p.tile_expert = tile_expert; p.num_m_tiles_ptr = num_m_tiles; p.expert_n = N;
-  p.ar_state = nullptr; p.ar_world = 1; p.ar_rank = 0; p.ar_mode = 0; p.ar_parity_stride = 0;
+  p.ar_state = nullptr; p.ar_world = 1; p.ar_rank = 0; p.ar_mode = 0; p.ar_parity_stride = 0; p.prefetch_b = 0;
   p.b_scale_expert_stride = (long long)((N + 127) / 128) * p.k_blocks;
   if (kind == 1) {
     if ((sa_k % 4) || sa_k < max_rows || (reinterpret_cast<uintptr_t>(a_scale) & 15)) return -6;
@@ -841,6 +879,7 @@ extern "C" int atlas_gemm_allreduce(int kind, const void* A, const void* B, cons
   p.ar_max_cycles = max_cycles > 0 ? max_cycles : 2000ll * 1000ll * 1000ll;
   const long long items = (long long)tiles * p.splits;
   int grid = (int)(items < num_sms ? items : num_sms);
+  p.prefetch_b = p.m_tiles <= 2 ? prefetch_depth() : 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (kind == 1) {
     if (block_n == 64) return launch_gemm<64, true, true>(ta, tb, p, grid, st);
