@@ -102,7 +102,8 @@ int atlas_attn_prefill(const void* q, long long ldq, void* out, long long ldo, c
                        float k_scale, float v_scale, int Hq, int Hkv, int D, int block_size, int window, void* stream);
 
 // ---- sampling (sampling.cu)
-int atlas_argmax(const void* logits, long long ld, int B, int V, int is_bf16, long long* out, void* stream);
+int atlas_argmax(const void* logits, long long ld, int B, int V, int is_bf16, long long* out, float* out_val,
+                 void* stream);
 int atlas_sample(const void* logits, long long ld, int B, int V, int is_bf16, const float* temperature,
                  const int* top_k, const float* top_p, const float* min_p, const float* uniform, long long* out,
                  void* stream);

@@ -20,7 +20,7 @@ from .config import EngineConfig, ModelConfig
 from .kv import BlockPool, RadixCache, SlotPool
 from .models import CacheStore, DecoderLM, ForwardBatch
 from .runner import ModelRunner
-from .sampling import Sampler, SamplingParams
+from .sampling import Sampler, SamplingParams, SamplerOutput
 from .sched import FinishReason, ScheduledSeq, Scheduler, SchedulerOutput, SeqStatus, Sequence
 from .sched.spec import SpecController
 from .utils.metrics import EngineStats
@@ -122,7 +122,10 @@ class LLMEngine:
                     request_id: Optional[str] = None, namespace: Hashable = 0, priority: int = 0,
                     timeout_s: Optional[float] = None, grammar: Any = None,
                     logits_processors: Optional[List[Callable]] = None, disable_spec: bool = False,
-                    stop_checker: Optional[Callable[[Sequence], bool]] = None, adapter_slot: int = 0) -> str:
+                    stop_checker: Optional[Callable[[Sequence], bool]] = None, adapter_slot: int = 0,
+                    needs_full_logits: bool = False) -> str:
+        """``needs_full_logits``: set on follower ranks for a request whose leader-side sampling needs the whole
+        logits row (grammar mask, logit processors), so that every rank takes the same path to the logits."""
         sampling = sampling or SamplingParams()
         sampling.validate()
         rid = request_id or f"req-{next(self._ids)}"
@@ -143,6 +146,7 @@ class LLMEngine:
                        deadline=(time.monotonic() + t_out) if t_out else None, grammar=grammar,
                        logits_processors=list(logits_processors or []), disable_spec=disable_spec,
                        adapter_slot=adapter_slot)
+        seq.needs_full_logits = bool(needs_full_logits or grammar is not None or logits_processors)
         self._seqs[rid] = seq
         if stop_checker is not None:
             self._stop_checkers[rid] = stop_checker
@@ -206,12 +210,18 @@ class LLMEngine:
         sampled: Dict[int, List[int]] = {}
         lps: Dict[int, list] = {}
         if rows:
+            seqs_rows = [out.items[i].seq for i in row_owner]
+            verify = any(out.items[i].verify_drafts for i in set(row_owner))
+            # vocab-parallel head and a plain greedy step: exchange one (max, index) pair per row instead of gathering
+            # the logits.  The test only reads replicated request state, so every rank decides alike.
+            greedy_tp = (getattr(self.model, "vocab_parallel", False) and not verify
+                         and self.sampler.fast_greedy(seqs_rows))
             with phase("logits"):
-                logits = self.runner.logits(hidden, rows)       # every rank: the vocab-parallel gather is a collective
+                # every rank: the vocab-parallel gather / exchange is a collective
+                logits = self.runner.greedy_tokens(hidden, rows) if greedy_tp else self.runner.logits(hidden, rows)
             if not follower:
-                seqs_rows = [out.items[i].seq for i in row_owner]
-                so = self.sampler(logits, seqs_rows) if not any(out.items[i].verify_drafts for i in set(row_owner)) \
-                    else self._sample_verify_rows(logits, out, row_owner)
+                so = SamplerOutput(logits.tolist()) if greedy_tp else (
+                    self.sampler(logits, seqs_rows) if not verify else self._sample_verify_rows(logits, out, row_owner))
                 for j, i in enumerate(row_owner):
                     sampled.setdefault(i, []).append(so.tokens[j])
                     if so.logprobs is not None and so.logprobs[j] is not None:

@@ -219,6 +219,24 @@ class DecoderLM:
             logits = self.pctx.comm.all_gather(logits, dim=-1)
         return logits
 
+    @torch.inference_mode()
+    def greedy_tokens(self, hidden: torch.Tensor, indices: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Argmax token per row without materialising the full-vocabulary logits on any rank: each rank takes the
+        argmax of its vocabulary shard, the ranks exchange one (max, index) pair per row and the best shard wins
+        (ties go to the lowest global index).  Replaces the all-gather of ``[rows, vocab]`` logits of
+        :meth:`compute_logits` when every row of the step is plain greedy."""
+        h = hidden if indices is None else hidden[indices]
+        logits = ops.linear(h, self.lm_head)
+        idx, val = ops.argmax(logits, with_value=True)
+        if not (self.vocab_parallel and self.pctx.comm is not None):
+            return idx
+        shard = self.cfg.vocab_size // self.pctx.tp_size
+        pair = torch.stack([val.double(), (idx + self.pctx.tp_rank * shard).double()], dim=1)       # [B, 2], exact
+        allp = self.pctx.comm.all_gather(pair, dim=1).view(pair.shape[0], self.pctx.tp_size, 2)
+        vals, ids = allp[..., 0], allp[..., 1]
+        best = ref.argmax_first(vals)
+        return ids.gather(1, best[:, None])[:, 0].to(torch.int64)
+
     def commit_spec(self, accepted_rows: List[int], cache: CacheStore) -> None:
         """After speculative verification: fold the accepted rows into every GDN layer's state."""
         for l in self.layers:

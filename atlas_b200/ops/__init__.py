@@ -192,10 +192,13 @@ def moe_route(logits, top_k, norm_topk, scoring="softmax"):
 
 
 # ----------------------------------------------------------------------------- sampling
-def argmax(logits: torch.Tensor) -> torch.Tensor:
+def argmax(logits: torch.Tensor, with_value: bool = False):
     if on_gpu(logits):
-        return cuda_ops().argmax(logits)
-    return ref.argmax_first(logits)
+        return cuda_ops().argmax(logits, with_value)
+    idx = ref.argmax_first(logits)
+    if with_value:
+        return idx, logits.float().gather(-1, idx[:, None])[:, 0]
+    return idx
 
 
 def sample(logits, temperature, top_k, top_p, min_p, uniform):

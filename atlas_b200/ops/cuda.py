@@ -53,7 +53,7 @@ def load() -> None:
                                        _i, _i, _i, _i, _vp]
     lib.atlas_attn_prefill_tc.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _f, _f, _f,
                                           _i, _i, _i, _i, _i, _vp, _vp]
-    lib.atlas_argmax.argtypes = [_vp, _ll, _i, _i, _i, _vp, _vp]
+    lib.atlas_argmax.argtypes = [_vp, _ll, _i, _i, _i, _vp, _vp, _vp]
     lib.atlas_sample.argtypes = [_vp, _ll, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]
     lib.atlas_spec_accept.argtypes = [_vp, _vp, _i, _i, _vp, _vp]
     _LIB = lib
@@ -405,14 +405,16 @@ def _tc_prefill_ok(q, Hq, Hkv, D, bs, window, k_cache) -> bool:
 
 
 # ----------------------------------------------------------------------------- sampling
-def argmax(logits: torch.Tensor) -> torch.Tensor:
+def argmax(logits: torch.Tensor, with_value: bool = False):
+    """Row-wise argmax (lowest index on ties); ``with_value`` also returns the row maxima as fp32."""
     B, V = logits.shape
     _dev(logits)
     assert logits.stride(1) == 1 and logits.dtype in (torch.bfloat16, torch.float32)
     out = torch.empty(B, dtype=torch.int64, device=logits.device)
+    val = torch.empty(B, dtype=torch.float32, device=logits.device) if with_value else None
     _check(lib().atlas_argmax(logits.data_ptr(), logits.stride(0), B, V, 1 if logits.dtype == torch.bfloat16 else 0,
-                              out.data_ptr(), _stream()), "argmax")
-    return out
+                              out.data_ptr(), _ptr(val), _stream()), "argmax")
+    return (out, val) if with_value else out
 
 
 def sample(logits, temperature, top_k, top_p, min_p, uniform):

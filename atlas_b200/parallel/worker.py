@@ -146,14 +146,16 @@ class DistributedEngine:
 
     def add_request(self, prompt_tokens, sampling: Optional[SamplingParams] = None, request_id: Optional[str] = None,
                     namespace=0, priority: int = 0, timeout_s: Optional[float] = None, grammar: Any = None,
-                    logits_processors=None, disable_spec: bool = False, stop_checker=None, adapter_slot: int = 0) -> str:
+                    logits_processors=None, disable_spec: bool = False, stop_checker=None, adapter_slot: int = 0,
+                    needs_full_logits: bool = False) -> str:
         assert self.control.is_leader, "requests enter on rank 0"
         sampling = sampling or SamplingParams()
         rid = self.engine.add_request(prompt_tokens, sampling, request_id, namespace, priority, timeout_s, grammar,
                                       logits_processors, disable_spec, stop_checker, adapter_slot)
         self.control.note_add(rid, [int(t) for t in prompt_tokens], sampling,
                               {"namespace": namespace, "priority": priority, "disable_spec": disable_spec,
-                               "adapter_slot": adapter_slot})
+                               "adapter_slot": adapter_slot,
+                               "needs_full_logits": bool(needs_full_logits or grammar is not None or logits_processors)})
         return rid
 
     def abort(self, request_id: str) -> bool:

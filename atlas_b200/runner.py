@@ -168,6 +168,11 @@ class ModelRunner:
         idx = self._stage("rows", rows, torch.int64)
         return self.model.compute_logits(hidden, idx)
 
+    def greedy_tokens(self, hidden: torch.Tensor, rows: List[int]) -> torch.Tensor:
+        if len(rows) == hidden.shape[0] and rows == list(range(len(rows))):
+            return self.model.greedy_tokens(hidden)
+        return self.model.greedy_tokens(hidden, self._stage("rows", rows, torch.int64))
+
     def copy_state(self, src_slot: int, dst_slot: int) -> None:
         for st in self.cache.states.values():
             st["conv"][dst_slot].copy_(st["conv"][src_slot])

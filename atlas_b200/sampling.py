@@ -149,14 +149,19 @@ class Sampler:
         p: SamplingParams = seq.sampling
         return (not p.greedy or p.needs_penalties or bool(p.logit_bias) or p.top_n_sigma > 0
                 or (p.min_tokens > 0 and seq.num_output_tokens < p.min_tokens)
-                or seq.grammar is not None or bool(seq.logits_processors) or p.logprobs)
+                or seq.grammar is not None or bool(seq.logits_processors) or p.logprobs
+                or getattr(seq, "needs_full_logits", False))
+
+    def fast_greedy(self, seqs: Sequence["object"]) -> bool:
+        """True when every row is plain greedy: the step only needs the argmax of each logits row."""
+        return not any(self._row_needs_slow_path(s) for s in seqs)
 
     @torch.inference_mode()
     def __call__(self, logits: torch.Tensor, seqs: Sequence["object"]) -> SamplerOutput:
         """``logits [B,V]`` (one row per sequence, same order)."""
         B = logits.shape[0]
         assert B == len(seqs)
-        if not any(self._row_needs_slow_path(s) for s in seqs):
+        if self.fast_greedy(seqs):
             return SamplerOutput(ops.argmax(logits).tolist())
         lf = logits.float().clone()
         dev = lf.device

@@ -152,3 +152,29 @@ def test_follower_gives_up_when_leader_vanishes():
     assert err and "timed out" in str(err[0])
     assert control.comm.unhealthy and fault.FAULT_LATCH.tripped
     fault.FAULT_LATCH.reset_for_tests()
+
+
+def test_vocab_parallel_greedy_and_leader_only_processors_agree_on_the_logits_path():
+    """Plain greedy steps exchange (max, index) pairs instead of gathering logits; a request whose leader-side sampling
+    needs the whole row (a logits processor that only exists on rank 0) must switch every rank to the gather."""
+    prompts = _prompts()
+    sp = SamplingParams(max_tokens=8, ignore_eos=True)
+    base = LLMEngine(build_model(tiny_dense()).init_random(0), _ecfg()).generate(prompts[:2], sp)
+    seen = []
+
+    def ban_token(row, seq):
+        seen.append(int(row.shape[-1]))
+        return row
+
+    def leader(de):
+        assert de.engine.model.vocab_parallel
+        a = de.add_request(prompts[0], SamplingParams(max_tokens=8, ignore_eos=True))
+        for _ in range(3):
+            de.step()                                   # greedy-only steps: pair exchange
+        b = de.add_request(prompts[1], SamplingParams(max_tokens=8, ignore_eos=True), logits_processors=[ban_token])
+        done = _drain(de, [a, b])
+        return [done[a].output_tokens, done[b].output_tokens]
+
+    got, followers = _run_world(tiny_dense, _ecfg(), leader)
+    assert got == [o.output_tokens for o in base]
+    assert seen and all(v == tiny_dense().vocab_size for v in seen)      # the processor saw full-vocabulary rows
