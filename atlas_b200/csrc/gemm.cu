@@ -462,18 +462,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (live && store_now) {
 #pragma unroll
           for (int i = 0; i < HALF; ++i) acc[i] = 0.f;
-          for (int src = 0; src < p.ar_world; ++src) {
-            const uint4* sp = reinterpret_cast<const uint4*>(p.ar_data[p.ar_rank] + par_off +
-                                                             ((size_t)src * n_tiles_all + tile_id) * kTileBytes) + frag;
+          // sources are taken a few at a time so that their loads are in flight together; the adds keep rank order
+          constexpr int kSrcBatch = kVec <= 4 ? 4 : 2;
+          for (int s0 = 0; s0 < p.ar_world; s0 += kSrcBatch) {
+            uint4 raw[kSrcBatch][kVec];
 #pragma unroll
-            for (int jv = 0; jv < kVec; ++jv) {
-              const uint4 raw = src == p.ar_rank ? mine[jv] : __ldcg(sp + (size_t)jv * kBlockM);
-              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            for (int b = 0; b < kSrcBatch; ++b) {
+              const int src = s0 + b;
+              if (src >= p.ar_world) break;
+              const uint4* sp = reinterpret_cast<const uint4*>(p.ar_data[p.ar_rank] + par_off +
+                                                               ((size_t)src * n_tiles_all + tile_id) * kTileBytes) + frag;
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float2 f = __bfloat1622float2(h[i]);
-                acc[8 * jv + 2 * i] += f.x;
-                acc[8 * jv + 2 * i + 1] += f.y;
+              for (int jv = 0; jv < kVec; ++jv) raw[b][jv] = src == p.ar_rank ? mine[jv] : __ldcg(sp + (size_t)jv * kBlockM);
+            }
+#pragma unroll
+            for (int b = 0; b < kSrcBatch; ++b) {
+              if (s0 + b >= p.ar_world) break;
+#pragma unroll
+              for (int jv = 0; jv < kVec; ++jv) {
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[b][jv]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float2 f = __bfloat1622float2(h[i]);
+                  acc[8 * jv + 2 * i] += f.x;
+                  acc[8 * jv + 2 * i + 1] += f.y;
+                }
               }
             }
           }
@@ -556,11 +569,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const int gm = m0 + r, gn = n0 + c8 * 8;
             if (gm >= M_rows || gn >= p.N) continue;
             float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int src = 0; src < p.ar_world; ++src) {      // fixed order: identical bits on every rank
-              const uint4 raw = *reinterpret_cast<const uint4*>(
-                  p.ar_data[p.ar_rank] + (size_t)src * p.ar_part_src_stride + (size_t)j * (kBlockM * BLOCK_N * 2) +
-                  ((size_t)r * BLOCK_N + c8 * 8) * 2);
-              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            uint4 raws[8];
+#pragma unroll
+            for (int src = 0; src < 8; ++src)                 // all loads first, then the adds in rank order
+              if (src < p.ar_world)
+                raws[src] = *reinterpret_cast<const uint4*>(
+                    p.ar_data[p.ar_rank] + (size_t)src * p.ar_part_src_stride + (size_t)j * (kBlockM * BLOCK_N * 2) +
+                    ((size_t)r * BLOCK_N + c8 * 8) * 2);
+#pragma unroll
+            for (int src = 0; src < 8; ++src) {               // fixed order: identical bits on every rank
+              if (src >= p.ar_world) break;
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raws[src]);
 #pragma unroll
               for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); sum[2 * i] += f.x; sum[2 * i + 1] += f.y; }
             }
