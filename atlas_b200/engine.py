@@ -66,7 +66,14 @@ class LLMEngine:
         self.state_pool = SlotPool(n_active) if self.hybrid else None
         self.snapshot_base = n_active
         self.radix = RadixCache(self.pool, snapshot_slots=n_snap) if self.cfg.enable_prefix_caching else None
-        self.scheduler = Scheduler(self.cfg, self.pool, self.radix, self.state_pool, self.hybrid)
+        self.host_tier = None
+        if self.cfg.swap_space_gb > 0:
+            from .kv.host_tier import HostKVTier
+            per_block = max(1, model.kv_bytes_per_block(self.cfg.block_size, self.kv_dtype))
+            n_host = int(self.cfg.swap_space_gb * (1 << 30)) // per_block
+            if n_host > 0:
+                self.host_tier = HostKVTier(self.cache, n_host, self.cfg.max_num_seqs if self.hybrid else 0)
+        self.scheduler = Scheduler(self.cfg, self.pool, self.radix, self.state_pool, self.hybrid, host_tier=self.host_tier)
         self.sampler = Sampler(self.mcfg.vocab_size, self.mcfg.eos_ids())
         self.runner = ModelRunner(model, self.cache, self.cfg)
         self.spec = SpecController(self, self.cfg) if (self.cfg.speculative and model.mtp is not None
@@ -180,6 +187,13 @@ class LLMEngine:
             results.append(self._make_output(s, []))
             self._seqs.pop(s.request_id, None)
         sched.finished_queue.clear()
+        # host-tier traffic of this plan: saves first (a released block may already belong to someone else), then restores
+        for dev_blocks, host_blocks, state_slot, host_state in out.swap_out:
+            self.host_tier.copy_out(dev_blocks, host_blocks, state_slot, host_state)
+        for host_blocks, dev_blocks, host_state, state_slot in out.swap_in:
+            self.host_tier.copy_in(host_blocks, dev_blocks, host_state, state_slot)
+            self.host_tier.free(host_blocks)
+            self.host_tier.free_state(host_state)
         if out.empty:
             if ctl is not None:
                 ctl.finish_step(None if follower else _empty_outcome())

@@ -1,0 +1,93 @@
+"""Host-memory tier for the KV cache: a preempted decode keeps its computed KV blocks (and, for hybrid models, its
+recurrent state) in pinned host memory instead of recomputing its whole context on resume.
+
+The scheduler owns the bookkeeping (which sequence holds which host blocks) through the small allocator interface of
+:class:`HostKVTier` (``num_free`` / ``alloc`` / ``free``); the engine performs the copies it lists in
+``SchedulerOutput.swap_out`` / ``swap_in`` on the compute stream before the step's forward pass, swap-outs first, so a
+device block that changes hands inside one step is saved before its new owner writes it, and host blocks are only
+returned to the free list after the copy that reads them has been issued.
+
+Sized by ``--swap-space-gb``.  Reference behaviour replaced: ``crates/spark-runtime/src/kv_host_tier/`` (arena + restore),
+``crates/spark-server/src/scheduler/preempt.rs`` and ``restore_queue.rs`` (swap instead of recompute, parked restores).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+
+class HostKVTier:
+    def __init__(self, cache, num_host_blocks: int, num_state_slots: int = 0):
+        self.cache = cache
+        self.num_blocks = int(num_host_blocks)
+        self._free: List[int] = list(range(self.num_blocks - 1, -1, -1))
+        pin = any(k.is_cuda for k, _ in cache.kv.values())
+        self.k: Dict[int, torch.Tensor] = {}
+        self.v: Dict[int, torch.Tensor] = {}
+        for l, (k, v) in cache.kv.items():
+            self.k[l] = torch.empty((self.num_blocks,) + tuple(k.shape[1:]), dtype=k.dtype, pin_memory=pin)
+            self.v[l] = torch.empty((self.num_blocks,) + tuple(v.shape[1:]), dtype=v.dtype, pin_memory=pin)
+        self.num_state_slots = int(num_state_slots) if cache.states else 0
+        self._free_states: List[int] = list(range(self.num_state_slots - 1, -1, -1))
+        self.states: Dict[int, Dict[str, torch.Tensor]] = {}
+        for l, st in cache.states.items():
+            self.states[l] = {name: torch.empty((self.num_state_slots,) + tuple(t.shape[1:]), dtype=t.dtype, pin_memory=pin)
+                              for name, t in st.items() if name in ("conv", "h")}
+        self.blocks_out = 0
+        self.blocks_in = 0
+
+    # ------------------------------------------------------------------ allocator (scheduler side)
+    @property
+    def num_free(self) -> int:
+        return len(self._free)
+
+    @property
+    def num_free_states(self) -> int:
+        return len(self._free_states)
+
+    def alloc(self, n: int) -> List[int]:
+        assert n <= len(self._free), "host tier exhausted"
+        return [self._free.pop() for _ in range(n)]
+
+    def free(self, ids: List[int]) -> None:
+        self._free.extend(ids)
+        assert len(self._free) <= self.num_blocks, "host block freed twice"
+
+    def alloc_state(self) -> int:
+        return self._free_states.pop()
+
+    def free_state(self, slot: Optional[int]) -> None:
+        if slot is not None:
+            self._free_states.append(slot)
+
+    # ------------------------------------------------------------------ copies (engine side)
+    def copy_out(self, dev_blocks: List[int], host_blocks: List[int], state_slot: Optional[int] = None,
+                 host_state: Optional[int] = None) -> None:
+        assert len(dev_blocks) == len(host_blocks)
+        if dev_blocks:
+            hb = torch.tensor(host_blocks, dtype=torch.int64)
+            for l, (k, v) in self.cache.kv.items():
+                db = torch.tensor(dev_blocks, dtype=torch.int64, device=k.device)
+                self.k[l][hb] = k.index_select(0, db).to("cpu").view(self.k[l].dtype)
+                self.v[l][hb] = v.index_select(0, db).to("cpu").view(self.v[l].dtype)
+            self.blocks_out += len(dev_blocks)
+        if host_state is not None and state_slot is not None:
+            for l, st in self.cache.states.items():
+                for name, host in self.states[l].items():
+                    host[host_state].copy_(st[name][state_slot])
+
+    def copy_in(self, host_blocks: List[int], dev_blocks: List[int], host_state: Optional[int] = None,
+                state_slot: Optional[int] = None) -> None:
+        assert len(dev_blocks) == len(host_blocks)
+        if dev_blocks:
+            hb = torch.tensor(host_blocks, dtype=torch.int64)
+            for l, (k, v) in self.cache.kv.items():
+                db = torch.tensor(dev_blocks, dtype=torch.int64, device=k.device)
+                k.index_copy_(0, db, self.k[l][hb].to(k.device, non_blocking=True))
+                v.index_copy_(0, db, self.v[l][hb].to(v.device, non_blocking=True))
+            self.blocks_in += len(dev_blocks)
+        if host_state is not None and state_slot is not None:
+            for l, st in self.cache.states.items():
+                for name, host in self.states[l].items():
+                    st[name][state_slot].copy_(host[host_state], non_blocking=True)

@@ -30,8 +30,12 @@ from .sequence import FinishReason, ScheduledSeq, SchedulerOutput, SeqStatus, Se
 class Scheduler:
     def __init__(self, cfg: EngineConfig, pool: BlockPool, radix: Optional[RadixCache] = None,
                  state_pool: Optional[SlotPool] = None, hybrid: bool = False,
-                 policy: Optional[SchedulingPolicy] = None):
+                 policy: Optional[SchedulingPolicy] = None, host_tier=None):
         self.cfg, self.pool, self.radix, self.state_pool, self.hybrid = cfg, pool, radix, state_pool, hybrid
+        self.host_tier = host_tier                    # kv.host_tier.HostKVTier or None: swap instead of recompute
+        self.swapped: Deque[Sequence] = deque()
+        self._resumed_now: List[Sequence] = []        # resumed in the current schedule() call: not victims yet
+        self.num_swaps = 0
         self.bs = pool.block_size
         self.policy = policy or make_policy(cfg.scheduling_policy, cfg.tbt_deadline_ms)
         self.waiting: Deque[Sequence] = deque()
@@ -48,7 +52,7 @@ class Scheduler:
         self.waiting.append(seq)
 
     def abort(self, request_id: str, reason: FinishReason = FinishReason.ABORT) -> Optional[Sequence]:
-        for q in (self.waiting, self.prefilling, self.running):
+        for q in (self.waiting, self.prefilling, self.running, self.swapped):
             for s in list(q):
                 if s.request_id == request_id:
                     q.remove(s)
@@ -59,7 +63,7 @@ class Scheduler:
 
     @property
     def num_unfinished(self) -> int:
-        return len(self.waiting) + len(self.prefilling) + len(self.running)
+        return len(self.waiting) + len(self.prefilling) + len(self.running) + len(self.swapped)
 
     def has_work(self) -> bool:
         return self.num_unfinished > 0
@@ -97,8 +101,64 @@ class Scheduler:
             self.state_pool.free(seq.state_slot)
         seq.state_slot, seq.has_state = None, False
         seq.drafts = []
+        if seq.host_blocks or seq.host_state is not None:
+            self.host_tier.free(seq.host_blocks)
+            self.host_tier.free_state(seq.host_state)
+            seq.host_blocks, seq.host_state = [], None
+
+    def _try_swap_out(self, victim: Sequence, out: SchedulerOutput) -> bool:
+        """Park a decoding sequence's computed KV (and recurrent state) in the host tier.  Only sequences whose
+        context is fully computed qualify; the engine copies before anything else touches the released blocks."""
+        ht = self.host_tier
+        if ht is None or victim not in self.running or victim.num_computed <= 0 or victim in self._resumed_now:
+            return False
+        n_used = min(self.pool.blocks_for_tokens(victim.num_computed), len(victim.blocks))
+        need_state = self.hybrid and victim.state_slot is not None
+        if ht.num_free < n_used or (need_state and ht.num_free_states == 0):
+            return False
+        host_blocks = ht.alloc(n_used)
+        host_state = ht.alloc_state() if need_state else None
+        out.swap_out.append((list(victim.blocks[:n_used]), list(host_blocks), victim.state_slot, host_state))
+        self.running.remove(victim)
+        keep_computed, had_state = victim.num_computed, victim.has_state
+        self._release(victim, publish=True)
+        victim.host_blocks, victim.host_state = host_blocks, host_state
+        victim.num_computed, victim.has_state = keep_computed, had_state
+        victim.status = SeqStatus.SWAPPED
+        victim.num_preemptions += 1
+        self.num_swaps += 1
+        self.swapped.append(victim)
+        return True
+
+    def _resume_swapped(self, out: SchedulerOutput) -> None:
+        """Bring parked sequences back (oldest first) while blocks for their context plus the admission headroom are
+        available; they rejoin the decode set of this very step."""
+        while self.swapped:
+            seq = self.swapped[0]
+            if self.num_unfinished - len(self.waiting) - len(self.swapped) >= self.cfg.max_num_seqs:
+                return
+            if self.hybrid and self.state_pool is not None and seq.host_state is not None and self.state_pool.num_free == 0:
+                return
+            need = self._admission_blocks(seq, 0)
+            avail = self.pool.num_free + (self.radix.evictable_blocks() if self.radix is not None else 0)
+            n_used = len(seq.host_blocks)
+            if need > avail or not self._reclaim(n_used):
+                return
+            self.swapped.popleft()
+            seq.blocks = self.pool.alloc(n_used)
+            slot = None
+            if seq.host_state is not None:
+                slot = self.state_pool.alloc()
+                seq.state_slot = slot
+            out.swap_in.append((list(seq.host_blocks), list(seq.blocks), seq.host_state, slot))
+            seq.host_blocks, seq.host_state = [], None       # the engine returns them to the tier after the copy
+            seq.status = SeqStatus.RUNNING
+            self.running.append(seq)
+            self._resumed_now.append(seq)
 
     def _preempt(self, victim: Sequence, out: SchedulerOutput) -> None:
+        if self._try_swap_out(victim, out):
+            return
         (self.running if victim in self.running else self.prefilling).remove(victim)
         # hybrid sequences cannot resume from KV alone; their published blocks only help at snapshot depths
         self._release(victim, publish=True)
@@ -159,6 +219,11 @@ class Scheduler:
             self._expire_deadlines(now)
         if self._last_decode_time is None:
             self._last_decode_time = now
+
+        # 0. sequences parked in the host tier come back before anything new is admitted
+        self._resumed_now = []
+        if self.swapped:
+            self._resume_swapped(out)
 
         # 1. decodes (+ draft rows)
         decode_items: List[ScheduledSeq] = []
@@ -221,7 +286,7 @@ class Scheduler:
     def _pick_victim(self, exclude: Sequence) -> Optional[Sequence]:
         for pool in (self.prefilling, self.running):
             for s in reversed(pool):
-                if s is not exclude:
+                if s is not exclude and s not in self._resumed_now:
                     return s
         return None
 
@@ -268,7 +333,7 @@ class Scheduler:
         return self.finished_queue[n0:]
 
     def _expire_deadlines(self, now: float) -> None:
-        for q in (self.waiting, self.prefilling, self.running):
+        for q in (self.waiting, self.prefilling, self.running, self.swapped):
             for s in list(q):
                 if s.deadline is not None and now > s.deadline:
                     q.remove(s)
@@ -310,5 +375,5 @@ class Scheduler:
     def snapshot(self) -> Dict[str, int]:
         return {"waiting": len(self.waiting), "prefilling": len(self.prefilling), "running": len(self.running),
                 "kv_free_blocks": self.pool.num_free, "kv_total_blocks": self.pool.num_blocks,
-                "preemptions": self.num_preemptions,
+                "preemptions": self.num_preemptions, "swapped": len(self.swapped), "swaps": self.num_swaps,
                 "state_slots_free": self.state_pool.num_free if self.state_pool else 0}

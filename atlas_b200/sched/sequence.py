@@ -14,6 +14,7 @@ class SeqStatus(enum.Enum):
     PREFILL = "prefill"          # admitted, prompt (or resume) chunks still to compute
     RUNNING = "running"          # decoding
     PREEMPTED = "preempted"      # blocks released, will be recomputed on resume
+    SWAPPED = "swapped"          # computed KV (and recurrent state) parked in the host tier, resumes without recompute
     FINISHED = "finished"
 
 
@@ -55,6 +56,8 @@ class Sequence:
     finish_time: Optional[float] = None
     first_scheduled_time: Optional[float] = None
     num_preemptions: int = 0
+    host_blocks: List[int] = field(default_factory=list)  # host-tier blocks while SWAPPED
+    host_state: Optional[int] = None
     logprobs: List[Any] = field(default_factory=list)
     spec_accepted: int = 0
     spec_proposed: int = 0
@@ -113,6 +116,8 @@ class SchedulerOutput:
     items: List[ScheduledSeq] = field(default_factory=list)
     preempted: List[Sequence] = field(default_factory=list)
     restored_snapshots: List[tuple] = field(default_factory=list)   # (snapshot_slot, seq_slot)
+    swap_out: List[tuple] = field(default_factory=list)             # (device blocks, host blocks, state slot, host state)
+    swap_in: List[tuple] = field(default_factory=list)              # (host blocks, device blocks, host state, state slot)
     snapshot_requests: List[tuple] = field(default_factory=list)    # (item index, rows from chunk start, snapshot slot, node)
 
     @property

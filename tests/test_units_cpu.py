@@ -326,3 +326,28 @@ def test_fault_latch_classification():
     ok = FaultLatch(probe=lambda: True)
     assert ok.observe_exception(RuntimeError("CUDA error: out of memory")) is Fatality.REQUEST_SCOPED and not ok.tripped
     assert ok.observe_status_word(0x1234) is Fatality.REQUEST_SCOPED and ok.request_scoped_failures == 2
+
+
+@pytest.mark.parametrize("hybrid", [False, True])
+def test_host_tier_swaps_instead_of_recomputing(hybrid):
+    """With swap space, a preempted decode parks its KV (and recurrent state) in host memory and resumes without
+    recomputing its context: same tokens as an uncontended run, fewer prefill tokens than the recompute path."""
+    from atlas_b200.config import tiny_hybrid
+    mk = tiny_hybrid if hybrid else tiny_dense
+    prompts = _prompts(4, 40)
+    sp = SamplingParams(max_tokens=40, ignore_eos=True)
+
+    def eng(**kw):
+        return LLMEngine(build_model(mk()).init_random(0), EngineConfig(block_size=16, max_num_seqs=8, max_prefill_tokens=64, **kw))
+
+    want = [o.output_tokens for o in eng(num_kv_blocks=64).generate(prompts, sp)]
+    recompute = eng(num_kv_blocks=14)
+    assert [o.output_tokens for o in recompute.generate(prompts, sp)] == want
+    swap = eng(num_kv_blocks=14, swap_space_gb=0.01)
+    assert swap.host_tier is not None and swap.host_tier.num_blocks >= 8
+    got = [o.output_tokens for o in swap.generate(prompts, sp)]
+    assert got == want
+    assert swap.scheduler.num_swaps > 0 and swap.host_tier.blocks_in == swap.host_tier.blocks_out > 0
+    assert swap.stats.prefill_tokens < recompute.stats.prefill_tokens
+    assert swap.host_tier.num_free == swap.host_tier.num_blocks and not swap.scheduler.swapped
+    swap.pool.check_invariants()
