@@ -17,6 +17,11 @@ from typing import Dict, List, Optional
 import torch
 
 
+def _raw(t: torch.Tensor) -> torch.Tensor:
+    """8-bit float tensors are moved as bytes (indexing kernels do not exist for every float8 type)."""
+    return t.view(torch.uint8) if t.element_size() == 1 else t
+
+
 class HostKVTier:
     def __init__(self, cache, num_host_blocks: int, num_state_slots: int = 0):
         self.cache = cache
@@ -69,8 +74,8 @@ class HostKVTier:
             hb = torch.tensor(host_blocks, dtype=torch.int64)
             for l, (k, v) in self.cache.kv.items():
                 db = torch.tensor(dev_blocks, dtype=torch.int64, device=k.device)
-                self.k[l][hb] = k.index_select(0, db).to("cpu").view(self.k[l].dtype)
-                self.v[l][hb] = v.index_select(0, db).to("cpu").view(self.v[l].dtype)
+                _raw(self.k[l])[hb] = _raw(k).index_select(0, db).to("cpu")
+                _raw(self.v[l])[hb] = _raw(v).index_select(0, db).to("cpu")
             self.blocks_out += len(dev_blocks)
         if host_state is not None and state_slot is not None:
             for l, st in self.cache.states.items():
@@ -84,8 +89,8 @@ class HostKVTier:
             hb = torch.tensor(host_blocks, dtype=torch.int64)
             for l, (k, v) in self.cache.kv.items():
                 db = torch.tensor(dev_blocks, dtype=torch.int64, device=k.device)
-                k.index_copy_(0, db, self.k[l][hb].to(k.device, non_blocking=True))
-                v.index_copy_(0, db, self.v[l][hb].to(v.device, non_blocking=True))
+                _raw(k).index_copy_(0, db, _raw(self.k[l])[hb].to(k.device))
+                _raw(v).index_copy_(0, db, _raw(self.v[l])[hb].to(v.device))
             self.blocks_in += len(dev_blocks)
         if host_state is not None and state_slot is not None:
             for l, st in self.cache.states.items():
