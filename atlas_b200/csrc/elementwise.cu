@@ -205,6 +205,7 @@ struct RopeKvParams {
   void* k_cache; void* v_cache;
   const int* slot_mapping;
   int T, Hq, Hkv, D, rotary_dim, block_size, kv_fp8, plus_one;
+  int v_separate;          // V rows are written by v_write_pages_kernel (prefill-size batches), not here
   float eps, inv_k_scale, inv_v_scale;
 };
 
@@ -215,7 +216,7 @@ rope_kv_write_kernel(const RopeKvParams p) {
   chain_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long unit = (long long)blockIdx.x * 4 + warp;
-  const int heads = p.Hq + 2 * p.Hkv;
+  const int heads = p.Hq + (p.v_separate ? 1 : 2) * p.Hkv;
   if (unit >= (long long)p.T * heads) return;
   const int t = (int)(unit / heads);
   const int h = (int)(unit % heads);
@@ -290,6 +291,61 @@ rope_kv_write_kernel(const RopeKvParams p) {
         vc[(long long)(e + 1) * p.block_size] = __float2bfloat16_rn(o[1]);
       }
     }
+  }
+}
+
+// V rows of a prefill-size batch -> the transposed FP8 page layout [blk][head][d][tok16].  One warp per (16 consecutive
+// batch rows, kv head).  When the 16 rows fill one page in order (the common case inside a prompt chunk) every lane
+// gathers 16 tokens for its dims and writes whole 16-byte page rows; otherwise each row falls back to byte stores.
+__global__ void __launch_bounds__(128)
+v_write_pages_kernel(const RopeKvParams p) {
+  chain_trigger();
+  chain_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * 4 + warp;
+  const int groups = (p.T + 15) / 16;
+  if (unit >= (long long)groups * p.Hkv) return;
+  const int g = (int)(unit / p.Hkv), hh = (int)(unit % p.Hkv);
+  const int t0 = g * 16, D = p.D;
+  const int my_slot = (lane < 16 && t0 + lane < p.T) ? p.slot_mapping[t0 + lane] : -2;
+  const int slot0 = __shfl_sync(0xffffffffu, my_slot, 0);
+  const bool in_order = lane >= 16 || (slot0 >= 0 && my_slot == slot0 + lane);
+  const bool fast = __all_sync(0xffffffffu, in_order) && (slot0 % 16) == 0 && t0 + 16 <= p.T;
+  uint8_t* vc_all = reinterpret_cast<uint8_t*>(p.v_cache);
+  if (fast) {
+    uint8_t* page = vc_all + ((long long)(slot0 / 16) * p.Hkv + hh) * (long long)D * 16;
+    for (int d0 = lane * 4; d0 < D; d0 += 128) {
+      uint32_t col[4][4];                       // [dim][token quad] packed fp8
+#pragma unroll
+      for (int tq = 0; tq < 4; ++tq) {
+        float vals[4][4];                       // [token in quad][dim]
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(p.v + (long long)(t0 + tq * 4 + i) * p.ldv + hh * D + d0);
+          const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+          const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+          vals[i][0] = a.x; vals[i][1] = a.y; vals[i][2] = b.x; vals[i][3] = b.y;
+        }
+#pragma unroll
+        for (int d = 0; d < 4; ++d) {
+          uint32_t w = 0;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) w |= (uint32_t)f32_to_fp8_e4m3(vals[i][d] * p.inv_v_scale) << (8 * i);
+          col[d][tq] = w;
+        }
+      }
+#pragma unroll
+      for (int d = 0; d < 4; ++d)
+        *reinterpret_cast<uint4*>(page + (long long)(d0 + d) * 16) = make_uint4(col[d][0], col[d][1], col[d][2], col[d][3]);
+    }
+    return;
+  }
+  for (int i = 0; i < 16 && t0 + i < p.T; ++i) {
+    const int slot = __shfl_sync(0xffffffffu, my_slot, i);
+    if (slot < 0) continue;
+    uint8_t* vc = vc_all + ((long long)(slot / 16) * p.Hkv + hh) * (long long)D * 16 + (slot % 16);
+    const __nv_bfloat16* src = p.v + (long long)(t0 + i) * p.ldv + hh * D;
+    for (int e = lane; e < D; e += 32) vc[(long long)e * 16] = f32_to_fp8_e4m3(__bfloat162float(src[e]) * p.inv_v_scale);
   }
 }
 
@@ -384,9 +440,9 @@ extern "C" int atlas_rmsnorm(const void* x, long long ldx, const void* residual,
   auto RO = reinterpret_cast<__nv_bfloat16*>(res_out);
   auto Y = reinterpret_cast<__nv_bfloat16*>(y);
   auto Qp = reinterpret_cast<uint8_t*>(q);
-  if (iters == 1) launch_chain(rmsnorm_kernel<1>, dim3(T), dim3(threads), 0, st, X, ldx, R, ldr, W, RO, ldro, Y, ldy, Qp, ldq, scale, scale_ld, H, eps, plus_one);
-  else if (iters == 2) launch_chain(rmsnorm_kernel<2>, dim3(T), dim3(threads), 0, st, X, ldx, R, ldr, W, RO, ldro, Y, ldy, Qp, ldq, scale, scale_ld, H, eps, plus_one);
-  else if (iters == 4) launch_chain(rmsnorm_kernel<4>, dim3(T), dim3(threads), 0, st, X, ldx, R, ldr, W, RO, ldro, Y, ldy, Qp, ldq, scale, scale_ld, H, eps, plus_one);
+  if (iters == 1) launch_chain_if(T <= 256, rmsnorm_kernel<1>, dim3(T), dim3(threads), 0, st, X, ldx, R, ldr, W, RO, ldro, Y, ldy, Qp, ldq, scale, scale_ld, H, eps, plus_one);
+  else if (iters == 2) launch_chain_if(T <= 256, rmsnorm_kernel<2>, dim3(T), dim3(threads), 0, st, X, ldx, R, ldr, W, RO, ldro, Y, ldy, Qp, ldq, scale, scale_ld, H, eps, plus_one);
+  else if (iters == 4) launch_chain_if(T <= 256, rmsnorm_kernel<4>, dim3(T), dim3(threads), 0, st, X, ldx, R, ldr, W, RO, ldro, Y, ldy, Qp, ldq, scale, scale_ld, H, eps, plus_one);
   else return -3;
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
 }
@@ -396,7 +452,7 @@ extern "C" int atlas_silu_mul(const void* gu, long long ld, int T, int I, void* 
   if (T <= 0) return 0;
   if (I % 8 || (q && I % 128)) return -1;
   dim3 grid(T, (I / 8 + 255) / 256);
-  launch_chain(silu_mul_kernel, grid, dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+  launch_chain_if(T <= 256, silu_mul_kernel, grid, dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
       reinterpret_cast<const __nv_bfloat16*>(gu), ld, I, reinterpret_cast<__nv_bfloat16*>(y), ldy,
       reinterpret_cast<uint8_t*>(q), ldq, scale, scale_ld, live_tiles);
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
@@ -407,7 +463,7 @@ extern "C" int atlas_quant_fp8(const void* x, long long ld, int T, int K, void* 
   if (T <= 0) return 0;
   if (K % 128) return -1;
   dim3 grid(T, (K / 8 + 255) / 256);
-  launch_chain(quant_fp8_kernel, grid, dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+  launch_chain_if(T <= 256, quant_fp8_kernel, grid, dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
       reinterpret_cast<const __nv_bfloat16*>(x), ld, K, reinterpret_cast<uint8_t*>(q), ldq, scale, scale_ld);
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
 }
@@ -429,9 +485,17 @@ extern "C" int atlas_rope_kv_write(void* q, long long ldq, const void* k, long l
   p.k_cache = k_cache; p.v_cache = v_cache; p.slot_mapping = slot_mapping;
   p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.rotary_dim = rotary_dim; p.block_size = block_size;
   p.kv_fp8 = kv_fp8; p.plus_one = plus_one; p.eps = eps; p.inv_k_scale = 1.f / k_scale; p.inv_v_scale = 1.f / v_scale;
-  const long long units = (long long)T * (Hq + 2 * Hkv);
+  // prefill-size batches with 16-token FP8 pages: V goes through the page-row writer (16-byte stores)
+  p.v_separate = (T >= 256 && kv_fp8 && block_size == 16 && D % 4 == 0 && (ldv % 4) == 0 &&
+                  (reinterpret_cast<uintptr_t>(v) & 7) == 0) ? 1 : 0;
+  const long long units = (long long)T * (Hq + (p.v_separate ? 1 : 2) * Hkv);
   const int grid = (int)((units + 3) / 4);
-  launch_chain(rope_kv_write_kernel, dim3(grid), dim3(128), 4 * D * sizeof(float), reinterpret_cast<cudaStream_t>(stream), p);
+  launch_chain_if(T <= 256, rope_kv_write_kernel, dim3(grid), dim3(128), 4 * D * sizeof(float), reinterpret_cast<cudaStream_t>(stream), p);
+  if (cudaGetLastError() != cudaSuccess) return -20;
+  if (p.v_separate) {
+    const long long vunits = (long long)((T + 15) / 16) * Hkv;
+    launch_chain_if(false, v_write_pages_kernel, dim3((unsigned)((vunits + 3) / 4)), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream), p);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
 }
 

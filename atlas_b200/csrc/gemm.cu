@@ -697,7 +697,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
     if (e != cudaSuccess) return -20;
     attr_done = true;
   }
-  return launch_chain(kern, dim3(grid), dim3(gemm_threads(BLOCK_N, FP8)), (size_t)Cfg::kSmemBytes, st, ta, tb, p) == cudaSuccess ? 0 : -21;
+  return launch_chain_if(p.m_tiles <= 2 && p.tile_expert == nullptr, kern, dim3(grid), dim3(gemm_threads(BLOCK_N, FP8)),
+                         (size_t)Cfg::kSmemBytes, st, ta, tb, p) == cudaSuccess ? 0 : -21;
 }
 
 // k-slices of weights requested into L2 ahead of the tile ring for decode-size GEMMs (ATLAS_GEMM_PREFETCH, 0 = off)

@@ -292,7 +292,12 @@ def qk_norm_rope_kv_write(q, k, v, positions, rope_cache, rotary_dim, k_cache, v
     return q
 
 
+_FORCE_DECODE_SPLITS = int(os.environ.get("ATLAS_DECODE_SPLITS", "0"))
+
+
 def decode_splits(B: int, hkv: int, max_seq_len: int, sms: int) -> int:
+    if _FORCE_DECODE_SPLITS:
+        return _FORCE_DECODE_SPLITS
     ctas = B * hkv
     if ctas >= 2 * sms:
         return 1
