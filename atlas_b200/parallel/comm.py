@@ -87,6 +87,10 @@ class TorchDistBackend(CommBackend):
         self._run("all_reduce", lambda: self.dist.all_reduce(t, group=self.group))
         return t
 
+    def all_reduce_async(self, t):
+        """Starts the reduction and returns a handle whose ``wait()`` orders the current stream after it."""
+        return self._run("all_reduce", lambda: self.dist.all_reduce(t, group=self.group, async_op=True))
+
     def all_gather(self, t, dim=0):
         def go():
             outs = [torch.empty_like(t) for _ in range(self.world_size)]

@@ -230,6 +230,12 @@ class SymmBackend(CommBackend):
         return _device_view(self._fdata + off.value, (M, N), torch.bfloat16, self.device)
 
     # everything else: the bootstrap backend
+    def all_reduce_async(self, t):
+        """Large messages only (the caller overlaps them with compute): NCCL on its own stream."""
+        self._guard()
+        self.calls["fallback"] += 1
+        return self.base.all_reduce_async(t)
+
     def all_gather(self, t, dim=0): return self.base.all_gather(t, dim)
     def reduce_scatter(self, t, dim=0): return self.base.reduce_scatter(t, dim)
     def broadcast(self, t, src=0): return self.base.broadcast(t, src)
