@@ -245,6 +245,48 @@ def run(model: str = "llama3-8b", decode_batch: int = 128, ctx: int = 1152, chun
                                                     None, None, 1e-6, False))
         add(f"rope_kv_write T={n_seq * L}", ms, bytes_=n_seq * L * (Hq + 2 * Hkv) * D * 2 * 2)
 
+    if only and "gdn" in only:
+        # Gated-DeltaNet prefill (Qwen3-Next geometry): conv + chunked scan + state write, one layer
+        from atlas_b200.layers import ParallelCtx
+        from atlas_b200.layers.gdn import GatedDeltaNet
+        from atlas_b200.ops import cuda_gdn
+        gcfg = PRESETS["qwen3-next-80b"]()
+        layer = GatedDeltaNet(gcfg, 0, ParallelCtx(), "dense")
+        layer.conv_w = (torch.randn(layer.conv_dim, layer.W, device=dev) * 0.2).bfloat16()
+        layer.dt_bias = torch.rand(layer.hv, device=dev)
+        layer.A_log = torch.log(torch.rand(layer.hv, device=dev) * 15 + 1)
+        T.use_graph = False
+        for n_seq, L in ((8, 1024), (1, chunk)):
+            st_ = layer.alloc_state(n_seq + 1, dev, torch.bfloat16)
+            mixed = torch.randn(n_seq * L, layer.conv_dim, device=dev).bfloat16()
+            ga = torch.randn(n_seq * L, layer.hv, device=dev).bfloat16()
+            gb = torch.randn(n_seq * L, layer.hv, device=dev).bfloat16()
+            fbg = ForwardBatch.build([[0] * L] * n_seq, [0] * n_seq, [list(range((L + 15) // 16))] * n_seq, 16, device=dev,
+                                     state_slots=list(range(n_seq)), has_state=[False] * n_seq)
+            for chunked in (True, False):
+                cuda_gdn.USE_CHUNKED = chunked
+                ms = T.time(lambda: K.gdn_forward(layer, mixed, ga, gb, fbg, st_, commit=True), iters=3)
+                add(f"gdn_prefill Hk={layer.hk} Hv={layer.hv} D=128 seqs={n_seq} L={L} {'chunked' if chunked else 'sequential'}", ms,
+                    bytes_=n_seq * L * (layer.conv_dim * 2 * 2 + layer.hv * 128 * 2))
+        cuda_gdn.USE_CHUNKED = True
+        T.use_graph = True
+
+    if only and "moe" in only:
+        # one MoE FFN (Qwen3-30B-A3B geometry, NVFP4 experts): route + align + gather + grouped GEMMs + combine
+        from atlas_b200.layers.moe import ExpertWeights
+        E, Hm, Im, topk = 128, 2048, 768, 8
+        exw = ExpertWeights.from_dense((torch.randn(E, 2 * Im, Hm, device=dev) * 0.05).bfloat16(),
+                                       (torch.randn(E, Hm, Im, device=dev) * 0.05).bfloat16(), "nvfp4")
+        T.use_graph = False
+        for M in (decode_batch, chunk):
+            xm = torch.randn(M, Hm, device=dev).bfloat16()
+            tw, ti = ref.moe_route(torch.randn(M, E, device=dev), topk, True)
+            tw, ti = tw.contiguous(), ti.contiguous()
+            ms = T.time(lambda: K.moe_forward(xm, tw, ti, exw, 0, None, "allreduce"), iters=3)
+            wbytes = E * 3 * Im * Hm * 0.5625
+            add(f"moe_ffn nvfp4 T={M} E={E} top{topk} H={Hm} I={Im}", ms, bytes_=wbytes, flops=2 * M * topk * 3 * Im * Hm)
+        T.use_graph = True
+
     if not only or "sample" in only:
         lg = torch.randn(decode_batch, cfg.vocab_size, device=dev).bfloat16()
         ms = T.time(lambda: K.argmax(lg))
