@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 import torch
@@ -202,6 +203,21 @@ def _ones(n: int, dev) -> torch.Tensor:
     return t
 
 
+_SMALL_MOE = os.environ.get("ATLAS_MOE_SMALL", "1") not in ("0", "false")
+SMALL_MOE_ROWS_PER_EXPERT = 16
+
+
+def _small_moe_ok(pairs: int, E: int, H: int, I: int) -> bool:
+    return (_SMALL_MOE and pairs <= SMALL_MOE_ROWS_PER_EXPERT * E and H % 256 == 0 and I % 256 == 0)
+
+
+def _bind_small(lib) -> None:
+    if not getattr(lib, "_small_moe_bound", False):
+        vp, i32, ll = C.c_void_p, C.c_int, C.c_longlong
+        lib.atlas_moe_small_w4.argtypes = [i32, vp, ll, vp, vp, vp, i32, vp, vp, vp, vp, ll, i32, i32, vp]
+        lib._small_moe_bound = True
+
+
 def _moe_local(x, topk_w, topk_ids, experts, e_lo, addend: Optional[torch.Tensor] = None):
     """Local experts only: align -> gather (+quant) -> grouped GEMM -> SiLU*mul -> grouped GEMM -> weighted combine."""
     T, H = x.shape
@@ -224,6 +240,22 @@ def _moe_local(x, topk_w, topk_ids, experts, e_lo, addend: Optional[torch.Tensor
     def bn_for(n):
         return 128 if n % 128 == 0 else 64
 
+    if kind == 2 and _small_moe_ok(T * k, E, H, I):
+        # decode-size batch on NVFP4 experts: a few rows per expert, so stream the weights through the register-level
+        # dequant kernel (rows gathered by token inside it, SiLU fused) instead of 128-row tcgen05 tiles
+        _bind_small(lib)
+        act = torch.empty(max_rows, I, dtype=torch.bfloat16, device=dev)
+        K._check(lib.atlas_moe_small_w4(1, x.data_ptr(), x.stride(0), row_token.data_ptr(), tile_expert.data_ptr(),
+                                        num_tiles.data_ptr(), max_rows // 128, w13.data_ptr(), s13[0].data_ptr(),
+                                        s13[1].data_ptr(), act.data_ptr(), I, H, 2 * I, st), "moe_small_gate_up")
+        y = torch.empty(max_rows, H, dtype=torch.bfloat16, device=dev)
+        K._check(lib.atlas_moe_small_w4(0, act.data_ptr(), I, row_token.data_ptr(), tile_expert.data_ptr(),
+                                        num_tiles.data_ptr(), max_rows // 128, w2.data_ptr(), s2[0].data_ptr(),
+                                        s2[1].data_ptr(), y.data_ptr(), H, I, H, st), "moe_small_down")
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        K._check(lib.atlas_moe_combine(y.data_ptr(), H, slot_of.data_ptr(), topk_w.data_ptr(), T, k, H, K._ptr(addend),
+                                       addend.stride(0) if addend is not None else 0, out.data_ptr(), H, st), "moe_combine")
+        return out
     if kind == 1:
         xq = torch.empty(max_rows, H, dtype=FP8, device=dev)
         xs = torch.empty(H // 128, max_rows, dtype=torch.float32, device=dev)

@@ -63,6 +63,39 @@ def test_moe_forward(K, kind, T):
     assert _rel_rms(out_l, want_l) < (2e-2 if kind == "dense" else 6e-2)
 
 
+@pytest.mark.parametrize("T,hot", [(3, False), (40, False), (40, True)])
+def test_moe_small_batch_nvfp4_kernel(K, T, hot):
+    """Decode-size NVFP4 MoE (register-level dequant, tokens on the MMA N dimension) against the fp32 restatement and
+    the grouped tcgen05 path; ``hot`` sends every token to expert 0 as well, so one expert needs two 32-token passes."""
+    from atlas_b200.ops import cuda_ext
+    torch.manual_seed(2)
+    E, H, I, k = 16, 512, 256, 4
+    w13 = (torch.randn(E, 2 * I, H, device=DEV) * 0.05).bfloat16()
+    w2 = (torch.randn(E, H, I, device=DEV) * 0.05).bfloat16()
+    ex = ExpertWeights.from_dense(w13, w2, "nvfp4")
+    x = torch.randn(T, H, device=DEV).bfloat16()
+    tw, ti = ref.moe_route(torch.randn(T, E, device=DEV), k, True)
+    tw, ti = tw.contiguous(), ti.contiguous()
+    if hot:
+        ti[:, 0] = 0
+        for r in range(T):                       # keep the k experts of a token distinct
+            others = [e for e in range(1, E)]
+            ti[r, 1:] = torch.tensor(others[r % 8:r % 8 + k - 1], device=DEV, dtype=ti.dtype)
+    assert cuda_ext._small_moe_ok(T * k, E, H, I)
+    out = K.moe_forward(x, tw, ti, ex, 0, None, "auto")
+    cuda_ext._SMALL_MOE = False
+    try:
+        grouped = K.moe_forward(x, tw, ti, ex, 0, None, "auto")
+    finally:
+        cuda_ext._SMALL_MOE = True
+    d13, d2 = ex.dequantized()
+    want = ref.moe_experts(x, d13, d2, tw, ti, 0)
+    torch.cuda.synchronize()
+    assert K.check_status() == 0
+    assert _rel_rms(out, want) < 2e-2, _rel_rms(out, want)
+    assert _rel_rms(out, grouped) < 2e-2, _rel_rms(out, grouped)
+
+
 def _hybrid_cfg(quant="none"):
     return ModelConfig(model_type="qwen3_next", family="hybrid", vocab_size=2048, hidden_size=512, intermediate_size=1024,
                        num_hidden_layers=4, num_attention_heads=8, num_key_value_heads=2, head_dim=128, rope_theta=1e6,
