@@ -294,6 +294,90 @@ rope_kv_write_kernel(const RopeKvParams p) {
   }
 }
 
+// Same contract as rope_kv_write_kernel for head_dim = rotary_dim = 128: a lane owns four consecutive dims, the rotation
+// partner (d +- 64) sits in lane ^ 16, so the whole unit stays in registers (one 8-byte load and store per lane, no
+// shared memory).
+__global__ void __launch_bounds__(128)
+rope_kv_write_d128_kernel(const RopeKvParams p) {
+  chain_trigger();
+  chain_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * 4 + warp;
+  const int heads = p.Hq + (p.v_separate ? 1 : 2) * p.Hkv;
+  if (unit >= (long long)p.T * heads) return;
+  const int t = (int)(unit / heads);
+  const int h = (int)(unit % heads);
+  constexpr int D = 128;
+  const bool is_q = h < p.Hq;
+  const bool is_k = !is_q && h < p.Hq + p.Hkv;
+  const int hh = is_q ? h : (is_k ? h - p.Hq : h - p.Hq - p.Hkv);
+  const __nv_bfloat16* src = is_q ? p.q + t * p.ldq + hh * D : (is_k ? p.k + t * p.ldk + hh * D : p.v + t * p.ldv + hh * D);
+  const int slot = p.slot_mapping[t];
+  if (!is_q && slot < 0) return;
+  const int d0 = lane * 4;
+  float v[4];
+  {
+    const uint2 raw = *reinterpret_cast<const uint2*>(src + d0);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+  }
+  const __nv_bfloat16* nw = is_q ? p.q_norm_w : (is_k ? p.k_norm_w : nullptr);
+  if (nw) {
+    const float ss = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
+    const float rstd = rsqrtf(ss / (float)D + p.eps);
+    const uint2 wr = *reinterpret_cast<const uint2*>(nw + d0);
+    const float2 wa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wr.x));
+    const float2 wb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wr.y));
+    const float w4[4] = {wa.x, wa.y, wb.x, wb.y};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)      // round like the unfused op chain would (norm output is bf16)
+      v[i] = __bfloat162float(__float2bfloat16_rn(v[i] * rstd * (w4[i] + (p.plus_one ? 1.f : 0.f))));
+  }
+  float o[4] = {v[0], v[1], v[2], v[3]};
+  if (is_q || is_k) {
+    const float* cs = p.rope + (long long)p.positions[t] * D;
+    const int dd = d0 & 63;
+    const float4 c4 = *reinterpret_cast<const float4*>(cs + dd);
+    const float4 s4 = *reinterpret_cast<const float4*>(cs + 64 + dd);
+    const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float pv = __shfl_xor_sync(0xffffffffu, v[i], 16);
+      o[i] = lane < 16 ? v[i] * cc[i] - pv * sn[i] : v[i] * cc[i] + pv * sn[i];
+    }
+  }
+  if (is_q) {
+    uint2 pk;
+    pk.x = pack_bf16x2(o[0], o[1]);
+    pk.y = pack_bf16x2(o[2], o[3]);
+    *reinterpret_cast<uint2*>(p.q + t * p.ldq + hh * D + d0) = pk;
+    return;
+  }
+  const int blk = slot / p.block_size, tok_in_blk = slot % p.block_size;
+  if (is_k) {
+    const long long kbase = (((long long)blk * p.Hkv + hh) * p.block_size + tok_in_blk) * D + d0;
+    if (p.kv_fp8) {
+      uint32_t w = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) w |= (uint32_t)f32_to_fp8_e4m3(o[i] * p.inv_k_scale) << (8 * i);
+      *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(p.k_cache) + kbase) = w;
+    } else {
+      uint2 pk;
+      pk.x = pack_bf16x2(o[0], o[1]);
+      pk.y = pack_bf16x2(o[2], o[3]);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.k_cache) + kbase) = pk;
+    }
+    return;
+  }
+  const long long vbase = ((long long)blk * p.Hkv + hh) * (long long)D * p.block_size + tok_in_blk;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (p.kv_fp8) reinterpret_cast<uint8_t*>(p.v_cache)[vbase + (long long)(d0 + i) * p.block_size] = f32_to_fp8_e4m3(o[i] * p.inv_v_scale);
+    else reinterpret_cast<__nv_bfloat16*>(p.v_cache)[vbase + (long long)(d0 + i) * p.block_size] = __float2bfloat16_rn(o[i]);
+  }
+}
+
 // V rows of a prefill-size batch -> the transposed FP8 page layout [blk][head][d][tok16].  One warp per (16 consecutive
 // batch rows, kv head).  When the 16 rows fill one page in order (the common case inside a prompt chunk) every lane
 // gathers 16 tokens for its dims and writes whole 16-byte page rows; otherwise each row falls back to byte stores.
@@ -490,7 +574,13 @@ extern "C" int atlas_rope_kv_write(void* q, long long ldq, const void* k, long l
                   (reinterpret_cast<uintptr_t>(v) & 7) == 0) ? 1 : 0;
   const long long units = (long long)T * (Hq + (p.v_separate ? 1 : 2) * Hkv);
   const int grid = (int)((units + 3) / 4);
-  launch_chain_if(T <= 256, rope_kv_write_kernel, dim3(grid), dim3(128), 4 * D * sizeof(float), reinterpret_cast<cudaStream_t>(stream), p);
+  const bool d128 = D == 128 && rotary_dim == 128 && (ldq % 4) == 0 && (ldk % 4) == 0 && (ldv % 4) == 0 &&
+                    ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 7) == 0 &&
+                    (reinterpret_cast<uintptr_t>(rope) & 15) == 0;
+  if (d128)
+    launch_chain_if(T <= 256, rope_kv_write_d128_kernel, dim3(grid), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream), p);
+  else
+    launch_chain_if(T <= 256, rope_kv_write_kernel, dim3(grid), dim3(128), 4 * D * sizeof(float), reinterpret_cast<cudaStream_t>(stream), p);
   if (cudaGetLastError() != cudaSuccess) return -20;
   if (p.v_separate) {
     const long long vunits = (long long)((T + 15) / 16) * Hkv;

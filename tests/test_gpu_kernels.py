@@ -147,7 +147,7 @@ def _mk_cache(K, nb, bs, hkv, d):
     return K.alloc_kv_cache(nb, bs, hkv, d, torch.float8_e4m3fn, DEV)
 
 
-@pytest.mark.parametrize("D,rot,qknorm", [(128, 128, False), (64, 64, True), (256, 64, True)])
+@pytest.mark.parametrize("D,rot,qknorm", [(128, 128, False), (128, 128, True), (128, 64, True), (64, 64, True), (256, 64, True)])
 def test_rope_kv_write(K, D, rot, qknorm):
     torch.manual_seed(5)
     T, Hq, Hkv, bs, nb = 19, 4, 2, 16, 8
