@@ -214,6 +214,37 @@ def gemm_plan(M: int, N: int, K: int, kind: int, sms: int) -> Tuple[int, int]:
     return bn, splits
 
 
+GEMV_MAX_ROWS = 8
+# Off by default: measured on B200 (Llama-3-8B shapes, cold L2) the register-level kernel ties the tcgen05 tile at one row
+# (gate_up 43 vs 48 us, down 30 vs 30 us) and loses at eight (55 vs 51 us, 40 vs 31 us): it is bound by the staging
+# barriers and the fp8 -> f16 conversion pipe, not by HBM.
+_GEMV = os.environ.get("ATLAS_GEMV", "0") not in ("0", "false")
+
+
+def _gemv_fp8(a, b, a_scale, b_scale, out, sms: int, d: int) -> torch.Tensor:
+    """One to eight activation rows: weights stream through the register-level kernel (``csrc/gemv_fp8.cu``) instead of
+    a 128-row tcgen05 tile; K is split so that about four CTAs per SM are in flight."""
+    M, K = a.shape
+    N = b.shape[0]
+    L = lib()
+    if not getattr(L, "_gemv_bound", False):
+        L.atlas_gemv_fp8_block.argtypes = [_vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _i, _vp, _vp, _vp]
+        L._gemv_bound = True
+    if a_scale.stride(0) != 1:
+        a_scale = a_scale.t().contiguous().t()
+    ctas = (N + 63) // 64
+    splits = max(1, min((4 * sms + ctas - 1) // ctas, K // 512, 16))
+    ws = cnt = None
+    if splits > 1:
+        ws = scratch("gemm_ws", _GEMM_WS_BYTES, a.device)
+        cnt = scratch("gemm_counters", 1 << 18, a.device)
+        assert splits * 8 * N * 4 <= _GEMM_WS_BYTES and ctas * 4 <= (1 << 18)
+    _check(L.atlas_gemv_fp8_block(a.data_ptr(), b.data_ptr(), out.data_ptr(), a_scale.data_ptr(), a_scale.stride(1),
+                                  b_scale.data_ptr(), b_scale.shape[1], M, N, K, a.stride(0), b.stride(0), out.stride(0),
+                                  splits, _ptr(ws), _ptr(cnt), _stream()), "gemv_fp8")
+    return out
+
+
 def _gemm(kind: int, a: torch.Tensor, b: torch.Tensor, a_scale, b_scale, out: Optional[torch.Tensor]) -> torch.Tensor:
     M, K = a.shape
     N = b.shape[0]
@@ -223,6 +254,8 @@ def _gemm(kind: int, a: torch.Tensor, b: torch.Tensor, a_scale, b_scale, out: Op
         out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
     assert out.stride(1) == 1 and out.dtype == torch.bfloat16
     sms = _num_sms[d]
+    if kind == 1 and M <= GEMV_MAX_ROWS and K % 128 == 0 and N % 16 == 0 and out.stride(1) == 1 and _GEMV:
+        return _gemv_fp8(a, b, a_scale, b_scale, out, sms, d)
     bn, splits = gemm_plan(M, N, K, kind, sms)
     ws = cnt = None
     if splits > 1:
