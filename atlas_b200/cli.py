@@ -51,6 +51,8 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--ssm-cache-slots", type=int, default=16)
     s.add_argument("--ssm-checkpoint-interval", type=int, default=256)
     s.add_argument("--swap-space-gb", type=float, default=0.0)
+    s.add_argument("--high-speed-swap-gb", type=float, default=0.0, help="file-backed KV tier below the host tier")
+    s.add_argument("--high-speed-swap-path", default="", help="directory of the swap file (an NVMe mount)")
     s.add_argument("--quantization", default="auto", choices=["auto", "none", "fp8_block", "nvfp4"],
                    help="auto: what the checkpoint ships; otherwise quantise high-precision weights at load")
     s.add_argument("--dtype", default=None)
@@ -126,7 +128,8 @@ def _engine_config(args, mcfg):
                         num_drafts=args.num_drafts or (1 if args.speculative else (3 if args.ngram_speculative else 0)),
                         ngram_speculative=args.ngram_speculative, ngram_max=args.ngram_max, ngram_min=args.ngram_min,
                         mtp_gate=True if args.mtp_gate is None else args.mtp_gate, ssm_cache_slots=args.ssm_cache_slots,
-                        ssm_checkpoint_interval=args.ssm_checkpoint_interval, swap_space_gb=args.swap_space_gb,
+                        ssm_checkpoint_interval=args.ssm_checkpoint_interval, swap_space_gb=args.swap_space_gb, disk_swap_gb=args.high_speed_swap_gb,
+                        disk_swap_path=args.high_speed_swap_path,
                         use_cuda_graphs=not args.no_cuda_graphs, tp_size=max(1, args.tp_size), ep_size=max(1, args.ep_size),
                         seed=args.seed, request_timeout_s=args.request_timeout)
 

@@ -365,6 +365,8 @@ class EngineConfig:
     ssm_cache_slots: int = 16
     ssm_checkpoint_interval: int = 256
     swap_space_gb: float = 0.0
+    disk_swap_gb: float = 0.0               # file-backed tier below the host tier (0 = off)
+    disk_swap_path: str = ""                # directory of the swap file (default: the system temp directory)
     use_cuda_graphs: bool = True
     tp_size: int = 1
     ep_size: int = 1

@@ -72,7 +72,8 @@ class LLMEngine:
             per_block = max(1, model.kv_bytes_per_block(self.cfg.block_size, self.kv_dtype))
             n_host = int(self.cfg.swap_space_gb * (1 << 30)) // per_block
             if n_host > 0:
-                self.host_tier = HostKVTier(self.cache, n_host, self.cfg.max_num_seqs if self.hybrid else 0)
+                self.host_tier = HostKVTier(self.cache, n_host, self.cfg.max_num_seqs if self.hybrid else 0,
+                                            disk_gb=self.cfg.disk_swap_gb, disk_dir=self.cfg.disk_swap_path)
         self.scheduler = Scheduler(self.cfg, self.pool, self.radix, self.state_pool, self.hybrid, host_tier=self.host_tier)
         self.sampler = Sampler(self.mcfg.vocab_size, self.mcfg.eos_ids())
         self.runner = ModelRunner(model, self.cache, self.cfg)
@@ -188,8 +189,13 @@ class LLMEngine:
             self._seqs.pop(s.request_id, None)
         sched.finished_queue.clear()
         # host-tier traffic of this plan: saves first (a released block may already belong to someone else), then restores
+        for host_blocks, records in out.disk_out:
+            self.host_tier.spill(host_blocks, records)
         for dev_blocks, host_blocks, state_slot, host_state in out.swap_out:
             self.host_tier.copy_out(dev_blocks, host_blocks, state_slot, host_state)
+        for records, host_blocks in out.disk_in:
+            self.host_tier.unspill(records, host_blocks)
+            self.host_tier.disk.free(records)
         for host_blocks, dev_blocks, host_state, state_slot in out.swap_in:
             self.host_tier.copy_in(host_blocks, dev_blocks, host_state, state_slot)
             self.host_tier.free(host_blocks)

@@ -12,6 +12,8 @@ Sized by ``--swap-space-gb``.  Reference behaviour replaced: ``crates/spark-runt
 """
 from __future__ import annotations
 
+import os
+import tempfile
 from typing import Dict, List, Optional
 
 import torch
@@ -22,8 +24,60 @@ def _raw(t: torch.Tensor) -> torch.Tensor:
     return t.view(torch.uint8) if t.element_size() == 1 else t
 
 
+class DiskKVTier:
+    """File-backed block store below the host tier: one fixed-size record per KV block (all layers' K and V slices of
+    that block back to back), written and read with positional I/O on one preallocated file.  Parked sequences whose
+    turn to resume is furthest away are spilled here when the host tier is full and come back through host blocks.
+    Reference behaviour replaced: ``crates/avarok-tier/src/direct_swap`` (swap file) and the NVMe tier of
+    ``crates/spark-storage/src/high_speed_swap.rs``."""
+
+    def __init__(self, record_bytes: int, num_records: int, directory: str = ""):
+        self.record_bytes, self.num_records = int(record_bytes), int(num_records)
+        fd, self.path = tempfile.mkstemp(prefix="atlas_kv_swap_", suffix=".bin", dir=directory or None)
+        self.fd = fd
+        os.ftruncate(fd, self.record_bytes * self.num_records)
+        self._free: List[int] = list(range(self.num_records - 1, -1, -1))
+        self.records_out = 0
+        self.records_in = 0
+
+    @property
+    def num_free(self) -> int:
+        return len(self._free)
+
+    def alloc(self, n: int) -> List[int]:
+        assert n <= len(self._free), "disk tier exhausted"
+        return [self._free.pop() for _ in range(n)]
+
+    def free(self, ids: List[int]) -> None:
+        self._free.extend(ids)
+
+    def write(self, rec: int, data: bytes) -> None:
+        assert len(data) == self.record_bytes
+        os.pwrite(self.fd, data, rec * self.record_bytes)
+        self.records_out += 1
+
+    def read(self, rec: int) -> bytes:
+        self.records_in += 1
+        return os.pread(self.fd, self.record_bytes, rec * self.record_bytes)
+
+    def close(self) -> None:
+        if self.fd is not None:
+            os.close(self.fd)
+            self.fd = None
+            try:
+                os.unlink(self.path)
+            except OSError:
+                pass
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class HostKVTier:
-    def __init__(self, cache, num_host_blocks: int, num_state_slots: int = 0):
+    def __init__(self, cache, num_host_blocks: int, num_state_slots: int = 0, disk_gb: float = 0.0, disk_dir: str = ""):
         self.cache = cache
         self.num_blocks = int(num_host_blocks)
         self._free: List[int] = list(range(self.num_blocks - 1, -1, -1))
@@ -41,6 +95,12 @@ class HostKVTier:
                               for name, t in st.items() if name in ("conv", "h")}
         self.blocks_out = 0
         self.blocks_in = 0
+        self.record_bytes = sum(k[0].numel() * k.element_size() + v[0].numel() * v.element_size() for k, v in cache.kv.values())
+        self.disk: Optional[DiskKVTier] = None
+        if disk_gb > 0 and self.record_bytes > 0:
+            n_rec = int(disk_gb * (1 << 30)) // self.record_bytes
+            if n_rec > 0:
+                self.disk = DiskKVTier(self.record_bytes, n_rec, disk_dir)
 
     # ------------------------------------------------------------------ allocator (scheduler side)
     @property
@@ -65,6 +125,27 @@ class HostKVTier:
     def free_state(self, slot: Optional[int]) -> None:
         if slot is not None:
             self._free_states.append(slot)
+
+    # ------------------------------------------------------------------ host <-> disk (engine side)
+    def spill(self, host_blocks: List[int], disk_records: List[int]) -> None:
+        """Host blocks -> disk records (the host blocks are free again afterwards; the scheduler accounts for that)."""
+        for hb, rec in zip(host_blocks, disk_records):
+            parts = []
+            for l in self.k:
+                parts.append(_raw(self.k[l][hb]).contiguous().view(torch.uint8).numpy().tobytes())
+                parts.append(_raw(self.v[l][hb]).contiguous().view(torch.uint8).numpy().tobytes())
+            self.disk.write(rec, b"".join(parts))
+
+    def unspill(self, disk_records: List[int], host_blocks: List[int]) -> None:
+        for rec, hb in zip(disk_records, host_blocks):
+            data = memoryview(self.disk.read(rec))
+            off = 0
+            for l in self.k:
+                for t in (self.k[l], self.v[l]):
+                    n = t[hb].numel() * t.element_size()
+                    flat = torch.frombuffer(bytearray(data[off:off + n]), dtype=torch.uint8)
+                    t[hb].view(torch.uint8).reshape(-1).copy_(flat)
+                    off += n
 
     # ------------------------------------------------------------------ copies (engine side)
     def copy_out(self, dev_blocks: List[int], host_blocks: List[int], state_slot: Optional[int] = None,

@@ -36,6 +36,7 @@ class Scheduler:
         self.swapped: Deque[Sequence] = deque()
         self._resumed_now: List[Sequence] = []        # resumed in the current schedule() call: not victims yet
         self.num_swaps = 0
+        self.num_spills = 0
         self.bs = pool.block_size
         self.policy = policy or make_policy(cfg.scheduling_policy, cfg.tbt_deadline_ms)
         self.waiting: Deque[Sequence] = deque()
@@ -101,10 +102,31 @@ class Scheduler:
             self.state_pool.free(seq.state_slot)
         seq.state_slot, seq.has_state = None, False
         seq.drafts = []
-        if seq.host_blocks or seq.host_state is not None:
+        if seq.host_blocks or seq.host_state is not None or seq.disk_blocks:
             self.host_tier.free(seq.host_blocks)
             self.host_tier.free_state(seq.host_state)
-            seq.host_blocks, seq.host_state = [], None
+            if seq.disk_blocks:
+                self.host_tier.disk.free(seq.disk_blocks)
+            seq.host_blocks, seq.host_state, seq.disk_blocks = [], None, []
+
+    def _spill_to_disk(self, need_host: int, out: SchedulerOutput, keep: Optional[Sequence] = None) -> bool:
+        """Free ``need_host`` host blocks by moving parked sequences to the disk tier, starting with the one whose turn
+        to resume is furthest away.  The engine writes the records before any copy that reuses the host blocks."""
+        ht = self.host_tier
+        disk = getattr(ht, "disk", None)
+        if disk is None:
+            return ht.num_free >= need_host
+        for seq in reversed(self.swapped):
+            if ht.num_free >= need_host:
+                break
+            if seq is keep or not seq.host_blocks or disk.num_free < len(seq.host_blocks):
+                continue
+            records = disk.alloc(len(seq.host_blocks))
+            out.disk_out.append((list(seq.host_blocks), list(records)))
+            ht.free(seq.host_blocks)
+            seq.host_blocks, seq.disk_blocks = [], records
+            self.num_spills += 1
+        return ht.num_free >= need_host
 
     def _try_swap_out(self, victim: Sequence, out: SchedulerOutput) -> bool:
         """Park a decoding sequence's computed KV (and recurrent state) in the host tier.  Only sequences whose
@@ -114,7 +136,9 @@ class Scheduler:
             return False
         n_used = min(self.pool.blocks_for_tokens(victim.num_computed), len(victim.blocks))
         need_state = self.hybrid and victim.state_slot is not None
-        if ht.num_free < n_used or (need_state and ht.num_free_states == 0):
+        if need_state and ht.num_free_states == 0:
+            return False
+        if ht.num_free < n_used and not self._spill_to_disk(n_used, out):
             return False
         host_blocks = ht.alloc(n_used)
         host_state = ht.alloc_state() if need_state else None
@@ -141,8 +165,18 @@ class Scheduler:
                 return
             need = self._admission_blocks(seq, 0)
             avail = self.pool.num_free + (self.radix.evictable_blocks() if self.radix is not None else 0)
-            n_used = len(seq.host_blocks)
-            if need > avail or not self._reclaim(n_used):
+            n_used = len(seq.host_blocks) + len(seq.disk_blocks)
+            if need > avail:
+                return
+            if seq.disk_blocks:
+                # back through host blocks: the engine reads the records into them before the host -> device copy
+                ht = self.host_tier
+                if ht.num_free < n_used and not self._spill_to_disk(n_used, out, keep=seq):
+                    return
+                seq.host_blocks = ht.alloc(n_used)
+                out.disk_in.append((list(seq.disk_blocks), list(seq.host_blocks)))
+                seq.disk_blocks = []                  # the engine returns the records to the disk tier after reading
+            if not self._reclaim(n_used):
                 return
             self.swapped.popleft()
             seq.blocks = self.pool.alloc(n_used)

@@ -58,6 +58,7 @@ class Sequence:
     num_preemptions: int = 0
     host_blocks: List[int] = field(default_factory=list)  # host-tier blocks while SWAPPED
     host_state: Optional[int] = None
+    disk_blocks: List[int] = field(default_factory=list)  # disk-tier records while spilled below the host tier
     logprobs: List[Any] = field(default_factory=list)
     spec_accepted: int = 0
     spec_proposed: int = 0
@@ -118,6 +119,8 @@ class SchedulerOutput:
     restored_snapshots: List[tuple] = field(default_factory=list)   # (snapshot_slot, seq_slot)
     swap_out: List[tuple] = field(default_factory=list)             # (device blocks, host blocks, state slot, host state)
     swap_in: List[tuple] = field(default_factory=list)              # (host blocks, device blocks, host state, state slot)
+    disk_out: List[tuple] = field(default_factory=list)             # (host blocks, disk records): spilled before the swap-outs
+    disk_in: List[tuple] = field(default_factory=list)              # (disk records, host blocks): staged before the swap-ins
     snapshot_requests: List[tuple] = field(default_factory=list)    # (item index, rows from chunk start, snapshot slot, node)
 
     @property

@@ -351,3 +351,30 @@ def test_host_tier_swaps_instead_of_recomputing(hybrid):
     assert swap.stats.prefill_tokens < recompute.stats.prefill_tokens
     assert swap.host_tier.num_free == swap.host_tier.num_blocks and not swap.scheduler.swapped
     swap.pool.check_invariants()
+
+
+def test_disk_tier_below_host_tier(tmp_path):
+    """A host tier too small for all parked sequences spills the ones that resume last to a swap file and brings them
+    back through host blocks; tokens match the uncontended run and every tier ends empty."""
+    prompts = _prompts(6, 40)
+    sp = SamplingParams(max_tokens=40, ignore_eos=True)
+
+    def eng(**kw):
+        return LLMEngine(build_model(tiny_dense()).init_random(0), EngineConfig(block_size=16, max_num_seqs=8, max_prefill_tokens=64, **kw))
+
+    want = [o.output_tokens for o in eng(num_kv_blocks=96).generate(prompts, sp)]
+    e = eng(num_kv_blocks=14, swap_space_gb=0.01, disk_swap_gb=0.01, disk_swap_path=str(tmp_path))
+    per_block = e.host_tier.record_bytes
+    e.host_tier._free = e.host_tier._free[:6]                 # shrink the host tier to six blocks: one parked sequence
+    e.host_tier.num_blocks = 6
+    got = [o.output_tokens for o in e.generate(prompts, sp)]
+    assert got == want
+    disk = e.host_tier.disk
+    assert disk is not None and disk.record_bytes == per_block
+    assert e.scheduler.num_spills > 0 and disk.records_out == disk.records_in > 0
+    assert disk.num_free == disk.num_records and e.host_tier.num_free == 6 and not e.scheduler.swapped
+    e.pool.check_invariants()
+    path = disk.path
+    disk.close()
+    import os
+    assert not os.path.exists(path)
