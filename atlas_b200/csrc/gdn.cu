@@ -201,21 +201,28 @@ ATLAS_DEVICE void warp_tile_tf32(float (&c)[4], int m0, int n0, int K, FA a_at, 
   }
 }
 
+// DVC = value columns per CTA.  The columns of the state evolve independently (the solve and every product below are
+// column-wise in v), so a head can be cut into 128 / DVC CTAs (grid.z) when sequences x heads alone would leave SMs idle;
+// each CTA then repeats the K K^T / Q K^T products, which do not depend on v.
+template <int DVC>
 __global__ void __launch_bounds__(256, 1)
 gdn_chunk_kernel(const GdnParams p) {
   constexpr int DK = 128, DV = 128;
+  constexpr int LDV = DVC + 4;              // leading dimension of the [.][DVC] tiles
+  constexpr int NT = DVC / 8;               // 8-wide column tiles of a slice
   extern __shared__ float gsm[];
-  float* sh = gsm;                          // state [DK][kGLd]
-  float* sK = sh + DK * kGLd;               // [64][kGLd]
+  float* sh = gsm;                          // state slice [DK][LDV]
+  float* sK = sh + DK * LDV;                // [64][kGLd]
   float* sQ = sK + kGC * kGLd;
-  float* sV = sQ + kGC * kGLd;              // v, then B, then D (in place)
-  float* sA = sV + kGC * kGLd;              // [64][kGLdS]
+  float* sV = sQ + kGC * kGLd;              // [64][LDV]: v, then B, then D (in place)
+  float* sA = sV + kGC * LDV;               // [64][kGLdS]
   float* sP = sA + kGC * kGLdS;
   float* sG = sP + kGC * kGLdS;             // running log-decay [64]
   float* sBeta = sG + kGC;                  // [64]
   float* sE = sBeta + kGC;                  // e^{G_i}
   float* sW = sE + kGC;                     // e^{G_C - G_i}
   const int hv = blockIdx.x, bseq = blockIdx.y;
+  const int v0 = blockIdx.z * DVC;          // first value column of this CTA
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t4 = lane & 3;
   const int hk = hv / (p.Hv / p.Hk);
@@ -225,7 +232,7 @@ gdn_chunk_kernel(const GdnParams p) {
   const long long slot = p.state_slots[bseq];
   float* hs = p.h + ((slot * p.Hv + hv) * (long long)DK) * DV;
   const bool live = p.has_state[bseq] != 0;
-  for (int i = tid; i < DK * DV; i += 256) sh[(i >> 7) * kGLd + (i & 127)] = live ? hs[i] : 0.f;
+  for (int i = tid; i < DK * DVC; i += 256) sh[(i / DVC) * LDV + (i % DVC)] = live ? hs[(i / DVC) * DV + v0 + (i % DVC)] : 0.f;
   const float neg_a = -__expf(p.A_log[hv]);
   const float dtb = p.dt_bias[hv];
   const int kd = p.Hk * DK;
@@ -245,7 +252,7 @@ gdn_chunk_kernel(const GdnParams p) {
         const __nv_bfloat16* row = p.y + (long long)(q0 + c0 + i) * p.ldy;
         const uint2 rq = *reinterpret_cast<const uint2*>(row + hk * DK + lane * 4);
         const uint2 rk = *reinterpret_cast<const uint2*>(row + kd + hk * DK + lane * 4);
-        const uint2 rv = *reinterpret_cast<const uint2*>(row + 2 * kd + hv * DV + lane * 4);
+        const uint2 rv = lane * 4 < DVC ? *reinterpret_cast<const uint2*>(row + 2 * kd + hv * DV + v0 + lane * 4) : make_uint2(0u, 0u);
         const __nv_bfloat162* hq = reinterpret_cast<const __nv_bfloat162*>(&rq);
         const __nv_bfloat162* hkk = reinterpret_cast<const __nv_bfloat162*>(&rk);
         const __nv_bfloat162* hvv = reinterpret_cast<const __nv_bfloat162*>(&rv);
@@ -261,7 +268,7 @@ gdn_chunk_kernel(const GdnParams p) {
       for (int e = 0; e < 4; ++e) {
         sQ[i * kGLd + lane * 4 + e] = q[e] * qn;
         sK[i * kGLd + lane * 4 + e] = k[e] * kn;
-        sV[i * kGLd + lane * 4 + e] = v[e];
+        if (lane * 4 < DVC) sV[i * LDV + lane * 4 + e] = v[e];
       }
       if (lane == 0) {
         float gi = 0.f, bi = 0.f;
@@ -292,13 +299,13 @@ gdn_chunk_kernel(const GdnParams p) {
     }
     __syncthreads();
     // ---- 2. B = beta (v - e^G (K h0)); A and P from K K^T and Q K^T
-    for (int tile = warp; tile < 64; tile += 8) {
-      const int m0 = (tile >> 4) * 16, n0 = (tile & 15) * 8;
+    for (int tile = warp; tile < 4 * NT; tile += 8) {
+      const int m0 = (tile / NT) * 16, n0 = (tile % NT) * 8;
       float c[4] = {0.f, 0.f, 0.f, 0.f};
-      warp_tile_tf32(c, m0, n0, DK, [&](int m, int k) { return sK[m * kGLd + k]; }, [&](int k, int nn) { return sh[k * kGLd + nn]; }, lane);
+      warp_tile_tf32(c, m0, n0, DK, [&](int m, int k) { return sK[m * kGLd + k]; }, [&](int k, int nn) { return sh[k * LDV + nn]; }, lane);
       for (int e = 0; e < 4; ++e) {
         const int i = m0 + g + (e >> 1) * 8, j = n0 + 2 * t4 + (e & 1);
-        sV[i * kGLd + j] = sBeta[i] * (sV[i * kGLd + j] - sE[i] * c[e]);
+        sV[i * LDV + j] = sBeta[i] * (sV[i * LDV + j] - sE[i] * c[e]);
       }
     }
     for (int tile = warp; tile < 64; tile += 8) {
@@ -317,32 +324,32 @@ gdn_chunk_kernel(const GdnParams p) {
     }
     __syncthreads();
     // ---- 3. forward substitution (I + A) D = B, one value column per thread
-    if (tid < DV) {
+    if (tid < DVC) {
       float d[kGC];
 #pragma unroll
       for (int i = 0; i < kGC; ++i) {
-        float acc = sV[i * kGLd + tid];
+        float acc = sV[i * LDV + tid];
 #pragma unroll
         for (int j = 0; j < i; ++j) acc = fmaf(-sA[i * kGLdS + j], d[j], acc);
         d[i] = acc;
       }
 #pragma unroll
-      for (int i = 0; i < kGC; ++i) sV[i * kGLd + tid] = d[i];
+      for (int i = 0; i < kGC; ++i) sV[i * LDV + tid] = d[i];
     }
     __syncthreads();
     // ---- 4. o = e^G (Q h0) + P D
-    for (int tile = warp; tile < 64; tile += 8) {
-      const int m0 = (tile >> 4) * 16, n0 = (tile & 15) * 8;
+    for (int tile = warp; tile < 4 * NT; tile += 8) {
+      const int m0 = (tile / NT) * 16, n0 = (tile % NT) * 8;
       float c[4] = {0.f, 0.f, 0.f, 0.f};
-      warp_tile_tf32(c, m0, n0, DK, [&](int m, int k) { return sQ[m * kGLd + k]; }, [&](int k, int nn) { return sh[k * kGLd + nn]; }, lane);
+      warp_tile_tf32(c, m0, n0, DK, [&](int m, int k) { return sQ[m * kGLd + k]; }, [&](int k, int nn) { return sh[k * LDV + nn]; }, lane);
       const float e0 = sE[m0 + g], e1 = sE[m0 + g + 8];
       c[0] *= e0; c[1] *= e0; c[2] *= e1; c[3] *= e1;
-      warp_tile_tf32(c, m0, n0, kGC, [&](int m, int k) { return sP[m * kGLdS + k]; }, [&](int k, int nn) { return sV[k * kGLd + nn]; }, lane);
+      warp_tile_tf32(c, m0, n0, kGC, [&](int m, int k) { return sP[m * kGLdS + k]; }, [&](int k, int nn) { return sV[k * LDV + nn]; }, lane);
       for (int hlf = 0; hlf < 2; ++hlf) {
         const int i = m0 + g + hlf * 8;
         if (i < rows) {
           __nv_bfloat162 o2 = __floats2bfloat162_rn(c[2 * hlf], c[2 * hlf + 1]);
-          *reinterpret_cast<__nv_bfloat162*>(p.out + (long long)(q0 + c0 + i) * p.ldo + hv * DV + n0 + 2 * t4) = o2;
+          *reinterpret_cast<__nv_bfloat162*>(p.out + (long long)(q0 + c0 + i) * p.ldo + hv * DV + v0 + n0 + 2 * t4) = o2;
         }
       }
     }
@@ -350,26 +357,26 @@ gdn_chunk_kernel(const GdnParams p) {
     // ---- 5. h = e^{G_C} h0 + sum_j e^{G_C - G_j} k_j (x) D_j
     {
       const float gC = sE[kGC - 1];
-      for (int tile = warp; tile < 128; tile += 8) {
-        const int m0 = (tile >> 4) * 16, n0 = (tile & 15) * 8;
+      for (int tile = warp; tile < 8 * NT; tile += 8) {
+        const int m0 = (tile / NT) * 16, n0 = (tile % NT) * 8;
         float c[4];
-        for (int e = 0; e < 4; ++e) c[e] = sh[(m0 + g + (e >> 1) * 8) * kGLd + n0 + 2 * t4 + (e & 1)] * gC;
+        for (int e = 0; e < 4; ++e) c[e] = sh[(m0 + g + (e >> 1) * 8) * LDV + n0 + 2 * t4 + (e & 1)] * gC;
         warp_tile_tf32(c, m0, n0, kGC, [&](int m, int k) { return sK[k * kGLd + m] * sW[k]; },
-                       [&](int k, int nn) { return sV[k * kGLd + nn]; }, lane);
-        for (int e = 0; e < 4; ++e) sh[(m0 + g + (e >> 1) * 8) * kGLd + n0 + 2 * t4 + (e & 1)] = c[e];
+                       [&](int k, int nn) { return sV[k * LDV + nn]; }, lane);
+        for (int e = 0; e < 4; ++e) sh[(m0 + g + (e >> 1) * 8) * LDV + n0 + 2 * t4 + (e & 1)] = c[e];
       }
     }
     __syncthreads();
     for (int s = 0; s < snaps; ++s) {
       if (p.snap_rows[bseq * snaps + s] == c0 + rows) {
         float* dst = p.h + (((long long)p.snap_slots[bseq * snaps + s] * p.Hv + hv) * (long long)DK) * DV;
-        for (int i = tid; i < DK * DV; i += 256) dst[i] = sh[(i >> 7) * kGLd + (i & 127)];
+        for (int i = tid; i < DK * DVC; i += 256) dst[(i / DVC) * DV + v0 + (i % DVC)] = sh[(i / DVC) * LDV + (i % DVC)];
       }
     }
     c0 += rows;
   }
   if (p.commit)
-    for (int i = tid; i < DK * DV; i += 256) hs[i] = sh[(i >> 7) * kGLd + (i & 127)];
+    for (int i = tid; i < DK * DVC; i += 256) hs[(i / DVC) * DV + v0 + (i % DVC)] = sh[(i / DVC) * LDV + (i % DVC)];
 }
 
 }  // namespace atlas
@@ -446,13 +453,35 @@ extern "C" int atlas_gdn_chunked(const void* y, long long ldy, const void* a, lo
   p.query_start_loc = query_start_loc; p.state_slots = state_slots; p.has_state = has_state; p.limit = nullptr;
   p.snap_rows = snap_rows; p.snap_slots = snap_slots; p.num_snaps_per_seq = num_snaps_per_seq;
   p.Hk = Hk; p.Hv = Hv; p.Dv = Dv; p.commit = commit; p.scale = 1.f / sqrtf((float)Dk);
-  constexpr int kSmem = (128 * kGLd + 3 * kGC * kGLd + 2 * kGC * kGLdS + 4 * kGC) * 4;
-  static bool attr_done = false;
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return -20;
-    attr_done = true;
+  // value-column slices per head: as many as keep the grid within the SM count (few long sequences), else one
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      num_sms = 1;
   }
-  dim3 grid(Hv, B);
-  gdn_chunk_kernel<<<grid, 256, kSmem, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  int split = 1;
+  if (const char* e = getenv("ATLAS_GDN_SPLIT")) split = atoi(e);
+  else if ((long long)Hv * B * 4 <= num_sms) split = 4;
+  else if ((long long)Hv * B * 2 <= num_sms) split = 2;
+  if (split != 1 && split != 2 && split != 4) return -3;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  dim3 grid(Hv, B, split);
+  auto smem_of = [](int dvc) { return (128 * (dvc + 4) + 2 * kGC * kGLd + kGC * (dvc + 4) + 2 * kGC * kGLdS + 4 * kGC) * 4; };
+  static bool attr_done[3] = {false, false, false};
+  cudaError_t rc = cudaSuccess;
+  if (split == 1) {
+    if (!attr_done[0]) { rc = cudaFuncSetAttribute(gdn_chunk_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_of(128)); attr_done[0] = true; }
+    if (rc != cudaSuccess) return -20;
+    gdn_chunk_kernel<128><<<grid, 256, smem_of(128), st>>>(p);
+  } else if (split == 2) {
+    if (!attr_done[1]) { rc = cudaFuncSetAttribute(gdn_chunk_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_of(64)); attr_done[1] = true; }
+    if (rc != cudaSuccess) return -20;
+    gdn_chunk_kernel<64><<<grid, 256, smem_of(64), st>>>(p);
+  } else {
+    if (!attr_done[2]) { rc = cudaFuncSetAttribute(gdn_chunk_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_of(32)); attr_done[2] = true; }
+    if (rc != cudaSuccess) return -20;
+    gdn_chunk_kernel<32><<<grid, 256, smem_of(32), st>>>(p);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }

@@ -138,11 +138,13 @@ def test_gdn_layer_kernels_match_reference(K):
     assert _rel_rms(st_k2["conv"], st_r2["conv"]) < 1e-2
 
 
-def test_gdn_chunked_matches_recurrence(K):
+@pytest.mark.parametrize("split", ["1", "2", "4"])
+def test_gdn_chunked_matches_recurrence(K, split, monkeypatch):
     """The 64-token chunked kernel (TF32 tensor cores) against the sequential recurrence kernel and the fp32 PyTorch
     recurrence: outputs, final state and mid-chunk snapshots, for sequences that start from a stored state or from
     zero, end inside a chunk, or are a single token."""
     from atlas_b200.ops import cuda_gdn
+    monkeypatch.setenv("ATLAS_GDN_SPLIT", split)       # value-column slices per head (read at every launch)
     cfg = _hybrid_cfg()
     cfg.linear_key_head_dim = cfg.linear_value_head_dim = 128
     cfg.linear_num_key_heads, cfg.linear_num_value_heads = 2, 4
