@@ -18,6 +18,7 @@ from typing import Any, AsyncIterator, Dict, List, Optional
 from ..sampling import SamplingParams
 from .grammar import GrammarSpec
 from .reasoning import ReasoningSplitter, ThinkingBudget
+from .loop_detector import LoopDetector
 from .tokenizer import IncrementalDetokenizer, render_chat
 from .tool_parsers import StreamingToolParser, ToolCall, get_parser
 
@@ -193,7 +194,9 @@ class Generator:
             raise ValueError(f"adapter '{req.adapter}' is not loaded")
         gen_iter = s.engine.generate(toks, sp, request_id="req-" + req.request_id, namespace=ns, adapter_slot=adapter_slot,
                                      grammar=_GrammarAdapter(grammar) if grammar else None,
-                                     logits_processors=procs, timeout_s=req.timeout_s, disable_spec=req.disable_spec)
+                                     logits_processors=procs, timeout_s=req.timeout_s, disable_spec=req.disable_spec,
+                                     stop_checker=(LoopDetector(span=int(s.args.get("loop_guard_span") or 128))
+                                                   if s.args.get("loop_guard") else None))
         final = None
         if req.echo and prompt_text:
             yield GenDelta(content=prompt_text)

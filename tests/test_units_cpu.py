@@ -378,3 +378,36 @@ def test_disk_tier_below_host_tier(tmp_path):
     disk.close()
     import os
     assert not os.path.exists(path)
+
+
+def test_loop_detector_and_engine_stop():
+    from atlas_b200.server.loop_detector import LoopDetector
+    det = LoopDetector(span=32, max_period=8, min_repeats=4, stride=1)
+    g = torch.Generator().manual_seed(0)
+    rnd = torch.randint(0, 1000, (200,), generator=g).tolist()
+    assert det.check(rnd) is None
+    assert det.check(rnd + [7, 8, 9] * 10) is None                  # 30 periodic tokens < span
+    assert det.check(rnd + [7, 8, 9] * 11) == 3
+    assert det.check(rnd + [5] * 32) == 1
+    assert det.check([1, 2] * 8) is None                            # shorter than the span
+    long_p = list(range(10))
+    assert LoopDetector(span=32, max_period=8, min_repeats=4).check(rnd + long_p * 8) is None     # period 10 > max_period
+    assert LoopDetector(span=32, max_period=16, min_repeats=4).check(rnd + long_p * 8) == 10
+
+    # engine: a checker that fires ends the request with reason "stop" before max_tokens
+    eng = _engine(num_kv_blocks=64)
+    fired = LoopDetector(span=8, max_period=4, min_repeats=2, stride=1)
+
+    class Forced:                              # make the model emit a cycle: every row is forced to token (n % 2)
+        def __call__(self, row, seq):
+            row = torch.full_like(row, float("-inf"))
+            row[seq.num_output_tokens % 2] = 0.0
+            return row
+    rid = eng.add_request(_prompts(1, 12)[0], SamplingParams(max_tokens=64, ignore_eos=True), logits_processors=[Forced()],
+                          stop_checker=fired)
+    outs = {}
+    while eng.has_unfinished():
+        for o in eng.step():
+            outs[o.request_id] = o
+    assert outs[rid].finish_reason == "stop" and fired.period == 2
+    assert 8 <= len(outs[rid].output_tokens) < 64
