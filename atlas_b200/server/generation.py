@@ -19,6 +19,7 @@ from ..sampling import SamplingParams
 from .grammar import GrammarSpec
 from .reasoning import ReasoningSplitter, ThinkingBudget
 from .loop_detector import LoopDetector
+from .compaction import compact_messages
 from .tokenizer import IncrementalDetokenizer, render_chat
 from .tool_parsers import StreamingToolParser, ToolCall, get_parser
 
@@ -122,12 +123,21 @@ class Generator:
         elif req.messages is not None:
             if not isinstance(req.messages, list) or not req.messages:
                 raise BadRequest("'messages' must be a non-empty array", "messages")
-            try:
-                text = render_chat(tk, req.messages, tools, add_generation_prompt=True, enable_thinking=thinking,
+            def render(msgs):
+                return render_chat(tk, msgs, tools, add_generation_prompt=True, enable_thinking=thinking,
                                    **req.chat_template_kwargs)
+            try:
+                text = render(req.messages)
             except Exception as e:
                 raise BadRequest(f"chat template failed: {e}", "messages")
             toks = tk.encode(text)
+            if s.args.get("context_compaction"):
+                reserve = int(s.args.get("compaction_reserve_tokens") or 256)
+                budget = s.engine.engine.cfg.max_seq_len - reserve
+                if len(toks) > budget:
+                    msgs, self.last_compaction = compact_messages(req.messages, lambda m: len(tk.encode(render(m))), budget)
+                    text = render(msgs)
+                    toks = tk.encode(text)
         else:
             text = req.prompt or ""
             toks = tk.encode(text, add_special_tokens=bool(tk.bos_token_id is not None and s.args.get("add_bos", False)))

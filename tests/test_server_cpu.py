@@ -196,3 +196,27 @@ def test_fault_latch_turns_service_unavailable():
     finally:
         FAULT_LATCH.reset_for_tests()
         aeng.shutdown(drain=False)
+
+
+def test_over_long_chat_is_compacted_or_rejected():
+    """Without compaction an over-long conversation is a 400 (context_length_exceeded); with it the old turns are
+    elided / dropped and the request is served."""
+    msgs = [{"role": "system", "content": "be brief"}]
+    for i in range(12):
+        msgs.append({"role": "user", "content": f"question {i} " + "lorem ipsum " * 8})
+        msgs.append({"role": "assistant", "content": f"answer {i} " + "dolor sit " * 8})
+    msgs.append({"role": "user", "content": "final?"})
+    body = {"model": "tiny", "messages": msgs, "max_tokens": 4}
+    c, aeng, _ = _client()
+    try:
+        r = c.post("/v1/chat/completions", json=body)
+        assert r.status_code == 400 and r.json()["error"]["code"] == "context_length_exceeded"
+    finally:
+        aeng.shutdown(drain=False)
+    c, aeng, state = _client({"context_compaction": True, "compaction_reserve_tokens": 64})
+    try:
+        r = c.post("/v1/chat/completions", json=body)
+        assert r.status_code == 200, r.text
+        assert r.json()["usage"]["prompt_tokens"] <= 1024 - 64
+    finally:
+        aeng.shutdown(drain=False)

@@ -411,3 +411,33 @@ def test_loop_detector_and_engine_stop():
             outs[o.request_id] = o
     assert outs[rid].finish_reason == "stop" and fired.period == 2
     assert 8 <= len(outs[rid].output_tokens) < 64
+
+
+def test_context_compaction_stages():
+    from atlas_b200.server.compaction import compact_messages
+    count = lambda msgs: sum(len(str(m.get("content") or "")) // 4 + 4 for m in msgs)      # ~4 characters per token
+    sys_m = {"role": "system", "content": "You are terse."}
+    big_tool = {"role": "tool", "tool_call_id": "a", "content": "x" * 20000}
+    chat = [sys_m,
+            {"role": "user", "content": "list the files"},
+            {"role": "assistant", "content": "", "tool_calls": [{"id": "a", "type": "function", "function": {"name": "ls", "arguments": "{}"}}]},
+            big_tool,
+            {"role": "assistant", "content": "done " * 200},
+            {"role": "user", "content": "q" * 8000},
+            {"role": "assistant", "content": "ok"},
+            {"role": "user", "content": "and now?"},
+            {"role": "assistant", "content": "sure"},
+            {"role": "user", "content": "last question"}]
+    same, rep = compact_messages(chat, count, budget=100000)
+    assert same == chat and rep["stage"] == 0
+    out, rep = compact_messages(chat, count, budget=4000)           # eliding the tool result is enough
+    assert rep["stage"] == 1 and rep["elided"] == 1 and rep["dropped"] == 0 and count(out) <= 4000
+    assert "elided" in out[3]["content"] and out[3]["content"].startswith("x") and len(out) == len(chat)
+    assert chat[3]["content"] == "x" * 20000                        # the caller's list is untouched
+    out, rep = compact_messages(chat, count, budget=1200)           # user turn has to shrink too
+    assert rep["stage"] == 2 and count(out) <= 1200
+    out, rep = compact_messages(chat, count, budget=150)            # old turns are dropped, tool result with its call
+    assert rep["stage"] == 3 and rep["dropped"] >= 4
+    assert out[0] == sys_m and out[1]["role"] == "system" and "left out" in out[1]["content"]
+    assert [m["content"] for m in out[-4:]] == [m["content"] for m in chat[-4:]]
+    assert not any(m.get("role") == "tool" for m in out)
