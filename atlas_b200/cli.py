@@ -158,6 +158,11 @@ def load_for_serving(args, pctx, device):
         return model, None
     from .config import ModelConfig
     from .loader import Checkpoint, load_weights
+    from .utils.model_resolver import ModelNotFound, resolve_model
+    try:
+        args.model = resolve_model(args.model)          # hub-style ids resolve to a local snapshot (offline)
+    except ModelNotFound as e:
+        raise SystemExit(str(e))
     mcfg = ModelConfig.from_pretrained(args.model)
     if args.quantization not in ("auto", "none"):
         mcfg.quant = QuantConfig(method=args.quantization)

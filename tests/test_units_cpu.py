@@ -441,3 +441,41 @@ def test_context_compaction_stages():
     assert out[0] == sys_m and out[1]["role"] == "system" and "left out" in out[1]["content"]
     assert [m["content"] for m in out[-4:]] == [m["content"] for m in chat[-4:]]
     assert not any(m.get("role") == "tool" for m in out)
+
+
+def test_model_resolver_offline(tmp_path, monkeypatch):
+    from atlas_b200.utils.model_resolver import ModelNotFound, resolve_model
+    import os, time
+    local = tmp_path / "ckpt"
+    local.mkdir()
+    (local / "config.json").write_text("{}")
+    assert resolve_model(str(local)) == str(local)
+    assert resolve_model("preset:tiny-dense") == "preset:tiny-dense"
+    empty = tmp_path / "empty"
+    empty.mkdir()
+    with pytest.raises(ModelNotFound):
+        resolve_model(str(empty))
+    # search directories
+    models = tmp_path / "models"
+    (models / "Llama-X").mkdir(parents=True)
+    (models / "Llama-X" / "config.json").write_text("{}")
+    monkeypatch.setenv("ATLAS_MODEL_DIRS", str(models))
+    assert resolve_model("meta/Llama-X") == str(models / "Llama-X")
+    # hub cache: refs/main wins, else the newest snapshot with a config
+    cache = tmp_path / "hf" / "hub"
+    snaps = cache / "models--org--name" / "snapshots"
+    for rev in ("aaa", "bbb"):
+        (snaps / rev).mkdir(parents=True)
+        (snaps / rev / "config.json").write_text("{}")
+        time.sleep(0.02)
+    monkeypatch.setenv("HF_HOME", str(tmp_path / "hf"))
+    monkeypatch.delenv("HF_HUB_CACHE", raising=False)
+    assert resolve_model("org/name") == str(snaps / "bbb")
+    refs = cache / "models--org--name" / "refs"
+    refs.mkdir()
+    (refs / "main").write_text("aaa\n")
+    assert resolve_model("org/name") == str(snaps / "aaa")
+    assert resolve_model("org/name", revision="bbb") == str(snaps / "bbb")
+    with pytest.raises(ModelNotFound) as ei:
+        resolve_model("org/other")
+    assert "models--org--other" in str(ei.value)
