@@ -77,6 +77,8 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--dump", default=None, help="directory receiving one JSON file per request")
     s.add_argument("--context-compaction", action="store_true",
                    help="elide / drop old chat turns so that an over-long conversation fits the context window")
+    s.add_argument("--no-output-sanitizer", action="store_true",
+                   help="do not treat leaked chat-template markers in the output text as end of turn")
     s.add_argument("--loop-guard", action="store_true", help="end a generation whose output repeats with a short period")
     s.add_argument("--loop-guard-span", type=int, default=128, help="tokens that must be periodic before the guard fires")
     s.add_argument("--check-kernels", action="store_true", help="run the kernel self-test before serving")
@@ -246,7 +248,7 @@ def cmd_serve(argv: List[str]) -> int:
     state = ServerState(aeng, tokenizer, args.served_model_name or os.path.basename(args.model.rstrip("/")) or args.model,
                         {"api_keys": keys if (keys or args.require_auth) else None, "rate_limit_rpm": args.rate_limit_rpm,
                          "tool_call_parser": args.tool_call_parser, "disable_thinking": args.disable_thinking,
-                         "max_thinking_budget": args.max_thinking_budget, "dump": args.dump, "profile": args.profile, "loop_guard": args.loop_guard, "context_compaction": args.context_compaction,
+                         "max_thinking_budget": args.max_thinking_budget, "dump": args.dump, "profile": args.profile, "loop_guard": args.loop_guard, "no_output_sanitizer": args.no_output_sanitizer, "context_compaction": args.context_compaction,
                          "loop_guard_span": args.loop_guard_span,
                          "serve_plan": plan})
     for spec in args.lora_adapter:

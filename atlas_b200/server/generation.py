@@ -20,6 +20,7 @@ from .grammar import GrammarSpec
 from .reasoning import ReasoningSplitter, ThinkingBudget
 from .loop_detector import LoopDetector
 from .compaction import compact_messages
+from .sanitizer import guarded_stops
 from .tokenizer import IncrementalDetokenizer, render_chat
 from .tool_parsers import StreamingToolParser, ToolCall, get_parser
 
@@ -191,7 +192,7 @@ class Generator:
         detok = IncrementalDetokenizer(s.tokenizer)
         reasoning = ReasoningSplitter(starts_in_reasoning=False) if (thinking or s.args.get("always_split_reasoning")) else None
         tool_stream = StreamingToolParser(get_parser(s.tool_parser_name, tools)) if tools else None
-        stops = [x for x in req.stop if x]
+        stops = guarded_stops(req.stop, enabled=not s.args.get("no_output_sanitizer"))
         hold = max((len(x) for x in stops), default=0)
         pending = ""              # text held back while it could be the start of a stop string
         stopped = False

@@ -479,3 +479,11 @@ def test_model_resolver_offline(tmp_path, monkeypatch):
     with pytest.raises(ModelNotFound) as ei:
         resolve_model("org/other")
     assert "models--org--other" in str(ei.value)
+
+
+def test_output_sanitizer_stops():
+    from atlas_b200.server.sanitizer import LEAK_MARKERS, guarded_stops
+    assert guarded_stops(["END", ""], enabled=False) == ["END"]
+    got = guarded_stops(["END", "<|im_end|>"])
+    assert got[:2] == ["END", "<|im_end|>"] and got.count("<|im_end|>") == 1
+    assert set(LEAK_MARKERS) <= set(got)
