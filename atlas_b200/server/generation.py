@@ -22,7 +22,7 @@ from .loop_detector import LoopDetector
 from .compaction import compact_messages
 from .sanitizer import guarded_stops
 from .tokenizer import IncrementalDetokenizer, render_chat
-from .tool_parsers import StreamingToolParser, ToolCall, get_parser
+from .tool_parsers import StreamingToolParser, ToolCall, get_parser, dedupe_calls
 
 
 @dataclass
@@ -265,6 +265,7 @@ class Generator:
         calls: List[ToolCall] = []
         if tool_stream:
             rest, calls = tool_stream.finish()
+            calls = dedupe_calls(calls)
             d.content += rest
             if calls and not req.parallel_tool_calls:
                 calls = calls[:1]

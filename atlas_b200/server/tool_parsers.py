@@ -33,6 +33,23 @@ class ToolCall:
                 "function": {"name": self.name, "arguments": self.arguments}}
 
 
+def dedupe_calls(calls: List["ToolCall"]) -> List["ToolCall"]:
+    """Drop repeated calls of one turn that name the same function with the same arguments (compared as parsed JSON, so
+    key order and whitespace do not matter); the first occurrence stays.  Models in a repetition loop emit the same
+    call several times, and executing it more than once is never what the client wants.
+    Reference behaviour replaced: ``crates/spark-server/src/tool_arg_dedup.rs``."""
+    seen, out = set(), []
+    for c in calls:
+        try:
+            key = (c.name, json.dumps(json.loads(c.arguments), sort_keys=True))
+        except (ValueError, TypeError):
+            key = (c.name, c.arguments)
+        if key not in seen:
+            seen.add(key)
+            out.append(c)
+    return out
+
+
 def _json_args(v: Any) -> str:
     if isinstance(v, str):
         try:

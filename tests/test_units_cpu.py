@@ -487,3 +487,14 @@ def test_output_sanitizer_stops():
     got = guarded_stops(["END", "<|im_end|>"])
     assert got[:2] == ["END", "<|im_end|>"] and got.count("<|im_end|>") == 1
     assert set(LEAK_MARKERS) <= set(got)
+
+
+def test_tool_call_dedupe():
+    from atlas_b200.server.tool_parsers import ToolCall, dedupe_calls
+    calls = [ToolCall("ls", '{"path": "/", "all": true}'), ToolCall("ls", '{"all":true,"path":"/"}'),
+             ToolCall("ls", '{"path": "/tmp"}'), ToolCall("cat", '{"path": "/"}'), ToolCall("cat", "not json"),
+             ToolCall("cat", "not json")]
+    out = dedupe_calls(calls)
+    assert [(c.name, c.arguments) for c in out] == [("ls", '{"path": "/", "all": true}'), ("ls", '{"path": "/tmp"}'),
+                                                    ("cat", '{"path": "/"}'), ("cat", "not json")]
+    assert out[0] is calls[0]
