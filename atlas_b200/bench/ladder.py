@@ -244,6 +244,8 @@ def _inprocess_engine(model_spec: str, device: Optional[str], max_len: int, conc
         mcfg = PRESETS[model_spec.split(":", 1)[1]]()
         if dev.type == "cpu":
             mcfg.dtype = "float32"
+        elif mcfg.dtype == "float32":
+            mcfg.dtype = "bfloat16"          # the GPU kernels take bf16 activations; the tiny presets default to fp32
         mcfg.max_position_embeddings = max(mcfg.max_position_embeddings, max_len + 64)
         model = build_model(mcfg, device=dev).init_random(0, max_pos=max_len + 64)
     else:

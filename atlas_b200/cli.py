@@ -155,6 +155,8 @@ def load_for_serving(args, pctx, device):
             mcfg.dtype = args.dtype
         elif device.type == "cpu":
             mcfg.dtype = "float32"
+        elif mcfg.dtype == "float32":
+            mcfg.dtype = "bfloat16"          # the GPU kernels take bf16 activations; the tiny presets default to fp32
         mcfg.max_position_embeddings = max(mcfg.max_position_embeddings, min(args.max_seq_len, 1 << 17))
         model = build_model(mcfg, pctx, device=device).init_random(args.seed, max_pos=min(args.max_seq_len, mcfg.max_position_embeddings) + 64)
         return model, None
