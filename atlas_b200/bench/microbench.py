@@ -125,25 +125,6 @@ def run(model: str = "llama3-8b", decode_batch: int = 128, ctx: int = 1152, chun
         add(f"gemm_bf16 M={M} N=8192 K={H}", ms, flops=2 * M * 8192 * H, bytes_=2 * (M * H + 8192 * H + M * 8192))
         del w, w2
 
-    if only and "mma_rate" in only:
-        # raw tensor-core issue rate (no memory traffic): tells an instruction-rate bound from an operand-feed bound
-        import ctypes
-        lib = K.lib()
-        lib.atlas_probe_mma_rate.restype = ctypes.c_float
-        lib.atlas_probe_mma_rate.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
-        d = K._dev(torch.zeros(1, device=dev))
-        iters = 2000
-        for kind, name, kbytes in ((0, "bf16", 16), (1, "e4m3", 32)):
-            for n in (64, 128, 256):
-                for grid in (1, K._num_sms[d]):
-                    ms = lib.atlas_probe_mma_rate(kind, n, iters, grid, K._status_ptr[d], K._stream())
-                    per = ms * 1e6 / (iters * 4)
-                    r = {"kernel": f"tcgen05.mma {name} M=128 N={n} grid={grid}", "ns_per_mma": round(per, 1),
-                         "TFLOP/s": round(iters * 4 * 2.0 * 128 * n * kbytes * grid / ms / 1e9, 0)}
-                    rows.append(r)
-                    print(json.dumps(r), flush=True)
-        return rows
-
     if not only or "nvfp4" in only:
         # NVFP4 weight-only GEMM: packed weights (0.5 B) + block scales (1/16 B) per weight are the HBM traffic
         for M in (decode_batch, chunk):

@@ -608,12 +608,7 @@ static int launch_decode_bs(const AttnParams& p, int B, status_t* status, cudaSt
   const int merge_bytes = (64 + 4 * 8 * D) * (int)sizeof(float);
   const int ring_bytes = stages * stage_bytes > merge_bytes ? stages * stage_bytes : merge_bytes;
   const int smem = 512 + kBtSmemEntries * 4 + ring_bytes;
-  static int attr_smem = 0;
-  if (smem > attr_smem) {
-    if (cudaFuncSetAttribute(attn_decode_kernel<D, BS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return -20;
-    attr_smem = smem;
-  }
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(attn_decode_kernel<D, BS>), smem) != cudaSuccess) return -20;
   dim3 grid(p.Hkv, p.num_splits, B);
   if (launch_chain(attn_decode_kernel<D, BS>, grid, dim3(kDecodeThreads), (size_t)smem, st, p, stages, status) != cudaSuccess) return -21;
   if (p.num_splits > 1) {
@@ -718,6 +713,8 @@ extern "C" int atlas_attn_decode_noalloc(const void* q, long long ldq, void* out
                                          unsigned long long* status, void* stream) {
   if (B <= 0) return 0;
   if (num_splits < 1) num_splits = 1;
+  // shape checks first: the size test below is only meaningful for positive, supported Hq / Hkv / D
+  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || block_size <= 0 || block_size % 16 || (D != 64 && D != 128 && D != 256)) return -1;
   const long long need = (long long)B * Hq * num_splits * (D + 2);
   if (need > (long long)ATLAS_NOALLOC_DECODE_SCRATCH_FLOATS) return ATLAS_NOALLOC_ERR_TOO_LARGE;
   int dev = -1;

@@ -488,11 +488,7 @@ extern "C" int atlas_attn_prefill_tc(const void* q, long long ldq, void* out, lo
   p.qk_scale_log2 = scale * k_scale * 1.4426950408889634f; p.v_scale = v_scale;
   p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.total_tokens = total_tokens; p.status = status;
   constexpr int kSmem = 8 * kSub + kTcStages * kStageBytes + 256 + 1024;
-  static bool attr_done = false;
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return -20;
-    attr_done = true;
-  }
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(attn_prefill_tc_kernel), kSmem) != cudaSuccess) return -20;
   dim3 grid(num_tiles, Hkv);
   attn_prefill_tc_kernel<<<grid, kTcThreads, kSmem, reinterpret_cast<cudaStream_t>(stream)>>>(tq, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;

@@ -139,40 +139,82 @@ allreduce_oneshot_kernel(const SymmCtx c, const uint4* __restrict__ in, uint4* _
 }
 
 // Two-shot.  Data area layout per slot: [input copy: n8 vectors][result: n8 vectors].
+//   copy-in   every block stages its sub-range of the PEERS' slices into the local slot (the own slice is read from `in`)
+//   reduce    rank r pulls its slice from every peer with UNROLL independent 16-byte loads per peer in flight per thread,
+//             adds in rank order, writes the sum into `out` locally and pushes it into every peer's result area
+//   gather    after the second barrier the other owners' slices are copied from the local result area to `out`
+// Block b of every rank covers the same sub-range of every slice, so a block only needs block b of each peer (one flag
+// per (phase, block, source)), and the grid covers all SMs.
+template <int UNROLL>
 __global__ void __launch_bounds__(512)
-allreduce_twoshot_kernel(const SymmCtx c, const uint4* __restrict__ in, uint4* __restrict__ out, size_t n8,
+allreduce_twoshot_kernel(const SymmCtx c, const uint4* in, uint4* out, size_t n8,       // `in` may alias `out`
                          size_t slot_bytes, unsigned int* state, status_t* status, long long max_cycles) {
   __shared__ int ok_slot;
   const uint32_t epoch = state[0] + 1;
   const size_t slot_off = (size_t)(epoch & 1u) * slot_bytes;
   const size_t res_off = slot_off + n8 * sizeof(uint4);
-  // every block owns the same sub-range of every rank's slice
   const size_t per_rank = (n8 + c.world - 1) / c.world;
   const size_t per_blk = (per_rank + gridDim.x - 1) / gridDim.x;
+  const size_t step = (size_t)blockDim.x * 4;
   uint4* mine = reinterpret_cast<uint4*>(c.data[c.rank] + slot_off);
   for (int r = 0; r < c.world; ++r) {
+    if (r == c.rank) continue;
     const size_t lo = r * per_rank + per_blk * blockIdx.x;
     const size_t hi = min(min(n8, (r + 1) * per_rank), lo + per_blk);
-    for (size_t i = lo + threadIdx.x; i < hi; i += blockDim.x) mine[i] = in[i];
+    for (size_t i0 = lo + threadIdx.x; i0 < hi; i0 += step) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { const size_t i = i0 + (size_t)u * blockDim.x; if (i < hi) v[u] = in[i]; }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { const size_t i = i0 + (size_t)u * blockDim.x; if (i < hi) mine[i] = v[u]; }
+    }
   }
   bool ok = peer_barrier(c, 0, epoch, status, max_cycles, &ok_slot);
   if (ok) {
     const size_t lo = c.rank * per_rank + per_blk * blockIdx.x;
     const size_t hi = min(min(n8, (size_t)(c.rank + 1) * per_rank), lo + per_blk);
-    for (size_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      sum_over_ranks(c, slot_off, i, acc);
-      const uint4 v = pack_bf16x8(acc);
-      for (int r = 0; r < c.world; ++r) reinterpret_cast<uint4*>(c.data[r] + res_off)[i] = v;
+    for (size_t i0 = lo + threadIdx.x; i0 < hi; i0 += (size_t)blockDim.x * UNROLL) {
+      uint4 v[kMaxRanks][UNROLL];
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r) {
+        if (r >= c.world) break;
+        const uint4* src = r == c.rank ? in : reinterpret_cast<const uint4*>(c.data[r] + slot_off);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const size_t i = i0 + (size_t)u * blockDim.x;
+          if (i < hi) v[r][u] = src[i];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const size_t i = i0 + (size_t)u * blockDim.x;
+        if (i >= hi) break;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+          if (r < c.world) add_bf16x8(acc, v[r][u]);              // rank order: identical bits on every rank
+        const uint4 o = pack_bf16x8(acc);
+        out[i] = o;
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+          if (r < c.world && r != c.rank) reinterpret_cast<uint4*>(c.data[r] + res_off)[i] = o;
+      }
     }
   }
   ok = peer_barrier(c, 1, epoch, status, max_cycles, &ok_slot) && ok;
   if (ok) {
     const uint4* res = reinterpret_cast<const uint4*>(c.data[c.rank] + res_off);
     for (int r = 0; r < c.world; ++r) {
+      if (r == c.rank) continue;
       const size_t lo = r * per_rank + per_blk * blockIdx.x;
       const size_t hi = min(min(n8, (r + 1) * per_rank), lo + per_blk);
-      for (size_t i = lo + threadIdx.x; i < hi; i += blockDim.x) out[i] = res[i];
+      for (size_t i0 = lo + threadIdx.x; i0 < hi; i0 += step) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { const size_t i = i0 + (size_t)u * blockDim.x; if (i < hi) v[u] = __ldcs(res + i); }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { const size_t i = i0 + (size_t)u * blockDim.x; if (i < hi) out[i] = v[u]; }
+      }
     }
   }
   finish_call(state, epoch);
@@ -192,6 +234,8 @@ alltoall_rows_kernel(const SymmCtx c, const uint4* __restrict__ in, const int* _
   const size_t region_bytes = 16 + (size_t)region_rows * row_vecs * sizeof(uint4);
   for (int d = 0; d < c.world; ++d) {
     const int r0 = send_off[d], r1 = send_off[d + 1];
+    // more rows than the destination region holds: recorded as a bounds error (the host raises), the excess is not sent
+    if (r1 - r0 > region_rows && blockIdx.x == 0 && threadIdx.x == 0) report_status(status, kBoundsError, 0x511);
     const int nrows = min(r1 - r0, region_rows);
     uint8_t* region = c.data[d] + slot_off + (size_t)c.rank * region_bytes;
     if (blockIdx.x == 0 && threadIdx.x == 0) *reinterpret_cast<int*>(region) = nrows;
@@ -283,9 +327,12 @@ extern "C" int atlas_allreduce_bf16(int kind, void* const* data, void* const* fl
   if (kind == 0)
     allreduce_oneshot_kernel<<<blocks, 512, 0, st>>>(c, reinterpret_cast<const uint4*>(in), reinterpret_cast<uint4*>(out), n8,
                                                       slot_bytes, state, status, mc);
+  else if (world <= 4)
+    allreduce_twoshot_kernel<4><<<blocks, 512, 0, st>>>(c, reinterpret_cast<const uint4*>(in), reinterpret_cast<uint4*>(out),
+                                                         n8, slot_bytes, state, status, mc);
   else
-    allreduce_twoshot_kernel<<<blocks, 512, 0, st>>>(c, reinterpret_cast<const uint4*>(in), reinterpret_cast<uint4*>(out), n8,
-                                                      slot_bytes, state, status, mc);
+    allreduce_twoshot_kernel<2><<<blocks, 512, 0, st>>>(c, reinterpret_cast<const uint4*>(in), reinterpret_cast<uint4*>(out),
+                                                         n8, slot_bytes, state, status, mc);
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
 }
 

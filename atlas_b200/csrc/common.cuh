@@ -12,7 +12,10 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <cstdlib>
+#include <map>
+#include <mutex>
 #include <stdint.h>
+#include <utility>
 
 #define ATLAS_DEVICE __device__ __forceinline__
 
@@ -259,6 +262,22 @@ ATLAS_DEVICE float warp_max(float v) {
 // A kernel launched the ordinary way is unaffected by either instruction.
 ATLAS_DEVICE void chain_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 ATLAS_DEVICE void chain_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+// The dynamic shared-memory limit of a kernel is a per-device attribute: remember what was set for every
+// (kernel, device) pair so that a process driving several GPUs raises it on each of them.
+inline cudaError_t ensure_dynamic_smem(const void* kern, int bytes) {
+  static std::mutex mu;
+  static std::map<std::pair<const void*, int>, int> done;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  int& have = done[std::make_pair(kern, dev)];
+  if (have >= bytes) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) have = bytes;
+  return e;
+}
 
 inline bool chain_enabled() {
   static const bool on = [] {

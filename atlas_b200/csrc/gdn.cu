@@ -468,19 +468,14 @@ extern "C" int atlas_gdn_chunked(const void* y, long long ldy, const void* a, lo
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   dim3 grid(Hv, B, split);
   auto smem_of = [](int dvc) { return (128 * (dvc + 4) + 2 * kGC * kGLd + kGC * (dvc + 4) + 2 * kGC * kGLdS + 4 * kGC) * 4; };
-  static bool attr_done[3] = {false, false, false};
-  cudaError_t rc = cudaSuccess;
   if (split == 1) {
-    if (!attr_done[0]) { rc = cudaFuncSetAttribute(gdn_chunk_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_of(128)); attr_done[0] = true; }
-    if (rc != cudaSuccess) return -20;
+    if (ensure_dynamic_smem(reinterpret_cast<const void*>(gdn_chunk_kernel<128>), smem_of(128)) != cudaSuccess) return -20;
     gdn_chunk_kernel<128><<<grid, 256, smem_of(128), st>>>(p);
   } else if (split == 2) {
-    if (!attr_done[1]) { rc = cudaFuncSetAttribute(gdn_chunk_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_of(64)); attr_done[1] = true; }
-    if (rc != cudaSuccess) return -20;
+    if (ensure_dynamic_smem(reinterpret_cast<const void*>(gdn_chunk_kernel<64>), smem_of(64)) != cudaSuccess) return -20;
     gdn_chunk_kernel<64><<<grid, 256, smem_of(64), st>>>(p);
   } else {
-    if (!attr_done[2]) { rc = cudaFuncSetAttribute(gdn_chunk_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_of(32)); attr_done[2] = true; }
-    if (rc != cudaSuccess) return -20;
+    if (ensure_dynamic_smem(reinterpret_cast<const void*>(gdn_chunk_kernel<32>), smem_of(32)) != cudaSuccess) return -20;
     gdn_chunk_kernel<32><<<grid, 256, smem_of(32), st>>>(p);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -21;

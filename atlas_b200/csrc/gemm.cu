@@ -690,13 +690,8 @@ static int make_tmap_kmajor(CUtensorMap* out, const void* ptr, uint64_t rows, ui
 template <int BLOCK_N, bool FP8, bool FUSE_AR = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
   using Cfg = GemmCfg<BLOCK_N>;
-  static bool attr_done = false;
   auto kern = gemm_tcgen05_kernel<BLOCK_N, FP8, FUSE_AR>;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-    if (e != cudaSuccess) return -20;
-    attr_done = true;
-  }
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), Cfg::kSmemBytes) != cudaSuccess) return -20;
   return launch_chain_if(p.m_tiles <= 2 && p.tile_expert == nullptr, kern, dim3(grid), dim3(gemm_threads(BLOCK_N, FP8)),
                          (size_t)Cfg::kSmemBytes, st, ta, tb, p) == cudaSuccess ? 0 : -21;
 }

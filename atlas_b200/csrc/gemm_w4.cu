@@ -325,12 +325,8 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 template <int BLOCK_N>
 static int launch_w4(const CUtensorMap& ta, const CUtensorMap& tp, const W4Params& p, int grid, cudaStream_t st) {
   using Cfg = W4Cfg<BLOCK_N>;
-  static bool attr_done = false;
   auto kern = gemm_w4a16_tcgen05_kernel<BLOCK_N>;
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return -20;
-    attr_done = true;
-  }
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), Cfg::kSmemBytes) != cudaSuccess) return -20;
   kern<<<grid, kW4Threads, Cfg::kSmemBytes, st>>>(ta, tp, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }

@@ -41,7 +41,7 @@ int atlas_gated_rmsnorm(const void* x, long long ldx, const void* z, long long l
 int atlas_moe_route(const void* logits, long long ld, int is_bf16, int T, int E, int k, int norm, int sigmoid,
                     float* w_out, int* id_out, void* stream);
 int atlas_moe_align(const int* topk_ids, int T, int k, int e_lo, int E_local, int* slot_of, int* row_token,
-                    int* tile_expert, int* num_tiles, int max_rows, void* stream);
+                    int* tile_expert, int* num_tiles, int max_rows, unsigned long long* status, void* stream);
 int atlas_moe_gather(const void* x, long long ldx, const int* row_token, const int* num_tiles, int max_rows, int H,
                      void* y, void* q, float* scale, long long scale_ld, void* stream);
 int atlas_moe_combine(const void* y, long long ldy, const int* slot_of, const float* topk_w, int T, int k, int H,

@@ -75,35 +75,43 @@ moe_route_kernel(const T* __restrict__ logits, long long ld, int T_, int E, int 
 
 // Single CTA (1024 threads).  counts/offsets live in shared memory (E <= 1024).
 // slot_of[t*k+j] = row in the expert-sorted buffer, or -1 for experts outside [e_lo, e_lo + E_local).
+// The per-expert tile counts are prefix-summed by the whole block (one expert per thread, log-step scan).  A pair whose
+// row would fall beyond max_rows is dropped and recorded as a bounds error in the status word.
 __global__ void __launch_bounds__(1024)
 moe_align_kernel(const int* __restrict__ topk_ids, int n_pairs, int e_lo, int E_local, int* __restrict__ slot_of,
                  int* __restrict__ row_token, int* __restrict__ tile_expert, int* __restrict__ num_tiles,
-                 int max_rows, int k) {
+                 int max_rows, int k, status_t* status) {
   __shared__ int counts[1024];
-  __shared__ int offsets[1025];
+  __shared__ int scan[2][1024];
   __shared__ int cursor[1024];
   const int tid = threadIdx.x;
-  for (int e = tid; e < E_local; e += blockDim.x) { counts[e] = 0; cursor[e] = 0; }
+  counts[tid] = 0;
+  cursor[tid] = 0;
   __syncthreads();
   for (int i = tid; i < n_pairs; i += blockDim.x) {
     const int e = topk_ids[i] - e_lo;
     if (e >= 0 && e < E_local) atomicAdd(&counts[e], 1);
   }
   __syncthreads();
-  if (tid == 0) {
-    int off = 0, tiles = 0;
-    for (int e = 0; e < E_local; ++e) {
-      offsets[e] = off;
-      const int nt = (counts[e] + 127) >> 7;
-      for (int i = 0; i < nt; ++i) tile_expert[tiles + i] = e;
-      tiles += nt;
-      off += nt << 7;
-    }
-    offsets[E_local] = off;
-    *num_tiles = tiles;
-  }
+  const int my_tiles = tid < E_local ? (counts[tid] + 127) >> 7 : 0;
+  int cur = 0;
+  scan[0][tid] = my_tiles;
   __syncthreads();
-  const int total = offsets[E_local];
+  for (int d = 1; d < 1024; d <<= 1) {               // inclusive scan of the tile counts
+    const int v = scan[cur][tid] + (tid >= d ? scan[cur][tid - d] : 0);
+    scan[cur ^ 1][tid] = v;
+    cur ^= 1;
+    __syncthreads();
+  }
+  const int tile0 = scan[cur][tid] - my_tiles;        // exclusive prefix = first tile of this expert
+  const int max_tiles = max_rows >> 7;
+  for (int i = 0; i < my_tiles; ++i)
+    if (tile0 + i < max_tiles) tile_expert[tile0 + i] = tid;
+  if (tid == 1023) {
+    const int tiles = scan[cur][1023];
+    if (tiles > max_tiles) report_status(status, kBoundsError, 0x700);
+    *num_tiles = min(tiles, max_tiles);
+  }
   for (int r = tid; r < max_rows; r += blockDim.x) row_token[r] = -1;
   __syncthreads();
   // Rank inside an expert: pairs are visited in index order by a fixed thread, but threads race on the cursor;
@@ -112,12 +120,12 @@ moe_align_kernel(const int* __restrict__ topk_ids, int n_pairs, int e_lo, int E_
     const int e = topk_ids[i] - e_lo;
     int slot = -1;
     if (e >= 0 && e < E_local) {
-      slot = offsets[e] + atomicAdd(&cursor[e], 1);
-      if (slot < max_rows) row_token[slot] = i / k; else slot = -1;
+      slot = ((scan[cur][e] - ((counts[e] + 127) >> 7)) << 7) + atomicAdd(&cursor[e], 1);
+      if (slot < max_rows) row_token[slot] = i / k;
+      else { slot = -1; report_status(status, kBoundsError, 0x701); }
     }
     slot_of[i] = slot;
   }
-  (void)total;
 }
 
 // xs[row] = x[row_token[row]] ; optional FP8 group quantisation (scales k-group major over sorted rows)
@@ -259,10 +267,10 @@ extern "C" int atlas_moe_route(const void* logits, long long ld, int is_bf16, in
 }
 
 extern "C" int atlas_moe_align(const int* topk_ids, int T, int k, int e_lo, int E_local, int* slot_of, int* row_token,
-                               int* tile_expert, int* num_tiles, int max_rows, void* stream) {
-  if (E_local > 1024) return -1;
+                               int* tile_expert, int* num_tiles, int max_rows, unsigned long long* status, void* stream) {
+  if (E_local > 1024 || max_rows % 128) return -1;
   moe_align_kernel<<<1, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(topk_ids, T * k, e_lo, E_local, slot_of, row_token,
-                                                                          tile_expert, num_tiles, max_rows, k);
+                                                                          tile_expert, num_tiles, max_rows, k, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
 }
 

@@ -15,7 +15,8 @@
 //     16 MiB; e.g. 128 sequences x 32 heads x 7 splits at D = 128).  Larger requests return ATLAS_NOALLOC_ERR_TOO_LARGE
 //     and launch nothing.  Every GPU that loads the library holds the 16 MiB until the process exits.
 //   * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
-//     current) and remembers it.  Make that first call outside any CUDA stream capture.
+//     current) and remembers it.  Make that first call outside any CUDA stream capture, and from one host thread:
+//     the remembered address is written without a lock, so two threads must not race on a device's first call.
 //   * All calls on a device share the one array and it keeps the previous call's contents.  Nothing in it needs
 //     zeroing (each launch rewrites every entry it later reads), but two calls that overlap on the GPU — different
 //     streams, or graphs replayed concurrently — race on it.  Serialise them.

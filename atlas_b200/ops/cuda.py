@@ -104,14 +104,50 @@ def check_status(device: Optional[int] = None, clear: bool = True) -> int:
     return int(lib().atlas_read_status(d, 1 if clear else 0))
 
 
-def scratch(name: str, nbytes: int, device) -> torch.Tensor:
-    """Per-device persistent scratch (grown on demand, never shrunk): stable addresses for CUDA graphs."""
-    key = (device.index if device.index is not None else torch.cuda.current_device(), name)
+_scratch_frozen = False
+
+
+def freeze_scratch() -> None:
+    """Called before the first CUDA-graph capture: from here on a scratch buffer is never replaced, because captured
+    kernels keep the old address."""
+    global _scratch_frozen
+    _scratch_frozen = True
+
+
+def scratch(name: str, nbytes: int, device, zero_new=None) -> torch.Tensor:
+    """Per-device persistent scratch.  A buffer grows on demand until the first CUDA graph has been captured; after
+    that a request larger than the buffer raises instead of handing captured kernels' memory back to the allocator
+    (reserve the worst case up front with :func:`reserve_scratch`)."""
+    key = (device.index if device.index is not None else (torch.cuda.current_device() if device.type == "cuda" else -1), name)
     buf = _scratch.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        if buf is not None and _scratch_frozen:
+            raise KernelError(f"scratch '{name}' holds {buf.numel()} bytes, {nbytes} requested after a CUDA graph was "
+                              "captured: reserve the worst case before capturing")
+        alloc = _scratch_alloc or (lambda n, dev: torch.zeros(n, dtype=torch.uint8, device=dev))
+        buf = alloc(max(nbytes, 1 << 20), device)
         _scratch[key] = buf
     return buf
+
+
+_scratch_alloc = None      # tests replace the allocator to exercise the policy without a GPU
+
+
+def reserve_scratch(name: str, nbytes: int, device) -> torch.Tensor:
+    """Make sure ``name`` holds at least ``nbytes`` (call before any graph capture)."""
+    return scratch(name, nbytes, device)
+
+
+def attention_scratch_bytes(batch_sizes, hq: int, hkv: int, d: int, max_seq_len: int, sms: int) -> Tuple[int, int]:
+    """Worst case of the split-K decode attention partials over the given batch sizes: (bytes of the partial outputs,
+    bytes of the partial (max, sum) pairs)."""
+    po = pml = 0
+    for b in batch_sizes:
+        s = decode_splits(b, hkv, max_seq_len, sms)
+        if s > 1:
+            po = max(po, b * hq * s * d * 4)
+            pml = max(pml, b * hq * s * 2 * 4)
+    return po, pml
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -214,37 +250,6 @@ def gemm_plan(M: int, N: int, K: int, kind: int, sms: int) -> Tuple[int, int]:
     return bn, splits
 
 
-GEMV_MAX_ROWS = 8
-# Off by default: measured on B200 (Llama-3-8B shapes, cold L2) the register-level kernel ties the tcgen05 tile at one row
-# (gate_up 43 vs 48 us, down 30 vs 30 us) and loses at eight (55 vs 51 us, 40 vs 31 us): it is bound by the staging
-# barriers and the fp8 -> f16 conversion pipe, not by HBM.
-_GEMV = os.environ.get("ATLAS_GEMV", "0") not in ("0", "false")
-
-
-def _gemv_fp8(a, b, a_scale, b_scale, out, sms: int, d: int) -> torch.Tensor:
-    """One to eight activation rows: weights stream through the register-level kernel (``csrc/gemv_fp8.cu``) instead of
-    a 128-row tcgen05 tile; K is split so that about four CTAs per SM are in flight."""
-    M, K = a.shape
-    N = b.shape[0]
-    L = lib()
-    if not getattr(L, "_gemv_bound", False):
-        L.atlas_gemv_fp8_block.argtypes = [_vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _i, _vp, _vp, _vp]
-        L._gemv_bound = True
-    if a_scale.stride(0) != 1:
-        a_scale = a_scale.t().contiguous().t()
-    ctas = (N + 63) // 64
-    splits = max(1, min((4 * sms + ctas - 1) // ctas, K // 512, 16))
-    ws = cnt = None
-    if splits > 1:
-        ws = scratch("gemm_ws", _GEMM_WS_BYTES, a.device)
-        cnt = scratch("gemm_counters", 1 << 18, a.device)
-        assert splits * 8 * N * 4 <= _GEMM_WS_BYTES and ctas * 4 <= (1 << 18)
-    _check(L.atlas_gemv_fp8_block(a.data_ptr(), b.data_ptr(), out.data_ptr(), a_scale.data_ptr(), a_scale.stride(1),
-                                  b_scale.data_ptr(), b_scale.shape[1], M, N, K, a.stride(0), b.stride(0), out.stride(0),
-                                  splits, _ptr(ws), _ptr(cnt), _stream()), "gemv_fp8")
-    return out
-
-
 def _gemm(kind: int, a: torch.Tensor, b: torch.Tensor, a_scale, b_scale, out: Optional[torch.Tensor]) -> torch.Tensor:
     M, K = a.shape
     N = b.shape[0]
@@ -254,8 +259,6 @@ def _gemm(kind: int, a: torch.Tensor, b: torch.Tensor, a_scale, b_scale, out: Op
         out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
     assert out.stride(1) == 1 and out.dtype == torch.bfloat16
     sms = _num_sms[d]
-    if kind == 1 and M <= GEMV_MAX_ROWS and K % 128 == 0 and N % 16 == 0 and out.stride(1) == 1 and _GEMV:
-        return _gemv_fp8(a, b, a_scale, b_scale, out, sms, d)
     bn, splits = gemm_plan(M, N, K, kind, sms)
     ws = cnt = None
     if splits > 1:

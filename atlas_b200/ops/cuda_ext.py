@@ -15,7 +15,7 @@ FP8 = torch.float8_e4m3fn
 
 def bind(lib) -> None:
     lib.atlas_moe_route.argtypes = [_vp, _ll, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp]
-    lib.atlas_moe_align.argtypes = [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp]
+    lib.atlas_moe_align.argtypes = [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp]
     lib.atlas_moe_gather.argtypes = [_vp, _ll, _vp, _vp, _i, _i, _vp, _vp, _vp, _ll, _vp]
     lib.atlas_moe_combine.argtypes = [_vp, _ll, _vp, _vp, _i, _i, _i, _vp, _ll, _vp, _ll, _vp]
     lib.atlas_gemm_grouped.argtypes = [_i, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _i, _vp, _vp, _i, _vp, _vp]
@@ -235,7 +235,7 @@ def _moe_local(x, topk_w, topk_ids, experts, e_lo, addend: Optional[torch.Tensor
     tile_expert = torch.empty(max_rows // 128, dtype=torch.int32, device=dev)
     num_tiles = torch.empty(1, dtype=torch.int32, device=dev)
     K._check(lib.atlas_moe_align(topk_ids.data_ptr(), T, k, e_lo, E, slot_of.data_ptr(), row_token.data_ptr(),
-                                 tile_expert.data_ptr(), num_tiles.data_ptr(), max_rows, st), "moe_align")
+                                 tile_expert.data_ptr(), num_tiles.data_ptr(), max_rows, status, st), "moe_align")
 
     def bn_for(n):
         return 128 if n % 128 == 0 else 64

@@ -23,7 +23,7 @@ from .comm import CommBackend, CommError, TorchDistBackend
 
 _vp, _i, _ll, _sz = C.c_void_p, C.c_int, C.c_longlong, C.c_size_t
 ONESHOT_MAX_BYTES = 2 << 20
-P2P_MAX_BYTES = 4 << 20          # above this NCCL's ring/tree is faster than the two-shot kernel (measured at 2 ranks)
+P2P_MAX_BYTES = int(os.environ.get("ATLAS_P2P_MAX_BYTES", str(64 << 20)))   # larger messages go to the bootstrap backend
 FUSED_DECODE_MAX_K = 4096
 FUSED_MAX_OUT_BYTES = 2 << 20    # the fused GEMM+all-reduce pays off for decode-size outputs
 # one-shot form of the fused kernel (partials pushed to every peer) while the pushed bytes per rank stay below this
@@ -52,6 +52,7 @@ class SymmBackend(CommBackend):
                                             _ll, _vp]
         torch.cuda.set_device(device)
         self.dev_index = K._dev(torch.empty(1, device=device))
+        self.sms = K._num_sms[self.dev_index]
         flag_bytes = 2 * 256 * 8 * 4
         self._data = self._alloc(2 * self.slot_bytes)
         self._flags = self._alloc(flag_bytes)
@@ -143,7 +144,8 @@ class SymmBackend(CommBackend):
             return self.base.all_reduce(t)
         self.calls["oneshot" if kind == 0 else "twoshot"] += 1
         K = self.K
-        blocks = max(1, min(self.blocks, nbytes // 16384))       # every block pays one flag exchange per peer
+        # every block pays one flag exchange per peer; the two-shot form wants every SM streaming
+        blocks = max(1, min(self.blocks, nbytes // 16384)) if kind == 0 else max(1, min(self.sms, 256, nbytes // 65536))
         rc = self.lib.atlas_allreduce_bf16(kind, self.data_arr, self.flag_arr, self.rank, self.world_size, t.data_ptr(),
                                            t.data_ptr(), nbytes, self.slot_bytes, self.state.data_ptr(), blocks,
                                            K._status_ptr[self.dev_index], self.wait_cycles, K._stream())
@@ -164,7 +166,7 @@ class SymmBackend(CommBackend):
         self.calls["alltoall"] += 1
         rc = self.lib.atlas_alltoall_rows(self.data_arr, self.flag_arr, self.rank, self.world_size, rows.data_ptr(),
                                           send_off.data_ptr(), out.data_ptr(), recv_off.data_ptr(), row_bytes, region_rows,
-                                          self.slot_bytes, self.state.data_ptr(), self.blocks, K._status_ptr[self.dev_index],
+                                          self.slot_bytes, self.state.data_ptr(), min(self.blocks, self.sms), K._status_ptr[self.dev_index],
                                           self.wait_cycles, K._stream())
         K._check(rc, "alltoall_rows")
         return out, recv_off

@@ -39,6 +39,36 @@ class ModelRunner:
         self.d2h_bytes = 0
         self.graph_replays = 0
         self._pin: Dict[str, torch.Tensor] = {}
+        if self.on_gpu:
+            self._reserve_attention_scratch()
+
+    def graph_batch_sizes(self) -> List[int]:
+        """Every batch size a decode step can be padded to under this configuration."""
+        top = max(self.cfg.max_batch_size, self.cfg.max_num_seqs)
+        sizes = [b for b in _GRAPH_BATCH_SIZES if b <= top]
+        sizes.append(_pad_batch(top))
+        return sorted(set(sizes + list(range(1, min(top, 8) + 1))))
+
+    def _reserve_attention_scratch(self) -> None:
+        """Size the split-K decode attention scratch for the largest case any later step can ask for, so that the
+        buffers captured into CUDA graphs are never replaced."""
+        from .ops import cuda as K
+        mixers = [l.mixer for l in self.model.layers if l.kind == "attention"]
+        if getattr(self.model, "mtp", None) is not None and getattr(self.model.mtp, "layer", None) is not None:
+            mixers.append(self.model.mtp.layer.mixer)
+        if not mixers:
+            return
+        d = K._dev(torch.empty(1, device=self.device))
+        sms = K._num_sms[d]
+        top = max(self.graph_batch_sizes())            # eager mixed steps can carry any number of decode rows up to this
+        sizes = list(range(1, top + 1))
+        po = pml = 0
+        for m in mixers:
+            a, b = K.attention_scratch_bytes(sizes, m.hq, m.hkv, m.d, self.cfg.max_seq_len, sms)
+            po, pml = max(po, a), max(pml, b)
+        if po:
+            K.reserve_scratch("attn_part_o", po, self.device)
+            K.reserve_scratch("attn_part_ml", pml, self.device)
 
     # ------------------------------------------------------------------ batch assembly
     def _stage(self, name: str, data, dtype: torch.dtype) -> torch.Tensor:
@@ -238,6 +268,7 @@ class _DecodeGraph:
             torch.cuda.current_stream().wait_stream(s)
             self.graph = torch.cuda.CUDAGraph()
             from .ops import cuda as K
+            K.freeze_scratch()
             n0 = K.launch_count
             with torch.cuda.graph(self.graph):
                 self.out = r.model.forward(fb, r.cache)

@@ -210,6 +210,14 @@ class Scheduler:
         total = self.pool.blocks_for_tokens(seq.num_tokens + headroom)
         return total - cached_tokens // self.bs
 
+    def _outstanding_prefill_blocks(self) -> int:
+        """Blocks that already-admitted prefills still have to allocate for their prompts.  Admission counts them as
+        taken: a prompt admitted on blocks an earlier, partly allocated prefill needs would leave both stuck."""
+        short = 0
+        for s in self.prefilling:
+            short += max(0, self.pool.blocks_for_tokens(s.num_tokens) - len(s.blocks))
+        return short
+
     def _try_admit(self, seq: Sequence, out: SchedulerOutput) -> bool:
         if self.hybrid and self.state_pool is not None and self.state_pool.num_free == 0:
             return False
@@ -220,6 +228,7 @@ class Scheduler:
             cached = match.num_tokens
         need = self._admission_blocks(seq, cached)
         avail = self.pool.num_free + (self.radix.evictable_blocks() if self.radix is not None else 0)
+        avail -= self._outstanding_prefill_blocks()
         if need > avail:
             if match is not None and match.nodes:
                 self.radix.release(match.nodes)
@@ -308,6 +317,15 @@ class Scheduler:
                 if item is not None:
                     prefill_items.append(item)
                     budget -= item.num_tokens
+
+        # Nothing could be planned although prompts are in flight: every free block is held by partly allocated prefills
+        # and no decode ran that could have picked a victim.  The youngest prefill gives its blocks back (computed full
+        # blocks go to the prefix cache first) so that the oldest one can finish.
+        if not decode_items and not prefill_items and len(self.prefilling) > 1 and budget > 0:
+            self._preempt(self.prefilling[-1], out)
+            item = self._plan_prefill_chunk(self.prefilling[0], budget, out, 0)
+            if item is not None:
+                prefill_items.append(item)
 
         # verify rows (q_len > 1) are not "decodes" for the attention kernels: order pure decodes first
         pure = [d for d in decode_items if d.is_decode]

@@ -15,6 +15,7 @@ from atlas_b200.models import build_model
 from atlas_b200.ops import reference as ref
 from atlas_b200.parallel.comm import CommError, FakeWorld
 from atlas_b200.sampling import RequestRng, SamplingParams
+from atlas_b200.sched import FinishReason, SeqStatus
 from atlas_b200.server.reasoning import ReasoningSplitter, split_reasoning
 from atlas_b200.server.tool_parsers import StreamingToolParser, default_parser_for, get_parser
 from atlas_b200.utils.fault import Fatality, FaultLatch, classify_probe
@@ -220,6 +221,52 @@ def test_preemption_resumes_and_matches_uncontended_run():
     assert got == want
     assert tight.scheduler.num_preemptions > 0
     tight.pool.check_invariants()
+
+
+def test_prefill_budget_not_a_block_multiple_cannot_livelock():
+    """A long and a short prompt share a pool that holds the long one with little to spare and the per-step prefill
+    budget is not a multiple of the block size: the second prompt must not be admitted on blocks the first still
+    needs, and if prefills ever hold every block without one of them being able to advance, one yields."""
+    from atlas_b200.sched import Scheduler
+    from atlas_b200.sched.sequence import Sequence
+    cfg = EngineConfig(block_size=16, num_kv_blocks=200, max_num_seqs=8, max_prefill_tokens=1000, max_seq_len=4096,
+                       admission_watermark_tokens=0)
+    pool = BlockPool(200, 16)
+    sch = Scheduler(cfg, pool)
+    a = Sequence("a", list(range(3180)), SamplingParams(max_tokens=1, ignore_eos=True))
+    b = Sequence("b", list(range(100)), SamplingParams(max_tokens=1, ignore_eos=True))
+    sch.add(a)
+    sch.add(b)
+    idle = 0
+    for _ in range(64):
+        out = sch.schedule()
+        if not out.items:
+            idle += 1
+            assert idle < 3, "scheduler makes no progress"
+            continue
+        idle = 0
+        for it in out.items:
+            sch.on_chunk_computed(it)
+            if it.seq.num_computed >= it.seq.num_tokens:
+                sch.finish(it.seq, FinishReason.LENGTH)
+        if not sch.has_work():
+            break
+    assert not sch.has_work()
+    pool.check_invariants()
+
+    # forced form of the same state: two partly allocated prefills hold every block
+    pool2 = BlockPool(8, 16)
+    sch2 = Scheduler(EngineConfig(block_size=16, num_kv_blocks=8, max_num_seqs=8, max_prefill_tokens=64,
+                                  max_seq_len=4096), pool2)
+    x = Sequence("x", list(range(100)), SamplingParams(max_tokens=1, ignore_eos=True))
+    y = Sequence("y", list(range(100)), SamplingParams(max_tokens=1, ignore_eos=True))
+    for s_ in (x, y):
+        s_.status = SeqStatus.PREFILL
+        s_.blocks = pool2.alloc(4)
+        s_.num_computed = 64
+        sch2.prefilling.append(s_)
+    out = sch2.schedule()
+    assert out.items and out.items[0].seq is x and y in sch2.waiting
 
 
 def test_admission_and_rejection():
@@ -498,3 +545,32 @@ def test_tool_call_dedupe():
     assert [(c.name, c.arguments) for c in out] == [("ls", '{"path": "/", "all": true}'), ("ls", '{"path": "/tmp"}'),
                                                     ("cat", '{"path": "/"}'), ("cat", "not json")]
     assert out[0] is calls[0]
+
+
+# ----------------------------------------------------------------------------------------------------- kernel scratch
+@pytest.mark.parametrize("preset,tp", [("qwen3-30b-a3b", 1), ("llama3-70b", 1), ("llama3-70b", 8)])
+def test_attention_scratch_is_reserved_once_and_never_replaced(preset, tp, monkeypatch):
+    """The split-K decode attention partials live in a persistent buffer whose address CUDA graphs capture.  Sized for
+    the worst padded batch up front, the buffer must be the same object for every batch size, and once a graph
+    exists a larger request must raise instead of reallocating."""
+    from atlas_b200.config import PRESETS
+    from atlas_b200.ops import cuda as K
+    from atlas_b200.runner import _GRAPH_BATCH_SIZES
+    cfg = PRESETS[preset]()
+    hq, hkv, d = cfg.num_attention_heads // tp, max(1, cfg.num_key_value_heads // tp), cfg.head_dim
+    monkeypatch.setattr(K, "_scratch_alloc", lambda n, dev: torch.zeros(n, dtype=torch.uint8))
+    monkeypatch.setattr(K, "_scratch", {})
+    monkeypatch.setattr(K, "_scratch_frozen", False)
+    dev = torch.device("cpu")
+    sizes = [b for b in _GRAPH_BATCH_SIZES if b <= 128]
+    po, pml = K.attention_scratch_bytes(sizes, hq, hkv, d, 8192, 148)
+    assert po > 0
+    K.reserve_scratch("attn_part_o", po, dev)
+    K.freeze_scratch()
+    base = K.scratch("attn_part_o", 1, dev).data_ptr()
+    for b in sizes:
+        s = K.decode_splits(b, hkv, 8192, 148)
+        if s > 1:
+            assert K.scratch("attn_part_o", b * hq * s * d * 4, dev).data_ptr() == base
+    with pytest.raises(K.KernelError):
+        K.scratch("attn_part_o", max(po, 1 << 20) + 1, dev)

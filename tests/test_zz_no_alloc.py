@@ -14,7 +14,8 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def test_noalloc_decode_matches_regular_entry_twice():
+@pytest.mark.parametrize("D,splits", [(128, 5), (64, 3), (128, 1)])
+def test_noalloc_decode_matches_regular_entry_twice(D, splits):
     from atlas_b200.models.batch import ForwardBatch
     from atlas_b200.ops import cuda as K
     K.load()
@@ -24,7 +25,7 @@ def test_noalloc_decode_matches_regular_entry_twice():
     fn.argtypes = [vp, ll, vp, ll, vp, vp, vp, i, vp, vp, i, f, f, f, i, i, i, i, i, i, vp, vp]
     fn.restype = i
     dev = "cuda"
-    Hq, Hkv, D, bs = 8, 2, 128, 16
+    Hq, Hkv, bs = 8, 2, 16
     for round_, ctxs in enumerate(([700, 33, 1500], [90, 2047, 640])):
         torch.manual_seed(40 + round_)
         B = len(ctxs)
@@ -43,7 +44,6 @@ def test_noalloc_decode_matches_regular_entry_twice():
         want = K.paged_attention(q, kc, vc, fb, D ** -0.5, 0.7, 1.3, None)       # regular entry (allocates its scratch)
         d = K._dev(q)
         out = torch.empty_like(want)
-        splits = 5
         torch.cuda.synchronize()
         rc = fn(q.data_ptr(), q.stride(0), out.data_ptr(), Hq * D, kc.data_ptr(), vc.data_ptr(), fb.block_tables.data_ptr(),
                 fb.block_tables.stride(0), fb.seq_lens.data_ptr(), fb.query_start_loc.data_ptr(), B, D ** -0.5, 0.7, 1.3,
@@ -57,3 +57,8 @@ def test_noalloc_decode_matches_regular_entry_twice():
             fb.block_tables.stride(0), fb.seq_lens.data_ptr(), fb.query_start_loc.data_ptr(), 4096, D ** -0.5, 0.7, 1.3,
             Hq, Hkv, D, bs, 0, 64, K._status_ptr[d], torch.cuda.current_stream().cuda_stream)
     assert rc == -100
+    # unsupported shapes are refused before the size test
+    rc = fn(q.data_ptr(), q.stride(0), out.data_ptr(), Hq * D, kc.data_ptr(), vc.data_ptr(), fb.block_tables.data_ptr(),
+            fb.block_tables.stride(0), fb.seq_lens.data_ptr(), fb.query_start_loc.data_ptr(), B, D ** -0.5, 0.7, 1.3,
+            0, Hkv, D, bs, 0, 2, K._status_ptr[d], torch.cuda.current_stream().cuda_stream)
+    assert rc == -1
