@@ -26,11 +26,12 @@ namespace atlas {
 constexpr int kBlockM = 128;
 constexpr int kRowBytes = 128;            // one swizzle row = one BLOCK_K slice
 constexpr int kCtrlWarps = 2;            // warp 0: TMA producer, warp 1: MMA issuer
-// Epilogue warps: eight (two per TMEM lane quadrant) except for the 256-wide FP8 tile, whose per-k-group fold keeps the
-// whole accumulator in registers: sixteen warps of 64 columns each stay under the register budget where eight warps of
-// 128 columns spill.
+constexpr int kRowsPerReadyFlag = 8;     // granularity of the "rows have arrived" flags of a gathered A operand
+// Epilogue warps: eight (two per TMEM lane quadrant) or sixteen.  The FP8 path keeps the whole accumulator of a tile in
+// registers across its per-k-group folds: 128 x 256 / (32 x warps) floats per thread, i.e. 128 with eight warps (fits
+// the 200-register budget of a 320-thread CTA) and 64 with sixteen (112-register budget of a 576-thread CTA).
 __host__ __device__ constexpr int epi_warps(int block_n, bool fp8) { return (fp8 && block_n == 256) ? 16 : 8; }
-__host__ __device__ constexpr int gemm_threads(int block_n, bool fp8) { return 32 * (kCtrlWarps + epi_warps(block_n, fp8)); }
+__host__ __device__ constexpr int gemm_threads_w(int warps) { return 32 * (kCtrlWarps + warps); }
 
 template <int BLOCK_N>
 struct GemmCfg {
@@ -76,7 +77,13 @@ struct GemmParams {
   size_t ar_result_off;         // byte offset of the [M, N] bf16 result inside the area
   int ar_rank, ar_world, ar_max_tiles;
   int prefetch_b;               // k-slices of B to request into L2 ahead of the tile ring (0 = off)
-  int ar_mode;                  // 0 = two-shot (owner reduces, result pushed back), 1 = one-shot (partials pushed to all)
+  int ar_mode;                  // 0 = two-shot (owner reduces, result pushed back), 1 = one-shot (partials pushed to all),
+                                // 2 = reduce-scatter (partials pushed to the row block's owner, nothing comes back)
+  int rs_tiles_per_rank;        // mode 2: m-tiles (128-row blocks) owned by each rank, in rank order
+  // gathered A operand (sequence-parallel all-gather -> GEMM): rows of A are written into this rank's memory by their
+  // owners; one flag per group of kRowsPerReadyFlag rows carries the epoch of the gather that filled it
+  const uint32_t* a_ready;
+  const unsigned int* a_ready_epoch;
   size_t ar_parity_stride;      // one-shot: bytes between the two epoch-parity halves of the partial area
   const int* tile_expert;       // nullptr = plain GEMM
   const int* num_m_tiles_ptr;   // device-side tile count (the host cannot know it)
@@ -117,13 +124,29 @@ ATLAS_DEVICE bool wait_flag_eq(const uint32_t* p, uint32_t want, status_t* statu
 //   drain        a rank leaves the kernel once it has seen final_flag of every tile, so the next kernel in the stream
 //                finds the whole [M, N] result in its own memory.
 // Transfers therefore overlap the math tile by tile; flags carry the call's epoch, so nothing is ever reset.
-template <int BLOCK_N, bool FP8, bool FUSE_AR = false>
-__global__ void __launch_bounds__(gemm_threads(BLOCK_N, FP8), 1)
+// acc{0,1} += v{0,1} * s on the packed fp32 pipe (one instruction for two lanes of the accumulator)
+ATLAS_DEVICE void ffma2(float& a0, float& a1, uint32_t v0, uint32_t v1, uint64_t s2) {
+  asm("{\n\t.reg .b64 a, v;\n\t"
+      "mov.b64 a, {%0, %1};\n\t"
+      "mov.b64 v, {%2, %3};\n\t"
+      "fma.rn.f32x2 a, v, %4, a;\n\t"
+      "mov.b64 {%0, %1}, a;\n\t}\n"
+      : "+f"(a0), "+f"(a1)
+      : "r"(v0), "r"(v1), "l"(s2));
+}
+ATLAS_DEVICE uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+
+template <int BLOCK_N, bool FP8, bool FUSE_AR = false, int EPW = epi_warps(BLOCK_N, FP8)>
+__global__ void __launch_bounds__(gemm_threads_w(EPW), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmParams p) {
   using Cfg = GemmCfg<BLOCK_N>;
   constexpr int kStages = Cfg::kStages;
-  constexpr int kEpiWarps = epi_warps(BLOCK_N, FP8);
+  constexpr int kEpiWarps = EPW;
   constexpr int kParts = kEpiWarps / 4;                 // column slices of a tile, one per warp of a lane quadrant
   constexpr int HALF = BLOCK_N / kParts;                // columns per epilogue thread
   constexpr int kElemsPerRow = FP8 ? 128 : 64;          // BLOCK_K in elements
@@ -209,11 +232,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      uint32_t stage = 0, phase = 0, sc_slot = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-        const int m_tile = item % m_tiles;
+    // The whole warp walks the work items; lane 0 issues the copies.  When A is a gathered operand the warp first polls
+    // the arrival flags of the tile's row groups (one flag per lane) and remembers which m-tiles it has seen complete.
+    uint32_t stage = 0, phase = 0, sc_slot = 0;
+    bool ok = true;
+    uint32_t seen[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};         // m-tiles known to be complete (up to 256)
+    const uint32_t want_epoch = p.a_ready ? *p.a_ready_epoch : 0u;
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      const int m_tile = item % m_tiles;
+      if (p.a_ready != nullptr && !((m_tile < 256) && (seen[m_tile >> 5] >> (m_tile & 31) & 1u))) {
+        constexpr int kGroups = kBlockM / kRowsPerReadyFlag;      // 16 flags per m-tile
+        const int row = m_tile * kBlockM + lane * kRowsPerReadyFlag;
+        bool mine = true;
+        if (lane < kGroups && row < p.M)
+          mine = wait_flag_eq(p.a_ready + (size_t)m_tile * kGroups + lane, want_epoch, p.status, 0x620, p.ar_max_cycles);
+        ok = __all_sync(0xffffffffu, mine);
+        if (!ok) { if (lane == 0) *abort_flag = 1u; break; }
+        if (m_tile < 256) seen[m_tile >> 5] |= 1u << (m_tile & 31);
+        // the rows were written by other GPUs' ordinary stores and are read below by the copy engine
+        asm volatile("fence.proxy.async;\n" ::: "memory");
+      }
+      if (lane == 0) {
         const int rest = item / m_tiles;
         const int n_tile = rest % p.n_tiles;
         const int split = rest / p.n_tiles;
@@ -236,10 +275,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
-      if (!ok) {
-        // give copies that are already in flight time to land before the CTA's shared memory goes away
-        for (int i = 0; i < 64; ++i) __nanosleep(1000);
-      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    }
+    if (!ok && lane == 0) {
+      // give copies that are already in flight time to land before the CTA's shared memory goes away
+      for (int i = 0; i < 64; ++i) __nanosleep(1000);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
@@ -337,12 +377,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           const uint32_t taddr = tmem_base + t_lane + buf * BLOCK_N + half * HALF;
           // Pull the partial tile into registers with back-to-back tcgen05.ld, hand the TMEM buffer back to the
           // MMA issuer as soon as the loads have landed, and only then fold the scales in.
-          constexpr int kChunk = (HALF < 64 || kEpiWarps > 8) ? 32 : 64;
+          // Chunks of the tile row go TMEM -> registers -> packed FMAs; the TMEM buffer returns to the MMA issuer as
+          // soon as the last chunk's load has landed.  The chunk width is what the register budget leaves next to the
+          // accumulators: 64 columns for a 64-column thread, 32 for 128 columns, 16 under the 112-register budget.
+          constexpr int kChunk = kEpiWarps > 8 ? 16 : (HALF > 64 ? 32 : 64);
+          const uint64_t s2 = pack_f32x2(s, s);
 #pragma unroll
           for (int c0 = 0; c0 < HALF; c0 += kChunk) {
-            uint32_t r[kChunk / 32][32];
+            uint32_t r[kChunk];
+            if constexpr (kChunk == 16) {
+              tmem_ld_32x32b_x16(taddr + c0, r);
+            } else {
 #pragma unroll
-            for (int c = 0; c < kChunk / 32; ++c) tmem_ld_32x32b_x32(taddr + c0 + c * 32, r[c]);
+              for (int c = 0; c < kChunk / 32; ++c) tmem_ld_32x32b_x32(taddr + c0 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+            }
             tmem_ld_wait();
             if (c0 + kChunk >= HALF) {
               tc_fence_before();
@@ -350,10 +398,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               if (lane == 0) mbar_arrive(&acc_empty[buf]);
             }
 #pragma unroll
-            for (int c = 0; c < kChunk / 32; ++c)
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                acc[c0 + c * 32 + i] = fmaf(__uint_as_float(r[c][i]), s, acc[c0 + c * 32 + i]);
+            for (int i = 0; i < kChunk; i += 2) ffma2(acc[c0 + i], acc[c0 + i + 1], r[i], r[i + 1], s2);
           }
           ++acc_iter;
         }
@@ -491,6 +536,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             }
           }
         }
+      } else if (FUSE_AR && p.ar_mode == 2) {
+        // ---- reduce-scatter: the bf16 partial goes into the row block owner's area [source rank][local row][N]
+        // (row-major, so the owner's reduce + norm kernel streams whole rows); one flag per (tile, source) follows.
+        store_now = false;
+        const int owner = min(m_tile / p.rs_tiles_per_rank, p.ar_world - 1);
+        const int local_tile = m_tile - owner * p.rs_tiles_per_rank;
+        if (ok && m < M_rows) {
+          __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.ar_data[owner] + (size_t)p.ar_rank * p.ar_part_src_stride) +
+                                ((size_t)local_tile * kBlockM + row_in_tile) * p.N;
+#pragma unroll
+          for (int j = 0; j < HALF; j += 8) {
+            const int n = n_base + j;
+            if (n + 8 <= p.N) {
+              uint4 v;
+              v.x = pack_bf16x2(acc[j + 0], acc[j + 1]);
+              v.y = pack_bf16x2(acc[j + 2], acc[j + 3]);
+              v.z = pack_bf16x2(acc[j + 4], acc[j + 5]);
+              v.w = pack_bf16x2(acc[j + 6], acc[j + 7]);
+              *reinterpret_cast<uint4*>(drow + n) = v;
+            }
+          }
+        }
+        asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
+        if (epi_tid == 0)
+          st_release_sys_u32(p.ar_flags[owner] + ((size_t)local_tile * p.n_tiles + n_tile) * 8 + p.ar_rank, ar_epoch);
       } else if (FUSE_AR) {
         store_now = false;
         const int tile_id = n_tile * m_tiles + m_tile;
@@ -534,8 +604,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
       }
     }
-    if (FUSE_AR && p.ar_mode == 1) {
-      // nothing to drain: partial areas alternate with the epoch parity, and a rank can only be one call ahead
+    if (FUSE_AR && p.ar_mode != 0) {
+      // nothing to drain.  One-shot: partial areas alternate with the epoch parity, and a rank can only be one call
+      // ahead.  Reduce-scatter: the owner's reduce kernel waits on the tile flags, and a peer cannot reach its next
+      // reduce-scatter GEMM before it has consumed every row this rank gathers from those partials.
       asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
       if (epi_tid == 0) {
         __threadfence();
@@ -687,12 +759,12 @@ static int make_tmap_kmajor(CUtensorMap* out, const void* ptr, uint64_t rows, ui
   return make_tmap_2d(out, ptr, rows, cols, ld, box_rows, esize, 128u, true);
 }
 
-template <int BLOCK_N, bool FP8, bool FUSE_AR = false>
+template <int BLOCK_N, bool FP8, bool FUSE_AR = false, int EPW = epi_warps(BLOCK_N, FP8)>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
   using Cfg = GemmCfg<BLOCK_N>;
-  auto kern = gemm_tcgen05_kernel<BLOCK_N, FP8, FUSE_AR>;
+  auto kern = gemm_tcgen05_kernel<BLOCK_N, FP8, FUSE_AR, EPW>;
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), Cfg::kSmemBytes) != cudaSuccess) return -20;
-  return launch_chain_if(p.m_tiles <= 2 && p.tile_expert == nullptr, kern, dim3(grid), dim3(gemm_threads(BLOCK_N, FP8)),
+  return launch_chain_if(p.m_tiles <= 2 && p.tile_expert == nullptr, kern, dim3(grid), dim3(gemm_threads_w(EPW)),
                          (size_t)Cfg::kSmemBytes, st, ta, tb, p) == cudaSuccess ? 0 : -21;
 }
 
@@ -706,6 +778,15 @@ static int prefetch_depth() {
   return d;
 }
 
+// Epilogue warps of the 256-wide FP8 tile (ATLAS_GEMM_EPW256 = 8 or 16)
+static int wide_fp8_epilogue_warps() {
+  static const int w = [] {
+    const char* e = getenv("ATLAS_GEMM_EPW256");
+    return (e && atoi(e) == 8) ? 8 : 16;
+  }();
+  return w;
+}
+
 }  // namespace atlas
 
 using namespace atlas;
@@ -714,10 +795,11 @@ using namespace atlas;
 // (scale(m, g) = a_scale[g * sa_k + m]) with sa_k a multiple of 4 and at least m_tiles*128, so that a 128-row
 // slice is one aligned bulk copy.  With splits > 1, `workspace` needs splits*m_tiles*n_tiles*128*block_n floats and
 // `counters` m_tiles*n_tiles zero-initialised ints.  Returns 0 or a negative error code.
-extern "C" int atlas_gemm(int kind, const void* A, const void* B, void* C, const float* a_scale, long long sa_m,
-                          long long sa_k, const float* b_scale, int b_scale_ld, int M, int N, int K, long long lda,
-                          long long ldb, long long ldc, int block_n, int splits, float* workspace, int* counters,
-                          int num_sms, unsigned long long* status, void* stream) {
+static int gemm_impl(int kind, const void* A, const void* B, void* C, const float* a_scale, long long sa_m,
+                     long long sa_k, const float* b_scale, int b_scale_ld, int M, int N, int K, long long lda,
+                     long long ldb, long long ldc, int block_n, int splits, float* workspace, int* counters,
+                     int num_sms, unsigned long long* status, void* stream, const uint32_t* a_ready,
+                     const unsigned int* a_ready_epoch, long long max_cycles) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const uint32_t esize = kind == 1 ? 1 : 2;
   const int elems_per_row = 128 / esize;
@@ -730,11 +812,13 @@ extern "C" int atlas_gemm(int kind, const void* A, const void* B, void* C, const
   if (rc) return rc;
   rc = make_tmap_kmajor(&tb, B, N, K, ldb, block_n, esize);
   if (rc) return rc;
-  GemmParams p;
+  GemmParams p = {};
   p.C = C; p.a_scale = a_scale; p.b_scale = b_scale; p.workspace = workspace; p.counters = counters;
   p.status = status; p.ldc = ldc; p.sa_k = sa_k; p.M = M; p.N = N; p.K = K;
   p.tile_expert = nullptr; p.num_m_tiles_ptr = nullptr; p.expert_n = 0; p.b_scale_expert_stride = 0;
   p.ar_state = nullptr; p.ar_world = 1; p.ar_rank = 0; p.ar_mode = 0; p.ar_parity_stride = 0; p.prefetch_b = 0;
+  p.rs_tiles_per_rank = 1; p.a_ready = a_ready; p.a_ready_epoch = a_ready_epoch;
+  p.ar_max_cycles = max_cycles > 0 ? max_cycles : kMbarMaxCycles;
   p.k_blocks = (K + elems_per_row - 1) / elems_per_row;
   if (splits < 1) splits = 1;
   if (splits > p.k_blocks) splits = p.k_blocks;
@@ -757,11 +841,34 @@ extern "C" int atlas_gemm(int kind, const void* A, const void* B, void* C, const
   if (kind == 1) {
     if (block_n == 64) return launch_gemm<64, true>(ta, tb, p, grid, st);
     if (block_n == 128) return launch_gemm<128, true>(ta, tb, p, grid, st);
+    if (wide_fp8_epilogue_warps() == 8) return launch_gemm<256, true, false, 8>(ta, tb, p, grid, st);
     return launch_gemm<256, true>(ta, tb, p, grid, st);
   }
   if (block_n == 64) return launch_gemm<64, false>(ta, tb, p, grid, st);
   if (block_n == 128) return launch_gemm<128, false>(ta, tb, p, grid, st);
   return launch_gemm<256, false>(ta, tb, p, grid, st);
+}
+
+extern "C" int atlas_gemm(int kind, const void* A, const void* B, void* C, const float* a_scale, long long sa_m,
+                          long long sa_k, const float* b_scale, int b_scale_ld, int M, int N, int K, long long lda,
+                          long long ldb, long long ldc, int block_n, int splits, float* workspace, int* counters,
+                          int num_sms, unsigned long long* status, void* stream) {
+  return gemm_impl(kind, A, B, C, a_scale, sa_m, sa_k, b_scale, b_scale_ld, M, N, K, lda, ldb, ldc, block_n, splits, workspace,
+                   counters, num_sms, status, stream, nullptr, nullptr, 0);
+}
+
+// All-gather -> GEMM: the rows of A (and their scales) are written into this rank's memory by the ranks that own them;
+// `a_ready` holds one flag per 8 rows and a row group is complete once its flag has reached *a_ready_epoch.  The TMA
+// producer polls the flags of a tile's rows before it loads the tile, so the GEMM starts on the rows that are already
+// there and the gather overlaps the math.  Everything else is atlas_gemm.
+extern "C" int atlas_gemm_gathered(int kind, const void* A, const void* B, void* C, const float* a_scale, long long sa_m,
+                                   long long sa_k, const float* b_scale, int b_scale_ld, int M, int N, int K, long long lda,
+                                   long long ldb, long long ldc, int block_n, int splits, float* workspace, int* counters,
+                                   int num_sms, unsigned long long* status, void* stream, const void* a_ready,
+                                   const unsigned int* a_ready_epoch, long long max_cycles) {
+  if (!a_ready || !a_ready_epoch) return -30;
+  return gemm_impl(kind, A, B, C, a_scale, sa_m, sa_k, b_scale, b_scale_ld, M, N, K, lda, ldb, ldc, block_n, splits, workspace,
+                   counters, num_sms, status, stream, reinterpret_cast<const uint32_t*>(a_ready), a_ready_epoch, max_cycles);
 }
 
 // Grouped (MoE) GEMM: C[r, :] = A[r, :] * B[e(r)]^T for expert-sorted rows.  `A` has `max_rows` rows (a multiple of
@@ -785,7 +892,7 @@ extern "C" int atlas_gemm_grouped(int kind, const void* A, const void* B, void* 
   if (rc) return rc;
   rc = make_tmap_kmajor(&tb, B, (uint64_t)E * N, K, ldb, block_n, esize);
   if (rc) return rc;
-  GemmParams p;
+  GemmParams p = {};
   p.C = C; p.a_scale = a_scale; p.b_scale = b_scale; p.workspace = nullptr; p.counters = nullptr;
   p.status = status; p.ldc = ldc; p.sa_k = sa_k; p.M = max_rows; p.N = N; p.K = K;
   p.k_blocks = (K + elems_per_row - 1) / elems_per_row;
@@ -796,6 +903,7 @@ extern "C" int atlas_gemm_grouped(int kind, const void* A, const void* B, void* 
   p.vec_ok = ((ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
   p.tile_expert = tile_expert; p.num_m_tiles_ptr = num_m_tiles; p.expert_n = N;
   p.ar_state = nullptr; p.ar_world = 1; p.ar_rank = 0; p.ar_mode = 0; p.ar_parity_stride = 0; p.prefetch_b = 0;
+  p.rs_tiles_per_rank = 1; p.a_ready = nullptr; p.a_ready_epoch = nullptr; p.ar_max_cycles = kMbarMaxCycles;
   p.b_scale_expert_stride = (long long)((N + 127) / 128) * p.k_blocks;
   if (kind == 1) {
     if ((sa_k % 4) || sa_k < max_rows || (reinterpret_cast<uintptr_t>(a_scale) & 15)) return -6;
@@ -843,7 +951,7 @@ extern "C" int atlas_gemm_allreduce(int kind, const void* A, const void* B, cons
   if (rc) return rc;
   rc = make_tmap_kmajor(&tb, B, N, K, ldb, block_n, esize);
   if (rc) return rc;
-  GemmParams p;
+  GemmParams p = {};
   p.C = nullptr; p.a_scale = a_scale; p.b_scale = b_scale; p.workspace = nullptr; p.counters = nullptr;
   p.status = status; p.ldc = N; p.sa_k = sa_k; p.M = M; p.N = N; p.K = K;
   p.k_blocks = (K + elems_per_row - 1) / elems_per_row;
@@ -862,6 +970,7 @@ extern "C" int atlas_gemm_allreduce(int kind, const void* A, const void* B, cons
   p.b_scale_ld = b_scale_ld;
   p.vec_ok = mode == 1 ? (((ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0) : 1;
   p.tile_expert = nullptr; p.num_m_tiles_ptr = nullptr; p.expert_n = 0; p.b_scale_expert_stride = 0;
+  p.rs_tiles_per_rank = 1; p.a_ready = nullptr; p.a_ready_epoch = nullptr;
   if (kind == 1) {
     if ((sa_k % 4) || sa_k < (long long)p.m_tiles * kBlockM || (reinterpret_cast<uintptr_t>(a_scale) & 15)) return -6;
     if (p.kb_per_split > 512) return -8;
@@ -895,6 +1004,70 @@ extern "C" int atlas_gemm_allreduce(int kind, const void* A, const void* B, cons
   const long long items = (long long)tiles * p.splits;
   int grid = (int)(items < num_sms ? items : num_sms);
   p.prefetch_b = p.m_tiles <= 2 ? prefetch_depth() : 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (kind == 1) {
+    if (block_n == 64) return launch_gemm<64, true, true>(ta, tb, p, grid, st);
+    return launch_gemm<128, true, true>(ta, tb, p, grid, st);
+  }
+  if (block_n == 64) return launch_gemm<64, false, true>(ta, tb, p, grid, st);
+  return launch_gemm<128, false, true>(ta, tb, p, grid, st);
+}
+
+// Row-parallel GEMM fused with the reduce-scatter of its output (sequence-parallel tensor parallelism).  Rank r owns the
+// row blocks (m-tiles of 128 rows) [r * tiles_per_rank, (r + 1) * tiles_per_rank).  Every rank computes its K-shard's
+// partial of the whole [M, N] output; the epilogue stores each bf16 partial tile into the OWNER's area with peer stores,
+//   data[owner] + rank * part_src_stride + ((m_tile - owner * tiles_per_rank) * 128 + row) * N * 2,
+// and raises flags[owner][((m_tile - owner * tiles_per_rank) * n_tiles + n_tile) * 8 + rank] to the call's epoch
+// (state[0] + 1; state[0] holds that epoch once the kernel has finished).  Nothing is reduced here and nothing comes
+// back: atlas_sp_reduce_norm_gather on the owner sums the partials.  `flag_words` is the capacity of a flag area.
+extern "C" int atlas_gemm_reduce_scatter(int kind, const void* A, const void* B, const float* a_scale, long long sa_k,
+                                         const float* b_scale, int b_scale_ld, int M, int N, int K, long long lda,
+                                         long long ldb, int block_n, void* const* data, void* const* flags, int rank,
+                                         int world, unsigned int* state, size_t part_src_stride, int tiles_per_rank,
+                                         size_t flag_words, int num_sms, long long max_cycles, unsigned long long* status,
+                                         void* stream, int* n_tiles_out) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const uint32_t esize = kind == 1 ? 1 : 2;
+  const int elems_per_row = 128 / esize;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -1;
+  if ((lda * esize) % 16 || (ldb * esize) % 16) return -2;
+  if (kind == 1 && (K % 128)) return -3;
+  if (block_n != 64 && block_n != 128) return -4;
+  if (N % 8 || world < 1 || world > 8 || tiles_per_rank < 1) return -5;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_kmajor(&ta, A, M, K, lda, kBlockM, esize);
+  if (rc) return rc;
+  rc = make_tmap_kmajor(&tb, B, N, K, ldb, block_n, esize);
+  if (rc) return rc;
+  GemmParams p = {};
+  p.C = nullptr; p.a_scale = a_scale; p.b_scale = b_scale; p.workspace = nullptr; p.counters = nullptr;
+  p.status = status; p.ldc = N; p.sa_k = sa_k; p.M = M; p.N = N; p.K = K;
+  p.k_blocks = (K + elems_per_row - 1) / elems_per_row;
+  p.splits = 1; p.kb_per_split = p.k_blocks;
+  p.m_tiles = (M + kBlockM - 1) / kBlockM;
+  p.n_tiles = (N + block_n - 1) / block_n;
+  if (n_tiles_out) *n_tiles_out = p.n_tiles;
+  p.b_scale_ld = b_scale_ld; p.vec_ok = 1;
+  p.tile_expert = nullptr; p.num_m_tiles_ptr = nullptr; p.expert_n = 0; p.b_scale_expert_stride = 0;
+  p.a_ready = nullptr; p.a_ready_epoch = nullptr;
+  if (kind == 1) {
+    if ((sa_k % 4) || sa_k < (long long)p.m_tiles * kBlockM || (reinterpret_cast<uintptr_t>(a_scale) & 15)) return -6;
+    if (p.kb_per_split > 512) return -8;
+  }
+  if ((long long)tiles_per_rank * world < p.m_tiles) return -11;                        // every row block needs an owner
+  if ((size_t)tiles_per_rank * p.n_tiles * 8 > flag_words) return -12;
+  if ((size_t)tiles_per_rank * kBlockM * N * 2 > part_src_stride) return -12;
+  p.ar_mode = 2; p.rs_tiles_per_rank = tiles_per_rank;
+  p.ar_parity_stride = 0; p.ar_part_src_stride = part_src_stride; p.ar_result_off = 0;
+  for (int i = 0; i < 8; ++i) {
+    p.ar_data[i] = i < world ? reinterpret_cast<uint8_t*>(data[i]) : nullptr;
+    p.ar_flags[i] = i < world ? reinterpret_cast<uint32_t*>(flags[i]) : nullptr;
+  }
+  p.ar_state = state; p.ar_rank = rank; p.ar_world = world; p.ar_max_tiles = 0;
+  p.ar_max_cycles = max_cycles > 0 ? max_cycles : kMbarMaxCycles;
+  const long long items = (long long)p.m_tiles * p.n_tiles;
+  int grid = (int)(items < num_sms ? items : num_sms);
+  p.prefetch_b = 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (kind == 1) {
     if (block_n == 64) return launch_gemm<64, true, true>(ta, tb, p, grid, st);

@@ -76,6 +76,8 @@ class LLMEngine:
                                             disk_gb=self.cfg.disk_swap_gb, disk_dir=self.cfg.disk_swap_path)
         self.scheduler = Scheduler(self.cfg, self.pool, self.radix, self.state_pool, self.hybrid, host_tier=self.host_tier)
         self.sampler = Sampler(self.mcfg.vocab_size, self.mcfg.eos_ids())
+        # largest step this engine can build: sizes the sequence-parallel peer-memory area once
+        model.sp_capacity_hint = self.cfg.max_prefill_tokens + self.cfg.max_num_seqs * (1 + max(0, self.cfg.num_drafts))
         self.runner = ModelRunner(model, self.cache, self.cfg)
         self.spec = SpecController(self, self.cfg) if (self.cfg.speculative and model.mtp is not None
                                                          and self.cfg.num_drafts > 0) else None

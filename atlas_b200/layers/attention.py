@@ -79,6 +79,17 @@ class Attention:
     # ------------------------------------------------------------------ forward
     def forward(self, act: Act, batch, kv: Tuple[torch.Tensor, torch.Tensor, float, float],
                 rope_cache: torch.Tensor) -> torch.Tensor:
+        out = self.mix(act, batch, kv, rope_cache)
+        y = self.pctx.row_parallel_linear(out, self.o)
+        if self.lora is not None and batch.adapter_rows is not None:
+            if y._base is not None:
+                y = y.clone()               # the fused path returns a view of its reduction area
+            add_delta(y, self.lora, f"layers.{self.layer_idx}.self_attn.o_proj", out, batch)
+        return y
+
+    def mix(self, act: Act, batch, kv: Tuple[torch.Tensor, torch.Tensor, float, float],
+            rope_cache: torch.Tensor) -> torch.Tensor:
+        """Everything before the output projection: this rank's heads' attention output ``[T, hq * d]``."""
         cfg = self.cfg
         k_cache, v_cache, k_scale, v_scale = kv
         qkv = ops.linear(act, self.qkv)
@@ -100,9 +111,4 @@ class Attention:
         if self.gated:
             gate = qkv[:, nq + 2 * nkv:]
             out = (out.float() * torch.sigmoid(gate.float())).to(out.dtype)
-        y = self.pctx.row_parallel_linear(out, self.o)
-        if self.lora is not None and batch.adapter_rows is not None:
-            if y._base is not None:
-                y = y.clone()               # the fused path returns a view of its reduction area
-            add_delta(y, self.lora, f"layers.{self.layer_idx}.self_attn.o_proj", out, batch)
-        return y
+        return out

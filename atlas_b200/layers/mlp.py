@@ -40,6 +40,10 @@ class DenseMLP:
                   randn_weight(gen, self.inter, h, std, dtype, device),
                   randn_weight(gen, h, self.inter, std, dtype, device))
 
+    def hidden_act(self, act: Act) -> Act:
+        """gate|up GEMM + SiLU * mul: the input of the down projection (no adapters)."""
+        return ops.silu_mul_act(ops.linear(act, self.gate_up), want_fp8=self.down.kind == "fp8_block")
+
     def forward(self, act: Act, reduce: bool = True, batch=None) -> torch.Tensor:
         gu = ops.linear(act, self.gate_up)
         use_lora = self.lora is not None and batch is not None and batch.adapter_rows is not None and self.lora_prefix

@@ -9,6 +9,7 @@ Reference parity: ``crates/spark-model/src/model/`` (``TransformerModel``), the 
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Tuple
 
@@ -20,6 +21,10 @@ from ..layers import Attention, DenseMLP, GatedDeltaNet, MoE, ParallelCtx
 from ..layers.common import make_weight, randn_weight, shard_rows
 from ..ops import Act, LinearWeight, reference as ref
 from .batch import ForwardBatch
+
+# tensor-parallel steps with at least this many rows run sequence-parallel (reduce-scatter / all-gather fused into the
+# GEMMs); smaller steps keep the replicated residual stream and the fused GEMM + all-reduce
+SEQ_PARALLEL_MIN_TOKENS = int(os.environ.get("ATLAS_SP_MIN_TOKENS", "1024"))
 
 _DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16,
            "torch.float32": torch.float32, "torch.bfloat16": torch.bfloat16, "torch.float16": torch.float16}
@@ -129,6 +134,7 @@ class DecoderLM:
             self.mtp = MTPHead(cfg, self.pctx, ep_mode)
         tp = self.pctx.tp_size
         self.vocab_parallel = tp > 1 and cfg.vocab_size % tp == 0
+        self.sp_capacity_hint = 0            # the engine sets this to its largest step so the area is allocated once
 
     # ------------------------------------------------------------------ weights
     def init_random(self, seed: int = 0, std: float = 0.02, max_pos: Optional[int] = None) -> "DecoderLM":
@@ -200,10 +206,58 @@ class DecoderLM:
     def embed_tokens(self, ids: torch.Tensor) -> torch.Tensor:
         return self.embed[ids.long()]
 
+    # ------------------------------------------------------------------ sequence-parallel prefill (tensor parallel)
+    def _seq_parallel_area(self, batch: ForwardBatch, T: int):
+        """The peer-memory area for a sequence-parallel step, or None when this step takes the replicated path.
+        Decided from the model, the configuration and the step's row count only, so every rank decides alike."""
+        p = self.pctx
+        if p.tp_size <= 1 or p.comm is None or not hasattr(p.comm, "seq_parallel") or T < SEQ_PARALLEL_MIN_TOKENS:
+            return None
+        if batch.adapter_rows is not None or self.device.type != "cuda" or ops.FORCE_REFERENCE:
+            return None
+        if torch.cuda.is_current_stream_capturing():
+            return None
+        ok = getattr(self, "_sp_model_ok", None)
+        if ok is None:
+            ok = self.dtype == torch.bfloat16 and self.cfg.hidden_size % 256 == 0 and all(
+                l.kind == "attention" and not l.is_moe and l.ffn.shard and l.mixer.qkv.kind == "fp8_block"
+                and l.mixer.o.kind == "fp8_block" and l.ffn.gate_up.kind == "fp8_block" and l.ffn.down.kind == "fp8_block"
+                and l.mixer.o.bias is None and l.ffn.down.bias is None for l in self.layers)
+            self._sp_model_ok = ok
+        if not ok:
+            return None
+        return p.comm.seq_parallel(max(T, self.sp_capacity_hint), self.cfg.hidden_size)
+
+    def _forward_seq_parallel(self, x: torch.Tensor, batch: ForwardBatch, cache: CacheStore, sp) -> torch.Tensor:
+        """Dense tensor-parallel layers with a row-sharded residual stream: every row-parallel GEMM scatters its
+        partial tiles to the row owners, the owner reduces, normalises and quantises its rows once and gathers them to
+        all ranks, and the next column-parallel GEMM consumes the rows as they arrive."""
+        cfg = self.cfg
+        eps, p1 = cfg.rms_norm_eps, cfg.norm_plus_one
+        res = sp.residual_shard(x)
+        act, _ = ops.rmsnorm_act(x, self.layers[0].input_norm, eps, None, p1, True)
+        n = len(self.layers)
+        hidden = None
+        for i, layer in enumerate(self.layers):
+            out = layer.mixer.mix(act, batch, cache.layer_kv(layer.idx), self.rope_cache)
+            sp.gemm_rs(Act(x=out), layer.mixer.o)
+            act = sp.reduce_norm(res, layer.post_norm, eps, p1)
+            sp.gemm_rs(layer.ffn.hidden_act(act), layer.ffn.down)
+            if i + 1 < n:
+                act = sp.reduce_norm(res, self.layers[i + 1].input_norm, eps, p1)
+            else:
+                hidden = sp.reduce_hidden(res)
+        self.last_prenorm = (hidden, None)
+        y, _ = ops.rmsnorm(hidden, self.final_norm, eps, None, p1)
+        return y
+
     @torch.inference_mode()
     def forward(self, batch: ForwardBatch, cache: CacheStore) -> torch.Tensor:
         """Returns the final-normed hidden states ``[T,H]`` of every row."""
         x = batch.inputs_embeds if batch.inputs_embeds is not None else self.embed_tokens(batch.input_ids)
+        sp = self._seq_parallel_area(batch, x.shape[0])
+        if sp is not None:
+            return self._forward_seq_parallel(x, batch, cache, sp)
         residual = None
         for layer in self.layers:
             x, residual = layer.forward(x, residual, batch, cache, self.rope_cache)

@@ -84,6 +84,9 @@ class Act:
     q: Optional[torch.Tensor] = None
     s: Optional[torch.Tensor] = None
     dtype: Optional[torch.dtype] = None      # dtype of the tensor the quantised form was made from
+    # rows still arriving from other ranks (sequence-parallel all-gather): (flags address, epoch address, wait cycles);
+    # the consuming GEMM polls the flags tile by tile (parallel/seqpar.py)
+    ready: Optional[tuple] = None
 
     @property
     def out_dtype(self) -> torch.dtype:
@@ -146,7 +149,7 @@ def linear(a, w: LinearWeight, out: Optional[torch.Tensor] = None) -> torch.Tens
     if w.kind == "fp8_block":
         q, s = act.fp8()
         if dev_cuda:
-            y = cuda_ops().gemm_fp8_block(q, s, w.weight, w.scale, out=out)
+            y = cuda_ops().gemm_fp8_block(q, s, w.weight, w.scale, out=out, ready=act.ready)
         else:
             y = Q.fp8_block_gemm_ref(q, s, w.weight, w.scale, out_dtype=act.out_dtype)
     elif w.kind == "nvfp4":

@@ -41,6 +41,7 @@ def load() -> None:
     lib.atlas_status_ptr.restype = C.c_void_p
     lib.atlas_read_status.restype = C.c_ulonglong
     lib.atlas_gemm.argtypes = [_i, _vp, _vp, _vp, _vp, _ll, _ll, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _vp, _i, _vp, _vp]
+    lib.atlas_gemm_gathered.argtypes = lib.atlas_gemm.argtypes + [_vp, _vp, _ll]
     lib.atlas_rmsnorm.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _ll, _i, _i, _f, _i, _vp]
     lib.atlas_silu_mul.argtypes = [_vp, _ll, _i, _i, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp]
     lib.atlas_quant_fp8.argtypes = [_vp, _ll, _i, _i, _vp, _ll, _vp, _ll, _vp]
@@ -232,7 +233,9 @@ def gemm_plan(M: int, N: int, K: int, kind: int, sms: int) -> Tuple[int, int]:
     if _FORCE_BLOCK_N:
         bn = _FORCE_BLOCK_N
     elif kind == 0 and m_tiles * ((N + 255) // 256) >= 2 * sms and N % 256 == 0:
-        bn = 256          # bf16 accumulates in TMEM; the fp8 path folds scales in registers and prefers 128
+        bn = 256          # bf16 accumulates in TMEM across K
+    elif kind == 1 and m_tiles * ((N + 255) // 256) >= sms and N % 256 == 0:
+        bn = 256          # fp8: half the per-k-group buffer handshakes per FLOP and 0.75x the shared-memory fill of 128
     elif m_tiles * ((N + 127) // 128) >= sms:
         bn = 128
     elif kind == 1 and m_tiles == 1 and K >= 8192 and N % 128 == 0:
@@ -250,7 +253,8 @@ def gemm_plan(M: int, N: int, K: int, kind: int, sms: int) -> Tuple[int, int]:
     return bn, splits
 
 
-def _gemm(kind: int, a: torch.Tensor, b: torch.Tensor, a_scale, b_scale, out: Optional[torch.Tensor]) -> torch.Tensor:
+def _gemm(kind: int, a: torch.Tensor, b: torch.Tensor, a_scale, b_scale, out: Optional[torch.Tensor],
+          ready: Optional[tuple] = None) -> torch.Tensor:
     M, K = a.shape
     N = b.shape[0]
     d = _dev(a)
@@ -260,6 +264,8 @@ def _gemm(kind: int, a: torch.Tensor, b: torch.Tensor, a_scale, b_scale, out: Op
     assert out.stride(1) == 1 and out.dtype == torch.bfloat16
     sms = _num_sms[d]
     bn, splits = gemm_plan(M, N, K, kind, sms)
+    if ready is not None:
+        splits = 1
     ws = cnt = None
     if splits > 1:
         ws = scratch("gemm_ws", _GEMM_WS_BYTES, a.device)
@@ -268,14 +274,22 @@ def _gemm(kind: int, a: torch.Tensor, b: torch.Tensor, a_scale, b_scale, out: Op
     if kind == 1:
         kb = a_scale.shape[1]
         if a_scale.stride(0) != 1 or a_scale.stride(1) % 4 or a_scale.stride(1) < (M + 127) // 128 * 128 or a_scale.data_ptr() % 16:
+            if ready is not None:
+                raise KernelError("gathered activation scales must already be in the GEMM's k-group-major layout")
             fixed = _scale_buf(M, kb, a.device)
             fixed.copy_(a_scale)
             a_scale = fixed
         sa_m, sa_k = a_scale.stride(0), a_scale.stride(1)
         assert b_scale.is_contiguous() and b_scale.dtype == torch.float32 and a_scale.dtype == torch.float32
-    _check(lib().atlas_gemm(kind, a.data_ptr(), b.data_ptr(), out.data_ptr(), _ptr(a_scale), sa_m, sa_k, _ptr(b_scale),
-                            b_scale.shape[1] if b_scale is not None else 0, M, N, K, a.stride(0), b.stride(0),
-                            out.stride(0), bn, splits, _ptr(ws), _ptr(cnt), sms, _status_ptr[d], _stream()), "gemm")
+    args = (kind, a.data_ptr(), b.data_ptr(), out.data_ptr(), _ptr(a_scale), sa_m, sa_k, _ptr(b_scale),
+            b_scale.shape[1] if b_scale is not None else 0, M, N, K, a.stride(0), b.stride(0),
+            out.stride(0), bn, splits, _ptr(ws), _ptr(cnt), sms, _status_ptr[d], _stream())
+    if ready is not None:
+        # gathered operand: the scales must be read in place (they arrive with the rows), never through a staged copy
+        assert a_scale is None or a_scale.data_ptr() % 16 == 0
+        _check(lib().atlas_gemm_gathered(*args, ready[0], ready[1], ready[2]), "gemm_gathered")
+    else:
+        _check(lib().atlas_gemm(*args), "gemm")
     return out
 
 
@@ -286,9 +300,9 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out=None) -> torch.Tensor:
     return _gemm(0, x, w, None, None, out)
 
 
-def gemm_fp8_block(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor, out=None) -> torch.Tensor:
+def gemm_fp8_block(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor, out=None, ready=None) -> torch.Tensor:
     assert xq.dtype == FP8 and wq.dtype == FP8
-    return _gemm(1, xq, wq, xs, ws, out)
+    return _gemm(1, xq, wq, xs, ws, out, ready)
 
 
 def gemm_nvfp4(x, packed, bscale, gscale, out=None):

@@ -130,6 +130,36 @@ def main() -> int:
             st = K.check_status()
             rel = float((y.float() - ref).pow(2).mean().sqrt() / ref.pow(2).mean().sqrt())
             report(f"gemm_allreduce {kind} M={M} N={N} K={Kfull}", y is not None and rel < 2e-2 and st == 0, rel_rms=rel, status=st)
+    # ---- sequence-parallel layer half: GEMM -> reduce-scatter, owner reduce + norm + quantise + all-gather, gathered GEMM
+    from atlas_b200.ops import linear
+    for (T, H, Kfull, N2) in ((1024, 1024, 2048, 512), (2000, 2048, 4096, 768), (300, 512, 1024, 256)):
+        torch.manual_seed(31)
+        xf = (torch.randn(T, Kfull, device=device) * 0.5).bfloat16()
+        wf = torch.randn(H, Kfull, device=device) * 0.05
+        resid = torch.randn(T, H, device=device).bfloat16()
+        norm_w = (torch.randn(H, device=device) * 0.2 + 1.0).bfloat16()
+        w2 = LinearWeight.from_dense(torch.randn(N2, H, device=device) * 0.05, "fp8_block")
+        ks = Kfull // world
+        act = Act(x=xf[:, rank * ks:(rank + 1) * ks].contiguous())
+        w = LinearWeight.from_dense(wf[:, rank * ks:(rank + 1) * ks].contiguous(), "fp8_block")
+        sp = symm.seq_parallel(T, H)
+        ref = K.gemm_fp8_block(*act.fp8(), w.weight, w.scale).float()
+        dist.all_reduce(ref)
+        h = ref + resid.float()
+        normed = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-6) * norm_w.float()
+        want = normed @ w2.dequantized().float().t()
+        for rep in range(2):                      # twice: the second pass reuses every buffer and flag
+            sp.gemm_rs(act, w)
+            shard = sp.residual_shard(resid)
+            y = linear(sp.reduce_norm(shard, norm_w, 1e-6), w2)
+        sp.gemm_rs(act, w)
+        shard2 = sp.residual_shard(resid)
+        hid = sp.reduce_hidden(shard2)
+        torch.cuda.synchronize()
+        st = K.check_status()
+        rel = lambda a, b: float((a.float() - b).pow(2).mean().sqrt() / b.pow(2).mean().sqrt())
+        r_y, r_h = rel(y, want), rel(hid, h)
+        report(f"seq_parallel T={T} H={H} K={Kfull}", r_y < 4e-2 and r_h < 1e-2 and st == 0, rel_out=r_y, rel_hidden=r_h, status=st)
     # ---- expert-parallel MoE: dispatch / combine over peer memory vs local experts + all-reduce vs the fp32 oracle
     from atlas_b200.layers import ParallelCtx
     from atlas_b200.layers.moe import ExpertWeights
@@ -213,6 +243,48 @@ def main() -> int:
                                   "graph_gemm_only_us": round(g_g * 1e3, 1), "gemm_plus_nccl_us": round(t_u * 1e3, 1),
                                   "gemm_only_us": round(t_g * 1e3, 1), "roofline_us": round(roof_us, 1),
                                   "frac_of_roofline": round(roof_us / (t_f * 1e3), 3)}), flush=True)
+    if args.bench:
+        # one layer half at prefill size: row-parallel GEMM + reduction + norm/quant + the next column-parallel GEMM,
+        # sequence-parallel (fused, peer memory) against GEMM + NCCL all-reduce + norm kernel + GEMM
+        for (T, H, Kfull, N2full, tag) in ((8192, 4096, 4096, 28672, "o_proj -> gate_up, 8B"), (8192, 4096, 14336, 6144, "down -> qkv, 8B")):
+            ks = (Kfull // world) // 128 * 128
+            n2 = (N2full // world) // 128 * 128
+            act = Act(x=torch.randn(T, ks, device=device).bfloat16())
+            act.fp8()
+            w = LinearWeight.from_dense(torch.randn(H, ks, device=device) * 0.05, "fp8_block")
+            w2 = LinearWeight.from_dense(torch.randn(n2, H, device=device) * 0.05, "fp8_block")
+            resid = torch.randn(T, H, device=device).bfloat16()
+            norm_w = torch.ones(H, device=device).bfloat16()
+            sp = symm.seq_parallel(T, H)
+            shard = sp.residual_shard(resid)
+            out2 = torch.empty(T, n2, dtype=torch.bfloat16, device=device)
+
+            def fused():
+                sp.gemm_rs(act, w)
+                linear(sp.reduce_norm(shard, norm_w, 1e-6), w2, out=out2)
+
+            def unfused():
+                y = K.gemm_fp8_block(act.q, act.s, w.weight, w.scale)
+                dist.all_reduce(y)
+                q, s_, _ = K.rmsnorm(y, norm_w, 1e-6, resid, False, quant=True)
+                K.gemm_fp8_block(q, s_, w2.weight, w2.scale, out=out2)
+
+            def gemms_only():
+                K.gemm_fp8_block(act.q, act.s, w.weight, w.scale)
+                K.gemm_fp8_block(sp_q, sp_s, w2.weight, w2.scale, out=out2)
+            sp_q, sp_s = K.quant_fp8(resid)
+            t_f = _max_over_ranks(_time(fused, iters=10), dist, device)
+            t_u = _max_over_ranks(_time(unfused, iters=10), dist, device)
+            t_g = _max_over_ranks(_time(gemms_only, iters=10), dist, device)
+            st = K.check_status()
+            if rank == 0:
+                flops = 2.0 * T * H * ks + 2.0 * T * n2 * H
+                nv_bytes = (world - 1) / world * T * H * 3.0          # bf16 partials out + FP8 rows in, per rank
+                roof_us = max(flops / 1640.6e12, nv_bytes / 770e9) * 1e6
+                print(json.dumps({"bench": "seq_parallel_layer_half", "shape": tag, "T": T, "H": H, "K_per_rank": ks,
+                                  "N2_per_rank": n2, "fused_us": round(t_f * 1e3, 1), "gemm_nccl_norm_gemm_us": round(t_u * 1e3, 1),
+                                  "two_gemms_only_us": round(t_g * 1e3, 1), "roofline_us": round(roof_us, 1),
+                                  "frac_of_roofline": round(roof_us / (t_f * 1e3), 3), "status": st}), flush=True)
     if args.engine:
         from atlas_b200.config import EngineConfig, ModelConfig, QuantConfig
         from atlas_b200.engine import LLMEngine
@@ -224,15 +296,19 @@ def main() -> int:
                           max_position_embeddings=2048, quant=QuantConfig(method="fp8_block", kv_cache_dtype="fp8"))
         g = torch.Generator().manual_seed(5)
         prompts = [torch.randint(0, 4096, (40 + 3 * i,), generator=g).tolist() for i in range(4)]
+        prompts.append(torch.randint(0, 4096, (1300,), generator=g).tolist())      # long enough for the sequence-parallel path
         outs = {}
         for name, comm in (("nccl", base), ("p2p", symm)):
             p2 = ParallelCtx(topo.tp_rank, topo.tp_size, 0, 1, comm, None)
             model = build_model(cfg, p2, device=device).init_random(0)
-            eng = LLMEngine(model, EngineConfig(num_kv_blocks=128, max_num_seqs=8, max_seq_len=512, use_cuda_graphs=(name == "p2p")))
+            eng = LLMEngine(model, EngineConfig(num_kv_blocks=256, max_num_seqs=8, max_seq_len=2048, max_prefill_tokens=2048,
+                                                use_cuda_graphs=(name == "p2p")))
             outs[name] = [o.output_tokens for o in eng.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))]
             torch.cuda.synchronize()
         same = sum(a == b for a, b in zip(outs["nccl"], outs["p2p"]))
-        report("engine tp nccl vs p2p", same >= 3 and K.check_status() == 0, identical=same, fused_calls=symm.calls["gemm_allreduce"])
+        sp_calls = sum(a.calls["gemm_rs"] for a in symm._sp_areas.values())
+        report("engine tp nccl vs p2p", same >= 4 and K.check_status() == 0, identical=same, of=len(prompts),
+               fused_calls=symm.calls["gemm_allreduce"], seq_parallel_gemms=sp_calls)
     dist.barrier()
     symm.close()
     dist.destroy_process_group()

@@ -89,6 +89,8 @@ class SymmBackend(CommBackend):
                                              C.POINTER(_vp), _i, _i, _vp, _sz, _i, C.POINTER(_sz), _i, _ll, _vp, _vp,
                                              _i, _vp, _ll, _i, _vp, _vp]
         base.barrier()
+        self._sp_areas, self._sp_mem = {}, []
+        self.sp_min_capacity = int(os.environ.get("ATLAS_SP_MIN_CAPACITY", "8192"))
         self.calls = {"oneshot": 0, "twoshot": 0, "alltoall": 0, "fallback": 0, "gemm_allreduce": 0, "gemm_allreduce_oneshot": 0}
 
     # ------------------------------------------------------------------ IPC plumbing
@@ -116,9 +118,10 @@ class SymmBackend(CommBackend):
         for p in self._opened:
             self.lib.atlas_ipc_close(p)
         self._opened = []
-        for p in (self._data, self._flags, self._fdata, self._fflags):
+        for p in [self._data, self._flags, self._fdata, self._fflags] + self._sp_mem:
             if p:
                 self.lib.atlas_symm_free(p)
+        self._sp_mem, self._sp_areas = [], {}
         self._data = self._flags = 0
 
     def check(self) -> None:
@@ -230,6 +233,31 @@ class SymmBackend(CommBackend):
             self.calls["gemm_allreduce_oneshot"] += 1
             return out
         return _device_view(self._fdata + off.value, (M, N), torch.bfloat16, self.device)
+
+    def seq_parallel(self, tokens: int, hidden: int):
+        """The sequence-parallel area (``parallel/seqpar.py``) sized for at least ``tokens`` rows of width ``hidden``:
+        allocated symmetrically on every rank and mapped over CUDA IPC on first use (a collective call: every rank
+        reaches it with the same arguments).  Returns None when the shape is not covered."""
+        self._guard()
+        if hidden % 256 or hidden > 16384 or self.world_size > 8:
+            return None
+        sp = self._sp_areas.get(hidden)
+        if sp is not None and sp.t_pad >= tokens:
+            return sp
+        from .seqpar import SeqParallelArea
+        cap = max(tokens, self.sp_min_capacity)
+        new = SeqParallelArea(self.rank, self.world_size, cap, hidden, self.device, self.wait_cycles)
+        torch.cuda.synchronize(self.device)          # nobody may still be inside kernels that use the old area
+        self.base.barrier()
+        base = self._alloc(new.nbytes)
+        new.adopt(base)
+        self._sp_mem.append(base)
+        handles = [None] * self.world_size
+        self.base.dist.all_gather_object(handles, self._export(base), group=self.base.group)
+        new.connect([base if r == self.rank else self._open(h) for r, h in enumerate(handles)])
+        self.base.barrier()
+        self._sp_areas[hidden] = new
+        return new
 
     # everything else: the bootstrap backend
     def all_reduce_async(self, t):

@@ -64,12 +64,73 @@ def _clock_summary(proc):
     return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def _torch_nccl_arm(args, mcfg, topo, device, real_stdout) -> int:
+    """This repository's own library baseline (see ``atlas_b200/bench/torch_baseline.py``): same wave, same model shape,
+    stock PyTorch / cuBLASLt / NCCL kernels only."""
+    import torch
+    from atlas_b200.bench.torch_baseline import TorchNcclDecoder
+    world, rank = topo.world_size, topo.rank
+    model = TorchNcclDecoder(mcfg, rank, world, device)
+    model.alloc_cache(args.concurrency, args.isl + args.osl + 8)
+    gen = torch.Generator().manual_seed(1234)
+    pinned = torch.empty(args.concurrency, args.isl, dtype=torch.long).pin_memory()
+
+    def wave():
+        pinned.copy_(torch.randint(0, mcfg.vocab_size, (args.concurrency, args.isl), generator=gen))
+        return model.wave(pinned, args.osl)
+
+    def sync_all():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+    for _ in range(max(1, min(args.warmup, 3))):
+        wave()
+    sync_all()
+    sampler = _clock_sampler(torch.cuda.current_device()) if rank == 0 else None
+    t0 = time.perf_counter()
+    tokens, dev_s, ttfts = 0, 0.0, []
+    for _ in range(args.steps):
+        n, tt, d = wave()
+        tokens += n
+        dev_s += d
+        ttfts += tt
+    sync_all()
+    wall = time.perf_counter() - t0
+    clocks = _clock_summary(sampler) if rank == 0 else None
+    t = torch.tensor([wall, dev_s], dtype=torch.float64, device=device)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    wall, dev_s = float(t[0]), float(t[1])
+    if rank == 0:
+        line = {"metric": "aggregate output tok/s (concurrency wave, ISL/OSL)", "value": round(tokens / dev_s, 2), "unit": "tok/s",
+                "n_gpus": world, "steps": args.steps, "warmup": min(args.warmup, 3), "ms_per_step": round(wall * 1e3 / args.steps, 3),
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "fp8-e4m3 weights and activations (row-wise scales, cuBLASLt), bf16 KV",
+                "data": "synthetic: uniform-random token ids, random-init N(0,0.02) weights quantized to fp8",
+                "config": {"model": args.model, "global_batch": args.concurrency, "seq_len": args.isl + args.osl, "isl": args.isl,
+                           "osl": args.osl, "parallelism": f"tp{world}", "collectives": "nccl" if world > 1 else "none",
+                           "l2": "inputs larger than L2", "step": "one wave of `global_batch` concurrent requests, prefill + decode",
+                           "note": "THIS REPOSITORY'S OWN BASELINE, not the upstream reference: eager PyTorch, torch._scaled_mm, "
+                                   "SDPA, dense KV cache, static batch, no scheduler, no CUDA graphs"},
+                "clocks": clocks,
+                "e2e": {"value": round(tokens / wall, 2), "unit": "tok/s", "h2d_bytes_per_step": args.concurrency * args.isl * 8,
+                        "d2h_bytes_per_step": args.concurrency * args.osl * 8, "note": "per wave"},
+                "gpu_launches": 0, "ttft_p50_ms": round(statistics.median(ttfts) * 1e3, 2),
+                "tpot_ms": round((wall / args.steps) * 1e3 / args.osl, 3), "impl": "torch-nccl (own baseline)"}
+        os.write(real_stdout, (json.dumps(line) + "\n").encode())
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="atlas_b200", choices=["atlas_b200", "reference"])
+    ap.add_argument("--impl", default="atlas_b200", choices=["atlas_b200", "reference", "torch-nccl"],
+                    help="atlas_b200: this engine; reference: the upstream project (not buildable here, prints why); "
+                         "torch-nccl: this repository's own library baseline (torch._scaled_mm + SDPA + NCCL, eager)")
+    ap.add_argument("--ladder", default="1,8,32", help="extra concurrency rungs reported under `ladder` ('' = none)")
+    ap.add_argument("--ladder-steps", type=int, default=2)
     ap.add_argument("--model", default="llama3-8b")
     ap.add_argument("--concurrency", type=int, default=128)
     ap.add_argument("--isl", type=int, default=1024)
@@ -121,6 +182,12 @@ def main():
     mcfg = PRESETS[args.model]()
     if args.layers:
         mcfg.num_hidden_layers = args.layers
+    if args.impl == "torch-nccl":
+        rc = _torch_nccl_arm(args, mcfg, topo, device, real_stdout)
+        if world > 1:
+            torch.distributed.barrier()
+            torch.distributed.destroy_process_group()
+        return rc
     max_len = args.isl + args.osl + 16
     mcfg.max_position_embeddings = max(4096, max_len)
     model = build_model(mcfg, pctx, device=device).init_random(0, max_pos=max_len + 16)
@@ -136,8 +203,9 @@ def main():
     sp = SamplingParams(max_tokens=args.osl, temperature=0.0, ignore_eos=True)
     gen = torch.Generator().manual_seed(1234)
 
-    def wave():
-        prompts = [torch.randint(0, mcfg.vocab_size, (args.isl,), generator=gen).tolist() for _ in range(args.concurrency)]
+    def wave(conc=None):
+        conc = conc or args.concurrency
+        prompts = [torch.randint(0, mcfg.vocab_size, (args.isl,), generator=gen).tolist() for _ in range(conc)]
         if args.shared_prefix:
             shared = torch.randint(0, mcfg.vocab_size, (args.shared_prefix,), generator=gen).tolist()
             for i in range(0, len(prompts), 2):
@@ -175,12 +243,45 @@ def main():
     wall = time.perf_counter() - t0
     clocks = _clock_summary(sampler) if rank == 0 else None
     dev_s = eng.device_time_ms / 1e3
+    st = K.check_status()
+    if st:
+        # a bounded device-side wait gave up inside the timed region: whatever was timed is not the workload
+        print(f"bench.py: device status word {st:#x} after the timed waves: result discarded", file=sys.stderr)
+        return 3
+    main_launches = (K.launch_count - launches0) + (eng.runner.graph_replays - replays0) * eng.runner.kernels_per_graph()
+    main_steps, main_h2d = eng.stats.steps - steps0, eng.runner.h2d_bytes - h2d0
+    main_phase = {k: {"ms": round(v[0], 1), "engine_steps": v[1]} for k, v in eng.device_phase_ms.items()}
+    # the lower rungs of the concurrency ladder (same engine, same request shape): one warm-up wave, then timed waves
+    ladder = []
+    for c in [int(x) for x in args.ladder.split(",") if x.strip()]:
+        if c >= args.concurrency:
+            continue
+        wave(c)
+        sync_all()
+        eng.device_time_ms = 0.0
+        w0 = time.perf_counter()
+        n_tok, tt_all = 0, []
+        for _ in range(max(1, args.ladder_steps)):
+            n, tt = wave(c)
+            n_tok += n
+            tt_all += [t for t in tt if t is not None]
+        sync_all()
+        w = time.perf_counter() - w0
+        tl = torch.tensor([w, eng.device_time_ms / 1e3], dtype=torch.float64, device=device)
+        if world > 1:
+            torch.distributed.all_reduce(tl, op=torch.distributed.ReduceOp.MAX)
+        w, d_s = float(tl[0]), float(tl[1])
+        ladder.append({"concurrency": c, "value": round(n_tok / d_s, 2) if d_s > 0 else None, "e2e": round(n_tok / w, 2),
+                       "ttft_p50_ms": round(statistics.median(tt_all) * 1e3, 2) if tt_all else None,
+                       "tpot_ms": round(w / max(1, args.ladder_steps) * 1e3 / args.osl, 3)})
+    if K.check_status():
+        print("bench.py: device status word set during the ladder rungs", file=sys.stderr)
+        return 3
     t = torch.tensor([wall, dev_s], dtype=torch.float64, device=device)
     if world > 1:
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
     wall, dev_s = float(t[0]), float(t[1])
-    eng_steps = eng.stats.steps - steps0
-    launches = (K.launch_count - launches0) + (eng.runner.graph_replays - replays0) * eng.runner.kernels_per_graph()
+    eng_steps, launches = main_steps, main_launches
     qm = mcfg.quant.method
     dtype_desc = {"fp8_block": "fp8-e4m3 weights (128x128 scales) + fp8 KV, bf16 activations",
                   "nvfp4": "nvfp4 weights (e2m1, e4m3 scale per 16, fp32 global)" + (" for experts, bf16 elsewhere" if mcfg.quant.experts_only else "") + " + fp8 KV, bf16 activations",
@@ -205,13 +306,14 @@ def main():
                        "prefix_hit_tokens": (eng.radix.stats.hit_tokens if eng.radix is not None else 0)},
             "clocks": clocks,
             "e2e": {"value": round(e2e, 2), "unit": "tok/s",
-                    "h2d_bytes_per_step": int((eng.runner.h2d_bytes - h2d0) / max(1, eng_steps)),
+                    "h2d_bytes_per_step": int(main_h2d / max(1, eng_steps)),
                     "d2h_bytes_per_step": int(8 * tokens / max(1, eng_steps)),
                     "note": "per engine step; every step copies token ids / positions / slots / block tables from pinned host memory and reads the sampled token ids back"},
             "gpu_launches": int(launches),
             "ttft_p50_ms": round(statistics.median(ttfts) * 1e3, 2) if ttfts else None,
             "tpot_ms": round((wall / args.steps) * 1e3 / args.osl, 3),
-            "device_phase_ms": {k: {"ms": round(v[0], 1), "engine_steps": v[1]} for k, v in eng.device_phase_ms.items()},
+            "device_phase_ms": main_phase,
+            "ladder": ladder,
             "impl": "atlas_b200",
         }
         sys.stdout.flush()
