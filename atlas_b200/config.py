@@ -24,6 +24,7 @@ _FAMILY_ALIASES = {
     "qwen3_next": "hybrid", "qwen3_5": "hybrid", "qwen35": "hybrid",
     "qwen3_5_moe": "hybrid", "qwen35_moe": "hybrid", "qwen3_6_moe": "hybrid",
     "holo3_1_moe": "hybrid",
+    "nemotron_h": "hybrid", "nemotron_h_puzzle": "hybrid",
 }
 
 
@@ -117,6 +118,15 @@ class ModelConfig:
     linear_key_head_dim: int = 128
     linear_value_head_dim: int = 128
     linear_conv_kernel_dim: int = 4
+    # single-module blocks (Nemotron-H): per layer "mamba" | "attention" | "mlp"; empty for the other families
+    block_types: List[str] = field(default_factory=list)
+    mamba_num_heads: int = 0
+    mamba_head_dim: int = 64
+    ssm_state_size: int = 128
+    mamba_n_groups: int = 8
+    mamba_conv_kernel: int = 4
+    mamba_dt_min: float = 0.0
+    mlp_activation: str = "silu_glu"  # silu_glu (gated SwiGLU) | relu2 (up -> relu^2 -> down)
     # MTP speculative head
     mtp_num_layers: int = 0
     # numerics
@@ -139,7 +149,9 @@ class ModelConfig:
         return int(self.head_dim * self.partial_rotary_factor)
 
     def layer_kind(self, i: int) -> str:
-        """Mixer kind of layer ``i``: ``attention`` or ``gdn``."""
+        """Mixer kind of layer ``i``: ``attention``, ``gdn``, ``mamba2`` or ``none`` (an FFN-only block)."""
+        if self.block_types:
+            return {"mamba": "mamba2", "attention": "attention"}.get(self.block_types[i], "none")
         if self.family != "hybrid":
             return "attention"
         if self.layer_types:
@@ -147,6 +159,8 @@ class ModelConfig:
         return "attention" if (i + 1) % self.full_attention_interval == 0 else "gdn"
 
     def is_moe_layer(self, i: int) -> bool:
+        if self.block_types:
+            return self.block_types[i] == "moe"
         if self.num_experts <= 0 or i in self.mlp_only_layers:
             return False
         return (i + 1) % max(1, self.decoder_sparse_step) == 0
@@ -172,6 +186,11 @@ class ModelConfig:
             if self.layer_kind(i) == "attention":
                 qmul = 2 if self.attn_output_gate else 1
                 n += h * (self.q_size * qmul + 2 * self.kv_size) + self.q_size * h
+            elif self.layer_kind(i) == "mamba2":
+                di = self.mamba_num_heads * self.mamba_head_dim
+                n += h * (2 * di + 2 * self.mamba_n_groups * self.ssm_state_size + self.mamba_num_heads) + di * h
+            elif self.layer_kind(i) == "none":
+                pass
             else:
                 kd = self.linear_num_key_heads * self.linear_key_head_dim
                 vd = self.linear_num_value_heads * self.linear_value_head_dim
@@ -179,6 +198,8 @@ class ModelConfig:
             if self.is_moe_layer(i):
                 n += self.num_experts * 3 * h * self.moe_intermediate_size + h * self.num_experts
                 n += 3 * h * self.shared_expert_intermediate_size
+            elif self.block_types:
+                n += 2 * h * self.intermediate_size if self.block_types[i] == "mlp" else 0
             else:
                 n += 3 * h * self.intermediate_size
         return n
@@ -203,7 +224,7 @@ class ModelConfig:
             model_type=mt, family=fam,
             vocab_size=int(cfg["vocab_size"]), hidden_size=hs,
             intermediate_size=int(cfg.get("intermediate_size", 0) or 0),
-            num_hidden_layers=int(cfg["num_hidden_layers"]),
+            num_hidden_layers=int(cfg.get("num_hidden_layers") or len(cfg.get("layers_block_type") or cfg.get("hybrid_override_pattern") or [])),
             num_attention_heads=nh,
             num_key_value_heads=int(cfg.get("num_key_value_heads", nh)),
             head_dim=int(cfg.get("head_dim") or hs // nh),
@@ -240,6 +261,25 @@ class ModelConfig:
         )
         if mt == "mixtral":
             c.moe_intermediate_size = c.intermediate_size
+        if mt.startswith("nemotron_h"):
+            blocks = cfg.get("layers_block_type")
+            if not blocks and cfg.get("hybrid_override_pattern"):
+                blocks = [{"M": "mamba", "*": "attention", "-": "mlp", "E": "moe"}[ch] for ch in cfg["hybrid_override_pattern"]]
+            c.block_types = list(blocks or [])
+            c.num_hidden_layers = len(c.block_types)
+            c.mamba_num_heads = int(cfg.get("mamba_num_heads", 128))
+            c.mamba_head_dim = int(cfg.get("mamba_head_dim", 64))
+            c.ssm_state_size = int(cfg.get("ssm_state_size", 128))
+            c.mamba_n_groups = int(cfg.get("n_groups", 8))
+            c.mamba_conv_kernel = int(cfg.get("conv_kernel", 4))
+            c.mamba_dt_min = float(cfg.get("time_step_min", 0.001))
+            c.mlp_activation = "relu2"
+            c.rms_norm_eps = float(cfg.get("layer_norm_epsilon", cfg.get("rms_norm_eps", 1e-5)))
+            c.partial_rotary_factor = 0.0                     # attention blocks carry no positional rotation
+            c.qk_norm = c.attn_output_gate = c.norm_plus_one = False
+            c.num_experts = c.num_experts_per_tok = 0
+            if "moe" in c.block_types:
+                raise ValueError("nemotron_h checkpoints with MoE blocks are not supported")
         c.validate()
         return c
 
@@ -260,7 +300,7 @@ class ModelConfig:
             raise ValueError("num_attention_heads must be a multiple of num_key_value_heads")
         if self.num_experts and not self.num_experts_per_tok:
             raise ValueError("MoE config needs num_experts_per_tok")
-        if self.family == "hybrid" and not self.linear_num_value_heads:
+        if self.family == "hybrid" and not self.linear_num_value_heads and not self.block_types:
             raise ValueError("hybrid config needs linear_num_value_heads")
 
     def to_dict(self) -> Dict[str, Any]:
@@ -334,10 +374,31 @@ def tiny_hybrid(dtype: str = "float32") -> ModelConfig:
                        max_position_embeddings=4096, dtype=dtype)
 
 
+def tiny_nemotron_h(dtype: str = "float32") -> ModelConfig:
+    """Nemotron-H style stack of single-module blocks: Mamba-2, position-free attention and relu^2 MLP."""
+    return ModelConfig(model_type="nemotron_h", family="hybrid", vocab_size=1024, hidden_size=256, intermediate_size=512,
+                       num_hidden_layers=6, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                       partial_rotary_factor=0.0, rms_norm_eps=1e-5,
+                       block_types=["mamba", "mlp", "mamba", "attention", "mlp", "mamba"], mamba_num_heads=8,
+                       mamba_head_dim=32, ssm_state_size=32, mamba_n_groups=2, mamba_conv_kernel=4, mamba_dt_min=0.001,
+                       mlp_activation="relu2", max_position_embeddings=4096, dtype=dtype)
+
+
+def nemotron_h_8b(quant: str = "none") -> ModelConfig:
+    pattern = "M-M-M-MM-M-M-M*-M-M-M*-M-M-M-M*-M-M-M-M*-M-MM-M-M-M-M-M-"
+    blocks = [{"M": "mamba", "*": "attention", "-": "mlp"}[ch] for ch in pattern]
+    return ModelConfig(model_type="nemotron_h", family="hybrid", vocab_size=131072, hidden_size=4096, intermediate_size=21504,
+                       num_hidden_layers=len(blocks), num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                       partial_rotary_factor=0.0, rms_norm_eps=1e-5, block_types=blocks, mamba_num_heads=128, mamba_head_dim=64,
+                       ssm_state_size=128, mamba_n_groups=8, mamba_conv_kernel=4, mamba_dt_min=0.001, mlp_activation="relu2",
+                       max_position_embeddings=8192, quant=QuantConfig(method=quant, kv_cache_dtype="fp8"))
+
+
 PRESETS = {
     "tiny-dense": tiny_dense, "tiny-moe": tiny_moe, "tiny-hybrid": tiny_hybrid,
     "llama3-8b": llama3_8b, "llama3-70b": llama3_70b,
     "qwen3-30b-a3b": qwen3_30b_a3b, "qwen3-next-80b": qwen3_next_80b,
+    "tiny-nemotron-h": tiny_nemotron_h, "nemotron-h-8b": nemotron_h_8b,
 }
 
 

@@ -19,7 +19,8 @@ __global__ void __launch_bounds__(256)
 gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ w, int C, int W,
                 const __nv_bfloat16* __restrict__ conv_state, const int* __restrict__ seq_of_token,
                 const int* __restrict__ query_start_loc, const int* __restrict__ state_slots,
-                const unsigned char* __restrict__ has_state, __nv_bfloat16* y, long long ldy, int T) {
+                const unsigned char* __restrict__ has_state, __nv_bfloat16* y, long long ldy, int T,
+                const __nv_bfloat16* __restrict__ bias) {
   const int t = blockIdx.x;           // rows on grid.x (no 65535 limit)
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C || t >= T) return;
@@ -28,7 +29,7 @@ gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_b
   const int rel = t - q0;                      // row inside this sequence's chunk
   const long long slot = state_slots[b];
   const bool live = has_state[b] != 0;
-  float acc = 0.f;
+  float acc = bias ? __bfloat162float(bias[c]) : 0.f;
   // tap i multiplies the input i - (W-1) rows back... weight[c][W-1] is the current row
   for (int i = 0; i < W; ++i) {
     const int back = W - 1 - i;                // rows back from t
@@ -392,7 +393,22 @@ extern "C" int atlas_gdn_conv(const void* x, long long ldx, const void* w, int C
   gdn_conv_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), ldx, reinterpret_cast<const __nv_bfloat16*>(w), C, W,
       reinterpret_cast<const __nv_bfloat16*>(conv_state), seq_of_token, query_start_loc, state_slots, has_state,
-      reinterpret_cast<__nv_bfloat16*>(y), ldy, T);
+      reinterpret_cast<__nv_bfloat16*>(y), ldy, T, nullptr);
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+// Same depth-wise causal convolution + SiLU with a per-channel bias (Mamba-2 blocks).
+extern "C" int atlas_conv1d_bias_silu(const void* x, long long ldx, const void* w, const void* bias, int C, int W,
+                                      const void* conv_state, const int* seq_of_token, const int* query_start_loc,
+                                      const int* state_slots, const unsigned char* has_state, void* y, long long ldy, int T,
+                                      void* stream) {
+  if (T <= 0) return 0;
+  if (W < 2 || W > 8) return -1;
+  dim3 grid(T, (C + 255) / 256);
+  gdn_conv_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), ldx, reinterpret_cast<const __nv_bfloat16*>(w), C, W,
+      reinterpret_cast<const __nv_bfloat16*>(conv_state), seq_of_token, query_start_loc, state_slots, has_state,
+      reinterpret_cast<__nv_bfloat16*>(y), ldy, T, reinterpret_cast<const __nv_bfloat16*>(bias));
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
 }
 

@@ -31,7 +31,9 @@ constexpr int kRowsPerReadyFlag = 8;     // granularity of the "rows have arrive
 // registers across its per-k-group folds: 128 x 256 / (32 x warps) floats per thread, i.e. 128 with eight warps (fits
 // the 200-register budget of a 320-thread CTA) and 64 with sixteen (112-register budget of a 576-thread CTA).
 __host__ __device__ constexpr int epi_warps(int block_n, bool fp8) { return (fp8 && block_n == 256) ? 16 : 8; }
-__host__ __device__ constexpr int gemm_threads_w(int warps) { return 32 * (kCtrlWarps + warps); }
+// The fused-collective variants carry one more warp that raises the peers' flags (see the signal warp in the kernel);
+// warps are allocated four at a time, so ten and eleven warps cost the same.
+__host__ __device__ constexpr int gemm_threads_w(int warps, bool fuse = false) { return 32 * (kCtrlWarps + warps + (fuse ? 1 : 0)); }
 
 template <int BLOCK_N>
 struct GemmCfg {
@@ -48,7 +50,8 @@ struct GemmCfg {
   static constexpr int kScaleRingBytes = kScaleSlots * kBlockM * 4;   // per slot: 128 activation scales (fp32)
   static constexpr int kBScaleMax = 512;                          // k-groups of one split kept in shared memory
   static constexpr int kBScaleBytes = 2 * 2 * kBScaleMax * 4;     // double-buffered over tiles, two 128-column groups
-  static constexpr int kSmemBytes = kStages * kStageBytes + kScaleRingBytes + kBScaleBytes + 1024 /*align*/ + 512 /*barriers*/;
+  static constexpr int kXchBytes = 2 * 4 * kBlockM * 4;           // fused epilogues: per-row partial (max, sum of squares) of up to four column slices
+  static constexpr int kSmemBytes = kStages * kStageBytes + kScaleRingBytes + kBScaleBytes + kXchBytes + 1024 /*align*/ + 512 /*barriers*/;
 };
 
 struct GemmParams {
@@ -85,6 +88,23 @@ struct GemmParams {
   const uint32_t* a_ready;
   const unsigned int* a_ready_epoch;
   size_t ar_parity_stride;      // one-shot: bytes between the two epoch-parity halves of the partial area
+  // ---- fused epilogues (epi_mode != 0 replaces the bf16 store of C)
+  //   1  C = [gate | up] of a SwiGLU projection (B is the stack [gate rows; up rows], N = 2 * act_cols): the tile takes 32-row
+  //      chunks of gate and up alternately, the epilogue computes silu(gate) * up, quantises it to FP8 in 128-wide groups
+  //      and stores rows + scales (scales k-group major, like every activation scale of this library)
+  //   2  C + residual -> residual (in place); (new residual * norm weight) quantised to FP8 in 128-wide groups -> q_out /
+  //      s_out; per-row sums of squares of each column tile -> ss_out[n_tile][row].  The row's 1/rms factor is NOT
+  //      applied here: RMSNorm's per-row factor commutes with the next linear layer, whose GEMM applies it (ss_in).
+  // ss_in (any mode): this GEMM's A operand is such a deferred-norm activation: every output row is multiplied by
+  // rsqrt(sum_j ss_in[j][row] * ss_inv_h + ss_eps) before anything else happens to it.
+  int epi_mode;
+  int act_cols;                 // mode 1: number of activation columns (= N / 2)
+  uint8_t* q_out; long long ldq;
+  float* s_out; long long s_ld;
+  __nv_bfloat16* residual; long long ldr;
+  const __nv_bfloat16* norm_w; int norm_plus_one;
+  float* ss_out; long long ss_out_ld;
+  const float* ss_in; int ss_in_parts; long long ss_in_ld; float ss_inv_h, ss_eps;
   const int* tile_expert;       // nullptr = plain GEMM
   const int* num_m_tiles_ptr;   // device-side tile count (the host cannot know it)
   int expert_n;                 // output features per expert
@@ -141,7 +161,7 @@ ATLAS_DEVICE uint64_t pack_f32x2(float lo, float hi) {
 }
 
 template <int BLOCK_N, bool FP8, bool FUSE_AR = false, int EPW = epi_warps(BLOCK_N, FP8)>
-__global__ void __launch_bounds__(gemm_threads_w(EPW), 1)
+__global__ void __launch_bounds__(gemm_threads_w(EPW, FUSE_AR), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmParams p) {
   using Cfg = GemmCfg<BLOCK_N>;
@@ -157,7 +177,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   constexpr int kScaleSlots = Cfg::kScaleSlots;
   float* sc_ring = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes);        // [kScaleSlots][128]
   float* bs_smem = sc_ring + kScaleSlots * kBlockM;                                     // [2][kBScaleMax]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + Cfg::kScaleRingBytes + Cfg::kBScaleBytes);
+  float* xch = bs_smem + Cfg::kBScaleBytes / 4;                                        // [2][4][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + Cfg::kScaleRingBytes + Cfg::kBScaleBytes + Cfg::kXchBytes);
   uint64_t* full = bars;
   uint64_t* empty = bars + kStages;
   uint64_t* acc_full = bars + 2 * kStages;
@@ -167,6 +188,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sc_full + kScaleSlots);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile int* ticket_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  // reduce-scatter mode: epilogue -> signal warp handshake (two slots), so that the system-scope release that publishes
+  // a tile's peer stores is not paid by the warps that fold the next tile
+  uint64_t* sig_full = reinterpret_cast<uint64_t*>(tmem_slot + 4);
+  uint64_t* sig_free = sig_full + 2;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -180,6 +205,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     for (int b = 0; b < kAcc; ++b) {
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], kEpiWarps);
+    }
+    if (FUSE_AR) {
+      for (int b = 0; b < 2; ++b) { mbar_init(&sig_full[b], kEpiWarps); mbar_init(&sig_free[b], 1); }
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -269,8 +297,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             if (++sc_slot == kScaleSlots) sc_slot = 0;
           }
           tma_load_2d(sa, &tmap_a, &full[stage], kb * kElemsPerRow, m_tile * kBlockM);
-          tma_load_2d(sa + Cfg::kABytes, &tmap_b, &full[stage], kb * kElemsPerRow,
-                      (p.tile_expert ? p.tile_expert[m_tile] * p.expert_n : 0) + n_tile * BLOCK_N);
+          if (p.epi_mode == 1) {
+            // 32-row chunks, gate and up alternating, so that an epilogue thread's 64 columns are 32 gate values and
+            // the 32 up values of the same activation columns (the tensor map of B has a 32-row box in this mode)
+            const int a0 = n_tile * (BLOCK_N / 2);
+#pragma unroll
+            for (int c = 0; c < BLOCK_N / 32; ++c)
+              tma_load_2d(sa + Cfg::kABytes + c * 32 * kRowBytes, &tmap_b, &full[stage], kb * kElemsPerRow,
+                          ((c & 1) ? p.act_cols : 0) + a0 + (c >> 1) * 32);
+          } else {
+            tma_load_2d(sa + Cfg::kABytes, &tmap_b, &full[stage], kb * kElemsPerRow,
+                        (p.tile_expert ? p.tile_expert[m_tile] * p.expert_n : 0) + n_tile * BLOCK_N);
+          }
           if (pf_on) pf_step();
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -321,6 +359,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (!FP8) { umma_commit(&acc_full[acc_iter % kAcc]); ++acc_iter; }
       }
     }
+  } else if (FUSE_AR && warp == kCtrlWarps + kEpiWarps) {
+    // ------------------------------------------------------------------ signal warp (reduce-scatter mode)
+    // For every tile, in the CTA's item order: wait until all epilogue warps have issued the tile's peer stores, then
+    // raise the tile's flag at the owner with a system-scope release (cumulative over those stores through the
+    // barrier).  The release waits for the stores to be acknowledged over NVLink; here that costs nobody anything.
+    if (p.ar_mode == 2 && lane == 0) {
+      uint32_t it = 0;
+      for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it) {
+        const uint32_t slot = it & 1u, ph = (it >> 1) & 1u;
+        if (!mbar_wait(&sig_full[slot], ph, abort_flag, p.status, 0x630)) break;
+        const int m_tile = item % m_tiles;
+        const int n_tile = (item / m_tiles) % p.n_tiles;
+        const int owner = min(m_tile / p.rs_tiles_per_rank, p.ar_world - 1);
+        const int local_tile = m_tile - owner * p.rs_tiles_per_rank;
+        if (*abort_flag == 0u)
+          st_release_sys_u32(p.ar_flags[owner] + ((size_t)local_tile * p.n_tiles + n_tile) * 8 + p.ar_rank, ar_epoch);
+        mbar_arrive(&sig_free[slot]);
+      }
+    }
   } else if (warp >= kCtrlWarps) {
     // ------------------------------------------------------------------ epilogue
     const int e = warp - kCtrlWarps;
@@ -332,6 +389,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     uint32_t acc_iter = 0;
     uint32_t tile_iter = 0;
     uint32_t sc_slot = 0, sc_phase = 0;      // mirrors the producer's position in the activation-scale ring
+    uint32_t rs_it = 0;                      // tiles handed to the signal warp (reduce-scatter mode)
     bool ok = true;
     float acc[HALF];
     // This loop never exits early: the split-K path below uses named barriers that need all eight warps.
@@ -352,10 +410,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       ++tile_iter;
       if (FP8) {
         const int nkb = kb1 - kb0;
-        constexpr int kRows = BLOCK_N > 128 ? 2 : 1;
+        const int kRows = (BLOCK_N > 128 || p.epi_mode == 1) ? 2 : 1;
         for (int i = epi_tid; i < kRows * nkb; i += 32 * kEpiWarps) {
           const int r = i / nkb, g = i - r * nkb;
-          const int nb = (n_tile * BLOCK_N) / 128 + r;
+          // SwiGLU mode: row 0 = the gate rows' block, row 1 = the up rows' block of this tile's activation columns
+          const int nb = p.epi_mode == 1 ? ((r ? p.act_cols : 0) + n_tile * (BLOCK_N / 2)) / 128 : (n_tile * BLOCK_N) / 128 + r;
           const float* bsrc = p.b_scale + (p.tile_expert ? (size_t)p.tile_expert[m_tile] * p.b_scale_expert_stride : 0);
           bs_buf[r * Cfg::kBScaleMax + g] = (nb * 128 < p.N) ? __ldg(bsrc + (size_t)nb * p.b_scale_ld + kb0 + g) : 0.f;
         }
@@ -366,13 +425,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       } else if (FP8) {
 #pragma unroll
         for (int i = 0; i < HALF; ++i) acc[i] = 0.f;
-        const float* bs_row = bs_buf + ((half * HALF) / 128) * Cfg::kBScaleMax;
+        const float* bs_row = bs_buf + (p.epi_mode == 1 ? 0 : ((half * HALF) / 128) * Cfg::kBScaleMax);
+        const float* bs_row_up = bs_buf + Cfg::kBScaleMax;          // SwiGLU mode: scales of the up rows
         for (int kb = kb0; kb < kb1; ++kb) {
           const uint32_t buf = acc_iter % kAcc, aph = (acc_iter / kAcc) & 1u;
           if (!mbar_wait(&acc_full[buf], aph, abort_flag, p.status, 0x300)) { ok = false; break; }
           tc_fence_after();
           if (!mbar_wait(&sc_full[sc_slot], sc_phase, abort_flag, p.status, 0x302)) { ok = false; break; }
-          const float s = sc_ring[sc_slot * kBlockM + row_in_tile] * bs_row[kb - kb0];
+          const float a_s = sc_ring[sc_slot * kBlockM + row_in_tile];
+          const float s = a_s * bs_row[kb - kb0];
           if (++sc_slot == kScaleSlots) { sc_slot = 0; sc_phase ^= 1u; }
           const uint32_t taddr = tmem_base + t_lane + buf * BLOCK_N + half * HALF;
           // Pull the partial tile into registers with back-to-back tcgen05.ld, hand the TMEM buffer back to the
@@ -382,6 +443,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           // accumulators: 64 columns for a 64-column thread, 32 for 128 columns, 16 under the 112-register budget.
           constexpr int kChunk = kEpiWarps > 8 ? 16 : (HALF > 64 ? 32 : 64);
           const uint64_t s2 = pack_f32x2(s, s);
+          uint64_t s2_up = s2;
+          if (HALF == 64 && p.epi_mode == 1) { const float su = a_s * bs_row_up[kb - kb0]; s2_up = pack_f32x2(su, su); }
 #pragma unroll
           for (int c0 = 0; c0 < HALF; c0 += kChunk) {
             uint32_t r[kChunk];
@@ -398,7 +461,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               if (lane == 0) mbar_arrive(&acc_empty[buf]);
             }
 #pragma unroll
-            for (int i = 0; i < kChunk; i += 2) ffma2(acc[c0 + i], acc[c0 + i + 1], r[i], r[i + 1], s2);
+            for (int i = 0; i < kChunk; i += 2)
+              ffma2(acc[c0 + i], acc[c0 + i + 1], r[i], r[i + 1], (HALF == 64 && c0 + i >= 32) ? s2_up : s2);
           }
           ++acc_iter;
         }
@@ -558,9 +622,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             }
           }
         }
-        asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
-        if (epi_tid == 0)
-          st_release_sys_u32(p.ar_flags[owner] + ((size_t)local_tile * p.n_tiles + n_tile) * 8 + p.ar_rank, ar_epoch);
+        // hand the tile to the signal warp: slot (item count & 1), reused once the signal warp has released it
+        {
+          const uint32_t slot = rs_it & 1u, round = rs_it >> 1;
+          __syncwarp();
+          if (lane == 0) {
+            if (round > 0 && !mbar_wait(&sig_free[slot], (round - 1) & 1u, abort_flag, p.status, 0x631)) ok = false;
+            mbar_arrive(&sig_full[slot]);
+          }
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          ++rs_it;
+        }
       } else if (FUSE_AR) {
         store_now = false;
         const int tile_id = n_tile * m_tiles + m_tile;
@@ -584,6 +656,114 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (epi_tid == 0)
           st_release_sys_u32(p.ar_flags[owner] + (size_t)tile_id * 8 + p.ar_rank, ar_epoch);
       }
+      // ---- deferred RMSNorm factor of the A operand: one multiplier per output row
+      if (p.ss_in != nullptr && store_now && m < M_rows) {
+        float t = 0.f;
+        for (int j = 0; j < p.ss_in_parts; ++j) t += __ldg(p.ss_in + (size_t)j * p.ss_in_ld + m);
+        const float rstd = rsqrtf(t * p.ss_inv_h + p.ss_eps);
+#pragma unroll
+        for (int i = 0; i < HALF; ++i) acc[i] *= rstd;
+      }
+      if (HALF == 64 && p.epi_mode == 1) {
+        // ---- SwiGLU + FP8 group quantisation: acc[0..31] = gate, acc[32..63] = up of activation columns
+        // a0 + 32 * half + i; the four column slices of the 256-wide tile share one 128-wide quantisation group
+        constexpr int kPartsPerGroup = 256 / BLOCK_N == 1 ? 4 : 2;       // 128-wide tiles hold half a group: not used
+        const bool live = store_now && m < M_rows;
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float g = acc[i], u = acc[32 + i];
+          const float v = __bfloat162float(__float2bfloat16_rn(__fdividef(g, 1.f + __expf(-g)) * u));
+          acc[i] = v;
+          amax = fmaxf(amax, fabsf(v));
+        }
+        xch[half * kBlockM + row_in_tile] = amax;
+        asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
+        const int g0 = (half / kPartsPerGroup) * kPartsPerGroup;
+#pragma unroll
+        for (int j = 0; j < kPartsPerGroup; ++j) amax = fmaxf(amax, xch[(g0 + j) * kBlockM + row_in_tile]);
+        if (live) {
+          const float sc = fmaxf(amax, 1e-10f) / 448.f;
+          const float inv = __frcp_rn(sc);
+          const int col = n_tile * (BLOCK_N / 2) + half * 32;
+          uint32_t w[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(acc[4 * j] * inv, acc[4 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+            const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(acc[4 * j + 2] * inv, acc[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+            w[j] = lo | (hi << 16);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(p.q_out + (size_t)m * p.ldq + col);
+          dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+          dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+          if (half == g0) p.s_out[(size_t)(col >> 7) * p.s_ld + m] = sc;
+        }
+        asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));      // the exchange area is reused by the next tile
+      } else if (HALF == 64 && p.epi_mode == 2) {
+        // ---- residual add + RMSNorm weight + FP8 group quantisation + per-row sum of squares of this column tile
+        constexpr int kPartsPerGroup = 2;                               // two 64-column threads per 128-wide group
+        const bool live = store_now && m < M_rows;
+        float amax = 0.f, ss = 0.f;
+        if (live) {
+          __nv_bfloat16* rrow = p.residual + (size_t)m * p.ldr + n_base;
+#pragma unroll
+          for (int j = 0; j < HALF; j += 8) {
+            const uint4 rv = *reinterpret_cast<const uint4*>(rrow + j);
+            const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rv);
+            uint4 ov;
+            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 r2 = __bfloat1622float2(rh[i]);
+              oh[i] = __floats2bfloat162_rn(acc[j + 2 * i] + r2.x, acc[j + 2 * i + 1] + r2.y);
+              const float2 h2 = __bfloat1622float2(oh[i]);          // the rounded residual stream is what gets normalised
+              acc[j + 2 * i] = h2.x; acc[j + 2 * i + 1] = h2.y;
+              ss += h2.x * h2.x + h2.y * h2.y;
+            }
+            *reinterpret_cast<uint4*>(rrow + j) = ov;
+            const uint4 wv = __ldg(reinterpret_cast<const uint4*>(p.norm_w + n_base + j));
+            const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float2 w2 = __bfloat1622float2(wh[i]);
+              if (p.norm_plus_one) { w2.x += 1.f; w2.y += 1.f; }
+              acc[j + 2 * i] *= w2.x; acc[j + 2 * i + 1] *= w2.y;
+              amax = fmaxf(amax, fmaxf(fabsf(acc[j + 2 * i]), fabsf(acc[j + 2 * i + 1])));
+            }
+          }
+        }
+        xch[half * kBlockM + row_in_tile] = amax;
+        xch[(4 + half) * kBlockM + row_in_tile] = ss;
+        asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
+        const int g0 = (half / kPartsPerGroup) * kPartsPerGroup;
+#pragma unroll
+        for (int j = 0; j < kPartsPerGroup; ++j) amax = fmaxf(amax, xch[(g0 + j) * kBlockM + row_in_tile]);
+        if (live) {
+          const float sc = fmaxf(amax, 1e-20f) / 448.f;
+          const float inv = __frcp_rn(sc);
+          uint4* dst = reinterpret_cast<uint4*>(p.q_out + (size_t)m * p.ldq + n_base);
+#pragma unroll
+          for (int v4 = 0; v4 < HALF / 16; ++v4) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int b = v4 * 16 + j * 4;
+              const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(acc[b] * inv, acc[b + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+              const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(acc[b + 2] * inv, acc[b + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+              w[j] = lo | (hi << 16);
+            }
+            dst[v4] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          if (half == g0) p.s_out[(size_t)(n_base >> 7) * p.s_ld + m] = sc;
+          if (half == 0) {
+            float t = 0.f;
+#pragma unroll
+            for (int j = 0; j < kParts; ++j) t += xch[(4 + j) * kBlockM + row_in_tile];      // fixed order
+            p.ss_out[(size_t)n_tile * p.ss_out_ld + m] = t;
+          }
+        }
+        asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
+      } else
       if (store_now && m < M_rows) {
         __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * p.ldc;
 #pragma unroll
@@ -764,7 +944,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
   using Cfg = GemmCfg<BLOCK_N>;
   auto kern = gemm_tcgen05_kernel<BLOCK_N, FP8, FUSE_AR, EPW>;
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), Cfg::kSmemBytes) != cudaSuccess) return -20;
-  return launch_chain_if(p.m_tiles <= 2 && p.tile_expert == nullptr, kern, dim3(grid), dim3(gemm_threads_w(EPW)),
+  return launch_chain_if(p.m_tiles <= 2 && p.tile_expert == nullptr, kern, dim3(grid), dim3(gemm_threads_w(EPW, FUSE_AR)),
                          (size_t)Cfg::kSmemBytes, st, ta, tb, p) == cudaSuccess ? 0 : -21;
 }
 
@@ -799,7 +979,7 @@ static int gemm_impl(int kind, const void* A, const void* B, void* C, const floa
                      long long sa_k, const float* b_scale, int b_scale_ld, int M, int N, int K, long long lda,
                      long long ldb, long long ldc, int block_n, int splits, float* workspace, int* counters,
                      int num_sms, unsigned long long* status, void* stream, const uint32_t* a_ready,
-                     const unsigned int* a_ready_epoch, long long max_cycles) {
+                     const unsigned int* a_ready_epoch, long long max_cycles, const AtlasEpilogue* epi = nullptr) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const uint32_t esize = kind == 1 ? 1 : 2;
   const int elems_per_row = 128 / esize;
@@ -807,14 +987,34 @@ static int gemm_impl(int kind, const void* A, const void* B, void* C, const floa
   if ((lda * esize) % 16 || (ldb * esize) % 16) return -2;
   if (kind == 1 && (K % 128)) return -3;
   if (block_n != 64 && block_n != 128 && block_n != 256) return -4;
+  const int epi_mode = epi ? epi->mode : 0;
+  if (epi_mode < 0 || epi_mode > 2) return -40;
+  if (epi_mode != 0) {
+    // fused epilogues exist for the FP8 kernels whose epilogue threads hold 64 columns of a row
+    if (kind != 1 || !epi->q_out || !epi->s_out || (epi->ldq % 16) || (reinterpret_cast<uintptr_t>(epi->q_out) & 15)) return -41;
+    if (block_n == 256 && wide_fp8_epilogue_warps() != 16) return -42;
+    if (epi_mode == 1 && (block_n != 256 || (N % 256) || ((N / 2) % 128))) return -43;
+    if (epi_mode == 2 && ((block_n != 128 && block_n != 256) || (N % block_n) || !epi->residual || !epi->norm_w || !epi->ss_out ||
+                          (epi->ldr % 8) || (reinterpret_cast<uintptr_t>(epi->residual) & 15) ||
+                          (reinterpret_cast<uintptr_t>(epi->norm_w) & 15)))
+      return -44;
+  }
   CUtensorMap ta, tb;
   int rc = make_tmap_kmajor(&ta, A, M, K, lda, kBlockM, esize);
   if (rc) return rc;
-  rc = make_tmap_kmajor(&tb, B, N, K, ldb, block_n, esize);
+  rc = make_tmap_kmajor(&tb, B, N, K, ldb, epi_mode == 1 ? 32 : block_n, esize);
   if (rc) return rc;
   GemmParams p = {};
   p.C = C; p.a_scale = a_scale; p.b_scale = b_scale; p.workspace = workspace; p.counters = counters;
   p.status = status; p.ldc = ldc; p.sa_k = sa_k; p.M = M; p.N = N; p.K = K;
+  p.epi_mode = epi_mode;
+  if (epi) {
+    p.act_cols = N / 2; p.q_out = reinterpret_cast<uint8_t*>(epi->q_out); p.ldq = epi->ldq; p.s_out = epi->s_out; p.s_ld = epi->s_ld;
+    p.residual = reinterpret_cast<__nv_bfloat16*>(epi->residual); p.ldr = epi->ldr;
+    p.norm_w = reinterpret_cast<const __nv_bfloat16*>(epi->norm_w); p.norm_plus_one = epi->norm_plus_one;
+    p.ss_out = epi->ss_out; p.ss_out_ld = epi->ss_out_ld;
+    p.ss_in = epi->ss_in; p.ss_in_parts = epi->ss_in_parts; p.ss_in_ld = epi->ss_in_ld; p.ss_inv_h = epi->ss_inv_h; p.ss_eps = epi->ss_eps;
+  }
   p.tile_expert = nullptr; p.num_m_tiles_ptr = nullptr; p.expert_n = 0; p.b_scale_expert_stride = 0;
   p.ar_state = nullptr; p.ar_world = 1; p.ar_rank = 0; p.ar_mode = 0; p.ar_parity_stride = 0; p.prefetch_b = 0;
   p.rs_tiles_per_rank = 1; p.a_ready = a_ready; p.a_ready_epoch = a_ready_epoch;
@@ -826,7 +1026,7 @@ static int gemm_impl(int kind, const void* A, const void* B, void* C, const floa
   p.splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
   if (p.splits > 1 && (!workspace || !counters)) return -5;
   p.m_tiles = (M + kBlockM - 1) / kBlockM;
-  p.n_tiles = (N + block_n - 1) / block_n;
+  p.n_tiles = epi_mode == 1 ? (N / 2) / (block_n / 2) : (N + block_n - 1) / block_n;
   if (kind == 1) {
     if (sa_m != 1 || (sa_k % 4) || sa_k < (long long)p.m_tiles * kBlockM) return -6;
     if ((reinterpret_cast<uintptr_t>(a_scale) & 15)) return -7;
@@ -869,6 +1069,18 @@ extern "C" int atlas_gemm_gathered(int kind, const void* A, const void* B, void*
   if (!a_ready || !a_ready_epoch) return -30;
   return gemm_impl(kind, A, B, C, a_scale, sa_m, sa_k, b_scale, b_scale_ld, M, N, K, lda, ldb, ldc, block_n, splits, workspace,
                    counters, num_sms, status, stream, reinterpret_cast<const uint32_t*>(a_ready), a_ready_epoch, max_cycles);
+}
+
+// atlas_gemm with a fused epilogue and / or a deferred RMSNorm factor on the A operand (see AtlasEpilogue in host_api.h
+// and the epi_mode notes in GemmParams).  `C` is unused when epi->mode != 0.
+extern "C" int atlas_gemm_fused(int kind, const void* A, const void* B, void* C, const float* a_scale, long long sa_m,
+                                long long sa_k, const float* b_scale, int b_scale_ld, int M, int N, int K, long long lda,
+                                long long ldb, long long ldc, int block_n, int splits, float* workspace, int* counters,
+                                int num_sms, unsigned long long* status, void* stream, const AtlasEpilogue* epi,
+                                const void* a_ready, const unsigned int* a_ready_epoch, long long max_cycles) {
+  if (!epi) return -40;
+  return gemm_impl(kind, A, B, C, a_scale, sa_m, sa_k, b_scale, b_scale_ld, M, N, K, lda, ldb, ldc, block_n, splits, workspace,
+                   counters, num_sms, status, stream, reinterpret_cast<const uint32_t*>(a_ready), a_ready_epoch, max_cycles, epi);
 }
 
 // Grouped (MoE) GEMM: C[r, :] = A[r, :] * B[e(r)]^T for expert-sorted rows.  `A` has `max_rows` rows (a multiple of

@@ -21,6 +21,25 @@ int atlas_gemm(int kind, const void* A, const void* B, void* C, const float* a_s
                long long ldb, long long ldc, int block_n, int splits, float* workspace, int* counters,
                int num_sms, unsigned long long* status, void* stream);
 
+// Fused epilogue of atlas_gemm_fused (FP8 block-scaled GEMMs).
+//   mode 0  plain bf16 store of C (only the deferred-norm factor below is applied)
+//   mode 1  B = [gate rows; up rows] (N = 2 * I): silu(gate) * up, FP8 e4m3 in 128-wide groups -> q_out [M, I] (row stride
+//           ldq) and s_out (scale(m, g) = s_out[g * s_ld + m])
+//   mode 2  C + residual -> residual (in place, row stride ldr); (residual * norm_w [+1]) FP8-quantised -> q_out / s_out;
+//           per-row sum of squares of every column tile -> ss_out[tile * ss_out_ld + m].  The 1/rms factor of the row is
+//           left to the GEMM that consumes q_out, which gets the same array as ss_in.
+//   ss_in   (any mode) deferred RMSNorm factor of the A operand: every output row m is scaled by
+//           rsqrt(sum_{j < ss_in_parts} ss_in[j * ss_in_ld + m] * ss_inv_h + ss_eps).
+typedef struct AtlasEpilogue {
+  int mode;
+  void* q_out; long long ldq;
+  float* s_out; long long s_ld;
+  void* residual; long long ldr;
+  const void* norm_w; int norm_plus_one;
+  float* ss_out; long long ss_out_ld;
+  const float* ss_in; int ss_in_parts; long long ss_in_ld; float ss_inv_h; float ss_eps;
+} AtlasEpilogue;
+
 // ---- fused elementwise / norm / rope / KV write (elementwise.cu)
 int atlas_rmsnorm(const void* x, long long ldx, const void* residual, long long ldr, const void* w, void* res_out,
                   long long ldro, void* y, long long ldy, void* q, long long ldq, float* scale, long long scale_ld,
@@ -108,6 +127,7 @@ int atlas_sample(const void* logits, long long ld, int B, int V, int is_bf16, co
                  const int* top_k, const float* top_p, const float* min_p, const float* uniform, long long* out,
                  void* stream);
 int atlas_spec_accept(const long long* draft, const long long* target, int B, int K, int* n_acc, void* stream);
+int atlas_logit_edits(float* logits, long long ld, int B, int V, const void* edits, int n, void* stream);
 
 #ifdef __cplusplus
 }

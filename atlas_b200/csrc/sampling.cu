@@ -307,13 +307,38 @@ sample_kernel(const T* __restrict__ logits, long long ld, int V, const float* te
   }
 }
 
-// Greedy speculative acceptance: draft [B,K], target [B,K+1] -> n_accepted [B]
+// Greedy speculative acceptance: draft [B,K] (-1 = no draft at that depth), target [B,K+1] -> n_accepted [B]
 __global__ void spec_accept_kernel(const long long* draft, const long long* target, int K, int* n_acc, int B) {
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
   int n = 0;
-  while (n < K && draft[(long long)b * K + n] == target[(long long)b * (K + 1) + n]) ++n;
+  while (n < K && draft[(long long)b * K + n] >= 0 && draft[(long long)b * K + n] == target[(long long)b * (K + 1) + n]) ++n;
   n_acc[b] = n;
+}
+
+// Sparse logit edits of one sampling step, one thread per (row, token) pair; a pair appears at most once in the list,
+// so no two threads touch the same element.  The edit is the composition, in the pipeline's order, of
+//   x += add          (logit bias)
+//   x = x > 0 ? x / rep : x * rep      (repetition penalty, rep != 1)
+//   x -= sub          (presence + frequency + DRY penalties)
+//   x = -inf          (flag bit 0: token banned at this step, e.g. EOS before min_tokens)
+struct LogitEdit {
+  int row, token;
+  float add, rep, sub;
+  int flags;
+};
+__global__ void __launch_bounds__(256)
+logit_edit_kernel(float* logits, long long ld, const LogitEdit* __restrict__ edits, int n, int V, int B) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const LogitEdit e = edits[i];
+  if (e.row < 0 || e.row >= B || e.token < 0 || e.token >= V) return;
+  float* p = logits + (long long)e.row * ld + e.token;
+  float x = *p + e.add;
+  if (e.rep != 1.f) x = x > 0.f ? x / e.rep : x * e.rep;
+  x -= e.sub;
+  if (e.flags & 1) x = -INFINITY;
+  *p = x;
 }
 
 }  // namespace atlas
@@ -348,5 +373,14 @@ extern "C" int atlas_sample(const void* logits, long long ld, int B, int V, int 
 extern "C" int atlas_spec_accept(const long long* draft, const long long* target, int B, int K, int* n_acc, void* stream) {
   if (B <= 0) return 0;
   spec_accept_kernel<<<(B + 127) / 128, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(draft, target, K, n_acc, B);
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+// `edits`: n records of {int row, int token, float add, float rep, float sub, int flags} (24 bytes each) on the device;
+// `logits` fp32 [B, V] with row stride ld, edited in place.
+extern "C" int atlas_logit_edits(float* logits, long long ld, int B, int V, const void* edits, int n, void* stream) {
+  if (n <= 0) return 0;
+  logit_edit_kernel<<<(n + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      logits, ld, reinterpret_cast<const LogitEdit*>(edits), n, V, B);
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
 }

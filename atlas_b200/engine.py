@@ -241,6 +241,7 @@ class LLMEngine:
             with phase("logits"):
                 # every rank: the vocab-parallel gather / exchange is a collective
                 logits = self.runner.greedy_tokens(hidden, rows) if greedy_tp else self.runner.logits(hidden, rows)
+            self._device_accept = None
             if not follower:
                 so = SamplerOutput(logits.tolist()) if greedy_tp else (
                     self.sampler(logits, seqs_rows) if not verify else self._sample_verify_rows(logits, out, row_owner))
@@ -296,9 +297,13 @@ class LLMEngine:
             new_tokens: List[int] = []
             if it.verify_drafts:
                 targets = sampled[idx]
-                n_acc = 0
-                while n_acc < it.verify_drafts and seq.drafts[n_acc] == targets[n_acc]:
-                    n_acc += 1
+                dev_acc = getattr(self, "_device_accept", None)
+                if dev_acc is not None and idx in dev_acc:
+                    n_acc = dev_acc[idx]                    # counted on the device (spec_accept kernel)
+                else:
+                    n_acc = 0
+                    while n_acc < it.verify_drafts and seq.drafts[n_acc] == targets[n_acc]:
+                        n_acc += 1
                 new_tokens = targets[:n_acc + 1]
                 seq.spec_proposed += it.verify_drafts
                 seq.spec_accepted += n_acc
@@ -359,8 +364,28 @@ class LLMEngine:
             k = seen.get(i, 0)
             seen[i] = k + 1
             seqs.append(_RowView(out.items[i].seq, k))
-        so = self.sampler(logits, seqs)
-        return so
+        toks, lps = self.sampler.sample_tensor(logits, seqs)
+        # draft acceptance on the device: one (draft, target) row per verify item, then a single read-back of the
+        # sampled tokens together with the accepted counts
+        items = [i for i in dict.fromkeys(row_owner) if out.items[i].verify_drafts]
+        kmax = max(out.items[i].verify_drafts for i in items)
+        draft = torch.full((len(items), kmax), -1, dtype=torch.int64)
+        gather = torch.zeros(len(items), kmax + 1, dtype=torch.int64)
+        first_row: Dict[int, int] = {}
+        for r, i in enumerate(row_owner):
+            first_row.setdefault(i, r)
+        for j, i in enumerate(items):
+            k = out.items[i].verify_drafts
+            draft[j, :k] = torch.tensor(out.items[i].seq.drafts[:k], dtype=torch.int64)
+            gather[j, :k + 1] = torch.arange(first_row[i], first_row[i] + k + 1)
+        dev = toks.device
+        if dev.type == "cuda":
+            draft, gather = draft.pin_memory().to(dev, non_blocking=True), gather.pin_memory().to(dev, non_blocking=True)
+        from . import ops as _ops
+        n_acc = _ops.spec_accept(draft, toks[gather])
+        both = torch.cat([toks, n_acc.to(torch.int64)]).tolist()
+        self._device_accept = {i: int(both[len(row_owner) + j]) for j, i in enumerate(items)}
+        return SamplerOutput(both[:len(row_owner)], lps)
 
     def _append_tokens(self, seq: Sequence, toks: List[int], now: float, lps: Optional[list]) -> List[int]:
         """Append sampled tokens, stopping at EOS / stop ids / max_tokens.  Returns the tokens kept."""

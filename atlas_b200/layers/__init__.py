@@ -4,3 +4,4 @@ from .attention import Attention  # noqa: F401
 from .mlp import DenseMLP  # noqa: F401
 from .moe import MoE  # noqa: F401
 from .gdn import GatedDeltaNet  # noqa: F401
+from .mamba2 import Mamba2Mixer  # noqa: F401

@@ -19,8 +19,10 @@ from .common import ParallelCtx, make_weight, randn_weight, shard_cols, shard_ro
 
 class DenseMLP:
     def __init__(self, cfg: ModelConfig, pctx: ParallelCtx, quant_kind: str, intermediate: Optional[int] = None,
-                 shard: bool = True):
+                 shard: bool = True, activation: Optional[str] = None):
         self.cfg, self.pctx, self.quant_kind = cfg, pctx, quant_kind
+        # "silu_glu": gate|up GEMM -> silu(gate) * up; "relu2": a single up GEMM -> relu(up)^2 (Nemotron-H)
+        self.activation = activation or getattr(cfg, "mlp_activation", "silu_glu")
         self.inter = intermediate or cfg.intermediate_size
         self.shard = shard and pctx.tp_size > 1 and self.inter % (pctx.tp_size * 128) == 0
         self.gate_up: Optional[LinearWeight] = None
@@ -28,9 +30,12 @@ class DenseMLP:
         self.lora = None                    # lora.LoraSet shared by the model's layers
         self.lora_prefix = ""               # e.g. "layers.3.mlp."
 
-    def load(self, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> None:
+    def load(self, gate: Optional[torch.Tensor], up: torch.Tensor, down: torch.Tensor) -> None:
         tp, r = (self.pctx.tp_size, self.pctx.tp_rank) if self.shard else (1, 0)
-        gu = torch.cat([shard_rows(gate, r, tp), shard_rows(up, r, tp)], 0)
+        if self.activation == "relu2":
+            gu = shard_rows(up, r, tp)
+        else:
+            gu = torch.cat([shard_rows(gate, r, tp), shard_rows(up, r, tp)], 0)
         self.gate_up = make_weight(gu, self.quant_kind)
         self.down = make_weight(shard_cols(down, r, tp).contiguous(), self.quant_kind)
 
@@ -42,11 +47,23 @@ class DenseMLP:
 
     def hidden_act(self, act: Act) -> Act:
         """gate|up GEMM + SiLU * mul: the input of the down projection (no adapters)."""
+        if self.down.kind == "fp8_block" and ops.swiglu_fusable(act, self.gate_up):
+            return ops.linear_swiglu(act, self.gate_up)
         return ops.silu_mul_act(ops.linear(act, self.gate_up), want_fp8=self.down.kind == "fp8_block")
 
+    def _relu2(self, act: Act, reduce: bool) -> torch.Tensor:
+        u = ops.linear(act, self.gate_up)
+        a = ops.relu_squared(u)
+        return self.pctx.row_parallel_linear(a, self.down) if (self.shard and reduce) else ops.linear(a, self.down)
+
     def forward(self, act: Act, reduce: bool = True, batch=None) -> torch.Tensor:
-        gu = ops.linear(act, self.gate_up)
+        if self.activation == "relu2":
+            return self._relu2(act, reduce)
         use_lora = self.lora is not None and batch is not None and batch.adapter_rows is not None and self.lora_prefix
+        if not use_lora and self.down.kind == "fp8_block" and ops.swiglu_fusable(act, self.gate_up):
+            a = ops.linear_swiglu(act, self.gate_up)
+            return self.pctx.row_parallel_linear(a, self.down) if (self.shard and reduce) else ops.linear(a, self.down)
+        gu = ops.linear(act, self.gate_up)
         if use_lora:
             xin, half = act.plain(), gu.shape[1] // 2
             add_delta(gu, self.lora, self.lora_prefix + "gate_proj", xin, batch, 0, half)

@@ -161,9 +161,68 @@ def _load_layer(ck, pre, layer, model, dense_kind, expert_kind) -> None:
         _load_mlp(ck, f"{pre}.mlp", layer.ffn, model, dense_kind)
 
 
+def _load_mamba2(ck, pre, mixer, model, kind) -> None:
+    """HF ``mixer.in_proj`` rows are ``[z | x | B | C | dt]`` over all heads / groups; the rank's slices are cut on the
+    (possibly quantised) tensor and re-fused."""
+    cfg, r = mixer.cfg, mixer.pctx.tp_rank
+    HP, GN, Hh = cfg.mamba_num_heads * cfg.mamba_head_dim, cfg.mamba_n_groups * cfg.ssm_state_size, cfg.mamba_num_heads
+    di, gn, hh = mixer.d_inner, mixer.g * mixer.n, mixer.h
+    inp = ck.linear(f"{pre}.in_proj")
+    offs = [0, HP, 2 * HP, 2 * HP + GN, 2 * HP + 2 * GN]
+    sizes = [di, di, gn, gn, hh]
+    parts = [inp.rows(o + r * n, o + (r + 1) * n) for o, n in zip(offs, sizes)]
+    fused = cat_rows(parts)
+    mixer.in_proj = _lin(fused, kind, model)
+    cw = ck.get(f"{pre}.conv1d.weight")
+    cw = cw.reshape(cw.shape[0], -1)
+    cut = lambda t: torch.cat([t[o + r * n:o + (r + 1) * n] for o, n in zip([0, HP, HP + GN], [di, gn, gn])], 0)
+    mixer.conv_w = cut(cw).to(device=model.device, dtype=model.dtype).contiguous()
+    cb = ck.maybe(f"{pre}.conv1d.bias")
+    mixer.conv_b = None if cb is None else cut(cb).to(device=model.device, dtype=model.dtype).contiguous()
+    hs = slice(r * hh, (r + 1) * hh)
+    mixer.A_log = ck.get(f"{pre}.A_log")[hs].float().to(model.device).contiguous()
+    mixer.D = ck.get(f"{pre}.D")[hs].float().to(model.device).contiguous()
+    mixer.dt_bias = ck.get(f"{pre}.dt_bias")[hs].float().to(model.device).contiguous()
+    mixer.norm_w = ck.get(f"{pre}.norm.weight")[r * di:(r + 1) * di].to(device=model.device, dtype=model.dtype).contiguous()
+    mixer.out_proj = _lin(ck.linear(f"{pre}.out_proj").cols(r * di, (r + 1) * di), kind, model)
+
+
+def _load_single_blocks(model: DecoderLM, ck: Checkpoint, dense_kind: str) -> None:
+    """Nemotron-H naming: ``backbone.embeddings``, ``backbone.layers.N.{norm, mixer.*}``, ``backbone.norm_f``."""
+    root = "backbone" if any(k.startswith("backbone.") for k in ck.keys()) else "model"
+    emb = ck.maybe(f"{root}.embeddings.weight")
+    if emb is None:
+        emb = ck.get(f"{root}.embedding.weight")            # spelling of the original checkpoints
+    model.embed = emb.to(device=model.device, dtype=model.dtype)
+    for i, blk in enumerate(model.layers):
+        pre = f"{root}.layers.{i}"
+        blk.input_norm = _vec(ck, f"{pre}.norm.weight", model)
+        if blk.kind == "mamba2":
+            _load_mamba2(ck, f"{pre}.mixer", blk.mixer, model, dense_kind)
+        elif blk.kind == "attention":
+            _load_attention(ck, f"{pre}.mixer", blk.mixer, model, dense_kind)
+        else:
+            mlp = blk.ffn
+            tp, r = (mlp.pctx.tp_size, mlp.pctx.tp_rank) if mlp.shard else (1, 0)
+            s = mlp.inter // tp
+            mlp.gate_up = _lin(ck.linear(f"{pre}.mixer.up_proj").rows(r * s, (r + 1) * s), dense_kind, model)
+            mlp.down = _lin(ck.linear(f"{pre}.mixer.down_proj").cols(r * s, (r + 1) * s), dense_kind, model)
+    model.final_norm = _vec(ck, f"{root}.norm_f.weight", model)
+    head = ck.maybe("lm_head.weight")
+    if head is None or model.cfg.tie_word_embeddings:
+        head = model.embed
+    model.set_lm_head(head.to(device=model.device, dtype=model.dtype))
+    model.mtp = None
+    ck.close()
+
+
 def load_weights(model: DecoderLM, ck: Checkpoint) -> None:
     cfg = model.cfg
     dense_kind, expert_kind = quant_kinds(cfg)
+    if cfg.block_types:
+        if any(k.endswith((".weight_scale_inv", ".weight_scale", ".weight_packed")) for k in ck.keys()):
+            dense_kind = "dense"
+        return _load_single_blocks(model, ck, dense_kind)
     if any(k.endswith((".weight_scale_inv", ".weight_scale", ".weight_packed")) for k in ck.keys()):
         # a pre-quantised checkpoint: what it left in high precision (its ignore list) stays in high precision
         dense_kind = expert_kind = "dense"

@@ -17,7 +17,7 @@ import torch
 
 from .. import ops
 from ..config import ModelConfig
-from ..layers import Attention, DenseMLP, GatedDeltaNet, MoE, ParallelCtx
+from ..layers import Attention, DenseMLP, GatedDeltaNet, Mamba2Mixer, MoE, ParallelCtx
 from ..layers.common import make_weight, randn_weight, shard_rows
 from ..ops import Act, LinearWeight, reference as ref
 from .batch import ForwardBatch
@@ -99,20 +99,95 @@ class DecoderLayer:
     def _ffn_fp8(self) -> bool:
         return (not self.is_moe) and self.ffn.gate_up.kind == "fp8_block"
 
-    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor], batch: ForwardBatch, cache: CacheStore,
-                rope_cache: torch.Tensor):
+    def accepts_prenormed(self) -> bool:
+        """This layer's input norm may be applied by the previous layer's down projection (deferred 1/rms factor): its
+        only consumer of the normalised input is an FP8 linear layer."""
+        return self.kind == "attention" and self.mixer.qkv.kind == "fp8_block" and self.mixer.lora is None
+
+    def forward(self, x, residual: Optional[torch.Tensor], batch: ForwardBatch, cache: CacheStore,
+                rope_cache: torch.Tensor, next_norm: Optional[torch.Tensor] = None):
+        """``x`` is the previous layer's output (to be added to ``residual`` and normalised here) or, when that layer
+        already did both in its down projection's epilogue, the normalised activations as an ``Act``.  With
+        ``next_norm`` (the next layer's input norm weight) this layer may do the same for its successor and return an
+        ``Act`` in place of the plain output."""
         cfg = self.cfg
-        if residual is None:
-            act, _ = ops.rmsnorm_act(x, self.input_norm, cfg.rms_norm_eps, None, cfg.norm_plus_one, self._mixer_fp8())
+        eps, p1 = cfg.rms_norm_eps, cfg.norm_plus_one
+        if isinstance(x, Act):
+            act = x
+        elif residual is None:
+            act, _ = ops.rmsnorm_act(x, self.input_norm, eps, None, p1, self._mixer_fp8())
             residual = x
         else:
-            act, residual = ops.rmsnorm_act(x, self.input_norm, cfg.rms_norm_eps, residual, cfg.norm_plus_one, self._mixer_fp8())
-        if self.kind == "attention":
+            act, residual = ops.rmsnorm_act(x, self.input_norm, eps, residual, p1, self._mixer_fp8())
+        single = self.mixer.pctx.tp_size == 1
+        no_lora = batch.adapter_rows is None
+        dense_fp8_ffn = self._ffn_fp8() and self.ffn.down.kind == "fp8_block"
+        if (self.kind == "attention" and single and no_lora and dense_fp8_ffn
+                and ops.residual_norm_fusable(act, self.mixer.o) and residual.is_contiguous()):
+            # o_proj + residual add + post-attention norm + FP8 quantisation in the projection's epilogue
+            out = self.mixer.mix(act, batch, cache.layer_kv(self.idx), rope_cache)
+            act, residual = ops.linear_residual_norm(Act(x=out), self.mixer.o, residual, self.post_norm, eps, p1)
+        else:
+            if self.kind == "attention":
+                h = self.mixer.forward(act, batch, cache.layer_kv(self.idx), rope_cache)
+            else:
+                h = self.mixer.forward(act, batch, cache.states[self.idx])
+            act, residual = ops.rmsnorm_act(h, self.post_norm, eps, residual, p1, self._ffn_fp8())
+        if (next_norm is not None and single and no_lora and dense_fp8_ffn and residual.is_contiguous()
+                and ops.residual_norm_fusable(act, self.ffn.down) and ops.on_gpu(residual)):
+            # down_proj + residual add + the NEXT layer's input norm + FP8 quantisation in one epilogue
+            return ops.linear_residual_norm(self.ffn.hidden_act(act), self.ffn.down, residual, next_norm, eps, p1)
+        h = self.ffn.forward(act) if self.is_moe else self.ffn.forward(act, batch=batch)
+        return h, residual
+
+
+class SingleBlock:
+    """A pre-norm residual block around ONE module (Nemotron-H): a Mamba-2 mixer, a position-free attention layer or a
+    two-projection relu^2 MLP.  Same ``forward`` protocol as :class:`DecoderLayer`: the block's output is added to the
+    residual stream by the next block's norm kernel."""
+
+    def __init__(self, cfg: ModelConfig, idx: int, pctx: ParallelCtx):
+        self.cfg, self.idx = cfg, idx
+        dense_kind, _ = quant_kinds(cfg)
+        self.block = cfg.block_types[idx]
+        self.kind = cfg.layer_kind(idx)
+        self.is_moe = False
+        self.mixer = self.ffn = None
+        if self.kind == "mamba2":
+            self.mixer = Mamba2Mixer(cfg, idx, pctx, dense_kind)
+        elif self.kind == "attention":
+            self.mixer = Attention(cfg, idx, pctx, dense_kind)
+        elif self.block == "mlp":
+            self.ffn = DenseMLP(cfg, pctx, dense_kind, activation="relu2")
+        else:
+            raise ValueError(f"unsupported block type '{self.block}'")
+        self.input_norm: Optional[torch.Tensor] = None
+        self.post_norm = None
+
+    def init_random(self, gen, std, dtype, device):
+        self.input_norm = torch.ones(self.cfg.hidden_size, dtype=dtype, device=device)
+        (self.mixer or self.ffn).init_random(gen, std, dtype, device)
+
+    def accepts_prenormed(self) -> bool:
+        return False
+
+    def _fp8_in(self) -> bool:
+        w = self.mixer.in_proj if self.kind == "mamba2" else (self.mixer.qkv if self.kind == "attention" else self.ffn.gate_up)
+        return w.kind == "fp8_block"
+
+    def forward(self, x, residual, batch: ForwardBatch, cache: CacheStore, rope_cache, next_norm=None):
+        cfg = self.cfg
+        if residual is None:
+            act, _ = ops.rmsnorm_act(x, self.input_norm, cfg.rms_norm_eps, None, cfg.norm_plus_one, self._fp8_in())
+            residual = x
+        else:
+            act, residual = ops.rmsnorm_act(x, self.input_norm, cfg.rms_norm_eps, residual, cfg.norm_plus_one, self._fp8_in())
+        if self.kind == "mamba2":
+            h = self.mixer.forward(act, batch, cache.states[self.idx])
+        elif self.kind == "attention":
             h = self.mixer.forward(act, batch, cache.layer_kv(self.idx), rope_cache)
         else:
-            h = self.mixer.forward(act, batch, cache.states[self.idx])
-        act, residual = ops.rmsnorm_act(h, self.post_norm, cfg.rms_norm_eps, residual, cfg.norm_plus_one, self._ffn_fp8())
-        h = self.ffn.forward(act) if self.is_moe else self.ffn.forward(act, batch=batch)
+            h = self.ffn.forward(act, batch=batch)
         return h, residual
 
 
@@ -123,7 +198,10 @@ class DecoderLM:
         self.pctx = pctx or ParallelCtx()
         self.device = torch.device(device)
         self.dtype = torch_dtype(cfg.dtype)
-        self.layers = [DecoderLayer(cfg, i, self.pctx, ep_mode) for i in range(cfg.num_hidden_layers)]
+        if cfg.block_types:
+            self.layers = [SingleBlock(cfg, i, self.pctx) for i in range(cfg.num_hidden_layers)]
+        else:
+            self.layers = [DecoderLayer(cfg, i, self.pctx, ep_mode) for i in range(cfg.num_hidden_layers)]
         self.embed: Optional[torch.Tensor] = None
         self.final_norm: Optional[torch.Tensor] = None
         self.lm_head: Optional[LinearWeight] = None          # vocab-parallel slice under TP
@@ -183,7 +261,8 @@ class DecoderLM:
         return [l.idx for l in self.layers if l.kind == "attention"]
 
     def gdn_layers(self) -> List[int]:
-        return [l.idx for l in self.layers if l.kind == "gdn"]
+        """Layers with a recurrent state slot (Gated DeltaNet or Mamba-2)."""
+        return [l.idx for l in self.layers if l.kind in ("gdn", "mamba2")]
 
     def kv_bytes_per_block(self, block_size: int, kv_dtype: torch.dtype) -> int:
         n_attn = len(self.attention_layers()) + (1 if self.mtp is not None else 0)
@@ -196,7 +275,7 @@ class DecoderLM:
             if l.kind == "attention":
                 store.kv[l.idx] = alloc_kv(num_blocks, block_size, l.mixer.hkv, self.cfg.head_dim, kv_dtype, self.device)
                 store.kv_scales[l.idx] = (1.0, 1.0)
-            else:
+            elif l.kind in ("gdn", "mamba2"):
                 store.states[l.idx] = l.mixer.alloc_state(max(1, state_slots), self.device, self.dtype)
         if self.mtp is not None:
             self.mtp.alloc_cache(store, num_blocks, block_size, kv_dtype, self.device)
@@ -259,8 +338,13 @@ class DecoderLM:
         if sp is not None:
             return self._forward_seq_parallel(x, batch, cache, sp)
         residual = None
-        for layer in self.layers:
-            x, residual = layer.forward(x, residual, batch, cache, self.rope_cache)
+        if batch.inputs_embeds is not None:
+            x = x.clone()                     # fused epilogues update the residual stream in place
+        n = len(self.layers)
+        for i, layer in enumerate(self.layers):
+            nxt = self.layers[i + 1] if i + 1 < n else None
+            next_norm = nxt.input_norm if (nxt is not None and nxt.accepts_prenormed()) else None
+            x, residual = layer.forward(x, residual, batch, cache, self.rope_cache, next_norm=next_norm)
         self.last_prenorm = (x, residual)
         y, _ = ops.rmsnorm(x, self.final_norm, self.cfg.rms_norm_eps, residual, self.cfg.norm_plus_one)
         return y
@@ -294,7 +378,7 @@ class DecoderLM:
     def commit_spec(self, accepted_rows: List[int], cache: CacheStore) -> None:
         """After speculative verification: fold the accepted rows into every GDN layer's state."""
         for l in self.layers:
-            if l.kind == "gdn":
+            if l.kind in ("gdn", "mamba2"):
                 l.mixer.commit(accepted_rows, cache.states[l.idx])
 
     # ------------------------------------------------------------------ oracle

@@ -87,6 +87,10 @@ class Act:
     # rows still arriving from other ranks (sequence-parallel all-gather): (flags address, epoch address, wait cycles);
     # the consuming GEMM polls the flags tile by tile (parallel/seqpar.py)
     ready: Optional[tuple] = None
+    # deferred RMSNorm factor: ``(q, s)`` hold ``residual * norm_weight`` and every row still has to be multiplied by
+    # rsqrt(sum over parts of sums[part, row] / H + eps); tuple ``(sums [parts, rows_pad] fp32, parts, H, eps)``.  The
+    # factor commutes with a linear layer, so the consuming GEMM applies it to its output rows.
+    row_ss: Optional[tuple] = None
 
     @property
     def out_dtype(self) -> torch.dtype:
@@ -94,7 +98,11 @@ class Act:
 
     def plain(self) -> torch.Tensor:
         if self.x is None:
-            self.x = (self.q.float().view(self.q.shape[0], -1, 128) * self.s[..., None]).view(self.q.shape).to(self.out_dtype)
+            x = (self.q.float().view(self.q.shape[0], -1, 128) * self.s[..., None]).view(self.q.shape)
+            if self.row_ss is not None:
+                sums, parts, h, eps = self.row_ss
+                x = x * torch.rsqrt(sums[:parts, :x.shape[0]].sum(0) / h + eps)[:, None]
+            self.x = x.to(self.out_dtype)
         return self.x
 
     def fp8(self) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -128,6 +136,13 @@ def rmsnorm_act(x, w, eps, residual=None, plus_one=False, want_fp8=False) -> Tup
     return Act(x=y), r
 
 
+def relu_squared(x: torch.Tensor) -> torch.Tensor:
+    """``relu(x) ** 2`` (the activation of Nemotron-H's two-projection MLP)."""
+    if on_gpu(x) and x.dtype == torch.bfloat16 and x.stride(-1) == 1:
+        return cuda_ops().relu_squared(x)
+    return torch.relu(x).square()
+
+
 def silu_mul_act(gate_up: torch.Tensor, want_fp8=False) -> Act:
     inter = gate_up.shape[-1] // 2
     if want_fp8 and inter % 128 == 0:
@@ -146,7 +161,11 @@ def linear(a, w: LinearWeight, out: Optional[torch.Tensor] = None) -> torch.Tens
     """``y = a @ W^T (+ bias)``; ``a`` is a tensor or an :class:`Act`."""
     act = a if isinstance(a, Act) else Act(x=a)
     dev_cuda = on_gpu(act.x if act.x is not None else act.q)
-    if w.kind == "fp8_block":
+    if w.kind == "fp8_block" and act.row_ss is not None and dev_cuda:
+        y = cuda_ops().gemm_fp8_fused(act.q, act.s, w.weight, w.scale, mode=0, out=out, ss_in=act.row_ss, ready=act.ready)
+    elif w.kind == "fp8_block":
+        if act.row_ss is not None:
+            act = Act(x=act.plain())
         q, s = act.fp8()
         if dev_cuda:
             y = cuda_ops().gemm_fp8_block(q, s, w.weight, w.scale, out=out, ready=act.ready)
@@ -167,6 +186,45 @@ def linear(a, w: LinearWeight, out: Optional[torch.Tensor] = None) -> torch.Tens
     if w.bias is not None:
         y = y + w.bias
     return y
+
+
+FUSED_EPILOGUES = True      # tests switch this off to compare against the unfused kernel sequence
+
+
+def swiglu_fusable(a, w: LinearWeight) -> bool:
+    """The gate|up GEMM can apply SiLU * mul and the FP8 quantisation of its output in its own epilogue."""
+    act = a if isinstance(a, Act) else Act(x=a)
+    probe = act.x if act.x is not None else act.q
+    return (FUSED_EPILOGUES and on_gpu(probe) and w.kind == "fp8_block" and w.bias is None and w.weight.shape[0] % 256 == 0
+            and (w.weight.shape[0] // 2) % 128 == 0)
+
+
+def linear_swiglu(a, w: LinearWeight) -> Act:
+    """``silu(gate) * up`` of the stacked gate|up projection as FP8 group-quantised activations (one kernel)."""
+    act = a if isinstance(a, Act) else Act(x=a)
+    if act.row_ss is None:
+        q, s = act.fp8()
+    else:
+        q, s = act.q, act.s
+    qo, so = cuda_ops().gemm_fp8_fused(q, s, w.weight, w.scale, mode=1, ss_in=act.row_ss, ready=act.ready)
+    return Act(q=qo, s=so, dtype=act.out_dtype)
+
+
+def residual_norm_fusable(a, w: LinearWeight) -> bool:
+    act = a if isinstance(a, Act) else Act(x=a)
+    probe = act.x if act.x is not None else act.q
+    return (FUSED_EPILOGUES and on_gpu(probe) and w.kind == "fp8_block" and w.bias is None and w.weight.shape[0] % 128 == 0
+            and act.row_ss is None)
+
+
+def linear_residual_norm(a, w: LinearWeight, residual: torch.Tensor, norm_w: torch.Tensor, eps: float, plus_one: bool):
+    """``residual += a @ W^T`` (in place) and the FP8 form of ``residual * norm_w`` with the row's 1/rms factor left to
+    the consumer (``Act.row_ss``): projection, residual add, RMSNorm and quantisation in one kernel."""
+    act = a if isinstance(a, Act) else Act(x=a)
+    q, s = act.fp8()
+    qo, so, (sums, parts) = cuda_ops().gemm_fp8_fused(q, s, w.weight, w.scale, mode=2, residual=residual, norm_w=norm_w,
+                                                      plus_one=plus_one, ready=act.ready)
+    return Act(q=qo, s=so, dtype=residual.dtype, row_ss=(sums, parts, w.weight.shape[0], eps)), residual
 
 
 # ----------------------------------------------------------------------------- attention
@@ -208,3 +266,30 @@ def sample(logits, temperature, top_k, top_p, min_p, uniform):
     if on_gpu(logits):
         return cuda_ops().sample(logits, temperature, top_k, top_p, min_p, uniform)
     return ref.sample(logits, temperature, top_k, top_p, min_p, uniform)
+
+
+def logit_edits(logits: torch.Tensor, edits: torch.Tensor) -> None:
+    """In-place sparse edits of fp32 ``logits [B, V]``.  ``edits`` is an int32 ``[n, 6]`` tensor of records
+    ``(row, token, add, rep, sub, flags)`` with the three floats stored as their bit patterns; a (row, token) pair
+    appears at most once.  Per record: ``x += add``; ``x = x / rep if x > 0 else x * rep``; ``x -= sub``; bit 0 of
+    ``flags`` sets ``x = -inf``."""
+    if edits.shape[0] == 0:
+        return
+    if on_gpu(logits):
+        cuda_ops().logit_edits(logits, edits)
+        return
+    rows, toks = edits[:, 0].long(), edits[:, 1].long()
+    add, rep, sub = (edits[:, i].view(torch.float32) for i in (2, 3, 4))
+    x = logits[rows, toks] + add
+    x = torch.where(rep != 1.0, torch.where(x > 0, x / rep, x * rep), x) - sub
+    x = torch.where((edits[:, 5] & 1).bool(), torch.full_like(x, float("-inf")), x)
+    logits[rows, toks] = x
+
+
+def spec_accept(draft: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
+    """Greedy draft acceptance: ``draft [B, K]`` (-1 pads), ``target [B, K+1]`` -> accepted draft count per row."""
+    if on_gpu(draft):
+        return cuda_ops().spec_accept(draft, target)
+    B, K = draft.shape
+    ok = (draft == target[:, :K]) & (draft >= 0)
+    return ok.long().cumprod(1).sum(1).to(torch.int32)

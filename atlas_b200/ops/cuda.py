@@ -293,6 +293,97 @@ def _gemm(kind: int, a: torch.Tensor, b: torch.Tensor, a_scale, b_scale, out: Op
     return out
 
 
+class _Epilogue(C.Structure):
+    """Mirror of ``AtlasEpilogue`` (csrc/host_api.h)."""
+    _fields_ = [("mode", _i), ("q_out", _vp), ("ldq", _ll), ("s_out", _vp), ("s_ld", _ll), ("residual", _vp), ("ldr", _ll),
+                ("norm_w", _vp), ("norm_plus_one", _i), ("ss_out", _vp), ("ss_out_ld", _ll), ("ss_in", _vp),
+                ("ss_in_parts", _i), ("ss_in_ld", _ll), ("ss_inv_h", _f), ("ss_eps", _f)]
+
+
+def fused_block_n(mode: int, M: int, N: int, K: int, sms: int) -> Tuple[int, int]:
+    """Tile width and K splits of a fused-epilogue FP8 GEMM: the epilogue needs whole 128-wide quantisation groups
+    inside a tile, i.e. 256-wide tiles for the SwiGLU form and 128- or 256-wide tiles for the residual + norm form."""
+    bn, _ = gemm_plan(M, N, K, 1, sms)
+    if mode == 1:
+        bn = 256
+    elif mode == 2:
+        bn = 256 if (bn == 256 and N % 256 == 0) else 128
+    k_blocks = (K + 127) // 128
+    m_tiles = (M + 127) // 128
+    tiles = m_tiles * ((N // 2) // 128 if mode == 1 else (N + bn - 1) // bn)
+    splits = 1
+    if tiles * 2 <= sms and k_blocks >= 8:
+        splits = max(1, min(sms // tiles, k_blocks // 4, 16))
+    while splits > 1 and splits * m_tiles * 128 * ((N + bn - 1) // bn) * bn * 4 > _GEMM_WS_BYTES:
+        splits -= 1
+    return bn, splits
+
+
+def gemm_fp8_fused(xq, xs, wq, ws, mode: int = 0, out=None, residual=None, norm_w=None, plus_one=False, ss_in=None, ready=None):
+    """FP8 block-scaled GEMM with a fused epilogue (``atlas_gemm_fused``).
+
+    mode 0: returns ``out [M, N]`` bf16.  mode 1 (``wq`` = stacked gate and up rows): returns ``(q [M, N/2] fp8, scales)``
+    of ``silu(gate) * up``.  mode 2: adds ``residual`` (updated in place), returns ``(q [M, N] fp8, scales, ss)`` where
+    ``q`` is the FP8 form of ``residual * norm_w`` and ``ss = (sums [tiles, M_pad], tiles)`` holds the per-row sums of
+    squares the consumer needs for the row's 1/rms factor.  ``ss_in = (sums, tiles, H, eps)`` applies such a deferred
+    factor of the A operand to the output rows."""
+    M, K = xq.shape
+    N = wq.shape[0]
+    d = _dev(xq)
+    sms = _num_sms[d]
+    assert xq.dtype == FP8 and wq.dtype == FP8 and xq.stride(1) == 1 and wq.stride(1) == 1
+    if xs.stride(0) != 1 or xs.stride(1) % 4 or xs.stride(1) < (M + 127) // 128 * 128 or xs.data_ptr() % 16:
+        if ready is not None:
+            raise KernelError("gathered activation scales must already be in the GEMM's k-group-major layout")
+        fixed = _scale_buf(M, xs.shape[1], xq.device)
+        fixed.copy_(xs)
+        xs = fixed
+    bn, splits = fused_block_n(mode, M, N, K, sms) if mode else gemm_plan(M, N, K, 1, sms)
+    if ready is not None:
+        splits = 1
+    wsp = cnt = None
+    if splits > 1:
+        wsp = scratch("gemm_ws", _GEMM_WS_BYTES, xq.device)
+        cnt = scratch("gemm_counters", 1 << 18, xq.device)
+    e = _Epilogue()
+    e.mode = mode
+    res = None
+    if mode == 0:
+        if out is None:
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=xq.device)
+        res = out
+    elif mode == 1:
+        I = N // 2
+        q = torch.empty(M, I, dtype=FP8, device=xq.device)
+        sc = _scale_buf(M, I // 128, xq.device)
+        e.q_out, e.ldq, e.s_out, e.s_ld = q.data_ptr(), I, sc.data_ptr(), sc.stride(1)
+        res = (q, sc)
+    else:
+        assert residual is not None and residual.dtype == torch.bfloat16 and residual.stride(1) == 1 and residual.shape == (M, N)
+        assert norm_w.dtype == torch.bfloat16 and norm_w.is_contiguous()
+        q = torch.empty(M, N, dtype=FP8, device=xq.device)
+        sc = _scale_buf(M, N // 128, xq.device)
+        tiles = N // bn
+        ssb = torch.empty(tiles, (M + 127) // 128 * 128, dtype=torch.float32, device=xq.device)
+        e.q_out, e.ldq, e.s_out, e.s_ld = q.data_ptr(), N, sc.data_ptr(), sc.stride(1)
+        e.residual, e.ldr, e.norm_w, e.norm_plus_one = residual.data_ptr(), residual.stride(0), norm_w.data_ptr(), 1 if plus_one else 0
+        e.ss_out, e.ss_out_ld = ssb.data_ptr(), ssb.stride(0)
+        res = (q, sc, (ssb, tiles))
+    if ss_in is not None:
+        sums, parts, H, eps = ss_in
+        e.ss_in, e.ss_in_parts, e.ss_in_ld, e.ss_inv_h, e.ss_eps = sums.data_ptr(), parts, sums.stride(0), 1.0 / H, float(eps)
+    L = lib()
+    if not getattr(L, "_fused_bound", False):
+        L.atlas_gemm_fused.argtypes = L.atlas_gemm.argtypes + [C.POINTER(_Epilogue), _vp, _vp, _ll]
+        L._fused_bound = True
+    rdy = ready if ready is not None else (None, None, 0)
+    _check(L.atlas_gemm_fused(1, xq.data_ptr(), wq.data_ptr(), _ptr(out) if mode == 0 else None, xs.data_ptr(), xs.stride(0),
+                              xs.stride(1), ws.data_ptr(), ws.shape[1], M, N, K, xq.stride(0), wq.stride(0),
+                              out.stride(0) if mode == 0 else 0, bn, splits, _ptr(wsp), _ptr(cnt), sms, _status_ptr[d], _stream(),
+                              C.byref(e), rdy[0], rdy[1], rdy[2]), "gemm_fused")
+    return res
+
+
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out=None) -> torch.Tensor:
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     if x.stride(1) != 1 or (x.stride(0) * 2) % 16 or x.data_ptr() % 16:
@@ -487,6 +578,18 @@ def sample(logits, temperature, top_k, top_p, min_p, uniform):
     return out
 
 
+def logit_edits(logits: torch.Tensor, edits: torch.Tensor) -> None:
+    """Apply ``edits [n, 6]`` (int32 view of {row, token, add, rep, sub, flags} records) to fp32 ``logits`` in place."""
+    B, V = logits.shape
+    _dev(logits)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and edits.dtype == torch.int32 and edits.is_contiguous()
+    L = lib()
+    if not getattr(L, "_edits_bound", False):
+        L.atlas_logit_edits.argtypes = [_vp, _ll, _i, _i, _vp, _i, _vp]
+        L._edits_bound = True
+    _check(L.atlas_logit_edits(logits.data_ptr(), logits.stride(0), B, V, edits.data_ptr(), edits.shape[0], _stream()), "logit_edits")
+
+
 def spec_accept(draft: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
     B, K = draft.shape
     _dev(draft)
@@ -515,3 +618,23 @@ def gdn_forward(layer, mixed, a, b, batch, state, commit):
 def gdn_commit(layer, mixed, a, b, qlens, slots, has_state, state, num_accepted_rows):
     from . import cuda_ext
     return cuda_ext.gdn_commit(layer, mixed, a, b, qlens, slots, has_state, state, num_accepted_rows)
+
+
+def mamba2_forward(layer, xbc, dt, batch, state, commit):
+    from . import cuda_gdn
+    return cuda_gdn.mamba2_forward(layer, xbc, dt, batch, state, commit)
+
+
+def mamba2_commit(layer, xbc, dt, qlens, slots, has_state, state, num_accepted_rows):
+    from . import cuda_gdn
+    return cuda_gdn.mamba2_commit(layer, xbc, dt, qlens, slots, has_state, state, num_accepted_rows)
+
+
+def mamba2_gated_norm(y, z, w, group, eps):
+    from . import cuda_gdn
+    return cuda_gdn.mamba2_gated_norm(y, z, w, group, eps)
+
+
+def relu_squared(x):
+    from . import cuda_gdn
+    return cuda_gdn.relu_squared(x)

@@ -107,3 +107,81 @@ def gdn_forward(layer, mixed, a, b, batch, state, commit):
 def gdn_commit(layer, mixed, a, b, qlens, slots, has_state, state, num_accepted_rows):
     meta = _Meta(qlens, slots, has_state, mixed.device, None, limit=list(num_accepted_rows))
     _run(layer, mixed, a, b, meta, state, True)
+
+
+# ----------------------------------------------------------------------------- Mamba-2 (csrc/mamba2.cu)
+_m2_bound = False
+
+
+def _m2lib():
+    global _m2_bound
+    lib = _lib()
+    if not _m2_bound:
+        _f = C.c_float
+        lib.atlas_conv1d_bias_silu.argtypes = [_vp, _ll, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _vp]
+        lib.atlas_mamba2_scan.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _f, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _i,
+                                          _i, _i, _i, _i, _i, _i, _vp]
+        lib.atlas_mamba2_gated_norm.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _ll, _i, _i, _i, _f, _vp]
+        lib.atlas_relu2.argtypes = [_vp, _ll, _vp, _ll, _i, _i, _vp]
+        _m2_bound = True
+    return lib
+
+
+def _mamba2_run(layer, xbc, dt, meta: _Meta, state, commit: bool):
+    lib, st = _m2lib(), K._stream()
+    K._dev(xbc)
+    T, Cc = xbc.shape
+    conv, h = state["conv"], state["h"]
+    assert conv.dtype == torch.bfloat16 and h.dtype == torch.float32 and conv.is_contiguous() and h.is_contiguous()
+    assert xbc.dtype == torch.bfloat16 and xbc.stride(1) == 1 and dt.stride(1) == 1
+    y = torch.empty(T, Cc, dtype=torch.bfloat16, device=xbc.device)
+    out = torch.empty(T, layer.d_inner, dtype=torch.bfloat16, device=xbc.device)
+    cw = layer.conv_w if layer.conv_w.dtype == torch.bfloat16 else layer.conv_w.bfloat16()
+    cb = None if layer.conv_b is None else (layer.conv_b if layer.conv_b.dtype == torch.bfloat16 else layer.conv_b.bfloat16())
+    K._check(lib.atlas_conv1d_bias_silu(xbc.data_ptr(), xbc.stride(0), cw.data_ptr(), K._ptr(cb), Cc, layer.W, conv.data_ptr(),
+                                        meta.seq_of.data_ptr(), meta.qsl.data_ptr(), meta.slots.data_ptr(), meta.has.data_ptr(),
+                                        y.data_ptr(), Cc, T, st), "mamba2_conv")
+    K._check(lib.atlas_mamba2_scan(y.data_ptr(), Cc, dt.data_ptr(), dt.stride(0), layer.A_log.data_ptr(), layer.D.data_ptr(),
+                                   layer.dt_bias.data_ptr(), float(layer.cfg.mamba_dt_min), h.data_ptr(), out.data_ptr(),
+                                   layer.d_inner, meta.qsl.data_ptr(), meta.slots.data_ptr(), meta.has.data_ptr(),
+                                   K._ptr(meta.limit), meta.snap_rows.data_ptr(), meta.snap_slots.data_ptr(), meta.snaps, meta.B,
+                                   layer.h, layer.p, layer.n, layer.g, 1 if commit else 0, st), "mamba2_scan")
+    if commit:
+        K._check(lib.atlas_gdn_conv_state(xbc.data_ptr(), xbc.stride(0), Cc, layer.W, conv.data_ptr(), meta.qsl.data_ptr(),
+                                          meta.slots.data_ptr(), meta.has.data_ptr(), K._ptr(meta.limit),
+                                          meta.snap_rows.data_ptr(), meta.snap_slots.data_ptr(), meta.snaps, meta.B, st),
+                 "mamba2_conv_state")
+    return out
+
+
+def mamba2_forward(layer, xbc, dt, batch, state, commit):
+    meta = getattr(batch, "_gdn_meta", None)
+    if meta is None:
+        meta = _Meta(batch.query_lens_host, batch.state_slots_host, batch.has_state_host, xbc.device, batch.snapshot_plan)
+        batch._gdn_meta = meta
+    return _mamba2_run(layer, xbc, dt, meta, state, commit)
+
+
+def mamba2_commit(layer, xbc, dt, qlens, slots, has_state, state, num_accepted_rows):
+    meta = _Meta(qlens, slots, has_state, xbc.device, None, limit=list(num_accepted_rows))
+    _mamba2_run(layer, xbc, dt, meta, state, True)
+
+
+def mamba2_gated_norm(y, z, w, group: int, eps: float):
+    T, dI = y.shape
+    out = torch.empty(T, dI, dtype=torch.bfloat16, device=y.device)
+    wb = w if w.dtype == torch.bfloat16 else w.bfloat16()
+    K._check(_m2lib().atlas_mamba2_gated_norm(y.data_ptr(), y.stride(0), z.data_ptr(), z.stride(0), wb.data_ptr(), out.data_ptr(),
+                                              dI, T, dI // group, group, float(eps), K._stream()), "mamba2_gated_norm")
+    return out
+
+
+def relu_squared(x):
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
+        x2 = x2.contiguous()
+    out = torch.empty(x2.shape, dtype=x.dtype, device=x.device)
+    K._dev(x2)
+    K._check(_m2lib().atlas_relu2(x2.data_ptr(), x2.stride(0), out.data_ptr(), out.stride(0), x2.shape[0], x2.shape[1],
+                                  K._stream()), "relu2")
+    return out.view(x.shape)

@@ -69,6 +69,8 @@ def build_rope_cache(rotary_dim: int, max_pos: int, theta: float, scaling: Optio
 
     Supports plain, linear, llama3 and YaRN scaling (reference: ``kernels/gb10/common/rope.cu``).
     """
+    if rotary_dim <= 0:                  # position-free attention (no rotation)
+        return torch.zeros(max_pos, 0, dtype=torch.float32, device=device)
     half = rotary_dim // 2
     inv_freq = 1.0 / (theta ** (torch.arange(0, half, dtype=torch.float64) * 2.0 / rotary_dim))
     mscale = 1.0

@@ -273,6 +273,22 @@ def main() -> int:
                 K.gemm_fp8_block(act.q, act.s, w.weight, w.scale)
                 K.gemm_fp8_block(sp_q, sp_s, w2.weight, w2.scale, out=out2)
             sp_q, sp_s = K.quant_fp8(resid)
+            # the three kernels of the fused form on their own (flags of the previous call stay valid, so each can repeat)
+            fused()
+            t_k1 = _max_over_ranks(_time(lambda: sp.gemm_rs(act, w), iters=10), dist, device)
+            t_g1 = _max_over_ranks(_time(lambda: K.gemm_fp8_block(act.q, act.s, w.weight, w.scale), iters=10), dist, device)
+            sp.gemm_rs(act, w)
+            t_k2 = _max_over_ranks(_time(lambda: sp.reduce_norm(shard, norm_w, 1e-6), iters=10), dist, device)
+            ready_act = sp.reduce_norm(shard, norm_w, 1e-6)
+            t_k3 = _max_over_ranks(_time(lambda: linear(ready_act, w2, out=out2), iters=10), dist, device)
+            t_g2 = _max_over_ranks(_time(lambda: K.gemm_fp8_block(sp_q, sp_s, w2.weight, w2.scale, out=out2), iters=10), dist, device)
+            ar_buf = torch.zeros(T, H, dtype=torch.bfloat16, device=device)
+            t_nccl = _max_over_ranks(_time(lambda: dist.all_reduce(ar_buf), iters=10), dist, device)
+            if rank == 0:
+                print(json.dumps({"bench": "seq_parallel_parts", "shape": tag, "gemm_rs_us": round(t_k1 * 1e3, 1),
+                                  "plain_gemm1_us": round(t_g1 * 1e3, 1), "reduce_norm_gather_us": round(t_k2 * 1e3, 1),
+                                  "gathered_gemm2_us": round(t_k3 * 1e3, 1), "plain_gemm2_us": round(t_g2 * 1e3, 1),
+                                  "nccl_allreduce_TxH_us": round(t_nccl * 1e3, 1)}), flush=True)
             t_f = _max_over_ranks(_time(fused, iters=10), dist, device)
             t_u = _max_over_ranks(_time(unfused, iters=10), dist, device)
             t_g = _max_over_ranks(_time(gemms_only, iters=10), dist, device)

@@ -156,46 +156,111 @@ class Sampler:
         """True when every row is plain greedy: the step only needs the argmax of each logits row."""
         return not any(self._row_needs_slow_path(s) for s in seqs)
 
+    # ------------------------------------------------------------------ sparse edits (bias, min-tokens, penalties)
+    def _row_edits(self, i: int, s, stage_bias: bool, stage_pen: bool, out: Dict[tuple, list]) -> None:
+        """Collect this row's (token -> [add, rep, sub, flags]) edits.  ``stage_bias``: logit bias and the min-tokens
+        ban; ``stage_pen``: repetition / presence / frequency / DRY penalties."""
+        p: SamplingParams = s.sampling
+
+        def slot(tok: int) -> list:
+            e = out.get((i, tok))
+            if e is None:
+                e = out[(i, tok)] = [0.0, 1.0, 0.0, 0]
+            return e
+        if stage_bias:
+            for tok, v in p.logit_bias.items():
+                if 0 <= tok < self.vocab:
+                    slot(tok)[0] += float(v)
+            if p.min_tokens > 0 and s.num_output_tokens < p.min_tokens:
+                for tok in list(self.eos_ids) + list(p.stop_token_ids):
+                    if 0 <= tok < self.vocab:
+                        slot(tok)[3] |= 1
+        if stage_pen and p.needs_penalties:
+            out_toks = s.output_tokens
+            hist = s.prompt_tokens + out_toks
+            if p.repetition_window > 0:
+                hist = hist[-p.repetition_window:]
+            if p.repetition_penalty != 1.0:
+                for tok in set(hist):
+                    slot(tok)[1] = float(p.repetition_penalty)
+            if (p.presence_penalty or p.frequency_penalty) and out_toks:
+                counts: Dict[int, int] = {}
+                for t in out_toks:
+                    counts[t] = counts.get(t, 0) + 1
+                for tok, c in counts.items():
+                    slot(tok)[2] += p.frequency_penalty * c + p.presence_penalty
+            if p.dry_multiplier > 0:
+                for tok, pen in dry_penalty(s.prompt_tokens + out_toks, p, self.vocab).items():
+                    slot(tok)[2] += pen
+
+    def _apply_edits(self, lf: torch.Tensor, edits: Dict[tuple, list]) -> None:
+        """One upload and one kernel for the whole step's edit list."""
+        if not edits:
+            return
+        import numpy as np
+        n = len(edits)
+        rec = np.empty((n, 6), dtype=np.int32)
+        keys = np.fromiter((k for rt in edits.keys() for k in rt), dtype=np.int64, count=2 * n).reshape(n, 2)
+        vals = np.asarray(list(edits.values()), dtype=np.float64)
+        rec[:, 0:2] = keys
+        rec[:, 2:5] = vals[:, 0:3].astype(np.float32).view(np.int32)
+        rec[:, 5] = vals[:, 3].astype(np.int32)
+        t = torch.from_numpy(rec)
+        if lf.is_cuda:
+            t = t.pin_memory().to(lf.device, non_blocking=True)
+        ops.logit_edits(lf, t)
+
     @torch.inference_mode()
     def __call__(self, logits: torch.Tensor, seqs: Sequence["object"]) -> SamplerOutput:
         """``logits [B,V]`` (one row per sequence, same order)."""
+        toks, lps = self.sample_tensor(logits, seqs)
+        return SamplerOutput(toks.tolist(), lps)
+
+    @torch.inference_mode()
+    def sample_tensor(self, logits: torch.Tensor, seqs: Sequence["object"]):
+        """Like calling the sampler, but the tokens stay on the device (``int64 [B]``); returns ``(tokens, logprobs)``."""
         B = logits.shape[0]
         assert B == len(seqs)
         if self.fast_greedy(seqs):
-            return SamplerOutput(ops.argmax(logits).tolist())
+            return ops.argmax(logits), None
         lf = logits.float().clone()
         dev = lf.device
+        # Bias, the min-tokens ban and the penalties are sparse: the whole step's edits go to the device as one list and
+        # one kernel applies them.  A mask (-inf) commutes with every one of these edits, so the grammar masks can run
+        # after them; only rows with caller-supplied processors keep the two-stage order (bias -> processors -> penalties).
+        staged = [i for i, s in enumerate(seqs) if s.logits_processors]
+        edits: Dict[tuple, list] = {}
         for i, s in enumerate(seqs):
-            p: SamplingParams = s.sampling
-            if p.logit_bias:
-                idx = torch.tensor(list(p.logit_bias.keys()), device=dev, dtype=torch.long)
-                lf[i, idx] += torch.tensor(list(p.logit_bias.values()), device=dev, dtype=torch.float32)
-            if p.min_tokens > 0 and s.num_output_tokens < p.min_tokens:
-                stop_ids = list(self.eos_ids) + list(p.stop_token_ids)
-                if stop_ids:
-                    lf[i, torch.tensor(stop_ids, device=dev, dtype=torch.long)] = float("-inf")
+            self._row_edits(i, s, True, i not in staged, edits)
+        self._apply_edits(lf, edits)
+        for i, s in enumerate(seqs):
             if s.grammar is not None:
                 mask = s.grammar.token_mask(self.vocab)
                 if mask is not None:
                     lf[i] = lf[i].masked_fill(~mask.to(dev), float("-inf"))
             for proc in s.logits_processors:
                 lf[i] = proc(lf[i], s)
-            if p.needs_penalties:
-                lf[i] = self._penalise_row(lf[i], s)
-            if p.top_n_sigma > 0:
-                lf[i] = top_n_sigma_mask(lf[i:i + 1], p.top_n_sigma)[0]
-        temp = torch.tensor([s.sampling.temperature for s in seqs], dtype=torch.float32, device=dev)
-        if bool((temp <= 0).all()):
+        if staged:
+            late: Dict[tuple, list] = {}
+            for i in staged:
+                self._row_edits(i, seqs[i], False, True, late)
+            self._apply_edits(lf, late)
+        for i, s in enumerate(seqs):
+            if s.sampling.top_n_sigma > 0:
+                lf[i] = top_n_sigma_mask(lf[i:i + 1], s.sampling.top_n_sigma)[0]
+        if all(s.sampling.temperature <= 0 for s in seqs):
             toks = ops.argmax(lf)
         else:
-            top_k = torch.tensor([s.sampling.top_k for s in seqs], dtype=torch.int32, device=dev)
-            top_p = torch.tensor([s.sampling.top_p for s in seqs], dtype=torch.float32, device=dev)
-            min_p = torch.tensor([s.sampling.min_p for s in seqs], dtype=torch.float32, device=dev)
-            u = torch.tensor([s.rng.uniform(s.num_output_tokens) for s in seqs], dtype=torch.float32, device=dev)
-            toks = ops.sample(lf, temp, top_k, top_p, min_p, u)
-        toks_l = toks.tolist()
+            # the five per-row sampling parameters travel as one packed upload
+            par = torch.tensor([[s.sampling.temperature, float(s.sampling.top_k), s.sampling.top_p, s.sampling.min_p,
+                                 s.rng.uniform(s.num_output_tokens)] for s in seqs], dtype=torch.float32)
+            if lf.is_cuda:
+                par = par.pin_memory().to(dev, non_blocking=True)
+            par = par.t().contiguous()
+            toks = ops.sample(lf, par[0], par[1].to(torch.int32), par[2], par[3], par[4])
         lps = None
         if any(s.sampling.logprobs for s in seqs):
+            toks_l = toks.tolist()
             lps = []
             logp = torch.log_softmax(lf, -1)
             for i, s in enumerate(seqs):
@@ -208,29 +273,4 @@ class Sampler:
                     tv, ti = torch.topk(logp[i], k)
                     entry["top"] = list(zip(ti.tolist(), tv.tolist()))
                 lps.append(entry)
-        return SamplerOutput(toks_l, lps)
-
-    def _penalise_row(self, row: torch.Tensor, s) -> torch.Tensor:
-        p: SamplingParams = s.sampling
-        dev = row.device
-        out_toks = s.output_tokens
-        hist = s.prompt_tokens + out_toks
-        if p.repetition_window > 0:
-            hist = hist[-p.repetition_window:]
-        if p.repetition_penalty != 1.0 and hist:
-            idx = torch.tensor(sorted(set(hist)), device=dev, dtype=torch.long)
-            vals = row[idx]
-            row[idx] = torch.where(vals > 0, vals / p.repetition_penalty, vals * p.repetition_penalty)
-        if (p.presence_penalty or p.frequency_penalty) and out_toks:
-            counts: Dict[int, int] = {}
-            for t in out_toks:
-                counts[t] = counts.get(t, 0) + 1
-            idx = torch.tensor(list(counts.keys()), device=dev, dtype=torch.long)
-            c = torch.tensor(list(counts.values()), device=dev, dtype=torch.float32)
-            row[idx] -= p.frequency_penalty * c + p.presence_penalty
-        if p.dry_multiplier > 0:
-            pen = dry_penalty(s.prompt_tokens + out_toks, p, self.vocab)
-            if pen:
-                idx = torch.tensor(list(pen.keys()), device=dev, dtype=torch.long)
-                row[idx] -= torch.tensor(list(pen.values()), device=dev, dtype=torch.float32)
-        return row
+        return toks, lps

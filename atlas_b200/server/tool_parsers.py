@@ -11,7 +11,7 @@ Dialects: ``hermes`` (``<tool_call>{json}</tool_call>``), ``qwen3_coder`` / ``qw
 (``<｜tool▁call▁begin｜>name<｜tool▁sep｜>{json}<｜tool▁call▁end｜>``), ``gemma`` (```` ```tool_code```` blocks).
 
 Reference parity: ``crates/spark-server/src/tool_parser/*`` (hermes, qwen3_coder, qwen3_xml, mistral, gemma4,
-minimax_xml, deepseek_v4_dsml, bare_json) and the streaming emitters used by ``api/chat_stream/handle_token.rs``.
+minimax_xml, deepseek_v4_dsml, bare_json, lfm3, poolside_v1) and the streaming emitters used by ``api/chat_stream/handle_token.rs``.
 """
 from __future__ import annotations
 
@@ -83,6 +83,7 @@ def _coerce_param(v: str, schema: Optional[dict]) -> Any:
 class ToolParser:
     name = "base"
     markers: Tuple[str, ...] = ()           # strings whose prefix must be held back while streaming
+    system_prompt_tools = True              # False: the model's own chat template renders the tool schemas
 
     def __init__(self, tools: Optional[List[dict]] = None):
         self.tools = tools or []
@@ -133,6 +134,51 @@ class Qwen3CoderParser(ToolParser):
         content = re.sub(r"<tool_call>.*?(?:</tool_call>|$)", "", text, flags=re.S)
         content = self._fn.sub("", content).strip()
         return content, calls
+
+
+class Lfm3Parser(Qwen3CoderParser):
+    """LFM3 emits the qwen3_coder block form (``<tool_call><function=NAME><parameter=K>V</parameter></function>``), so
+    extraction and typed coercion are shared; what differs is the prompt side: the checkpoint's own chat template
+    already renders the tool schemas, so this dialect adds no tool instructions of its own
+    (``system_prompt_tools`` is False; reference: ``crates/spark-server/src/tool_parser/lfm3.rs``)."""
+    name = "lfm3"
+    system_prompt_tools = False
+
+
+class PoolsideV1Parser(ToolParser):
+    """``<tool_call>NAME<arg_key>K</arg_key><arg_value>V</arg_value>...</tool_call>``; values are text, coerced by the
+    declared schema type (reference: ``crates/spark-server/src/tool_parser/poolside_v1.rs``)."""
+    name = "poolside_v1"
+    markers = ("<tool_call>",)
+    system_prompt_tools = False
+    _call = re.compile(r"<tool_call>\s*([^<\s]+)\s*(.*?)(?:</tool_call>|$)", re.S)
+    _kv = re.compile(r"<arg_key>(.*?)</arg_key>\s*<arg_value>(.*?)(?:</arg_value>|(?=<arg_key>)|$)", re.S)
+
+    def parse(self, text):
+        calls = []
+        for m in self._call.finditer(text):
+            name, body = m.group(1), m.group(2)
+            props = self.schemas.get(name, {})
+            args = {k.strip(): _coerce_param(v, props.get(k.strip())) for k, v in self._kv.findall(body)}
+            calls.append(ToolCall(name, json.dumps(args, ensure_ascii=False)))
+        if not calls:
+            return text, []
+        return self._call.sub("", text).strip(), calls
+
+    @staticmethod
+    def format_tool_calls(calls: List[dict]) -> str:
+        """Earlier assistant tool calls rendered back into the dialect (for templates that expect raw text)."""
+        out = []
+        for c in calls:
+            fn = c.get("function", c)
+            try:
+                args = json.loads(fn.get("arguments") or "{}")
+            except ValueError:
+                args = {}
+            body = "".join(f"<arg_key>{k}</arg_key><arg_value>{v if isinstance(v, str) else json.dumps(v)}</arg_value>"
+                           for k, v in (args.items() if isinstance(args, dict) else []))
+            out.append(f"<tool_call>{fn.get('name', '')}{body}</tool_call>")
+        return "".join(out)
 
 
 class MistralParser(ToolParser):
@@ -304,7 +350,8 @@ def _lenient_json(s: str) -> Any:
 
 
 PARSERS = {c.name: c for c in (HermesParser, Qwen3CoderParser, MistralParser, BareJsonParser, MinimaxXmlParser,
-                               DeepseekDsmlParser, GemmaParser)}
+                               DeepseekDsmlParser, GemmaParser, Lfm3Parser, PoolsideV1Parser)}
+PARSERS["poolside"] = PoolsideV1Parser
 PARSERS["qwen3_xml"] = Qwen3CoderParser
 PARSERS["llama3_json"] = BareJsonParser
 PARSERS["gemma4"] = GemmaParser
@@ -332,6 +379,10 @@ def default_parser_for(model_type: str) -> str:
         return "minimax_xml"
     if mt.startswith("deepseek"):
         return "deepseek_dsml"
+    if mt.startswith("lfm"):
+        return "lfm3"
+    if mt.startswith(("laguna", "poolside")):
+        return "poolside_v1"
     return "hermes"
 
 

@@ -343,3 +343,61 @@ def test_lora_bgmv(K):
     assert torch.equal(y[:, :128], y0[:, :128]) and torch.equal(y[:, 128 + N:], y0[:, 128 + N:])
     assert torch.equal(y[slots == 0], y0[slots == 0])
     torch.testing.assert_close(y.float(), want, atol=3e-2, rtol=2e-2)
+
+
+# ----------------------------------------------------------------------------------------------------- fused GEMM epilogues
+@pytest.mark.parametrize("M,I,Kd", [(128, 1024, 512), (300, 2048, 1024), (5, 256, 256)])
+def test_gemm_fused_swiglu_quant(K, M, I, Kd):
+    """gate|up GEMM whose epilogue applies SiLU * mul and quantises to FP8 groups: against fp32 silu(gate) * up of the
+    dequantised operands, and against the unfused kernel sequence."""
+    torch.manual_seed(5)
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    w = torch.randn(2 * I, Kd, device=DEV) * 0.05
+    wq, ws = Q.quantize_fp8_block(w)
+    xq, xs = K.quant_fp8(x)
+    q, s = K.gemm_fp8_fused(xq, xs, wq, ws, mode=1)
+    gu = Q.fp8_block_gemm_ref(xq, xs.contiguous(), wq, ws, out_dtype=torch.float32)
+    want = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    _status_ok(K)
+    deq = (q.float().view(M, -1, 128) * s.contiguous()[..., None]).view(M, I)
+    assert _rel_rms(deq, want) < 4e-2
+    q2, s2 = K.silu_mul(K.gemm_fp8_block(xq, xs, wq, ws), quant=True)
+    deq2 = (q2.float().view(M, -1, 128) * s2.contiguous()[..., None]).view(M, I)
+    assert _rel_rms(deq, deq2) < 3e-2
+
+
+@pytest.mark.parametrize("M,N,Kd,plus_one", [(128, 1024, 512, False), (300, 2048, 4096, True), (3, 512, 2048, False)])
+def test_gemm_fused_residual_norm_quant_and_deferred_factor(K, M, N, Kd, plus_one):
+    """Row-parallel-style GEMM whose epilogue adds the residual, multiplies by the norm weight and quantises, leaving the
+    1/rms factor to the consumer GEMM: the pair must equal GEMM -> residual add -> RMSNorm -> GEMM in fp32."""
+    torch.manual_seed(6)
+    eps = 1e-6
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    w = torch.randn(N, Kd, device=DEV) * 0.05
+    resid = torch.randn(M, N, device=DEV).bfloat16()
+    norm_w = (torch.randn(N, device=DEV) * 0.2 + (0.0 if plus_one else 1.0)).bfloat16()
+    w2 = torch.randn(384, N, device=DEV) * 0.05
+    wq, ws = Q.quantize_fp8_block(w)
+    w2q, w2s = Q.quantize_fp8_block(w2)
+    xq, xs = K.quant_fp8(x)
+    res = resid.clone()
+    q, s, (ss, tiles) = K.gemm_fp8_fused(xq, xs, wq, ws, mode=2, residual=res, norm_w=norm_w, plus_one=plus_one)
+    y = K.gemm_fp8_fused(q, s, w2q, w2s, mode=0, ss_in=(ss, tiles, N, eps))
+    _status_ok(K)
+    h = Q.fp8_block_gemm_ref(xq, xs.contiguous(), wq, ws, out_dtype=torch.float32) + resid.float()
+    assert _rel_rms(res, h) < 1e-2
+    weff = norm_w.float() + (1.0 if plus_one else 0.0)
+    normed = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps) * weff
+    want = normed @ Q.dequantize_fp8_block(w2q, w2s).float().t()
+    assert _rel_rms(y, want) < 4e-2
+    rstd = torch.rsqrt(ss[:, :M].sum(0) / N + eps)
+    assert _rel_rms(rstd, torch.rsqrt(h.pow(2).mean(-1) + eps)) < 1e-2
+    # the deferred factor also composes with the SwiGLU epilogue
+    wg = torch.randn(512, N, device=DEV) * 0.05
+    wgq, wgs = Q.quantize_fp8_block(wg)
+    qa, sa = K.gemm_fp8_fused(q, s, wgq, wgs, mode=1, ss_in=(ss, tiles, N, eps))
+    gu = normed @ Q.dequantize_fp8_block(wgq, wgs).float().t()
+    want_a = torch.nn.functional.silu(gu[:, :256]) * gu[:, 256:]
+    deq = (qa.float().view(M, -1, 128) * sa.contiguous()[..., None]).view(M, 256)
+    _status_ok(K)
+    assert _rel_rms(deq, want_a) < 6e-2

@@ -96,3 +96,54 @@ def test_gathered_gemm_wait_expires_cleanly():
     want = linear(Act(q=q, s=s, dtype=torch.bfloat16), w)
     torch.cuda.synchronize()
     assert K.check_status() == 0 and torch.equal(y, want)
+
+
+def test_allreduce_wait_expires_and_poisons_then_recovers():
+    """`atlas_allreduce_bf16` with world = 2 on ONE GPU: the second "rank" is a local buffer whose flags nobody raises,
+    so the kernel's bounded wait on the peer runs out.  The kernel must return, the status word must name the
+    barrier site, a communicator reading it must poison itself, and after the word is cleared a healthy call works."""
+    import ctypes as C
+    from atlas_b200.ops import cuda as K
+    from atlas_b200.parallel.comm import CommBackend, CommError
+    K.load()
+    lib = K.lib()
+    vp, i, ll, sz = C.c_void_p, C.c_int, C.c_longlong, C.c_size_t
+    lib.atlas_allreduce_bf16.argtypes = [i, C.POINTER(vp), C.POINTER(vp), i, i, vp, vp, sz, sz, vp, i, vp, ll, vp]
+    slot = 1 << 20
+    data = [torch.zeros(2 * slot, dtype=torch.uint8, device=DEV) for _ in range(2)]
+    flags = [torch.zeros(2 * 256 * 8, dtype=torch.int32, device=DEV) for _ in range(2)]
+    state = torch.zeros(4, dtype=torch.int32, device=DEV)
+    x = torch.randn(4096, device=DEV).bfloat16()
+    y = torch.empty_like(x)
+    d = K._dev(x)
+    darr = (vp * 8)(*([t.data_ptr() for t in data] + [None] * 6))
+    farr = (vp * 8)(*([t.data_ptr() for t in flags] + [None] * 6))
+    for kind in (0, 1):
+        rc = lib.atlas_allreduce_bf16(kind, darr, farr, 0, 2, x.data_ptr(), y.data_ptr(), x.numel() * 2, slot, state.data_ptr(), 2,
+                                      K._status_ptr[d], 1_000_000, torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        torch.cuda.synchronize()                       # the kernel came back by itself
+        st = K.check_status(clear=False)
+        assert st & 0xFF == 2 and ((st >> 8) & 0xFFFFFF) in (0x500, 0x501), hex(st)
+
+        class _Probe(CommBackend):
+            name = "probe"
+
+            def check(self):
+                s = K.check_status()
+                if s:
+                    self.poison(f"peer wait expired ({s:#x})")
+                    raise CommError("expired")
+        c = _Probe()
+        with pytest.raises(CommError):
+            c.check()
+        assert c.unhealthy
+        with pytest.raises(CommError):
+            c._guard()
+        assert K.check_status() == 0                   # cleared by the read above
+    # world = 1 degenerates to a copy through the slot and must be healthy after the expired calls
+    state.zero_()
+    rc = lib.atlas_allreduce_bf16(0, darr, farr, 0, 1, x.data_ptr(), y.data_ptr(), x.numel() * 2, slot, state.data_ptr(), 2,
+                                  K._status_ptr[d], 1_000_000, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert rc == 0 and K.check_status() == 0 and torch.equal(x, y)

@@ -42,12 +42,21 @@ def _hf(kind: str):
                                            partial_rotary_factor=0.25, layer_types=["linear_attention", "full_attention"],
                                            **common)
         m = transformers.Qwen3NextForCausalLM(cfg)
+    elif kind == "nemotron_h":
+        cfg = transformers.NemotronHConfig(vocab_size=512, hidden_size=256, layers_block_type=["mamba", "attention", "mamba", "mamba"],
+                                           num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=512,
+                                           mamba_num_heads=8, mamba_head_dim=32, ssm_state_size=32, n_groups=2, conv_kernel=4,
+                                           chunk_size=64, max_position_embeddings=256, tie_word_embeddings=False,
+                                           use_mamba_kernels=False)
+        # chunk_size covers the whole test sequence: the eager fallback of the oracle passes state between chunks
+        # inexactly (its output moves by ~1e-3 with the chunk size), a single chunk is the exact recurrence
+        m = transformers.NemotronHForCausalLM(cfg)
     else:
         raise ValueError(kind)
     m = m.float().eval()
     with torch.no_grad():                      # make norms / biases non-trivial
         for n, p in m.named_parameters():
-            if n.endswith("norm.weight") or n.endswith("layernorm.weight"):
+            if n.endswith("norm.weight") or n.endswith("layernorm.weight") or n.endswith("norm_f.weight"):
                 p.add_(torch.randn_like(p) * 0.1)
             elif n.endswith(".bias"):
                 p.copy_(torch.randn_like(p) * 0.1)
@@ -63,7 +72,7 @@ def _ours_logits(model, toks):
     return model.forward_dense_reference(toks)
 
 
-@pytest.mark.parametrize("kind", ["llama", "qwen2", "qwen3", "qwen3_moe", "qwen3_next"])
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "qwen3", "qwen3_moe", "qwen3_next", "nemotron_h"])
 def test_logits_match_transformers(kind, tmp_path):
     hf = _hf(kind)
     path = _save(hf, tmp_path)
@@ -75,7 +84,7 @@ def test_logits_match_transformers(kind, tmp_path):
     torch.testing.assert_close(got, want, atol=2e-4, rtol=1e-3)
 
 
-@pytest.mark.parametrize("kind", ["qwen3", "qwen3_next"])
+@pytest.mark.parametrize("kind", ["qwen3", "qwen3_next", "nemotron_h"])
 def test_sharded_load_matches_full(kind, tmp_path):
     """TP=2 (dense) / TP=2+EP=2 (hybrid MoE): the ranks, run in lock-step over the in-process fake communicator,
     reproduce the single-rank logits."""

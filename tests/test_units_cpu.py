@@ -31,6 +31,8 @@ TOOLS = [{"type": "function", "function": {"name": "get_weather", "parameters": 
     ("mistral", 'Sure.[TOOL_CALLS][{"name": "get_weather", "arguments": {"city": "Oslo", "days": 3}}]'),
     ("minimax_xml", 'Sure.<minimax:tool_call>\n<invoke name="get_weather">\n<parameter name="city">Oslo</parameter>\n<parameter name="days">3</parameter>\n</invoke>\n</minimax:tool_call>'),
     ("gemma", 'Sure.\n```tool_code\nget_weather(city="Oslo", days=3)\n```'),
+    ("lfm3", "Sure.<tool_call>\n<function=get_weather>\n<parameter=city>\nOslo\n</parameter>\n<parameter=days>\n3\n</parameter>\n</function>\n</tool_call>"),
+    ("poolside_v1", "Sure.<tool_call>get_weather<arg_key>city</arg_key><arg_value>Oslo</arg_value><arg_key>days</arg_key><arg_value>3</arg_value></tool_call>"),
 ])
 def test_tool_parsers_extract_calls(name, text):
     content, calls = get_parser(name, TOOLS).parse(text)
