@@ -220,6 +220,52 @@ allreduce_twoshot_kernel(const SymmCtx c, const uint4* in, uint4* out, size_t n8
   finish_call(state, epoch);
 }
 
+// Expert-parallel combine fused with its reduction (activations replicated across the group, every rank runs its own
+// experts): the weighted top-k sum of this rank's expert outputs is formed straight into the local slot (it never
+// exists as a separate tensor), one flag exchange follows, and every rank then sums all ranks' partials out of their
+// slots in rank order and adds the residual / shared-expert term.  One launch replaces combine + all-reduce.
+//   y [rows, H] expert outputs of the expert-sorted rows, slot_of [T*k] row of each (token, choice) pair or -1 when the
+//   expert lives on another rank, topk_w [T*k] router weights.
+__global__ void __launch_bounds__(512)
+moe_combine_allreduce_kernel(const SymmCtx c, const __nv_bfloat16* __restrict__ y, long long ldy,
+                             const int* __restrict__ slot_of, const float* __restrict__ topk_w, int T, int k, int H,
+                             const __nv_bfloat16* addend, long long ld_add, __nv_bfloat16* out, long long ldo,
+                             size_t slot_bytes, unsigned int* state, status_t* status, long long max_cycles) {
+  __shared__ int ok_slot;
+  const uint32_t epoch = state[0] + 1;
+  const int hv = H >> 3;                                   // 16-byte vectors per row
+  const size_t n8 = (size_t)T * hv;
+  const size_t per = (n8 + gridDim.x - 1) / gridDim.x;
+  const size_t lo = per * blockIdx.x, hi = min(n8, lo + per);
+  const size_t slot_off = (size_t)(epoch & 1u) * slot_bytes;
+  uint4* mine = reinterpret_cast<uint4*>(c.data[c.rank] + slot_off);
+  for (size_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const int t = (int)(i / hv), e = (int)(i % hv) * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < k; ++j) {
+      const int slot = slot_of[t * k + j];
+      if (slot < 0) continue;
+      const float w = topk_w[t * k + j];
+      const uint4 raw = *reinterpret_cast<const uint4*>(y + (long long)slot * ldy + e);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) { const float2 f = __bfloat1622float2(h[q]); acc[2 * q] += w * f.x; acc[2 * q + 1] += w * f.y; }
+    }
+    mine[i] = pack_bf16x8(acc);
+  }
+  const bool ok = peer_barrier(c, 0, epoch, status, max_cycles, &ok_slot);
+  if (ok) {
+    for (size_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      const int t = (int)(i / hv), e = (int)(i % hv) * 8;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      sum_over_ranks(c, slot_off, i, acc);
+      if (addend) add_bf16x8(acc, *reinterpret_cast<const uint4*>(addend + (long long)t * ld_add + e));
+      *reinterpret_cast<uint4*>(out + (long long)t * ldo + e) = pack_bf16x8(acc);
+    }
+  }
+  finish_call(state, epoch);
+}
+
 // All-to-all of variable row counts (expert-parallel dispatch / combine).  Rank s sends rows
 // [send_off[d], send_off[d+1]) of `in` to rank d; they land in d's slot at region s (capacity `region_rows`), with the
 // count in the region header.  After the barrier every rank compacts its regions into `out` and writes recv_off.
@@ -348,5 +394,23 @@ extern "C" int atlas_alltoall_rows(void* const* data, void* const* flags, int ra
   alltoall_rows_kernel<<<blocks, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       c, reinterpret_cast<const uint4*>(in), send_off, reinterpret_cast<uint4*>(out), recv_off, row_bytes / 16, region_rows,
       slot_bytes, state, status, mc);
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+// Expert outputs -> weighted top-k sum -> sum over the expert-parallel group (+ addend) in one kernel; see
+// moe_combine_allreduce_kernel.  T * H * 2 bytes must fit one slot; meant for decode-size steps.
+extern "C" int atlas_moe_combine_allreduce(void* const* data, void* const* flags, int rank, int world, const void* y,
+                                           long long ldy, const int* slot_of, const float* topk_w, int T, int k, int H,
+                                           const void* addend, long long ld_add, void* out, long long ldo, size_t slot_bytes,
+                                           unsigned int* state, int blocks, unsigned long long* status, long long max_cycles,
+                                           void* stream) {
+  if (T <= 0) return 0;
+  if (H % 8 || world > kMaxRanks || blocks > kMaxCommBlocks || blocks < 1 || (ldy % 8) || (ldo % 8) || (addend && (ld_add % 8)))
+    return -1;
+  if ((size_t)T * H * 2 > slot_bytes) return -2;
+  SymmCtx c = make_ctx(data, flags, rank, world);
+  moe_combine_allreduce_kernel<<<blocks, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      c, reinterpret_cast<const __nv_bfloat16*>(y), ldy, slot_of, topk_w, T, k, H, reinterpret_cast<const __nv_bfloat16*>(addend),
+      ld_add, reinterpret_cast<__nv_bfloat16*>(out), ldo, slot_bytes, state, status, max_cycles > 0 ? max_cycles : kFlagMaxCycles);
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
 }

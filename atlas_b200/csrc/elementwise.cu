@@ -504,6 +504,51 @@ lora_bgmv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const long 
   }
 }
 
+// x[t, :] *= sigmoid(gate[t, :]) in place (the output gate of gated attention); n % 8 == 0
+__global__ void __launch_bounds__(256)
+sigmoid_gate_mul_kernel(__nv_bfloat16* x, long long ldx, const __nv_bfloat16* __restrict__ gate, long long ldg, int n) {
+  const long long t = blockIdx.x;
+  for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8; c < n; c += gridDim.y * blockDim.x * 8) {
+    float xv[8], gv[8];
+    load8(x + t * ldx + c, xv);
+    load8(gate + t * ldg + c, gv);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) xv[i] *= 1.f / (1.f + __expf(-gv[i]));
+    store8(x + t * ldx + c, xv);
+  }
+}
+
+// y[t, :] += s[t, :] * sigmoid(<x[t, :], wg>)   (shared expert behind a scalar gate); one CTA per row
+__global__ void __launch_bounds__(256)
+shared_expert_blend_kernel(__nv_bfloat16* y, long long ldy, const __nv_bfloat16* __restrict__ s, long long lds,
+                           const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ wg, int H) {
+  const long long t = blockIdx.x;
+  __shared__ float red[8];
+  float dot = 0.f;
+  for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+    float xv[8], wv[8];
+    load8(x + t * ldx + c, xv);
+    load8(wg + c, wv);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dot += xv[i] * wv[i];
+  }
+  dot = warp_sum(dot);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = dot;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float g = 1.f / (1.f + __expf(-tot));
+  for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+    float yv[8], sv[8];
+    load8(y + t * ldy + c, yv);
+    load8(s + t * lds + c, sv);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) yv[i] += sv[i] * g;
+    store8(y + t * ldy + c, yv);
+  }
+}
+
 }  // namespace atlas
 
 using namespace atlas;
@@ -617,5 +662,24 @@ extern "C" int atlas_lora_bgmv(const void* x, long long ldx, const long long* sl
   }
   lora_bgmv_kernel<<<T, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), ldx, slot, lp, reinterpret_cast<__nv_bfloat16*>(y), ldy, col0, K, N);
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+extern "C" int atlas_sigmoid_gate_mul(void* x, long long ldx, const void* gate, long long ldg, int T, int n, void* stream) {
+  if (T <= 0 || n <= 0) return 0;
+  if (n % 8 || ldx % 8 || ldg % 8 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(gate) & 15)) return -1;
+  dim3 grid(T, (n / 8 + 255) / 256);
+  sigmoid_gate_mul_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__nv_bfloat16*>(x), ldx, reinterpret_cast<const __nv_bfloat16*>(gate), ldg, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+extern "C" int atlas_shared_expert_blend(void* y, long long ldy, const void* s, long long lds, const void* x, long long ldx,
+                                         const void* wg, int T, int H, void* stream) {
+  if (T <= 0) return 0;
+  if (H % 8 || ldy % 8 || lds % 8 || ldx % 8) return -1;
+  shared_expert_blend_kernel<<<T, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__nv_bfloat16*>(y), ldy, reinterpret_cast<const __nv_bfloat16*>(s), lds,
+      reinterpret_cast<const __nv_bfloat16*>(x), ldx, reinterpret_cast<const __nv_bfloat16*>(wg), H);
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
 }

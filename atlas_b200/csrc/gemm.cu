@@ -606,9 +606,46 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         store_now = false;
         const int owner = min(m_tile / p.rs_tiles_per_rank, p.ar_world - 1);
         const int local_tile = m_tile - owner * p.rs_tiles_per_rank;
-        if (ok && m < M_rows) {
-          __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.ar_data[owner] + (size_t)p.ar_rank * p.ar_part_src_stride) +
-                                ((size_t)local_tile * kBlockM + row_in_tile) * p.N;
+        __nv_bfloat16* dbase = reinterpret_cast<__nv_bfloat16*>(p.ar_data[owner] + (size_t)p.ar_rank * p.ar_part_src_stride) +
+                               (size_t)local_tile * kBlockM * p.N;
+        if constexpr (HALF == 64) {
+          // A thread holds 64 consecutive columns of ONE row, so a warp-wide 16-byte store would touch 32 rows: 32
+          // separate 16-byte writes, which NVLink carries poorly.  The eight 16-byte vectors are transposed across each
+          // group of eight lanes first (butterfly of shuffles): afterwards eight neighbouring lanes hold the eight
+          // vectors of one row and every store instruction writes four whole 128-byte row segments.
+          uint4 v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            v[j].x = pack_bf16x2(acc[8 * j + 0], acc[8 * j + 1]);
+            v[j].y = pack_bf16x2(acc[8 * j + 2], acc[8 * j + 3]);
+            v[j].z = pack_bf16x2(acc[8 * j + 4], acc[8 * j + 5]);
+            v[j].w = pack_bf16x2(acc[8 * j + 6], acc[8 * j + 7]);
+          }
+#pragma unroll
+          for (int sft = 4; sft >= 1; sft >>= 1) {
+            const bool up = (lane & sft) != 0;
+#pragma unroll
+            for (int a = 0; a < 8; ++a) {
+              if (a & sft) continue;
+              const uint4 snd = up ? v[a] : v[a | sft];
+              uint4 rcv;
+              rcv.x = __shfl_xor_sync(0xffffffffu, snd.x, sft);
+              rcv.y = __shfl_xor_sync(0xffffffffu, snd.y, sft);
+              rcv.z = __shfl_xor_sync(0xffffffffu, snd.z, sft);
+              rcv.w = __shfl_xor_sync(0xffffffffu, snd.w, sft);
+              if (up) v[a] = rcv; else v[a | sft] = rcv;
+            }
+          }
+          // now v[i] = vector (lane & 7) of row 8 * (lane >> 3) + i of this warp's 32 rows
+          const int col = n_base + 8 * (lane & 7);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r_in_tile = lane_group * 32 + 8 * (lane >> 3) + i;
+            if (ok && m_tile * kBlockM + r_in_tile < M_rows && col + 8 <= p.N)
+              *reinterpret_cast<uint4*>(dbase + (size_t)r_in_tile * p.N + col) = v[i];
+          }
+        } else if (ok && m < M_rows) {
+          __nv_bfloat16* drow = dbase + (size_t)row_in_tile * p.N;
 #pragma unroll
           for (int j = 0; j < HALF; j += 8) {
             const int n = n_base + j;
@@ -1244,7 +1281,8 @@ extern "C" int atlas_gemm_reduce_scatter(int kind, const void* A, const void* B,
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -1;
   if ((lda * esize) % 16 || (ldb * esize) % 16) return -2;
   if (kind == 1 && (K % 128)) return -3;
-  if (block_n != 64 && block_n != 128) return -4;
+  if (block_n != 64 && block_n != 128 && block_n != 256) return -4;
+  if (block_n == 256 && (kind != 1 || wide_fp8_epilogue_warps() != 16)) return -4;    // the wide tile exists for FP8 only
   if (N % 8 || world < 1 || world > 8 || tiles_per_rank < 1) return -5;
   CUtensorMap ta, tb;
   int rc = make_tmap_kmajor(&ta, A, M, K, lda, kBlockM, esize);
@@ -1283,6 +1321,7 @@ extern "C" int atlas_gemm_reduce_scatter(int kind, const void* A, const void* B,
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (kind == 1) {
     if (block_n == 64) return launch_gemm<64, true, true>(ta, tb, p, grid, st);
+    if (block_n == 256) return launch_gemm<256, true, true, 16>(ta, tb, p, grid, st);
     return launch_gemm<128, true, true>(ta, tb, p, grid, st);
   }
   if (block_n == 64) return launch_gemm<64, false, true>(ta, tb, p, grid, st);

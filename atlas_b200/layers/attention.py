@@ -110,5 +110,8 @@ class Attention:
         out = out.reshape(T, nq)
         if self.gated:
             gate = qkv[:, nq + 2 * nkv:]
-            out = (out.float() * torch.sigmoid(gate.float())).to(out.dtype)
+            if ops.on_gpu(out) and out.dtype == torch.bfloat16 and nq % 8 == 0 and gate.stride(0) % 8 == 0 and gate.data_ptr() % 16 == 0:
+                out = ops.cuda_ops().sigmoid_gate_mul(out, gate)          # one kernel, in place
+            else:
+                out = (out.float() * torch.sigmoid(gate.float())).to(out.dtype)
         return out

@@ -130,6 +130,9 @@ class MoE:
             y = self._forward_ref(x, topk_w, topk_ids)
         if self.shared is not None:
             s = self.shared.forward(act, reduce=False)
+            if (self.shared_gate is not None and ops.on_gpu(x) and x.dtype == torch.bfloat16 and y.dtype == torch.bfloat16
+                    and self.shared_gate.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and y.is_contiguous()):
+                return ops.cuda_ops().shared_expert_blend(y if y._base is None else y.clone(), s, x, self.shared_gate)
             if self.shared_gate is not None:
                 g = torch.sigmoid(x.float() @ self.shared_gate.float().t())
                 s = (s.float() * g).to(s.dtype)

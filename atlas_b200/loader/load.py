@@ -26,6 +26,10 @@ from .qtensor import QTensor, as_q, cat_rows, to_linear
 
 def load_model(path: str, pctx: Optional[ParallelCtx] = None, device="cpu", dtype: Optional[str] = None,
                max_pos: Optional[int] = None, with_mtp: Optional[bool] = None) -> DecoderLM:
+    gguf_path = _gguf_file(path)
+    if gguf_path is not None:
+        from .gguf import load_gguf_model
+        return load_gguf_model(gguf_path, pctx, device=device, dtype=dtype, max_pos=max_pos)
     cfg = ModelConfig.from_pretrained(path)
     if dtype:
         cfg.dtype = dtype
@@ -33,6 +37,17 @@ def load_model(path: str, pctx: Optional[ParallelCtx] = None, device="cpu", dtyp
     load_weights(model, Checkpoint(path))
     model.finalize(max_pos)
     return model
+
+
+def _gguf_file(path: str) -> Optional[str]:
+    """``path`` itself when it is a ``.gguf`` file, or the single ``.gguf`` inside a directory without ``config.json``."""
+    if os.path.isfile(path) and path.endswith(".gguf"):
+        return path
+    if os.path.isdir(path) and not os.path.exists(os.path.join(path, "config.json")):
+        found = sorted(f for f in os.listdir(path) if f.endswith(".gguf"))
+        if len(found) == 1:
+            return os.path.join(path, found[0])
+    return None
 
 
 def _vec(ck: Checkpoint, name: str, model: DecoderLM, dtype=None) -> Optional[torch.Tensor]:

@@ -638,3 +638,31 @@ def mamba2_gated_norm(y, z, w, group, eps):
 def relu_squared(x):
     from . import cuda_gdn
     return cuda_gdn.relu_squared(x)
+
+
+def sigmoid_gate_mul(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """``x *= sigmoid(gate)`` in place, rows of ``n`` bf16 values (``gate`` may be a strided column view)."""
+    T, n = x.shape
+    _dev(x)
+    L = lib()
+    if not getattr(L, "_gate_bound", False):
+        L.atlas_sigmoid_gate_mul.argtypes = [_vp, _ll, _vp, _ll, _i, _i, _vp]
+        L.atlas_shared_expert_blend.argtypes = [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _i, _i, _vp]
+        L._gate_bound = True
+    _check(L.atlas_sigmoid_gate_mul(x.data_ptr(), x.stride(0), gate.data_ptr(), gate.stride(0), T, n, _stream()), "sigmoid_gate_mul")
+    return x
+
+
+def shared_expert_blend(y: torch.Tensor, s: torch.Tensor, x: torch.Tensor, wg: torch.Tensor) -> torch.Tensor:
+    """``y += s * sigmoid(x @ wg^T)`` in place (``wg [1, H]``)."""
+    T, H = y.shape
+    _dev(y)
+    sigmoid_gate_mul  # binds the entry points on first use of either
+    L = lib()
+    if not getattr(L, "_gate_bound", False):
+        L.atlas_sigmoid_gate_mul.argtypes = [_vp, _ll, _vp, _ll, _i, _i, _vp]
+        L.atlas_shared_expert_blend.argtypes = [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _i, _i, _vp]
+        L._gate_bound = True
+    _check(L.atlas_shared_expert_blend(y.data_ptr(), y.stride(0), s.data_ptr(), s.stride(0), x.data_ptr(), x.stride(0),
+                                       wg.data_ptr(), T, H, _stream()), "shared_expert_blend")
+    return y

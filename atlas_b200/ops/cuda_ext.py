@@ -133,11 +133,19 @@ def moe_forward(x, topk_w, topk_ids, experts, e_lo, pctx, ep_mode, addend: Optio
             out = _moe_forward_alltoall(x, topk_w, topk_ids, experts, e_lo, pctx, comm, addend)
             if out is not None:
                 return out
-    out = _moe_local(x, topk_w, topk_ids, experts, e_lo, addend)
+    comm = None
     if pctx is not None and pctx.ep_size > 1:
         comm = pctx.ep_comm if pctx.ep_comm is not None else pctx.comm
-        if comm is not None:
-            out = comm.all_reduce(out)
+    if comm is None:
+        return _moe_local(x, topk_w, topk_ids, experts, e_lo, addend)
+    # every rank runs its own experts on the replicated rows; the partial outputs are summed over the group.  With a
+    # peer-memory backend and a decode-size step the weighted combine and that sum are ONE kernel.
+    fused = comm if hasattr(comm, "moe_combine_all_reduce") else None
+    out, reduced = _moe_local(x, topk_w, topk_ids, experts, e_lo, addend, fused_comm=fused, grouped=True)
+    if not reduced:
+        out = comm.all_reduce(out)
+        if addend is not None:
+            out = out + addend
     return out
 
 
@@ -218,7 +226,22 @@ def _bind_small(lib) -> None:
         lib._small_moe_bound = True
 
 
-def _moe_local(x, topk_w, topk_ids, experts, e_lo, addend: Optional[torch.Tensor] = None):
+def _finish(lib, y, slot_of, topk_w, T, k, H, addend, fused_comm, grouped, dev, st):
+    """Weighted combine of the expert outputs.  ``grouped`` (expert-parallel caller): returns ``(out, reduced)``; the
+    combine is fused with the group reduction (addend included) when the peer-memory backend takes the step, otherwise
+    the local partial comes back WITHOUT the addend, which must be added once after the reduction."""
+    if grouped and fused_comm is not None:
+        out = fused_comm.moe_combine_all_reduce(y, slot_of, topk_w, T, k, addend)
+        if out is not None:
+            return out, True
+    local_addend = None if grouped else addend
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    K._check(lib.atlas_moe_combine(y.data_ptr(), H, slot_of.data_ptr(), topk_w.data_ptr(), T, k, H, K._ptr(local_addend),
+                                   local_addend.stride(0) if local_addend is not None else 0, out.data_ptr(), H, st), "moe_combine")
+    return (out, False) if grouped else out
+
+
+def _moe_local(x, topk_w, topk_ids, experts, e_lo, addend: Optional[torch.Tensor] = None, fused_comm=None, grouped=False):
     """Local experts only: align -> gather (+quant) -> grouped GEMM -> SiLU*mul -> grouped GEMM -> weighted combine."""
     T, H = x.shape
     k = topk_ids.shape[1]
@@ -252,10 +275,7 @@ def _moe_local(x, topk_w, topk_ids, experts, e_lo, addend: Optional[torch.Tensor
         K._check(lib.atlas_moe_small_w4(0, act.data_ptr(), I, row_token.data_ptr(), tile_expert.data_ptr(),
                                         num_tiles.data_ptr(), max_rows // 128, w2.data_ptr(), s2[0].data_ptr(),
                                         s2[1].data_ptr(), y.data_ptr(), H, I, H, st), "moe_small_down")
-        out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
-        K._check(lib.atlas_moe_combine(y.data_ptr(), H, slot_of.data_ptr(), topk_w.data_ptr(), T, k, H, K._ptr(addend),
-                                       addend.stride(0) if addend is not None else 0, out.data_ptr(), H, st), "moe_combine")
-        return out
+        return _finish(lib, y, slot_of, topk_w, T, k, H, addend, fused_comm, grouped, dev, st)
     if kind == 1:
         xq = torch.empty(max_rows, H, dtype=FP8, device=dev)
         xs = torch.empty(H // 128, max_rows, dtype=torch.float32, device=dev)
@@ -296,10 +316,7 @@ def _moe_local(x, topk_w, topk_ids, experts, e_lo, addend: Optional[torch.Tensor
         K._check(lib.atlas_gemm_grouped(kind, a2.data_ptr(), w2.data_ptr(), y.data_ptr(), K._ptr(a2s), max_rows, K._ptr(s2),
                                         max_rows, H, I, E, I, I, H, bn_for(H), tile_expert.data_ptr(), num_tiles.data_ptr(),
                                         sms, status, st), "moe_gemm2")
-    out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
-    K._check(lib.atlas_moe_combine(y.data_ptr(), H, slot_of.data_ptr(), topk_w.data_ptr(), T, k, H, K._ptr(addend),
-                                   addend.stride(0) if addend is not None else 0, out.data_ptr(), H, st), "moe_combine")
-    return out
+    return _finish(lib, y, slot_of, topk_w, T, k, H, addend, fused_comm, grouped, dev, st)
 
 
 # ----------------------------------------------------------------------------- GDN (bound when gdn.cu is present)

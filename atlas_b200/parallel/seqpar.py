@@ -160,7 +160,11 @@ class SeqParallelArea:
         d = K._dev(a)
         sms = K._num_sms[d]
         tpr, _, _ = self._row_range(T)
-        bn = 128 if ((T + 127) // 128) * (N // 128) >= sms else 64
+        m_tiles = (T + 127) // 128
+        if kind == 1 and N % 256 == 0 and m_tiles * (N // 256) >= sms:
+            bn = 256                # prefill-size FP8: the wide tile (see ops.cuda.gemm_plan)
+        else:
+            bn = 128 if m_tiles * (N // 128) >= sms else 64
         nt = _i(0)
         rc = self.lib.atlas_gemm_reduce_scatter(kind, a.data_ptr(), b.data_ptr(), K._ptr(a_scale),
                                                 a_scale.stride(1) if a_scale is not None else 0, K._ptr(b_scale),

@@ -174,6 +174,31 @@ class SymmBackend(CommBackend):
         K._check(rc, "alltoall_rows")
         return out, recv_off
 
+    def moe_combine_all_reduce(self, y: torch.Tensor, slot_of: torch.Tensor, topk_w: torch.Tensor, T: int, k: int,
+                               addend: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """Weighted top-k combine of this rank's expert outputs fused with the sum over the group (one kernel).
+        Returns None when the step is too large for the one-exchange form (the caller combines, then all-reduces)."""
+        self._guard()
+        H = y.shape[1]
+        nbytes = T * H * 2
+        if y.dtype != torch.bfloat16 or H % 8 or nbytes > min(ONESHOT_MAX_BYTES, self.slot_bytes) or y.stride(1) != 1:
+            return None
+        K = self.K
+        if not getattr(self.lib, "_mca_bound", False):
+            self.lib.atlas_moe_combine_allreduce.argtypes = [C.POINTER(_vp), C.POINTER(_vp), _i, _i, _vp, _ll, _vp, _vp, _i, _i, _i,
+                                                             _vp, _ll, _vp, _ll, _sz, _vp, _i, _vp, _ll, _vp]
+            self.lib._mca_bound = True
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=y.device)
+        blocks = max(1, min(self.blocks, nbytes // 16384))
+        rc = self.lib.atlas_moe_combine_allreduce(self.data_arr, self.flag_arr, self.rank, self.world_size, y.data_ptr(),
+                                                  y.stride(0), slot_of.data_ptr(), topk_w.data_ptr(), T, k, H, K._ptr(addend),
+                                                  addend.stride(0) if addend is not None else 0, out.data_ptr(), H,
+                                                  self.slot_bytes, self.state.data_ptr(), blocks,
+                                                  K._status_ptr[self.dev_index], self.wait_cycles, K._stream())
+        K._check(rc, "moe_combine_allreduce")
+        self.calls["moe_combine_allreduce"] = self.calls.get("moe_combine_allreduce", 0) + 1
+        return out
+
     def gemm_allreduce(self, act, w) -> Optional[torch.Tensor]:
         """``sum over ranks of (act_shard @ W_shard^T)`` with the reduction fused into the GEMM kernel.  Returns a
         view of the result inside this rank's fused area (valid until the next fused call), or None when the
