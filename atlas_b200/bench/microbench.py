@@ -108,7 +108,28 @@ def run(model: str = "llama3-8b", decode_batch: int = 128, ctx: int = 1152, chun
                 bn, sp = K.gemm_plan(M, N, Kd, 1, 148)
                 add(f"gemm_fp8 {name} M={M} N={N} K={Kd}", ms, bytes_=N * Kd + M * Kd + 2 * M * N, flops=2 * M * N * Kd,
                     note=f"block_n={bn} splits={sp}")
-                del wq, ws
+                # fused epilogues of the same shape: SwiGLU + FP8 quant (gate_up), residual + norm weight + FP8 quant (o, down)
+                if name == "gate_up" and (N // 2) % 128 == 0:
+                    ms = T.time(lambda: K.gemm_fp8_fused(xq, xs, wq, ws, mode=1))
+                    add(f"gemm_fp8+swiglu+quant {name} M={M}", ms, bytes_=N * Kd + M * Kd + M * N // 2, flops=2 * M * N * Kd)
+                if name in ("o", "down") and N % 128 == 0:
+                    res = torch.randn(M, N, device=dev).bfloat16()
+                    nw = torch.ones(N, device=dev).bfloat16()
+                    ms = T.time(lambda: K.gemm_fp8_fused(xq, xs, wq, ws, mode=2, residual=res, norm_w=nw))
+                    add(f"gemm_fp8+residual+norm+quant {name} M={M}", ms, bytes_=N * Kd + M * Kd + 5 * M * N, flops=2 * M * N * Kd)
+                # the library's FP8 GEMM (cuBLASLt through torch._scaled_mm, ONE scale per tensor: no 128x128 block fold)
+                # and its bf16 GEMM on the same shape
+                try:
+                    one = torch.ones((), device=dev)
+                    ms = T.time(lambda: torch._scaled_mm(xq, wq.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16))
+                    add(f"library fp8 tensorwise (_scaled_mm) {name} M={M}", ms, bytes_=N * Kd + M * Kd + 2 * M * N,
+                        flops=2 * M * N * Kd, note="no block scales: a lower bound the block-scaled kernel cannot reach")
+                except Exception as exc:                                       # pragma: no cover
+                    print(json.dumps({"kernel": f"_scaled_mm {name}", "error": repr(exc)[:200]}), flush=True)
+                xb, wb = x[:, :Kd].contiguous(), torch.randn(N, Kd, device=dev).bfloat16()
+                ms = T.time(lambda: torch.matmul(xb, wb.t()))
+                add(f"library bf16 (cuBLAS) {name} M={M}", ms, bytes_=2 * (N * Kd + M * Kd + M * N), flops=2 * M * N * Kd)
+                del wq, ws, wb
         # lm_head bf16
         M = decode_batch
         w = (torch.randn(cfg.vocab_size, H, device=dev) * 0.02).bfloat16()

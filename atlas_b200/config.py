@@ -21,10 +21,11 @@ from typing import Any, Dict, List, Optional, Tuple
 _FAMILY_ALIASES = {
     "llama": "dense", "mistral": "dense", "qwen2": "dense", "qwen3": "dense",
     "qwen3_moe": "moe", "qwen3_vl_moe": "moe", "mixtral": "moe", "minimax_m2": "moe",
-    "qwen3_next": "hybrid", "qwen3_5": "hybrid", "qwen35": "hybrid",
-    "qwen3_5_moe": "hybrid", "qwen35_moe": "hybrid", "qwen3_6_moe": "hybrid",
+    "qwen3_next": "hybrid", "qwen3_5": "hybrid", "qwen35": "hybrid", "qwen3_5_text": "hybrid",
+    "qwen3_5_moe": "hybrid", "qwen35_moe": "hybrid", "qwen3_6_moe": "hybrid", "qwen3_5_moe_text": "hybrid",
     "holo3_1_moe": "hybrid",
     "nemotron_h": "hybrid", "nemotron_h_puzzle": "hybrid",
+    "deepseek_v2": "moe", "deepseek_v3": "moe", "deepseek_v32": "moe", "kimi_k2": "moe",
 }
 
 
@@ -107,7 +108,12 @@ class ModelConfig:
     moe_intermediate_size: int = 0
     shared_expert_intermediate_size: int = 0
     norm_topk_prob: bool = True
-    router_scoring: str = "softmax"   # softmax | sigmoid
+    router_scoring: str = "softmax"   # softmax | sigmoid | sqrtsoftplus
+    routed_scaling_factor: float = 1.0
+    router_n_group: int = 0           # group-limited routing (DeepSeek-V3): experts split into n_group groups ...
+    router_topk_group: int = 0        # ... of which the topk_group best stay eligible
+    router_selection_bias: bool = False   # per-expert e_score_correction_bias used for selection only
+    num_hash_layers: int = 0          # first MoE layers select experts by a static token-id table (DeepSeek-V4)
     decoder_sparse_step: int = 1
     mlp_only_layers: List[int] = field(default_factory=list)
     # hybrid (Gated DeltaNet)
@@ -127,6 +133,14 @@ class ModelConfig:
     mamba_conv_kernel: int = 4
     mamba_dt_min: float = 0.0
     mlp_activation: str = "silu_glu"  # silu_glu (gated SwiGLU) | relu2 (up -> relu^2 -> down)
+    # multi-head latent attention (DeepSeek): 0 = plain GQA.  head_dim is then the padded cache width
+    kv_lora_rank: int = 0
+    q_lora_rank: int = 0
+    qk_nope_head_dim: int = 0
+    qk_rope_head_dim: int = 0
+    v_head_dim: int = 0
+    rope_interleaved: bool = True     # checkpoint stores rotary columns as (even, odd) pairs
+    first_k_dense_replace: int = 0    # leading layers with a dense FFN in an otherwise MoE model
     # MTP speculative head
     mtp_num_layers: int = 0
     # numerics
@@ -161,7 +175,7 @@ class ModelConfig:
     def is_moe_layer(self, i: int) -> bool:
         if self.block_types:
             return self.block_types[i] == "moe"
-        if self.num_experts <= 0 or i in self.mlp_only_layers:
+        if self.num_experts <= 0 or i in self.mlp_only_layers or i < self.first_k_dense_replace:
             return False
         return (i + 1) % max(1, self.decoder_sparse_step) == 0
 
@@ -245,6 +259,11 @@ class ModelConfig:
             shared_expert_intermediate_size=int(cfg.get("shared_expert_intermediate_size", 0) or 0),
             norm_topk_prob=bool(cfg.get("norm_topk_prob", True)),
             router_scoring=str(cfg.get("scoring_func", "softmax")),
+            routed_scaling_factor=float(cfg.get("routed_scaling_factor", 1.0) or 1.0),
+            router_n_group=int(cfg.get("n_group", 0) or 0),
+            router_topk_group=int(cfg.get("topk_group", 0) or 0),
+            router_selection_bias=bool(cfg.get("router_selection_bias", cfg.get("topk_method", "") == "noaux_tc")),
+            num_hash_layers=int(cfg.get("num_hash_layers", 0) or 0),
             decoder_sparse_step=int(cfg.get("decoder_sparse_step", 1) or 1),
             mlp_only_layers=list(cfg.get("mlp_only_layers", []) or []),
             layer_types=list(cfg.get("layer_types", []) or []),
@@ -261,6 +280,24 @@ class ModelConfig:
         )
         if mt == "mixtral":
             c.moe_intermediate_size = c.intermediate_size
+        if mt.startswith("deepseek") or mt == "kimi_k2":
+            c.num_experts = int(cfg.get("n_routed_experts", 0) or 0)
+            c.shared_expert_intermediate_size = c.moe_intermediate_size * int(cfg.get("n_shared_experts", 0) or 0)
+            c.first_k_dense_replace = int(cfg.get("first_k_dense_replace", 0) or 0)
+            c.decoder_sparse_step = int(cfg.get("moe_layer_freq", 1) or 1)
+            c.router_scoring = str(cfg.get("scoring_func", "sigmoid" if mt != "deepseek_v2" else "softmax"))
+            c.router_selection_bias = mt != "deepseek_v2"
+            c.num_key_value_heads = nh
+            c.kv_lora_rank = int(cfg.get("kv_lora_rank", 512))
+            c.q_lora_rank = int(cfg.get("q_lora_rank") or 0)
+            c.qk_nope_head_dim = int(cfg.get("qk_nope_head_dim", 128))
+            c.qk_rope_head_dim = int(cfg.get("qk_rope_head_dim", 64))
+            c.v_head_dim = int(cfg.get("v_head_dim", 128))
+            c.rope_interleaved = bool(cfg.get("rope_interleave", True))
+            need = max(c.qk_nope_head_dim + c.qk_rope_head_dim, c.v_head_dim)
+            c.head_dim = next((d for d in (64, 128, 256) if d >= need), need)
+            c.partial_rotary_factor = c.qk_rope_head_dim / c.head_dim
+            c.qk_norm = False
         if mt.startswith("nemotron_h"):
             blocks = cfg.get("layers_block_type")
             if not blocks and cfg.get("hybrid_override_pattern"):
@@ -384,6 +421,18 @@ def tiny_nemotron_h(dtype: str = "float32") -> ModelConfig:
                        mlp_activation="relu2", max_position_embeddings=4096, dtype=dtype)
 
 
+def tiny_deepseek(dtype: str = "float32") -> ModelConfig:
+    """DeepSeek-V3 style: latent attention, a leading dense layer, then MoE layers with a group-limited sigmoid router,
+    selection bias, weight scale and an ungated shared expert."""
+    return ModelConfig(model_type="deepseek_v3", family="moe", vocab_size=1024, hidden_size=256, intermediate_size=512,
+                       num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4, head_dim=64,
+                       partial_rotary_factor=0.25, kv_lora_rank=64, q_lora_rank=96, qk_nope_head_dim=32, qk_rope_head_dim=16,
+                       v_head_dim=32, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128,
+                       shared_expert_intermediate_size=128, first_k_dense_replace=1, router_scoring="sigmoid",
+                       router_selection_bias=True, router_n_group=4, router_topk_group=2, routed_scaling_factor=2.5,
+                       max_position_embeddings=4096, dtype=dtype)
+
+
 def nemotron_h_8b(quant: str = "none") -> ModelConfig:
     pattern = "M-M-M-MM-M-M-M*-M-M-M*-M-M-M-M*-M-M-M-M*-M-MM-M-M-M-M-M-"
     blocks = [{"M": "mamba", "*": "attention", "-": "mlp"}[ch] for ch in pattern]
@@ -398,7 +447,7 @@ PRESETS = {
     "tiny-dense": tiny_dense, "tiny-moe": tiny_moe, "tiny-hybrid": tiny_hybrid,
     "llama3-8b": llama3_8b, "llama3-70b": llama3_70b,
     "qwen3-30b-a3b": qwen3_30b_a3b, "qwen3-next-80b": qwen3_next_80b,
-    "tiny-nemotron-h": tiny_nemotron_h, "nemotron-h-8b": nemotron_h_8b,
+    "tiny-nemotron-h": tiny_nemotron_h, "nemotron-h-8b": nemotron_h_8b, "tiny-deepseek": tiny_deepseek,
 }
 
 
@@ -409,6 +458,7 @@ class EngineConfig:
     max_seq_len: int = 32768
     block_size: int = 16
     kv_cache_dtype: str = "auto"
+    kv_high_precision_layers: tuple = ()      # attention layers that keep a 16-bit cache when kv_cache_dtype is fp8
     gpu_memory_utilization: float = 0.90
     num_kv_blocks: Optional[int] = None       # explicit override (tests / CPU)
     max_num_seqs: int = 128

@@ -56,10 +56,19 @@ ATLAS_DEVICE uint32_t pack_f16x2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
+ATLAS_DEVICE void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
 
-template <int D, bool PREFILL>
+// KV16: the cache holds bf16 (two bytes per element, same page layouts); queries, probabilities and the cache then meet
+// in bf16 MMAs and no scale applies.  Otherwise FP8 e4m3 bytes widened to f16.
+template <int D, bool PREFILL, bool KV16 = false>
 __global__ void __launch_bounds__(128)
 paged_attn_kernel(const AttnParams p) {
+  constexpr int ES = KV16 ? 2 : 1;      // bytes per cache element
   constexpr int KS = D / 16;            // k-steps of QK^T
   constexpr int NT = D / 8;             // n-tiles of PV
   constexpr int DQ = D / 4;             // dims owned by one thread of a quad
@@ -109,8 +118,8 @@ paged_attn_kernel(const AttnParams p) {
           v[0] = __low2float(lo) * p.qk_scale_log2; v[1] = __high2float(lo) * p.qk_scale_log2;
           v[2] = __low2float(hi) * p.qk_scale_log2; v[3] = __high2float(hi) * p.qk_scale_log2;
         }
-        qf[ks][h] = pack_f16x2(v[0], v[1]);         // a0 / a1 : k = c*2 + {0,1}
-        qf[ks][2 + h] = pack_f16x2(v[2], v[3]);     // a2 / a3 : k = c*2 + 8 + {0,1}
+        qf[ks][h] = KV16 ? pack_bf16x2(v[0], v[1]) : pack_f16x2(v[0], v[1]);         // a0 / a1 : k = c*2 + {0,1}
+        qf[ks][2 + h] = KV16 ? pack_bf16x2(v[2], v[3]) : pack_f16x2(v[2], v[3]);     // a2 / a3 : k = c*2 + 8 + {0,1}
       }
     }
   }
@@ -150,8 +159,8 @@ paged_attn_kernel(const AttnParams p) {
     const int tok0 = pg << 4;
     const int blk = bt[tok0 / bs];
     const int off = tok0 % bs;
-    const uint8_t* kpage = p.k_cache + (((long long)blk * p.Hkv + kvh) * bs + off) * D;
-    const uint8_t* vpage = p.v_cache + ((long long)blk * p.Hkv + kvh) * (long long)D * bs + off;
+    const uint8_t* kpage = p.k_cache + ((((long long)blk * p.Hkv + kvh) * bs + off) * D) * ES;
+    const uint8_t* vpage = p.v_cache + (((long long)blk * p.Hkv + kvh) * (long long)D * bs + off) * ES;
 
     // ---- S = Q K^T for the 16 tokens of this page
     float s[2][4];
@@ -159,7 +168,15 @@ paged_attn_kernel(const AttnParams p) {
     for (int i = 0; i < 2; ++i) {
       s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
       const int tok_in_page = (rq >> 1) * 4 + 2 * i + (rq & 1);
-      const uint4* krow = reinterpret_cast<const uint4*>(kpage + tok_in_page * D + c * DQ);
+      const uint4* krow = reinterpret_cast<const uint4*>(kpage + (tok_in_page * D + c * DQ) * ES);
+      if constexpr (KV16) {
+#pragma unroll
+        for (int v4 = 0; v4 < DQ / 8; ++v4) {          // eight bf16 = two k-steps
+          const uint4 raw = __ldg(krow + v4);
+          mma_bf16(s[i], qf[v4 * 2], raw.x, raw.y);
+          mma_bf16(s[i], qf[v4 * 2 + 1], raw.z, raw.w);
+        }
+      } else {
 #pragma unroll
       for (int v4 = 0; v4 < DQ / 16; ++v4) {
         const uint4 raw = __ldg(krow + v4);
@@ -170,6 +187,7 @@ paged_attn_kernel(const AttnParams p) {
           const uint32_t b1 = fp8x2_to_f16x2((uint16_t)(w[wi] >> 16));
           mma_f16(s[i], qf[v4 * 4 + wi], b0, b1);
         }
+      }
       }
     }
     // ---- mask + online softmax.  s[i][j] (row rq) and s[i][2+j] (row rq+8) belong to token tok0 + c*4 + 2i + j.
@@ -212,10 +230,15 @@ paged_attn_kernel(const AttnParams p) {
           pv[i][e] = x;
           l_run[h] += x;
         }
-      pf[0] = pack_f16x2(pv[0][0], pv[0][1]);
-      pf[1] = pack_f16x2(pv[0][2], pv[0][3]);
-      pf[2] = pack_f16x2(pv[1][0], pv[1][1]);
-      pf[3] = pack_f16x2(pv[1][2], pv[1][3]);
+      if (KV16) {
+        pf[0] = pack_bf16x2(pv[0][0], pv[0][1]); pf[1] = pack_bf16x2(pv[0][2], pv[0][3]);
+        pf[2] = pack_bf16x2(pv[1][0], pv[1][1]); pf[3] = pack_bf16x2(pv[1][2], pv[1][3]);
+      } else {
+        pf[0] = pack_f16x2(pv[0][0], pv[0][1]);
+        pf[1] = pack_f16x2(pv[0][2], pv[0][3]);
+        pf[2] = pack_f16x2(pv[1][0], pv[1][1]);
+        pf[3] = pack_f16x2(pv[1][2], pv[1][3]);
+      }
     }
     // tokens past the sequence end may hold stale bytes: zero them so 0 * garbage cannot produce NaN
     uint32_t vmask = 0xFFFFFFFFu;
@@ -231,12 +254,22 @@ paged_attn_kernel(const AttnParams p) {
     // ---- O = alpha * O + P V
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
+      uint32_t b0, b1;
+      if constexpr (KV16) {
+        // four bf16 of one V^T row; vmask carries one byte flag per token, widened here to 16-bit lanes
+        const uint2 w2 = __ldg(reinterpret_cast<const uint2*>(vpage + ((long long)(j * 8 + rq) * bs + c * 4) * 2));
+        const uint32_t m0 = ((vmask & 0xFFu) ? 0xFFFFu : 0u) | ((vmask & 0xFF00u) ? 0xFFFF0000u : 0u);
+        const uint32_t m1 = ((vmask & 0xFF0000u) ? 0xFFFFu : 0u) | ((vmask & 0xFF000000u) ? 0xFFFF0000u : 0u);
+        b0 = w2.x & m0;
+        b1 = w2.y & m1;
+      } else {
       const uint32_t word = __ldg(reinterpret_cast<const uint32_t*>(vpage + (long long)(j * 8 + rq) * bs + c * 4)) & vmask;
-      const uint32_t b0 = fp8x2_to_f16x2((uint16_t)(word & 0xFFFFu));
-      const uint32_t b1 = fp8x2_to_f16x2((uint16_t)(word >> 16));
+      b0 = fp8x2_to_f16x2((uint16_t)(word & 0xFFFFu));
+      b1 = fp8x2_to_f16x2((uint16_t)(word >> 16));
+      }
       o[j][0] *= alpha[0]; o[j][1] *= alpha[0];
       o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
-      mma_f16(o[j], pf, b0, b1);
+      if (KV16) mma_bf16(o[j], pf, b0, b1); else mma_f16(o[j], pf, b0, b1);
     }
   }
   // quad-reduce the row sums
@@ -694,6 +727,64 @@ extern "C" int atlas_attn_prefill(const void* q, long long ldq, void* out, long 
   if (D == 64) return launch_prefill<64>(p, st);
   if (D == 128) return launch_prefill<128>(p, st);
   return launch_prefill<256>(p, st);
+}
+
+// ---- bf16 KV cache (high-precision layers, accuracy checks): the general mma.sync kernel in both roles.
+template <int D>
+static int launch_kv16(const AttnParams& p, int B, bool prefill, cudaStream_t st) {
+  if (prefill) {
+    dim3 grid((p.num_tiles + 3) / 4, p.Hq);
+    paged_attn_kernel<D, true, true><<<grid, 128, 0, st>>>(p);
+    return cudaGetLastError() == cudaSuccess ? 0 : -21;
+  }
+  const int smem = (128 + 4 * 16 * D) * (int)sizeof(float);
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(paged_attn_kernel<D, false, true>), smem) != cudaSuccess) return -20;
+  dim3 grid(p.Hkv, p.num_splits, B);
+  paged_attn_kernel<D, false, true><<<grid, 128, smem, st>>>(p);
+  if (cudaGetLastError() != cudaSuccess) return -21;
+  if (p.num_splits > 1) {
+    dim3 g2(p.Hq, B);
+    attn_merge_kernel<<<g2, D, 0, st>>>(p.part_o, p.part_ml, p.out, p.ldo, p.query_start_loc, p.seq_base, p.Hq, D, p.num_splits,
+                                       p.v_scale);
+    if (cudaGetLastError() != cudaSuccess) return -22;
+  }
+  return 0;
+}
+
+// Same contracts as atlas_attn_decode / atlas_attn_prefill with a bf16 cache (K [nb, Hkv, bs, D], V [nb, Hkv, D, bs]).
+extern "C" int atlas_attn_decode_kv16(const void* q, long long ldq, void* out, long long ldo, const void* k_cache,
+                                      const void* v_cache, const int* block_tables, int bt_ld, const int* seq_lens,
+                                      const int* query_start_loc, int seq_base, int B, float scale, int Hq, int Hkv, int D,
+                                      int block_size, int window, int num_splits, float* part_o, float* part_ml, void* stream) {
+  if (B <= 0) return 0;
+  AttnParams p;
+  int rc = fill_common(p, q, ldq, out, ldo, k_cache, v_cache, block_tables, bt_ld, seq_lens, query_start_loc, seq_base, scale,
+                       1.f, 1.f, Hq, Hkv, D, block_size, window);
+  if (rc) return rc;
+  if (Hq / Hkv > 16) return -5;
+  p.num_splits = num_splits < 1 ? 1 : num_splits;
+  if (p.num_splits > 1 && (!part_o || !part_ml)) return -3;
+  p.part_o = part_o; p.part_ml = part_ml;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (D == 64) return launch_kv16<64>(p, B, false, st);
+  if (D == 128) return launch_kv16<128>(p, B, false, st);
+  return launch_kv16<256>(p, B, false, st);
+}
+
+extern "C" int atlas_attn_prefill_kv16(const void* q, long long ldq, void* out, long long ldo, const void* k_cache,
+                                       const void* v_cache, const int* block_tables, int bt_ld, const int* seq_lens,
+                                       const int* query_start_loc, const int* tile_seq, const int* tile_q0, int num_tiles,
+                                       float scale, int Hq, int Hkv, int D, int block_size, int window, void* stream) {
+  if (num_tiles <= 0) return 0;
+  AttnParams p;
+  int rc = fill_common(p, q, ldq, out, ldo, k_cache, v_cache, block_tables, bt_ld, seq_lens, query_start_loc, 0, scale, 1.f,
+                       1.f, Hq, Hkv, D, block_size, window);
+  if (rc) return rc;
+  p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.num_tiles = num_tiles;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (D == 64) return launch_kv16<64>(p, 0, true, st);
+  if (D == 128) return launch_kv16<128>(p, 0, true, st);
+  return launch_kv16<256>(p, 0, true, st);
 }
 
 // ================================================================================ allocation-free decode attention

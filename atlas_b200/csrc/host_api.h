@@ -59,6 +59,9 @@ int atlas_gated_rmsnorm(const void* x, long long ldx, const void* z, long long l
 // ---- MoE (moe.cu) and grouped GEMM (gemm.cu)
 int atlas_moe_route(const void* logits, long long ld, int is_bf16, int T, int E, int k, int norm, int sigmoid,
                     float* w_out, int* id_out, void* stream);
+int atlas_moe_route_ex(const void* logits, long long ld, int is_bf16, int T, int E, int k, int norm, int score_mode,
+                       const float* sel_bias, int n_group, int topk_group, const int* hash_table, const int* token_ids,
+                       float out_scale, float* w_out, int* id_out, void* stream);
 int atlas_moe_align(const int* topk_ids, int T, int k, int e_lo, int E_local, int* slot_of, int* row_token,
                     int* tile_expert, int* num_tiles, int max_rows, unsigned long long* status, void* stream);
 int atlas_moe_gather(const void* x, long long ldx, const int* row_token, const int* num_tiles, int max_rows, int H,

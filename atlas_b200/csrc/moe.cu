@@ -11,16 +11,40 @@
 
 namespace atlas {
 
+// Router options beyond plain top-k of softmax / sigmoid scores (all optional):
+//   score_mode 2   sqrt(softplus(logit)) scores
+//   sel_bias       per-expert correction added for SELECTION only; weights come from the unbiased scores
+//   n_group / topk_group   group-limited routing: experts split into n_group equal groups, a group scores the sum of
+//                  its two best (score + bias), only the topk_group best groups stay eligible
+//   hash_table     static selection: expert ids of token id `tok` are hash_table[tok * k ...]; scores still weight them
+//   out_scale      factor on the final weights (routed_scaling_factor)
+// Reference ops replaced: kernels/gb10/common/{moe_topk_sqrtsoftplus,moe_topk_softmax_bias,moe_hash_route,moe_gate_topk}.cu
+struct RouteOpts {
+  int score_mode;            // 0 softmax, 1 sigmoid, 2 sqrt-softplus
+  const float* sel_bias;     // [E] or null
+  int n_group, topk_group;   // 0 / 0 = off
+  const int* hash_table;     // [vocab, k] or null
+  const int* token_ids;      // [T] (with hash_table)
+  float out_scale;
+};
+
+__device__ __forceinline__ float route_score(float x, float mx, int mode) {
+  if (mode == 1) return 1.f / (1.f + __expf(-x));
+  if (mode == 2) return sqrtf(x > 20.f ? x : log1pf(__expf(x)));
+  return __expf(x - mx);
+}
+
 // one warp per token; E <= 1024
 template <typename T>
 __global__ void __launch_bounds__(128)
-moe_route_kernel(const T* __restrict__ logits, long long ld, int T_, int E, int k, int norm, int sigmoid,
+moe_route_kernel(const T* __restrict__ logits, long long ld, int T_, int E, int k, int norm, RouteOpts o,
                  float* __restrict__ w_out, int* __restrict__ id_out) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * 4 + warp;
   if (t >= T_) return;
   constexpr int kMaxPer = 32;
-  float v[kMaxPer];
+  float v[kMaxPer];            // unbiased scores (weights)
+  float sel[kMaxPer];          // selection keys
   const int per = (E + 31) / 32;
   float mx = -INFINITY;
 #pragma unroll
@@ -34,41 +58,105 @@ moe_route_kernel(const T* __restrict__ logits, long long ld, int T_, int E, int 
 #pragma unroll
   for (int i = 0; i < kMaxPer; ++i) {
     if (i < per && v[i] > -INFINITY) {
-      v[i] = sigmoid ? 1.f / (1.f + __expf(-v[i])) : __expf(v[i] - mx);
-      sum += sigmoid ? 0.f : v[i];
+      v[i] = route_score(v[i], mx, o.score_mode);
+      sum += o.score_mode == 0 ? v[i] : 0.f;
     }
   }
   sum = warp_sum(sum);
-  const float inv = sigmoid ? 1.f : 1.f / sum;
+  const float inv = o.score_mode == 0 ? 1.f / sum : 1.f;
+  // selection keys: the normalised score plus the selection-only correction
+#pragma unroll
+  for (int i = 0; i < kMaxPer; ++i) {
+    const int e = i * 32 + lane;
+    sel[i] = (i < per && e < E && v[i] > -INFINITY) ? v[i] * inv + (o.sel_bias ? o.sel_bias[e] : 0.f) : -INFINITY;
+  }
+
+  if (o.hash_table != nullptr) {
+    // static selection: lane j < k owns pick j and scores its expert straight from the logits row
+    const int tok = o.token_ids[t];
+    int my_e = lane < k ? o.hash_table[(long long)tok * k + lane] : 0;
+    my_e = min(max(my_e, 0), E - 1);
+    const float my_w = lane < k ? route_score((float)logits[t * ld + my_e], mx, o.score_mode) * inv : 0.f;
+    float wsum = warp_sum(lane < k ? my_w : 0.f);
+    if (lane < k) {
+      w_out[(long long)t * k + lane] = (norm ? my_w / (wsum + 1e-20f) : my_w) * o.out_scale;
+      id_out[(long long)t * k + lane] = my_e;
+    }
+    return;
+  }
+
+  if (o.n_group > 1 && o.topk_group > 0 && o.topk_group < o.n_group) {
+    const int gsz = E / o.n_group;
+    float my_g = -INFINITY;                    // lane g holds the score of group g
+#pragma unroll 1
+    for (int g = 0; g < o.n_group; ++g) {
+      float a = -INFINITY, b = -INFINITY;      // two best of the group seen by this lane
+#pragma unroll
+      for (int i = 0; i < kMaxPer; ++i) {
+        const int e = i * 32 + lane;
+        if (i < per && e < E && e / gsz == g) {
+          const float x = sel[i];
+          if (x > a) { b = a; a = x; } else if (x > b) { b = x; }
+        }
+      }
+#pragma unroll
+      for (int sft = 16; sft > 0; sft >>= 1) {
+        const float oa = __shfl_xor_sync(0xffffffffu, a, sft), ob = __shfl_xor_sync(0xffffffffu, b, sft);
+        const float hi = fmaxf(a, oa), lo = fmaxf(fminf(a, oa), fmaxf(b, ob));
+        a = hi; b = lo;
+      }
+      if (lane == g) my_g = a + (gsz > 1 ? b : 0.f);
+    }
+    unsigned keep = 0;
+    for (int j = 0; j < o.topk_group; ++j) {
+      float best = my_g;
+      int bg = lane;
+#pragma unroll
+      for (int sft = 16; sft > 0; sft >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, sft);
+        const int og = __shfl_xor_sync(0xffffffffu, bg, sft);
+        if (ob > best || (ob == best && og < bg)) { best = ob; bg = og; }
+      }
+      keep |= 1u << bg;
+      if (lane == bg) my_g = -INFINITY;
+    }
+#pragma unroll
+    for (int i = 0; i < kMaxPer; ++i) {
+      const int e = i * 32 + lane;
+      if (i < per && e < E && !((keep >> (e / gsz)) & 1u)) sel[i] = -INFINITY;
+    }
+  }
+
   float wsum = 0.f;
   float my_w = 0.f;
   int my_id = 0;
   for (int j = 0; j < k; ++j) {
-    float best = -INFINITY;
+    float best = -INFINITY, bw = 0.f;
     int bi = 0x7FFFFFFF;
 #pragma unroll
     for (int i = 0; i < kMaxPer; ++i) {
       const int e = i * 32 + lane;
-      if (i < per && e < E && (v[i] > best)) { best = v[i]; bi = e; }
+      if (i < per && e < E && (sel[i] > best)) { best = sel[i]; bi = e; bw = v[i]; }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    for (int sft = 16; sft > 0; sft >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, sft);
+      const float ow = __shfl_xor_sync(0xffffffffu, bw, sft);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, sft);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; bw = ow; }
     }
     // remove the winner (ties resolve to the lowest expert id)
     if ((bi & 31) == lane) {
 #pragma unroll
       for (int i = 0; i < kMaxPer; ++i)
-        if (i == (bi >> 5)) v[i] = -INFINITY;
+        if (i == (bi >> 5)) sel[i] = -INFINITY;
     }
-    const float pw = best * inv;
+    const float pw = bw * inv;
     wsum += pw;
     if (lane == j) { my_w = pw; my_id = bi; }
   }
   if (lane < k) {
-    w_out[(long long)t * k + lane] = norm ? my_w / fmaxf(wsum, 1e-20f) : my_w;
+    w_out[(long long)t * k + lane] = (norm ? my_w / fmaxf(wsum, 1e-20f) : my_w) * o.out_scale;
     id_out[(long long)t * k + lane] = my_id;
   }
 }
@@ -255,15 +343,34 @@ moe_recv_ids_kernel(const uint8_t* __restrict__ recv, int row_bytes, int H, cons
 
 using namespace atlas;
 
-extern "C" int atlas_moe_route(const void* logits, long long ld, int is_bf16, int T, int E, int k, int norm, int sigmoid,
-                               float* w_out, int* id_out, void* stream) {
+static int route_launch(const void* logits, long long ld, int is_bf16, int T, int E, int k, int norm, RouteOpts o,
+                        float* w_out, int* id_out, void* stream) {
   if (T <= 0) return 0;
   if (E > 1024 || k > 32 || k > E) return -1;
+  if (o.n_group > 1 && (o.n_group > 32 || E % o.n_group)) return -1;
+  if (o.hash_table && !o.token_ids) return -1;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int grid = (T + 3) / 4;
-  if (is_bf16) moe_route_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(logits), ld, T, E, k, norm, sigmoid, w_out, id_out);
-  else moe_route_kernel<float><<<grid, 128, 0, st>>>(reinterpret_cast<const float*>(logits), ld, T, E, k, norm, sigmoid, w_out, id_out);
+  if (is_bf16) moe_route_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(logits), ld, T, E, k, norm, o, w_out, id_out);
+  else moe_route_kernel<float><<<grid, 128, 0, st>>>(reinterpret_cast<const float*>(logits), ld, T, E, k, norm, o, w_out, id_out);
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+extern "C" int atlas_moe_route(const void* logits, long long ld, int is_bf16, int T, int E, int k, int norm, int sigmoid,
+                               float* w_out, int* id_out, void* stream) {
+  RouteOpts o = {};
+  o.score_mode = sigmoid ? 1 : 0;
+  o.out_scale = 1.f;
+  return route_launch(logits, ld, is_bf16, T, E, k, norm, o, w_out, id_out, stream);
+}
+
+extern "C" int atlas_moe_route_ex(const void* logits, long long ld, int is_bf16, int T, int E, int k, int norm, int score_mode,
+                                  const float* sel_bias, int n_group, int topk_group, const int* hash_table,
+                                  const int* token_ids, float out_scale, float* w_out, int* id_out, void* stream) {
+  RouteOpts o = {};
+  o.score_mode = score_mode; o.sel_bias = sel_bias; o.n_group = n_group; o.topk_group = topk_group;
+  o.hash_table = hash_table; o.token_ids = token_ids; o.out_scale = out_scale;
+  return route_launch(logits, ld, is_bf16, T, E, k, norm, o, w_out, id_out, stream);
 }
 
 extern "C" int atlas_moe_align(const int* topk_ids, int T, int k, int e_lo, int E_local, int* slot_of, int* row_token,

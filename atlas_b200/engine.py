@@ -57,7 +57,8 @@ class LLMEngine:
         num_blocks = self.cfg.num_kv_blocks or self._profile_num_blocks()
         n_active = self.cfg.max_num_seqs if self.hybrid else 0
         n_snap = self.cfg.ssm_cache_slots if (self.hybrid and self.cfg.enable_prefix_caching) else 0
-        self.cache: CacheStore = model.alloc_cache(num_blocks, self.cfg.block_size, self.kv_dtype, n_active + n_snap)
+        self.cache: CacheStore = model.alloc_cache(num_blocks, self.cfg.block_size, self.kv_dtype, n_active + n_snap,
+                                                   high_precision_layers=self.cfg.kv_high_precision_layers)
         if os.environ.get("ATLAS_NATIVE_RUNTIME", "0") not in ("0", "", "false"):
             from .runtime_native import NativeBlockPool          # C++ pool, same interface
             self.pool = NativeBlockPool(num_blocks, self.cfg.block_size)
@@ -69,7 +70,7 @@ class LLMEngine:
         self.host_tier = None
         if self.cfg.swap_space_gb > 0:
             from .kv.host_tier import HostKVTier
-            per_block = max(1, model.kv_bytes_per_block(self.cfg.block_size, self.kv_dtype))
+            per_block = max(1, model.kv_bytes_per_block(self.cfg.block_size, self.kv_dtype, self.cfg.kv_high_precision_layers))
             n_host = int(self.cfg.swap_space_gb * (1 << 30)) // per_block
             if n_host > 0:
                 self.host_tier = HostKVTier(self.cache, n_host, self.cfg.max_num_seqs if self.hybrid else 0,
@@ -99,14 +100,14 @@ class LLMEngine:
         want = self.cfg.kv_cache_dtype
         if want == "auto":
             want = self.mcfg.quant.kv_cache_dtype
-        if want == "fp8" or (want == "auto" and self.model.device.type == "cuda"):
-            return torch.float8_e4m3fn      # the GPU attention kernels are FP8-KV only
         if want == "bf16":
-            return torch.bfloat16
+            return torch.bfloat16           # GPU: the general mma.sync attention kernel on a 16-bit cache
+        if want == "fp8" or (want == "auto" and self.model.device.type == "cuda"):
+            return torch.float8_e4m3fn      # default on a GPU: the bulk-copy decode and tcgen05 prefill kernels
         return self.model.dtype
 
     def _profile_num_blocks(self) -> int:
-        per_block = max(1, self.model.kv_bytes_per_block(self.cfg.block_size, self.kv_dtype))
+        per_block = max(1, self.model.kv_bytes_per_block(self.cfg.block_size, self.kv_dtype, self.cfg.kv_high_precision_layers))
         if self.model.device.type == "cuda":
             free, total = torch.cuda.mem_get_info(self.model.device)
             budget = int(total * self.cfg.gpu_memory_utilization) - (total - free)

@@ -88,6 +88,8 @@ class MoE:
         self.experts: Optional[ExpertWeights] = None
         self.shared: Optional[DenseMLP] = None
         self.shared_gate: Optional[torch.Tensor] = None
+        self.router_bias: Optional[torch.Tensor] = None      # fp32 [E]: selection-only correction (e_score_correction_bias)
+        self.hash_table: Optional[torch.Tensor] = None       # int32 [vocab, k]: static token-id -> expert ids
         if cfg.shared_expert_intermediate_size:
             self.shared = DenseMLP(cfg, pctx, dense_kind, cfg.shared_expert_intermediate_size, shard=False)
 
@@ -114,16 +116,21 @@ class MoE:
                 w2_l.append(b.to(device=device, dtype=dtype))
         assert len(w13_l) == n_local
         self.router = LinearWeight("dense", router)
+        if cfg.router_selection_bias:
+            self.router_bias = (torch.rand(cfg.num_experts, generator=gen, device=gen.device) * 0.1).to(device)
         self.experts = ExpertWeights.from_dense(torch.stack(w13_l), torch.stack(w2_l), self.expert_kind)
         if self.shared is not None:
             self.shared.init_random(gen, std, dtype, device)
             self.shared_gate = randn_weight(gen, 1, h, std, dtype, device)
 
     # ------------------------------------------------------------------ forward
-    def forward(self, act: Act) -> torch.Tensor:
+    def forward(self, act: Act, token_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
         x = act.plain()
+        cfg = self.cfg
         logits = ops.linear(x, self.router)
-        topk_w, topk_ids = ops.moe_route(logits, self.top_k, self.cfg.norm_topk_prob, self.cfg.router_scoring)
+        topk_w, topk_ids = ops.moe_route(logits, self.top_k, cfg.norm_topk_prob, cfg.router_scoring, self.router_bias,
+                                         cfg.router_n_group, cfg.router_topk_group, cfg.routed_scaling_factor,
+                                         self.hash_table, token_ids if self.hash_table is not None else None)
         if ops.on_gpu(x):
             y = ops.cuda_ops().moe_forward(x, topk_w, topk_ids, self.experts, self.e_lo, self.pctx, self.ep_mode)
         else:

@@ -83,6 +83,20 @@ def _load_attention(ck, pre, mixer, model, kind) -> None:
     mixer.k_norm = _vec(ck, f"{pre}.k_norm.weight", model)
 
 
+def _load_mla(ck, pre, mixer, model, kind) -> None:
+    """Latent attention: the rope rows of ``q_b`` / ``kv_a`` are reordered and moved in front of the nope rows, which
+    crosses the 128-row scale blocks of a block-quantised checkpoint, so these (small) projections are dequantised
+    and quantised again in the loaded layout."""
+    dq = lambda n: ck.linear(f"{pre}.{n}").dequant().float()
+    has_qa = ck.has(f"{pre}.q_a_proj.weight")
+    q_a = dq("q_a_proj") if has_qa else None
+    q_b = dq("q_b_proj") if has_qa else dq("q_proj")
+    norm = lambda n: ck.get(f"{pre}.{n}.weight").to(device=model.device, dtype=model.dtype).contiguous()
+    cast = lambda t: None if t is None else t.to(device=model.device, dtype=model.dtype)
+    mixer.load(cast(q_a), norm("q_a_layernorm") if has_qa else None, cast(q_b), cast(dq("kv_a_proj_with_mqa")),
+               norm("kv_a_layernorm"), cast(dq("kv_b_proj")), cast(dq("o_proj")), mixer.cfg.rope_interleaved)
+
+
 def _load_mlp(ck, pre, mlp, model, kind) -> None:
     tp, r = (mlp.pctx.tp_size, mlp.pctx.tp_rank) if mlp.shard else (1, 0)
     g, u, dn = (ck.linear(f"{pre}.{n}_proj") for n in ("gate", "up", "down"))
@@ -122,8 +136,12 @@ def _load_moe(ck, pre, moe, model, dense_kind, expert_kind) -> None:
         p13.append(cat_rows([g, u]))
         p2.append(as_q(dn))
     moe.experts = _stack_experts(p13, p2, expert_kind, model)
+    bias = ck.maybe(f"{pre}.gate.e_score_correction_bias")
+    if bias is not None:
+        moe.router_bias = bias.float().to(model.device).contiguous()
     if moe.shared is not None:
-        _load_mlp(ck, f"{pre}.shared_expert", moe.shared, model, dense_kind)
+        shared = "shared_experts" if ck.has(f"{pre}.shared_experts.gate_proj.weight") else "shared_expert"
+        _load_mlp(ck, f"{pre}.{shared}", moe.shared, model, dense_kind)
         sg = ck.maybe(f"{pre}.shared_expert_gate.weight")
         moe.shared_gate = None if sg is None else sg.to(device=model.device, dtype=model.dtype)
 
@@ -134,16 +152,26 @@ def _load_gdn(ck, pre, mixer, model, kind) -> None:
     cfg, tp, r = mixer.cfg, mixer.pctx.tp_size, mixer.pctx.tp_rank
     HK, HV, dk, dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, mixer.dk, mixer.dv
     rep = HV // HK
-    qkvz, ba = ck.linear(f"{pre}.in_proj_qkvz"), ck.linear(f"{pre}.in_proj_ba")
-    grp = 2 * dk + 2 * rep * dv
-    heads = range(r * mixer.hk, (r + 1) * mixer.hk)
-    seg = lambda lo, hi: [qkvz.rows(h * grp + lo, h * grp + hi) for h in heads]
-    qs, ks = seg(0, dk), seg(dk, 2 * dk)
-    vs, zs = seg(2 * dk, 2 * dk + rep * dv), seg(2 * dk + rep * dv, grp)
-    bs = [ba.rows(h * 2 * rep, h * 2 * rep + rep) for h in heads]
-    as_ = [ba.rows(h * 2 * rep + rep, (h + 1) * 2 * rep) for h in heads]
-    main = cat_rows(qs + ks + vs + zs)
-    tail = cat_rows(bs + as_)
+    if ck.has(f"{pre}.in_proj_qkv.weight"):
+        # Qwen3.5 layout: flat [q | k | v] rows plus separate z, b and a projections (value head i pairs with key head
+        # i // rep, so a rank's heads are contiguous row ranges)
+        qkv, zp = ck.linear(f"{pre}.in_proj_qkv"), ck.linear(f"{pre}.in_proj_z")
+        bp, ap = ck.linear(f"{pre}.in_proj_b"), ck.linear(f"{pre}.in_proj_a")
+        KDf, kd, vd, hv_n = HK * dk, mixer.kd, mixer.vd, mixer.hv
+        main = cat_rows([qkv.rows(r * kd, (r + 1) * kd), qkv.rows(KDf + r * kd, KDf + (r + 1) * kd),
+                         qkv.rows(2 * KDf + r * vd, 2 * KDf + (r + 1) * vd), zp.rows(r * vd, (r + 1) * vd)])
+        tail = cat_rows([bp.rows(r * hv_n, (r + 1) * hv_n), ap.rows(r * hv_n, (r + 1) * hv_n)])
+    else:
+        qkvz, ba = ck.linear(f"{pre}.in_proj_qkvz"), ck.linear(f"{pre}.in_proj_ba")
+        grp = 2 * dk + 2 * rep * dv
+        heads = range(r * mixer.hk, (r + 1) * mixer.hk)
+        seg = lambda lo, hi: [qkvz.rows(h * grp + lo, h * grp + hi) for h in heads]
+        qs, ks = seg(0, dk), seg(dk, 2 * dk)
+        vs, zs = seg(2 * dk, 2 * dk + rep * dv), seg(2 * dk + rep * dv, grp)
+        bs = [ba.rows(h * 2 * rep, h * 2 * rep + rep) for h in heads]
+        as_ = [ba.rows(h * 2 * rep + rep, (h + 1) * 2 * rep) for h in heads]
+        main = cat_rows(qs + ks + vs + zs)
+        tail = cat_rows(bs + as_)
     if main.kind == "fp8_block" and main.weight.shape[0] % 128 == 0 and tail.kind == "fp8_block":
         fused = cat_rows([main, tail])
     elif main.kind == tail.kind == "dense":
@@ -166,7 +194,9 @@ def _load_gdn(ck, pre, mixer, model, kind) -> None:
 def _load_layer(ck, pre, layer, model, dense_kind, expert_kind) -> None:
     layer.input_norm = _vec(ck, f"{pre}.input_layernorm.weight", model)
     layer.post_norm = _vec(ck, f"{pre}.post_attention_layernorm.weight", model)
-    if layer.kind == "attention":
+    if layer.kind == "attention" and layer.cfg.kv_lora_rank > 0:
+        _load_mla(ck, f"{pre}.self_attn", layer.mixer, model, dense_kind)
+    elif layer.kind == "attention":
         _load_attention(ck, f"{pre}.self_attn", layer.mixer, model, dense_kind)
     else:
         _load_gdn(ck, f"{pre}.linear_attn", layer.mixer, model, dense_kind)

@@ -17,7 +17,7 @@ import torch
 
 from .. import ops
 from ..config import ModelConfig
-from ..layers import Attention, DenseMLP, GatedDeltaNet, Mamba2Mixer, MoE, ParallelCtx
+from ..layers import Attention, DenseMLP, GatedDeltaNet, Mamba2Mixer, MLAttention, MoE, ParallelCtx
 from ..layers.common import make_weight, randn_weight, shard_rows
 from ..ops import Act, LinearWeight, reference as ref
 from .batch import ForwardBatch
@@ -37,7 +37,7 @@ def kv_dtype_is_fp8(dtype) -> bool:
 def alloc_kv(num_blocks: int, block_size: int, hkv: int, d: int, dtype, device):
     """Paged K and V pools as logical ``[num_blocks, block_size, Hkv, D]`` tensors (the GPU pools are views
     of the kernels' physical layout)."""
-    if torch.device(device).type == "cuda" and kv_dtype_is_fp8(dtype):
+    if torch.device(device).type == "cuda" and (kv_dtype_is_fp8(dtype) or dtype == torch.bfloat16):
         return ops.cuda_ops().alloc_kv_cache(num_blocks, block_size, hkv, d, dtype, device)
     shape = (num_blocks, block_size, hkv, d)
     return torch.zeros(shape, dtype=dtype, device=device), torch.zeros(shape, dtype=dtype, device=device)
@@ -79,7 +79,8 @@ class DecoderLayer:
         self.cfg, self.idx = cfg, idx
         dense_kind, expert_kind = quant_kinds(cfg)
         self.kind = "attention" if force_attention else cfg.layer_kind(idx)
-        self.mixer = Attention(cfg, idx, pctx, dense_kind) if self.kind == "attention" else GatedDeltaNet(cfg, idx, pctx, dense_kind)
+        attn_cls = MLAttention if cfg.kv_lora_rank > 0 else Attention
+        self.mixer = attn_cls(cfg, idx, pctx, dense_kind) if self.kind == "attention" else GatedDeltaNet(cfg, idx, pctx, dense_kind)
         self.is_moe = (cfg.num_experts > 0) if force_attention else cfg.is_moe_layer(idx)
         self.ffn = MoE(cfg, pctx, expert_kind, dense_kind, ep_mode) if self.is_moe else DenseMLP(cfg, pctx, dense_kind)
         self.input_norm: Optional[torch.Tensor] = None
@@ -102,7 +103,8 @@ class DecoderLayer:
     def accepts_prenormed(self) -> bool:
         """This layer's input norm may be applied by the previous layer's down projection (deferred 1/rms factor): its
         only consumer of the normalised input is an FP8 linear layer."""
-        return self.kind == "attention" and self.mixer.qkv.kind == "fp8_block" and self.mixer.lora is None
+        return (self.kind == "attention" and isinstance(self.mixer, Attention) and self.mixer.qkv.kind == "fp8_block"
+                and self.mixer.lora is None)
 
     def forward(self, x, residual: Optional[torch.Tensor], batch: ForwardBatch, cache: CacheStore,
                 rope_cache: torch.Tensor, next_norm: Optional[torch.Tensor] = None):
@@ -137,7 +139,11 @@ class DecoderLayer:
                 and ops.residual_norm_fusable(act, self.ffn.down) and ops.on_gpu(residual)):
             # down_proj + residual add + the NEXT layer's input norm + FP8 quantisation in one epilogue
             return ops.linear_residual_norm(self.ffn.hidden_act(act), self.ffn.down, residual, next_norm, eps, p1)
-        h = self.ffn.forward(act) if self.is_moe else self.ffn.forward(act, batch=batch)
+        if self.is_moe:
+            hashed = self.ffn.hash_table is not None and batch.input_ids is not None
+            h = self.ffn.forward(act, batch.input_ids.to(torch.int32) if hashed else None)
+        else:
+            h = self.ffn.forward(act, batch=batch)
         return h, residual
 
 
@@ -264,16 +270,23 @@ class DecoderLM:
         """Layers with a recurrent state slot (Gated DeltaNet or Mamba-2)."""
         return [l.idx for l in self.layers if l.kind in ("gdn", "mamba2")]
 
-    def kv_bytes_per_block(self, block_size: int, kv_dtype: torch.dtype) -> int:
+    def kv_bytes_per_block(self, block_size: int, kv_dtype: torch.dtype, high_precision_layers=()) -> int:
         n_attn = len(self.attention_layers()) + (1 if self.mtp is not None else 0)
         hkv = self.layers[self.attention_layers()[0]].mixer.hkv if n_attn else 0
-        return 2 * n_attn * block_size * hkv * self.cfg.head_dim * kv_dtype.itemsize
+        n_hi = len([i for i in self.attention_layers() if i in set(high_precision_layers)])
+        per = 2 * block_size * hkv * self.cfg.head_dim
+        return per * ((n_attn - n_hi) * kv_dtype.itemsize + n_hi * max(2, kv_dtype.itemsize))
 
-    def alloc_cache(self, num_blocks: int, block_size: int, kv_dtype: torch.dtype, state_slots: int = 0) -> CacheStore:
+    def alloc_cache(self, num_blocks: int, block_size: int, kv_dtype: torch.dtype, state_slots: int = 0,
+                    high_precision_layers=()) -> CacheStore:
+        """``high_precision_layers``: attention layers whose cache stays in 16 bits when ``kv_dtype`` is FP8 (the layers
+        most sensitive to KV quantisation, typically the first and last ones)."""
         store = CacheStore(block_size=block_size, num_blocks=num_blocks)
+        hi = set(high_precision_layers)
         for l in self.layers:
             if l.kind == "attention":
-                store.kv[l.idx] = alloc_kv(num_blocks, block_size, l.mixer.hkv, self.cfg.head_dim, kv_dtype, self.device)
+                dt = (torch.bfloat16 if self.dtype == torch.bfloat16 else self.dtype) if (l.idx in hi and kv_dtype_is_fp8(kv_dtype)) else kv_dtype
+                store.kv[l.idx] = alloc_kv(num_blocks, block_size, l.mixer.hkv, self.cfg.head_dim, dt, self.device)
                 store.kv_scales[l.idx] = (1.0, 1.0)
             elif l.kind in ("gdn", "mamba2"):
                 store.states[l.idx] = l.mixer.alloc_state(max(1, state_slots), self.device, self.dtype)

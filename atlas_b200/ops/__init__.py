@@ -246,10 +246,11 @@ def paged_attention(q, k_cache, v_cache, batch, scale, k_scale=1.0, v_scale=1.0,
 
 
 # ----------------------------------------------------------------------------- MoE
-def moe_route(logits, top_k, norm_topk, scoring="softmax"):
+def moe_route(logits, top_k, norm_topk, scoring="softmax", bias=None, n_group=0, topk_group=0, scale=1.0, hash_table=None,
+              token_ids=None):
     if on_gpu(logits):
-        return cuda_ops().moe_route(logits, top_k, norm_topk, scoring)
-    return ref.moe_route(logits, top_k, norm_topk, scoring)
+        return cuda_ops().moe_route(logits, top_k, norm_topk, scoring, bias, n_group, topk_group, scale, hash_table, token_ids)
+    return ref.moe_route(logits, top_k, norm_topk, scoring, bias, n_group, topk_group, scale, hash_table, token_ids)
 
 
 # ----------------------------------------------------------------------------- sampling

@@ -414,8 +414,8 @@ def _kv_layout_ok(k_cache: torch.Tensor, v_cache: torch.Tensor) -> None:
     nb, bs, hkv, d = k_cache.shape
     if k_cache.stride() != (hkv * bs * d, d, bs * d, 1) or v_cache.stride() != (hkv * bs * d, 1, d * bs, bs):
         raise KernelError("KV cache is not in the kernel layout (allocate it with ops.cuda.alloc_kv_cache)")
-    if k_cache.dtype != FP8:
-        raise KernelError("the GPU attention kernels read an FP8 (e4m3) KV cache")
+    if k_cache.dtype not in (FP8, torch.bfloat16):
+        raise KernelError("the GPU attention kernels read an FP8 (e4m3) or bf16 KV cache")
 
 
 def qk_norm_rope_kv_write(q, k, v, positions, rope_cache, rotary_dim, k_cache, v_cache, slot_mapping, k_scale, v_scale,
@@ -430,7 +430,7 @@ def qk_norm_rope_kv_write(q, k, v, positions, rope_cache, rotary_dim, k_cache, v
     _check(lib().atlas_rope_kv_write(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
                                      positions.data_ptr(), rope_cache.data_ptr(), _ptr(q_norm_w), _ptr(k_norm_w),
                                      k_cache.data_ptr(), v_cache.data_ptr(), slot_mapping.data_ptr(), T, Hq, Hkv, D,
-                                     rotary_dim, bs, 1, 1 if norm_plus_one else 0, float(eps), float(k_scale),
+                                     rotary_dim, bs, 1 if k_cache.dtype == FP8 else 0, 1 if norm_plus_one else 0, float(eps), float(k_scale),
                                      float(v_scale), _stream()), "rope_kv_write")
     return q
 
@@ -458,6 +458,8 @@ def paged_attention(q, k_cache, v_cache, batch, scale, k_scale, v_scale, sliding
     window = int(sliding_window or 0)
     nd = batch.num_decodes
     st = _stream()
+    if k_cache.dtype == torch.bfloat16:
+        return _paged_attention_kv16(q, out, k_cache, v_cache, batch, scale, window, d)
     if nd > 0:
         splits = decode_splits(nd, Hkv, batch.max_seq_len, _num_sms[d])
         po = pml = None
@@ -508,6 +510,46 @@ def paged_attention(q, k_cache, v_cache, batch, scale, k_scale, v_scale, sliding
                                         batch.query_start_loc.data_ptr(), tdev[0].data_ptr(), tdev[1].data_ptr(),
                                         n_tiles, float(scale), float(k_scale), float(v_scale), Hq, Hkv, D, bs, window,
                                         st), "attn_prefill")
+    return out
+
+
+def _paged_attention_kv16(q, out, k_cache, v_cache, batch, scale, window, d):
+    """bf16 KV cache: the general mma.sync kernel serves decode rows (split-K + merge) and prefill tiles."""
+    T, Hq, D = q.shape
+    nb, bs, Hkv, _ = k_cache.shape
+    L = lib()
+    if not getattr(L, "_kv16_bound", False):
+        L.atlas_attn_decode_kv16.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _f, _i, _i, _i, _i, _i, _i,
+                                             _vp, _vp, _vp]
+        L.atlas_attn_prefill_kv16.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _f, _i, _i, _i, _i, _i, _vp]
+        L._kv16_bound = True
+    bt, st, nd = batch.block_tables, _stream(), batch.num_decodes
+    if nd > 0:
+        splits = decode_splits(nd, Hkv, batch.max_seq_len, _num_sms[d])
+        po = pml = None
+        if splits > 1:
+            po = scratch("attn_part_o", nd * Hq * splits * D * 4, q.device)
+            pml = scratch("attn_part_ml", nd * Hq * splits * 2 * 4, q.device)
+        _check(L.atlas_attn_decode_kv16(q.data_ptr(), q.stride(0), out.data_ptr(), Hq * D, k_cache.data_ptr(), v_cache.data_ptr(),
+                                        bt.data_ptr(), bt.stride(0), batch.seq_lens.data_ptr(), batch.query_start_loc.data_ptr(),
+                                        0, nd, float(scale), Hq, Hkv, D, bs, window, splits, _ptr(po), _ptr(pml), st),
+               "attn_decode_kv16")
+    if batch.num_seqs > nd:
+        tiles = getattr(batch, "_attn_tiles", None)
+        if tiles is None:
+            ts, tq = [], []
+            for i in range(nd, batch.num_seqs):
+                for q0 in range(0, batch.query_lens_host[i], 16):
+                    ts.append(i)
+                    tq.append(q0)
+            host = torch.tensor([ts, tq], dtype=torch.int32).pin_memory()
+            tiles = (host.to(q.device, non_blocking=True), len(ts))
+            batch._attn_tiles = tiles
+        tdev, n_tiles = tiles
+        _check(L.atlas_attn_prefill_kv16(q.data_ptr(), q.stride(0), out.data_ptr(), Hq * D, k_cache.data_ptr(), v_cache.data_ptr(),
+                                         bt.data_ptr(), bt.stride(0), batch.seq_lens.data_ptr(), batch.query_start_loc.data_ptr(),
+                                         tdev[0].data_ptr(), tdev[1].data_ptr(), n_tiles, float(scale), Hq, Hkv, D, bs, window, st),
+               "attn_prefill_kv16")
     return out
 
 
@@ -600,9 +642,9 @@ def spec_accept(draft: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
 
 
 # ----------------------------------------------------------------------------- MoE / GDN (cuda_ext)
-def moe_route(logits, top_k, norm_topk, scoring):
+def moe_route(logits, top_k, norm_topk, scoring, bias=None, n_group=0, topk_group=0, scale=1.0, hash_table=None, token_ids=None):
     from . import cuda_ext
-    return cuda_ext.moe_route(logits, top_k, norm_topk, scoring)
+    return cuda_ext.moe_route(logits, top_k, norm_topk, scoring, bias, n_group, topk_group, scale, hash_table, token_ids)
 
 
 def moe_forward(x, topk_w, topk_ids, experts, e_lo, pctx, ep_mode):

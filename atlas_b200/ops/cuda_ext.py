@@ -89,16 +89,35 @@ _nvfp4_cache = {}
 
 
 # ----------------------------------------------------------------------------- MoE
-def moe_route(logits, top_k, norm_topk, scoring):
+_SCORE_MODES = {"softmax": 0, "sigmoid": 1, "sqrtsoftplus": 2}
+
+
+def moe_route(logits, top_k, norm_topk, scoring, bias=None, n_group=0, topk_group=0, scale=1.0, hash_table=None, token_ids=None):
     T, E = logits.shape
     K._dev(logits)
     if logits.dtype not in (torch.bfloat16, torch.float32):
         logits = logits.float()
     w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
     ids = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
-    K._check(K.lib().atlas_moe_route(logits.data_ptr(), logits.stride(0), 1 if logits.dtype == torch.bfloat16 else 0, T, E,
-                                     top_k, 1 if norm_topk else 0, 1 if scoring == "sigmoid" else 0, w.data_ptr(),
-                                     ids.data_ptr(), K._stream()), "moe_route")
+    plain = bias is None and hash_table is None and scale == 1.0 and not (n_group > 1 and 0 < topk_group < n_group)
+    if plain and scoring in ("softmax", "sigmoid"):
+        K._check(K.lib().atlas_moe_route(logits.data_ptr(), logits.stride(0), 1 if logits.dtype == torch.bfloat16 else 0, T, E,
+                                         top_k, 1 if norm_topk else 0, 1 if scoring == "sigmoid" else 0, w.data_ptr(),
+                                         ids.data_ptr(), K._stream()), "moe_route")
+        return w, ids
+    L = K.lib()
+    if not getattr(L, "_route_ex_bound", False):
+        L.atlas_moe_route_ex.argtypes = [_vp, _ll, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp, _vp, C.c_float, _vp, _vp, _vp]
+        L._route_ex_bound = True
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == E
+    if hash_table is not None:
+        assert hash_table.dtype == torch.int32 and hash_table.is_contiguous() and hash_table.shape[1] == top_k
+        assert token_ids is not None and token_ids.dtype == torch.int32 and token_ids.numel() == T
+    K._check(L.atlas_moe_route_ex(logits.data_ptr(), logits.stride(0), 1 if logits.dtype == torch.bfloat16 else 0, T, E, top_k,
+                                  1 if norm_topk else 0, _SCORE_MODES[scoring], K._ptr(bias), int(n_group), int(topk_group),
+                                  K._ptr(hash_table), K._ptr(token_ids), float(scale), w.data_ptr(), ids.data_ptr(), K._stream()),
+             "moe_route_ex")
     return w, ids
 
 

@@ -98,7 +98,13 @@ def build_rope_cache(rotary_dim: int, max_pos: int, theta: float, scaling: Optio
             ramp = ((torch.arange(half, dtype=torch.float64) - low) / max(high - low, 1e-3)).clamp(0, 1)
             mask = 1 - ramp
             inv_freq = inv_freq / factor * (1 - mask) + inv_freq * mask
-            mscale = float(scaling.get("attention_factor") or (0.1 * math.log(factor) + 1.0 if factor > 1 else 1.0))
+            get = lambda m: 1.0 if factor <= 1 else 0.1 * m * math.log(factor) + 1.0
+            if scaling.get("attention_factor"):
+                mscale = float(scaling["attention_factor"])
+            elif scaling.get("mscale") and scaling.get("mscale_all_dim"):     # DeepSeek convention: ratio of the two
+                mscale = get(float(scaling["mscale"])) / get(float(scaling["mscale_all_dim"]))
+            else:
+                mscale = get(1.0)
     t = torch.arange(max_pos, dtype=torch.float64)
     freqs = torch.outer(t, inv_freq)
     cache = torch.cat([freqs.cos() * mscale, freqs.sin() * mscale], dim=-1).float()
@@ -207,14 +213,48 @@ def silu_mul_quant_fp8(gate_up: torch.Tensor, group: int = 128):
 
 
 # ----------------------------------------------------------------------------- MoE
-def moe_route(logits: torch.Tensor, top_k: int, norm_topk: bool, scoring: str = "softmax"):
-    """Router scores -> (weights ``[T,k]`` fp32, expert ids ``[T,k]`` int32); ties pick the lower id."""
+def route_scores(logits: torch.Tensor, scoring: str) -> torch.Tensor:
     lf = logits.float()
-    probs = torch.softmax(lf, -1) if scoring == "softmax" else torch.sigmoid(lf)
-    w, ids = torch.topk(probs, top_k, dim=-1, sorted=True)
+    if scoring == "sigmoid":
+        return torch.sigmoid(lf)
+    if scoring == "sqrtsoftplus":
+        return torch.sqrt(F.softplus(lf))
+    return torch.softmax(lf, -1)
+
+
+def moe_route(logits: torch.Tensor, top_k: int, norm_topk: bool, scoring: str = "softmax", bias: Optional[torch.Tensor] = None,
+              n_group: int = 0, topk_group: int = 0, scale: float = 1.0, hash_table: Optional[torch.Tensor] = None,
+              token_ids: Optional[torch.Tensor] = None):
+    """Router scores -> (weights ``[T,k]`` fp32, expert ids ``[T,k]`` int32); ties pick the lower id.
+
+    ``bias`` biases the SELECTION only (weights come from the unbiased scores).  ``n_group`` / ``topk_group``: a group
+    scores the sum of its two best biased scores and only the best ``topk_group`` groups stay eligible.  ``hash_table
+    [vocab, k]`` replaces selection by a lookup on ``token_ids``.  ``scale`` multiplies the final weights.
+    """
+    probs = route_scores(logits, scoring)
+    if hash_table is not None:
+        ids = hash_table.to(logits.device)[token_ids.long()].long().clamp(0, probs.shape[-1] - 1)
+        w = probs.gather(-1, ids)
+        if norm_topk:
+            w = w / (w.sum(-1, keepdim=True) + 1e-20)
+        return w * scale, ids.to(torch.int32)
+    sel = probs if bias is None else probs + bias.float()
+    if n_group > 1 and 0 < topk_group < n_group:
+        T, E = sel.shape
+        g = sel.view(T, n_group, E // n_group)
+        gs = g.topk(min(2, g.shape[-1]), dim=-1).values.sum(-1)
+        keep = torch.zeros_like(gs, dtype=torch.bool).scatter_(1, _topk_low_ties(gs, topk_group), True)
+        sel = g.masked_fill(~keep[..., None], float("-inf")).view(T, E)
+    ids = _topk_low_ties(sel, top_k)
+    w = probs.gather(-1, ids)
     if norm_topk:
         w = w / w.sum(-1, keepdim=True).clamp_min(1e-20)
-    return w, ids.to(torch.int32)
+    return w * scale, ids.to(torch.int32)
+
+
+def _topk_low_ties(x: torch.Tensor, k: int) -> torch.Tensor:
+    """Indices of the k largest along the last dim, descending, ties to the lower index (a stable sort gives that)."""
+    return torch.sort(x, dim=-1, descending=True, stable=True).indices[..., :k]
 
 
 def moe_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: torch.Tensor,

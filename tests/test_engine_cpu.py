@@ -3,7 +3,7 @@ reproduce a plain eager forward (greedy tokens and logits)."""
 import pytest
 import torch
 
-from atlas_b200.config import EngineConfig, tiny_dense, tiny_hybrid, tiny_moe, tiny_nemotron_h
+from atlas_b200.config import EngineConfig, tiny_deepseek, tiny_dense, tiny_hybrid, tiny_moe, tiny_nemotron_h
 from atlas_b200.engine import LLMEngine
 from atlas_b200.models import ForwardBatch, build_model
 from atlas_b200.sampling import SamplingParams
@@ -21,7 +21,7 @@ def _eager_greedy(model, prompt, n):
     return toks[len(prompt):]
 
 
-@pytest.mark.parametrize("mk", [tiny_dense, tiny_moe, tiny_hybrid, tiny_nemotron_h])
+@pytest.mark.parametrize("mk", [tiny_dense, tiny_moe, tiny_hybrid, tiny_nemotron_h, tiny_deepseek])
 def test_engine_matches_eager_greedy(mk):
     model = build_model(mk()).init_random(0)
     eng = LLMEngine(model, EngineConfig(block_size=16, num_kv_blocks=64, max_num_seqs=8, max_prefill_tokens=48))
@@ -33,7 +33,7 @@ def test_engine_matches_eager_greedy(mk):
     eng.pool.check_invariants()
 
 
-@pytest.mark.parametrize("mk", [tiny_dense, tiny_moe, tiny_hybrid, tiny_nemotron_h])
+@pytest.mark.parametrize("mk", [tiny_dense, tiny_moe, tiny_hybrid, tiny_nemotron_h, tiny_deepseek])
 def test_paged_chunked_logits_match_eager(mk):
     model = build_model(mk()).init_random(0)
     toks = _prompts(1, 40)[0]

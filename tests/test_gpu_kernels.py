@@ -205,7 +205,7 @@ def test_rope_kv_write_prefill_pages(K):
     assert float((vc.float() - vc_r.float()).abs().max()) < 0.6        # no misplaced rows (values are O(1))
 
 
-def _attention_case(K, D, Hq, Hkv, qlens, ctxs, bs=16, window=None, seed=6):
+def _attention_case(K, D, Hq, Hkv, qlens, ctxs, bs=16, window=None, seed=6, kv_dtype=torch.float8_e4m3fn):
     from atlas_b200.models.batch import ForwardBatch
     torch.manual_seed(seed)
     B = len(qlens)
@@ -217,21 +217,59 @@ def _attention_case(K, D, Hq, Hkv, qlens, ctxs, bs=16, window=None, seed=6):
     for n in nblk:
         tables.append(perm[off:off + n])
         off += n
-    kc, vc = _mk_cache(K, nb, bs, Hkv, D)
+    kc, vc = K.alloc_kv_cache(nb, bs, Hkv, D, kv_dtype, DEV)
     # fill the cache through the logical view
     kf = (torch.randn(nb, bs, Hkv, D, device=DEV) * 0.5)
     vf = (torch.randn(nb, bs, Hkv, D, device=DEV) * 0.5)
-    kc.copy_(kf.to(torch.float8_e4m3fn))
-    vc.copy_(vf.to(torch.float8_e4m3fn))
+    kc.copy_(kf.to(kv_dtype))
+    vc.copy_(vf.to(kv_dtype))
     toks = [[0] * q for q in qlens]
     fb = ForwardBatch.build(toks, ctxs, tables, bs, device=DEV)
     T = sum(qlens)
     q = (torch.randn(T, Hq, D, device=DEV) * 0.5).bfloat16()
     scale = D ** -0.5
-    out = K.paged_attention(q, kc, vc, fb, scale, 0.7, 1.3, window)
-    want = ref.paged_attention(q, kc, vc, fb.block_tables, fb.seq_lens, fb.query_start_loc, scale, 0.7, 1.3, window)
+    ks, vs = (0.7, 1.3) if kv_dtype == torch.float8_e4m3fn else (1.0, 1.0)      # a 16-bit cache stores unscaled values
+    out = K.paged_attention(q, kc, vc, fb, scale, ks, vs, window)
+    want = ref.paged_attention(q, kc, vc, fb.block_tables, fb.seq_lens, fb.query_start_loc, scale, ks, vs, window)
     _status_ok(K)
     return out, want
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(128, 8, 2), (64, 4, 4), (256, 16, 2), (128, 32, 8)])
+def test_attention_bf16_cache(K, D, Hq, Hkv):
+    """16-bit KV cache: decode rows (short, page-boundary and split-K lengths), prefill chunks and a mixed batch."""
+    out, want = _attention_case(K, D, Hq, Hkv, qlens=[1, 1, 1, 1, 1], ctxs=[1, 15, 16, 200, 3000], kv_dtype=torch.bfloat16)
+    assert _rel_rms(out, want) < 1.5e-2
+    torch.testing.assert_close(out.float(), want.float(), atol=3e-2, rtol=5e-2)
+    out, want = _attention_case(K, D, Hq, Hkv, qlens=[1, 1, 40, 16, 5, 130], ctxs=[33, 700, 0, 48, 100, 77],
+                                kv_dtype=torch.bfloat16)
+    assert _rel_rms(out, want) < 1.5e-2
+    torch.testing.assert_close(out.float(), want.float(), atol=3e-2, rtol=5e-2)
+
+
+def test_attention_bf16_cache_window_big_pages(K):
+    out, want = _attention_case(K, 128, 8, 2, qlens=[1, 1, 50], ctxs=[300, 40, 90], bs=64, window=64, kv_dtype=torch.bfloat16)
+    assert _rel_rms(out, want) < 1.5e-2
+
+
+def test_rope_kv_write_bf16_cache(K):
+    torch.manual_seed(16)
+    D, Hq, Hkv, bs, nb = 128, 8, 2, 16, 24
+    for T in (5, 300):
+        qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=DEV).bfloat16()
+        q = qkv[:, :Hq * D].view(T, Hq, D)
+        k = qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
+        v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+        pos = torch.arange(T, device=DEV, dtype=torch.int32)
+        slots = torch.randperm(nb * bs, device=DEV)[:T].to(torch.int32)
+        rope = ref.build_rope_cache(D, 512, 1e6, None, DEV)
+        kc, vc = K.alloc_kv_cache(nb, bs, Hkv, D, torch.bfloat16, DEV)
+        kc_r, vc_r = torch.zeros_like(kc.contiguous()), torch.zeros_like(vc.contiguous())
+        ref.qk_norm_rope_kv_write(q.clone(), k, v, pos, rope, D, kc_r, vc_r, slots, 1.0, 1.0, None, None, 1e-6, False)
+        K.qk_norm_rope_kv_write(q, k, v, pos, rope, D, kc, vc, slots, 1.0, 1.0, None, None, 1e-6, False)
+        _status_ok(K)
+        assert _rel_rms(kc.float(), kc_r.float()) < 1e-2
+        assert _rel_rms(vc.float(), vc_r.float()) < 1e-2
 
 
 @pytest.mark.parametrize("D,Hq,Hkv", [(128, 8, 2), (64, 4, 4), (256, 16, 2), (128, 32, 8)])
@@ -270,6 +308,26 @@ def test_attention_sliding_window_and_big_pages(K):
 def test_attention_decode_long_splitk(K):
     out, want = _attention_case(K, 128, 8, 1, qlens=[1, 1], ctxs=[5000, 9000])
     assert _rel_rms(out, want) < 2e-2
+
+
+@pytest.mark.parametrize("scoring,bias,groups,hashed", [("sigmoid", True, (8, 4), False), ("sqrtsoftplus", True, (0, 0), False),
+                                                        ("softmax", True, (0, 0), False), ("sqrtsoftplus", False, (0, 0), True),
+                                                        ("sigmoid", False, (4, 2), False)])
+def test_moe_route_variants(K, scoring, bias, groups, hashed):
+    torch.manual_seed(21)
+    T, E, k = 300, 256, 8
+    lg = torch.randn(T, E, device=DEV).bfloat16()
+    b = (torch.randn(E, device=DEV) * 0.2) if bias else None
+    tab = torch.stack([torch.randperm(E, device=DEV)[:k] for _ in range(500)]).to(torch.int32) if hashed else None
+    tok = torch.randint(0, 500, (T,), device=DEV, dtype=torch.int32) if hashed else None
+    w, ids = K.moe_route(lg, k, True, scoring, b, groups[0], groups[1], 2.5, tab, tok)
+    w_r, ids_r = ref.moe_route(lg, k, True, scoring, b, groups[0], groups[1], 2.5, tab, tok)
+    # near-ties may order differently in fp32: compare the selected sets through a dense scatter of the weights
+    dense = torch.zeros(T, E, device=DEV).scatter_(1, ids.long(), w)
+    dense_r = torch.zeros(T, E, device=DEV).scatter_(1, ids_r.long(), w_r)
+    assert (ids.long().sort(-1).values == ids_r.long().sort(-1).values).float().mean() > 0.995
+    assert float((dense - dense_r).abs().max()) < 0.05 * 2.5
+    torch.testing.assert_close(w.sum(-1), torch.full((T,), 2.5, device=DEV), atol=1e-3, rtol=1e-3)
 
 
 # ----------------------------------------------------------------------------- sampling

@@ -186,7 +186,7 @@ def test_gdn_chunked_matches_recurrence(K, split, monkeypatch):
         assert _rel_rms(st_c["h"][slot], st_r["h"][slot]) < 1e-2, slot
 
 
-def _logits_both_ways(cfg, prompt_len=48):
+def _logits_both_ways(cfg, prompt_len=48, kv_dtype=torch.float8_e4m3fn, high_precision_layers=()):
     model = build_model(cfg, device=DEV).init_random(0)
     g = torch.Generator().manual_seed(3)
     toks = torch.randint(0, cfg.vocab_size, (prompt_len,), generator=g).tolist()
@@ -194,7 +194,7 @@ def _logits_both_ways(cfg, prompt_len=48):
     for force in (False, True):
         ops.FORCE_REFERENCE = force
         try:
-            cache = model.alloc_cache(8, 16, torch.float8_e4m3fn, state_slots=2)
+            cache = model.alloc_cache(8, 16, kv_dtype, state_slots=2, high_precision_layers=high_precision_layers)
             fb = ForwardBatch.build([toks[:30]], [0], [[3, 1, 4, 0]], 16, device=DEV, state_slots=[1], has_state=[False], all_logits=True)
             l1 = model.compute_logits(model.forward(fb, cache))
             fb = ForwardBatch.build([toks[30:]], [30], [[3, 1, 4, 0]], 16, device=DEV, state_slots=[1], has_state=[True], all_logits=True)
@@ -207,9 +207,25 @@ def _logits_both_ways(cfg, prompt_len=48):
     return outs
 
 
-@pytest.mark.parametrize("name", ["dense_fp8", "dense_bf16", "moe_fp8", "hybrid_bf16", "hybrid_fp8", "nemotron_bf16", "nemotron_fp8"])
+@pytest.mark.parametrize("name", ["dense_fp8", "dense_bf16", "moe_fp8", "hybrid_bf16", "hybrid_fp8", "nemotron_bf16", "nemotron_fp8",
+                                  "dense_fp8_kvbf16", "dense_fp8_kvmixed", "mla_bf16", "mla_fp8"])
 def test_model_logits_kernels_vs_reference(K, name):
-    if name.startswith("nemotron"):
+    kv_dtype, hi = torch.float8_e4m3fn, ()
+    if name.endswith("kvbf16"):
+        kv_dtype = torch.bfloat16                       # 16-bit paged cache on the general attention kernel
+    if name.endswith("kvmixed"):
+        hi = (0, 2)                                     # FP8 cache with two layers kept in 16 bits
+    if name.startswith("mla"):
+        # latent attention (low-rank q / kv projections, shared rotary key part) + group-limited sigmoid router with a
+        # selection bias, a shared expert and a leading dense layer (DeepSeek-V3 shape)
+        cfg = ModelConfig(model_type="deepseek_v3", family="moe", vocab_size=2048, hidden_size=512, intermediate_size=1024,
+                          num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=8, head_dim=256,
+                          partial_rotary_factor=0.25, kv_lora_rank=128, q_lora_rank=256, qk_nope_head_dim=128,
+                          qk_rope_head_dim=64, v_head_dim=128, num_experts=16, num_experts_per_tok=4, moe_intermediate_size=256,
+                          shared_expert_intermediate_size=256, first_k_dense_replace=1, router_scoring="sigmoid",
+                          router_selection_bias=True, router_n_group=4, router_topk_group=2, routed_scaling_factor=2.5,
+                          max_position_embeddings=4096, quant=QuantConfig(method="fp8_block" if name.endswith("fp8") else "none"))
+    elif name.startswith("nemotron"):
         # Mamba-2 / position-free attention / relu^2 MLP blocks (Nemotron-H), three steps: chunk, chunk with state, decode
         cfg = ModelConfig(model_type="nemotron_h", family="hybrid", vocab_size=2048, hidden_size=512, intermediate_size=1024,
                           num_hidden_layers=5, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
@@ -228,12 +244,12 @@ def test_model_logits_kernels_vs_reference(K, name):
                           max_position_embeddings=4096, quant=QuantConfig(method="fp8_block"))
     else:
         cfg = _hybrid_cfg("fp8_block" if name.endswith("fp8") else "none")
-    got, want = _logits_both_ways(cfg)
+    got, want = _logits_both_ways(cfg, kv_dtype=kv_dtype, high_precision_layers=hi)
     torch.cuda.synchronize()
     assert K.check_status() == 0
     # fp8 activations feeding a top-2-of-8 router flip a few expert choices between the two paths; that case is
     # judged more loosely (the same layers pass the tight bound in bf16 and with a wider top-k)
-    loose = name == "hybrid_fp8"
+    loose = name in ("hybrid_fp8", "mla_fp8")
     assert _rel_rms(got, want) < (0.35 if loose else 8e-2), _rel_rms(got, want)
     agree = (got.argmax(-1) == want.argmax(-1)).float().mean().item()
     assert agree > (0.5 if loose else 0.85), agree

@@ -42,6 +42,29 @@ def _hf(kind: str):
                                            partial_rotary_factor=0.25, layer_types=["linear_attention", "full_attention"],
                                            **common)
         m = transformers.Qwen3NextForCausalLM(cfg)
+    elif kind == "qwen3_5":
+        cfg = transformers.Qwen3_5TextConfig(intermediate_size=512, linear_num_key_heads=2, linear_num_value_heads=4,
+                                             linear_key_head_dim=64, linear_value_head_dim=64, linear_conv_kernel_dim=4,
+                                             layer_types=["linear_attention", "full_attention"], **common)
+        m = transformers.Qwen3_5ForCausalLM(cfg)
+    elif kind == "qwen3_5_moe":
+        cfg = transformers.Qwen3_5MoeTextConfig(moe_intermediate_size=128, shared_expert_intermediate_size=128, num_experts=8,
+                                                num_experts_per_tok=2, linear_num_key_heads=2, linear_num_value_heads=4,
+                                                linear_key_head_dim=64, linear_value_head_dim=64, linear_conv_kernel_dim=4,
+                                                layer_types=["linear_attention", "full_attention"], **common)
+        m = transformers.Qwen3_5MoeForCausalLM(cfg)
+    elif kind == "deepseek_v3":
+        cfg = transformers.DeepseekV3Config(vocab_size=512, hidden_size=256, num_hidden_layers=3, num_attention_heads=4,
+                                            num_key_value_heads=4, intermediate_size=512, moe_intermediate_size=128,
+                                            n_routed_experts=8, num_experts_per_tok=2, n_shared_experts=1, n_group=4, topk_group=2,
+                                            first_k_dense_replace=1, kv_lora_rank=64, q_lora_rank=96, qk_nope_head_dim=32,
+                                            qk_rope_head_dim=16, v_head_dim=32, max_position_embeddings=256,
+                                            routed_scaling_factor=2.5, norm_topk_prob=True, tie_word_embeddings=False)
+        m = transformers.DeepseekV3ForCausalLM(cfg)
+        with torch.no_grad():
+            for n, b in m.named_buffers():
+                if n.endswith("e_score_correction_bias"):
+                    b.copy_(torch.rand_like(b) * 0.2)
     elif kind == "nemotron_h":
         cfg = transformers.NemotronHConfig(vocab_size=512, hidden_size=256, layers_block_type=["mamba", "attention", "mamba", "mamba"],
                                            num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=512,
@@ -72,7 +95,7 @@ def _ours_logits(model, toks):
     return model.forward_dense_reference(toks)
 
 
-@pytest.mark.parametrize("kind", ["llama", "qwen2", "qwen3", "qwen3_moe", "qwen3_next", "nemotron_h"])
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "qwen3", "qwen3_moe", "qwen3_next", "qwen3_5", "qwen3_5_moe", "nemotron_h", "deepseek_v3"])
 def test_logits_match_transformers(kind, tmp_path):
     hf = _hf(kind)
     path = _save(hf, tmp_path)
@@ -84,7 +107,7 @@ def test_logits_match_transformers(kind, tmp_path):
     torch.testing.assert_close(got, want, atol=2e-4, rtol=1e-3)
 
 
-@pytest.mark.parametrize("kind", ["qwen3", "qwen3_next", "nemotron_h"])
+@pytest.mark.parametrize("kind", ["qwen3", "qwen3_next", "qwen3_5", "nemotron_h", "deepseek_v3"])
 def test_sharded_load_matches_full(kind, tmp_path):
     """TP=2 (dense) / TP=2+EP=2 (hybrid MoE): the ranks, run in lock-step over the in-process fake communicator,
     reproduce the single-rank logits."""

@@ -576,3 +576,30 @@ def test_attention_scratch_is_reserved_once_and_never_replaced(preset, tp, monke
             assert K.scratch("attn_part_o", b * hq * s * d * 4, dev).data_ptr() == base
     with pytest.raises(K.KernelError):
         K.scratch("attn_part_o", max(po, 1 << 20) + 1, dev)
+
+
+def test_router_variants_reference():
+    """Selection bias, group-limited routing, sqrt-softplus scores, static hash selection and the weight scale, each
+    against a direct restatement of the published routing rule."""
+    import torch
+    from atlas_b200.ops import reference as ref
+    torch.manual_seed(0)
+    lg = torch.randn(7, 64)
+    w, i = ref.moe_route(lg, 4, True)
+    w0 = torch.softmax(lg, -1).topk(4).values
+    assert torch.allclose(w, w0 / w0.sum(-1, keepdim=True))
+    b = torch.randn(64) * 0.1
+    w, i = ref.moe_route(lg, 4, True, "sigmoid", b, 8, 3, 2.5)
+    sc = torch.sigmoid(lg)
+    s2 = sc + b
+    gi = s2.view(7, 8, 8).topk(2, -1).values.sum(-1).topk(3, -1).indices
+    mask = torch.zeros(7, 8).scatter_(1, gi, 1)[..., None].expand(7, 8, 8).reshape(7, 64).bool()
+    ti = s2.masked_fill(~mask, 0.0).topk(4, -1).indices
+    tw = sc.gather(1, ti)
+    assert (ti == i).all() and torch.allclose(tw / (tw.sum(-1, keepdim=True) + 1e-20) * 2.5, w, atol=1e-6)
+    tab = torch.randint(0, 64, (100, 4), dtype=torch.int32)
+    tok = torch.randint(0, 100, (7,), dtype=torch.int32)
+    w, i = ref.moe_route(lg, 4, True, "sqrtsoftplus", None, 0, 0, 1.5, tab, tok)
+    assert (i == tab[tok.long()]).all() and torch.allclose(w.sum(-1), torch.full((7,), 1.5))
+    sp = torch.sqrt(torch.nn.functional.softplus(lg)).gather(1, i.long())
+    assert torch.allclose(w, sp / sp.sum(-1, keepdim=True) * 1.5, atol=1e-6)
