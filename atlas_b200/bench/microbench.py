@@ -159,6 +159,24 @@ def run(model: str = "llama3-8b", decode_batch: int = 128, ctx: int = 1152, chun
                     flops=2 * M * N * Kd)
                 del pk, bs, gs
 
+    if not only or "w4a4" in only:
+        # NVFP4 x NVFP4 on the block-scaled tensor cores: the GEMM alone, and with the activation quantiser in front
+        from atlas_b200.ops import cuda_fp4 as F4
+        for M in (decode_batch, chunk):
+            x = torch.randn(M, max(H, I), device=dev).bfloat16()
+            for name, N, Kd in gemms:
+                pk, bs, gs = Q.quantize_nvfp4(torch.randn(N, Kd, device=dev) * 0.02)
+                wsf = F4.sf_atoms(bs)
+                col = gs.expand(N).contiguous()
+                xa = x[:, :Kd].contiguous()
+                xq, xsf, xrs = F4.quant_nvfp4(xa)
+                out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+                ms = T.time(lambda: F4.gemm_w4a4(xq, xsf, xrs, pk, wsf, col, out=out))
+                add(f"gemm_nvfp4_w4a4 {name} M={M} N={N} K={Kd}", ms, bytes_=(N + M) * Kd * 9 // 16 + 2 * M * N, flops=2 * M * N * Kd)
+                ms = T.time(lambda: F4.quant_nvfp4(xa))
+                add(f"quant_nvfp4 {name} M={M} K={Kd}", ms, bytes_=M * Kd * 2 + M * Kd * 9 // 16)
+                del pk, bs, gs, wsf
+
     if only and only.startswith("one:"):
         # one FP8 GEMM shape, few launches, no graph: the case to put under a profiler.  only = "one:<name>:<M>"
         _, name, m_s = only.split(":")
