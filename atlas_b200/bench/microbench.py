@@ -95,7 +95,7 @@ def run(model: str = "llama3-8b", decode_batch: int = 128, ctx: int = 1152, chun
     H, I = cfg.hidden_size, cfg.intermediate_size
     qkv_n = cfg.q_size + 2 * cfg.kv_size
     gemms = [("qkv", qkv_n, H), ("o", H, cfg.q_size), ("gate_up", 2 * I, H), ("down", H, I)]
-    if not only or "gemm" in only:
+    if not only or only == "gemm":
         for M in (decode_batch, chunk):
             x = torch.randn(M, max(H, I), device=dev).bfloat16()
             for name, N, Kd in gemms:
@@ -159,7 +159,7 @@ def run(model: str = "llama3-8b", decode_batch: int = 128, ctx: int = 1152, chun
                     flops=2 * M * N * Kd)
                 del pk, bs, gs
 
-    if not only or "w4a4" in only:
+    if not only or only == "w4a4":
         # NVFP4 x NVFP4 on the block-scaled tensor cores: the GEMM alone, and with the activation quantiser in front
         from atlas_b200.ops import cuda_fp4 as F4
         for M in (decode_batch, chunk):
@@ -176,6 +176,22 @@ def run(model: str = "llama3-8b", decode_batch: int = 128, ctx: int = 1152, chun
                 ms = T.time(lambda: F4.quant_nvfp4(xa))
                 add(f"quant_nvfp4 {name} M={M} K={Kd}", ms, bytes_=M * Kd * 2 + M * Kd * 9 // 16)
                 del pk, bs, gs, wsf
+
+    if only and only.startswith("one4:"):
+        # one NVFP4 x NVFP4 GEMM shape, few launches, no graph: the case to put under a profiler.  only = "one4:<name>:<M>"
+        from atlas_b200.ops import cuda_fp4 as F4
+        _, name, m_s = only.split(":")
+        M = int(m_s)
+        N, Kd = {n: (a, b) for n, a, b in gemms}[name]
+        pk, bs, gs = Q.quantize_nvfp4(torch.randn(N, Kd, device=dev) * 0.02)
+        wsf, col = F4.sf_atoms(bs), gs.expand(N).contiguous()
+        xq, xsf, xrs = F4.quant_nvfp4(torch.randn(M, Kd, device=dev).bfloat16())
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        T.use_graph = False
+        ms = T.time(lambda: F4.gemm_w4a4(xq, xsf, xrs, pk, wsf, col, out=out), iters=3, warmup=2)
+        add(f"gemm_nvfp4_w4a4 {name} M={M} N={N} K={Kd}", ms, bytes_=(N + M) * Kd * 9 // 16 + 2 * M * N, flops=2 * M * N * Kd,
+            note="eager launch")
+        return rows
 
     if only and only.startswith("one:"):
         # one FP8 GEMM shape, few launches, no graph: the case to put under a profiler.  only = "one:<name>:<M>"

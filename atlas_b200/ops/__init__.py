@@ -7,6 +7,7 @@ built ``libatlas_b200_kernels.so`` raises instead of silently running eager PyTo
 from __future__ import annotations
 
 from dataclasses import dataclass
+import os
 from typing import List, Optional, Tuple
 
 import torch
@@ -173,8 +174,14 @@ def linear(a, w: LinearWeight, out: Optional[torch.Tensor] = None) -> torch.Tens
             y = Q.fp8_block_gemm_ref(q, s, w.weight, w.scale, out_dtype=act.out_dtype)
     elif w.kind == "nvfp4":
         x = act.plain()
-        if dev_cuda:
+        w4a4 = NVFP4_ACTIVATIONS and x.shape[-1] % 64 == 0
+        if dev_cuda and w4a4:
+            from . import cuda_fp4
+            y = cuda_fp4.linear_w4a4(x, w, out=out)
+        elif dev_cuda:
             y = cuda_ops().gemm_nvfp4(x, w.weight, w.scale, w.gscale, out=out)
+        elif w4a4:
+            y = (ref.quant_nvfp4_rowwise(x) @ w.dequantized().t()).to(x.dtype)
         else:
             y = (x.float() @ w.dequantized().t()).to(x.dtype)
     else:
@@ -187,6 +194,10 @@ def linear(a, w: LinearWeight, out: Optional[torch.Tensor] = None) -> torch.Tens
         y = y + w.bias
     return y
 
+
+# NVFP4 weights: quantise the activations to NVFP4 too and run the block-scaled FP4 x FP4 tensor-core GEMM (what an
+# "NVFP4" ModelOpt checkpoint is calibrated for); off = weight-only (activations stay bf16)
+NVFP4_ACTIVATIONS = os.environ.get("ATLAS_NVFP4_W4A4", "0") == "1"
 
 FUSED_EPILOGUES = True      # tests switch this off to compare against the unfused kernel sequence
 

@@ -83,3 +83,20 @@ def dequant(q: torch.Tensor, sf: torch.Tensor, outer: Optional[torch.Tensor], ro
     s = sf_from_atoms(sf, rows, k).view(torch.float8_e4m3fn)
     g = torch.ones(1, device=q.device) if outer is None else outer
     return Q.dequantize_nvfp4(q, s, g)
+
+
+def linear_w4a4(x: torch.Tensor, w, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ W^T`` for an NVFP4 ``LinearWeight`` with the activations quantised to NVFP4 on the fly (per-row second-level
+    scale).  The weight's scale factors are put into atom order once and cached on the weight object."""
+    cache = getattr(w, "_w4a4", None)
+    if cache is None:
+        N = w.weight.shape[0]
+        g = w.gscale.float().reshape(-1)
+        col = (g.expand(N) if g.numel() == 1 else g).contiguous()
+        cache = w._w4a4 = (sf_atoms(w.scale), col)
+    if x.dtype != torch.bfloat16:
+        x = x.bfloat16()
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    xq, xsf, xrs = quant_nvfp4(x)
+    return gemm_w4a4(xq, xsf, xrs, w.weight, cache[0], cache[1], out=out)

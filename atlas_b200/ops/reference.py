@@ -213,6 +213,23 @@ def silu_mul_quant_fp8(gate_up: torch.Tensor, group: int = 128):
 
 
 # ----------------------------------------------------------------------------- MoE
+def quant_nvfp4_rowwise(x: torch.Tensor) -> torch.Tensor:
+    """What the W4A4 path's activation quantiser stands for, as an fp32 matrix: per row a second-level scale
+    ``g = amax / (6 * 448)``, per 16 values an e4m3 scale factor against ``g``, values rounded to e2m1."""
+    from ..quant import E2M1_MAX, _e2m1_lut, _round_to_e2m1_code
+    xf = x.float()
+    T, K = xf.shape
+    amax = xf.abs().amax(-1, keepdim=True)
+    g = torch.where(amax > 0, amax / (E2M1_MAX * FP8_MAX), torch.ones_like(amax))
+    grp = xf.view(T, K // 16, 16)
+    s8 = (grp.abs().amax(-1) / (E2M1_MAX * g)).clamp(max=FP8_MAX).to(FP8).float()
+    s = s8 * g
+    inv = torch.where(s > 0, 1.0 / s, torch.zeros_like(s))
+    codes = _round_to_e2m1_code(grp * inv[..., None])
+    vals = _e2m1_lut(x.device)[codes.long()]
+    return (vals * s[..., None]).view(T, K)
+
+
 def route_scores(logits: torch.Tensor, scoring: str) -> torch.Tensor:
     lf = logits.float()
     if scoring == "sigmoid":

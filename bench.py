@@ -108,7 +108,7 @@ def _torch_nccl_arm(args, mcfg, topo, device, real_stdout) -> int:
                 "dtype": "fp8-e4m3 weights and activations (row-wise scales, cuBLASLt), bf16 KV",
                 "data": "synthetic: uniform-random token ids, random-init N(0,0.02) weights quantized to fp8",
                 "config": {"model": args.model, "global_batch": args.concurrency, "seq_len": args.isl + args.osl, "isl": args.isl,
-                           "osl": args.osl, "parallelism": f"tp{world}", "collectives": "nccl" if world > 1 else "none",
+                           "osl": args.osl, "parallelism": f"tp{topo.tp_size}" + (f"+ep{topo.ep_size}" if topo.ep_size > 1 else ""), "collectives": "nccl" if world > 1 else "none",
                            "l2": "inputs larger than L2", "step": "one wave of `global_batch` concurrent requests, prefill + decode",
                            "note": "THIS REPOSITORY'S OWN BASELINE, not the upstream reference: eager PyTorch, torch._scaled_mm, "
                                    "SDPA, dense KV cache, static batch, no scheduler, no CUDA graphs"},
@@ -143,6 +143,14 @@ def main():
     ap.add_argument("--num-drafts", type=int, default=3)
     ap.add_argument("--prefix-cache", action="store_true")
     ap.add_argument("--shared-prefix", type=int, default=0, help="every second prompt starts with the same N tokens")
+    ap.add_argument("--ep", type=int, default=0,
+                    help="expert-parallel size for MoE models (0 = none; N = every rank owns 1/N of the experts while attention "
+                         "stays tensor parallel over all ranks)")
+    ap.add_argument("--ep-mode", default="auto", choices=["auto", "allreduce", "alltoall"],
+                    help="expert-parallel data path: local experts + fused combine/all-reduce, or peer-memory all-to-all")
+    ap.add_argument("--ngram-speculative", action="store_true", help="prompt-lookup drafts (no draft model), --num-drafts deep")
+    ap.add_argument("--nvfp4-activations", action="store_true",
+                    help="NVFP4 checkpoints: quantise activations to NVFP4 too (block-scaled FP4 x FP4 tensor-core GEMM)")
     ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"],
                     help="tensor-parallel collectives: this engine's peer-memory kernels (default) or the NCCL baseline")
     args = ap.parse_args()
@@ -170,13 +178,18 @@ def main():
         if args.gpus > 1:
             print(f"bench.py: --gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})", file=sys.stderr)
             return 2
-    topo, pctx, device = init_distributed(tp_size=world)
+    topo, pctx, device = init_distributed(tp_size=world, ep_size=args.ep if world > 1 else 0)
     rank = topo.rank
+    if args.nvfp4_activations:
+        from atlas_b200 import ops as _ops
+        _ops.NVFP4_ACTIVATIONS = True
     from atlas_b200.ops import cuda as K
     symm = None
     if world > 1 and args.comm == "p2p":
         from atlas_b200.parallel.symm import SymmBackend
         symm = SymmBackend(pctx.comm, device)
+        if pctx.ep_comm is pctx.comm:
+            pctx.ep_comm = symm
         pctx.comm = symm
 
     mcfg = PRESETS[args.model]()
@@ -190,12 +203,13 @@ def main():
         return rc
     max_len = args.isl + args.osl + 16
     mcfg.max_position_embeddings = max(4096, max_len)
-    model = build_model(mcfg, pctx, device=device).init_random(0, max_pos=max_len + 16)
+    model = build_model(mcfg, pctx, device=device, ep_mode=args.ep_mode).init_random(0, max_pos=max_len + 16)
     blocks_per_seq = (max_len + args.block_size - 1) // args.block_size + 1
     ecfg = EngineConfig(max_seq_len=max_len, block_size=args.block_size, max_num_seqs=max(args.concurrency, 1),
                         max_batch_size=max(args.concurrency, 1), max_prefill_tokens=args.max_prefill_tokens,
                         num_kv_blocks=blocks_per_seq * args.concurrency + 64, enable_prefix_caching=args.prefix_cache,
-                        speculative=args.speculative, num_drafts=args.num_drafts if args.speculative else 0,
+                        speculative=args.speculative, ngram_speculative=args.ngram_speculative,
+                        num_drafts=args.num_drafts if (args.speculative or args.ngram_speculative) else 0,
                         ssm_cache_slots=max(16, args.concurrency + 8),
                         use_cuda_graphs=not args.no_graphs, tp_size=world)
     eng = LLMEngine(model, ecfg)
@@ -298,10 +312,11 @@ def main():
             "data": "synthetic: uniform-random token ids, random-init N(0,0.02) weights" + quant_desc,
             "config": {"model": args.model + ("" if not args.layers else f"-TRUNCATED-{args.layers}L-INVALID"),
                        "global_batch": args.concurrency, "seq_len": args.isl + args.osl, "isl": args.isl, "osl": args.osl,
-                       "parallelism": f"tp{world}", "collectives": (args.comm if world > 1 else "none"), "l2": "inputs larger than L2 (8 GB weights + KV stream every step)",
+                       "parallelism": f"tp{topo.tp_size}" + (f"+ep{topo.ep_size}" if topo.ep_size > 1 else ""), "collectives": (args.comm if world > 1 else "none"), "l2": "inputs larger than L2 (8 GB weights + KV stream every step)",
                        "step": "one wave of `global_batch` concurrent requests, prefill + decode",
                        "engine_steps_per_wave": eng_steps / max(1, args.steps), "cuda_graphs": not args.no_graphs,
-                       "speculative": bool(args.speculative), "prefix_cache": bool(args.prefix_cache),
+                       "speculative": bool(args.speculative or args.ngram_speculative), "nvfp4_activations": bool(args.nvfp4_activations),
+                       "ep_mode": args.ep_mode if topo.ep_size > 1 else None, "prefix_cache": bool(args.prefix_cache),
                        "spec_accept_rate": (eng.stats.spec_accepted / eng.stats.spec_proposed) if eng.stats.spec_proposed else None,
                        "prefix_hit_tokens": (eng.radix.stats.hit_tokens if eng.radix is not None else 0)},
             "clocks": clocks,
