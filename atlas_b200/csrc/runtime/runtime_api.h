@@ -56,6 +56,27 @@ void atlas_fault_reset_for_tests(void);
 // aligned bounce buffers (falls back to buffered reads where O_DIRECT is refused).  Returns bytes read or -errno.
 long long atlas_read_file(const char* path, long long offset, long long len, void* dst, int threads, long long chunk);
 
+// ---- grammar-constrained decoding (grammar.cpp) ------------------------------------------------------------------------
+typedef struct atlas_grammar atlas_grammar;
+typedef struct atlas_vocab atlas_vocab;
+typedef struct atlas_matcher atlas_matcher;
+// EBNF text -> grammar (NULL on a syntax error, message copied to err).  `root` names the start rule ("root" if empty).
+atlas_grammar* atlas_grammar_compile(const char* text, const char* root, char* err, int errcap);
+void atlas_grammar_destroy(atlas_grammar*);
+int atlas_grammar_num_rules(const atlas_grammar*);
+// Token t is bytes[offsets[t] .. offsets[t+1]); tokens without bytes (specials) are never allowed by a grammar.
+atlas_vocab* atlas_vocab_create(const uint8_t* bytes, const int64_t* offsets, int n_tokens);
+void atlas_vocab_destroy(atlas_vocab*);
+int atlas_vocab_num_nodes(const atlas_vocab*);
+atlas_matcher* atlas_matcher_create(const atlas_grammar*, const atlas_vocab*);
+void atlas_matcher_destroy(atlas_matcher*);
+int atlas_matcher_can_end(const atlas_matcher*);
+int atlas_matcher_exhausted(const atlas_matcher*);
+int atlas_matcher_mask(atlas_matcher*, uint32_t* bits, int n_words);
+int atlas_matcher_accept_bytes(atlas_matcher*, const uint8_t* bytes, int n);
+int atlas_matcher_rollback(atlas_matcher*, int n);
+int atlas_matcher_num_stacks(const atlas_matcher*);
+
 #ifdef __cplusplus
 }
 #endif

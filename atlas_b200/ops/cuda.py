@@ -19,6 +19,10 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(os.path.dirname(_HERE), "_C", "libatlas_b200_kernels.so")
 
 launch_count = 0
+# When a list: every kernel-launching call appends (name, CUDA event recorded right after the launch); the time between
+# consecutive events is the device time of that call plus whatever ran on the stream since the previous one
+# (``bench/step_profile.py`` turns it into a per-kernel table).  None = off.
+device_marks = None
 _status_ptr: Dict[int, int] = {}
 _num_sms: Dict[int, int] = {}
 _scratch: Dict[Tuple[int, str], torch.Tensor] = {}
@@ -93,6 +97,10 @@ def _check(rc: int, what: str) -> None:
     launch_count += 1
     if _TRACER.enabled:
         _TRACER.launch(what)
+    if device_marks is not None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        device_marks.append((what, ev))
     if rc != 0:
         raise KernelError(f"{what} failed with code {rc}")
 

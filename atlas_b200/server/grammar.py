@@ -1,8 +1,8 @@
 """Constrained decoding: JSON-object / JSON-schema / tool-call / EBNF grammars compiled to per-step token masks.
 
-Uses the ``xgrammar`` package when it is importable (compiled grammars are cached per schema); otherwise a
-reduced built-in matcher enforces "the output is one JSON value" at the byte level for byte-level tokenizers
-and is a no-op for others.
+Default backend: the engine's own matcher (``server/ebnf.py`` over the native ``csrc/runtime/grammar.cpp``): grammars
+are compiled once per distinct spec, the tokenizer's vocabulary once per engine.  ``ATLAS_GRAMMAR_BACKEND=xgrammar``
+selects the upstream ``xgrammar`` package instead when it is importable.
 
 Reference parity: ``crates/xgrammar`` + ``crates/spark-server/src/grammar/{engine,compile_tools,mask_cache}.rs``;
 ``GrammarSpec::{ToolCall, JsonObject, JsonSchema, Ebnf}`` (``api/inference_types.rs``).
@@ -42,6 +42,10 @@ class GrammarEngine:
         self._xgr = None
         self._compiler = None
         self._cache: Dict[str, Any] = {}
+        self._vocab = None                       # ebnf.Vocabulary, built on first use
+        import os
+        if os.environ.get("ATLAS_GRAMMAR_BACKEND", "native") != "xgrammar":
+            return
         try:
             import xgrammar as xgr
             tk = getattr(tokenizer, "tk", None)
@@ -59,7 +63,7 @@ class GrammarEngine:
 
     @property
     def backend(self) -> str:
-        return "xgrammar" if self._xgr is not None else "builtin"
+        return "xgrammar" if self._xgr is not None else "native"
 
     def matcher(self, spec: GrammarSpec):
         if self._xgr is not None:
@@ -78,9 +82,27 @@ class GrammarEngine:
                     raise ValueError(f"unknown grammar kind {spec.kind}")
                 self._cache[key] = cg
             return _XgrMatcher(self._xgr, cg, self.vocab_size)
-        if isinstance(getattr(self.tokenizer, "encode", None), object) and self.tokenizer.__class__.__name__ == "ByteTokenizer":
-            return _ByteJsonMatcher(self.vocab_size)
-        return None
+        from . import ebnf
+        if self._vocab is None:
+            toks = ebnf.token_bytes(self.tokenizer, self.vocab_size)
+            if not any(toks):
+                return None                      # a tokenizer whose token bytes are unknown cannot be masked
+            self._vocab = ebnf.Vocabulary(toks, list(getattr(self.tokenizer, "eos_token_ids", []) or []))
+        key = json.dumps([spec.kind, spec.schema, spec.ebnf, spec.tools], sort_keys=True, default=str)
+        cg = self._cache.get(key)
+        if cg is None:
+            if spec.kind == "json_object":
+                text = ebnf.JSON_OBJECT_GRAMMAR
+            elif spec.kind == "json_schema":
+                text = ebnf.schema_to_ebnf(spec.schema or {})
+            elif spec.kind == "tool_call":
+                text = ebnf.schema_to_ebnf(tools_to_schema(spec.tools or []))
+            elif spec.kind == "ebnf":
+                text = spec.ebnf or ""
+            else:
+                raise ValueError(f"unknown grammar kind {spec.kind}")
+            cg = self._cache[key] = ebnf.CompiledGrammar(text)
+        return ebnf.EbnfMatcher(cg, self._vocab)
 
 
 class _XgrMatcher:
