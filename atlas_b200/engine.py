@@ -82,6 +82,13 @@ class LLMEngine:
         self.runner = ModelRunner(model, self.cache, self.cfg)
         self.spec = SpecController(self, self.cfg) if (self.cfg.speculative and model.mtp is not None
                                                          and self.cfg.num_drafts > 0) else None
+        if self.spec is None and self.cfg.speculative and getattr(model, "dflash", None) is not None and self.cfg.num_drafts > 0:
+            from .sched.spec import DFlashSpecController
+            model.dflash.alloc_cache(num_blocks, self.cfg.block_size)
+            model.dflash.finalize(self.cfg.max_seq_len + self.cfg.num_drafts + 8)
+            model.capture_layers = tuple(model.dflash.dcfg.target_layer_ids)
+            model.graph_safe = False            # the captured states must be this step's tensors, not a graph's
+            self.spec = DFlashSpecController(self, self.cfg)
         if self.spec is None and self.cfg.ngram_speculative and self.cfg.num_drafts > 0:
             from .sched.spec import NgramSpecController
             self.spec = NgramSpecController(self, self.cfg)     # draft-model-free: works for every architecture

@@ -219,6 +219,10 @@ class DecoderLM:
         tp = self.pctx.tp_size
         self.vocab_parallel = tp > 1 and cfg.vocab_size % tp == 0
         self.sp_capacity_hint = 0            # the engine sets this to its largest step so the area is allocated once
+        # layers whose output (the residual stream after the layer) is kept per step for a conditioned draft model
+        self.capture_layers: Tuple[int, ...] = ()
+        self.aux_hidden: List[torch.Tensor] = []
+        self.dflash = None                   # models.dflash.BlockDiffusionDrafter
 
     # ------------------------------------------------------------------ weights
     def init_random(self, seed: int = 0, std: float = 0.02, max_pos: Optional[int] = None) -> "DecoderLM":
@@ -347,17 +351,21 @@ class DecoderLM:
     def forward(self, batch: ForwardBatch, cache: CacheStore) -> torch.Tensor:
         """Returns the final-normed hidden states ``[T,H]`` of every row."""
         x = batch.inputs_embeds if batch.inputs_embeds is not None else self.embed_tokens(batch.input_ids)
-        sp = self._seq_parallel_area(batch, x.shape[0])
+        sp = self._seq_parallel_area(batch, x.shape[0]) if not self.capture_layers else None
         if sp is not None:
             return self._forward_seq_parallel(x, batch, cache, sp)
         residual = None
         if batch.inputs_embeds is not None:
             x = x.clone()                     # fused epilogues update the residual stream in place
         n = len(self.layers)
+        self.aux_hidden = []
         for i, layer in enumerate(self.layers):
             nxt = self.layers[i + 1] if i + 1 < n else None
             next_norm = nxt.input_norm if (nxt is not None and nxt.accepts_prenormed()) else None
             x, residual = layer.forward(x, residual, batch, cache, self.rope_cache, next_norm=next_norm)
+            if i in self.capture_layers:
+                # the stream after layer i: already summed when the layer's epilogue handed over normalised activations
+                self.aux_hidden.append(residual.clone() if isinstance(x, Act) else (x + residual if residual is not None else x.clone()))
         self.last_prenorm = (x, residual)
         y, _ = ops.rmsnorm(x, self.final_norm, self.cfg.rms_norm_eps, residual, self.cfg.norm_plus_one)
         return y

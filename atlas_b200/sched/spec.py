@@ -217,3 +217,63 @@ class NgramSpecController:
             seq.drafts = drafts
             any_draft |= bool(drafts)
         self.proposed_steps += 1 if any_draft else 0
+
+
+class DFlashSpecController:
+    """Drafts from the block-diffusion draft model (``models/dflash.py``): after every target step the states of the
+    captured target layers at the kept rows become context keys / values of the drafter, then ONE drafter forward per
+    step proposes ``num_drafts`` tokens for every decoding sequence.  Verification, acceptance and the throughput gate
+    are shared with the other proposers.  Reference parity: ``crates/spark-model/src/layers/dflash_head/propose.rs``,
+    ``crates/spark-server/src/scheduler/spec_step.rs``."""
+
+    def __init__(self, engine, cfg: EngineConfig):
+        self.engine, self.cfg = engine, cfg
+        self.k = max(1, cfg.num_drafts)
+        self.gate = MtpGate(enabled=cfg.mtp_gate)
+        self.drafter = engine.model.dflash
+        self.proposed_steps = 0
+
+    def active(self) -> bool:
+        return True
+
+    @torch.inference_mode()
+    def after_step(self, out: SchedulerOutput, batch: ForwardBatch, hidden, sampled, kept_rows) -> None:
+        eng, model, d = self.engine, self.engine.model, self.drafter
+        bs = eng.cfg.block_size
+        aux = model.aux_hidden
+        if len(aux) != len(d.dcfg.target_layer_ids):
+            return
+        rows, pos, slots = [], [], []
+        want = []
+        r0 = 0
+        for idx, it in enumerate(out.items):
+            seq, m, n_in = it.seq, kept_rows[idx], it.num_tokens
+            if not seq.finished and m > 0:
+                for j in range(m):
+                    p = it.start + j
+                    rows.append(r0 + j)
+                    pos.append(p)
+                    slots.append(seq.blocks[p // bs] * bs + p % bs)
+                if (it.sample and seq.status == SeqStatus.RUNNING and not seq.disable_spec
+                        and seq.num_tokens == it.start + m + 1):
+                    want.append((seq, it.start + m))
+            r0 += n_in
+        if rows:
+            ridx = torch.tensor(rows, dtype=torch.long, device=model.device)
+            feats = d.context_features([a[ridx] for a in aux])
+            d.add_context(feats, torch.tensor(pos, dtype=torch.int32, device=model.device),
+                          torch.tensor(slots, dtype=torch.int32, device=model.device))
+        if not want or not self.gate.use_spec():
+            return
+        ready = []
+        for seq, ctx in want:
+            room = seq.sampling.max_tokens - seq.num_output_tokens - 1
+            k = max(0, min(self.k, room))
+            if k > 0 and eng.scheduler._ensure_blocks(seq, ctx + self.k + 1):
+                ready.append((seq, ctx, k))
+        if not ready:
+            return
+        drafts = d.propose([s.token_at(c) for s, c, _ in ready], [c for _, c, _ in ready], [s.blocks for s, _, _ in ready], self.k)
+        for (seq, _, k), dr in zip(ready, drafts):
+            seq.drafts = dr[:k]
+        self.proposed_steps += 1

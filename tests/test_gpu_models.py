@@ -279,6 +279,33 @@ def test_engine_on_gpu_with_graphs_and_prefix_cache(K):
     assert [o.output_tokens for o in again] == [o.output_tokens for o in a[:2]]
 
 
+def test_engine_with_block_diffusion_drafter_on_gpu(K):
+    """FP8 target + 16-bit drafter cache on the GPU kernels: the drafter's one-pass block forward runs through the bf16
+    decode-attention path, drafts are verified by the target, and greedy output stays that of plain decoding (up to the
+    near-tie flips the verify-vs-decode kernel choice can cause with random weights)."""
+    from atlas_b200.models.dflash import BlockDiffusionDrafter, DFlashConfig
+    cfg = ModelConfig(model_type="llama", family="dense", vocab_size=4096, hidden_size=1024, intermediate_size=2048,
+                      num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=2, head_dim=128, rope_theta=5e5,
+                      max_position_embeddings=2048, quant=QuantConfig(method="fp8_block", kv_cache_dtype="fp8"))
+    model = build_model(cfg, device=DEV).init_random(0)
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, 4096, (30 + 11 * i,), generator=g).tolist() for i in range(4)]
+    sp = SamplingParams(max_tokens=12, ignore_eos=True)
+    ecfg = dict(num_kv_blocks=128, max_num_seqs=8, max_seq_len=512, max_prefill_tokens=128, enable_prefix_caching=False)
+    base = LLMEngine(model, EngineConfig(use_cuda_graphs=False, **ecfg)).generate(prompts, sp)
+    dcfg = DFlashConfig(hidden_size=1024, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=8,
+                        num_key_value_heads=2, head_dim=128, block_len=5, target_layer_ids=[0, 2])
+    model.dflash = BlockDiffusionDrafter(dcfg, model).init_random(1)
+    eng = LLMEngine(model, EngineConfig(speculative=True, num_drafts=4, mtp_gate=False, **ecfg))
+    out = eng.generate(prompts, sp)
+    torch.cuda.synchronize()
+    assert K.check_status() == 0
+    assert eng.stats.spec_proposed > 0 and all(len(o.output_tokens) == 12 for o in out)
+    same = sum(x.output_tokens == y.output_tokens for x, y in zip(out, base))
+    assert same >= 3, same
+    model.dflash, model.capture_layers = None, ()
+
+
 def test_host_tier_swap_on_gpu(K):
     """FP8 KV blocks parked in pinned host memory and restored: same tokens as the uncontended run."""
     cfg = ModelConfig(model_type="llama", family="dense", vocab_size=4096, hidden_size=1024, intermediate_size=2048,
