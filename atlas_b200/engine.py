@@ -96,6 +96,7 @@ class LLMEngine:
         self.control = None               # parallel.worker.StepControl when several processes serve one model
         self._eos_set = frozenset(self.mcfg.eos_ids())
         self.time_device = False          # accumulate CUDA-event time of each step's GPU work
+        self._pipe = None                 # pipeline.DecodePipeline (lag-one decode loop), created on first use
         self.device_phase_ms: Dict[str, list] = {}     # phase -> [ms, steps] (steps with any multi-token item count as prefill)
         self.device_time_ms = 0.0
         self._seqs: Dict[str, Sequence] = {}
@@ -189,6 +190,13 @@ class LLMEngine:
         t0 = time.monotonic()
         sched = self.scheduler
         ctl = self.control
+        if ctl is None and self.spec is None and self.cfg.async_decode and self.model.device.type == "cuda":
+            if self._pipe is None:
+                from .pipeline import DecodePipeline
+                self._pipe = DecodePipeline(self)
+            piped = self._pipe.step()
+            if piped is not None:
+                return piped
         follower = ctl is not None and not ctl.is_leader
         now_plan = ctl.begin_step(self) if ctl is not None else None
         with phase("schedule"):

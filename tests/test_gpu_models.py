@@ -279,6 +279,50 @@ def test_engine_on_gpu_with_graphs_and_prefix_cache(K):
     assert [o.output_tokens for o in again] == [o.output_tokens for o in a[:2]]
 
 
+def test_lag_one_decode_pipeline_matches_synchronous_loop(K):
+    """The pipelined decode loop (next step launched before the previous step's tokens are read) must produce exactly
+    the tokens of the synchronous loop: same kernels, same graphs, same order.  Covers sequences that stop at different
+    lengths (the pipeline drains and restarts), an EOS-style stop token found one step late, and a request that arrives
+    while the pipeline is running."""
+    cfg = ModelConfig(model_type="llama", family="dense", vocab_size=4096, hidden_size=1024, intermediate_size=2048,
+                      num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2, head_dim=128, rope_theta=5e5,
+                      max_position_embeddings=2048, quant=QuantConfig(method="fp8_block", kv_cache_dtype="fp8"))
+    model = build_model(cfg, device=DEV).init_random(0)
+    g = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, 4096, (20 + 9 * i,), generator=g).tolist() for i in range(5)]
+    lens = [24, 9, 17, 24, 13]
+    base_cfg = dict(num_kv_blocks=256, max_num_seqs=8, max_seq_len=512, max_prefill_tokens=256, enable_prefix_caching=False)
+
+    def run(async_decode, stop_ids=None, late=False):
+        eng = LLMEngine(model, EngineConfig(async_decode=async_decode, **base_cfg))
+        rids = [eng.add_request(p, SamplingParams(max_tokens=n, ignore_eos=True, stop_token_ids=list(stop_ids or [])))
+                for p, n in zip(prompts[:4], lens[:4])]
+        outs, steps = {}, 0
+        while eng.has_unfinished():
+            for o in eng.step():
+                if o.finished:
+                    outs[o.request_id] = o.output_tokens
+            steps += 1
+            if late and steps == 12:
+                rids.append(eng.add_request(prompts[4], SamplingParams(max_tokens=lens[4], ignore_eos=True)))
+        torch.cuda.synchronize()
+        return [outs[r] for r in rids], eng
+
+    sync, _ = run(False)
+    piped, eng = run(True)
+    assert K.check_status() == 0
+    assert eng._pipe is not None and eng._pipe.steps > 10           # the pipeline really ran
+    assert piped == sync
+    # a stop token taken from the middle of a sequence: found when its step retires, one launch late
+    stop_tok = sync[0][10]
+    s2, _ = run(False, [stop_tok])
+    p2, _ = run(True, [stop_tok])
+    assert p2 == s2 and len(s2[0]) <= 11
+    s3, _ = run(False, late=True)
+    p3, _ = run(True, late=True)
+    assert p3 == s3 and len(p3) == 5
+
+
 def test_engine_with_block_diffusion_drafter_on_gpu(K):
     """FP8 target + 16-bit drafter cache on the GPU kernels: the drafter's one-pass block forward runs through the bf16
     decode-attention path, drafts are verified by the target, and greedy output stays that of plain decoding (up to the
