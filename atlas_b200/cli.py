@@ -53,6 +53,8 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--ssm-cache-slots", type=int, default=16)
     s.add_argument("--ssm-checkpoint-interval", type=int, default=256)
     s.add_argument("--swap-space-gb", type=float, default=0.0)
+    s.add_argument("--no-memory-watchdog", action="store_true",
+                   help="do not poll free device / host memory (soft floor pauses admission, hard floor trips the fault latch)")
     s.add_argument("--high-speed-swap-gb", type=float, default=0.0, help="file-backed KV tier below the host tier")
     s.add_argument("--high-speed-swap-path", default="", help="directory of the swap file (an NVMe mount)")
     s.add_argument("--quantization", default="auto", choices=["auto", "none", "fp8_block", "nvfp4"],
@@ -232,6 +234,9 @@ def cmd_serve(argv: List[str]) -> int:
     ecfg = _engine_config(args, model.cfg)
     engine = LLMEngine(model, ecfg)
     log(f"engine ready: {engine.pool.num_blocks} KV blocks of {ecfg.block_size} tokens")
+    if device.type == "cuda" and not args.no_memory_watchdog:
+        from .utils.watchdog import attach
+        attach(engine).start()
 
     if control is not None and not control.is_leader:
         from .parallel.worker import worker_loop

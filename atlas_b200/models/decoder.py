@@ -300,6 +300,9 @@ class DecoderLM:
 
     # ------------------------------------------------------------------ forward
     def embed_tokens(self, ids: torch.Tensor) -> torch.Tensor:
+        from ..ops import checked
+        if checked.ENABLED:
+            checked.index_range("input_ids", ids, 0, self.cfg.vocab_size)
         return self.embed[ids.long()]
 
     # ------------------------------------------------------------------ sequence-parallel prefill (tensor parallel)

@@ -13,6 +13,7 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from ..utils.trace import TRACER as _TRACER
+from . import checked
 
 _LIB = None
 _HERE = os.path.dirname(os.path.abspath(__file__))
@@ -133,7 +134,8 @@ def scratch(name: str, nbytes: int, device, zero_new=None) -> torch.Tensor:
         if buf is not None and _scratch_frozen:
             raise KernelError(f"scratch '{name}' holds {buf.numel()} bytes, {nbytes} requested after a CUDA graph was "
                               "captured: reserve the worst case before capturing")
-        alloc = _scratch_alloc or (lambda n, dev: torch.zeros(n, dtype=torch.uint8, device=dev))
+        from ..utils import guards
+        alloc = _scratch_alloc or (lambda n, dev: guards.zeros(f"scratch.{name}", (n,), torch.uint8, dev))
         buf = alloc(max(nbytes, 1 << 20), device)
         _scratch[key] = buf
     return buf
@@ -413,8 +415,9 @@ def gemm_nvfp4(x, packed, bscale, gscale, out=None):
 def alloc_kv_cache(num_blocks: int, block_size: int, hkv: int, d: int, dtype, device):
     """Physical layout K ``[nb, Hkv, bs, D]``, V ``[nb, Hkv, D, bs]``; both returned as logical
     ``[nb, bs, Hkv, D]`` views so indexing code is layout-agnostic."""
-    k = torch.zeros(num_blocks, hkv, block_size, d, dtype=dtype, device=device).permute(0, 2, 1, 3)
-    v = torch.zeros(num_blocks, hkv, d, block_size, dtype=dtype, device=device).permute(0, 3, 1, 2)
+    from ..utils import guards
+    k = guards.zeros("kv.k", (num_blocks, hkv, block_size, d), dtype, device).permute(0, 2, 1, 3)
+    v = guards.zeros("kv.v", (num_blocks, hkv, d, block_size), dtype, device).permute(0, 3, 1, 2)
     return k, v
 
 
@@ -435,6 +438,8 @@ def qk_norm_rope_kv_write(q, k, v, positions, rope_cache, rotary_dim, k_cache, v
     assert q.stride(2) == 1 and q.stride(1) == D and k.stride(1) == D and v.stride(1) == D
     assert positions.dtype == torch.int32 and slot_mapping.dtype == torch.int32 and rope_cache.dtype == torch.float32
     bs = k_cache.shape[1]
+    if checked.ENABLED:
+        checked.kv_write(slot_mapping, positions, k_cache.shape[0], bs, rope_cache.shape[0] if rotary_dim else 0)
     _check(lib().atlas_rope_kv_write(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
                                      positions.data_ptr(), rope_cache.data_ptr(), _ptr(q_norm_w), _ptr(k_norm_w),
                                      k_cache.data_ptr(), v_cache.data_ptr(), slot_mapping.data_ptr(), T, Hq, Hkv, D,
@@ -466,6 +471,8 @@ def paged_attention(q, k_cache, v_cache, batch, scale, k_scale, v_scale, sliding
     window = int(sliding_window or 0)
     nd = batch.num_decodes
     st = _stream()
+    if checked.ENABLED:
+        checked.paged_read(batch.block_tables, batch.seq_lens, k_cache.shape[0], k_cache.shape[1])
     if k_cache.dtype == torch.bfloat16:
         return _paged_attention_kv16(q, out, k_cache, v_cache, batch, scale, window, d)
     if nd > 0:

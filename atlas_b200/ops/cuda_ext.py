@@ -261,6 +261,9 @@ def _finish(lib, y, slot_of, topk_w, T, k, H, addend, fused_comm, grouped, dev, 
 
 
 def _moe_local(x, topk_w, topk_ids, experts, e_lo, addend: Optional[torch.Tensor] = None, fused_comm=None, grouped=False):
+    if K.checked.ENABLED:
+        K.checked.index_range("topk_ids", topk_ids, 0, 1 << 20)
+        K.checked.finite("topk_w", topk_w)
     """Local experts only: align -> gather (+quant) -> grouped GEMM -> SiLU*mul -> grouped GEMM -> weighted combine."""
     T, H = x.shape
     k = topk_ids.shape[1]

@@ -48,6 +48,8 @@ class Scheduler:
         self._last_decode_time: Optional[float] = None
 
     # ------------------------------------------------------------------ queue ops
+        self.admission_paused = False       # set by the memory watchdog while free memory is under its soft floor
+
     def add(self, seq: Sequence) -> None:
         seq.status = SeqStatus.WAITING
         self.waiting.append(seq)
@@ -302,8 +304,8 @@ class Scheduler:
             prefill_items.append(item)
             budget -= item.num_tokens
 
-        # 3. admit new requests
-        if self.waiting:
+        # 3. admit new requests (not while the memory watchdog holds admission: running work drains first)
+        if self.waiting and not self.admission_paused:
             order = self.policy.order(list(self.waiting))
             for seq in order:
                 if budget <= 0 or self.num_unfinished - len(self.waiting) >= cfg.max_num_seqs:

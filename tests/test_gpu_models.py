@@ -371,3 +371,37 @@ def test_host_tier_swap_on_gpu(K):
     assert K.check_status() == 0
     assert e.scheduler.num_swaps > 0 and e.host_tier.blocks_in == e.host_tier.blocks_out > 0
     assert sum(a == b for a, b in zip(got, want)) >= 3, (got, want)      # batch composition differs between the runs
+
+
+def test_checked_mode_passes_clean_steps_and_names_a_bad_index(K, monkeypatch):
+    """Checked bindings: a normal prefill + decode goes through untouched; a slot outside the pool, a block table that
+    points past the pool and a duplicated slot each raise before the kernel is launched."""
+    from atlas_b200.ops import checked
+    monkeypatch.setattr(checked, "ENABLED", True)
+    cfg = ModelConfig(model_type="llama", family="dense", vocab_size=2048, hidden_size=512, intermediate_size=1024,
+                      num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2, head_dim=128, rope_theta=5e5,
+                      max_position_embeddings=1024, quant=QuantConfig(method="fp8_block"))
+    model = build_model(cfg, device=DEV).init_random(0)
+    cache = model.alloc_cache(8, 16, torch.float8_e4m3fn)
+    toks = list(range(1, 41))
+    fb = ForwardBatch.build([toks], [0], [[3, 1, 4]], 16, device=DEV)
+    model.compute_logits(model.forward(fb, cache))
+    fb = ForwardBatch.build([[7]], [40], [[3, 1, 4]], 16, device=DEV)
+    model.compute_logits(model.forward(fb, cache))
+    assert K.check_status() == 0
+    bad = ForwardBatch.build([[7]], [41], [[3, 1, 4]], 16, device=DEV)
+    bad.slot_mapping = torch.tensor([8 * 16 + 2], dtype=torch.int32, device=DEV)
+    with pytest.raises(checked.BoundsViolation, match="slot_mapping"):
+        model.forward(bad, cache)
+    bad = ForwardBatch.build([[7]], [41], [[3, 1, 9]], 16, device=DEV)
+    bad.slot_mapping = torch.tensor([4 * 16 + 9], dtype=torch.int32, device=DEV)
+    with pytest.raises(checked.BoundsViolation, match="block_tables"):
+        model.forward(bad, cache)
+    bad = ForwardBatch.build([[7, 8]], [41], [[3, 1, 4]], 16, device=DEV)
+    bad.slot_mapping = torch.tensor([4 * 16 + 9, 4 * 16 + 9], dtype=torch.int32, device=DEV)
+    with pytest.raises(checked.BoundsViolation, match="same cache slot"):
+        model.forward(bad, cache)
+    with pytest.raises(checked.BoundsViolation, match="input_ids"):
+        model.embed_tokens(torch.tensor([5000], device=DEV))
+    torch.cuda.synchronize()
+    assert K.check_status() == 0

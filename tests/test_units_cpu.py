@@ -603,3 +603,61 @@ def test_router_variants_reference():
     assert (i == tab[tok.long()]).all() and torch.allclose(w.sum(-1), torch.full((7,), 1.5))
     sp = torch.sqrt(torch.nn.functional.softplus(lg)).gather(1, i.long())
     assert torch.allclose(w, sp / sp.sum(-1, keepdim=True) * 1.5, atol=1e-6)
+
+
+def test_memory_watchdog_levels_and_engine_hooks():
+    """Soft floor pauses admission (with hysteresis), hard floor trips the latch once; driven by fake samples."""
+    from atlas_b200.utils.watchdog import Level, MemorySample, MemoryWatchdog, WatchdogConfig, decide, preflight
+    cfg = WatchdogConfig(soft_device_free=1000, hard_device_free=100, soft_host_available=0, hard_host_available=0,
+                         recover_factor=2.0)
+    mk = lambda free: MemorySample(free, 10000, 0)
+    assert decide(mk(5000), cfg) == Level.OK and decide(mk(999), cfg) == Level.SOFT and decide(mk(99), cfg) == Level.HARD
+    assert decide(mk(1500), cfg, Level.SOFT) == Level.SOFT and decide(mk(2001), cfg, Level.SOFT) == Level.OK
+    feed = iter([5000, 900, 1500, 2500, 50, 50])
+    events = []
+    wd = MemoryWatchdog(cfg, lambda: mk(next(feed)), on_soft=lambda on: events.append(("soft", on)),
+                        on_hard=lambda why: events.append(("hard", why)))
+    levels = [wd.poll() for _ in range(6)]
+    assert levels == [Level.OK, Level.SOFT, Level.SOFT, Level.OK, Level.HARD, Level.HARD]
+    assert events[0] == ("soft", True) and events[1] == ("soft", False) and events[2][0] == "hard" and len(events) == 3
+    assert "out of memory" in events[2][1]
+    assert preflight(8 << 30, 4 << 30, 16 << 30) is None and "needs" in preflight(8 << 30, 8 << 30, 16 << 30)
+    # paused admission: a waiting request is not admitted, running work continues
+    import torch
+    from atlas_b200.config import EngineConfig, tiny_dense
+    from atlas_b200.engine import LLMEngine
+    from atlas_b200.models import build_model
+    from atlas_b200.sampling import SamplingParams
+    eng = LLMEngine(build_model(tiny_dense("float32"), device="cpu").init_random(0), EngineConfig(num_kv_blocks=32, max_seq_len=64))
+    eng.scheduler.admission_paused = True
+    eng.add_request([1, 2, 3], SamplingParams(max_tokens=2, ignore_eos=True))
+    assert eng.step() == [] and len(eng.scheduler.waiting) == 1
+    eng.scheduler.admission_paused = False
+    while eng.has_unfinished():
+        eng.step()
+    assert not eng.scheduler.waiting
+
+
+def test_red_zone_guards_and_block_poison():
+    import torch
+    from atlas_b200.utils.guards import CANARY, GuardedAllocator, poison_block, zero_block
+    ga = GuardedAllocator(zone_bytes=64)
+    a = ga.alloc("a", (3, 5), torch.float32, "cpu")
+    b = ga.alloc("b", (7,), torch.bfloat16, "cpu")
+    assert a.shape == (3, 5) and float(a.abs().sum()) == 0 and ga.scan() == []
+    a.fill_(1.0)
+    b.fill_(2.0)
+    assert ga.scan() == []                                # writes inside the payload leave the bands alone
+    raw = ga.entries[0].raw
+    raw[64 + 60 + 3] = 7                                   # one byte past the end of `a` (60 payload bytes)
+    bad = ga.scan()
+    assert len(bad) == 1 and bad[0].name == "a" and bad[0].side == "above" and bad[0].offset == 3 and bad[0].value == 7
+    ga.repair()
+    assert ga.scan() == [] and int(raw[0]) == CANARY
+    assert [e["name"] for e in ga.ledger()] == ["a", "b"] and ga.ledger()[0]["bytes"] == 60
+    k = torch.zeros(4, 16, 2, 8, dtype=torch.float8_e4m3fn)
+    v = torch.zeros(4, 16, 2, 8, dtype=torch.bfloat16)
+    poison_block((k, v), 2)
+    assert float(k[2].float().min()) == 448.0 and float(v[2].float().min()) > 1e30 and float(k[1].float().abs().sum()) == 0
+    zero_block((k, v), 2)
+    assert float(k.float().abs().sum()) == 0 and float(v.float().abs().sum()) == 0
