@@ -141,6 +141,10 @@ class ModelConfig:
     v_head_dim: int = 0
     rope_interleaved: bool = True     # checkpoint stores rotary columns as (even, odd) pairs
     first_k_dense_replace: int = 0    # leading layers with a dense FFN in an otherwise MoE model
+    # multimodal: interleaved MRoPE sections (time, row, column), the image placeholder id and the vision tower's config
+    mrope_section: List[int] = field(default_factory=list)
+    image_token_id: int = -1
+    vision: Any = None                # models.vision.VisionConfig
     # MTP speculative head
     mtp_num_layers: int = 0
     # numerics
@@ -221,6 +225,7 @@ class ModelConfig:
     # ------------------------------------------------------------------ parsing
     @staticmethod
     def from_hf(cfg: Dict[str, Any]) -> "ModelConfig":
+        outer = cfg
         if "text_config" in cfg and isinstance(cfg["text_config"], dict):
             merged = dict(cfg["text_config"])
             for k in ("quantization_config", "torch_dtype"):
@@ -317,6 +322,13 @@ class ModelConfig:
             c.num_experts = c.num_experts_per_tok = 0
             if "moe" in c.block_types:
                 raise ValueError("nemotron_h checkpoints with MoE blocks are not supported")
+        c.mrope_section = list(rope_params.get("mrope_section") or (cfg.get("rope_scaling") or {}).get("mrope_section") or [])
+        if isinstance(outer.get("vision_config"), dict) and outer.get("image_token_id") is not None and fam == "hybrid":
+            from .models.vision import VisionConfig
+            c.vision = VisionConfig.from_hf(outer["vision_config"])
+            c.image_token_id = int(outer["image_token_id"])
+            if not c.mrope_section:
+                c.mrope_section = [11, 11, 10]
         c.validate()
         return c
 

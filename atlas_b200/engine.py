@@ -142,9 +142,11 @@ class LLMEngine:
                     timeout_s: Optional[float] = None, grammar: Any = None,
                     logits_processors: Optional[List[Callable]] = None, disable_spec: bool = False,
                     stop_checker: Optional[Callable[[Sequence], bool]] = None, adapter_slot: int = 0,
-                    needs_full_logits: bool = False) -> str:
+                    needs_full_logits: bool = False, images: Optional[List[tuple]] = None) -> str:
         """``needs_full_logits``: set on follower ranks for a request whose leader-side sampling needs the whole
-        logits row (grammar mask, logit processors), so that every rank takes the same path to the logits."""
+        logits row (grammar mask, logit processors), so that every rank takes the same path to the logits.
+        ``images``: ``(patches, (t, h, w))`` pairs (see ``models.vision.patchify``) for a prompt that already carries one
+        run of image placeholder tokens per image, ``h * w / merge^2`` tokens long."""
         sampling = sampling or SamplingParams()
         sampling.validate()
         rid = request_id or f"req-{next(self._ids)}"
@@ -166,6 +168,15 @@ class LLMEngine:
                        logits_processors=list(logits_processors or []), disable_spec=disable_spec,
                        adapter_slot=adapter_slot)
         seq.needs_full_logits = bool(needs_full_logits or grammar is not None or logits_processors)
+        if images:
+            if self.model.vision is None:
+                raise RequestRejected("this model has no vision tower")
+            from .models.vision import prepare
+            try:
+                seq.mm = prepare(self.model.vision, prompt, self.mcfg.image_token_id, images)
+            except ValueError as exc:
+                raise RequestRejected(str(exc))
+            seq.namespace = ("mm", rid)           # placeholder ids say nothing about the pixels: no prefix sharing
         self._seqs[rid] = seq
         if stop_checker is not None:
             self._stop_checkers[rid] = stop_checker

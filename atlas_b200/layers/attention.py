@@ -103,7 +103,8 @@ class Attention:
         q = qkv[:, :nq].view(T, self.hq, self.d)
         k = qkv[:, nq:nq + nkv].view(T, self.hkv, self.d)
         v = qkv[:, nq + nkv:nq + 2 * nkv].view(T, self.hkv, self.d)
-        q = ops.qk_norm_rope_kv_write(q, k, v, batch.positions, rope_cache, cfg.rotary_dim, k_cache, v_cache,
+        rope_pos, rope_cache = batch.rope_inputs(rope_cache, cfg.mrope_section)
+        q = ops.qk_norm_rope_kv_write(q, k, v, rope_pos, rope_cache, cfg.rotary_dim, k_cache, v_cache,
                                       batch.slot_mapping, k_scale, v_scale, self.q_norm, self.k_norm,
                                       cfg.rms_norm_eps, cfg.norm_plus_one)
         out = ops.paged_attention(q, k_cache, v_cache, batch, self.scale, k_scale, v_scale, cfg.sliding_window)

@@ -272,10 +272,17 @@ def load_weights(model: DecoderLM, ck: Checkpoint) -> None:
         # a pre-quantised checkpoint: what it left in high precision (its ignore list) stays in high precision
         dense_kind = expert_kind = "dense"
     root = "model" if any(k.startswith("model.layers.") for k in ck.keys()) else "model.language_model"
+    if not ck.has(f"{root}.embed_tokens.weight"):
+        # multimodal wrappers nest the text model under further prefixes: take whatever precedes the embedding table
+        root = next(k[:-len(".embed_tokens.weight")] for k in ck.keys() if k.endswith(".embed_tokens.weight") and "mtp" not in k)
     model.embed = ck.get(f"{root}.embed_tokens.weight").to(device=model.device, dtype=model.dtype)
     for i, layer in enumerate(model.layers):
         _load_layer(ck, f"{root}.layers.{i}", layer, model, dense_kind, expert_kind)
     model.final_norm = _vec(ck, f"{root}.norm.weight", model)
+    vis = next((k[:-len("patch_embed.proj.weight")] for k in ck.keys() if k.endswith("visual.patch_embed.proj.weight")), None)
+    if cfg.vision is not None and vis is not None:
+        from ..models.vision import VisionTower
+        model.vision = VisionTower(cfg.vision, model.device, model.dtype).load(ck.get, vis)
     head = ck.maybe("lm_head.weight")
     if head is None or cfg.tie_word_embeddings:
         head = model.embed

@@ -40,8 +40,22 @@ class ForwardBatch:
     snapshot_plan: Dict[int, List[Tuple[int, int]]] = field(default_factory=dict)
     # optional precomputed input embeddings (MTP head / multimodal rows)
     inputs_embeds: Optional[torch.Tensor] = None
+    # multimodal: three rotary position streams (time, row, column) per row; None for text-only steps
+    positions3: Optional[torch.Tensor] = None       # [3, T] int64
     # LoRA: adapter slot of every row (0 = base model); None when no row of the step uses an adapter
     adapter_rows: Optional[torch.Tensor] = None
+
+    def rope_inputs(self, rope_cache: torch.Tensor, mrope_section):
+        """(positions, rotary table) for the fused rope kernels: the model's table indexed by position for text-only
+        steps, a step-local table with one row per token (``positions = arange``) when three position streams are set."""
+        if self.positions3 is None:
+            return self.positions, rope_cache
+        hit = getattr(self, "_mrope", None)
+        if hit is None or hit[0] is not rope_cache:
+            from .vision import mrope_table
+            table = mrope_table(rope_cache, self.positions3, mrope_section or [11, 11, 10])
+            hit = self._mrope = (rope_cache, torch.arange(table.shape[0], dtype=torch.int32, device=table.device), table)
+        return hit[1], hit[2]
 
     @property
     def num_tokens(self) -> int:

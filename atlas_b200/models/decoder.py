@@ -223,6 +223,7 @@ class DecoderLM:
         self.capture_layers: Tuple[int, ...] = ()
         self.aux_hidden: List[torch.Tensor] = []
         self.dflash = None                   # models.dflash.BlockDiffusionDrafter
+        self.vision = None                   # models.vision.VisionTower (multimodal checkpoints)
 
     # ------------------------------------------------------------------ weights
     def init_random(self, seed: int = 0, std: float = 0.02, max_pos: Optional[int] = None) -> "DecoderLM":

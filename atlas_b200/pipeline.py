@@ -50,7 +50,7 @@ class DecodePipeline:
     def _simple(self, seq) -> bool:
         return (seq.status == SeqStatus.RUNNING and not seq.finished and seq.num_tokens == seq.num_computed + 1
                 and not seq.drafts and not seq.adapter_slot and seq.grammar is None and not seq.logits_processors
-                and not getattr(seq, "needs_full_logits", False))
+                and not getattr(seq, "needs_full_logits", False) and getattr(seq, "mm", None) is None)
 
     def _quiet(self) -> bool:
         s = self.eng.scheduler

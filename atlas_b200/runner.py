@@ -114,7 +114,8 @@ class ModelRunner:
         state_slots = [it.seq.state_slot if it.seq.state_slot is not None else 0 for it in items]
         has_state = [it.seq.has_state for it in items]
         spec_verify = False
-        if all(it.num_tokens == 1 and not it.verify_drafts for it in items):
+        any_mm = any(getattr(it.seq, "mm", None) is not None for it in items)
+        if not any_mm and all(it.num_tokens == 1 and not it.verify_drafts for it in items):
             # every row is one token of one sequence (decode, or a one-token chunk): vectorised
             starts = np.fromiter((it.start for it in items), dtype=np.int64, count=B)
             ids = np.fromiter((it.seq.token_at(it.start) for it in items), dtype=np.int64, count=B)
@@ -166,6 +167,8 @@ class ModelRunner:
             num_decodes=num_dec, max_query_len=max(qlens), max_seq_len=max(sl),
             seq_lens_host=sl, query_lens_host=qlens, spec_verify=spec_verify,
         )
+        if any_mm:
+            self._add_multimodal(fb, items, ids, qlens)
         if any(it.seq.adapter_slot for it in items):
             fb.adapter_rows = self._stage("adapter_rows", np.repeat(np.asarray([it.seq.adapter_slot for it in items], dtype=np.int64),
                                                                     np.asarray(qlens)), torch.int64)
@@ -176,10 +179,44 @@ class ModelRunner:
             fb.snapshot_plan.setdefault(item_idx, []).append((rows, snapshot_base + slot))
         return fb
 
+    def _add_multimodal(self, fb: ForwardBatch, items, ids: np.ndarray, qlens: List[int]) -> None:
+        """Three-stream rotary positions for every row and, where a chunk covers image placeholders, input embeddings
+        with those rows replaced by the vision tower's output."""
+        p3 = []
+        rows, src_seq, src_row = [], [], []
+        r0 = 0
+        for it, n in zip(items, qlens):
+            mm = getattr(it.seq, "mm", None)
+            if mm is None:
+                p3.append(np.broadcast_to(np.arange(it.start, it.start + n, dtype=np.int64), (3, n)))
+            else:
+                p3.append(mm.positions(it.start, it.start + n))
+                hi = min(it.start + n, mm.index_of.shape[0])
+                if hi > it.start:
+                    idx = mm.index_of[it.start:hi]
+                    for j in np.nonzero(idx >= 0)[0]:
+                        rows.append(r0 + int(j))
+                        src_seq.append(it.seq)
+                        src_row.append(int(idx[j]))
+            r0 += n
+        fb.positions3 = self._stage("pos3", np.ascontiguousarray(np.concatenate(p3, 1)), torch.int64).view(3, -1)
+        if rows:
+            emb = self.model.embed_tokens(fb.input_ids).clone()
+            by_seq: dict = {}
+            for r, s, j in zip(rows, src_seq, src_row):
+                by_seq.setdefault(id(s), (s, [], []))
+                by_seq[id(s)][1].append(r)
+                by_seq[id(s)][2].append(j)
+            for s, rr, jj in by_seq.values():
+                src = s.mm.embeds.to(device=emb.device, dtype=emb.dtype)
+                emb[torch.tensor(rr, device=emb.device)] = src[torch.tensor(jj, device=emb.device)]
+            fb.inputs_embeds = emb
+
     # ------------------------------------------------------------------ execution
     def _can_graph(self, batch: ForwardBatch) -> bool:
         return (self.on_gpu and self.cfg.use_cuda_graphs and batch.num_seqs > 0
                 and batch.num_decodes == batch.num_seqs and not batch.spec_verify and batch.adapter_rows is None
+                and batch.positions3 is None
                 and getattr(self.model, "graph_safe", True) and not self.model.gdn_layers())
 
     def forward(self, batch: ForwardBatch) -> torch.Tensor:

@@ -63,6 +63,7 @@ class Sequence:
     spec_accepted: int = 0
     spec_proposed: int = 0
     rng: RequestRng = None  # type: ignore
+    mm: Any = None                        # models.vision.MultiModalInputs of a request with images
 
     def __post_init__(self):
         if self.rng is None:

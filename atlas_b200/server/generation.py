@@ -144,6 +144,14 @@ class Generator:
             toks = tk.encode(text, add_special_tokens=bool(tk.bos_token_id is not None and s.args.get("add_bos", False)))
         if not toks:
             toks = [tk.bos_token_id if tk.bos_token_id is not None else 0]
+        req._images = []
+        model = s.engine.engine.model
+        if req.messages is not None and getattr(model, "vision", None) is not None:
+            from .multimodal import ImageError, prepare_images
+            try:
+                toks, req._images = prepare_images(req.messages, toks, model.cfg.vision, model.cfg.image_token_id)
+            except ImageError as e:
+                raise BadRequest(str(e), "messages")
         presets = s.args.get("sampling_presets", {})
         sp = sampling_from_fields(req.sampling, presets, max_default=s.args.get("default_max_tokens", 1024))
         if req.logprobs:
@@ -203,7 +211,8 @@ class Generator:
         adapter_slot = lora.slot_of(req.adapter or s.active_adapter) if lora is not None else 0
         if req.adapter and not adapter_slot:
             raise ValueError(f"adapter '{req.adapter}' is not loaded")
-        gen_iter = s.engine.generate(toks, sp, request_id="req-" + req.request_id, namespace=ns, adapter_slot=adapter_slot,
+        extra = {"images": req._images} if getattr(req, "_images", None) else {}
+        gen_iter = s.engine.generate(toks, sp, request_id="req-" + req.request_id, namespace=ns, adapter_slot=adapter_slot, **extra,
                                      grammar=_GrammarAdapter(grammar) if grammar else None,
                                      logits_processors=procs, timeout_s=req.timeout_s, disable_spec=req.disable_spec,
                                      stop_checker=(LoopDetector(span=int(s.args.get("loop_guard_span") or 128))

@@ -232,3 +232,68 @@ def test_fast_loader_gives_identical_tensors(tmp_path, monkeypatch):
         assert a.dtype == b.dtype and a.shape == b.shape and torch.equal(a, b)
     m = load_model(path, dtype="float32", with_mtp=False)
     assert m.layers[0].mixer.qkv.weight.shape[1] == 256
+
+
+def test_multimodal_logits_match_transformers(tmp_path):
+    """Qwen3.5 with its vision tower: an image in the middle of the prompt.  The tower output, the placeholder
+    substitution and the interleaved three-stream rotary positions together must reproduce the HF logits; a chunked
+    prefill followed by decode steps through the engine must continue at the right positions after the image."""
+    from atlas_b200.config import EngineConfig
+    from atlas_b200.engine import LLMEngine
+    from atlas_b200.models.batch import ForwardBatch
+    from atlas_b200.models.vision import prepare
+    from atlas_b200.sampling import SamplingParams
+    torch.manual_seed(0)
+    tc = dict(vocab_size=512, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+              max_position_embeddings=256, intermediate_size=512, linear_num_key_heads=2, linear_num_value_heads=4,
+              linear_key_head_dim=64, linear_value_head_dim=64, layer_types=["linear_attention", "full_attention"],
+              tie_word_embeddings=False)
+    vc = dict(depth=2, hidden_size=64, intermediate_size=128, num_heads=4, in_channels=3, patch_size=4, temporal_patch_size=2,
+              spatial_merge_size=2, out_hidden_size=256, num_position_embeddings=64)
+    cfg = transformers.Qwen3_5Config(text_config=tc, vision_config=vc, image_token_id=500, video_token_id=501,
+                                     vision_start_token_id=502, vision_end_token_id=503)
+    hf = transformers.Qwen3_5ForConditionalGeneration(cfg).float().eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("bias") or "norm" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    path = _save(hf, tmp_path)
+    grid = (1, 4, 6)                                            # 24 patches -> 6 placeholders
+    px = torch.randn(24, 3 * 2 * 4 * 4)
+    toks = [11, 12, 502] + [500] * 6 + [503, 13, 14, 15, 16, 17]
+    types = [1 if t == 500 else 0 for t in toks]
+    with torch.no_grad():
+        want = hf(input_ids=torch.tensor([toks]), pixel_values=px, image_grid_thw=torch.tensor([grid]),
+                  mm_token_type_ids=torch.tensor([types])).logits[0]
+    model = load_model(path, dtype="float32", with_mtp=False)
+    assert model.vision is not None and model.cfg.image_token_id == 500
+    mm = prepare(model.vision, toks, 500, [(px, grid)])
+    assert mm.delta == 3 - 6                                    # the image advances positions by max(2, 3), not by 6 tokens
+    cache = model.alloc_cache(4, 16, torch.float32, state_slots=1)
+    fb = ForwardBatch.build([toks], [0], [[0, 1, 2]], 16, state_slots=[0], has_state=[False], all_logits=True)
+    fb.positions3 = torch.from_numpy(mm.positions(0, len(toks)))
+    emb = model.embed_tokens(fb.input_ids).clone()
+    emb[torch.tensor(types).bool()] = mm.embeds
+    fb.inputs_embeds = emb
+    got = model.compute_logits(model.forward(fb, cache))
+    torch.testing.assert_close(got, want, atol=3e-4, rtol=1e-3)
+    # through the engine: chunked prefill (8-token chunks cut the image in two), then greedy decode; the oracle decodes
+    # by re-running the whole sequence
+    eng = LLMEngine(model, EngineConfig(num_kv_blocks=16, max_num_seqs=2, max_seq_len=64, max_prefill_tokens=8,
+                                        enable_prefix_caching=False))
+    eng.add_request(toks, SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True), images=[(px, grid)])
+    out = []
+    while eng.has_unfinished():
+        for o in eng.step():
+            if o.finished:
+                out = o.output_tokens
+    seq = list(toks)
+    ref_out = []
+    for _ in range(4):
+        with torch.no_grad():
+            lg = hf(input_ids=torch.tensor([seq]), pixel_values=px, image_grid_thw=torch.tensor([grid]),
+                    mm_token_type_ids=torch.tensor([[1 if t == 500 else 0 for t in seq]])).logits[0, -1]
+        nxt = int(lg.argmax())
+        ref_out.append(nxt)
+        seq.append(nxt)
+    assert out == ref_out

@@ -220,3 +220,35 @@ def test_over_long_chat_is_compacted_or_rejected():
         assert r.json()["usage"]["prompt_tokens"] <= 1024 - 64
     finally:
         aeng.shutdown(drain=False)
+
+
+def test_image_parts_are_decoded_patchified_and_placeholders_widened():
+    import base64
+    import io
+
+    import numpy as np
+    from PIL import Image
+
+    from atlas_b200.models.vision import VisionConfig, mrope_positions
+    from atlas_b200.server.multimodal import ImageError, expand_placeholders, extract_images, prepare_images
+    rng = np.random.default_rng(0)
+    buf = io.BytesIO()
+    Image.fromarray((rng.random((37, 50, 3)) * 255).astype(np.uint8)).save(buf, format="PNG")
+    b64 = base64.b64encode(buf.getvalue()).decode()
+    msgs = [{"role": "user", "content": [{"type": "text", "text": "look"},
+                                         {"type": "image_url", "image_url": {"url": "data:image/png;base64," + b64}},
+                                         {"type": "image", "source": {"type": "base64", "media_type": "image/png", "data": b64}}]}]
+    imgs = extract_images(msgs)
+    assert len(imgs) == 2 and imgs[0].shape == (37, 50, 3) and (imgs[0] == imgs[1]).all()
+    cfg = VisionConfig(patch_size=4, spatial_merge_size=2, temporal_patch_size=2, hidden_size=64, depth=1, num_heads=4,
+                       intermediate_size=128, out_hidden_size=256, num_position_embeddings=64)
+    toks, pairs = prepare_images(msgs, [1, 500, 2, 500, 3], cfg, 500)
+    (p0, g0), (p1, g1) = pairs
+    assert g0 == (1, 10, 12) and p0.shape == (120, 3 * 2 * 4 * 4) and toks.count(500) == 2 * 30
+    pos, delta = mrope_positions(toks, 500, [g0, g1], 2)
+    assert pos.shape == (3, len(toks)) and delta == (1 + 6 + 1 + 6 + 1) - len(toks)
+    assert pos[:, 0].tolist() == [0, 0, 0] and pos[1, 1:31].max() == 1 + 4 and pos[2, 1:31].max() == 1 + 5
+    with pytest.raises(ImageError):
+        expand_placeholders([1, 2], 500, [4])
+    with pytest.raises(ImageError):
+        extract_images([{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "https://example.com/x.png"}}]}])
