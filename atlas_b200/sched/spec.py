@@ -31,8 +31,12 @@ from .sequence import SchedulerOutput, SeqStatus
 class MtpGate:
     """Throughput arbitration between speculative and plain decode."""
 
-    def __init__(self, enabled: bool = True, window: int = 32, remeasure_every: int = 512, probe_steps: int = 16):
+    def __init__(self, enabled: bool = True, window: int = 32, remeasure_every: int = 512, probe_steps: int = 16, agree=None):
+        """``agree``: maps this rank's ``[seconds, tokens]`` of a finished probe to the values every rank uses (e.g. a
+        MAX all-reduce).  Ranks that run the same engine loop side by side time their steps a little differently; without
+        an agreed measurement they would pick different modes and issue different collectives."""
         self.enabled = enabled
+        self.agree = agree
         self.window, self.remeasure_every, self.probe_steps = window, remeasure_every, probe_steps
         self.mode = "spec"                       # spec | plain
         self.tps = {"spec": 0.0, "plain": 0.0}
@@ -57,6 +61,8 @@ class MtpGate:
         self._since_measure += 1
         if self._probing is not None and self._steps_in_mode >= self.probe_steps:
             sec, tok = self._acc[self._probing]
+            if self.agree is not None:
+                sec, tok = self.agree([sec, float(tok)])
             if sec > 0:
                 self.tps[self._probing] = tok / sec
             self._acc[self._probing] = [0.0, 0]
@@ -73,12 +79,34 @@ class MtpGate:
             self._acc[self._probing] = [0.0, 0]
 
 
+def rank_agreement(engine):
+    """The gate's ``agree`` hook for ranks that run the engine loop symmetrically (tensor / expert parallel without a
+    leader process): a MAX all-reduce of the probe measurement over the default process group.  None for one process or
+    when a leader imposes its decisions anyway."""
+    p = getattr(getattr(engine, "model", None), "pctx", None)
+    if p is None or getattr(engine, "control", None) is not None or max(p.tp_size, p.ep_size) <= 1:
+        return None
+    try:
+        import torch.distributed as dist
+        if not dist.is_initialized():
+            return None
+    except Exception:
+        return None
+    dev = engine.model.device
+
+    def agree(vals):
+        t = torch.tensor(vals, dtype=torch.float64, device=dev if dev.type == "cuda" else "cpu")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+    return agree
+
+
 class SpecController:
     def __init__(self, engine, cfg: EngineConfig):
         self.engine = engine
         self.cfg = cfg
         self.k = cfg.num_drafts
-        self.gate = MtpGate(enabled=cfg.mtp_gate)
+        self.gate = MtpGate(enabled=cfg.mtp_gate, agree=rank_agreement(engine))
 
     def active(self) -> bool:
         return True
@@ -174,7 +202,7 @@ class NgramSpecController:
         self.engine, self.cfg = engine, cfg
         self.k = max(1, cfg.num_drafts)
         self.n_max, self.n_min = max(1, cfg.ngram_max), max(1, min(cfg.ngram_min, cfg.ngram_max))
-        self.gate = MtpGate(enabled=cfg.mtp_gate)
+        self.gate = MtpGate(enabled=cfg.mtp_gate, agree=rank_agreement(engine))
         self.proposed_steps = 0
 
     def active(self) -> bool:
@@ -229,7 +257,7 @@ class DFlashSpecController:
     def __init__(self, engine, cfg: EngineConfig):
         self.engine, self.cfg = engine, cfg
         self.k = max(1, cfg.num_drafts)
-        self.gate = MtpGate(enabled=cfg.mtp_gate)
+        self.gate = MtpGate(enabled=cfg.mtp_gate, agree=rank_agreement(engine))
         self.drafter = engine.model.dflash
         self.proposed_steps = 0
 

@@ -178,7 +178,7 @@ def main():
         if args.gpus > 1:
             print(f"bench.py: --gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})", file=sys.stderr)
             return 2
-    topo, pctx, device = init_distributed(tp_size=world, ep_size=args.ep if world > 1 else 0)
+    topo, pctx, device = init_distributed(tp_size=world, ep_size=args.ep if world > 1 else 0, timeout_s=180.0)
     rank = topo.rank
     if args.nvfp4_activations:
         from atlas_b200 import ops as _ops

@@ -661,3 +661,29 @@ def test_red_zone_guards_and_block_poison():
     assert float(k[2].float().min()) == 448.0 and float(v[2].float().min()) > 1e30 and float(k[1].float().abs().sum()) == 0
     zero_block((k, v), 2)
     assert float(k.float().abs().sum()) == 0 and float(v.float().abs().sum()) == 0
+
+
+def test_spec_gate_uses_the_agreed_measurement():
+    """Two ranks time the same probe differently; with the agreement hook (here: the maximum of both) they reach the same
+    verdict, without it they would not."""
+    from atlas_b200.sched.spec import MtpGate
+
+    def run(times_spec, times_plain, agree):
+        g = MtpGate(enabled=True, probe_steps=4, agree=agree)
+        for t in times_spec:
+            g.record(True, t, 8)
+        for t in times_plain:
+            g.record(False, t, 4)
+        return g.mode
+
+    a = ([0.010] * 4, [0.0049] * 4)          # rank 0: spec 800 tok/s vs plain 816 tok/s -> plain
+    b = ([0.010] * 4, [0.0052] * 4)          # rank 1: spec 800 vs plain 769 -> spec
+    assert run(*a, None) == "plain" and run(*b, None) == "spec"
+    shared = {"spec": None, "plain": None}
+
+    def make(rank_vals_other):
+        it = iter(rank_vals_other)
+        return lambda v: [max(x, y) for x, y in zip(v, next(it))]
+    other_of_a = [[0.040, 32.0], [0.0208, 16.0]]     # what rank 1 measured for the two probes
+    other_of_b = [[0.040, 32.0], [0.0196, 16.0]]     # what rank 0 measured
+    assert run(*a, make(other_of_a)) == run(*b, make(other_of_b)) == "spec"
