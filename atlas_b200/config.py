@@ -19,7 +19,7 @@ from typing import Any, Dict, List, Optional, Tuple
 
 # model_type spellings accepted from config.json -> canonical family.
 _FAMILY_ALIASES = {
-    "llama": "dense", "mistral": "dense", "qwen2": "dense", "qwen3": "dense",
+    "llama": "dense", "mistral": "dense", "qwen2": "dense", "qwen3": "dense", "gemma3_text": "dense", "gemma3": "dense",
     "qwen3_moe": "moe", "qwen3_vl_moe": "moe", "mixtral": "moe", "minimax_m2": "moe",
     "qwen3_next": "hybrid", "qwen3_5": "hybrid", "qwen35": "hybrid", "qwen3_5_text": "hybrid",
     "qwen3_5_moe": "hybrid", "qwen35_moe": "hybrid", "qwen3_6_moe": "hybrid", "qwen3_5_moe_text": "hybrid",
@@ -141,6 +141,13 @@ class ModelConfig:
     v_head_dim: int = 0
     rope_interleaved: bool = True     # checkpoint stores rotary columns as (even, odd) pairs
     first_k_dense_replace: int = 0    # leading layers with a dense FFN in an otherwise MoE model
+    # Gemma: scaled embeddings, explicit attention scale, norms after the mixer and the FFN as well as before them, a
+    # separate rotary base for sliding-window layers, soft-capped output logits
+    embed_scale: float = 1.0
+    attn_scale: float = 0.0           # 0 = head_dim ** -0.5
+    sandwich_norms: bool = False
+    rope_local_theta: float = 0.0     # rotary base of the sliding-window layers (0 = same table as the other layers)
+    final_logit_softcapping: float = 0.0
     # multimodal: interleaved MRoPE sections (time, row, column), the image placeholder id and the vision tower's config
     mrope_section: List[int] = field(default_factory=list)
     image_token_id: int = -1
@@ -171,7 +178,7 @@ class ModelConfig:
         if self.block_types:
             return {"mamba": "mamba2", "attention": "attention"}.get(self.block_types[i], "none")
         if self.family != "hybrid":
-            return "attention"
+            return "attention"                # (Gemma's layer_types only choose the attention window)
         if self.layer_types:
             return "attention" if self.layer_types[i] == "full_attention" else "gdn"
         return "attention" if (i + 1) % self.full_attention_interval == 0 else "gdn"
@@ -283,6 +290,23 @@ class ModelConfig:
             quant=QuantConfig.from_hf(cfg.get("quantization_config")),
             bos_token_id=cfg.get("bos_token_id"), eos_token_id=cfg.get("eos_token_id"),
         )
+        if mt in ("gemma3_text", "gemma3"):
+            rp = cfg.get("rope_parameters") or {}
+            glob, loc = rp.get("full_attention") or {}, rp.get("sliding_attention") or {}
+            c.rope_theta = float(glob.get("rope_theta", cfg.get("rope_theta", 1e6)))
+            c.rope_scaling = glob if glob.get("rope_type", "default") != "default" else cfg.get("rope_scaling")
+            c.rope_local_theta = float(loc.get("rope_theta", cfg.get("rope_local_base_freq", 1e4)))
+            c.partial_rotary_factor = 1.0
+            c.norm_plus_one = c.qk_norm = c.sandwich_norms = True
+            c.embed_scale = float(hs) ** 0.5
+            c.attn_scale = float(cfg.get("query_pre_attn_scalar", c.head_dim)) ** -0.5
+            c.mlp_activation = "gelu_tanh_glu"
+            c.layer_types = list(cfg.get("layer_types") or [])
+            c.sliding_window = cfg.get("sliding_window")
+            c.final_logit_softcapping = float(cfg.get("final_logit_softcapping") or 0.0)
+            c.tie_word_embeddings = bool(cfg.get("tie_word_embeddings", True))
+            if cfg.get("attn_logit_softcapping"):
+                raise ValueError("attention logit soft-capping (Gemma-2) is not supported")
         if mt == "mixtral":
             c.moe_intermediate_size = c.intermediate_size
         if mt.startswith("deepseek") or mt == "kimi_k2":

@@ -134,7 +134,8 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bf
   }
 }
 
-// gate_up [T, 2I] -> silu(gate) * up, bf16 or fp8+scale
+// gate_up [T, 2I] -> act(gate) * up, bf16 or fp8+scale.  ACT 0: SiLU, 1: tanh-approximated GELU (Gemma).
+template <int ACT>
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, long long ld, int I, __nv_bfloat16* y, long long ldy, uint8_t* q,
                 long long ldq, float* scale, long long scale_ld, const int* live_tiles) {
@@ -152,7 +153,13 @@ silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, long long ld, int I, __nv_
     load8(gu + t * ld + I + e, u);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float s = __fdividef(g[i], 1.f + __expf(-g[i]));
+      float s;
+      if (ACT == 0) {
+        s = __fdividef(g[i], 1.f + __expf(-g[i]));
+      } else {
+        const float x = g[i];
+        s = 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+      }
       o[i] = __bfloat162float(__float2bfloat16_rn(s * u[i]));
       amax = fmaxf(amax, fabsf(o[i]));
     }
@@ -581,9 +588,20 @@ extern "C" int atlas_silu_mul(const void* gu, long long ld, int T, int I, void* 
   if (T <= 0) return 0;
   if (I % 8 || (q && I % 128)) return -1;
   dim3 grid(T, (I / 8 + 255) / 256);
-  launch_chain_if(T <= 256, silu_mul_kernel, grid, dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+  launch_chain_if(T <= 256, silu_mul_kernel<0>, grid, dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
       reinterpret_cast<const __nv_bfloat16*>(gu), ld, I, reinterpret_cast<__nv_bfloat16*>(y), ldy,
       reinterpret_cast<uint8_t*>(q), ldq, scale, scale_ld, live_tiles);
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+extern "C" int atlas_gelu_tanh_mul(const void* gu, long long ld, int T, int I, void* y, long long ldy, void* q,
+                                   long long ldq, float* scale, long long scale_ld, void* stream) {
+  if (T <= 0) return 0;
+  if (I % 8 || (q && I % 128)) return -1;
+  dim3 grid(T, (I / 8 + 255) / 256);
+  launch_chain_if(T <= 256, silu_mul_kernel<1>, grid, dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+      reinterpret_cast<const __nv_bfloat16*>(gu), ld, I, reinterpret_cast<__nv_bfloat16*>(y), ldy,
+      reinterpret_cast<uint8_t*>(q), ldq, scale, scale_ld, static_cast<const int*>(nullptr));
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
 }
 

@@ -57,6 +57,8 @@ int atlas_gated_rmsnorm(const void* x, long long ldx, const void* z, long long l
                         long long ldy, int T, int H, int D, float eps, void* stream);
 
 // ---- MoE (moe.cu) and grouped GEMM (gemm.cu)
+int atlas_gelu_tanh_mul(const void* gu, long long ld, int T, int I, void* y, long long ldy, void* q, long long ldq,
+                        float* scale, long long scale_ld, void* stream);
 int atlas_moe_route(const void* logits, long long ld, int is_bf16, int T, int E, int k, int norm, int sigmoid,
                     float* w_out, int* id_out, void* stream);
 int atlas_moe_route_ex(const void* logits, long long ld, int is_bf16, int T, int E, int k, int norm, int score_mode,

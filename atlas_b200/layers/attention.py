@@ -30,7 +30,11 @@ class Attention:
         self.kv_rep = max(1, tp // cfg.num_key_value_heads)     # ranks sharing one kv head
         self.d = cfg.head_dim
         self.gated = cfg.attn_output_gate
-        self.scale = self.d ** -0.5
+        self.scale = cfg.attn_scale or self.d ** -0.5
+        # models with per-layer attention kinds (Gemma): only "sliding_attention" layers use the window
+        kinds = cfg.layer_types if (cfg.family != "hybrid" and cfg.layer_types) else None
+        self.local = bool(kinds) and kinds[layer_idx] == "sliding_attention"
+        self.window = cfg.sliding_window if (kinds is None or self.local) else None
         self.quant_kind = quant_kind
         self.qkv: Optional[LinearWeight] = None
         self.o: Optional[LinearWeight] = None
@@ -107,7 +111,7 @@ class Attention:
         q = ops.qk_norm_rope_kv_write(q, k, v, rope_pos, rope_cache, cfg.rotary_dim, k_cache, v_cache,
                                       batch.slot_mapping, k_scale, v_scale, self.q_norm, self.k_norm,
                                       cfg.rms_norm_eps, cfg.norm_plus_one)
-        out = ops.paged_attention(q, k_cache, v_cache, batch, self.scale, k_scale, v_scale, cfg.sliding_window)
+        out = ops.paged_attention(q, k_cache, v_cache, batch, self.scale, k_scale, v_scale, self.window)
         out = out.reshape(T, nq)
         if self.gated:
             gate = qkv[:, nq + 2 * nkv:]

@@ -47,6 +47,8 @@ class DenseMLP:
 
     def hidden_act(self, act: Act) -> Act:
         """gate|up GEMM + SiLU * mul: the input of the down projection (no adapters)."""
+        if self.activation == "gelu_tanh_glu":
+            return ops.glu_act(ops.linear(act, self.gate_up), self.down.kind == "fp8_block", "gelu_tanh")
         if self.down.kind == "fp8_block" and ops.swiglu_fusable(act, self.gate_up):
             return ops.linear_swiglu(act, self.gate_up)
         return ops.silu_mul_act(ops.linear(act, self.gate_up), want_fp8=self.down.kind == "fp8_block")
@@ -60,6 +62,9 @@ class DenseMLP:
         if self.activation == "relu2":
             return self._relu2(act, reduce)
         use_lora = self.lora is not None and batch is not None and batch.adapter_rows is not None and self.lora_prefix
+        if self.activation == "gelu_tanh_glu" and not use_lora:
+            a = self.hidden_act(act)
+            return self.pctx.row_parallel_linear(a, self.down) if (self.shard and reduce) else ops.linear(a, self.down)
         if not use_lora and self.down.kind == "fp8_block" and ops.swiglu_fusable(act, self.gate_up):
             a = ops.linear_swiglu(act, self.gate_up)
             return self.pctx.row_parallel_linear(a, self.down) if (self.shard and reduce) else ops.linear(a, self.down)

@@ -194,6 +194,9 @@ def _load_gdn(ck, pre, mixer, model, kind) -> None:
 def _load_layer(ck, pre, layer, model, dense_kind, expert_kind) -> None:
     layer.input_norm = _vec(ck, f"{pre}.input_layernorm.weight", model)
     layer.post_norm = _vec(ck, f"{pre}.post_attention_layernorm.weight", model)
+    if layer.cfg.sandwich_norms:
+        layer.pre_ffn_norm = _vec(ck, f"{pre}.pre_feedforward_layernorm.weight", model)
+        layer.post_ffn_norm = _vec(ck, f"{pre}.post_feedforward_layernorm.weight", model)
     if layer.kind == "attention" and layer.cfg.kv_lora_rank > 0:
         _load_mla(ck, f"{pre}.self_attn", layer.mixer, model, dense_kind)
     elif layer.kind == "attention":

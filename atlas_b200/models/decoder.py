@@ -85,11 +85,19 @@ class DecoderLayer:
         self.ffn = MoE(cfg, pctx, expert_kind, dense_kind, ep_mode) if self.is_moe else DenseMLP(cfg, pctx, dense_kind)
         self.input_norm: Optional[torch.Tensor] = None
         self.post_norm: Optional[torch.Tensor] = None
+        # sandwich norms (Gemma): post_norm normalises the mixer's OUTPUT, pre_ffn_norm the FFN's input, post_ffn_norm
+        # the FFN's output; without them post_norm is the FFN's input norm
+        self.pre_ffn_norm: Optional[torch.Tensor] = None
+        self.post_ffn_norm: Optional[torch.Tensor] = None
+        self.rope_override: Optional[torch.Tensor] = None     # rotary table of sliding-window layers with their own base
 
     def init_random(self, gen, std, dtype, device):
         base = 0.0 if self.cfg.norm_plus_one else 1.0
         self.input_norm = torch.full((self.cfg.hidden_size,), base, dtype=dtype, device=device)
         self.post_norm = torch.full((self.cfg.hidden_size,), base, dtype=dtype, device=device)
+        if self.cfg.sandwich_norms:
+            self.pre_ffn_norm = torch.full((self.cfg.hidden_size,), base, dtype=dtype, device=device)
+            self.post_ffn_norm = torch.full((self.cfg.hidden_size,), base, dtype=dtype, device=device)
         self.mixer.init_random(gen, std, dtype, device)
         self.ffn.init_random(gen, std, dtype, device)
 
@@ -104,7 +112,7 @@ class DecoderLayer:
         """This layer's input norm may be applied by the previous layer's down projection (deferred 1/rms factor): its
         only consumer of the normalised input is an FP8 linear layer."""
         return (self.kind == "attention" and isinstance(self.mixer, Attention) and self.mixer.qkv.kind == "fp8_block"
-                and self.mixer.lora is None)
+                and self.mixer.lora is None and not self.cfg.sandwich_norms)
 
     def forward(self, x, residual: Optional[torch.Tensor], batch: ForwardBatch, cache: CacheStore,
                 rope_cache: torch.Tensor, next_norm: Optional[torch.Tensor] = None):
@@ -114,6 +122,8 @@ class DecoderLayer:
         ``Act`` in place of the plain output."""
         cfg = self.cfg
         eps, p1 = cfg.rms_norm_eps, cfg.norm_plus_one
+        if self.rope_override is not None:
+            rope_cache = self.rope_override
         if isinstance(x, Act):
             act = x
         elif residual is None:
@@ -121,6 +131,13 @@ class DecoderLayer:
             residual = x
         else:
             act, residual = ops.rmsnorm_act(x, self.input_norm, eps, residual, p1, self._mixer_fp8())
+        if cfg.sandwich_norms:
+            h = self.mixer.forward(act, batch, cache.layer_kv(self.idx), rope_cache)
+            h, _ = ops.rmsnorm(h, self.post_norm, eps, None, p1)
+            act, residual = ops.rmsnorm_act(h, self.pre_ffn_norm, eps, residual, p1, self._ffn_fp8())
+            h = self.ffn.forward(act, batch=batch)
+            h, _ = ops.rmsnorm(h, self.post_ffn_norm, eps, None, p1)
+            return h, residual
         single = self.mixer.pctx.tp_size == 1
         no_lora = batch.adapter_rows is None
         dense_fp8_ffn = self._ffn_fp8() and self.ffn.down.kind == "fp8_block"
@@ -266,6 +283,11 @@ class DecoderLM:
         cfg = self.cfg
         mp = max_pos or cfg.max_position_embeddings
         self.rope_cache = ref.build_rope_cache(cfg.rotary_dim, mp, cfg.rope_theta, cfg.rope_scaling, self.device)
+        if cfg.rope_local_theta:
+            local = ref.build_rope_cache(cfg.rotary_dim, mp, cfg.rope_local_theta, None, self.device)
+            for l in self.layers:
+                if l.kind == "attention" and getattr(l.mixer, "local", False):
+                    l.rope_override = local
 
     # ------------------------------------------------------------------ cache allocation
     def attention_layers(self) -> List[int]:
@@ -304,7 +326,10 @@ class DecoderLM:
         from ..ops import checked
         if checked.ENABLED:
             checked.index_range("input_ids", ids, 0, self.cfg.vocab_size)
-        return self.embed[ids.long()]
+        e = self.embed[ids.long()]
+        if self.cfg.embed_scale != 1.0:
+            e = e * torch.tensor(self.cfg.embed_scale, dtype=e.dtype)      # the factor is rounded to the weight dtype first
+        return e
 
     # ------------------------------------------------------------------ sequence-parallel prefill (tensor parallel)
     def _seq_parallel_area(self, batch: ForwardBatch, T: int):
@@ -319,7 +344,7 @@ class DecoderLM:
             return None
         ok = getattr(self, "_sp_model_ok", None)
         if ok is None:
-            ok = self.dtype == torch.bfloat16 and self.cfg.hidden_size % 256 == 0 and all(
+            ok = self.dtype == torch.bfloat16 and self.cfg.hidden_size % 256 == 0 and not self.cfg.sandwich_norms and all(
                 l.kind == "attention" and not l.is_moe and l.ffn.shard and l.mixer.qkv.kind == "fp8_block"
                 and l.mixer.o.kind == "fp8_block" and l.ffn.gate_up.kind == "fp8_block" and l.ffn.down.kind == "fp8_block"
                 and l.mixer.o.bias is None and l.ffn.down.bias is None for l in self.layers)
@@ -380,6 +405,9 @@ class DecoderLM:
         logits = ops.linear(h, self.lm_head)
         if self.vocab_parallel and self.pctx.comm is not None:
             logits = self.pctx.comm.all_gather(logits, dim=-1)
+        cap = self.cfg.final_logit_softcapping
+        if cap:
+            logits = torch.tanh(logits.float() / cap).mul_(cap).to(logits.dtype)
         return logits
 
     @torch.inference_mode()

@@ -144,6 +144,21 @@ def relu_squared(x: torch.Tensor) -> torch.Tensor:
     return torch.relu(x).square()
 
 
+def glu_act(gate_up: torch.Tensor, want_fp8=False, kind: str = "silu") -> Act:
+    """``act(gate) * up`` with ``kind`` in {silu, gelu_tanh}."""
+    if kind == "silu":
+        return silu_mul_act(gate_up, want_fp8)
+    inter = gate_up.shape[-1] // 2
+    gpu = on_gpu(gate_up) and gate_up.dtype == torch.bfloat16
+    if want_fp8 and inter % 128 == 0:
+        if gpu:
+            q, s = cuda_ops().gelu_tanh_mul(gate_up, quant=True)
+        else:
+            q, s = Q.per_token_group_quant_fp8(ref.gelu_tanh_mul(gate_up), 128)
+        return Act(q=q, s=s, dtype=gate_up.dtype)
+    return Act(x=cuda_ops().gelu_tanh_mul(gate_up) if gpu else ref.gelu_tanh_mul(gate_up))
+
+
 def silu_mul_act(gate_up: torch.Tensor, want_fp8=False) -> Act:
     inter = gate_up.shape[-1] // 2
     if want_fp8 and inter % 128 == 0:

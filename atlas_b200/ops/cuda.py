@@ -220,6 +220,28 @@ def silu_mul(gate_up: torch.Tensor, quant=False, live_tiles: Optional[torch.Tens
     return y
 
 
+def gelu_tanh_mul(gate_up: torch.Tensor, quant=False):
+    """``gelu_tanh(gate) * up`` of ``[T, 2I]`` (gate | up): bf16, or FP8 with 128-wide group scales."""
+    assert gate_up.dtype == torch.bfloat16 and gate_up.stride(1) == 1
+    T, I2 = gate_up.shape
+    I = I2 // 2
+    _dev(gate_up)
+    L = lib()
+    if not getattr(L, "_gelu_bound", False):
+        L.atlas_gelu_tanh_mul.argtypes = [_vp, _ll, _i, _i, _vp, _ll, _vp, _ll, _vp, _ll, _vp]
+        L._gelu_bound = True
+    if quant:
+        q = torch.empty(T, I, dtype=FP8, device=gate_up.device)
+        s = _scale_buf(T, I // 128, gate_up.device)
+        _check(L.atlas_gelu_tanh_mul(gate_up.data_ptr(), gate_up.stride(0), T, I, None, 0, q.data_ptr(), I, s.data_ptr(),
+                                     s.stride(1), _stream()), "gelu_tanh_mul")
+        return q, s
+    y = torch.empty(T, I, dtype=gate_up.dtype, device=gate_up.device)
+    _check(L.atlas_gelu_tanh_mul(gate_up.data_ptr(), gate_up.stride(0), T, I, y.data_ptr(), I, None, 0, None, 0, _stream()),
+           "gelu_tanh_mul")
+    return y
+
+
 def gated_rmsnorm(x, z, w, eps):
     T, H, D = x.shape
     _dev(x)

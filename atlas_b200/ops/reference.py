@@ -207,6 +207,12 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     return (F.silu(g) * u).to(gate_up.dtype)
 
 
+def gelu_tanh_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    i = gate_up.shape[-1] // 2
+    g, u = gate_up[..., :i].float(), gate_up[..., i:].float()
+    return (F.gelu(g, approximate="tanh") * u).to(gate_up.dtype)
+
+
 def silu_mul_quant_fp8(gate_up: torch.Tensor, group: int = 128):
     y = silu_mul(gate_up)
     return per_token_group_quant_fp8(y, group)

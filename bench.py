@@ -151,6 +151,9 @@ def main():
     ap.add_argument("--ngram-speculative", action="store_true", help="prompt-lookup drafts (no draft model), --num-drafts deep")
     ap.add_argument("--nvfp4-activations", action="store_true",
                     help="NVFP4 checkpoints: quantise activations to NVFP4 too (block-scaled FP4 x FP4 tensor-core GEMM)")
+    ap.add_argument("--ssm-checkpoint-interval", type=int, default=0,
+                    help="hybrid models: tokens between recurrent-state snapshots for the prefix cache (0 = engine default)")
+    ap.add_argument("--ssm-cache-slots", type=int, default=0, help="hybrid models: snapshot slots (0 = concurrency + 8)")
     ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"],
                     help="tensor-parallel collectives: this engine's peer-memory kernels (default) or the NCCL baseline")
     args = ap.parse_args()
@@ -210,7 +213,8 @@ def main():
                         num_kv_blocks=blocks_per_seq * args.concurrency + 64, enable_prefix_caching=args.prefix_cache,
                         speculative=args.speculative, ngram_speculative=args.ngram_speculative,
                         num_drafts=args.num_drafts if (args.speculative or args.ngram_speculative) else 0,
-                        ssm_cache_slots=max(16, args.concurrency + 8),
+                        ssm_cache_slots=args.ssm_cache_slots or max(16, args.concurrency + 8),
+                        **({"ssm_checkpoint_interval": args.ssm_checkpoint_interval} if args.ssm_checkpoint_interval else {}),
                         use_cuda_graphs=not args.no_graphs, tp_size=world)
     eng = LLMEngine(model, ecfg)
     eng.time_device = True

@@ -208,14 +208,25 @@ def _logits_both_ways(cfg, prompt_len=48, kv_dtype=torch.float8_e4m3fn, high_pre
 
 
 @pytest.mark.parametrize("name", ["dense_fp8", "dense_bf16", "moe_fp8", "hybrid_bf16", "hybrid_fp8", "nemotron_bf16", "nemotron_fp8",
-                                  "dense_fp8_kvbf16", "dense_fp8_kvmixed", "mla_bf16", "mla_fp8"])
+                                  "dense_fp8_kvbf16", "dense_fp8_kvmixed", "mla_bf16", "mla_fp8", "gemma_bf16", "gemma_fp8"])
 def test_model_logits_kernels_vs_reference(K, name):
     kv_dtype, hi = torch.float8_e4m3fn, ()
     if name.endswith("kvbf16"):
         kv_dtype = torch.bfloat16                       # 16-bit paged cache on the general attention kernel
     if name.endswith("kvmixed"):
         hi = (0, 2)                                     # FP8 cache with two layers kept in 16 bits
-    if name.startswith("mla"):
+    if name.startswith("gemma"):
+        # sandwich norms, GELU-gated FFN, scaled embeddings, explicit attention scale, sliding-window layers with their own
+        # rotary base next to a full-attention layer, soft-capped logits (Gemma-3 shape); the 48-token prompt is longer
+        # than the 32-token window
+        cfg = ModelConfig(model_type="gemma3_text", family="dense", vocab_size=2048, hidden_size=512, intermediate_size=1024,
+                          num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=2, head_dim=128, rope_theta=1e6,
+                          rope_local_theta=1e4, qk_norm=True, norm_plus_one=True, sandwich_norms=True, embed_scale=512 ** 0.5,
+                          attn_scale=96 ** -0.5, mlp_activation="gelu_tanh_glu", sliding_window=32,
+                          layer_types=["sliding_attention", "full_attention", "sliding_attention"],
+                          final_logit_softcapping=30.0, tie_word_embeddings=True, max_position_embeddings=4096,
+                          quant=QuantConfig(method="fp8_block" if name.endswith("fp8") else "none"))
+    elif name.startswith("mla"):
         # latent attention (low-rank q / kv projections, shared rotary key part) + group-limited sigmoid router with a
         # selection bias, a shared expert and a leading dense layer (DeepSeek-V3 shape)
         cfg = ModelConfig(model_type="deepseek_v3", family="moe", vocab_size=2048, hidden_size=512, intermediate_size=1024,

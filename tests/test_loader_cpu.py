@@ -65,6 +65,14 @@ def _hf(kind: str):
             for n, b in m.named_buffers():
                 if n.endswith("e_score_correction_bias"):
                     b.copy_(torch.rand_like(b) * 0.2)
+    elif kind == "gemma3":
+        cfg = transformers.Gemma3TextConfig(vocab_size=512, hidden_size=256, num_hidden_layers=4, num_attention_heads=4,
+                                            num_key_value_heads=2, head_dim=64, intermediate_size=512, sliding_window=8,
+                                            max_position_embeddings=256, query_pre_attn_scalar=96,
+                                            layer_types=["sliding_attention", "sliding_attention", "full_attention",
+                                                         "sliding_attention"], final_logit_softcapping=20.0,
+                                            tie_word_embeddings=True)
+        m = transformers.Gemma3ForCausalLM(cfg)
     elif kind == "nemotron_h":
         cfg = transformers.NemotronHConfig(vocab_size=512, hidden_size=256, layers_block_type=["mamba", "attention", "mamba", "mamba"],
                                            num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=512,
@@ -95,7 +103,7 @@ def _ours_logits(model, toks):
     return model.forward_dense_reference(toks)
 
 
-@pytest.mark.parametrize("kind", ["llama", "qwen2", "qwen3", "qwen3_moe", "qwen3_next", "qwen3_5", "qwen3_5_moe", "nemotron_h", "deepseek_v3"])
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "qwen3", "qwen3_moe", "qwen3_next", "qwen3_5", "qwen3_5_moe", "nemotron_h", "deepseek_v3", "gemma3"])
 def test_logits_match_transformers(kind, tmp_path):
     hf = _hf(kind)
     path = _save(hf, tmp_path)
@@ -107,7 +115,7 @@ def test_logits_match_transformers(kind, tmp_path):
     torch.testing.assert_close(got, want, atol=2e-4, rtol=1e-3)
 
 
-@pytest.mark.parametrize("kind", ["qwen3", "qwen3_next", "qwen3_5", "nemotron_h", "deepseek_v3"])
+@pytest.mark.parametrize("kind", ["qwen3", "qwen3_next", "qwen3_5", "nemotron_h", "deepseek_v3", "gemma3"])
 def test_sharded_load_matches_full(kind, tmp_path):
     """TP=2 (dense) / TP=2+EP=2 (hybrid MoE): the ranks, run in lock-step over the in-process fake communicator,
     reproduce the single-rank logits."""
