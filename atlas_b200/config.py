@@ -507,6 +507,7 @@ class EngineConfig:
     speculative: bool = False
     num_drafts: int = 0
     mtp_gate: bool = True
+    dcut_ratio: float = 0.0                   # > 0: keep this fraction of the batch's draft rows, ranked by drafter confidence
     ngram_speculative: bool = False           # prompt-lookup drafts (no draft model); uses num_drafts
     ngram_max: int = 4
     ngram_min: int = 2

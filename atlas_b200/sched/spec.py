@@ -107,6 +107,7 @@ class SpecController:
         self.cfg = cfg
         self.k = cfg.num_drafts
         self.gate = MtpGate(enabled=cfg.mtp_gate, agree=rank_agreement(engine))
+        self.dcut_pruned = 0                     # draft rows dropped by the verify-depth planner
 
     def active(self) -> bool:
         return True
@@ -160,9 +161,21 @@ class SpecController:
         cur_h = mh[sel]
         drafts: List[List[int]] = [[] for _ in want]
         seqs = [out.items[owners[i]].seq for i in want]
-        d = ops.argmax(model.compute_logits(cur_h)).tolist()
+        dcut_on = self.cfg.dcut_ratio > 0
+        conf: List[List[float]] = [[] for _ in want]            # ln of the drafter's top-1 probability per draft
+
+        def top1(h):
+            lg = model.compute_logits(h)
+            tok = ops.argmax(lg)
+            if not dcut_on:
+                return tok.tolist(), None
+            lp = lg.float().log_softmax(-1).gather(-1, tok.view(-1, 1).long())[:, 0]
+            return tok.tolist(), lp.tolist()
+        d, lp0 = top1(cur_h)
         for j, t in enumerate(d):
             drafts[j].append(int(t))
+            if lp0 is not None:
+                conf[j].append(float(lp0[j]))
         alive = list(range(len(want)))
         for step in range(1, self.k):
             # chain: position p+step, inputs (head hidden, previous draft)
@@ -176,15 +189,22 @@ class SpecController:
             fbc.num_decodes = 0
             hsel = cur_h[torch.tensor(alive, device=cur_h.device)] if len(alive) != cur_h.shape[0] else cur_h
             mh2 = mtp.forward(fbc, model.embed_tokens(fbc.input_ids), hsel, eng.cache, model.rope_cache)
-            d = ops.argmax(model.compute_logits(mh2)).tolist()
+            d, lpn = top1(mh2)
             nh = cur_h.clone()
             for jj, j in enumerate(alive):
                 drafts[j].append(int(d[jj]))
+                if lpn is not None:
+                    conf[j].append(float(lpn[jj]))
                 nh[j] = mh2[jj]
             cur_h = nh
+        keep = [len(x) for x in drafts]
+        if dcut_on:
+            from . import dcut
+            keep = dcut.plan(conf, self.cfg.dcut_ratio)        # verify depth per sequence from the drafter's confidence
+            self.dcut_pruned += sum(len(x) for x in drafts) - sum(keep)
         for j, s in enumerate(seqs):
             room = s.sampling.max_tokens - s.num_output_tokens - 1
-            s.drafts = drafts[j][:max(0, min(self.k, room))]
+            s.drafts = drafts[j][:max(0, min(self.k, room, keep[j]))]
 
 
 class NgramSpecController:

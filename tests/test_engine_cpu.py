@@ -59,6 +59,21 @@ def test_speculative_equals_plain_greedy():
     assert spec.stats.spec_proposed > 0
 
 
+def test_dcut_prunes_verify_rows_and_stays_lossless():
+    """Verify-depth planning from drafter confidence: fewer rows are verified, the output is still plain greedy."""
+    model = build_model(tiny_hybrid()).init_random(0)
+    prompts = _prompts()
+    sp = SamplingParams(max_tokens=12, ignore_eos=True)
+    base = LLMEngine(model, EngineConfig(num_kv_blocks=64, max_num_seqs=8)).generate(prompts, sp)
+    full = LLMEngine(model, EngineConfig(num_kv_blocks=64, max_num_seqs=8, speculative=True, num_drafts=3, mtp_gate=False))
+    full.generate(prompts, sp)
+    cut = LLMEngine(model, EngineConfig(num_kv_blocks=64, max_num_seqs=8, speculative=True, num_drafts=3, mtp_gate=False,
+                                        dcut_ratio=0.5))
+    outs = cut.generate(prompts, sp)
+    assert [o.output_tokens for o in outs] == [o.output_tokens for o in base]
+    assert cut.spec.dcut_pruned > 0 and 0 < cut.stats.spec_proposed < full.stats.spec_proposed
+
+
 def test_order_independence_with_sampling():
     """A seeded request draws the same tokens whatever else shares its batch."""
     model = build_model(tiny_dense()).init_random(0)
