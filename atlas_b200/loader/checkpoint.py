@@ -14,6 +14,7 @@ from typing import Dict, Iterable, List, Optional
 
 import torch
 
+from .. import quant as Q
 from .qtensor import QTensor
 
 
@@ -37,6 +38,12 @@ class Checkpoint:
                             self._where[k] = fn
         if not self._where:
             raise FileNotFoundError(f"no safetensors weights under {path}")
+        self.mlx_group_size = 0
+        cfg = os.path.join(path, "config.json")
+        if os.path.exists(cfg):
+            with open(cfg) as f:
+                q = (json.load(f).get("quantization") or {})
+            self.mlx_group_size = int(q.get("group_size", 0) or 0)
 
     def keys(self) -> Iterable[str]:
         return self._where.keys()
@@ -100,6 +107,21 @@ class Checkpoint:
         (``weight`` uint8 + ``weight_scale`` e4m3 + ``weight_scale_2``) and compressed-tensors NVFP4
         (``weight_packed`` + ``weight_scale`` + ``weight_global_scale``)."""
         w = self.maybe(prefix + ".weight")
+        # MXFP4 (32-value e2m1 blocks with e8m0 scales): "<prefix>.weight_blocks" / "<prefix>_blocks" + "..._scales"
+        for b, sc in ((prefix + ".weight_blocks", prefix + ".weight_scales"), (prefix + "_blocks", prefix + "_scales")):
+            if w is None and self.has(b) and self.has(sc):
+                blocks, scales = self.get(b).view(torch.uint8), self.get(sc).view(torch.uint8)
+                if blocks.dim() == 3:
+                    conv = Q.mxfp4_to_nvfp4(blocks, scales)
+                    if conv is not None:                 # same e2m1 codes, scales re-expressed: runs on the NVFP4 kernels
+                        return QTensor("nvfp4", conv[0], conv[1], conv[2])
+                return QTensor("dense", Q.dequantize_mxfp4(blocks, scales).to(torch.bfloat16))
+        # MLX affine quantisation: uint32-packed ``weight`` + ``scales`` + ``biases``
+        if w is not None and w.dtype in (torch.uint32, torch.int32) and self.has(prefix + ".scales") and self.has(prefix + ".biases"):
+            sc, bi = self.get(prefix + ".scales"), self.get(prefix + ".biases")
+            group = self.mlx_group_size or 64
+            bits = w.shape[1] * 32 // (sc.shape[1] * group)
+            return QTensor("dense", Q.dequantize_mlx(w.view(torch.int32), sc, bi, bits, group).to(sc.dtype))
         if w is None and self.has(prefix + ".weight_packed"):
             packed = self.get(prefix + ".weight_packed")
             g = self.get(prefix + ".weight_global_scale").float().reshape(-1)

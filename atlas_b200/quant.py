@@ -145,3 +145,73 @@ def quant_kv_fp8(x: torch.Tensor, scale: float) -> torch.Tensor:
 def f32_to_bf16_rne(x: torch.Tensor) -> torch.Tensor:
     """Round-to-nearest-even fp32 -> bf16 (what every kernel epilogue does)."""
     return x.to(torch.bfloat16)
+
+
+# ----------------------------------------------------------------------------- MXFP4 (OCP microscaling: 32 e2m1 values, e8m0 scale)
+def dequantize_mxfp4(blocks: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """``blocks [..., K/32, 16]`` uint8 (two e2m1 codes per byte, low nibble first), ``scales [..., K/32]`` uint8 e8m0
+    (value ``2 ** (s - 127)``) -> fp32 ``[..., K]``."""
+    lut = _e2m1_lut(blocks.device)
+    lo, hi = lut[(blocks & 0xF).long()], lut[(blocks >> 4).long()]
+    vals = torch.stack([lo, hi], -1).reshape(*blocks.shape[:-1], 32)
+    sc = torch.exp2(scales.to(torch.float32) - 127.0)
+    return (vals * sc[..., None]).reshape(*blocks.shape[:-2], -1)
+
+
+def quantize_mxfp4(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``w [N, K]`` -> (blocks ``[N, K/32, 16]`` uint8, scales ``[N, K/32]`` uint8 e8m0): power-of-two scale per 32 values
+    chosen so the block maximum fits under 6 (the e2m1 maximum)."""
+    N, K = w.shape
+    g = w.float().view(N, K // 32, 32)
+    amax = g.abs().amax(-1).clamp_min(2.0 ** -126)
+    e = torch.ceil(torch.log2(amax / E2M1_MAX)).clamp(-127, 127)
+    codes = _round_to_e2m1_code(g / torch.exp2(e)[..., None]).view(N, K // 32, 32)
+    blocks = (codes[..., 0::2] | (codes[..., 1::2] << 4)).contiguous()
+    return blocks, (e + 127).to(torch.uint8)
+
+
+def mxfp4_to_nvfp4(blocks: torch.Tensor, scales: torch.Tensor):
+    """Re-express MXFP4 ``[N, K/32, 16] + [N, K/32]`` in the NVFP4 layout this engine's kernels read: the codes are the
+    same e2m1 values; each 32-block scale becomes two 16-block e4m3 scales against one global power of two.  Exact when
+    the scales of the tensor span at most the 17 binades e4m3 holds exactly (2**-9 .. 2**8); returns None otherwise
+    (the caller widens to 16 bits instead)."""
+    N = blocks.shape[0]
+    e = scales.to(torch.int32) - 127
+    live = e[scales > 0] if bool((scales > 0).any()) else e
+    lo, hi = int(live.min()), int(live.max())
+    if hi - lo > 17:
+        return None
+    shift = hi - 8                                        # the largest scale maps to 2**8
+    rel = (e - shift).clamp(-9, 8)
+    s16 = torch.exp2(rel.float()).to(FP8)                 # powers of two in range are exact in e4m3
+    s16 = torch.where((scales == 0) & (e < lo), torch.zeros_like(s16.float()).to(FP8), s16)
+    packed = blocks.reshape(N, -1).contiguous()
+    return packed, s16.repeat_interleave(2, dim=-1).contiguous(), torch.tensor([2.0 ** shift], dtype=torch.float32)
+
+
+# ----------------------------------------------------------------------------- MLX affine group quantisation
+def dequantize_mlx(weight: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, bits: int, group_size: int) -> torch.Tensor:
+    """``weight [N, K * bits / 32]`` uint32 (values packed little-endian inside each word), ``scales`` / ``biases``
+    ``[N, K / group_size]`` -> fp32 ``[N, K]`` with ``w = q * scale + bias``."""
+    N = weight.shape[0]
+    per = 32 // bits
+    w = weight.to(torch.int64) & 0xFFFFFFFF
+    shifts = torch.arange(per, device=weight.device, dtype=torch.int64) * bits
+    q = ((w[..., None] >> shifts) & ((1 << bits) - 1)).reshape(N, -1).float()
+    K = q.shape[1]
+    s = scales.float().repeat_interleave(group_size, 1)[:, :K]
+    b = biases.float().repeat_interleave(group_size, 1)[:, :K]
+    return q * s + b
+
+
+def quantize_mlx(w: torch.Tensor, bits: int = 4, group_size: int = 64):
+    N, K = w.shape
+    g = w.float().view(N, K // group_size, group_size)
+    mn, mx = g.amin(-1), g.amax(-1)
+    scale = ((mx - mn) / ((1 << bits) - 1)).clamp_min(1e-12)
+    q = torch.round((g - mn[..., None]) / scale[..., None]).clamp(0, (1 << bits) - 1).to(torch.int64).view(N, K)
+    per = 32 // bits
+    shifts = torch.arange(per, dtype=torch.int64) * bits
+    packed = (q.view(N, K // per, per) << shifts).sum(-1)
+    packed = torch.where(packed >= (1 << 31), packed - (1 << 32), packed).to(torch.int32)
+    return packed, scale, mn

@@ -305,3 +305,47 @@ def test_multimodal_logits_match_transformers(tmp_path):
         ref_out.append(nxt)
         seq.append(nxt)
     assert out == ref_out
+
+
+@pytest.mark.parametrize("fmt", ["mxfp4", "mlx4", "mlx8"])
+def test_other_weight_containers(fmt, tmp_path):
+    """MXFP4 (32-value e2m1 blocks + e8m0 scales) and MLX affine group quantisation: a checkpoint rewritten in the
+    container loads and reproduces the logits of the same weights dequantised by hand."""
+    from safetensors.torch import load_file, save_file
+    hf = _hf("llama")
+    src = _save(hf, tmp_path / "src")
+    tensors = load_file(os.path.join(src, "model.safetensors"))
+    out, deq = {}, {}
+    for name, t in tensors.items():
+        if not (name.endswith("_proj.weight") and t.dim() == 2):
+            out[name] = deq[name] = t
+            continue
+        base = name[:-len(".weight")]
+        if fmt == "mxfp4":
+            b, sc = Q.quantize_mxfp4(t.float())
+            out[base + ".weight_blocks"], out[base + ".weight_scales"] = b, sc
+            deq[name] = Q.dequantize_mxfp4(b, sc)
+        else:
+            bits = 4 if fmt == "mlx4" else 8
+            w, sc, bi = Q.quantize_mlx(t.float(), bits, 64)
+            out[name], out[base + ".scales"], out[base + ".biases"] = w, sc, bi
+            deq[name] = Q.dequantize_mlx(w, sc, bi, bits, 64)
+            assert float((deq[name] - t.float()).abs().max()) < (0.02 if bits == 4 else 0.002)
+    dst = tmp_path / fmt
+    os.makedirs(dst)
+    save_file({k: v.contiguous() for k, v in out.items()}, os.path.join(dst, "model.safetensors"))
+    cfg = json.load(open(os.path.join(src, "config.json")))
+    if fmt == "mxfp4":
+        cfg["quantization_config"] = {"quant_method": "mxfp4"}
+    else:
+        cfg["quantization"] = {"group_size": 64, "bits": 4 if fmt == "mlx4" else 8}
+    json.dump(cfg, open(os.path.join(dst, "config.json"), "w"))
+    model = load_model(str(dst), dtype="float32", with_mtp=False)
+    if fmt == "mxfp4":
+        assert model.layers[0].mixer.qkv.kind == "nvfp4"            # kept in 4 bits, on the NVFP4 kernels' layout
+    toks = torch.randint(0, 512, (20,), generator=torch.Generator().manual_seed(7)).tolist()
+    got = _ours_logits(model, toks)
+    hf.load_state_dict({k: v.to(torch.float32) for k, v in deq.items()})
+    with torch.no_grad():
+        want = hf(torch.tensor([toks])).logits[0]
+    torch.testing.assert_close(got, want, atol=2e-3 if fmt == "mlx4" else 5e-4, rtol=1e-3)
