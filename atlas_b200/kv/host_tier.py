@@ -3,9 +3,10 @@ recurrent state) in pinned host memory instead of recomputing its whole context 
 
 The scheduler owns the bookkeeping (which sequence holds which host blocks) through the small allocator interface of
 :class:`HostKVTier` (``num_free`` / ``alloc`` / ``free``); the engine performs the copies it lists in
-``SchedulerOutput.swap_out`` / ``swap_in`` on the compute stream before the step's forward pass, swap-outs first, so a
-device block that changes hands inside one step is saved before its new owner writes it, and host blocks are only
-returned to the free list after the copy that reads them has been issued.
+``SchedulerOutput.swap_out`` / ``swap_in`` before the step's forward pass, swap-outs first, so a device block that
+changes hands inside one step is saved before its new owner writes it, and host blocks are only returned to the free
+list after the copy that reads them has been issued.  The copies themselves run on the tier's own stream (see
+:class:`HostKVTier`); the step only waits for the on-device gather / scatter, not for the PCIe transfers.
 
 Sized by ``--swap-space-gb``.  Reference behaviour replaced: ``crates/spark-runtime/src/kv_host_tier/`` (arena + restore),
 ``crates/spark-server/src/scheduler/preempt.rs`` and ``restore_queue.rs`` (swap instead of recompute, parked restores).
@@ -77,25 +78,42 @@ class DiskKVTier:
 
 
 class HostKVTier:
+    """Pinned host pool of fixed-size records: record ``hb`` holds one KV block of every layer (K then V, layer after
+    layer, the logical ``[block, head, dim]`` order of the pool views).
+
+    Copies run on a dedicated CUDA stream and never block the host: a swap-out gathers the blocks of each layer into one
+    device staging matrix (a handful of indexing kernels ordered after the compute stream by an event), then issues one
+    device-to-host copy per record; the compute stream waits for the gather only, so the freed device blocks can be
+    rewritten while the records are still travelling.  A swap-in is the mirror image (host-to-device copies into
+    staging, scatter kernels, the compute stream waits for the scatter).  The single copy stream orders every use of a
+    host record; the CPU only waits (``drain``) before it reads or writes records itself for the file tier."""
+
     def __init__(self, cache, num_host_blocks: int, num_state_slots: int = 0, disk_gb: float = 0.0, disk_dir: str = ""):
         self.cache = cache
         self.num_blocks = int(num_host_blocks)
         self._free: List[int] = list(range(self.num_blocks - 1, -1, -1))
-        pin = any(k.is_cuda for k, _ in cache.kv.values())
-        self.k: Dict[int, torch.Tensor] = {}
-        self.v: Dict[int, torch.Tensor] = {}
+        self.on_gpu = any(k.is_cuda for k, _ in cache.kv.values())
+        self.device = next((k.device for k, _ in cache.kv.values()), torch.device("cpu"))
+        # (layer, which, byte offset, bytes) of every slice of a record
+        self.layout: List[tuple] = []
+        off = 0
         for l, (k, v) in cache.kv.items():
-            self.k[l] = torch.empty((self.num_blocks,) + tuple(k.shape[1:]), dtype=k.dtype, pin_memory=pin)
-            self.v[l] = torch.empty((self.num_blocks,) + tuple(v.shape[1:]), dtype=v.dtype, pin_memory=pin)
+            for which, t in (("k", k), ("v", v)):
+                n = t[0].numel() * t.element_size()
+                self.layout.append((l, which, off, n))
+                off += n
+        self.record_bytes = off
+        self.pool = torch.empty(self.num_blocks, max(1, self.record_bytes), dtype=torch.uint8, pin_memory=self.on_gpu)
         self.num_state_slots = int(num_state_slots) if cache.states else 0
         self._free_states: List[int] = list(range(self.num_state_slots - 1, -1, -1))
         self.states: Dict[int, Dict[str, torch.Tensor]] = {}
         for l, st in cache.states.items():
-            self.states[l] = {name: torch.empty((self.num_state_slots,) + tuple(t.shape[1:]), dtype=t.dtype, pin_memory=pin)
+            self.states[l] = {name: torch.empty((self.num_state_slots,) + tuple(t.shape[1:]), dtype=t.dtype, pin_memory=self.on_gpu)
                               for name, t in st.items() if name in ("conv", "h")}
+        self.stream = torch.cuda.Stream(device=self.device) if self.on_gpu else None
+        self._staging: Optional[torch.Tensor] = None
         self.blocks_out = 0
         self.blocks_in = 0
-        self.record_bytes = sum(k[0].numel() * k.element_size() + v[0].numel() * v.element_size() for k, v in cache.kv.values())
         self.disk: Optional[DiskKVTier] = None
         if disk_gb > 0 and self.record_bytes > 0:
             n_rec = int(disk_gb * (1 << 30)) // self.record_bytes
@@ -126,54 +144,101 @@ class HostKVTier:
         if slot is not None:
             self._free_states.append(slot)
 
+    def drain(self) -> None:
+        """Wait until every issued copy has landed (before the CPU touches records)."""
+        if self.stream is not None:
+            self.stream.synchronize()
+
     # ------------------------------------------------------------------ host <-> disk (engine side)
     def spill(self, host_blocks: List[int], disk_records: List[int]) -> None:
-        """Host blocks -> disk records (the host blocks are free again afterwards; the scheduler accounts for that)."""
+        """Host records -> disk records (the host blocks are free again afterwards; the scheduler accounts for that)."""
+        self.drain()
         for hb, rec in zip(host_blocks, disk_records):
-            parts = []
-            for l in self.k:
-                parts.append(_raw(self.k[l][hb]).contiguous().view(torch.uint8).numpy().tobytes())
-                parts.append(_raw(self.v[l][hb]).contiguous().view(torch.uint8).numpy().tobytes())
-            self.disk.write(rec, b"".join(parts))
+            self.disk.write(rec, self.pool[hb].numpy().tobytes())
 
     def unspill(self, disk_records: List[int], host_blocks: List[int]) -> None:
+        self.drain()
         for rec, hb in zip(disk_records, host_blocks):
-            data = memoryview(self.disk.read(rec))
-            off = 0
-            for l in self.k:
-                for t in (self.k[l], self.v[l]):
-                    n = t[hb].numel() * t.element_size()
-                    flat = torch.frombuffer(bytearray(data[off:off + n]), dtype=torch.uint8)
-                    t[hb].view(torch.uint8).reshape(-1).copy_(flat)
-                    off += n
+            self.pool[hb].copy_(torch.frombuffer(bytearray(self.disk.read(rec)), dtype=torch.uint8))
 
     # ------------------------------------------------------------------ copies (engine side)
+    def _stage(self, n: int) -> torch.Tensor:
+        if self._staging is None or self._staging.shape[0] < n:
+            self._staging = torch.empty(max(n, 64), self.record_bytes, dtype=torch.uint8, device=self.device)
+        return self._staging[:n]
+
+    def _tensor(self, l: int, which: str) -> torch.Tensor:
+        k, v = self.cache.kv[l]
+        return k if which == "k" else v
+
     def copy_out(self, dev_blocks: List[int], host_blocks: List[int], state_slot: Optional[int] = None,
                  host_state: Optional[int] = None) -> None:
         assert len(dev_blocks) == len(host_blocks)
-        if dev_blocks:
-            hb = torch.tensor(host_blocks, dtype=torch.int64)
-            for l, (k, v) in self.cache.kv.items():
-                db = torch.tensor(dev_blocks, dtype=torch.int64, device=k.device)
-                _raw(self.k[l])[hb] = _raw(k).index_select(0, db).to("cpu")
-                _raw(self.v[l])[hb] = _raw(v).index_select(0, db).to("cpu")
-            self.blocks_out += len(dev_blocks)
-        if host_state is not None and state_slot is not None:
-            for l, st in self.cache.states.items():
-                for name, host in self.states[l].items():
-                    host[host_state].copy_(st[name][state_slot])
+        n = len(dev_blocks)
+        if self.on_gpu:
+            cur = torch.cuda.current_stream(self.device)
+            self.stream.wait_stream(cur)                      # the blocks' last writers have been issued on `cur`
+            with torch.cuda.stream(self.stream):
+                if n:
+                    db = torch.tensor(dev_blocks, dtype=torch.int64).pin_memory().to(self.device, non_blocking=True)
+                    st = self._stage(n)
+                    for l, which, off, nbytes in self.layout:
+                        t = self._tensor(l, which)
+                        st[:, off:off + nbytes] = _raw(t).index_select(0, db).reshape(n, -1).view(torch.uint8)
+                gathered = torch.cuda.Event()
+                gathered.record(self.stream)
+                for i, hb in enumerate(host_blocks):
+                    self.pool[hb].copy_(st[i], non_blocking=True)
+                if host_state is not None and state_slot is not None:
+                    for l, stt in self.cache.states.items():
+                        for name, host in self.states[l].items():
+                            host[host_state].copy_(stt[name][state_slot], non_blocking=True)
+                    gathered = torch.cuda.Event()
+                    gathered.record(self.stream)
+            cur.wait_event(gathered)                          # device blocks / state slot may be rewritten after this
+        else:
+            for i, (dbk, hb) in enumerate(zip(dev_blocks, host_blocks)):
+                for l, which, off, nbytes in self.layout:
+                    blk = self._tensor(l, which)[dbk].contiguous()
+                    self.pool[hb, off:off + nbytes] = _raw(blk).reshape(-1).view(torch.uint8)
+            if host_state is not None and state_slot is not None:
+                for l, stt in self.cache.states.items():
+                    for name, host in self.states[l].items():
+                        host[host_state].copy_(stt[name][state_slot])
+        self.blocks_out += n
 
     def copy_in(self, host_blocks: List[int], dev_blocks: List[int], host_state: Optional[int] = None,
                 state_slot: Optional[int] = None) -> None:
         assert len(dev_blocks) == len(host_blocks)
-        if dev_blocks:
-            hb = torch.tensor(host_blocks, dtype=torch.int64)
-            for l, (k, v) in self.cache.kv.items():
-                db = torch.tensor(dev_blocks, dtype=torch.int64, device=k.device)
-                _raw(k).index_copy_(0, db, _raw(self.k[l])[hb].to(k.device))
-                _raw(v).index_copy_(0, db, _raw(self.v[l])[hb].to(v.device))
-            self.blocks_in += len(dev_blocks)
-        if host_state is not None and state_slot is not None:
-            for l, st in self.cache.states.items():
-                for name, host in self.states[l].items():
-                    st[name][state_slot].copy_(host[host_state], non_blocking=True)
+        n = len(dev_blocks)
+        if self.on_gpu:
+            cur = torch.cuda.current_stream(self.device)
+            self.stream.wait_stream(cur)                      # earlier readers of the destination blocks are on `cur`
+            with torch.cuda.stream(self.stream):
+                if n:
+                    db = torch.tensor(dev_blocks, dtype=torch.int64).pin_memory().to(self.device, non_blocking=True)
+                    st = self._stage(n)
+                    for i, hb in enumerate(host_blocks):
+                        st[i].copy_(self.pool[hb], non_blocking=True)
+                    for l, which, off, nbytes in self.layout:
+                        t = self._tensor(l, which)
+                        src = st[:, off:off + nbytes].contiguous().view(_raw(t).dtype).view((n,) + tuple(t.shape[1:]))
+                        _raw(t).index_copy_(0, db, src)
+                if host_state is not None and state_slot is not None:
+                    for l, stt in self.cache.states.items():
+                        for name, host in self.states[l].items():
+                            stt[name][state_slot].copy_(host[host_state], non_blocking=True)
+                done = torch.cuda.Event()
+                done.record(self.stream)
+            cur.wait_event(done)
+        else:
+            for hb, dbk in zip(host_blocks, dev_blocks):
+                for l, which, off, nbytes in self.layout:
+                    t = self._tensor(l, which)
+                    src = self.pool[hb, off:off + nbytes].clone().view(_raw(t).dtype).view(tuple(t.shape[1:]))
+                    _raw(t)[dbk] = src
+            if host_state is not None and state_slot is not None:
+                for l, stt in self.cache.states.items():
+                    for name, host in self.states[l].items():
+                        stt[name][state_slot].copy_(host[host_state])
+        self.blocks_in += n
