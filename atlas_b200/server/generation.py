@@ -20,7 +20,7 @@ from .grammar import GrammarSpec
 from .reasoning import ReasoningSplitter, ThinkingBudget
 from .loop_detector import LoopDetector
 from .compaction import compact_messages
-from .sanitizer import guarded_stops
+from .sanitizer import ContentSanitizer, StreamGuards, guarded_stops
 from .tokenizer import IncrementalDetokenizer, render_chat
 from .tool_parsers import StreamingToolParser, ToolCall, get_parser, dedupe_calls
 
@@ -221,6 +221,18 @@ class Generator:
         if req.echo and prompt_text:
             yield GenDelta(content=prompt_text)
 
+        sanitize = not s.args.get("no_output_sanitizer")
+        content_filter = ContentSanitizer() if sanitize else None
+        guards = StreamGuards() if sanitize else None
+
+        def clean(c: str) -> str:
+            """Content channel only: leftover markup out, repetition watchdog fed with what the client will see."""
+            if content_filter is not None and c:
+                c = content_filter.feed(c)
+            if guards is not None and c:
+                guards.on_text(c)
+            return c
+
         def route(text: str) -> GenDelta:
             d = GenDelta()
             if not text:
@@ -228,7 +240,7 @@ class Generator:
             r, c = (reasoning.push(text) if reasoning else ("", text))
             d.reasoning = r
             if c:
-                d.content = tool_stream.push(c) if tool_stream else c
+                d.content = clean(tool_stream.push(c) if tool_stream else c)
             return d
 
         async for ev in gen_iter:
@@ -258,6 +270,8 @@ class Generator:
                 d.token_ids, d.logprobs = list(ev.tokens), ev.logprobs
                 if d.content or d.reasoning or d.token_ids:
                     yield d
+                if guards is not None and guards.tripped and not stopped:
+                    stopped = True                      # the visible text started to loop: end the turn here
                 if stopped:
                     s.engine.abort("req-" + req.request_id)
                     break
@@ -270,14 +284,18 @@ class Generator:
             r2, c2 = reasoning.finish()
             d.reasoning += r2
             if c2:
-                d.content += tool_stream.push(c2) if tool_stream else c2
+                d.content += clean(tool_stream.push(c2) if tool_stream else c2)
         calls: List[ToolCall] = []
         if tool_stream:
             rest, calls = tool_stream.finish()
             calls = dedupe_calls(calls)
-            d.content += rest
+            d.content += clean(rest)
             if calls and not req.parallel_tool_calls:
                 calls = calls[:1]
+            if guards is not None and len(calls) > guards.max_tool_calls:
+                calls = calls[:guards.max_tool_calls]    # a response with dozens of calls is a failure mode, not a plan
+        if content_filter is not None:
+            d.content += content_filter.flush()
         d.tool_calls = calls
         reason = "stop" if stopped else (final.finish_reason if final else "stop")
         if calls:

@@ -252,3 +252,37 @@ def test_image_parts_are_decoded_patchified_and_placeholders_widened():
         expand_placeholders([1, 2], 500, [4])
     with pytest.raises(ImageError):
         extract_images([{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "https://example.com/x.png"}}]}])
+
+
+def test_output_sanitizer_rules():
+    """Streaming content filter (markers split across chunks, suppressed envelopes, held tails), the complete-string
+    scrubbers and the per-response guards."""
+    from atlas_b200.server.sanitizer import (ContentSanitizer, StreamGuards, marker_prefix_hold, scrub_think_markers,
+                                             scrub_tool_tags, strip_orphan_tool_markup, DEFAULT_MARKERS)
+    s = ContentSanitizer()
+    chunks = ["Hello <to", 'ol_call>{"name": 1}</tool', "_call> world </thi", "nk>  done <func", "tion=foo> x </function> y <"]
+    shown = [s.feed(c) for c in chunks]
+    assert shown[0] == "Hello " and "".join(shown) + s.flush() == "Hello  world done  x  y "
+    # every prefix of the stream: nothing that later turns out to be markup is ever shown
+    text = 'ok <tool_call>{"a": 1}</tool_call> fine'
+    for cut in range(1, len(text)):
+        f = ContentSanitizer()
+        assert f.feed(text[:cut]) + f.feed(text[cut:]) + f.flush() == "ok  fine", cut
+    f = ContentSanitizer()
+    assert f.feed("text <tool_call>{never closed") == "text " and f.flush() == "" and f.dropped > 0
+    f = ContentSanitizer()
+    assert f.feed("a < b and c <") == "a < b and c " and f.flush() == ""        # a lone "<" could start a tag: held, then dropped
+    f = ContentSanitizer()
+    assert f.feed("1 <= 2") + f.flush() == "1 <= 2"
+    assert marker_prefix_hold("abc</tool", DEFAULT_MARKERS.all) == 6 and marker_prefix_hold("abc", DEFAULT_MARKERS.all) == 0
+    assert scrub_tool_tags("a<function=x>b</function>c<parameter=q") == "abc"
+    assert scrub_think_markers("391.</think>  17 x 23") == "391.17 x 23"
+    assert strip_orphan_tool_markup('the story."<tool_call>catch({})') == 'the story."'
+    g = StreamGuards()
+    line = "The quick brown fox jumps.\n"
+    assert not any(g.on_text(line) for _ in range(3)) and g.on_text(line) and g.tripped == "repeated_line"
+    g = StreamGuards()
+    assert not any(g.on_tool_call() for _ in range(12)) and g.on_tool_call() and g.tripped == "tool_call_cap"
+    g = StreamGuards()
+    assert not g.on_text("a perfectly ordinary paragraph without any repetition in it at all, just prose.")
+    assert g.on_text(" and again the same thirty-something characters" * 4) and g.tripped == "repeated_phrase"
