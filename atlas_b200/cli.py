@@ -32,6 +32,9 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--max-seq-len", type=int, default=32768)
     s.add_argument("--block-size", type=int, default=16)
     s.add_argument("--kv-cache-dtype", default="fp8", choices=["auto", "fp8", "bf16"])
+    s.add_argument("--sparse-attention-blocks", type=int, default=0,
+                   help="long contexts: decode attention reads at most this many KV blocks per sequence, chosen by a "
+                        "block predictor (first and most recent blocks always kept); 0 = dense attention")
     s.add_argument("--dcut-ratio", type=float, default=0.0,
                    help="speculative decoding: verify only this fraction of the draft rows (0.25 / 0.5 / 0.75), chosen by drafter confidence")
     s.add_argument("--kv-high-precision-layers", default="",
@@ -133,6 +136,7 @@ def _engine_config(args, mcfg):
     prefix = args.enable_prefix_caching if args.enable_prefix_caching is not None else True
     return EngineConfig(max_seq_len=min(args.max_seq_len, max(mcfg.max_position_embeddings, 1)), block_size=args.block_size,
                         kv_cache_dtype=args.kv_cache_dtype, dcut_ratio=args.dcut_ratio,
+                        sparse_attention_blocks=args.sparse_attention_blocks,
                         kv_high_precision_layers=tuple(int(v) for v in args.kv_high_precision_layers.split(",") if v.strip()),
                         gpu_memory_utilization=args.gpu_memory_utilization,
                         num_kv_blocks=args.num_kv_blocks, max_num_seqs=args.max_num_seqs, max_batch_size=args.max_batch_size,

@@ -494,6 +494,7 @@ class EngineConfig:
     max_seq_len: int = 32768
     block_size: int = 16
     kv_cache_dtype: str = "auto"
+    sparse_attention_blocks: int = 0          # > 0: decode attention reads at most this many KV blocks per sequence
     async_decode: bool = True                 # lag-one decode pipeline for plain greedy decode steps (GPU, CUDA graphs)
     kv_high_precision_layers: tuple = ()      # attention layers that keep a 16-bit cache when kv_cache_dtype is fp8
     gpu_memory_utilization: float = 0.90

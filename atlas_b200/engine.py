@@ -75,6 +75,14 @@ class LLMEngine:
             if n_host > 0:
                 self.host_tier = HostKVTier(self.cache, n_host, self.cfg.max_num_seqs if self.hybrid else 0,
                                             disk_gb=self.cfg.disk_swap_gb, disk_dir=self.cfg.disk_swap_path)
+        self.selector = None
+        if self.cfg.sparse_attention_blocks > 0:
+            from .kv.sparse_select import BlockSelector
+            from .layers import Attention
+            self.selector = BlockSelector(num_blocks, self.cfg.block_size, self.cfg.sparse_attention_blocks)
+            for l in model.layers:
+                if l.kind == "attention" and type(l.mixer) is Attention:
+                    l.mixer.selector = self.selector
         self.scheduler = Scheduler(self.cfg, self.pool, self.radix, self.state_pool, self.hybrid, host_tier=self.host_tier)
         self.sampler = Sampler(self.mcfg.vocab_size, self.mcfg.eos_ids())
         # largest step this engine can build: sizes the sequence-parallel peer-memory area once

@@ -41,6 +41,7 @@ class Attention:
         self.q_norm: Optional[torch.Tensor] = None
         self.k_norm: Optional[torch.Tensor] = None
         self.lora = None                    # lora.LoraSet shared by the model's layers
+        self.selector = None                # kv.sparse_select.BlockSelector: block-selected decode attention (long contexts)
 
     # ------------------------------------------------------------------ weights
     def _kv_slice(self, w: torch.Tensor) -> torch.Tensor:
@@ -111,7 +112,13 @@ class Attention:
         q = ops.qk_norm_rope_kv_write(q, k, v, rope_pos, rope_cache, cfg.rotary_dim, k_cache, v_cache,
                                       batch.slot_mapping, k_scale, v_scale, self.q_norm, self.k_norm,
                                       cfg.rms_norm_eps, cfg.norm_plus_one)
-        out = ops.paged_attention(q, k_cache, v_cache, batch, self.scale, k_scale, v_scale, self.window)
+        if self.selector is not None:
+            from ..kv.sparse_select import attend_selected
+            self.selector.on_write(self.layer_idx, k_cache, batch, k_scale)
+            out = attend_selected(ops.paged_attention, self.selector, self.layer_idx, q, k_cache, v_cache, batch, self.scale,
+                                  k_scale, v_scale, self.window)
+        else:
+            out = ops.paged_attention(q, k_cache, v_cache, batch, self.scale, k_scale, v_scale, self.window)
         out = out.reshape(T, nq)
         if self.gated:
             gate = qkv[:, nq + 2 * nkv:]

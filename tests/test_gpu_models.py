@@ -419,3 +419,28 @@ def test_checked_mode_passes_clean_steps_and_names_a_bad_index(K, monkeypatch):
         model.embed_tokens(torch.tensor([5000], device=DEV))
     torch.cuda.synchronize()
     assert K.check_status() == 0
+
+
+def test_block_selected_decode_attention_on_gpu(K):
+    """The block selector in front of the FP8 decode kernel (inside the captured decode graph): identical tokens while
+    every sequence fits the budget, bounded attention length beyond it."""
+    cfg = ModelConfig(model_type="llama", family="dense", vocab_size=4096, hidden_size=1024, intermediate_size=2048,
+                      num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2, head_dim=128, rope_theta=5e5,
+                      max_position_embeddings=2048, quant=QuantConfig(method="fp8_block", kv_cache_dtype="fp8"))
+    model = build_model(cfg, device=DEV).init_random(0)
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(0, 4096, (n,), generator=g).tolist() for n in (200, 90, 150)]
+    sp = SamplingParams(max_tokens=12, ignore_eos=True)
+    ecfg = dict(num_kv_blocks=256, max_num_seqs=8, max_seq_len=512, max_prefill_tokens=256, enable_prefix_caching=False)
+    dense = LLMEngine(model, EngineConfig(**ecfg)).generate(prompts, sp)
+    wide = LLMEngine(model, EngineConfig(sparse_attention_blocks=32, **ecfg))
+    out = wide.generate(prompts, sp)
+    torch.cuda.synchronize()
+    assert K.check_status() == 0
+    assert [o.output_tokens for o in out] == [o.output_tokens for o in dense]
+    narrow = LLMEngine(model, EngineConfig(sparse_attention_blocks=6, **ecfg))
+    out2 = narrow.generate(prompts, sp)
+    torch.cuda.synchronize()
+    assert K.check_status() == 0 and all(len(o.output_tokens) == 12 for o in out2)
+    for l in model.layers:
+        l.mixer.selector = None
