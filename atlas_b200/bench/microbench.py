@@ -209,6 +209,92 @@ def run(model: str = "llama3-8b", decode_batch: int = 128, ctx: int = 1152, chun
             note=f"block_n={bn} splits={sp} (eager launch)")
         return rows
 
+    if only == "stream":
+        # What the memory system gives a weight stream on its own (csrc/stream_probe.cu): tile copies through a ring, nothing
+        # else, in the [N, K] weight layout (a tile's rows one leading dimension apart) and packed tile by tile.
+        import ctypes as C
+        L = K.lib()
+        L.atlas_probe_tma_stream.argtypes = [C.c_void_p, C.c_longlong] + [C.c_int] * 7 + [C.c_void_p, C.c_void_p, C.c_void_p]
+        sink = torch.zeros(1, dtype=torch.int64, device=dev)
+        buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        buf.random_(0, 255)
+        K._dev(buf)
+        for box, stages, tiles, kbs, ctas, pieces in ((64, 8, 96, 32, 96, 1), (64, 8, 148, 32, 148, 1), (64, 8, 148, 32, 148, 4),
+                                                      (128, 6, 128, 32, 128, 1), (128, 6, 128, 32, 128, 4), (128, 6, 148, 32, 148, 1),
+                                                      (128, 6, 148, 32, 148, 4), (128, 6, 148, 32, 148, 8), (128, 12, 148, 32, 148, 1),
+                                                      (256, 4, 112, 32, 112, 1), (256, 4, 112, 32, 112, 8), (256, 6, 148, 32, 148, 1),
+                                                      (256, 6, 148, 32, 148, 8), (128, 6, 148, 112, 148, 1), (128, 6, 148, 112, 148, 4),
+                                                      # two and three CTAs per SM (the ring shrinks to fit)
+                                                      (128, 6, 296, 32, 296, 1), (64, 8, 296, 32, 296, 1), (64, 8, 444, 32, 444, 1),
+                                                      (128, 6, 296, 48, 296, 1), (64, 6, 592, 48, 592, 1)):
+            nbytes = tiles * kbs * box * 128
+            assert nbytes <= buf.numel()
+            for packed in (0, 1):
+                def fn():
+                    rc = L.atlas_probe_tma_stream(buf.data_ptr(), buf.numel(), tiles, kbs, box, stages, packed, ctas, pieces, K._status_ptr[0],
+                                                  sink.data_ptr(), K._stream())
+                    assert rc == 0, rc
+                ms = T.time(fn, iters=5)
+                add(f"tma_stream slot={box}x128B in {pieces} copies, stages={stages} ctas={ctas} k_slices={kbs} layout={'packed' if packed else 'weight'}",
+                    ms, bytes_=nbytes, note=f"{stages * box * 128 // 1024} KB in flight per CTA")
+        assert K.check_status() == 0
+        return rows
+
+    if only and only.startswith("timeline"):
+        # Where the time goes INSIDE one decode-size FP8 GEMM launch: every CTA stamps its phases (GemmParams::timeline),
+        # one traced launch per shape after warm-up, cold L2.  only = "timeline" or "timeline:<M>,<M>,..."
+        import ctypes as C
+        import statistics as st
+        ms_list = [int(v) for v in only.split(":")[1].split(",")] if ":" in only else [1, decode_batch]
+        L = K.lib()
+        L.atlas_gemm_set_timeline.argtypes = [C.c_void_p]
+        L.atlas_gemm_set_timeline.restype = None
+        tbuf = torch.zeros(160, 32, dtype=torch.int64, device=dev)
+        phases = [("prologue", 1, 2), ("wait_prev_kernel", 2, 3), ("first_issue", 3, 4), ("first_tile_lands", 4, 5),
+                  ("mma_first_to_last", 5, 6), ("last_fold_after_last_mma", 6, 8),
+                  ("splitk_exchange", 8, 9), ("final_epilogue", 9, 10), ("teardown", 10, 11), ("whole_cta", 1, 11),
+                  ("cluster_send", 9, 19), ("cluster_barrier", 19, 20), ("cluster_sum", 20, 21), ("cluster_store", 21, 10)]
+        for M in ms_list:
+            x = torch.randn(M, max(H, I), device=dev).bfloat16()
+            for name, N, Kd in gemms:
+                wq, ws = Q.quantize_fp8_block(torch.randn(N, Kd, device=dev) * 0.02)
+                xq, xs = K.quant_fp8(x[:, :Kd].contiguous())
+                res = torch.randn(M, N, device=dev).bfloat16()
+                nw = torch.ones(N, device=dev).bfloat16()
+                mode = 1 if name == "gate_up" else (2 if name in ("o", "down") else 0)
+                fn = (lambda: K.gemm_fp8_fused(xq, xs, wq, ws, mode=mode, residual=res if mode == 2 else None,
+                                               norm_w=nw if mode == 2 else None))
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize()
+                T.flush.fill_(1)
+                tbuf.zero_()
+                torch.cuda.synchronize()
+                L.atlas_gemm_set_timeline(tbuf.data_ptr())
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                L.atlas_gemm_set_timeline(None)
+                t = tbuf.cpu()
+                live = t[t[:, 0] != 0]
+                mhz = [float(r[11] - r[1]) / max(1.0, float(r[12] - r[0])) * 1e3 for r in live if r[12] > r[0]]
+                clk = st.median(mhz) if mhz else 1900.0
+                us = lambda cyc: cyc / clk
+                rec = {"kernel": f"timeline {name} M={M} N={N} K={Kd} mode={mode}", "ctas": int(live.shape[0]),
+                       "event_us": round(e0.elapsed_time(e1) * 1e3, 1),
+                       "span_us": round(float(live[:, 12].max() - live[:, 0].min()) / 1e3, 1),
+                       "entry_skew_us_max": round(float(live[:, 0].max() - live[:, 0].min()) / 1e3, 1), "sm_mhz": round(clk)}
+                for label, a, b in phases:
+                    d = [us(float(r[b] - r[a])) for r in live if r[a] and r[b]]
+                    if d:
+                        rec[label] = [round(st.median(d), 2), round(max(d), 2)]
+                rec["note"] = "phase values are [median, max] microseconds over the CTAs"
+                rows.append(rec)
+                print(json.dumps(rec), flush=True)
+        return rows
+
     if only and "sweep" in only:
         # tile / split-K sweep for the decode-size FP8 GEMMs
         for M in (decode_batch,):

@@ -39,6 +39,10 @@ struct AttnParams {
   float* part_ml;                               // [B, Hq, splits, 2]
   // prefill
   const int* tile_seq; const int* tile_q0; int num_tiles;
+  // decode, D == 128 only: write the output as FP8 with one scale per (row, head) -- a head is one 128-wide quantisation
+  // group of the output projection's A operand -- instead of bf16 `out`.  Scale of (row, head) at s_out[head * s_ld + row].
+  uint8_t* q_out; long long ldqo;
+  float* s_out; long long s_ld;
 };
 
 ATLAS_DEVICE void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -581,6 +585,9 @@ attn_decode_kernel(const AttnParams p, int stages, status_t* status) {
         if (head < G) sm_o[(warp * 8 + head) * D + dim] = o[mt][e];
       }
   }
+  const bool q8 = p.q_out != nullptr && p.num_splits == 1;
+  int* sm_amax = reinterpret_cast<int*>(sm_o + 4 * 8 * D);            // [8] per-head max |output| (float bits, >= 0)
+  if (q8 && threadIdx.x < 8) sm_amax[threadIdx.x] = 0;
   __syncthreads();
   for (int idx = threadIdx.x; idx < G * D; idx += kDecodeThreads) {
     const int r = idx / D, d = idx % D;
@@ -596,7 +603,17 @@ attn_decode_kernel(const AttnParams p, int stages, status_t* status) {
       l += f * sm_l[w * 8 + r];
     }
     const int head = kvh * G + r;
-    if (p.num_splits == 1) {
+    if (q8) {
+      // a warp's 32 consecutive idx lie inside one head (D and the thread count are multiples of 32): the value is
+      // parked in the first warp's slot, which only this thread reads, and the head's maximum is gathered per warp
+      const float inv = l > 0.f ? p.v_scale / l : 0.f;
+      const float v = __bfloat162float(__float2bfloat16_rn(acc * inv));
+      sm_o[r * D + d] = v;
+      float a = fabsf(v);
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, off));
+      if (lane == 0) atomicMax(&sm_amax[r], __float_as_int(a));
+    } else if (p.num_splits == 1) {
       const float inv = l > 0.f ? p.v_scale / l : 0.f;
       p.out[(long long)q_row0 * p.ldo + head * D + d] = __float2bfloat16_rn(acc * inv);
     } else {
@@ -608,12 +625,28 @@ attn_decode_kernel(const AttnParams p, int stages, status_t* status) {
       }
     }
   }
+  if (q8) {
+    __syncthreads();
+    for (int idx = threadIdx.x * 4; idx < G * D; idx += kDecodeThreads * 4) {
+      const int r = idx / D, d = idx % D;
+      const int head = kvh * G + r;
+      const float sc = fmaxf(__int_as_float(sm_amax[r]), 1e-10f) / 448.f;
+      const float inv = __frcp_rn(sc);
+      const float4 v = *reinterpret_cast<const float4*>(sm_o + r * D + d);
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v.x * inv, v.y * inv), __NV_SATFINITE, __NV_E4M3);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v.z * inv, v.w * inv), __NV_SATFINITE, __NV_E4M3);
+      *reinterpret_cast<uint32_t*>(p.q_out + (long long)q_row0 * p.ldqo + head * D + d) = lo | (hi << 16);
+      if (d == 0) p.s_out[(long long)head * p.s_ld + q_row0] = sc;
+    }
+  }
 }
 
 // Merge split partials: grid (Hq, B), D threads.
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   __nv_bfloat16* out, long long ldo, const int* query_start_loc, int seq_base, int Hq,
-                                  int D, int splits, float v_scale) {
+                                  int D, int splits, float v_scale, uint8_t* q_out, long long ldqo, float* s_out,
+                                  long long s_ld) {
+  __shared__ float wmax[8];
   const int head = blockIdx.x, bi = blockIdx.y, d = threadIdx.x;
   const long long base = ((long long)bi * Hq + head) * splits;
   chain_trigger();
@@ -629,7 +662,22 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
   }
   const float inv = l > 0.f ? v_scale / l : 0.f;
   const int row = query_start_loc[seq_base + bi];
-  out[(long long)row * ldo + head * D + d] = __float2bfloat16_rn(acc * inv);
+  if (q_out == nullptr) {
+    out[(long long)row * ldo + head * D + d] = __float2bfloat16_rn(acc * inv);
+    return;
+  }
+  // FP8 output, one scale per (row, head); D == 128 (the block is the quantisation group)
+  const float v = __bfloat162float(__float2bfloat16_rn(acc * inv));
+  float a = fabsf(v);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, off));
+  if ((d & 31) == 0) wmax[d >> 5] = a;
+  __syncthreads();
+  a = fmaxf(fmaxf(wmax[0], wmax[1]), fmaxf(wmax[2], wmax[3]));
+  const float sc = fmaxf(a, 1e-10f) / 448.f;
+  const __nv_fp8_storage_t q = __nv_cvt_float_to_fp8(v * __frcp_rn(sc), __NV_SATFINITE, __NV_E4M3);
+  q_out[(long long)row * ldqo + head * D + d] = q;
+  if (d == 0) s_out[(long long)head * s_ld + row] = sc;
 }
 
 template <int D, int BS>
@@ -638,7 +686,7 @@ static int launch_decode_bs(const AttnParams& p, int B, status_t* status, cudaSt
   int stages = (32 * 1024) / stage_bytes;
   stages = stages > 16 ? 16 : (stages < 4 ? 4 : stages);
   stages = (stages / 4) * 4;                       // block i -> stage i % stages -> warp i % 4
-  const int merge_bytes = (64 + 4 * 8 * D) * (int)sizeof(float);
+  const int merge_bytes = (64 + 4 * 8 * D + 8) * (int)sizeof(float);
   const int ring_bytes = stages * stage_bytes > merge_bytes ? stages * stage_bytes : merge_bytes;
   const int smem = 512 + kBtSmemEntries * 4 + ring_bytes;
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(attn_decode_kernel<D, BS>), smem) != cudaSuccess) return -20;
@@ -647,7 +695,7 @@ static int launch_decode_bs(const AttnParams& p, int B, status_t* status, cudaSt
   if (p.num_splits > 1) {
     dim3 g2(p.Hq, B);
     if (launch_chain(attn_merge_kernel, g2, dim3(D), 0, st, p.part_o, p.part_ml, p.out, p.ldo, p.query_start_loc, p.seq_base,
-                     p.Hq, D, p.num_splits, p.v_scale) != cudaSuccess)
+                     p.Hq, D, p.num_splits, p.v_scale, p.q_out, p.ldqo, p.s_out, p.s_ld) != cudaSuccess)
       return -22;
   }
   return 0;
@@ -684,6 +732,7 @@ static int fill_common(AttnParams& p, const void* q, long long ldq, void* out, l
   p.v_scale = v_scale;
   p.Hq = Hq; p.Hkv = Hkv; p.block_size = block_size; p.window = window;
   p.num_splits = 1; p.part_o = nullptr; p.part_ml = nullptr; p.tile_seq = nullptr; p.tile_q0 = nullptr; p.num_tiles = 0;
+  p.q_out = nullptr; p.ldqo = 0; p.s_out = nullptr; p.s_ld = 0;
   return 0;
 }
 
@@ -708,6 +757,30 @@ extern "C" int atlas_attn_decode(const void* q, long long ldq, void* out, long l
   if (D == 64) return launch_decode<64>(p, B, status, st);
   if (D == 128) return launch_decode<128>(p, B, status, st);
   return launch_decode<256>(p, B, status, st);
+}
+
+// The same with the output written as FP8 [row, Hq * 128] plus one scale per (row, head) in the k-group-major layout the
+// FP8 GEMMs read (scale of (row, head) at s_out[head * s_ld + row]): the activation quantisation in front of the output
+// projection happens where the rows are produced.  head_dim 128 only.  The values are rounded to bf16 before they are
+// quantised, so the result equals quantising the bf16 output of atlas_attn_decode.
+extern "C" int atlas_attn_decode_q8(const void* q, long long ldq, void* q_out, long long ldqo, float* s_out, long long s_ld,
+                                    const void* k_cache, const void* v_cache, const int* block_tables, int bt_ld,
+                                    const int* seq_lens, const int* query_start_loc, int seq_base, int B, float scale,
+                                    float k_scale, float v_scale, int Hq, int Hkv, int block_size, int window,
+                                    int num_splits, float* part_o, float* part_ml, unsigned long long* status, void* stream) {
+  if (B <= 0) return 0;
+  if (!q_out || !s_out || (ldqo % 4) || (reinterpret_cast<uintptr_t>(q_out) & 3)) return -6;
+  AttnParams p;
+  int rc = fill_common(p, q, ldq, nullptr, 0, k_cache, v_cache, block_tables, bt_ld, seq_lens, query_start_loc, seq_base,
+                       scale, k_scale, v_scale, Hq, Hkv, 128, block_size, window);
+  if (rc) return rc;
+  p.q_out = reinterpret_cast<uint8_t*>(q_out); p.ldqo = ldqo; p.s_out = s_out; p.s_ld = s_ld;
+  p.num_splits = num_splits < 1 ? 1 : num_splits;
+  if (p.num_splits > 1 && (!part_o || !part_ml)) return -3;
+  p.part_o = part_o; p.part_ml = part_ml;
+  if (p.block_size * 128 * 2 > 96 * 1024) return -4;
+  if (Hq / Hkv > 8) return -5;
+  return launch_decode<128>(p, B, status, reinterpret_cast<cudaStream_t>(stream));
 }
 
 // Prefill / verify attention: `num_tiles` 16-row query tiles described by (sequence index, first query row of the
@@ -745,7 +818,7 @@ static int launch_kv16(const AttnParams& p, int B, bool prefill, cudaStream_t st
   if (p.num_splits > 1) {
     dim3 g2(p.Hq, B);
     attn_merge_kernel<<<g2, D, 0, st>>>(p.part_o, p.part_ml, p.out, p.ldo, p.query_start_loc, p.seq_base, p.Hq, D, p.num_splits,
-                                       p.v_scale);
+                                       p.v_scale, nullptr, 0, nullptr, 0);
     if (cudaGetLastError() != cudaSuccess) return -22;
   }
   return 0;

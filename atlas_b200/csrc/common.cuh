@@ -269,6 +269,22 @@ ATLAS_DEVICE float warp_max(float v) {
 // chain_wait() blocks until the predecessor grid has completed and its memory operations are visible, so every global
 // memory access of such a kernel comes after it; chain_trigger() lets the next kernel in the stream start launching.
 // A kernel launched the ordinary way is unaffected by either instruction.
+// Thread-block cluster barrier (every thread of every CTA of the cluster takes part, like __syncthreads for the
+// cluster) and a store into the shared memory of another CTA of the cluster.  The arrive has release, the wait acquire
+// semantics at cluster scope, so distributed-shared-memory stores before the arrive are visible after the wait.
+ATLAS_DEVICE void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+ATLAS_DEVICE uint32_t cluster_map_shared(uint32_t local_smem_addr, uint32_t cta_rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(local_smem_addr), "r"(cta_rank));
+  return r;
+}
+ATLAS_DEVICE void st_cluster_f32x4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 ATLAS_DEVICE void chain_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 ATLAS_DEVICE void chain_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
@@ -310,6 +326,26 @@ inline cudaError_t launch_chain_if(bool early, void (*kern)(P...), dim3 grid, di
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = (early && chain_enabled()) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<P>(args)...);
+}
+// The same for a grid of thread-block clusters of `cluster_x` CTAs along x (grid.x a multiple of it).
+template <typename... P, typename... A>
+inline cudaError_t launch_chain_cluster(bool early, unsigned cluster_x, void (*kern)(P...), dim3 grid, dim3 block, size_t smem,
+                                        cudaStream_t st, A... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster_x;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (early && chain_enabled()) ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, kern, static_cast<P>(args)...);
 }
 template <typename... P, typename... A>

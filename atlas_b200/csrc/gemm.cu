@@ -69,6 +69,11 @@ struct GemmParams {
   int m_tiles, n_tiles;
   int b_scale_ld;           // k-groups per row of b_scale
   int vec_ok;               // 16-byte stores into C are legal
+  int cluster_splits;       // > 1: the K splits of a tile are the CTAs of one thread-block cluster (one item per CTA, a
+                            // single m-tile): partials meet in distributed shared memory instead of the workspace and
+                            // every CTA finishes 128 / cluster_splits rows of the tile (see cluster_tail)
+  int a_box_rows;           // rows of A one tile copy carries (8..128): decode-size problems copy only the rows that exist,
+                            // the rest of the 128-row operand slot keeps stale bytes whose output rows are never stored
   // grouped (MoE) mode: rows are expert-sorted and every expert's segment is padded to a multiple of 128 rows, so
   // m-tile i covers rows [128 i, 128 i + 128) and belongs to expert tile_expert[i]; B is the stack [E * expert_n, K].
   // fused all-reduce (row-parallel GEMM): peers' symmetric areas, see the FUSE_AR path of the kernel
@@ -105,6 +110,13 @@ struct GemmParams {
   const __nv_bfloat16* norm_w; int norm_plus_one;
   float* ss_out; long long ss_out_ld;
   const float* ss_in; int ss_in_parts; long long ss_in_ld; float ss_inv_h, ss_eps;
+  // phase trace (nullptr = off): 32 words per CTA; [0] / [12] the global nanosecond timer at entry / exit, the rest SM
+  // cycle counts: [1] entry, [2] barriers + TMEM ready, [3] previous kernel done, [4] first copies issued, [5] first tile
+  // landed, [6] last MMA committed, [8] last fold done, [9] split-K ticket known (cluster form: every CTA of the cluster
+  // past its k loop), [10] output stored, [11] exit; cluster split-K tail: [19] partial rows sent, [20] all partials here,
+  // [21] rows summed.  Nothing is stamped inside the per-slice loops of the epilogue warps: their register budget is
+  // what the fold needs.
+  unsigned long long* timeline;
   const int* tile_expert;       // nullptr = plain GEMM
   const int* num_m_tiles_ptr;   // device-side tile count (the host cannot know it)
   int expert_n;                 // output features per expert
@@ -160,7 +172,137 @@ ATLAS_DEVICE uint64_t pack_f32x2(float lo, float hi) {
   return r;
 }
 
-template <int BLOCK_N, bool FP8, bool FUSE_AR = false, int EPW = epi_warps(BLOCK_N, FP8)>
+// Work item -> (m-tile, n-tile, K split).  Cluster mode: consecutive CTAs are the splits of one n-tile.
+struct ItemPos { int m_tile, n_tile, split; };
+ATLAS_DEVICE ItemPos item_pos(const GemmParams& p, int item, int m_tiles) {
+  ItemPos r;
+  if (p.cluster_splits > 1) {
+    r.m_tile = 0; r.n_tile = item / p.cluster_splits; r.split = item % p.cluster_splits;
+  } else {
+    r.m_tile = item % m_tiles;
+    const int rest = item / m_tiles;
+    r.n_tile = rest % p.n_tiles; r.split = rest / p.n_tiles;
+  }
+  return r;
+}
+
+// Split-K tail of a 128 x 128 tile whose S splits form a thread-block cluster.  On entry every epilogue thread holds its
+// row's 64 partial sums (`acc`, thread = (row_in_tile, half)) and every CTA of the cluster is past its k loop, so the
+// operand rings are free.  The partial rows are scattered into the ring of the CTA that finishes them (CTA c takes rows
+// [c R, c R + R), R = 128 / S; 16-byte blocks XOR-swizzled by row so that neither side has bank conflicts), a cluster
+// barrier publishes them, and each CTA sums its rows in split order with 256 / R threads per row: row-contiguous residual
+// and output accesses, S times the parallelism of a last-ticket reduction, no global workspace, atomics or fences.
+template <int S>
+ATLAS_DEVICE void cluster_tail(const GemmParams& p, uint8_t* smem, const float (&acc)[64], int split, int half, int row_in_tile,
+                               int epi_tid, int n_tile, int M_rows, unsigned long long* tl) {
+  constexpr int kN = 128, R = kBlockM / S, TPR = 256 / R, CPT = kN / TPR;      // S = 4: 32 rows, 8 threads x 16 columns
+  float* xbuf = reinterpret_cast<float*>(smem);                                 // [S][R][128] fp32
+  {
+    const int dst_cta = row_in_tile / R, lr = row_in_tile % R;
+    const uint32_t remote = cluster_map_shared(smem_u32(xbuf) + (uint32_t)((split * R + lr) * kN * 4), (uint32_t)dst_cta);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int c4 = (half * 16 + j) ^ (lr & 31);
+      st_cluster_f32x4(remote + c4 * 16, acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+    }
+  }
+  if (tl && epi_tid == 0) tl[19] = clock64();
+  cluster_sync_all();
+  if (tl && epi_tid == 0) tl[20] = clock64();
+  const int fr = epi_tid / TPR, seg = epi_tid % TPR;
+  const int gm = split * R + fr;                         // the tile is the only m-tile
+  const int n0 = n_tile * kN + seg * CPT;
+  float v[CPT];
+#pragma unroll
+  for (int i = 0; i < CPT; ++i) v[i] = 0.f;
+#pragma unroll
+  for (int s = 0; s < S; ++s) {
+    const float* rowp = xbuf + (s * R + fr) * kN;
+#pragma unroll
+    for (int j = 0; j < CPT / 4; ++j) {
+      const int c4 = (seg * (CPT / 4) + j) ^ (fr & 31);
+      const float4 t = *reinterpret_cast<const float4*>(rowp + c4 * 4);
+      v[4 * j] += t.x; v[4 * j + 1] += t.y; v[4 * j + 2] += t.z; v[4 * j + 3] += t.w;
+    }
+  }
+  if (tl && epi_tid == 0) tl[21] = clock64();
+  const bool live = gm < M_rows;
+  if (p.ss_in != nullptr && live) {
+    float t = 0.f;
+    for (int j = 0; j < p.ss_in_parts; ++j) t += __ldg(p.ss_in + (size_t)j * p.ss_in_ld + gm);
+    const float rstd = rsqrtf(t * p.ss_inv_h + p.ss_eps);
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) v[i] *= rstd;
+  }
+  if (p.epi_mode == 2) {
+    float amax = 0.f, ss = 0.f;
+    if (live) {
+      __nv_bfloat16* rrow = p.residual + (size_t)gm * p.ldr + n0;
+      uint4 rv[CPT / 8], wv[CPT / 8];
+#pragma unroll
+      for (int j = 0; j < CPT / 8; ++j) {
+        rv[j] = *reinterpret_cast<const uint4*>(rrow + 8 * j);
+        wv[j] = __ldg(reinterpret_cast<const uint4*>(p.norm_w + n0 + 8 * j));
+      }
+#pragma unroll
+      for (int j = 0; j < CPT / 8; ++j) {
+        const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rv[j]);
+        const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wv[j]);
+        uint4 ov;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 r2 = __bfloat1622float2(rh[i]);
+          oh[i] = __floats2bfloat162_rn(v[8 * j + 2 * i] + r2.x, v[8 * j + 2 * i + 1] + r2.y);
+          const float2 h2 = __bfloat1622float2(oh[i]);          // the rounded residual stream is what gets normalised
+          ss += h2.x * h2.x + h2.y * h2.y;
+          float2 w2 = __bfloat1622float2(wh[i]);
+          if (p.norm_plus_one) { w2.x += 1.f; w2.y += 1.f; }
+          v[8 * j + 2 * i] = h2.x * w2.x; v[8 * j + 2 * i + 1] = h2.y * w2.y;
+          amax = fmaxf(amax, fmaxf(fabsf(v[8 * j + 2 * i]), fabsf(v[8 * j + 2 * i + 1])));
+        }
+        *reinterpret_cast<uint4*>(rrow + 8 * j) = ov;
+      }
+    }
+    // the TPR threads of a row are neighbouring lanes
+#pragma unroll
+    for (int off = 1; off < TPR; off <<= 1) {
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+      ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    }
+    if (live) {
+      const float sc = fmaxf(amax, 1e-20f) / 448.f;
+      const float inv = __frcp_rn(sc);
+      uint32_t w[CPT / 4];
+#pragma unroll
+      for (int j = 0; j < CPT / 4; ++j) {
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j] * inv, v[4 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j + 2] * inv, v[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+        w[j] = lo | (hi << 16);
+      }
+      uint4* dst = reinterpret_cast<uint4*>(p.q_out + (size_t)gm * p.ldq + n0);
+#pragma unroll
+      for (int j = 0; j < CPT / 16; ++j) dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+      if (seg == 0) {
+        p.s_out[(size_t)(n0 >> 7) * p.s_ld + gm] = sc;
+        p.ss_out[(size_t)n_tile * p.ss_out_ld + gm] = ss;
+      }
+    }
+  } else if (live) {
+    __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)gm * p.ldc + n0;
+#pragma unroll
+    for (int j = 0; j < CPT / 8; ++j) {
+      uint4 o;
+      o.x = pack_bf16x2(v[8 * j + 0], v[8 * j + 1]); o.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+      o.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]); o.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+      *reinterpret_cast<uint4*>(crow + 8 * j) = o;
+    }
+  }
+}
+
+// TRACE compiles the phase stamps of GemmParams::timeline in; the kernels that serve traffic are built without them (a
+// few extra instructions in the single-thread producer / MMA loops were worth 5 % of a prefill-size GEMM).
+template <int BLOCK_N, bool FP8, bool FUSE_AR = false, int EPW = epi_warps(BLOCK_N, FP8), bool TRACE = false>
 __global__ void __launch_bounds__(gemm_threads_w(EPW, FUSE_AR), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmParams p) {
@@ -195,6 +337,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  unsigned long long* const tl = (TRACE && p.timeline) ? p.timeline + (size_t)blockIdx.x * 32 : nullptr;
+  if (tl && threadIdx.x == 0) {
+    unsigned long long g;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(g));
+    tl[0] = g;
+    tl[1] = clock64();
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -224,9 +373,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const int pf_total = p.m_tiles * p.n_tiles * p.splits;
   auto pf_enter = [&]() {
     if (pf_item < pf_total) {
-      const int rest = pf_item / p.m_tiles;
-      const int split = rest / p.n_tiles;
-      pf_row = (rest % p.n_tiles) * BLOCK_N;
+      const ItemPos ip = item_pos(p, pf_item, p.m_tiles);
+      const int split = ip.split;
+      pf_row = ip.n_tile * BLOCK_N;
       pf_kb = split * p.kb_per_split;
       pf_kb1 = min(p.k_blocks, pf_kb + p.kb_per_split);
     }
@@ -249,7 +398,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (tl && threadIdx.x == 0) tl[2] = clock64();
   chain_wait();                         // barriers, TMEM and descriptors are set up; global memory from here on
+  if (tl && threadIdx.x == 0) tl[3] = clock64();
 
   const int m_tiles = p.tile_expert ? *p.num_m_tiles_ptr : p.m_tiles;
   const int total_items = m_tiles * p.n_tiles * p.splits;
@@ -267,7 +418,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     uint32_t seen[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};         // m-tiles known to be complete (up to 256)
     const uint32_t want_epoch = p.a_ready ? *p.a_ready_epoch : 0u;
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-      const int m_tile = item % m_tiles;
+      const ItemPos ip = item_pos(p, item, m_tiles);
+      const int m_tile = ip.m_tile;
       if (p.a_ready != nullptr && !((m_tile < 256) && (seen[m_tile >> 5] >> (m_tile & 31) & 1u))) {
         constexpr int kGroups = kBlockM / kRowsPerReadyFlag;      // 16 flags per m-tile
         const int row = m_tile * kBlockM + lane * kRowsPerReadyFlag;
@@ -281,15 +433,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         asm volatile("fence.proxy.async;\n" ::: "memory");
       }
       if (lane == 0) {
-        const int rest = item / m_tiles;
-        const int n_tile = rest % p.n_tiles;
-        const int split = rest / p.n_tiles;
+        const int n_tile = ip.n_tile;
+        const int split = ip.split;
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, 0x100)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
-          mbar_expect_tx(&full[stage], Cfg::kStageBytes);
+          mbar_expect_tx(&full[stage], p.a_box_rows * kRowBytes + Cfg::kBBytes);
           if (FP8) {
             mbar_expect_tx(&sc_full[sc_slot], kBlockM * 4);
             bulk_g2s(sc_ring + sc_slot * kBlockM, p.a_scale + (long long)kb * p.sa_k + m_tile * kBlockM, kBlockM * 4,
@@ -310,6 +461,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         (p.tile_expert ? p.tile_expert[m_tile] * p.expert_n : 0) + n_tile * BLOCK_N);
           }
           if (pf_on) pf_step();
+          if (tl && item == (int)blockIdx.x && kb == kb0) tl[4] = clock64();
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -319,13 +471,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       // give copies that are already in flight time to land before the CTA's shared memory goes away
       for (int i = 0; i < 64; ++i) __nanosleep(1000);
     }
+    if (p.cluster_splits > 1) {            // the epilogue warps' two cluster barriers need every thread of the CTA
+      __syncwarp();
+      cluster_sync_all();
+      cluster_sync_all();
+    }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       uint32_t stage = 0, phase = 0, acc_iter = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-        const int split = item / (m_tiles * p.n_tiles);
+        const int split = item_pos(p, item, m_tiles).split;
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
         if (!FP8) {
@@ -341,6 +498,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
           if (!mbar_wait(&full[stage], phase, abort_flag, p.status, 0x202)) { ok = false; break; }
           tc_fence_after();
+          if (tl && item == (int)blockIdx.x && kb == kb0) tl[5] = clock64();
           const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
           const uint64_t adesc = make_smem_desc_sw128(sa);
           const uint64_t bdesc = make_smem_desc_sw128(sa + Cfg::kABytes);
@@ -357,7 +515,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         if (!ok) break;
         if (!FP8) { umma_commit(&acc_full[acc_iter % kAcc]); ++acc_iter; }
+        if (tl) tl[6] = clock64();
       }
+    }
+    if (p.cluster_splits > 1) {
+      __syncwarp();
+      cluster_sync_all();
+      cluster_sync_all();
     }
   } else if (FUSE_AR && warp == kCtrlWarps + kEpiWarps) {
     // ------------------------------------------------------------------ signal warp (reduce-scatter mode)
@@ -395,10 +559,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // This loop never exits early: the split-K path below uses named barriers that need all eight warps.
     // Once a wait has failed (`ok` false) the remaining items only walk the barriers.
     for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
-      const int m_tile = item % m_tiles;
-      const int rest = item / m_tiles;
-      const int n_tile = rest % p.n_tiles;
-      const int split = rest / p.n_tiles;
+      const ItemPos ip = item_pos(p, item, m_tiles);
+      const int m_tile = ip.m_tile;
+      const int n_tile = ip.n_tile;
+      const int split = ip.split;
       const int kb0 = split * p.kb_per_split;
       const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
       const int m = m_tile * kBlockM + row_in_tile;
@@ -489,6 +653,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
 
       // ---- write out
+      if (tl && epi_tid == 0) tl[8] = clock64();
+      if constexpr (BLOCK_N == 128 && HALF == 64 && !FUSE_AR) {
+        if (p.cluster_splits > 1) {
+          // (a wait that ran out leaves rubbish in this CTA's partial; the status word already says so)
+          cluster_sync_all();              // every CTA of the cluster is past its k loop: the operand rings are free
+          if (tl && epi_tid == 0) tl[9] = clock64();
+          if (p.cluster_splits == 4) cluster_tail<4>(p, smem, acc, split, half, row_in_tile, epi_tid, n_tile, M_rows, tl);
+          else                       cluster_tail<2>(p, smem, acc, split, half, row_in_tile, epi_tid, n_tile, M_rows, tl);
+          continue;
+        }
+      }
       bool do_store = ok;
       if (p.splits > 1) {
         // fp32 partials go to the workspace in fragment order (float4 index j4, then epilogue thread), so every
@@ -498,7 +673,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const size_t tiles = (size_t)m_tiles * p.n_tiles;
         const size_t tile_id = (size_t)n_tile * m_tiles + m_tile;
         constexpr size_t kFrag4 = (size_t)(32 * kEpiWarps) * (HALF / 4);
-        if (ok) {
+        const bool row_live = m < M_rows;                      // rows past the problem's edge carry nothing worth moving
+        if (ok && row_live) {
           float4* dst = ws4 + ((size_t)split * tiles + tile_id) * kFrag4 + epi_tid;
 #pragma unroll
           for (int j4 = 0; j4 < HALF / 4; ++j4)
@@ -512,7 +688,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         do_store = ok && ticket == p.splits - 1;
         if (ticket == p.splits - 1) {
           __threadfence();
-          if (ok) {
+          if (ok && row_live) {
 #pragma unroll
             for (int i = 0; i < HALF; ++i) acc[i] = 0.f;
             for (int sp = 0; sp < p.splits; ++sp) {
@@ -528,6 +704,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kEpiWarps));
       }
+      if (tl && epi_tid == 0) tl[9] = clock64();
       bool store_now = do_store;
       if (FUSE_AR && p.ar_mode == 1) {
         // ---- one-shot: this tile's bf16 partial goes to every peer (fragment order: 16-byte vector jv of epilogue
@@ -821,6 +998,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
       }
     }
+    if (tl && epi_tid == 0) tl[10] = clock64();
     if (FUSE_AR && p.ar_mode != 0) {
       // nothing to drain.  One-shot: partial areas alternate with the epoch parity, and a rank can only be one call
       // ahead.  Reduce-scatter: the owner's reduce kernel waits on the tile flags, and a peer cannot reach its next
@@ -906,7 +1084,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
+  if (tl && threadIdx.x == 0) {
+    unsigned long long g;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(g));
+    tl[11] = clock64();
+    tl[12] = g;
+  }
 }
+
+// Trace buffer for the next launches of this library's tcgen05 GEMMs (32 words per CTA, see GemmParams::timeline);
+// nullptr switches tracing off again.  Meant for single launches under a microbenchmark, not for serving.
+static unsigned long long* g_gemm_timeline = nullptr;
+extern "C" void atlas_gemm_set_timeline(unsigned long long* buf) { g_gemm_timeline = buf; }
 
 // ================================================================================ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -979,10 +1168,34 @@ static int make_tmap_kmajor(CUtensorMap* out, const void* ptr, uint64_t rows, ui
 template <int BLOCK_N, bool FP8, bool FUSE_AR = false, int EPW = epi_warps(BLOCK_N, FP8)>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
   using Cfg = GemmCfg<BLOCK_N>;
-  auto kern = gemm_tcgen05_kernel<BLOCK_N, FP8, FUSE_AR, EPW>;
+  auto kern = gemm_tcgen05_kernel<BLOCK_N, FP8, FUSE_AR, EPW, false>;
+  if constexpr (!FUSE_AR) {
+    if (p.timeline != nullptr) kern = gemm_tcgen05_kernel<BLOCK_N, FP8, FUSE_AR, EPW, true>;
+  }
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), Cfg::kSmemBytes) != cudaSuccess) return -20;
+  if (p.cluster_splits > 1)
+    return launch_chain_cluster(true, (unsigned)p.cluster_splits, kern, dim3(grid), dim3(gemm_threads_w(EPW, FUSE_AR)),
+                                (size_t)Cfg::kSmemBytes, st, ta, tb, p) == cudaSuccess ? 0 : -21;
   return launch_chain_if(p.m_tiles <= 2 && p.tile_expert == nullptr, kern, dim3(grid), dim3(gemm_threads_w(EPW, FUSE_AR)),
                          (size_t)Cfg::kSmemBytes, st, ta, tb, p) == cudaSuccess ? 0 : -21;
+}
+
+// Rows of A per tile copy: a problem of at most 64 rows copies the next power of two of its row count (at least 8)
+// instead of the whole 128-row slot.  A CTA's copy engine ingests ~50 bytes per clock whatever the tile, so at decode
+// sizes the 16 KB activation tile (the same for every CTA, mostly padding) was taking a third to two thirds of the
+// ingest that the weight stream needs (ATLAS_GEMM_ABOX=0 restores whole-slot copies).
+static int a_box_for(int M) {
+  static const bool on = [] { const char* e = getenv("ATLAS_GEMM_ABOX"); return !(e && e[0] == '0'); }();
+  if (!on || M > 64) return kBlockM;
+  int b = 8;
+  while (b < M) b <<= 1;
+  return b;
+}
+
+// Split-K through thread-block clusters (ATLAS_GEMM_CLUSTER=0 keeps the workspace + last-ticket reduction everywhere)
+static bool cluster_splitk_enabled() {
+  static const bool on = [] { const char* e = getenv("ATLAS_GEMM_CLUSTER"); return !(e && e[0] == '0'); }();
+  return on;
 }
 
 // k-slices of weights requested into L2 ahead of the tile ring for decode-size GEMMs (ATLAS_GEMM_PREFETCH, 0 = off)
@@ -1037,11 +1250,14 @@ static int gemm_impl(int kind, const void* A, const void* B, void* C, const floa
       return -44;
   }
   CUtensorMap ta, tb;
-  int rc = make_tmap_kmajor(&ta, A, M, K, lda, kBlockM, esize);
+  const int a_box = a_box_for(M);
+  int rc = make_tmap_kmajor(&ta, A, M, K, lda, a_box, esize);
   if (rc) return rc;
   rc = make_tmap_kmajor(&tb, B, N, K, ldb, epi_mode == 1 ? 32 : block_n, esize);
   if (rc) return rc;
   GemmParams p = {};
+  p.timeline = g_gemm_timeline;
+  p.a_box_rows = a_box;
   p.C = C; p.a_scale = a_scale; p.b_scale = b_scale; p.workspace = workspace; p.counters = counters;
   p.status = status; p.ldc = ldc; p.sa_k = sa_k; p.M = M; p.N = N; p.K = K;
   p.epi_mode = epi_mode;
@@ -1073,6 +1289,12 @@ static int gemm_impl(int kind, const void* A, const void* B, void* C, const floa
   p.vec_ok = ((ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
   const long long items = (long long)p.m_tiles * p.n_tiles * p.splits;
   int grid = (int)(items < num_sms ? items : num_sms);
+  // One m-tile, 128-wide tiles, 2 or 4 splits and a CTA for every (tile, split): the splits of a tile run as a cluster
+  // and meet in distributed shared memory (cluster_tail) instead of in the global workspace.
+  p.cluster_splits = 1;
+  if (cluster_splitk_enabled() && p.m_tiles == 1 && block_n == 128 && (p.splits == 2 || p.splits == 4) && items <= num_sms &&
+      (epi_mode == 2 || (epi_mode == 0 && p.vec_ok)) && (N % 128) == 0 && a_ready == nullptr)
+    p.cluster_splits = p.splits;
   p.prefetch_b = p.m_tiles <= 2 ? prefetch_depth() : 0;      // weights read once from HBM: run ahead of the ring in L2
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (kind == 1) {
@@ -1142,6 +1364,8 @@ extern "C" int atlas_gemm_grouped(int kind, const void* A, const void* B, void* 
   rc = make_tmap_kmajor(&tb, B, (uint64_t)E * N, K, ldb, block_n, esize);
   if (rc) return rc;
   GemmParams p = {};
+  p.timeline = g_gemm_timeline;
+  p.a_box_rows = kBlockM;
   p.C = C; p.a_scale = a_scale; p.b_scale = b_scale; p.workspace = nullptr; p.counters = nullptr;
   p.status = status; p.ldc = ldc; p.sa_k = sa_k; p.M = max_rows; p.N = N; p.K = K;
   p.k_blocks = (K + elems_per_row - 1) / elems_per_row;
@@ -1185,7 +1409,8 @@ extern "C" int atlas_gemm_allreduce(int kind, const void* A, const void* B, cons
                                     long long ldb, int block_n, void* const* data, void* const* flags, int rank,
                                     int world, unsigned int* state, size_t area_bytes, int max_tiles, size_t* result_off_out,
                                     int num_sms, long long max_cycles, unsigned long long* status, void* stream, int mode,
-                                    void* C, long long ldc, int splits, float* workspace, int* counters) {
+                                    void* C, long long ldc, int splits, float* workspace, int* counters,
+                                    const AtlasEpilogue* epi) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const uint32_t esize = kind == 1 ? 1 : 2;
   const int elems_per_row = 128 / esize;
@@ -1195,18 +1420,39 @@ extern "C" int atlas_gemm_allreduce(int kind, const void* A, const void* B, cons
   if (block_n != 64 && block_n != 128) return -4;
   if (N % 8 || world < 1 || world > 8) return -5;
   if (mode != 0 && mode != 1) return -13;
+  // The one-shot form ends with the full sum in the epilogue threads' registers, so the residual + norm + FP8 epilogue
+  // (mode 2 of AtlasEpilogue) applies to it unchanged: every rank updates its own copy of the residual stream and writes
+  // its own quantised activations (identical bits everywhere, the partials are added in rank order).
+  const int epi_mode = epi ? epi->mode : 0;
+  if (epi_mode != 0) {
+    if (epi_mode != 2 || mode != 1 || kind != 1 || block_n != 128 || (N % 128)) return -44;
+    if (!epi->q_out || !epi->s_out || !epi->residual || !epi->norm_w || !epi->ss_out || (epi->ldq % 16) || (epi->ldr % 8) ||
+        ((reinterpret_cast<uintptr_t>(epi->q_out) | reinterpret_cast<uintptr_t>(epi->residual) |
+          reinterpret_cast<uintptr_t>(epi->norm_w)) & 15) || epi->ss_in)
+      return -44;
+  }
   CUtensorMap ta, tb;
-  int rc = make_tmap_kmajor(&ta, A, M, K, lda, kBlockM, esize);
+  const int a_box = a_box_for(M);
+  int rc = make_tmap_kmajor(&ta, A, M, K, lda, a_box, esize);
   if (rc) return rc;
   rc = make_tmap_kmajor(&tb, B, N, K, ldb, block_n, esize);
   if (rc) return rc;
   GemmParams p = {};
+  p.timeline = g_gemm_timeline;
+  p.a_box_rows = a_box;
   p.C = nullptr; p.a_scale = a_scale; p.b_scale = b_scale; p.workspace = nullptr; p.counters = nullptr;
   p.status = status; p.ldc = N; p.sa_k = sa_k; p.M = M; p.N = N; p.K = K;
+  p.epi_mode = epi_mode;
+  if (epi_mode == 2) {
+    p.q_out = reinterpret_cast<uint8_t*>(epi->q_out); p.ldq = epi->ldq; p.s_out = epi->s_out; p.s_ld = epi->s_ld;
+    p.residual = reinterpret_cast<__nv_bfloat16*>(epi->residual); p.ldr = epi->ldr;
+    p.norm_w = reinterpret_cast<const __nv_bfloat16*>(epi->norm_w); p.norm_plus_one = epi->norm_plus_one;
+    p.ss_out = epi->ss_out; p.ss_out_ld = epi->ss_out_ld;
+  }
   p.k_blocks = (K + elems_per_row - 1) / elems_per_row;
   p.splits = 1; p.kb_per_split = p.k_blocks;
   if (mode == 1) {
-    if (!C) return -14;
+    if (!C && epi_mode == 0) return -14;
     if (splits < 1) splits = 1;
     if (splits > p.k_blocks) splits = p.k_blocks;
     p.kb_per_split = (p.k_blocks + splits - 1) / splits;
@@ -1285,11 +1531,14 @@ extern "C" int atlas_gemm_reduce_scatter(int kind, const void* A, const void* B,
   if (block_n == 256 && (kind != 1 || wide_fp8_epilogue_warps() != 16)) return -4;    // the wide tile exists for FP8 only
   if (N % 8 || world < 1 || world > 8 || tiles_per_rank < 1) return -5;
   CUtensorMap ta, tb;
-  int rc = make_tmap_kmajor(&ta, A, M, K, lda, kBlockM, esize);
+  const int a_box = kBlockM;
+  int rc = make_tmap_kmajor(&ta, A, M, K, lda, a_box, esize);
   if (rc) return rc;
   rc = make_tmap_kmajor(&tb, B, N, K, ldb, block_n, esize);
   if (rc) return rc;
   GemmParams p = {};
+  p.timeline = g_gemm_timeline;
+  p.a_box_rows = a_box;
   p.C = nullptr; p.a_scale = a_scale; p.b_scale = b_scale; p.workspace = nullptr; p.counters = nullptr;
   p.status = status; p.ldc = N; p.sa_k = sa_k; p.M = M; p.N = N; p.K = K;
   p.k_blocks = (K + elems_per_row - 1) / elems_per_row;

@@ -120,6 +120,11 @@ int atlas_attn_decode(const void* q, long long ldq, void* out, long long ldo, co
                       int seq_base, int B, float scale, float k_scale, float v_scale, int Hq, int Hkv, int D,
                       int block_size, int window, int num_splits, float* part_o, float* part_ml,
                       unsigned long long* status, void* stream);
+int atlas_attn_decode_q8(const void* q, long long ldq, void* q_out, long long ldqo, float* s_out, long long s_ld,
+                         const void* k_cache, const void* v_cache, const int* block_tables, int bt_ld, const int* seq_lens,
+                         const int* query_start_loc, int seq_base, int B, float scale, float k_scale, float v_scale,
+                         int Hq, int Hkv, int block_size, int window, int num_splits, float* part_o, float* part_ml,
+                         unsigned long long* status, void* stream);
 int atlas_attn_prefill(const void* q, long long ldq, void* out, long long ldo, const void* k_cache,
                        const void* v_cache, const int* block_tables, int bt_ld, const int* seq_lens,
                        const int* query_start_loc, const int* tile_seq, const int* tile_q0, int num_tiles, float scale,

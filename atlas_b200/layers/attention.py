@@ -93,8 +93,9 @@ class Attention:
         return y
 
     def mix(self, act: Act, batch, kv: Tuple[torch.Tensor, torch.Tensor, float, float],
-            rope_cache: torch.Tensor) -> torch.Tensor:
-        """Everything before the output projection: this rank's heads' attention output ``[T, hq * d]``."""
+            rope_cache: torch.Tensor):
+        """Everything before the output projection: this rank's heads' attention output ``[T, hq * d]`` (a tensor, or an
+        ``Act`` holding its FP8 form when the attention kernel quantised it)."""
         cfg = self.cfg
         k_cache, v_cache, k_scale, v_scale = kv
         qkv = ops.linear(act, self.qkv)
@@ -118,6 +119,11 @@ class Attention:
             out = attend_selected(ops.paged_attention, self.selector, self.layer_idx, q, k_cache, v_cache, batch, self.scale,
                                   k_scale, v_scale, self.window)
         else:
+            if (self.o.kind == "fp8_block" and not self.gated and self.o.bias is None
+                    and (self.lora is None or batch.adapter_rows is None)):
+                a = ops.paged_attention_fp8_out(q, k_cache, v_cache, batch, self.scale, k_scale, v_scale, self.window)
+                if a is not None:
+                    return a                  # decode step: rows already quantised for the output projection
             out = ops.paged_attention(q, k_cache, v_cache, batch, self.scale, k_scale, v_scale, self.window)
         out = out.reshape(T, nq)
         if self.gated:

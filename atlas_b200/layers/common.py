@@ -44,6 +44,22 @@ class ParallelCtx:
                     return y
         return self.all_reduce(ops.linear(act, w))
 
+    def row_parallel_residual_norm(self, act, w, residual: torch.Tensor, norm_w: torch.Tensor, eps: float, plus_one: bool):
+        """Row-parallel projection whose kernel also sums over the TP group, adds the sum to ``residual`` (in place) and
+        emits the FP8 activations of ``residual * norm_w`` with the 1/rms factor deferred (``Act.row_ss``).  Returns
+        ``(Act, residual)`` or None when this backend / shape has no such kernel (nothing was launched)."""
+        from .. import ops
+        if not (self.tp_size > 1 and self.comm is not None and hasattr(self.comm, "gemm_allreduce")):
+            return None
+        if not ops.residual_norm_fusable(residual, w):
+            return None
+        a = act if isinstance(act, ops.Act) else ops.Act(x=act)
+        r = self.comm.gemm_allreduce(a, w, epilogue=(residual, norm_w, plus_one))
+        if r is None:
+            return None
+        q, s, (sums, parts) = r
+        return ops.Act(q=q, s=s, dtype=residual.dtype, row_ss=(sums, parts, w.weight.shape[0], eps)), residual
+
     def ep_all_reduce(self, t: torch.Tensor) -> torch.Tensor:
         c = self.ep_comm if self.ep_comm is not None else self.comm
         if self.ep_size > 1 and c is not None:

@@ -142,20 +142,40 @@ class DecoderLayer:
         no_lora = batch.adapter_rows is None
         dense_fp8_ffn = self._ffn_fp8() and self.ffn.down.kind == "fp8_block"
         if (self.kind == "attention" and single and no_lora and dense_fp8_ffn
-                and ops.residual_norm_fusable(act, self.mixer.o) and residual.is_contiguous()):
+                and ops.residual_norm_fusable(residual, self.mixer.o)):
             # o_proj + residual add + post-attention norm + FP8 quantisation in the projection's epilogue
             out = self.mixer.mix(act, batch, cache.layer_kv(self.idx), rope_cache)
-            act, residual = ops.linear_residual_norm(Act(x=out), self.mixer.o, residual, self.post_norm, eps, p1)
+            act, residual = ops.linear_residual_norm(out, self.mixer.o, residual, self.post_norm, eps, p1)
         else:
-            if self.kind == "attention":
+            fused = None
+            tp_fusable = (not single and no_lora and dense_fp8_ffn and isinstance(self.mixer, Attention)
+                          and getattr(self.ffn, "shard", False))
+            if self.kind == "attention" and tp_fusable:
+                # tensor parallel: o_proj + all-reduce + residual add + norm + FP8 quantisation in one kernel (decode-size
+                # outputs; larger ones return None before anything is launched)
+                out = self.mixer.mix(act, batch, cache.layer_kv(self.idx), rope_cache)
+                fused = self.mixer.pctx.row_parallel_residual_norm(out, self.mixer.o, residual, self.post_norm, eps, p1)
+                if fused is None:
+                    h = self.mixer.pctx.row_parallel_linear(out, self.mixer.o)
+            elif self.kind == "attention":
                 h = self.mixer.forward(act, batch, cache.layer_kv(self.idx), rope_cache)
             else:
                 h = self.mixer.forward(act, batch, cache.states[self.idx])
-            act, residual = ops.rmsnorm_act(h, self.post_norm, eps, residual, p1, self._ffn_fp8())
-        if (next_norm is not None and single and no_lora and dense_fp8_ffn and residual.is_contiguous()
-                and ops.residual_norm_fusable(act, self.ffn.down) and ops.on_gpu(residual)):
+            if fused is not None:
+                act, residual = fused
+            else:
+                act, residual = ops.rmsnorm_act(h, self.post_norm, eps, residual, p1, self._ffn_fp8())
+        if (next_norm is not None and single and no_lora and dense_fp8_ffn
+                and ops.residual_norm_fusable(residual, self.ffn.down)):
             # down_proj + residual add + the NEXT layer's input norm + FP8 quantisation in one epilogue
             return ops.linear_residual_norm(self.ffn.hidden_act(act), self.ffn.down, residual, next_norm, eps, p1)
+        if (next_norm is not None and not single and no_lora and dense_fp8_ffn and getattr(self.ffn, "shard", False)
+                and self.ffn.activation != "relu2" and ops.residual_norm_fusable(residual, self.ffn.down)):
+            a = self.ffn.hidden_act(act)
+            fused = self.ffn.pctx.row_parallel_residual_norm(a, self.ffn.down, residual, next_norm, eps, p1)
+            if fused is not None:
+                return fused
+            return self.ffn.pctx.row_parallel_linear(a, self.ffn.down), residual
         if self.is_moe:
             hashed = self.ffn.hash_table is not None and batch.input_ids is not None
             h = self.ffn.forward(act, batch.input_ids.to(torch.int32) if hashed else None)
@@ -365,7 +385,7 @@ class DecoderLM:
         hidden = None
         for i, layer in enumerate(self.layers):
             out = layer.mixer.mix(act, batch, cache.layer_kv(layer.idx), self.rope_cache)
-            sp.gemm_rs(Act(x=out), layer.mixer.o)
+            sp.gemm_rs(out if isinstance(out, Act) else Act(x=out), layer.mixer.o)
             act = sp.reduce_norm(res, layer.post_norm, eps, p1)
             sp.gemm_rs(layer.ffn.hidden_act(act), layer.ffn.down)
             if i + 1 < n:

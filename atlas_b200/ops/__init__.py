@@ -236,11 +236,12 @@ def linear_swiglu(a, w: LinearWeight) -> Act:
     return Act(q=qo, s=so, dtype=act.out_dtype)
 
 
-def residual_norm_fusable(a, w: LinearWeight) -> bool:
-    act = a if isinstance(a, Act) else Act(x=a)
-    probe = act.x if act.x is not None else act.q
-    return (FUSED_EPILOGUES and on_gpu(probe) and w.kind == "fp8_block" and w.bias is None and w.weight.shape[0] % 128 == 0
-            and act.row_ss is None)
+def residual_norm_fusable(residual: torch.Tensor, w: LinearWeight) -> bool:
+    """The projection ``w`` can add its output to ``residual`` and emit the normalised FP8 activations of the sum in its
+    own epilogue.  (The projection's input never carries a deferred 1/rms factor: it is an attention output or an
+    activation product, not a norm output.)"""
+    return (FUSED_EPILOGUES and on_gpu(residual) and w.kind == "fp8_block" and w.bias is None and w.weight.shape[0] % 128 == 0
+            and residual.dtype == torch.bfloat16 and residual.is_contiguous())
 
 
 def linear_residual_norm(a, w: LinearWeight, residual: torch.Tensor, norm_w: torch.Tensor, eps: float, plus_one: bool):
@@ -269,6 +270,15 @@ def paged_attention(q, k_cache, v_cache, batch, scale, k_scale=1.0, v_scale=1.0,
         return cuda_ops().paged_attention(q, k_cache, v_cache, batch, scale, k_scale, v_scale, sliding_window)
     return ref.paged_attention(q, k_cache, v_cache, batch.block_tables, batch.seq_lens, batch.query_start_loc,
                                scale, k_scale, v_scale, sliding_window)
+
+
+def paged_attention_fp8_out(q, k_cache, v_cache, batch, scale, k_scale=1.0, v_scale=1.0, sliding_window=None) -> Optional[Act]:
+    """Decode attention that hands its output over already group-quantised for an FP8 output projection (one kernel
+    less per layer); None when the step / cache / head size is not covered and the caller takes the bf16 path."""
+    if not (FUSED_EPILOGUES and on_gpu(q)):
+        return None
+    r = cuda_ops().paged_attention_q8(q, k_cache, v_cache, batch, scale, k_scale, v_scale, sliding_window)
+    return None if r is None else Act(q=r[0], s=r[1], dtype=q.dtype)
 
 
 # ----------------------------------------------------------------------------- MoE

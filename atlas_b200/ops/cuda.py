@@ -344,7 +344,9 @@ def fused_block_n(mode: int, M: int, N: int, K: int, sms: int) -> Tuple[int, int
     m_tiles = (M + 127) // 128
     tiles = m_tiles * ((N // 2) // 128 if mode == 1 else (N + bn - 1) // bn)
     splits = 1
-    if tiles * 2 <= sms and k_blocks >= 8:
+    if _FORCE_SPLITS:
+        splits = min(_FORCE_SPLITS, k_blocks)
+    elif tiles * 2 <= sms and k_blocks >= 8:
         splits = max(1, min(sms // tiles, k_blocks // 4, 16))
     while splits > 1 and splits * m_tiles * 128 * ((N + bn - 1) // bn) * bn * 4 > _GEMM_WS_BYTES:
         splits -= 1
@@ -548,6 +550,39 @@ def paged_attention(q, k_cache, v_cache, batch, scale, k_scale, v_scale, sliding
                                         n_tiles, float(scale), float(k_scale), float(v_scale), Hq, Hkv, D, bs, window,
                                         st), "attn_prefill")
     return out
+
+
+def paged_attention_q8(q, k_cache, v_cache, batch, scale, k_scale, v_scale, sliding_window):
+    """Decode attention whose kernel writes FP8 rows ``[T, Hq * D]`` and one scale per (row, head), the form the output
+    projection's FP8 GEMM reads, instead of bf16 (``atlas_attn_decode_q8``).  Covers pure decode steps on an FP8 cache
+    with head_dim 128; returns None otherwise (nothing launched)."""
+    T, Hq, D = q.shape
+    nb, bs, Hkv, _ = k_cache.shape
+    if D != 128 or k_cache.dtype != FP8 or batch.num_decodes != batch.num_seqs or batch.num_decodes != T or T == 0:
+        return None
+    d = _dev(q)
+    _kv_layout_ok(k_cache, v_cache)
+    if checked.ENABLED:
+        checked.paged_read(batch.block_tables, batch.seq_lens, k_cache.shape[0], k_cache.shape[1])
+    L = lib()
+    if not getattr(L, "_attn_q8_bound", False):
+        L.atlas_attn_decode_q8.argtypes = [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _f, _f, _f, _i,
+                                           _i, _i, _i, _i, _vp, _vp, _vp, _vp]
+        L._attn_q8_bound = True
+    qo = torch.empty(T, Hq * D, dtype=FP8, device=q.device)
+    so = _scale_buf(T, Hq, q.device)
+    splits = decode_splits(T, Hkv, batch.max_seq_len, _num_sms[d])
+    po = pml = None
+    if splits > 1:
+        po = scratch("attn_part_o", T * Hq * splits * D * 4, q.device)
+        pml = scratch("attn_part_ml", T * Hq * splits * 2 * 4, q.device)
+    bt = batch.block_tables
+    _check(L.atlas_attn_decode_q8(q.data_ptr(), q.stride(0), qo.data_ptr(), Hq * D, so.data_ptr(), so.stride(1),
+                                  k_cache.data_ptr(), v_cache.data_ptr(), bt.data_ptr(), bt.stride(0),
+                                  batch.seq_lens.data_ptr(), batch.query_start_loc.data_ptr(), 0, T, float(scale),
+                                  float(k_scale), float(v_scale), Hq, Hkv, bs, int(sliding_window or 0), splits, _ptr(po),
+                                  _ptr(pml), _status_ptr[d], _stream()), "attn_decode")
+    return qo, so
 
 
 def _paged_attention_kv16(q, out, k_cache, v_cache, batch, scale, window, d):

@@ -130,6 +130,37 @@ def main() -> int:
             st = K.check_status()
             rel = float((y.float() - ref).pow(2).mean().sqrt() / ref.pow(2).mean().sqrt())
             report(f"gemm_allreduce {kind} M={M} N={N} K={Kfull}", y is not None and rel < 2e-2 and st == 0, rel_rms=rel, status=st)
+    # ---- fused GEMM + all-reduce + residual add + norm weight + FP8 quantisation (decode-size outputs)
+    for (M, N, Kfull) in ((128, 1024, 2048), (37, 512, 8192), (5, 4096, 1024)):
+        torch.manual_seed(13)
+        xf = (torch.randn(M, Kfull, device=device) * 0.5).bfloat16()
+        wf = torch.randn(N, Kfull, device=device) * 0.05
+        resid0 = torch.randn(M, N, device=device).bfloat16()
+        norm_w = (torch.randn(N, device=device) * 0.2 + 1.0).bfloat16()
+        ks = Kfull // world
+        xs = xf[:, rank * ks:(rank + 1) * ks].contiguous()
+        if ks % 128:
+            report(f"gemm_allreduce_norm M={M} N={N} K={Kfull} (K shard not a multiple of 128)", True)
+            continue
+        w = LinearWeight.from_dense(wf[:, rank * ks:(rank + 1) * ks].contiguous(), "fp8_block")
+        resid = resid0.clone()
+        got = symm.gemm_allreduce(Act(x=xs), w, epilogue=(resid, norm_w, False))
+        if got is None:
+            report(f"gemm_allreduce_norm M={M} N={N} K={Kfull} (not fused by policy)", True)
+            continue
+        q, sc, (sums, parts) = got
+        y = symm.gemm_allreduce(Act(x=xs), w).float()            # the unfused sum, same kernel family
+        torch.cuda.synchronize()
+        st = K.check_status()
+        want_res = (y + resid0.float()).bfloat16()
+        res_ok = float((resid.float() - want_res.float()).abs().max()) <= 2 * float(want_res.float().abs().max()) * 2 ** -8
+        want = want_res.float() * norm_w.float()
+        deq = (q.float().view(M, -1, 128) * sc[..., None]).view(M, N)
+        rel = float((deq - want).pow(2).mean().sqrt() / want.pow(2).mean().sqrt())
+        ss = sums[:parts, :M].sum(0)
+        ss_rel = float(((ss - want_res.float().pow(2).sum(1)).abs() / want_res.float().pow(2).sum(1)).max())
+        report(f"gemm_allreduce_norm M={M} N={N} K={Kfull}", st == 0 and res_ok and rel < 4e-2 and ss_rel < 1e-3,
+               rel_rms=rel, ss_rel=ss_rel, residual_ok=res_ok, status=st)
     # ---- sequence-parallel layer half: GEMM -> reduce-scatter, owner reduce + norm + quantise + all-gather, gathered GEMM
     from atlas_b200.ops import linear
     for (T, H, Kfull, N2) in ((1024, 1024, 2048, 512), (2000, 2048, 4096, 768), (300, 512, 1024, 256)):

@@ -87,7 +87,7 @@ class SymmBackend(CommBackend):
         self.fflag_arr = (_vp * 8)(*(ff + [None] * (8 - len(ff))))
         lib.atlas_gemm_allreduce.argtypes = [_i, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _ll, _ll, _i, C.POINTER(_vp),
                                              C.POINTER(_vp), _i, _i, _vp, _sz, _i, C.POINTER(_sz), _i, _ll, _vp, _vp,
-                                             _i, _vp, _ll, _i, _vp, _vp]
+                                             _i, _vp, _ll, _i, _vp, _vp, _vp]
         base.barrier()
         self._sp_areas, self._sp_mem = {}, []
         self.sp_min_capacity = int(os.environ.get("ATLAS_SP_MIN_CAPACITY", "8192"))
@@ -199,12 +199,19 @@ class SymmBackend(CommBackend):
         self.calls["moe_combine_allreduce"] = self.calls.get("moe_combine_allreduce", 0) + 1
         return out
 
-    def gemm_allreduce(self, act, w) -> Optional[torch.Tensor]:
+    def gemm_allreduce(self, act, w, epilogue=None):
         """``sum over ranks of (act_shard @ W_shard^T)`` with the reduction fused into the GEMM kernel.  Returns a
         view of the result inside this rank's fused area (valid until the next fused call), or None when the
-        shape is not covered and the caller should use GEMM + all_reduce."""
+        shape is not covered and the caller should use GEMM + all_reduce.
+
+        ``epilogue = (residual, norm_w, plus_one)`` (one-shot form, FP8 weights only): the kernel also adds the sum to
+        ``residual`` in place and returns ``(q, scales, (row sums of squares, parts))``, the FP8 form of
+        ``residual * norm_w`` with the row's 1/rms factor left to the consumer, instead of the bf16 sum; None when the
+        shape is not covered (nothing has been launched then)."""
         self._guard()
         K = self.K
+        if epilogue is not None and (w.kind != "fp8_block" or w.weight.shape[0] % 128):
+            return None
         if w.kind == "fp8_block":
             q, sc = act.fp8()
             kind, a, a_scale, b, b_scale = 1, q, sc, w.weight, w.scale
@@ -226,15 +233,22 @@ class SymmBackend(CommBackend):
         splits = 1
         if oneshot:
             # every rank pushes its partial tiles to all peers and sums locally: one flag exchange, K may be split
-            bn, splits = K.gemm_plan(M, N, Kd, kind, sms)
-            bn = min(bn, 128)
+            if epilogue is not None:
+                bn, splits = K.fused_block_n(2, M, N, Kd, sms)
+                bn = 128
+            else:
+                bn, splits = K.gemm_plan(M, N, Kd, kind, sms)
+                bn = min(bn, 128)
             tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
             need = 4 * self.world_size * tiles * 128 * bn * 2 + 1024
             if splits > 1:
                 ws = K.scratch("gemm_ws", K._GEMM_WS_BYTES, a.device)
                 cnt = K.scratch("gemm_counters", 1 << 18, a.device)
-            out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+            if epilogue is None:
+                out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
         else:
+            if epilogue is not None:
+                return None
             if M <= 128 and Kd > FUSED_DECODE_MAX_K:
                 # decode-size rows with a long K and an output too large for the one-shot form: the two-shot kernel has
                 # no split-K, so it would run on N/64 CTAs only; split-K GEMM + all-reduce is faster there
@@ -244,6 +258,20 @@ class SymmBackend(CommBackend):
             need = 2 * (((tiles + self.world_size - 1) // self.world_size) * 128 * bn * 2 * self.world_size + 256 + M * N * 2) + 512
         if tiles > self.max_tiles or need > self.fused_bytes:
             return None
+        epi = res = None
+        if epilogue is not None:
+            residual, norm_w, plus_one = epilogue
+            assert residual.dtype == torch.bfloat16 and residual.stride(1) == 1 and residual.shape == (M, N)
+            assert norm_w.dtype == torch.bfloat16 and norm_w.is_contiguous()
+            qo = torch.empty(M, N, dtype=K.FP8, device=a.device)
+            so = K._scale_buf(M, N // 128, a.device)
+            ssb = torch.empty(N // bn, (M + 127) // 128 * 128, dtype=torch.float32, device=a.device)
+            epi = K._Epilogue()
+            epi.mode = 2
+            epi.q_out, epi.ldq, epi.s_out, epi.s_ld = qo.data_ptr(), N, so.data_ptr(), so.stride(1)
+            epi.residual, epi.ldr, epi.norm_w, epi.norm_plus_one = residual.data_ptr(), residual.stride(0), norm_w.data_ptr(), 1 if plus_one else 0
+            epi.ss_out, epi.ss_out_ld = ssb.data_ptr(), ssb.stride(0)
+            res = (qo, so, (ssb, N // bn))
         off = _sz(0)
         rc = self.lib.atlas_gemm_allreduce(kind, a.data_ptr(), b.data_ptr(), K._ptr(a_scale),
                                            a_scale.stride(1) if a_scale is not None else 0, K._ptr(b_scale),
@@ -251,12 +279,13 @@ class SymmBackend(CommBackend):
                                            bn, self.fdata_arr, self.fflag_arr, self.rank, self.world_size,
                                            self.fstate.data_ptr(), self.fused_bytes, self.max_tiles, C.byref(off), sms,
                                            self.wait_cycles, K._status_ptr[self.dev_index], K._stream(),
-                                           1 if oneshot else 0, K._ptr(out), N, splits, K._ptr(ws), K._ptr(cnt))
+                                           1 if oneshot else 0, K._ptr(out), N, splits, K._ptr(ws), K._ptr(cnt),
+                                           C.cast(C.byref(epi), _vp) if epi is not None else None)
         K._check(rc, "gemm_allreduce")
         self.calls["gemm_allreduce"] += 1
         if oneshot:
             self.calls["gemm_allreduce_oneshot"] += 1
-            return out
+            return res if epilogue is not None else out
         return _device_view(self._fdata + off.value, (M, N), torch.bfloat16, self.device)
 
     def seq_parallel(self, tokens: int, hidden: int):

@@ -305,6 +305,70 @@ def test_attention_sliding_window_and_big_pages(K):
     assert _rel_rms(out, want) < 2e-2
 
 
+def test_fused_gemm_rows_do_not_depend_on_the_batch(K):
+    """A row's result must not depend on how many other rows share its launch (decode rows and the same rows inside a
+    verify / mixed step go through the same tile plan): every fused epilogue form, 4 rows alone against the same 4 rows
+    in front of 16 others, bit for bit."""
+    from atlas_b200 import quant as Q
+    torch.manual_seed(41)
+    H, I = 1024, 2048
+    x = torch.randn(20, H, device=DEV).bfloat16()
+    xi = torch.randn(20, I, device=DEV).bfloat16()
+    w_gu, s_gu = Q.quantize_fp8_block(torch.randn(2 * I, H, device=DEV) * 0.05)
+    w_dn, s_dn = Q.quantize_fp8_block(torch.randn(H, I, device=DEV) * 0.05)
+    w_q, s_q = Q.quantize_fp8_block(torch.randn(1536, H, device=DEV) * 0.05)
+    nw = (torch.randn(H, device=DEV) * 0.2 + 1).bfloat16()
+    res = torch.randn(20, H, device=DEV).bfloat16()
+
+    def chain(rows):
+        xq, xs = K.quant_fp8(xi[:rows].contiguous())
+        r = res[:rows].clone()
+        q2, s2, (ss, parts) = K.gemm_fp8_fused(xq, xs, w_dn, s_dn, mode=2, residual=r, norm_w=nw)       # down + norm
+        y0 = K.gemm_fp8_fused(q2, s2, w_q, s_q, mode=0, ss_in=(ss, parts, H, 1e-5))                      # next qkv
+        q1, s1 = K.gemm_fp8_fused(q2, s2, w_gu, s_gu, mode=1, ss_in=(ss, parts, H, 1e-5))                # next gate|up
+        return r, q2.view(torch.uint8), s2, y0, q1.view(torch.uint8), s1
+
+    small, big = chain(4), chain(20)
+    _status_ok(K)
+    for a, b in zip(small, big):
+        assert torch.equal(a, b[:4])
+
+
+@pytest.mark.parametrize("Hq,Hkv,ctxs,window", [(32, 8, [1, 15, 16, 200, 1023] * 60, None),      # one split per sequence
+                                                  (8, 2, [5, 700, 9000], None),                    # split-K + merge kernel
+                                                  (16, 2, [300, 40], 64)])
+def test_attention_decode_fp8_output(K, Hq, Hkv, ctxs, window):
+    """Decode attention that writes FP8 rows + one scale per (row, head) must give exactly what quantising the bf16
+    output of the plain kernel gives (the values are rounded to bf16 before they are quantised)."""
+    from atlas_b200.models.batch import ForwardBatch
+    torch.manual_seed(26)
+    D, bs = 128, 16
+    B = len(ctxs)
+    nblk = [(c + 1 + bs - 1) // bs for c in ctxs]
+    nb = sum(nblk) + 3
+    perm = torch.randperm(nb).tolist()
+    tables, off = [], 0
+    for n in nblk:
+        tables.append(perm[off:off + n])
+        off += n
+    kc, vc = K.alloc_kv_cache(nb, bs, Hkv, D, torch.float8_e4m3fn, DEV)
+    kc.copy_((torch.randn(nb, bs, Hkv, D, device=DEV) * 0.5).to(torch.float8_e4m3fn))
+    vc.copy_((torch.randn(nb, bs, Hkv, D, device=DEV) * 0.5).to(torch.float8_e4m3fn))
+    fb = ForwardBatch.build([[0]] * B, ctxs, tables, bs, device=DEV)
+    q = (torch.randn(B, Hq, D, device=DEV) * 0.5).bfloat16()
+    out = K.paged_attention(q, kc, vc, fb, D ** -0.5, 0.7, 1.3, window)
+    got = K.paged_attention_q8(q, kc, vc, fb, D ** -0.5, 0.7, 1.3, window)
+    _status_ok(K)
+    assert got is not None
+    q8, sc = got
+    want_q, want_s = K.quant_fp8(out.view(B, Hq * D))
+    assert torch.equal(sc, want_s)
+    assert torch.equal(q8.view(torch.uint8), want_q.view(torch.uint8))
+    # not covered: a step with a prefill chunk in it
+    fb2 = ForwardBatch.build([[0], [0] * 5], [10, 3], [tables[0], tables[1]], bs, device=DEV)
+    assert K.paged_attention_q8(torch.zeros(6, Hq, D, device=DEV).bfloat16(), kc, vc, fb2, D ** -0.5, 1.0, 1.0, None) is None
+
+
 def test_attention_decode_long_splitk(K):
     out, want = _attention_case(K, 128, 8, 1, qlens=[1, 1], ctxs=[5000, 9000])
     assert _rel_rms(out, want) < 2e-2

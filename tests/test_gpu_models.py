@@ -350,7 +350,8 @@ def test_engine_with_block_diffusion_drafter_on_gpu(K):
     prompts = [torch.randint(0, 4096, (30 + 11 * i,), generator=g).tolist() for i in range(4)]
     sp = SamplingParams(max_tokens=12, ignore_eos=True)
     ecfg = dict(num_kv_blocks=128, max_num_seqs=8, max_seq_len=512, max_prefill_tokens=128, enable_prefix_caching=False)
-    base = LLMEngine(model, EngineConfig(use_cuda_graphs=False, **ecfg)).generate(prompts, sp)
+    sp_lp = SamplingParams(max_tokens=12, ignore_eos=True, logprobs=True, top_logprobs=8)
+    base = LLMEngine(model, EngineConfig(use_cuda_graphs=False, **ecfg)).generate(prompts, sp_lp)
     dcfg = DFlashConfig(hidden_size=1024, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=8,
                         num_key_value_heads=2, head_dim=128, block_len=5, target_layer_ids=[0, 2])
     model.dflash = BlockDiffusionDrafter(dcfg, model).init_random(1)
@@ -359,8 +360,19 @@ def test_engine_with_block_diffusion_drafter_on_gpu(K):
     torch.cuda.synchronize()
     assert K.check_status() == 0
     assert eng.stats.spec_proposed > 0 and all(len(o.output_tokens) == 12 for o in out)
-    same = sum(x.output_tokens == y.output_tokens for x, y in zip(out, base))
-    assert same >= 3, same
+    # Verify steps run the chunk attention kernel where plain decoding runs the decode kernel, and with random weights the
+    # two best logits are often closer than that difference: wherever the outputs part, the token the speculative engine
+    # took must be one plain decoding nearly took as well.
+    same = 0
+    for x, y in zip(out, base):
+        i = next((j for j, (a, b) in enumerate(zip(x.output_tokens, y.output_tokens)) if a != b), None)
+        if i is None:
+            same += 1
+            continue
+        top = dict(y.logprobs[i]["top"])
+        assert x.output_tokens[i] in top, (i, x.output_tokens[i], y.logprobs[i])
+        assert y.logprobs[i]["logprob"] - top[x.output_tokens[i]] < 0.25, (i, y.logprobs[i])
+    assert same >= 1, same
     model.dflash, model.capture_layers = None, ()
 
 
