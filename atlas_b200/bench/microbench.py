@@ -216,7 +216,7 @@ def run(model: str = "llama3-8b", decode_batch: int = 128, ctx: int = 1152, chun
         L = K.lib()
         L.atlas_probe_tma_stream.argtypes = [C.c_void_p, C.c_longlong] + [C.c_int] * 7 + [C.c_void_p, C.c_void_p, C.c_void_p]
         sink = torch.zeros(1, dtype=torch.int64, device=dev)
-        buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        buf = torch.empty(320 << 20, dtype=torch.uint8, device=dev)
         buf.random_(0, 255)
         K._dev(buf)
         for box, stages, tiles, kbs, ctas, pieces in ((64, 8, 96, 32, 96, 1), (64, 8, 148, 32, 148, 1), (64, 8, 148, 32, 148, 4),
@@ -237,6 +237,19 @@ def run(model: str = "llama3-8b", decode_batch: int = 128, ctx: int = 1152, chun
                 ms = T.time(fn, iters=5)
                 add(f"tma_stream slot={box}x128B in {pieces} copies, stages={stages} ctas={ctas} k_slices={kbs} layout={'packed' if packed else 'weight'}",
                     ms, bytes_=nbytes, note=f"{stages * box * 128 // 1024} KB in flight per CTA")
+        # per-thread 16-byte asynchronous copies instead of the copy engine: 4 KB chunks (a K + V page of one kv head), four
+        # warps per CTA, several CTAs per SM
+        L.atlas_probe_cpasync_stream.argtypes = [C.c_void_p, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+        for ctas, chunk, depth in ((148 * 4, 4096, 2), (148 * 4, 4096, 3), (148 * 4, 4096, 4), (148 * 6, 4096, 2), (148 * 8, 2048, 4),
+                                   (148 * 4, 2048, 6), (148 * 2, 8192, 4), (148 * 4, 8192, 2)):
+            per_warp = min(256, buf.numel() // (ctas * 4 * chunk))
+            nbytes = ctas * 4 * per_warp * chunk
+            def fn():
+                rc = L.atlas_probe_cpasync_stream(buf.data_ptr(), buf.numel(), ctas, chunk, depth, per_warp, sink.data_ptr(), K._stream())
+                assert rc == 0, rc
+            ms = T.time(fn, iters=5)
+            add(f"cp.async stream chunk={chunk}B depth={depth} ctas={ctas} ({ctas // 148} per SM) chunks_per_warp={per_warp}", ms,
+                bytes_=nbytes, note=f"{4 * depth * chunk // 1024} KB of ring per CTA")
         assert K.check_status() == 0
         return rows
 

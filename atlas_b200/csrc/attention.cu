@@ -382,6 +382,93 @@ ATLAS_DEVICE uint32_t movmatrix_trans(uint32_t v) {
   return r;
 }
 
+// Tail of the decode kernels: merge the four consumer warps' online-softmax states through shared memory (the KV ring is
+// dead by then) and write the rows out: bf16, FP8 + per-head scale, or split-K partials.  `o` holds O^T fragments (rows =
+// dims mt*16 + rq (+8), columns = heads 2c, 2c+1); `acc_scale` undoes a fixed scaling of the P operand.
+template <int D>
+ATLAS_DEVICE void decode_merge_store(const AttnParams& p, uint8_t* ring, const float (&o)[D / 16][4], const float (&m_run)[2],
+                                     const float (&l_run)[2], int warp, int lane, int G, int kvh, int split, int b, int q_row0,
+                                     float acc_scale) {
+  constexpr int MT = D / 16;
+  const int c = lane & 3, rq = lane >> 2;
+  // ---- merge the four consumer warps (the ring is dead now; reuse it)
+  __syncthreads();
+  float* sm_m = reinterpret_cast<float*>(ring);          // [4][8]
+  float* sm_l = sm_m + 32;                               // [4][8]
+  float* sm_o = sm_m + 64;                               // [4][8][D]
+  if (warp < 4) {
+    if (rq == 0) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        sm_m[warp * 8 + c * 2 + h] = m_run[h];
+        sm_l[warp * 8 + c * 2 + h] = l_run[h];
+      }
+    }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int head = c * 2 + (e & 1);
+        const int dim = mt * 16 + rq + 8 * (e >> 1);
+        if (head < G) sm_o[(warp * 8 + head) * D + dim] = o[mt][e];
+      }
+  }
+  const bool q8 = p.q_out != nullptr && p.num_splits == 1;
+  int* sm_amax = reinterpret_cast<int*>(sm_o + 4 * 8 * D);            // [8] per-head max |output| (float bits, >= 0)
+  if (q8 && threadIdx.x < 8) sm_amax[threadIdx.x] = 0;
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += (int)blockDim.x) {
+    const int r = idx / D, d = idx % D;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, sm_m[w * 8 + r]);
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = sm_m[w * 8 + r];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
+      acc += f * sm_o[(w * 8 + r) * D + d] * acc_scale;
+      l += f * sm_l[w * 8 + r];
+    }
+    const int head = kvh * G + r;
+    if (q8) {
+      // a warp's 32 consecutive idx lie inside one head (D and the thread count are multiples of 32): the value is
+      // parked in the first warp's slot, which only this thread reads, and the head's maximum is gathered per warp
+      const float inv = l > 0.f ? p.v_scale / l : 0.f;
+      const float v = __bfloat162float(__float2bfloat16_rn(acc * inv));
+      sm_o[r * D + d] = v;
+      float a = fabsf(v);
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, off));
+      if (lane == 0) atomicMax(&sm_amax[r], __float_as_int(a));
+    } else if (p.num_splits == 1) {
+      const float inv = l > 0.f ? p.v_scale / l : 0.f;
+      p.out[(long long)q_row0 * p.ldo + head * D + d] = __float2bfloat16_rn(acc * inv);
+    } else {
+      const long long pi = ((long long)(b - p.seq_base) * p.Hq + head) * p.num_splits + split;
+      p.part_o[pi * D + d] = acc;
+      if (d == 0) {
+        p.part_ml[pi * 2] = m;
+        p.part_ml[pi * 2 + 1] = l;
+      }
+    }
+  }
+  if (q8) {
+    __syncthreads();
+    for (int idx = threadIdx.x * 4; idx < G * D; idx += (int)blockDim.x * 4) {
+      const int r = idx / D, d = idx % D;
+      const int head = kvh * G + r;
+      const float sc = fmaxf(__int_as_float(sm_amax[r]), 1e-10f) / 448.f;
+      const float inv = __frcp_rn(sc);
+      const float4 v = *reinterpret_cast<const float4*>(sm_o + r * D + d);
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v.x * inv, v.y * inv), __NV_SATFINITE, __NV_E4M3);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v.z * inv, v.w * inv), __NV_SATFINITE, __NV_E4M3);
+      *reinterpret_cast<uint32_t*>(p.q_out + (long long)q_row0 * p.ldqo + head * D + d) = lo | (hi << 16);
+      if (d == 0) p.s_out[(long long)head * p.s_ld + q_row0] = sc;
+    }
+  }
+}
+
 template <int D, int BS>       // BS: block size known at compile time (0 = runtime)
 __global__ void __launch_bounds__(kDecodeThreads)
 attn_decode_kernel(const AttnParams p, int stages, status_t* status) {
@@ -563,82 +650,455 @@ attn_decode_kernel(const AttnParams p, int stages, status_t* status) {
     }
   }
 
-  // ---- merge the four consumer warps (the ring is dead now; reuse it)
+  decode_merge_store<D>(p, ring, o, m_run, l_run, warp, lane, G, kvh, split, b, q_row0, 1.f);
+}
+
+// The same tiles fed by per-thread 16-byte asynchronous copies instead of the bulk-copy engine: every warp streams its own
+// pages (page i of the CTA's range goes to warp i % 4) through a private ring of kCpDepth slots (2 or 3) and waits for them with
+// cp.async.wait_group, so there is no producer warp, no mbarrier and no wait that could run out.  The copy engine moves
+// the 2 KB K and V blocks of a page at ~26 KB/us per SM whatever the ring depth; 16-byte copies issued by all 128 threads
+// stream the same bytes at ~32 KB/us per SM (`microbench --only stream`).
+constexpr int kCpThreads = 128;
+template <int D, int BS, int kCpDepth>       // BS: block size known at compile time (0 = runtime)
+__global__ void __launch_bounds__(kCpThreads)
+attn_decode_cp_kernel(const AttnParams p) {
+  constexpr int KS = D / 16, MT = D / 16, DQ = D / 4;
+  extern __shared__ __align__(128) uint8_t dsm[];
+  const int bs = BS ? BS : p.block_size;
+  const int stage_bytes = 2 * bs * D;
+  int* bt_sm = reinterpret_cast<int*>(dsm);
+  uint8_t* ring = dsm + kBtSmemEntries * 4;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = lane & 3, rq = lane >> 2;
+  const int G = p.Hq / p.Hkv;
+  const int b = p.seq_base + blockIdx.z, kvh = blockIdx.x, split = blockIdx.y;
+  chain_trigger();
+  chain_wait();                       // global memory is only touched from here on
+  const int L = p.seq_lens[b];
+  const int q_row0 = p.query_start_loc[b];
+  const int n_blocks = (L + bs - 1) / bs;
+  const int per_split = (n_blocks + p.num_splits - 1) / p.num_splits;
+  int blk_lo = split * per_split;
+  const int blk_hi = min(n_blocks, (split + 1) * per_split);
+  if (p.window > 0) blk_lo = max(blk_lo, max(0, L - p.window) / bs);
+  const int n_mine = max(0, blk_hi - blk_lo);
+  const int* bt = p.block_tables + (long long)b * p.bt_ld + blk_lo;
+  for (int i = threadIdx.x; i < min(n_mine, kBtSmemEntries); i += kCpThreads) bt_sm[i] = bt[i];
   __syncthreads();
-  float* sm_m = reinterpret_cast<float*>(ring);          // [4][8]
-  float* sm_l = sm_m + 32;                               // [4][8]
-  float* sm_o = sm_m + 64;                               // [4][8][D]
-  if (warp < 4) {
-    if (rq == 0) {
+
+  // per-thread state: heads c*2, c*2+1 (n columns), dims mt*16 + rq (+8)
+  float o[MT][4];
+#pragma unroll
+  for (int j = 0; j < MT; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+
+  {
+    // ---- Q^T as B fragments: b0 = (k = c*2+{0,1}, n = rq) , b1 = (k = c*2+8+{0,1}, n = rq); n = head in group.
+    // dim permutation: MMA k index kk of k-step ks <-> dim c'*DQ + ks*4 + ..., matching the K bytes a thread reads.
+    uint32_t qb[KS][2];
+    {
+      const __nv_bfloat16* qrow = rq < G ? p.q + (long long)q_row0 * p.ldq + (kvh * G + rq) * D : nullptr;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (qrow) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(qrow + c * DQ + ks * 4);
+          const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+          const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+          v[0] = __low2float(lo) * p.qk_scale_log2; v[1] = __high2float(lo) * p.qk_scale_log2;
+          v[2] = __low2float(hi) * p.qk_scale_log2; v[3] = __high2float(hi) * p.qk_scale_log2;
+        }
+        qb[ks][0] = pack_f16x2(v[0], v[1]);
+        qb[ks][1] = pack_f16x2(v[2], v[3]);
+      }
+    }
+    const int win_lo = p.window > 0 ? L - 1 - p.window : -1;  // tokens <= win_lo are outside the window
+    // this thread's two token rows inside a page
+    const int tok_r0 = (rq >> 1) * 4 + (rq & 1);
+    const int tok_r1 = tok_r0 + 2;
+    // this warp's pages: i = warp + 4 k, slot k % kCpDepth of its private ring
+    uint8_t* myring = ring + (size_t)warp * kCpDepth * stage_bytes;
+    const int n_w = n_mine > warp ? (n_mine - warp + 3) / 4 : 0;
+    const int half_bytes = bs * D;
+    auto issue = [&](int k) {
+      const int i = warp + 4 * k;
+      const int blk = i < kBtSmemEntries ? bt_sm[i] : bt[i];
+      const long long off = ((long long)blk * p.Hkv + kvh) * (long long)half_bytes;
+      const uint32_t dst = smem_u32(myring + (size_t)(k % kCpDepth) * stage_bytes);
+      const uint8_t* ks = p.k_cache + off;
+      const uint8_t* vs = p.v_cache + off;
+      for (int o16 = lane * 16; o16 < half_bytes; o16 += 512) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + o16), "l"(ks + o16) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + half_bytes + o16), "l"(vs + o16) : "memory");
+      }
+    };
+#pragma unroll
+    for (int k = 0; k < kCpDepth - 1; ++k) {
+      if (k < n_w) issue(k);
+      asm volatile("cp.async.commit_group;\n" ::: "memory");
+    }
+    for (int k = 0; k < n_w; ++k) {
+      if (k + kCpDepth - 1 < n_w) issue(k + kCpDepth - 1);
+      asm volatile("cp.async.commit_group;\n" ::: "memory");
+      asm volatile("cp.async.wait_group %0;\n" ::"n"(kCpDepth - 1) : "memory");      // page k has landed
+      __syncwarp();
+      const int i = warp + 4 * k;
+      const uint8_t* kblk = myring + (size_t)(k % kCpDepth) * stage_bytes;
+      const uint8_t* vblk = kblk + bs * D;
+      const int blk_tok0 = (blk_lo + i) * bs;
+#pragma unroll 1
+      for (int sub = 0; sub * 16 < bs; ++sub) {
+        const int tok0 = blk_tok0 + sub * 16;
+        if (tok0 >= L) break;
+        // ---- S^T = K Q^T : rows = tokens (tok_r0 -> row rq, tok_r1 -> row rq+8), cols = heads
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint4* k0 = reinterpret_cast<const uint4*>(kblk + (sub * 16 + tok_r0) * D + c * DQ);
+        const uint4* k1 = reinterpret_cast<const uint4*>(kblk + (sub * 16 + tok_r1) * D + c * DQ);
+#pragma unroll
+        for (int v4 = 0; v4 < DQ / 16; ++v4) {
+          const uint4 ra = k0[v4], rb = k1[v4];
+          const uint32_t wa[4] = {ra.x, ra.y, ra.z, ra.w};
+          const uint32_t wb[4] = {rb.x, rb.y, rb.z, rb.w};
+#pragma unroll
+          for (int wi = 0; wi < 4; ++wi) {
+            uint32_t a[4];
+            fp8x4_to_f16x2x2(wa[wi], a[0], a[2]);      // row rq   : k lo / k hi
+            fp8x4_to_f16x2x2(wb[wi], a[1], a[3]);      // row rq+8
+            mma_f16(s, a, qb[v4 * 4 + wi][0], qb[v4 * 4 + wi][1]);
+          }
+        }
+        // ---- mask (token validity is per row), online softmax per head column
+        const bool in0 = (tok0 + tok_r0) < L && (tok0 + tok_r0) > win_lo;
+        const bool in1 = (tok0 + tok_r1) < L && (tok0 + tok_r1) > win_lo;
+        s[0] = in0 ? s[0] : -INFINITY; s[1] = in0 ? s[1] : -INFINITY;
+        s[2] = in1 ? s[2] : -INFINITY; s[3] = in1 ? s[3] : -INFINITY;
+        float mx[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 4));
+          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 8));
+          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 16));
+          mx[h] = fmaxf(mx[h], m_run[h]);
+        }
+        float alpha[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          alpha[h] = (mx[h] == -INFINITY) ? 1.f : exp2f(m_run[h] - mx[h]);
+          m_run[h] = mx[h];
+        }
+        float pv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int h = e & 1;
+          pv[e] = (mx[h] == -INFINITY) ? 0.f : exp2f(s[e] - mx[h]);
+        }
+        l_run[0] = l_run[0] * alpha[0] + pv[0] + pv[2];
+        l_run[1] = l_run[1] * alpha[1] + pv[1] + pv[3];
+        // P^T as the B operand of the PV product: transpose the two 8x8 (token x head) blocks
+        const uint32_t pb0 = movmatrix_trans(pack_f16x2(pv[0], pv[1]));
+        const uint32_t pb1 = movmatrix_trans(pack_f16x2(pv[2], pv[3]));
+        // after the transpose this thread holds head rq, tokens c*4+{0,1} (pb0) and c*4+{2,3} (pb1)
+        uint32_t vmask = 0xFFFFFFFFu;
+        {
+          const int first = tok0 + c * 4;
+          if (first + 3 >= L) {
+            vmask = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (first + j < L) vmask |= 0xFFu << (8 * j);
+          }
+        }
+        // rescale only when some head's running max moved (the accumulator's columns are heads c*2, c*2+1)
+        const bool rescale = __any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f);
+        // ---- O^T += V^T P^T : rows = dims, k = tokens
+        const uint8_t* vsub = vblk + sub * 16 + c * 4;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(vsub + (mt * 16 + rq) * bs) & vmask;
+          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(vsub + (mt * 16 + rq + 8) * bs) & vmask;
+          uint32_t a[4];
+          fp8x4_to_f16x2x2(w0, a[0], a[2]);
+          fp8x4_to_f16x2x2(w1, a[1], a[3]);
+          if (rescale) {
+            o[mt][0] *= alpha[0]; o[mt][1] *= alpha[1];
+            o[mt][2] *= alpha[0]; o[mt][3] *= alpha[1];
+          }
+          mma_f16(o[mt], a, pb0, pb1);
+        }
+      }
+      __syncwarp();                  // the slot is refilled two iterations from now
+    }
+    asm volatile("cp.async.wait_all;\n" ::: "memory");
+    // column (head) sums live split across the 8 row-lanes
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 4);
+      l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 8);
+      l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 16);
+    }
+  }
+
+  decode_merge_store<D>(p, ring, o, m_run, l_run, warp, lane, G, kvh, split, b, q_row0, 1.f);
+}
+
+// ----------------------------------------------------------------------------- decode on FP8 tensor-core tiles
+// The same pipeline (16-token pages only), but the cached bytes go into the tensor cores as they are:
+// mma.m16n8k32 with e4m3 operands.  Nothing is widened to f16, which is what the f16 form spends most of its issue
+// slots on.  The two operands that are not cached bytes keep 16-bit-class precision by being fed as TWO e4m3 terms each,
+// x = e4m3(x) + e4m3(x - e4m3(x)), accumulated into the same fp32 accumulator:
+//   S^T[16 tok x 8 heads] = K[16 x 32 dims] (Qhi^T + Qlo^T)      Q scaled per head to the e4m3 range, scale applied to S
+//   O^T[16 dims x 8 heads] += V^T[16 x 32 tok] (Phi^T + Plo^T)    P scaled by 256 (undone at the end)
+// A warp takes two pages per step so that the PV product's 32-token k dimension is full.
+ATLAS_DEVICE void mma_e4m3(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// two floats -> two e4m3 bytes (`lo` in bits 7..0, `hi` in bits 15..8) and back
+ATLAS_DEVICE uint32_t pack_e4m3x2(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+ATLAS_DEVICE float2 unpack_e4m3x2(uint32_t v) {
+  const uint32_t h = fp8x2_to_f16x2(static_cast<uint16_t>(v));
+  return __half22float2(*reinterpret_cast<const __half2*>(&h));
+}
+// (x0, x1) as a leading e4m3 pair and the e4m3 pair of what the first one missed
+ATLAS_DEVICE void split_e4m3x2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+  hi = pack_e4m3x2(x0, x1);
+  const float2 back = unpack_e4m3x2(hi);
+  lo = pack_e4m3x2(x0 - back.x, x1 - back.y);
+}
+
+template <int D>
+__global__ void __launch_bounds__(kDecodeThreads)
+attn_decode_f8_kernel(const AttnParams p, int stages, status_t* status) {
+  constexpr int KS = D / 32, MT = D / 16, DQ = D / 4, bs = 16;
+  constexpr float kPScale = 256.f;
+  extern __shared__ __align__(128) uint8_t dsm[];
+  constexpr int stage_bytes = 2 * bs * D;
+  uint64_t* full = reinterpret_cast<uint64_t*>(dsm);
+  uint64_t* empty = full + stages;
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(empty + stages);
+  int* bt_sm = reinterpret_cast<int*>(dsm + 512);
+  uint8_t* ring = dsm + 512 + kBtSmemEntries * 4;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = lane & 3, rq = lane >> 2;
+  const int G = p.Hq / p.Hkv;
+  const int b = p.seq_base + blockIdx.z, kvh = blockIdx.x, split = blockIdx.y;
+  chain_trigger();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  chain_wait();                       // everything above is on-chip; global memory is only touched from here on
+  const int L = p.seq_lens[b];
+  const int q_row0 = p.query_start_loc[b];
+  const int n_blocks = (L + bs - 1) / bs;
+  const int per_split = (n_blocks + p.num_splits - 1) / p.num_splits;
+  int blk_lo = split * per_split;
+  const int blk_hi = min(n_blocks, (split + 1) * per_split);
+  if (p.window > 0) blk_lo = max(blk_lo, max(0, L - p.window) / bs);
+  const int n_mine = max(0, blk_hi - blk_lo);
+  const int* bt = p.block_tables + (long long)b * p.bt_ld + blk_lo;
+  for (int i = threadIdx.x; i < min(n_mine, kBtSmemEntries); i += kDecodeThreads) bt_sm[i] = bt[i];
+  __syncthreads();
+
+  float o[MT][4];
+#pragma unroll
+  for (int j = 0; j < MT; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+
+  if (warp == 4) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int i = 0; i < n_mine && ok; ++i) {
+        const int st = i % stages;
+        if (!mbar_wait(&empty[st], ((i / stages) & 1) ^ 1u, abort_flag, status, 0x410)) { ok = false; break; }
+        const int blk = i < kBtSmemEntries ? bt_sm[i] : bt[i];
+        const long long off = ((long long)blk * p.Hkv + kvh) * (long long)bs * D;
+        uint8_t* dst = ring + (size_t)st * stage_bytes;
+        mbar_expect_tx(&full[st], stage_bytes);
+        bulk_g2s(dst, p.k_cache + off, bs * D, &full[st]);
+        bulk_g2s(dst + bs * D, p.v_cache + off, bs * D, &full[st]);
+      }
+      if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+  } else {
+    // ---- Q^T as e4m3 B fragments, two terms.  Thread (rq, c) holds head rq, dims [c*DQ, c*DQ + DQ): k index 4c+j of
+    // k-step ks is dim c*DQ + ks*8 + j, k index 16+4c+j is dim c*DQ + ks*8 + 4 + j -- the bytes of K a thread reads.
+    uint32_t qh[KS][2], ql[KS][2];
+    float sq[2];                       // S = accumulator * sq[h] for this thread's two head columns
+    {
+      float qv[DQ];
+      float amax = 0.f;
+      if (rq < G) {
+        const __nv_bfloat16* qrow = p.q + (long long)q_row0 * p.ldq + (kvh * G + rq) * D + c * DQ;
+#pragma unroll
+        for (int j = 0; j < DQ; j += 4) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(qrow + j);
+          const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+          const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+          qv[j] = __low2float(lo) * p.qk_scale_log2; qv[j + 1] = __high2float(lo) * p.qk_scale_log2;
+          qv[j + 2] = __low2float(hi) * p.qk_scale_log2; qv[j + 3] = __high2float(hi) * p.qk_scale_log2;
+        }
+#pragma unroll
+        for (int j = 0; j < DQ; ++j) amax = fmaxf(amax, fabsf(qv[j]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < DQ; ++j) qv[j] = 0.f;
+      }
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      const float qs = fmaxf(amax, 1e-30f) * (1.f / 448.f);
+      const float qinv = __frcp_rn(qs);
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+          uint32_t h0, l0, h1, l1;
+          split_e4m3x2(qv[ks * 8 + w * 4 + 0] * qinv, qv[ks * 8 + w * 4 + 1] * qinv, h0, l0);
+          split_e4m3x2(qv[ks * 8 + w * 4 + 2] * qinv, qv[ks * 8 + w * 4 + 3] * qinv, h1, l1);
+          qh[ks][w] = h0 | (h1 << 16);
+          ql[ks][w] = l0 | (l1 << 16);
+        }
+      sq[0] = __shfl_sync(0xffffffffu, qs, (2 * c) * 4);
+      sq[1] = __shfl_sync(0xffffffffu, qs, (2 * c + 1) * 4);
+    }
+    const int win_lo = p.window > 0 ? L - 1 - p.window : -1;  // tokens <= win_lo are outside the window
+    const int tok_r0 = (rq >> 1) * 4 + (rq & 1);               // this thread's two token rows inside a page
+    const int tok_r1 = tok_r0 + 2;
+    bool ok = true;
+    for (int u = warp; 2 * u < n_mine && ok; u += 4) {
+      const int i0 = 2 * u, i1 = i0 + 1;
+      const int st0 = i0 % stages, st1 = i1 % stages;
+      const int tokA = (blk_lo + i0) * bs;
+      const bool two = i1 < n_mine && tokA + bs < L;
+      if (!mbar_wait(&full[st0], (i0 / stages) & 1u, abort_flag, status, 0x411)) { ok = false; break; }
+      if (i1 < n_mine && !mbar_wait(&full[st1], (i1 / stages) & 1u, abort_flag, status, 0x412)) { ok = false; break; }
+      const uint8_t* kblk[2] = {ring + (size_t)st0 * stage_bytes, ring + (size_t)st1 * stage_bytes};
+      // ---- S^T = K Q^T for both pages: rows = tokens (tok_r0 -> row rq, tok_r1 -> row rq+8), cols = heads
+      float s[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+        if (j == 1 && !two) continue;
+        const uint4* k0 = reinterpret_cast<const uint4*>(kblk[j] + tok_r0 * D + c * DQ);
+        const uint4* k1 = reinterpret_cast<const uint4*>(kblk[j] + tok_r1 * D + c * DQ);
+#pragma unroll
+        for (int v4 = 0; v4 < DQ / 16; ++v4) {
+          const uint4 ra = k0[v4], rb = k1[v4];
+          const uint32_t wa[4] = {ra.x, ra.y, ra.z, ra.w};
+          const uint32_t wb[4] = {rb.x, rb.y, rb.z, rb.w};
+#pragma unroll
+          for (int hk = 0; hk < 2; ++hk) {
+            const uint32_t a[4] = {wa[2 * hk], wb[2 * hk], wa[2 * hk + 1], wb[2 * hk + 1]};
+            mma_e4m3(s[j], a, qh[v4 * 2 + hk][0], qh[v4 * 2 + hk][1]);
+            mma_e4m3(s[j], a, ql[v4 * 2 + hk][0], ql[v4 * 2 + hk][1]);
+          }
+        }
+      }
+      // ---- scale, mask (token validity is per row), online softmax per head column over the 32 tokens
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int t0 = tokA + j * bs;
+        const bool live = j == 0 || two;
+        const bool in0 = live && (t0 + tok_r0) < L && (t0 + tok_r0) > win_lo;
+        const bool in1 = live && (t0 + tok_r1) < L && (t0 + tok_r1) > win_lo;
+        s[j][0] = in0 ? s[j][0] * sq[0] : -INFINITY; s[j][1] = in0 ? s[j][1] * sq[1] : -INFINITY;
+        s[j][2] = in1 ? s[j][2] * sq[0] : -INFINITY; s[j][3] = in1 ? s[j][3] * sq[1] : -INFINITY;
+      }
+      float mx[2] = {fmaxf(fmaxf(s[0][0], s[0][2]), fmaxf(s[1][0], s[1][2])), fmaxf(fmaxf(s[0][1], s[0][3]), fmaxf(s[1][1], s[1][3]))};
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        sm_m[warp * 8 + c * 2 + h] = m_run[h];
-        sm_l[warp * 8 + c * 2 + h] = l_run[h];
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 4));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 8));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 16));
+        mx[h] = fmaxf(mx[h], m_run[h]);
+      }
+      float alpha[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        alpha[h] = (mx[h] == -INFINITY) ? 1.f : exp2f(m_run[h] - mx[h]);
+        m_run[h] = mx[h];
+      }
+      // P^T as the B operand of the PV product, two e4m3 terms.  A b16 unit carries one head's values of this thread's two
+      // token rows; the 8x8 transpose then leaves head rq's tokens 4c, 4c+2, 4c+1, 4c+3 in a register (put in order by a
+      // byte permute), i.e. the k indices 4c .. 4c+3 of the page.
+      uint32_t pbh[2], pbl[2];
+      float lsum[2] = {0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        float pv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int h = e & 1;
+          pv[e] = (mx[h] == -INFINITY) ? 0.f : exp2f(s[j][e] - mx[h]);
+        }
+        lsum[0] += pv[0] + pv[2];
+        lsum[1] += pv[1] + pv[3];
+        uint32_t h0, l0, h1, l1;
+        split_e4m3x2(pv[0] * kPScale, pv[2] * kPScale, h0, l0);      // head 2c:   (tok_r0, tok_r1)
+        split_e4m3x2(pv[1] * kPScale, pv[3] * kPScale, h1, l1);      // head 2c+1
+        pbh[j] = __byte_perm(movmatrix_trans(h0 | (h1 << 16)), 0u, 0x3120);
+        pbl[j] = __byte_perm(movmatrix_trans(l0 | (l1 << 16)), 0u, 0x3120);
+      }
+      l_run[0] = l_run[0] * alpha[0] + lsum[0];
+      l_run[1] = l_run[1] * alpha[1] + lsum[1];
+      // bytes of V^T past the sequence's end may hold anything (0 x NaN): mask them
+      uint32_t vmask[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int first = tokA + j * bs + c * 4;
+        vmask[j] = (j == 1 && !two) ? 0u : 0xFFFFFFFFu;
+        if (first + 3 >= L) {
+          uint32_t mk = 0;
+#pragma unroll
+          for (int t = 0; t < 4; ++t)
+            if (first + t < L) mk |= 0xFFu << (8 * t);
+          vmask[j] &= mk;
+        }
+      }
+      const bool rescale = __any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f);
+      // ---- O^T += V^T P^T : rows = dims, k = the 32 tokens of the two pages
+      const uint8_t* v0 = kblk[0] + bs * D + c * 4;
+      const uint8_t* v1 = kblk[1] + bs * D + c * 4;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        uint32_t a[4];
+        a[0] = *reinterpret_cast<const uint32_t*>(v0 + (mt * 16 + rq) * bs) & vmask[0];
+        a[1] = *reinterpret_cast<const uint32_t*>(v0 + (mt * 16 + rq + 8) * bs) & vmask[0];
+        a[2] = two ? (*reinterpret_cast<const uint32_t*>(v1 + (mt * 16 + rq) * bs) & vmask[1]) : 0u;
+        a[3] = two ? (*reinterpret_cast<const uint32_t*>(v1 + (mt * 16 + rq + 8) * bs) & vmask[1]) : 0u;
+        if (rescale) {
+          o[mt][0] *= alpha[0]; o[mt][1] *= alpha[1];
+          o[mt][2] *= alpha[0]; o[mt][3] *= alpha[1];
+        }
+        mma_e4m3(o[mt], a, pbh[0], pbh[1]);
+        mma_e4m3(o[mt], a, pbl[0], pbl[1]);
+      }
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&empty[st0]);
+        if (i1 < n_mine) mbar_arrive(&empty[st1]);
       }
     }
+    // column (head) sums live split across the 8 row-lanes
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int head = c * 2 + (e & 1);
-        const int dim = mt * 16 + rq + 8 * (e >> 1);
-        if (head < G) sm_o[(warp * 8 + head) * D + dim] = o[mt][e];
-      }
-  }
-  const bool q8 = p.q_out != nullptr && p.num_splits == 1;
-  int* sm_amax = reinterpret_cast<int*>(sm_o + 4 * 8 * D);            // [8] per-head max |output| (float bits, >= 0)
-  if (q8 && threadIdx.x < 8) sm_amax[threadIdx.x] = 0;
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < G * D; idx += kDecodeThreads) {
-    const int r = idx / D, d = idx % D;
-    float m = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) m = fmaxf(m, sm_m[w * 8 + r]);
-    float acc = 0.f, l = 0.f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float mw = sm_m[w * 8 + r];
-      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
-      acc += f * sm_o[(w * 8 + r) * D + d];
-      l += f * sm_l[w * 8 + r];
-    }
-    const int head = kvh * G + r;
-    if (q8) {
-      // a warp's 32 consecutive idx lie inside one head (D and the thread count are multiples of 32): the value is
-      // parked in the first warp's slot, which only this thread reads, and the head's maximum is gathered per warp
-      const float inv = l > 0.f ? p.v_scale / l : 0.f;
-      const float v = __bfloat162float(__float2bfloat16_rn(acc * inv));
-      sm_o[r * D + d] = v;
-      float a = fabsf(v);
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, off));
-      if (lane == 0) atomicMax(&sm_amax[r], __float_as_int(a));
-    } else if (p.num_splits == 1) {
-      const float inv = l > 0.f ? p.v_scale / l : 0.f;
-      p.out[(long long)q_row0 * p.ldo + head * D + d] = __float2bfloat16_rn(acc * inv);
-    } else {
-      const long long pi = ((long long)(b - p.seq_base) * p.Hq + head) * p.num_splits + split;
-      p.part_o[pi * D + d] = acc;
-      if (d == 0) {
-        p.part_ml[pi * 2] = m;
-        p.part_ml[pi * 2 + 1] = l;
-      }
+    for (int h = 0; h < 2; ++h) {
+      l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 4);
+      l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 8);
+      l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 16);
     }
   }
-  if (q8) {
-    __syncthreads();
-    for (int idx = threadIdx.x * 4; idx < G * D; idx += kDecodeThreads * 4) {
-      const int r = idx / D, d = idx % D;
-      const int head = kvh * G + r;
-      const float sc = fmaxf(__int_as_float(sm_amax[r]), 1e-10f) / 448.f;
-      const float inv = __frcp_rn(sc);
-      const float4 v = *reinterpret_cast<const float4*>(sm_o + r * D + d);
-      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v.x * inv, v.y * inv), __NV_SATFINITE, __NV_E4M3);
-      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v.z * inv, v.w * inv), __NV_SATFINITE, __NV_E4M3);
-      *reinterpret_cast<uint32_t*>(p.q_out + (long long)q_row0 * p.ldqo + head * D + d) = lo | (hi << 16);
-      if (d == 0) p.s_out[(long long)head * p.s_ld + q_row0] = sc;
-    }
-  }
+  decode_merge_store<D>(p, ring, o, m_run, l_run, warp, lane, G, kvh, split, b, q_row0, 1.f / kPScale);
 }
 
 // Merge split partials: grid (Hq, B), D threads.
@@ -680,11 +1140,33 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
   if (d == 0) s_out[(long long)head * s_ld + row] = sc;
 }
 
+// Which decode kernel serves 16-token pages: the f16 tensor-core form (default) or the e4m3 form (ATLAS_ATTN_F8MMA=1 or
+// atlas_attn_set_decode_f8).  Both are bound by how many bytes of KV a CTA keeps in flight, not by instruction issue: the
+// e4m3 form issues half the instructions per page but holds more registers (3 instead of 4 CTAs per SM) and measured
+// 102 us against 78 us on 128 sequences x 1152 tokens.
+static int g_decode_f8 = -1;
+static bool decode_f8_enabled() {
+  if (g_decode_f8 < 0) {
+    const char* e = getenv("ATLAS_ATTN_F8MMA");
+    g_decode_f8 = (e && e[0] == '1') ? 1 : 0;
+  }
+  return g_decode_f8 == 1;
+}
+// Bytes of KV ring per decode CTA (ATLAS_ATTN_RING_KB, default 32)
+static int decode_ring_bytes() {
+  static const int v = [] {
+    const char* e = getenv("ATLAS_ATTN_RING_KB");
+    const int kb = e ? atoi(e) : 32;
+    return (kb < 16 ? 16 : (kb > 96 ? 96 : kb)) * 1024;
+  }();
+  return v;
+}
+
 template <int D, int BS>
 static int launch_decode_bs(const AttnParams& p, int B, status_t* status, cudaStream_t st) {
   const int stage_bytes = 2 * p.block_size * D;
-  int stages = (32 * 1024) / stage_bytes;
-  stages = stages > 16 ? 16 : (stages < 4 ? 4 : stages);
+  int stages = decode_ring_bytes() / stage_bytes;
+  stages = stages > 24 ? 24 : (stages < 4 ? 4 : stages);
   stages = (stages / 4) * 4;                       // block i -> stage i % stages -> warp i % 4
   const int merge_bytes = (64 + 4 * 8 * D + 8) * (int)sizeof(float);
   const int ring_bytes = stages * stage_bytes > merge_bytes ? stages * stage_bytes : merge_bytes;
@@ -701,7 +1183,67 @@ static int launch_decode_bs(const AttnParams& p, int B, status_t* status, cudaSt
   return 0;
 }
 template <int D>
+static int launch_decode_f8(const AttnParams& p, int B, status_t* status, cudaStream_t st) {
+  constexpr int stage_bytes = 2 * 16 * D;
+  int stages = decode_ring_bytes() / stage_bytes;
+  stages = stages > 24 ? 24 : (stages < 8 ? 8 : stages);       // every consumer warp may hold two pages
+  stages = (stages / 8) * 8;
+  const int merge_bytes = (64 + 4 * 8 * D + 8) * (int)sizeof(float);
+  const int ring_bytes = stages * stage_bytes > merge_bytes ? stages * stage_bytes : merge_bytes;
+  const int smem = 512 + kBtSmemEntries * 4 + ring_bytes;
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(attn_decode_f8_kernel<D>), smem) != cudaSuccess) return -20;
+  dim3 grid(p.Hkv, p.num_splits, B);
+  if (launch_chain(attn_decode_f8_kernel<D>, grid, dim3(kDecodeThreads), (size_t)smem, st, p, stages, status) != cudaSuccess) return -21;
+  if (p.num_splits > 1) {
+    dim3 g2(p.Hq, B);
+    if (launch_chain(attn_merge_kernel, g2, dim3(D), 0, st, p.part_o, p.part_ml, p.out, p.ldo, p.query_start_loc, p.seq_base,
+                     p.Hq, D, p.num_splits, p.v_scale, p.q_out, p.ldqo, p.s_out, p.s_ld) != cudaSuccess)
+      return -22;
+  }
+  return 0;
+}
+
+// ATLAS_ATTN_CPASYNC=0 keeps the bulk-copy pipeline (producer warp + mbarriers)
+static bool decode_cpasync_enabled() {
+  static const bool on = [] { const char* e = getenv("ATLAS_ATTN_CPASYNC"); return !(e && e[0] == '0'); }();
+  return on;
+}
+
+// Slots of a warp's private page ring (ATLAS_ATTN_CP_DEPTH = 2 or 3)
+static int decode_cp_depth() {
+  static const int v = [] { const char* e = getenv("ATLAS_ATTN_CP_DEPTH"); return (e && atoi(e) == 2) ? 2 : 3; }();
+  return v;
+}
+
+template <int D, int BS, int kCpDepth>
+static int launch_decode_cp(const AttnParams& p, int B, cudaStream_t st) {
+  const int stage_bytes = 2 * p.block_size * D;
+  const int merge_bytes = (64 + 4 * 8 * D + 8) * (int)sizeof(float);
+  const int ring_bytes = 4 * kCpDepth * stage_bytes > merge_bytes ? 4 * kCpDepth * stage_bytes : merge_bytes;
+  const int smem = kBtSmemEntries * 4 + ring_bytes;
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(attn_decode_cp_kernel<D, BS, kCpDepth>), smem) != cudaSuccess) return -20;
+  dim3 grid(p.Hkv, p.num_splits, B);
+  if (launch_chain(attn_decode_cp_kernel<D, BS, kCpDepth>, grid, dim3(kCpThreads), (size_t)smem, st, p) != cudaSuccess) return -21;
+  if (p.num_splits > 1) {
+    dim3 g2(p.Hq, B);
+    if (launch_chain(attn_merge_kernel, g2, dim3(D), 0, st, p.part_o, p.part_ml, p.out, p.ldo, p.query_start_loc, p.seq_base,
+                     p.Hq, D, p.num_splits, p.v_scale, p.q_out, p.ldqo, p.s_out, p.s_ld) != cudaSuccess)
+      return -22;
+  }
+  return 0;
+}
+
+template <int D>
 static int launch_decode(const AttnParams& p, int B, status_t* status, cudaStream_t st) {
+  if (p.block_size == 16 && decode_f8_enabled()) return launch_decode_f8<D>(p, B, status, st);
+  if (decode_cpasync_enabled() && 4 * 3 * 2 * p.block_size * D <= 96 * 1024) {
+    if (decode_cp_depth() == 2) {
+      if (p.block_size == 16) return launch_decode_cp<D, 16, 2>(p, B, st);
+      return launch_decode_cp<D, 0, 2>(p, B, st);
+    }
+    if (p.block_size == 16) return launch_decode_cp<D, 16, 3>(p, B, st);
+    return launch_decode_cp<D, 0, 3>(p, B, st);
+  }
   if (p.block_size == 16) return launch_decode_bs<D, 16>(p, B, status, st);
   return launch_decode_bs<D, 0>(p, B, status, st);
 }
@@ -782,6 +1324,9 @@ extern "C" int atlas_attn_decode_q8(const void* q, long long ldq, void* q_out, l
   if (Hq / Hkv > 8) return -5;
   return launch_decode<128>(p, B, status, reinterpret_cast<cudaStream_t>(stream));
 }
+
+// Selects the decode kernel for 16-token pages at run time (1 = e4m3 tensor-core tiles, 0 = f16 tiles).
+extern "C" void atlas_attn_set_decode_f8(int on) { g_decode_f8 = on ? 1 : 0; }
 
 // Prefill / verify attention: `num_tiles` 16-row query tiles described by (sequence index, first query row of the
 // tile inside the sequence's chunk).

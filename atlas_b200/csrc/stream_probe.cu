@@ -62,9 +62,63 @@ tma_stream_probe_kernel(const __grid_constant__ CUtensorMap tmap, int box_rows, 
   }
 }
 
+// The same walk with per-thread 16-byte asynchronous copies (cp.async, no copy engine): every warp streams its own
+// `chunk_bytes` chunks (chunk index = warp-global index + k * total warps) through a private ring of `depth` chunks.
+__global__ void __launch_bounds__(128)
+cpasync_stream_probe_kernel(const uint8_t* __restrict__ data, int chunk_bytes, int depth, int chunks_per_warp, unsigned long long* sink) {
+  extern __shared__ __align__(128) uint8_t probe_cp[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warps_total = gridDim.x * 4;
+  const int gw = blockIdx.x * 4 + warp;
+  uint8_t* ring = probe_cp + (size_t)warp * depth * chunk_bytes;
+  auto issue = [&](int k) {
+    const uint8_t* src = data + ((size_t)gw + (size_t)k * warps_total) * chunk_bytes;
+    uint8_t* dst = ring + (size_t)(k % depth) * chunk_bytes;
+    for (int off = lane * 16; off < chunk_bytes; off += 512)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(dst + off)), "l"(src + off) : "memory");
+  };
+  for (int k = 0; k < depth - 1 && k < chunks_per_warp; ++k) {
+    issue(k);
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  }
+  unsigned long long acc = 0;
+  for (int k = 0; k < chunks_per_warp; ++k) {
+    if (k + depth - 1 < chunks_per_warp) issue(k + depth - 1);
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    // all but the newest depth - 1 groups are complete: chunk k has landed
+    switch (depth - 1) {
+      case 1: asm volatile("cp.async.wait_group 1;\n" ::: "memory"); break;
+      case 2: asm volatile("cp.async.wait_group 2;\n" ::: "memory"); break;
+      case 3: asm volatile("cp.async.wait_group 3;\n" ::: "memory"); break;
+      case 5: asm volatile("cp.async.wait_group 5;\n" ::: "memory"); break;
+      case 7: asm volatile("cp.async.wait_group 7;\n" ::: "memory"); break;
+      default: asm volatile("cp.async.wait_group 0;\n" ::: "memory"); break;
+    }
+    __syncwarp();
+    acc += *reinterpret_cast<volatile unsigned long long*>(ring + (size_t)(k % depth) * chunk_bytes + lane * 8);
+    __syncwarp();
+  }
+  if (acc == 0x1234567887654321ull) *sink = acc;
+}
+
 }  // namespace atlas
 
 using namespace atlas;
+
+// `ctas` CTAs of four warps; every warp walks chunks_per_warp chunks of chunk_bytes (a multiple of 512) with `depth`
+// (2, 3, 4, 6 or 8) chunks in flight.  The walk covers ctas * 4 * chunks_per_warp * chunk_bytes <= data_bytes.
+extern "C" int atlas_probe_cpasync_stream(const void* data, long long data_bytes, int ctas, int chunk_bytes, int depth,
+                                          int chunks_per_warp, unsigned long long* sink, void* stream) {
+  if (ctas <= 0 || chunk_bytes < 512 || chunk_bytes % 512 || chunks_per_warp <= 0) return -1;
+  if (depth != 2 && depth != 3 && depth != 4 && depth != 6 && depth != 8) return -1;
+  if ((long long)ctas * 4 * chunks_per_warp * chunk_bytes > data_bytes) return -3;
+  const size_t smem = (size_t)4 * depth * chunk_bytes;
+  if (smem > 200 * 1024) return -2;
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(cpasync_stream_probe_kernel), (int)smem) != cudaSuccess) return -20;
+  cpasync_stream_probe_kernel<<<ctas, 128, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint8_t*>(data), chunk_bytes, depth, chunks_per_warp, sink);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
 
 // `data` (data_bytes long) holds rows_total * ld bytes (weight layout: rows_total = tiles * box_rows rows of ld = k_blocks * 128 bytes;
 // packed: rows_total = tiles * k_blocks * box_rows rows of 128 bytes).  Returns 0 or a negative code.

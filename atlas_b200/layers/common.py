@@ -5,12 +5,21 @@ own shard (reference: ``crates/spark-model/src/tp_shard.rs:37-120``).
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Any, Optional
 
 import torch
 
 from ..ops import LinearWeight
+
+
+# Row-parallel projection + all-reduce + residual add + norm + FP8 quantisation in ONE kernel (the one-shot fused GEMM with
+# the residual / norm epilogue).  Numerically checked by the multi-rank self test, but off by default: the epilogue needs
+# 128-wide tiles, and the tile's last CTA then runs split-K reduction, peer exchange and the row epilogue back to back,
+# which measured slower at 2 GPUs (5.30 against 4.86 ms per decode step of the 8B shape) than 64-wide tiles plus a separate
+# norm kernel.  ATLAS_TP_FUSED_NORM=1 switches it on.
+TP_FUSED_NORM = os.environ.get("ATLAS_TP_FUSED_NORM", "0") == "1"
 
 
 @dataclass
@@ -49,6 +58,8 @@ class ParallelCtx:
         emits the FP8 activations of ``residual * norm_w`` with the 1/rms factor deferred (``Act.row_ss``).  Returns
         ``(Act, residual)`` or None when this backend / shape has no such kernel (nothing was launched)."""
         from .. import ops
+        if not TP_FUSED_NORM:
+            return None
         if not (self.tp_size > 1 and self.comm is not None and hasattr(self.comm, "gemm_allreduce")):
             return None
         if not ops.residual_norm_fusable(residual, w):
