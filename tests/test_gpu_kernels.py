@@ -369,6 +369,27 @@ def test_attention_decode_fp8_output(K, Hq, Hkv, ctxs, window):
     assert K.paged_attention_q8(torch.zeros(6, Hq, D, device=DEV).bfloat16(), kc, vc, fb2, D ** -0.5, 1.0, 1.0, None) is None
 
 
+@pytest.mark.parametrize("D,Hq,Hkv", [(128, 8, 2), (64, 4, 4), (128, 32, 8)])
+def test_attention_decode_e4m3_tiles(K, D, Hq, Hkv):
+    """The decode variant that feeds the cached bytes to e4m3 tensor-core tiles (Q and P as two e4m3 terms each) must
+    meet the same bounds as the default kernel: single pages, page boundaries, odd page counts, split-K."""
+    import ctypes as C
+    L = K.lib()
+    L.atlas_attn_set_decode_f8.argtypes = [C.c_int]
+    L.atlas_attn_set_decode_f8.restype = None
+    L.atlas_attn_set_decode_f8(1)
+    try:
+        out, want = _attention_case(K, D, Hq, Hkv, qlens=[1, 1, 1, 1, 1, 1], ctxs=[1, 15, 16, 40, 200, 1023])
+        assert _rel_rms(out, want) < 2e-2
+        torch.testing.assert_close(out.float(), want.float(), atol=3e-2, rtol=5e-2)
+        out, want = _attention_case(K, D, Hq, Hkv, qlens=[1, 1], ctxs=[5000, 9000])
+        assert _rel_rms(out, want) < 2e-2
+        out, want = _attention_case(K, D, Hq, Hkv, qlens=[1, 1], ctxs=[300, 40], window=64)
+        assert _rel_rms(out, want) < 2e-2
+    finally:
+        L.atlas_attn_set_decode_f8(0)
+
+
 def test_attention_decode_long_splitk(K):
     out, want = _attention_case(K, 128, 8, 1, qlens=[1, 1], ctxs=[5000, 9000])
     assert _rel_rms(out, want) < 2e-2
