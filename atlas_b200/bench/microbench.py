@@ -210,10 +210,11 @@ def run(model: str = "llama3-8b", decode_batch: int = 128, ctx: int = 1152, chun
         return rows
 
     if only == "stream":
-        # What the memory system gives a weight stream on its own (csrc/stream_probe.cu): tile copies through a ring, nothing
+        # What the memory system gives a weight stream on its own (bench/csrc/stream_probe.cu): tile copies through a ring, nothing
         # else, in the [N, K] weight layout (a tile's rows one leading dimension apart) and packed tile by tile.
         import ctypes as C
-        L = K.lib()
+        from atlas_b200 import build as _build
+        L = C.CDLL(_build.build_bench() if not os.path.exists(_build.BENCH_LIB) else _build.BENCH_LIB)
         L.atlas_probe_tma_stream.argtypes = [C.c_void_p, C.c_longlong] + [C.c_int] * 7 + [C.c_void_p, C.c_void_p, C.c_void_p]
         sink = torch.zeros(1, dtype=torch.int64, device=dev)
         buf = torch.empty(320 << 20, dtype=torch.uint8, device=dev)

@@ -2,6 +2,8 @@
 
 * ``atlas_b200/_C/libatlas_b200_kernels.so``  — every ``csrc/*.cu`` compiled for sm_100a
 * ``atlas_b200/_C/libatlas_b200_runtime.so``  — host runtime (``csrc/runtime/*.cpp``)
+* ``atlas_b200/_C/libatlas_b200_bench.so``    — kernels that only the benchmarks use (``bench/csrc/*.cu``: memory-stream
+  probes), kept out of the library the engine loads
 
 ``python -m atlas_b200.build`` rebuilds what is out of date.  nvcc cross-compiles without a GPU.
 """
@@ -21,6 +23,8 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 KERNEL_LIB = os.path.join(OUT, "libatlas_b200_kernels.so")
 RUNTIME_LIB = os.path.join(OUT, "libatlas_b200_runtime.so")
+BENCH_CSRC = os.path.join(HERE, "bench", "csrc")
+BENCH_LIB = os.path.join(OUT, "libatlas_b200_bench.so")
 
 
 def _nvcc() -> str:
@@ -78,9 +82,31 @@ def build_runtime(verbose: bool = False) -> str:
     return RUNTIME_LIB
 
 
+def build_bench(verbose: bool = False) -> str:
+    """Benchmark-only kernels; they use the kernel library's tensor-map helper, so that library is linked in."""
+    if not os.path.isdir(BENCH_CSRC):
+        return ""
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
+    cus = sorted(f for f in os.listdir(BENCH_CSRC) if f.endswith(".cu"))
+    objs, stale = [], False
+    for f in cus:
+        src, obj = os.path.join(BENCH_CSRC, f), os.path.join(OUT, "bench_" + f[:-3] + ".o")
+        objs.append(obj)
+        if _newer(src, obj, headers):
+            if verbose:
+                print(f"[atlas_b200.build] compiling bench/csrc/{f}", file=sys.stderr)
+            _run([_nvcc()] + NVCC_FLAGS + ["-I", CSRC, "-c", src, "-o", obj])
+            stale = True
+    if objs and (stale or not os.path.exists(BENCH_LIB)):
+        _run([_nvcc(), "-shared", "-o", BENCH_LIB] + objs + ["-L", OUT, "-latlas_b200_kernels", "-Xlinker", "-rpath=$ORIGIN",
+                                                             "-lcudart"])
+    return BENCH_LIB
+
+
 def build_all(verbose: bool = True) -> None:
     build_kernels(verbose)
     build_runtime(verbose)
+    build_bench(verbose)
 
 
 if __name__ == "__main__":
