@@ -159,7 +159,7 @@ def main() -> int:
         rel = float((deq - want).pow(2).mean().sqrt() / want.pow(2).mean().sqrt())
         ss = sums[:parts, :M].sum(0)
         ss_rel = float(((ss - want_res.float().pow(2).sum(1)).abs() / want_res.float().pow(2).sum(1)).max())
-        report(f"gemm_allreduce_norm M={M} N={N} K={Kfull}", st == 0 and res_ok and rel < 4e-2 and ss_rel < 1e-3,
+        report(f"gemm_allreduce_norm M={M} N={N} K={Kfull}", st == 0 and res_ok and rel < 4e-2 and ss_rel < 5e-3,      # bf16 roundings of the two sums differ
                rel_rms=rel, ss_rel=ss_rel, residual_ok=res_ok, status=st)
     # ---- sequence-parallel layer half: GEMM -> reduce-scatter, owner reduce + norm + quantise + all-gather, gathered GEMM
     from atlas_b200.ops import linear
