@@ -88,6 +88,9 @@ struct GemmParams {
   int ar_mode;                  // 0 = two-shot (owner reduces, result pushed back), 1 = one-shot (partials pushed to all),
                                 // 2 = reduce-scatter (partials pushed to the row block's owner, nothing comes back)
   int rs_tiles_per_rank;        // mode 2: m-tiles (128-row blocks) owned by each rank, in rank order
+  int rs_rows_per_rank;         // mode 2, > 0: a single m-tile whose ROWS are owned rank by rank in groups of this many rows
+                                // (a multiple of 8; decode-size steps): every row goes to its own owner, and the tile's flag is
+                                // raised at every rank that owns some of its rows
   // gathered A operand (sequence-parallel all-gather -> GEMM): rows of A are written into this rank's memory by their
   // owners; one flag per group of kRowsPerReadyFlag rows carries the epoch of the gather that filled it
   const uint32_t* a_ready;
@@ -528,7 +531,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // For every tile, in the CTA's item order: wait until all epilogue warps have issued the tile's peer stores, then
     // raise the tile's flag at the owner with a system-scope release (cumulative over those stores through the
     // barrier).  The release waits for the stores to be acknowledged over NVLink; here that costs nobody anything.
-    if (p.ar_mode == 2 && lane == 0) {
+    if (p.ar_mode == 2 && p.rs_rows_per_rank > 0) {
+      // row-level ownership: lane o tells rank o, for every rank that owns rows of the (only) m-tile
+      const int n_owners = min(p.ar_world, (M_rows + p.rs_rows_per_rank - 1) / p.rs_rows_per_rank);
+      uint32_t it = 0;
+      bool live = true;
+      for (int item = blockIdx.x; item < total_items && live; item += gridDim.x, ++it) {
+        const uint32_t slot = it & 1u, ph = (it >> 1) & 1u;
+        bool got = true;
+        if (lane == 0) got = mbar_wait(&sig_full[slot], ph, abort_flag, p.status, 0x630);
+        live = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+        if (!live) break;
+        const int n_tile = (item / m_tiles) % p.n_tiles;
+        if (lane < n_owners && *abort_flag == 0u)
+          st_release_sys_u32(p.ar_flags[lane] + (size_t)n_tile * 8 + p.ar_rank, ar_epoch);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sig_free[slot]);
+      }
+    } else if (p.ar_mode == 2 && lane == 0) {
       uint32_t it = 0;
       for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it) {
         const uint32_t slot = it & 1u, ph = (it >> 1) & 1u;
@@ -785,6 +805,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int local_tile = m_tile - owner * p.rs_tiles_per_rank;
         __nv_bfloat16* dbase = reinterpret_cast<__nv_bfloat16*>(p.ar_data[owner] + (size_t)p.ar_rank * p.ar_part_src_stride) +
                                (size_t)local_tile * kBlockM * p.N;
+        // row-level ownership (one m-tile): row r belongs to rank r / rows_per_rank and is its local row r % rows_per_rank
+        const int rpr = p.rs_rows_per_rank;
+        auto row_dst = [&](int r_in_tile) -> __nv_bfloat16* {
+          if (rpr <= 0) return dbase + (size_t)r_in_tile * p.N;
+          const int o = min(r_in_tile / rpr, p.ar_world - 1);
+          return reinterpret_cast<__nv_bfloat16*>(p.ar_data[o] + (size_t)p.ar_rank * p.ar_part_src_stride) +
+                 (size_t)(r_in_tile - o * rpr) * p.N;
+        };
         if constexpr (HALF == 64) {
           // A thread holds 64 consecutive columns of ONE row, so a warp-wide 16-byte store would touch 32 rows: 32
           // separate 16-byte writes, which NVLink carries poorly.  The eight 16-byte vectors are transposed across each
@@ -819,10 +847,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           for (int i = 0; i < 8; ++i) {
             const int r_in_tile = lane_group * 32 + 8 * (lane >> 3) + i;
             if (ok && m_tile * kBlockM + r_in_tile < M_rows && col + 8 <= p.N)
-              *reinterpret_cast<uint4*>(dbase + (size_t)r_in_tile * p.N + col) = v[i];
+              *reinterpret_cast<uint4*>(row_dst(r_in_tile) + col) = v[i];
           }
         } else if (ok && m < M_rows) {
-          __nv_bfloat16* drow = dbase + (size_t)row_in_tile * p.N;
+          __nv_bfloat16* drow = row_dst(row_in_tile);
 #pragma unroll
           for (int j = 0; j < HALF; j += 8) {
             const int n = n_base + j;
@@ -1520,7 +1548,7 @@ extern "C" int atlas_gemm_reduce_scatter(int kind, const void* A, const void* B,
                                          long long ldb, int block_n, void* const* data, void* const* flags, int rank,
                                          int world, unsigned int* state, size_t part_src_stride, int tiles_per_rank,
                                          size_t flag_words, int num_sms, long long max_cycles, unsigned long long* status,
-                                         void* stream, int* n_tiles_out) {
+                                         void* stream, int* n_tiles_out, int rows_per_rank) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const uint32_t esize = kind == 1 ? 1 : 2;
   const int elems_per_row = 128 / esize;
@@ -1557,6 +1585,9 @@ extern "C" int atlas_gemm_reduce_scatter(int kind, const void* A, const void* B,
   if ((size_t)tiles_per_rank * p.n_tiles * 8 > flag_words) return -12;
   if ((size_t)tiles_per_rank * kBlockM * N * 2 > part_src_stride) return -12;
   p.ar_mode = 2; p.rs_tiles_per_rank = tiles_per_rank;
+  // row-level ownership: one m-tile, groups of rows_per_rank rows (a multiple of 8) owned rank by rank
+  if (rows_per_rank > 0 && (rows_per_rank % 8 || M > kBlockM || tiles_per_rank != 1 || (long long)rows_per_rank * world < M)) return -15;
+  p.rs_rows_per_rank = rows_per_rank > 0 ? rows_per_rank : 0;
   p.ar_parity_stride = 0; p.ar_part_src_stride = part_src_stride; p.ar_result_off = 0;
   for (int i = 0; i < 8; ++i) {
     p.ar_data[i] = i < world ? reinterpret_cast<uint8_t*>(data[i]) : nullptr;

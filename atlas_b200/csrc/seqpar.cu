@@ -214,14 +214,15 @@ using namespace atlas;
 // mode 0: reduce + residual + RMSNorm + FP8 quantisation, gathered to every rank (ag_q / ag_s).
 // mode 1: reduce + residual, bf16 rows gathered to every rank (ag_h); norm_w unused.
 // `part`, `rs_flags`, `rs_state`, `residual` are local; the ag_* arrays hold one pointer per rank (own entry = local).
-// rows_own rows starting at global row `row0` belong to this rank; row0 % 128 == 0.
+// rows_own rows starting at global row `row0` belong to this rank; row0 is a multiple of 128, or, with row-level ownership
+// inside a single 128-row block (decode-size steps), of 8.
 extern "C" int atlas_sp_reduce_norm_gather(int mode, const void* part, size_t part_src_stride, const void* rs_flags,
                                            const unsigned int* rs_state, int n_tiles, void* residual, const void* norm_w,
                                            int plus_one, float eps, void* const* ag_q, void* const* ag_s, long long sa_k,
                                            void* const* ag_h, void* const* ag_flags, unsigned int* ag_state, int rank,
                                            int world, int H, int row0, int rows_own, long long max_cycles,
                                            unsigned long long* status, void* stream) {
-  if (world < 1 || world > kSpMaxRanks || H % 256 || H > 16384 || (row0 & 127)) return -1;
+  if (world < 1 || world > kSpMaxRanks || H % 256 || H > 16384 || (row0 & 7)) return -1;
   if (mode != 0 && mode != 1) return -2;
   if (mode == 0 && !norm_w) return -3;
   SpParams p;

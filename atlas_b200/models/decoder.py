@@ -25,6 +25,8 @@ from .batch import ForwardBatch
 # tensor-parallel steps with at least this many rows run sequence-parallel (reduce-scatter / all-gather fused into the
 # GEMMs); smaller steps keep the replicated residual stream and the fused GEMM + all-reduce
 SEQ_PARALLEL_MIN_TOKENS = int(os.environ.get("ATLAS_SP_MIN_TOKENS", "1024"))
+# smallest tensor-parallel group whose pure decode steps take the sequence-parallel path (0 = never)
+SEQ_PARALLEL_DECODE_MIN_WORLD = int(os.environ.get("ATLAS_SP_DECODE_MIN_WORLD", "4"))
 
 _DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16,
            "torch.float32": torch.float32, "torch.bfloat16": torch.bfloat16, "torch.float16": torch.float16}
@@ -356,12 +358,25 @@ class DecoderLM:
         """The peer-memory area for a sequence-parallel step, or None when this step takes the replicated path.
         Decided from the model, the configuration and the step's row count only, so every rank decides alike."""
         p = self.pctx
-        if p.tp_size <= 1 or p.comm is None or not hasattr(p.comm, "seq_parallel") or T < SEQ_PARALLEL_MIN_TOKENS:
+        if p.tp_size <= 1 or p.comm is None or not hasattr(p.comm, "seq_parallel"):
+            return None
+        # prefill-size steps are owned in 128-row blocks; pure decode steps of at most 128 rows are owned row by row
+        # (every rank reduces and normalises T / world rows), which pays off once the all-reduce latency of a wide
+        # group dominates the step
+        decode_sp = (SEQ_PARALLEL_DECODE_MIN_WORLD > 0 and p.tp_size >= SEQ_PARALLEL_DECODE_MIN_WORLD and T <= 128
+                     and batch.num_decodes == batch.num_seqs and batch.max_query_len == 1)
+        if T < SEQ_PARALLEL_MIN_TOKENS and not decode_sp:
             return None
         if batch.adapter_rows is not None or self.device.type != "cuda" or ops.FORCE_REFERENCE:
             return None
         if torch.cuda.is_current_stream_capturing():
-            return None
+            # a captured step may use an area that already exists (the eager passes before the capture create it); it
+            # must never allocate or rendezvous
+            areas = getattr(p.comm, "_sp_areas", None)
+            area = areas.get(self.cfg.hidden_size) if (decode_sp and areas) else None
+            if area is None or area.t_pad < T or not getattr(self, "_sp_model_ok", False):
+                return None
+            return area
         ok = getattr(self, "_sp_model_ok", None)
         if ok is None:
             ok = self.dtype == torch.bfloat16 and self.cfg.hidden_size % 256 == 0 and not self.cfg.sandwich_norms and all(

@@ -55,10 +55,22 @@ def device_view(ptr: int, shape, dtype: torch.dtype, device) -> torch.Tensor:
 
 
 def partition(T: int, world: int) -> Tuple[int, int]:
-    """(128-row blocks owned by each rank, rows per rank) for a step of ``T`` rows."""
+    """(128-row blocks owned by each rank, rows per rank) for a step of ``T`` rows.  A step of at most 128 rows (decode)
+    is owned row by row instead: every rank gets the same multiple of eight rows of the single block, so that all ranks
+    share the reduce + norm work of a decode step (``fine_rows``)."""
+    fine = fine_rows(T, world)
+    if fine:
+        return 1, fine
     tiles = (T + 127) // 128
     tpr = (tiles + world - 1) // world
     return tpr, tpr * 128
+
+
+def fine_rows(T: int, world: int) -> int:
+    """Rows per rank under row-level ownership, or 0 when the step is owned in 128-row blocks."""
+    if T > 128 or world < 2:
+        return 0
+    return ((T + world - 1) // world + ROWS_PER_FLAG - 1) // ROWS_PER_FLAG * ROWS_PER_FLAG
 
 
 class SeqParallelArea:
@@ -76,7 +88,8 @@ class SeqParallelArea:
         self.wait_cycles = int(wait_cycles)
         assert hidden % 256 == 0 and 1 <= world <= 8
         self.t_pad = _align(max(max_tokens, 128), 128)
-        tpr, rows_cap = partition(self.t_pad, world)
+        tpr = ((self.t_pad + 127) // 128 + world - 1) // world       # capacity by the 128-row block rule (covers row-level ownership)
+        rows_cap = tpr * 128
         self.rows_cap = rows_cap
         self.part_stride = _align(rows_cap * hidden * 2)
         self.flag_words_rs = tpr * (hidden // 64) * 8
@@ -102,7 +115,7 @@ class SeqParallelArea:
         if getattr(lib, "_sp_bound", False):
             return
         lib.atlas_gemm_reduce_scatter.argtypes = [_i, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _ll, _ll, _i, C.POINTER(_vp),
-                                                  C.POINTER(_vp), _i, _i, _vp, _sz, _i, _sz, _i, _ll, _vp, _vp, C.POINTER(_i)]
+                                                  C.POINTER(_vp), _i, _i, _vp, _sz, _i, _sz, _i, _ll, _vp, _vp, C.POINTER(_i), _i]
         lib.atlas_sp_reduce_norm_gather.argtypes = [_i, _vp, _sz, _vp, _vp, _i, _vp, _vp, _i, _f, C.POINTER(_vp), C.POINTER(_vp),
                                                     _ll, C.POINTER(_vp), C.POINTER(_vp), _vp, _i, _i, _i, _i, _i, _ll, _vp, _vp]
         lib.atlas_sp_wait_rows.argtypes = [_vp, _vp, _i, _ll, _vp, _vp]
@@ -171,7 +184,8 @@ class SeqParallelArea:
                                                 b_scale.shape[1] if b_scale is not None else 0, T, N, Kd, a.stride(0),
                                                 b.stride(0), bn, self.a_part, self.a_rsf, self.rank, self.world,
                                                 self.rs_state.data_ptr(), self.part_stride, tpr, self.flag_words_rs, sms,
-                                                self.wait_cycles, K._status_ptr[d], K._stream(), C.byref(nt))
+                                                self.wait_cycles, K._status_ptr[d], K._stream(), C.byref(nt),
+                                                fine_rows(T, self.world))
         K._check(rc, "gemm_reduce_scatter")
         self._n_tiles, self._T = nt.value, T
         self.calls["gemm_rs"] += 1

@@ -15,7 +15,10 @@ def _rel(a, b):
     return float((a - b).pow(2).mean().sqrt() / b.pow(2).mean().sqrt().clamp_min(1e-12))
 
 
-@pytest.mark.parametrize("T,world,H,Kr,plus_one", [(1000, 4, 1024, 512, False), (300, 8, 512, 256, True), (2048, 2, 2048, 1024, False)])
+@pytest.mark.parametrize("T,world,H,Kr,plus_one", [(1000, 4, 1024, 512, False), (300, 8, 512, 256, True), (2048, 2, 2048, 1024, False),
+                                                   # decode-size steps: the rows of the single 128-row block are owned rank by rank
+                                                   (128, 8, 512, 256, False), (100, 4, 1024, 512, True), (5, 8, 512, 256, False),
+                                                   (64, 2, 1024, 512, False)])
 def test_gemm_reduce_scatter_norm_gather_gemm(T, world, H, Kr, plus_one):
     from atlas_b200 import quant as Q
     from atlas_b200.ops import Act, LinearWeight, linear
