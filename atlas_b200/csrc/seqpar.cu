@@ -47,6 +47,7 @@ struct SpParams {
   long long max_cycles;
   float eps;
   int plus_one, rank, world, H, row0, rows_own, mode;
+  unsigned int* row_counters;           // per-row form: rows finished per group of eight local rows (local memory, zero between calls)
 };
 
 ATLAS_DEVICE void sp_st_release(uint32_t* p, uint32_t v) {
@@ -199,6 +200,124 @@ sp_reduce_norm_gather_kernel(const SpParams p) {
   }
 }
 
+// The same work with ONE ROW PER CTA (eight warps share the row's columns), for decode-size steps where a rank owns a
+// few dozen rows at most and eight rows per CTA would leave the GPU to two or four CTAs.  The arrival flag of a group of
+// eight rows is raised by whichever of its rows finishes last (a counter in local memory; every CTA fences its peer stores
+// before it counts itself, so the last one's release covers them all).
+__global__ void __launch_bounds__(256)
+sp_reduce_norm_gather_row_kernel(const SpParams p) {
+  __shared__ float sc_buf[128];
+  __shared__ float ss_part[8];
+  __shared__ int ok_slot;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int lrow = blockIdx.x;
+  const uint32_t rs_epoch = p.rs_state[0];
+  const uint32_t ag_epoch = p.ag_state[0] + 1u;
+  if (tid == 0) ok_slot = 1;
+  __syncthreads();
+  const bool mine = lrow < p.rows_own;
+  if (mine) {
+    const uint32_t* f = p.rs_flags;                       // row-level ownership: the single m-tile's flags
+    for (int i = tid; i < p.n_tiles * p.world; i += blockDim.x) {
+      const int src = i % p.world, nt = i / p.world;
+      if (!sp_wait(f + (size_t)nt * 8 + src, rs_epoch, p.status, 0x801, p.max_cycles)) ok_slot = 0;
+    }
+  }
+  __syncthreads();
+  const bool ok = ok_slot != 0;
+  const bool live = ok && mine;
+  const long long grow = (long long)p.row0 + lrow;
+  float ss = 0.f;
+  if (live) {
+    for (int j = warp; j < p.H / 256; j += 8) {
+      const int e = j * 256 + lane * 8;
+      uint4 raw[kSpMaxRanks];
+#pragma unroll
+      for (int s = 0; s < kSpMaxRanks; ++s)
+        if (s < p.world)
+          raw[s] = *reinterpret_cast<const uint4*>(p.part + (size_t)s * p.part_src_stride + ((size_t)lrow * p.H + e) * 2);
+      float h[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int s = 0; s < kSpMaxRanks; ++s) {            // rank order: the same bits whoever owns the row
+        if (s >= p.world) break;
+        float f[8];
+        sp_unpack8(raw[s], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h[i] += f[i];
+      }
+      if (p.residual) {
+        float r[8];
+        sp_unpack8(*reinterpret_cast<const uint4*>(p.residual + (size_t)lrow * p.H + e), r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h[i] += r[i];
+      }
+      const uint4 hb = sp_pack8(h);
+      if (p.residual) *reinterpret_cast<uint4*>(p.residual + (size_t)lrow * p.H + e) = hb;
+      if (p.mode == 1) {
+#pragma unroll
+        for (int d = 0; d < kSpMaxRanks; ++d)
+          if (d < p.world) *reinterpret_cast<uint4*>(p.ag_h[d] + grow * p.H + e) = hb;
+        continue;
+      }
+      sp_unpack8(hb, h);                                 // normalise what was stored (the rounded residual stream)
+      float wv[8], hw[8];
+      sp_unpack8(*reinterpret_cast<const uint4*>(p.norm_w + e), wv);
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        ss += h[i] * h[i];
+        hw[i] = h[i] * (p.plus_one ? wv[i] + 1.f : wv[i]);
+        amax = fmaxf(amax, fabsf(hw[i]));
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));   // 16 lanes = one group
+      const float sc = fmaxf(amax, 1e-20f) / kSpFp8Max;
+      const uint2 q = sp_quant8(hw, sc);
+#pragma unroll
+      for (int d = 0; d < kSpMaxRanks; ++d)
+        if (d < p.world) *reinterpret_cast<uint2*>(p.ag_q[d] + grow * p.H + e) = q;
+      if ((lane & 15) == 0) sc_buf[j * 2 + (lane >> 4)] = sc;
+    }
+    if (p.mode == 0) {
+      ss = warp_sum(ss);
+      if (lane == 0) ss_part[warp] = ss;
+    }
+  }
+  __syncthreads();
+  if (live && p.mode == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += ss_part[w];          // fixed order
+    const float rstd = rsqrtf(t / (float)p.H + p.eps);
+    const int groups = p.H >> 7;
+    for (int idx = tid; idx < groups * p.world; idx += blockDim.x) {
+      const int g = idx % groups, d = idx / groups;
+      p.ag_s[d][(long long)g * p.sa_k + grow] = sc_buf[g] * rstd;
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    if (live) {
+      __threadfence_system();                              // this row's peer stores, before it is counted
+      const int grp = lrow >> 3;
+      const unsigned int want = (unsigned int)min(kSpRowsPerCta, p.rows_own - grp * kSpRowsPerCta);
+      const unsigned int seen = atomicAdd(&p.row_counters[grp], 1u);
+      if (seen == want - 1u) {
+        p.row_counters[grp] = 0;
+        __threadfence_system();
+        for (int d = 0; d < p.world; ++d) sp_st_release(p.ag_flags[d] + ((p.row0 + grp * kSpRowsPerCta) >> 3), ag_epoch);
+      }
+    }
+    __threadfence();
+    const unsigned int done = atomicAdd(&p.ag_state[1], 1u);
+    if (done == gridDim.x - 1) {
+      p.ag_state[1] = 0;
+      __threadfence();
+      p.ag_state[0] = ag_epoch;
+    }
+  }
+}
+
 // Blocks until every 8-row group of rows [0, T) carries the epoch in state[0] (the gather that ran last on this stream).
 __global__ void __launch_bounds__(256)
 sp_wait_rows_kernel(const uint32_t* flags, const unsigned int* state, int groups, status_t* status, long long max_cycles) {
@@ -221,7 +340,7 @@ extern "C" int atlas_sp_reduce_norm_gather(int mode, const void* part, size_t pa
                                            int plus_one, float eps, void* const* ag_q, void* const* ag_s, long long sa_k,
                                            void* const* ag_h, void* const* ag_flags, unsigned int* ag_state, int rank,
                                            int world, int H, int row0, int rows_own, long long max_cycles,
-                                           unsigned long long* status, void* stream) {
+                                           unsigned long long* status, void* stream, unsigned int* row_counters) {
   if (world < 1 || world > kSpMaxRanks || H % 256 || H > 16384 || (row0 & 7)) return -1;
   if (mode != 0 && mode != 1) return -2;
   if (mode == 0 && !norm_w) return -3;
@@ -241,6 +360,12 @@ extern "C" int atlas_sp_reduce_norm_gather(int mode, const void* part, size_t pa
   p.max_cycles = max_cycles > 0 ? max_cycles : kMbarMaxCycles;
   p.eps = eps; p.plus_one = plus_one; p.rank = rank; p.world = world; p.H = H; p.row0 = row0; p.rows_own = rows_own;
   p.mode = mode;
+  p.row_counters = row_counters;
+  // decode-size steps (row-level ownership, row0 not on a 128-row boundary or few rows): one CTA per row
+  if (row_counters != nullptr && rows_own <= 64 && H <= 128 * 128) {
+    sp_reduce_norm_gather_row_kernel<<<rows_own > 0 ? rows_own : 1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+    return cudaGetLastError() == cudaSuccess ? 0 : -20;
+  }
   // a rank that owns no rows still takes part: the epoch of its gather state must advance with everyone else's
   const int grid = rows_own > 0 ? (rows_own + kSpRowsPerCta - 1) / kSpRowsPerCta : 1;
   sp_reduce_norm_gather_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);

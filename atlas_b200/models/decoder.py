@@ -26,7 +26,7 @@ from .batch import ForwardBatch
 # GEMMs); smaller steps keep the replicated residual stream and the fused GEMM + all-reduce
 SEQ_PARALLEL_MIN_TOKENS = int(os.environ.get("ATLAS_SP_MIN_TOKENS", "1024"))
 # smallest tensor-parallel group whose pure decode steps take the sequence-parallel path (0 = never)
-SEQ_PARALLEL_DECODE_MIN_WORLD = int(os.environ.get("ATLAS_SP_DECODE_MIN_WORLD", "4"))
+SEQ_PARALLEL_DECODE_MIN_WORLD = int(os.environ.get("ATLAS_SP_DECODE_MIN_WORLD", "0"))
 
 _DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16,
            "torch.float32": torch.float32, "torch.bfloat16": torch.bfloat16, "torch.float16": torch.float16}

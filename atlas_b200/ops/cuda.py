@@ -296,8 +296,8 @@ def _gemm(kind: int, a: torch.Tensor, b: torch.Tensor, a_scale, b_scale, out: Op
     assert out.stride(1) == 1 and out.dtype == torch.bfloat16
     sms = _num_sms[d]
     bn, splits = gemm_plan(M, N, K, kind, sms)
-    if ready is not None:
-        splits = 1
+    if ready is not None and M > 128:
+        splits = 1                      # prefill-size gathered operands: tiles start as their rows arrive, K stays whole
     ws = cnt = None
     if splits > 1:
         ws = scratch("gemm_ws", _GEMM_WS_BYTES, a.device)
@@ -373,8 +373,8 @@ def gemm_fp8_fused(xq, xs, wq, ws, mode: int = 0, out=None, residual=None, norm_
         fixed.copy_(xs)
         xs = fixed
     bn, splits = fused_block_n(mode, M, N, K, sms) if mode else gemm_plan(M, N, K, 1, sms)
-    if ready is not None:
-        splits = 1
+    if ready is not None and M > 128:
+        splits = 1                      # prefill-size gathered operands: tiles start as their rows arrive, K stays whole
     wsp = cnt = None
     if splits > 1:
         wsp = scratch("gemm_ws", _GEMM_WS_BYTES, xq.device)

@@ -106,6 +106,7 @@ class SeqParallelArea:
         self._keep = None
         self.rs_state = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.ag_state = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.row_counters = torch.zeros(rows_cap // ROWS_PER_FLAG + 1, dtype=torch.int32, device=self.device)
         self.peers: List[int] = []
         self._bind()
         self.calls = {"gemm_rs": 0, "reduce_norm": 0, "reduce_hidden": 0}
@@ -117,7 +118,7 @@ class SeqParallelArea:
         lib.atlas_gemm_reduce_scatter.argtypes = [_i, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _ll, _ll, _i, C.POINTER(_vp),
                                                   C.POINTER(_vp), _i, _i, _vp, _sz, _i, _sz, _i, _ll, _vp, _vp, C.POINTER(_i), _i]
         lib.atlas_sp_reduce_norm_gather.argtypes = [_i, _vp, _sz, _vp, _vp, _i, _vp, _vp, _i, _f, C.POINTER(_vp), C.POINTER(_vp),
-                                                    _ll, C.POINTER(_vp), C.POINTER(_vp), _vp, _i, _i, _i, _i, _i, _ll, _vp, _vp]
+                                                    _ll, C.POINTER(_vp), C.POINTER(_vp), _vp, _i, _i, _i, _i, _i, _ll, _vp, _vp, _vp]
         lib.atlas_sp_wait_rows.argtypes = [_vp, _vp, _i, _ll, _vp, _vp]
         lib._sp_bound = True
 
@@ -203,7 +204,7 @@ class SeqParallelArea:
                                                   K._ptr(norm_w), 1 if plus_one else 0, float(eps), self.a_agq, self.a_ags,
                                                   self.t_pad, self.a_agh, self.a_agf, self.ag_state.data_ptr(), self.rank,
                                                   self.world, self.H, row0, rows_own, self.wait_cycles, K._status_ptr[d],
-                                                  K._stream())
+                                                  K._stream(), self.row_counters.data_ptr() if fine_rows(T, self.world) else None)
         K._check(rc, "sp_reduce_norm_gather")
 
     def reduce_norm(self, residual: torch.Tensor, norm_w: torch.Tensor, eps: float, plus_one: bool = False):
