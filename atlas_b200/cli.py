@@ -51,6 +51,8 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--speculative", action="store_true")
     s.add_argument("--num-drafts", type=int, default=0)
     s.add_argument("--ngram-speculative", action="store_true", help="prompt-lookup drafts (no draft model)")
+    s.add_argument("--self-speculative", action="store_true", help="layer-skipping drafts from the target model itself")
+    s.add_argument("--self-spec-keep", type=float, default=0.5, help="fraction of the layers a self-speculative draft pass runs")
     s.add_argument("--ngram-max", type=int, default=4)
     s.add_argument("--ngram-min", type=int, default=2)
     s.add_argument("--mtp-gate", action="store_true", default=None)
@@ -143,8 +145,9 @@ def _engine_config(args, mcfg):
                         max_prefill_tokens=args.max_prefill_tokens, scheduling_policy=args.scheduling_policy,
                         tbt_deadline_ms=args.tbt_deadline_ms, enable_prefix_caching=prefix,
                         speculative=args.speculative,
-                        num_drafts=args.num_drafts or (1 if args.speculative else (3 if args.ngram_speculative else 0)),
+                        num_drafts=args.num_drafts or (1 if args.speculative else (3 if (args.ngram_speculative or args.self_speculative) else 0)),
                         ngram_speculative=args.ngram_speculative, ngram_max=args.ngram_max, ngram_min=args.ngram_min,
+                        self_speculative=args.self_speculative, self_spec_keep=args.self_spec_keep,
                         mtp_gate=True if args.mtp_gate is None else args.mtp_gate, ssm_cache_slots=args.ssm_cache_slots,
                         ssm_checkpoint_interval=args.ssm_checkpoint_interval, swap_space_gb=args.swap_space_gb, disk_swap_gb=args.high_speed_swap_gb,
                         disk_swap_path=args.high_speed_swap_path,

@@ -510,6 +510,8 @@ class EngineConfig:
     mtp_gate: bool = True
     dcut_ratio: float = 0.0                   # > 0: keep this fraction of the batch's draft rows, ranked by drafter confidence
     ngram_speculative: bool = False           # prompt-lookup drafts (no draft model); uses num_drafts
+    self_speculative: bool = False            # layer-skipping drafts from the target model itself; uses num_drafts
+    self_spec_keep: float = 0.5               # fraction of the layers the draft pass runs (first and last always kept)
     ngram_max: int = 4
     ngram_min: int = 2
     ssm_cache_slots: int = 16

@@ -97,6 +97,10 @@ class LLMEngine:
             model.capture_layers = tuple(model.dflash.dcfg.target_layer_ids)
             model.graph_safe = False            # the captured states must be this step's tensors, not a graph's
             self.spec = DFlashSpecController(self, self.cfg)
+        if self.spec is None and self.cfg.self_speculative and self.cfg.num_drafts > 0:
+            from .sched.spec import SelfSpecController
+            if SelfSpecController.supported(model):
+                self.spec = SelfSpecController(self, self.cfg)
         if self.spec is None and self.cfg.ngram_speculative and self.cfg.num_drafts > 0:
             from .sched.spec import NgramSpecController
             self.spec = NgramSpecController(self, self.cfg)     # draft-model-free: works for every architecture

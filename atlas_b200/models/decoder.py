@@ -412,15 +412,25 @@ class DecoderLM:
         return y
 
     @torch.inference_mode()
-    def forward(self, batch: ForwardBatch, cache: CacheStore) -> torch.Tensor:
-        """Returns the final-normed hidden states ``[T,H]`` of every row."""
+    def forward(self, batch: ForwardBatch, cache: CacheStore, layer_ids: Optional[List[int]] = None) -> torch.Tensor:
+        """Returns the final-normed hidden states ``[T,H]`` of every row.  ``layer_ids`` runs only those layers, in
+        order (the layer-skipping draft pass of self-speculative decoding: the kept layers read and write their own KV
+        entries, the skipped ones are not touched)."""
         x = batch.inputs_embeds if batch.inputs_embeds is not None else self.embed_tokens(batch.input_ids)
-        sp = self._seq_parallel_area(batch, x.shape[0]) if not self.capture_layers else None
+        sp = self._seq_parallel_area(batch, x.shape[0]) if (not self.capture_layers and layer_ids is None) else None
         if sp is not None:
             return self._forward_seq_parallel(x, batch, cache, sp)
         residual = None
         if batch.inputs_embeds is not None:
             x = x.clone()                     # fused epilogues update the residual stream in place
+        if layer_ids is not None:
+            layers = [self.layers[i] for i in layer_ids]
+            for k, layer in enumerate(layers):
+                nxt = layers[k + 1] if k + 1 < len(layers) else None
+                next_norm = nxt.input_norm if (nxt is not None and nxt.accepts_prenormed()) else None
+                x, residual = layer.forward(x, residual, batch, cache, self.rope_cache, next_norm=next_norm)
+            y, _ = ops.rmsnorm(x, self.final_norm, self.cfg.rms_norm_eps, residual, self.cfg.norm_plus_one)
+            return y
         n = len(self.layers)
         self.aux_hidden = []
         for i, layer in enumerate(self.layers):

@@ -325,3 +325,69 @@ class DFlashSpecController:
         for (seq, _, k), dr in zip(ready, drafts):
             seq.drafts = dr[:k]
         self.proposed_steps += 1
+
+
+def skip_layer_ids(num_layers: int, keep: float) -> List[int]:
+    """The layers a layer-skipping draft pass runs: the first and the last layer and an even spread in between."""
+    n_keep = max(2, min(num_layers, int(round(num_layers * keep)))) if num_layers > 1 else 1
+    if n_keep >= num_layers:
+        return list(range(num_layers))
+    ids = sorted({round(i * (num_layers - 1) / (n_keep - 1)) for i in range(n_keep)})
+    return [int(i) for i in ids]
+
+
+class SelfSpecController:
+    """Self-speculative decoding: the drafts come from the target model itself, run with most layers skipped.  After
+    every target step the sequences that just sampled a token take ``num_drafts`` chained draft steps through the kept
+    layers (one batched forward per step; the kept layers write their KV entries at the draft positions, which the
+    verify step recomputes and overwrites together with everybody else's), and the next target step verifies the
+    chain.  No extra weights, so it applies to every attention-only checkpoint; models with recurrent layers are left
+    out (a draft pass would advance their state).  Verification, acceptance and the throughput gate are shared with the
+    other proposers.  Reference parity: ``crates/spark-model/src/model/trait_impl/speculative.rs`` (layer-skipping
+    draft, ``generate_self_speculative_inner``), ``crates/spark-server/src/scheduler/spec_step.rs::step_self_spec``."""
+
+    def __init__(self, engine, cfg: EngineConfig):
+        self.engine, self.cfg = engine, cfg
+        self.k = max(1, cfg.num_drafts)
+        self.gate = MtpGate(enabled=cfg.mtp_gate, agree=rank_agreement(engine))
+        self.layer_ids = skip_layer_ids(len(engine.model.layers), cfg.self_spec_keep)
+        self.proposed_steps = 0
+
+    @staticmethod
+    def supported(model) -> bool:
+        return all(getattr(l, "kind", None) == "attention" for l in model.layers) and not getattr(model, "capture_layers", ())
+
+    def active(self) -> bool:
+        return True
+
+    @torch.inference_mode()
+    def after_step(self, out: SchedulerOutput, batch: ForwardBatch, hidden, sampled, kept_rows) -> None:
+        if not self.gate.use_spec():
+            return
+        eng, model = self.engine, self.engine.model
+        bs = eng.cfg.block_size
+        want = []
+        for idx, it in enumerate(out.items):
+            seq, m = it.seq, kept_rows[idx]
+            if (seq.finished or m <= 0 or not it.sample or seq.status != SeqStatus.RUNNING or seq.disable_spec
+                    or seq.num_tokens != it.start + m + 1):
+                continue
+            room = seq.sampling.max_tokens - seq.num_output_tokens - 1
+            k = max(0, min(self.k, room))
+            if k > 0 and eng.scheduler._ensure_blocks(seq, it.start + m + self.k + 1):
+                want.append((seq, it.start + m, k))
+        if not want:
+            return
+        seqs = [w[0] for w in want]
+        drafts: List[List[int]] = [[] for _ in want]
+        cur = [s.token_at(c) for s, c, _ in want]             # the token the target just sampled, at position c
+        for step in range(self.k):
+            fb = ForwardBatch.build([[t] for t in cur], [c + step for _, c, _ in want], [s.blocks for s in seqs], bs,
+                                    device=model.device)
+            h = model.forward(fb, eng.cache, layer_ids=self.layer_ids)
+            cur = [int(t) for t in ops.argmax(model.compute_logits(h)).tolist()]
+            for j, t in enumerate(cur):
+                drafts[j].append(t)
+        for (seq, _, k), dr in zip(want, drafts):
+            seq.drafts = dr[:k]
+        self.proposed_steps += 1

@@ -149,6 +149,7 @@ def main():
     ap.add_argument("--ep-mode", default="auto", choices=["auto", "allreduce", "alltoall"],
                     help="expert-parallel data path: local experts + fused combine/all-reduce, or peer-memory all-to-all")
     ap.add_argument("--ngram-speculative", action="store_true", help="prompt-lookup drafts (no draft model), --num-drafts deep")
+    ap.add_argument("--self-speculative", action="store_true", help="layer-skipping drafts from the target model itself")
     ap.add_argument("--nvfp4-activations", action="store_true",
                     help="NVFP4 checkpoints: quantise activations to NVFP4 too (block-scaled FP4 x FP4 tensor-core GEMM)")
     ap.add_argument("--ssm-checkpoint-interval", type=int, default=0,
@@ -211,8 +212,8 @@ def main():
     ecfg = EngineConfig(max_seq_len=max_len, block_size=args.block_size, max_num_seqs=max(args.concurrency, 1),
                         max_batch_size=max(args.concurrency, 1), max_prefill_tokens=args.max_prefill_tokens,
                         num_kv_blocks=blocks_per_seq * args.concurrency + 64, enable_prefix_caching=args.prefix_cache,
-                        speculative=args.speculative, ngram_speculative=args.ngram_speculative,
-                        num_drafts=args.num_drafts if (args.speculative or args.ngram_speculative) else 0,
+                        speculative=args.speculative, ngram_speculative=args.ngram_speculative, self_speculative=args.self_speculative,
+                        num_drafts=args.num_drafts if (args.speculative or args.ngram_speculative or args.self_speculative) else 0,
                         ssm_cache_slots=args.ssm_cache_slots or max(16, args.concurrency + 8),
                         **({"ssm_checkpoint_interval": args.ssm_checkpoint_interval} if args.ssm_checkpoint_interval else {}),
                         use_cuda_graphs=not args.no_graphs, tp_size=world)
@@ -319,7 +320,7 @@ def main():
                        "parallelism": f"tp{topo.tp_size}" + (f"+ep{topo.ep_size}" if topo.ep_size > 1 else ""), "collectives": (args.comm if world > 1 else "none"), "l2": "inputs larger than L2 (8 GB weights + KV stream every step)",
                        "step": "one wave of `global_batch` concurrent requests, prefill + decode",
                        "engine_steps_per_wave": eng_steps / max(1, args.steps), "cuda_graphs": not args.no_graphs,
-                       "speculative": bool(args.speculative or args.ngram_speculative), "nvfp4_activations": bool(args.nvfp4_activations),
+                       "speculative": bool(args.speculative or args.ngram_speculative or args.self_speculative), "nvfp4_activations": bool(args.nvfp4_activations),
                        "ep_mode": args.ep_mode if topo.ep_size > 1 else None, "prefix_cache": bool(args.prefix_cache),
                        "spec_accept_rate": (eng.stats.spec_accepted / eng.stats.spec_proposed) if eng.stats.spec_proposed else None,
                        "prefix_hit_tokens": (eng.radix.stats.hit_tokens if eng.radix is not None else 0)},
