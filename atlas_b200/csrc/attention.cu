@@ -69,10 +69,25 @@ ATLAS_DEVICE void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, u
 
 // KV16: the cache holds bf16 (two bytes per element, same page layouts); queries, probabilities and the cache then meet
 // in bf16 MMAs and no scale applies.  Otherwise FP8 e4m3 bytes widened to f16.
-template <int D, bool PREFILL, bool KV16 = false>
+// KV4: NVFP4 cache.  A (block, kv head) page of K is [bs][D/2] packed e2m1 bytes (even dim in the low nibble) followed by
+// [bs][D/16] e4m3 scales (one per token and 16 dims); a page of V is [D][bs/2] packed bytes (even TOKEN in the low nibble)
+// followed by [D/16][bs] scales (one per token and 16 dims, token-contiguous).  Both pages are bs * D * 9 / 16 bytes.  K is
+// widened to f16 and multiplied by its scale element by element (a k-step spans four scale groups); V's scales depend on
+// the token only inside a 16-dim group, so they are folded into the P operand, once per two n-tiles.
+ATLAS_DEVICE uint32_t e2m1x2_to_f16x2(uint32_t byte) {
+  uint32_t r;
+  asm("{\n\t.reg .b8 b;\n\tcvt.u8.u32 b, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, b;\n\t}\n" : "=r"(r) : "r"(byte));
+  return r;
+}
+ATLAS_DEVICE uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+template <int D, bool PREFILL, bool KV16 = false, bool KV4 = false>
 __global__ void __launch_bounds__(128)
 paged_attn_kernel(const AttnParams p) {
-  constexpr int ES = KV16 ? 2 : 1;      // bytes per cache element
+  constexpr int ES = KV16 ? 2 : 1;      // bytes per cache element (KV4 computes its own offsets)
   constexpr int KS = D / 16;            // k-steps of QK^T
   constexpr int NT = D / 8;             // n-tiles of PV
   constexpr int DQ = D / 4;             // dims owned by one thread of a quad
@@ -165,6 +180,8 @@ paged_attn_kernel(const AttnParams p) {
     const int off = tok0 % bs;
     const uint8_t* kpage = p.k_cache + ((((long long)blk * p.Hkv + kvh) * bs + off) * D) * ES;
     const uint8_t* vpage = p.v_cache + (((long long)blk * p.Hkv + kvh) * (long long)D * bs + off) * ES;
+    // NVFP4: start of this (block, kv head)'s K and V pages
+    const long long page4 = ((long long)blk * p.Hkv + kvh) * ((long long)bs * D * 9 / 16);
 
     // ---- S = Q K^T for the 16 tokens of this page
     float s[2][4];
@@ -173,7 +190,24 @@ paged_attn_kernel(const AttnParams p) {
       s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
       const int tok_in_page = (rq >> 1) * 4 + 2 * i + (rq & 1);
       const uint4* krow = reinterpret_cast<const uint4*>(kpage + (tok_in_page * D + c * DQ) * ES);
-      if constexpr (KV16) {
+      if constexpr (KV4) {
+        // this thread's DQ dims of the token: DQ / 2 packed bytes and DQ / 16 scales (k-step ks uses bytes 2 ks, 2 ks + 1)
+        const uint8_t* kd = p.k_cache + page4 + (long long)(off + tok_in_page) * (D / 2) + c * (DQ / 2);
+        const uint8_t* ksc = p.k_cache + page4 + (long long)bs * (D / 2) + (long long)(off + tok_in_page) * (D / 16) + c * (DQ / 16);
+#pragma unroll
+        for (int g = 0; g < DQ / 16; ++g) {
+          const uint32_t s2 = fp8x2_to_f16x2((uint16_t)(ksc[g] * 0x0101u));          // the scale in both halves
+          const uint2 raw = __ldg(reinterpret_cast<const uint2*>(kd) + g);               // 16 dims = four k-steps
+          const uint32_t w[2] = {raw.x, raw.y};
+#pragma unroll
+          for (int wi = 0; wi < 4; ++wi) {
+            const uint32_t two = (w[wi >> 1] >> (16 * (wi & 1))) & 0xFFFFu;
+            const uint32_t b0 = hmul2_u32(e2m1x2_to_f16x2(two & 0xFFu), s2);
+            const uint32_t b1 = hmul2_u32(e2m1x2_to_f16x2(two >> 8), s2);
+            mma_f16(s[i], qf[g * 4 + wi], b0, b1);
+          }
+        }
+      } else if constexpr (KV16) {
 #pragma unroll
         for (int v4 = 0; v4 < DQ / 8; ++v4) {          // eight bf16 = two k-steps
           const uint4 raw = __ldg(krow + v4);
@@ -256,10 +290,27 @@ paged_attn_kernel(const AttnParams p) {
       }
     }
     // ---- O = alpha * O + P V
+    uint32_t pfs[4] = {pf[0], pf[1], pf[2], pf[3]};
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
       uint32_t b0, b1;
-      if constexpr (KV16) {
+      if constexpr (KV4) {
+        const uint32_t m0 = ((vmask & 0xFFu) ? 0xFFFFu : 0u) | ((vmask & 0xFF00u) ? 0xFFFF0000u : 0u);
+        const uint32_t m1 = ((vmask & 0xFF0000u) ? 0xFFFFu : 0u) | ((vmask & 0xFF000000u) ? 0xFFFF0000u : 0u);
+        if ((j & 1) == 0) {
+          // scales of this thread's four tokens for dims [8 j, 8 j + 16): folded into P (stale scale bytes of tokens past
+          // the end are masked like the data)
+          const uint32_t sw = __ldg(reinterpret_cast<const uint32_t*>(p.v_cache + page4 + (long long)D * (bs / 2) +
+                                                                       (long long)(j >> 1) * bs + off + c * 4)) & vmask;
+          const uint32_t s01 = fp8x2_to_f16x2((uint16_t)(sw & 0xFFFFu)), s23 = fp8x2_to_f16x2((uint16_t)(sw >> 16));
+          pfs[0] = hmul2_u32(pf[0], s01); pfs[1] = hmul2_u32(pf[1], s01);
+          pfs[2] = hmul2_u32(pf[2], s23); pfs[3] = hmul2_u32(pf[3], s23);
+        }
+        const uint32_t two = __ldg(reinterpret_cast<const uint16_t*>(p.v_cache + page4 + (long long)(j * 8 + rq) * (bs / 2) +
+                                                                      ((off + c * 4) >> 1)));
+        b0 = e2m1x2_to_f16x2(two & 0xFFu) & m0;
+        b1 = e2m1x2_to_f16x2(two >> 8) & m1;
+      } else if constexpr (KV16) {
         // four bf16 of one V^T row; vmask carries one byte flag per token, widened here to 16-bit lanes
         const uint2 w2 = __ldg(reinterpret_cast<const uint2*>(vpage + ((long long)(j * 8 + rq) * bs + c * 4) * 2));
         const uint32_t m0 = ((vmask & 0xFFu) ? 0xFFFFu : 0u) | ((vmask & 0xFF00u) ? 0xFFFF0000u : 0u);
@@ -273,7 +324,7 @@ paged_attn_kernel(const AttnParams p) {
       }
       o[j][0] *= alpha[0]; o[j][1] *= alpha[0];
       o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
-      if (KV16) mma_bf16(o[j], pf, b0, b1); else mma_f16(o[j], pf, b0, b1);
+      if (KV16) mma_bf16(o[j], pf, b0, b1); else if (KV4) mma_f16(o[j], pfs, b0, b1); else mma_f16(o[j], pf, b0, b1);
     }
   }
   // quad-reduce the row sums
@@ -1367,6 +1418,67 @@ static int launch_kv16(const AttnParams& p, int B, bool prefill, cudaStream_t st
     if (cudaGetLastError() != cudaSuccess) return -22;
   }
   return 0;
+}
+
+// ---- NVFP4 KV cache: the general kernel in both roles (page layout in the comment above paged_attn_kernel).
+template <int D>
+static int launch_kv4(const AttnParams& p, int B, bool prefill, cudaStream_t st) {
+  if (prefill) {
+    dim3 grid((p.num_tiles + 3) / 4, p.Hq);
+    paged_attn_kernel<D, true, false, true><<<grid, 128, 0, st>>>(p);
+    return cudaGetLastError() == cudaSuccess ? 0 : -21;
+  }
+  const int smem = (128 + 4 * 16 * D) * (int)sizeof(float);
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(paged_attn_kernel<D, false, false, true>), smem) != cudaSuccess) return -20;
+  dim3 grid(p.Hkv, p.num_splits, B);
+  paged_attn_kernel<D, false, false, true><<<grid, 128, smem, st>>>(p);
+  if (cudaGetLastError() != cudaSuccess) return -21;
+  if (p.num_splits > 1) {
+    dim3 g2(p.Hq, B);
+    attn_merge_kernel<<<g2, D, 0, st>>>(p.part_o, p.part_ml, p.out, p.ldo, p.query_start_loc, p.seq_base, p.Hq, D, p.num_splits,
+                                       p.v_scale, nullptr, 0, nullptr, 0);
+    if (cudaGetLastError() != cudaSuccess) return -22;
+  }
+  return 0;
+}
+
+// Same contracts as atlas_attn_decode / atlas_attn_prefill with an NVFP4 cache; k_scale / v_scale are the tensors' second
+// level (global) scales.  head_dim 128 or 256, block_size a multiple of 16.
+extern "C" int atlas_attn_decode_kv4(const void* q, long long ldq, void* out, long long ldo, const void* k_cache,
+                                     const void* v_cache, const int* block_tables, int bt_ld, const int* seq_lens,
+                                     const int* query_start_loc, int seq_base, int B, float scale, float k_scale, float v_scale,
+                                     int Hq, int Hkv, int D, int block_size, int window, int num_splits, float* part_o,
+                                     float* part_ml, void* stream) {
+  if (B <= 0) return 0;
+  if (D != 128 && D != 256) return -1;
+  AttnParams p;
+  int rc = fill_common(p, q, ldq, out, ldo, k_cache, v_cache, block_tables, bt_ld, seq_lens, query_start_loc, seq_base, scale,
+                       k_scale, v_scale, Hq, Hkv, D, block_size, window);
+  if (rc) return rc;
+  if (Hq / Hkv > 16) return -5;
+  p.num_splits = num_splits < 1 ? 1 : num_splits;
+  if (p.num_splits > 1 && (!part_o || !part_ml)) return -3;
+  p.part_o = part_o; p.part_ml = part_ml;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (D == 128) return launch_kv4<128>(p, B, false, st);
+  return launch_kv4<256>(p, B, false, st);
+}
+
+extern "C" int atlas_attn_prefill_kv4(const void* q, long long ldq, void* out, long long ldo, const void* k_cache,
+                                      const void* v_cache, const int* block_tables, int bt_ld, const int* seq_lens,
+                                      const int* query_start_loc, const int* tile_seq, const int* tile_q0, int num_tiles,
+                                      float scale, float k_scale, float v_scale, int Hq, int Hkv, int D, int block_size,
+                                      int window, void* stream) {
+  if (num_tiles <= 0) return 0;
+  if (D != 128 && D != 256) return -1;
+  AttnParams p;
+  int rc = fill_common(p, q, ldq, out, ldo, k_cache, v_cache, block_tables, bt_ld, seq_lens, query_start_loc, 0, scale, k_scale,
+                       v_scale, Hq, Hkv, D, block_size, window);
+  if (rc) return rc;
+  p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.num_tiles = num_tiles;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (D == 128) return launch_kv4<128>(p, 0, true, st);
+  return launch_kv4<256>(p, 0, true, st);
 }
 
 // Same contracts as atlas_attn_decode / atlas_attn_prefill with a bf16 cache (K [nb, Hkv, bs, D], V [nb, Hkv, D, bs]).

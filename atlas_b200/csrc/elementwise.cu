@@ -362,6 +362,42 @@ rope_kv_write_d128_kernel(const RopeKvParams p) {
     return;
   }
   const int blk = slot / p.block_size, tok_in_blk = slot % p.block_size;
+  if (p.kv_fp8 == 2) {
+    // ---- NVFP4 cache (page layout: see paged_attn_kernel): one e4m3 scale per token and 16 dims = four lanes
+    const float inv_g = is_k ? p.inv_k_scale : p.inv_v_scale;
+    float x[4];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { x[i] = o[i] * inv_g; amax = fmaxf(amax, fabsf(x[i])); }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const uint8_t s8 = f32_to_fp8_e4m3(amax * (1.f / 6.f));
+    const float sdq = fp8_e4m3_to_f32(s8);
+    const float inv = sdq > 0.f ? __frcp_rn(sdq) : 0.f;
+    uint16_t lo8, hi8;                                           // (x0, x1) and (x2, x3): the first value in the low nibble
+    asm("{\n\t.reg .b8 b;\n\tcvt.rn.satfinite.e2m1x2.f32 b, %2, %1;\n\tcvt.u16.u8 %0, b;\n\t}\n" : "=h"(lo8) : "f"(x[0] * inv), "f"(x[1] * inv));
+    asm("{\n\t.reg .b8 b;\n\tcvt.rn.satfinite.e2m1x2.f32 b, %2, %1;\n\tcvt.u16.u8 %0, b;\n\t}\n" : "=h"(hi8) : "f"(x[2] * inv), "f"(x[3] * inv));
+    const long long page = ((long long)blk * p.Hkv + hh) * ((long long)p.block_size * D * 9 / 16);
+    if (is_k) {
+      uint8_t* base = reinterpret_cast<uint8_t*>(p.k_cache) + page;
+      *reinterpret_cast<uint16_t*>(base + (long long)tok_in_blk * (D / 2) + d0 / 2) = (uint16_t)(lo8 | (hi8 << 8));
+      if ((lane & 3) == 0) base[(long long)p.block_size * (D / 2) + (long long)tok_in_blk * (D / 16) + (d0 >> 4)] = s8;
+    } else {
+      // V^T: dim-major, two TOKENS per byte -> the neighbouring token's nibble shares the byte: word-wide atomics
+      uint8_t* base = reinterpret_cast<uint8_t*>(p.v_cache) + page;
+      const uint32_t nib[4] = {lo8 & 0xFu, (lo8 >> 4) & 0xFu, hi8 & 0xFu, (hi8 >> 4) & 0xFu};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const long long byte = (long long)(d0 + i) * (p.block_size / 2) + (tok_in_blk >> 1);
+        unsigned int* word = reinterpret_cast<unsigned int*>(base + (byte & ~3ll));
+        const int shift = (int)(byte & 3) * 8 + (tok_in_blk & 1) * 4;
+        atomicAnd(word, ~(0xFu << shift));
+        atomicOr(word, nib[i] << shift);
+      }
+      if ((lane & 3) == 0) base[(long long)D * (p.block_size / 2) + (long long)(d0 >> 4) * p.block_size + tok_in_blk] = s8;
+    }
+    return;
+  }
   if (is_k) {
     const long long kbase = (((long long)blk * p.Hkv + hh) * p.block_size + tok_in_blk) * D + d0;
     if (p.kv_fp8) {
@@ -633,13 +669,14 @@ extern "C" int atlas_rope_kv_write(void* q, long long ldq, const void* k, long l
   p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.rotary_dim = rotary_dim; p.block_size = block_size;
   p.kv_fp8 = kv_fp8; p.plus_one = plus_one; p.eps = eps; p.inv_k_scale = 1.f / k_scale; p.inv_v_scale = 1.f / v_scale;
   // prefill-size batches with 16-token FP8 pages: V goes through the page-row writer (16-byte stores)
-  p.v_separate = (T >= 256 && kv_fp8 && block_size == 16 && D % 4 == 0 && (ldv % 4) == 0 &&
+  p.v_separate = (T >= 256 && kv_fp8 == 1 && block_size == 16 && D % 4 == 0 && (ldv % 4) == 0 &&
                   (reinterpret_cast<uintptr_t>(v) & 7) == 0) ? 1 : 0;
   const long long units = (long long)T * (Hq + (p.v_separate ? 1 : 2) * Hkv);
   const int grid = (int)((units + 3) / 4);
   const bool d128 = D == 128 && rotary_dim == 128 && (ldq % 4) == 0 && (ldk % 4) == 0 && (ldv % 4) == 0 &&
                     ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 7) == 0 &&
                     (reinterpret_cast<uintptr_t>(rope) & 15) == 0;
+  if (kv_fp8 == 2 && (!d128 || block_size % 16)) return -2;          // the NVFP4 cache is written by the head_dim-128 kernel only
   if (d128)
     launch_chain_if(T <= 256, rope_kv_write_d128_kernel, dim3(grid), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream), p);
   else

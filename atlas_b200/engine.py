@@ -120,6 +120,15 @@ class LLMEngine:
         want = self.cfg.kv_cache_dtype
         if want == "auto":
             want = self.mcfg.quant.kv_cache_dtype
+        if want == "nvfp4":
+            # packed e2m1 + e4m3 block scales: 0.56 bytes per element.  The cache writer and the attention kernel exist for
+            # head_dim 128 with full rotary width on the GPU; anything else keeps the FP8 cache.
+            ok = (self.model.device.type == "cuda" and self.mcfg.head_dim == 128 and self.mcfg.rotary_dim == 128
+                  and self.mcfg.kv_lora_rank == 0 and self.cfg.block_size % 16 == 0 and not self.cfg.sparse_attention_blocks)
+            if ok:
+                from .models.decoder import KV_NVFP4
+                return KV_NVFP4
+            want = "fp8"
         if want == "bf16":
             return torch.bfloat16           # GPU: the general mma.sync attention kernel on a 16-bit cache
         if want == "fp8" or (want == "auto" and self.model.device.type == "cuda"):

@@ -36,11 +36,25 @@ def kv_dtype_is_fp8(dtype) -> bool:
     return dtype == torch.float8_e4m3fn
 
 
+KV_NVFP4 = torch.uint8          # cache dtype marker of the NVFP4 KV cache (packed e2m1 + e4m3 scales, GPU only)
+
+
+def kv_dtype_is_quantised(dtype) -> bool:
+    return dtype == torch.float8_e4m3fn or dtype == KV_NVFP4
+
+
+def kv_element_bytes(dtype) -> float:
+    """Bytes per cached element (NVFP4: half a byte of data plus one scale byte per 16 elements)."""
+    return 9.0 / 16.0 if dtype == KV_NVFP4 else float(dtype.itemsize)
+
+
 def alloc_kv(num_blocks: int, block_size: int, hkv: int, d: int, dtype, device):
     """Paged K and V pools as logical ``[num_blocks, block_size, Hkv, D]`` tensors (the GPU pools are views
     of the kernels' physical layout)."""
-    if torch.device(device).type == "cuda" and (kv_dtype_is_fp8(dtype) or dtype == torch.bfloat16):
+    if torch.device(device).type == "cuda" and (kv_dtype_is_quantised(dtype) or dtype == torch.bfloat16):
         return ops.cuda_ops().alloc_kv_cache(num_blocks, block_size, hkv, d, dtype, device)
+    if dtype == KV_NVFP4:
+        raise ValueError("the NVFP4 KV cache exists on the GPU kernels only")
     shape = (num_blocks, block_size, hkv, d)
     return torch.zeros(shape, dtype=dtype, device=device), torch.zeros(shape, dtype=dtype, device=device)
 
@@ -324,17 +338,17 @@ class DecoderLM:
         hkv = self.layers[self.attention_layers()[0]].mixer.hkv if n_attn else 0
         n_hi = len([i for i in self.attention_layers() if i in set(high_precision_layers)])
         per = 2 * block_size * hkv * self.cfg.head_dim
-        return per * ((n_attn - n_hi) * kv_dtype.itemsize + n_hi * max(2, kv_dtype.itemsize))
+        return int(per * ((n_attn - n_hi) * kv_element_bytes(kv_dtype) + n_hi * max(2.0, kv_element_bytes(kv_dtype))))
 
     def alloc_cache(self, num_blocks: int, block_size: int, kv_dtype: torch.dtype, state_slots: int = 0,
                     high_precision_layers=()) -> CacheStore:
-        """``high_precision_layers``: attention layers whose cache stays in 16 bits when ``kv_dtype`` is FP8 (the layers
-        most sensitive to KV quantisation, typically the first and last ones)."""
+        """``high_precision_layers``: attention layers whose cache stays in 16 bits when ``kv_dtype`` is FP8 or NVFP4 (the
+        layers most sensitive to KV quantisation, typically the first and last ones)."""
         store = CacheStore(block_size=block_size, num_blocks=num_blocks)
         hi = set(high_precision_layers)
         for l in self.layers:
             if l.kind == "attention":
-                dt = (torch.bfloat16 if self.dtype == torch.bfloat16 else self.dtype) if (l.idx in hi and kv_dtype_is_fp8(kv_dtype)) else kv_dtype
+                dt = (torch.bfloat16 if self.dtype == torch.bfloat16 else self.dtype) if (l.idx in hi and kv_dtype_is_quantised(kv_dtype)) else kv_dtype
                 store.kv[l.idx] = alloc_kv(num_blocks, block_size, l.mixer.hkv, self.cfg.head_dim, dt, self.device)
                 store.kv_scales[l.idx] = (1.0, 1.0)
             elif l.kind in ("gdn", "mamba2"):

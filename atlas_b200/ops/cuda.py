@@ -436,10 +436,33 @@ def gemm_nvfp4(x, packed, bscale, gscale, out=None):
 
 
 # ----------------------------------------------------------------------------- KV cache + attention
+NVFP4_KV = "nvfp4"        # cache dtype tag: packed e2m1 bytes + e4m3 scales, a uint8 tensor
+
+
+def is_nvfp4_kv(k_cache: torch.Tensor) -> bool:
+    return k_cache.dtype == torch.uint8
+
+
+def nvfp4_kv_head_dim(k_cache: torch.Tensor) -> int:
+    """head_dim of an NVFP4 cache view ``[nb, bs, Hkv, D * 9 / 16]``."""
+    return k_cache.shape[3] * 16 // 9
+
+
 def alloc_kv_cache(num_blocks: int, block_size: int, hkv: int, d: int, dtype, device):
     """Physical layout K ``[nb, Hkv, bs, D]``, V ``[nb, Hkv, D, bs]``; both returned as logical
-    ``[nb, bs, Hkv, D]`` views so indexing code is layout-agnostic."""
+    ``[nb, bs, Hkv, D]`` views so indexing code is layout-agnostic.
+
+    ``dtype = "nvfp4"``: every (block, kv head) page is ``bs * D * 9 / 16`` bytes, packed e2m1 data followed by e4m3
+    scales (one per token and 16 dims; the arrangement inside a page is the kernels' business, see ``paged_attn_kernel``
+    in csrc/attention.cu).  The tensors are uint8 views of logical shape ``[nb, bs, Hkv, D * 9 / 16]``: block-level copies
+    (prefix cache, host tier) work on them like on any other cache, element indexing does not."""
     from ..utils import guards
+    if dtype == NVFP4_KV or dtype == torch.uint8:
+        assert d % 16 == 0 and block_size % 16 == 0
+        w = d * 9 // 16
+        k = guards.zeros("kv.k", (num_blocks, hkv, block_size, w), torch.uint8, device).permute(0, 2, 1, 3)
+        v = guards.zeros("kv.v", (num_blocks, hkv, w, block_size), torch.uint8, device).permute(0, 3, 1, 2)
+        return k, v
     k = guards.zeros("kv.k", (num_blocks, hkv, block_size, d), dtype, device).permute(0, 2, 1, 3)
     v = guards.zeros("kv.v", (num_blocks, hkv, d, block_size), dtype, device).permute(0, 3, 1, 2)
     return k, v
@@ -449,8 +472,8 @@ def _kv_layout_ok(k_cache: torch.Tensor, v_cache: torch.Tensor) -> None:
     nb, bs, hkv, d = k_cache.shape
     if k_cache.stride() != (hkv * bs * d, d, bs * d, 1) or v_cache.stride() != (hkv * bs * d, 1, d * bs, bs):
         raise KernelError("KV cache is not in the kernel layout (allocate it with ops.cuda.alloc_kv_cache)")
-    if k_cache.dtype not in (FP8, torch.bfloat16):
-        raise KernelError("the GPU attention kernels read an FP8 (e4m3) or bf16 KV cache")
+    if k_cache.dtype not in (FP8, torch.bfloat16, torch.uint8):
+        raise KernelError("the GPU attention kernels read an FP8 (e4m3), bf16 or NVFP4 KV cache")
 
 
 def qk_norm_rope_kv_write(q, k, v, positions, rope_cache, rotary_dim, k_cache, v_cache, slot_mapping, k_scale, v_scale,
@@ -462,12 +485,15 @@ def qk_norm_rope_kv_write(q, k, v, positions, rope_cache, rotary_dim, k_cache, v
     assert q.stride(2) == 1 and q.stride(1) == D and k.stride(1) == D and v.stride(1) == D
     assert positions.dtype == torch.int32 and slot_mapping.dtype == torch.int32 and rope_cache.dtype == torch.float32
     bs = k_cache.shape[1]
+    if is_nvfp4_kv(k_cache) and nvfp4_kv_head_dim(k_cache) != D:
+        raise KernelError("NVFP4 KV cache was allocated for a different head_dim")
+    kv_mode = 2 if is_nvfp4_kv(k_cache) else (1 if k_cache.dtype == FP8 else 0)
     if checked.ENABLED:
         checked.kv_write(slot_mapping, positions, k_cache.shape[0], bs, rope_cache.shape[0] if rotary_dim else 0)
     _check(lib().atlas_rope_kv_write(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
                                      positions.data_ptr(), rope_cache.data_ptr(), _ptr(q_norm_w), _ptr(k_norm_w),
                                      k_cache.data_ptr(), v_cache.data_ptr(), slot_mapping.data_ptr(), T, Hq, Hkv, D,
-                                     rotary_dim, bs, 1 if k_cache.dtype == FP8 else 0, 1 if norm_plus_one else 0, float(eps), float(k_scale),
+                                     rotary_dim, bs, kv_mode, 1 if norm_plus_one else 0, float(eps), float(k_scale),
                                      float(v_scale), _stream()), "rope_kv_write")
     return q
 
@@ -499,6 +525,8 @@ def paged_attention(q, k_cache, v_cache, batch, scale, k_scale, v_scale, sliding
         checked.paged_read(batch.block_tables, batch.seq_lens, k_cache.shape[0], k_cache.shape[1])
     if k_cache.dtype == torch.bfloat16:
         return _paged_attention_kv16(q, out, k_cache, v_cache, batch, scale, window, d)
+    if is_nvfp4_kv(k_cache):
+        return _paged_attention_kv16(q, out, k_cache, v_cache, batch, scale, window, d, scales=(float(k_scale), float(v_scale)))
     if nd > 0:
         splits = decode_splits(nd, Hkv, batch.max_seq_len, _num_sms[d])
         po = pml = None
@@ -585,11 +613,21 @@ def paged_attention_q8(q, k_cache, v_cache, batch, scale, k_scale, v_scale, slid
     return qo, so
 
 
-def _paged_attention_kv16(q, out, k_cache, v_cache, batch, scale, window, d):
-    """bf16 KV cache: the general mma.sync kernel serves decode rows (split-K + merge) and prefill tiles."""
+def _paged_attention_kv16(q, out, k_cache, v_cache, batch, scale, window, d, scales=None):
+    """bf16 KV cache (or, with ``scales = (k_scale, v_scale)``, an NVFP4 one): the general mma.sync kernel serves decode
+    rows (split-K + merge) and prefill tiles."""
     T, Hq, D = q.shape
     nb, bs, Hkv, _ = k_cache.shape
     L = lib()
+    fp4 = scales is not None
+    if fp4 and not getattr(L, "_kv4_bound", False):
+        L.atlas_attn_decode_kv4.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _f, _f, _f, _i, _i, _i, _i, _i,
+                                            _i, _vp, _vp, _vp]
+        L.atlas_attn_prefill_kv4.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _f, _f, _f, _i, _i, _i,
+                                             _i, _i, _vp]
+        L._kv4_bound = True
+    if fp4 and D not in (128,):
+        raise KernelError("the NVFP4 KV cache is implemented for head_dim 128")
     if not getattr(L, "_kv16_bound", False):
         L.atlas_attn_decode_kv16.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _f, _i, _i, _i, _i, _i, _i,
                                              _vp, _vp, _vp]
@@ -602,10 +640,16 @@ def _paged_attention_kv16(q, out, k_cache, v_cache, batch, scale, window, d):
         if splits > 1:
             po = scratch("attn_part_o", nd * Hq * splits * D * 4, q.device)
             pml = scratch("attn_part_ml", nd * Hq * splits * 2 * 4, q.device)
-        _check(L.atlas_attn_decode_kv16(q.data_ptr(), q.stride(0), out.data_ptr(), Hq * D, k_cache.data_ptr(), v_cache.data_ptr(),
-                                        bt.data_ptr(), bt.stride(0), batch.seq_lens.data_ptr(), batch.query_start_loc.data_ptr(),
-                                        0, nd, float(scale), Hq, Hkv, D, bs, window, splits, _ptr(po), _ptr(pml), st),
-               "attn_decode_kv16")
+        if fp4:
+            _check(L.atlas_attn_decode_kv4(q.data_ptr(), q.stride(0), out.data_ptr(), Hq * D, k_cache.data_ptr(), v_cache.data_ptr(),
+                                           bt.data_ptr(), bt.stride(0), batch.seq_lens.data_ptr(), batch.query_start_loc.data_ptr(),
+                                           0, nd, float(scale), scales[0], scales[1], Hq, Hkv, D, bs, window, splits, _ptr(po),
+                                           _ptr(pml), st), "attn_decode_kv4")
+        else:
+            _check(L.atlas_attn_decode_kv16(q.data_ptr(), q.stride(0), out.data_ptr(), Hq * D, k_cache.data_ptr(), v_cache.data_ptr(),
+                                            bt.data_ptr(), bt.stride(0), batch.seq_lens.data_ptr(), batch.query_start_loc.data_ptr(),
+                                            0, nd, float(scale), Hq, Hkv, D, bs, window, splits, _ptr(po), _ptr(pml), st),
+                   "attn_decode_kv16")
     if batch.num_seqs > nd:
         tiles = getattr(batch, "_attn_tiles", None)
         if tiles is None:
@@ -618,10 +662,16 @@ def _paged_attention_kv16(q, out, k_cache, v_cache, batch, scale, window, d):
             tiles = (host.to(q.device, non_blocking=True), len(ts))
             batch._attn_tiles = tiles
         tdev, n_tiles = tiles
-        _check(L.atlas_attn_prefill_kv16(q.data_ptr(), q.stride(0), out.data_ptr(), Hq * D, k_cache.data_ptr(), v_cache.data_ptr(),
-                                         bt.data_ptr(), bt.stride(0), batch.seq_lens.data_ptr(), batch.query_start_loc.data_ptr(),
-                                         tdev[0].data_ptr(), tdev[1].data_ptr(), n_tiles, float(scale), Hq, Hkv, D, bs, window, st),
-               "attn_prefill_kv16")
+        if fp4:
+            _check(L.atlas_attn_prefill_kv4(q.data_ptr(), q.stride(0), out.data_ptr(), Hq * D, k_cache.data_ptr(), v_cache.data_ptr(),
+                                            bt.data_ptr(), bt.stride(0), batch.seq_lens.data_ptr(), batch.query_start_loc.data_ptr(),
+                                            tdev[0].data_ptr(), tdev[1].data_ptr(), n_tiles, float(scale), scales[0], scales[1], Hq,
+                                            Hkv, D, bs, window, st), "attn_prefill_kv4")
+        else:
+            _check(L.atlas_attn_prefill_kv16(q.data_ptr(), q.stride(0), out.data_ptr(), Hq * D, k_cache.data_ptr(), v_cache.data_ptr(),
+                                             bt.data_ptr(), bt.stride(0), batch.seq_lens.data_ptr(), batch.query_start_loc.data_ptr(),
+                                             tdev[0].data_ptr(), tdev[1].data_ptr(), n_tiles, float(scale), Hq, Hkv, D, bs, window, st),
+                   "attn_prefill_kv16")
     return out
 
 

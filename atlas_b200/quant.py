@@ -215,3 +215,35 @@ def quantize_mlx(w: torch.Tensor, bits: int = 4, group_size: int = 64):
     packed = (q.view(N, K // per, per) << shifts).sum(-1)
     packed = torch.where(packed >= (1 << 31), packed - (1 << 32), packed).to(torch.int32)
     return packed, scale, mn
+
+
+# ----------------------------------------------------------------------------- NVFP4 KV cache pages
+_E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def _e2m1_to_float(nibbles: torch.Tensor) -> torch.Tensor:
+    lut = torch.tensor(_E2M1_VALUES + tuple(-v for v in _E2M1_VALUES), dtype=torch.float32, device=nibbles.device)
+    return lut[nibbles.long()]
+
+
+def dequantize_nvfp4_kv(k_cache: torch.Tensor, v_cache: torch.Tensor, head_dim: int):
+    """The logical ``[nb, bs, Hkv, D]`` fp32 contents of an NVFP4 KV cache (uint8 views as allocated by
+    ``ops.cuda.alloc_kv_cache(..., "nvfp4", ...)``), WITHOUT the tensors' second-level scales.
+
+    Page of K per (block, kv head): ``[bs][D/2]`` packed e2m1 (even dim in the low nibble) then ``[bs][D/16]`` e4m3 scales;
+    page of V: ``[D][bs/2]`` packed (even token in the low nibble) then ``[D/16][bs]`` scales.  The oracle of the kernel
+    tests; reference parity: ``kernels/gb10/common/reshape_and_cache.cu`` (nvfp4 entry), ``paged_decode_attn_nvfp4.cu``."""
+    nb, bs, hkv, w = k_cache.shape
+    D = head_dim
+    assert w == D * 9 // 16
+    kp = k_cache.permute(0, 2, 1, 3).reshape(nb, hkv, bs * w)
+    kd = kp[..., :bs * D // 2].reshape(nb, hkv, bs, D // 2)
+    ks = kp[..., bs * D // 2:].reshape(nb, hkv, bs, D // 16).contiguous().view(torch.float8_e4m3fn).float()
+    kv = torch.stack([_e2m1_to_float(kd & 0xF), _e2m1_to_float(kd >> 4)], -1).reshape(nb, hkv, bs, D)
+    K = (kv.view(nb, hkv, bs, D // 16, 16) * ks[..., None]).reshape(nb, hkv, bs, D).permute(0, 2, 1, 3)
+    vp = v_cache.permute(0, 2, 3, 1).reshape(nb, hkv, w * bs)
+    vd = vp[..., :D * bs // 2].reshape(nb, hkv, D, bs // 2)
+    vs = vp[..., D * bs // 2:].reshape(nb, hkv, D // 16, bs).contiguous().view(torch.float8_e4m3fn).float()
+    vv = torch.stack([_e2m1_to_float(vd & 0xF), _e2m1_to_float(vd >> 4)], -1).reshape(nb, hkv, D, bs)
+    V = (vv.view(nb, hkv, D // 16, 16, bs) * vs[:, :, :, None, :]).reshape(nb, hkv, D, bs).permute(0, 3, 1, 2)
+    return K.contiguous(), V.contiguous()

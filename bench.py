@@ -149,6 +149,7 @@ def main():
     ap.add_argument("--ep-mode", default="auto", choices=["auto", "allreduce", "alltoall"],
                     help="expert-parallel data path: local experts + fused combine/all-reduce, or peer-memory all-to-all")
     ap.add_argument("--ngram-speculative", action="store_true", help="prompt-lookup drafts (no draft model), --num-drafts deep")
+    ap.add_argument("--kv-cache-dtype", default="fp8", choices=["fp8", "bf16", "nvfp4"], help="paged KV cache dtype (the headline uses fp8)")
     ap.add_argument("--self-speculative", action="store_true", help="layer-skipping drafts from the target model itself")
     ap.add_argument("--nvfp4-activations", action="store_true",
                     help="NVFP4 checkpoints: quantise activations to NVFP4 too (block-scaled FP4 x FP4 tensor-core GEMM)")
@@ -216,7 +217,7 @@ def main():
                         num_drafts=args.num_drafts if (args.speculative or args.ngram_speculative or args.self_speculative) else 0,
                         ssm_cache_slots=args.ssm_cache_slots or max(16, args.concurrency + 8),
                         **({"ssm_checkpoint_interval": args.ssm_checkpoint_interval} if args.ssm_checkpoint_interval else {}),
-                        use_cuda_graphs=not args.no_graphs, tp_size=world)
+                        use_cuda_graphs=not args.no_graphs, tp_size=world, kv_cache_dtype=args.kv_cache_dtype)
     eng = LLMEngine(model, ecfg)
     eng.time_device = True
     sp = SamplingParams(max_tokens=args.osl, temperature=0.0, ignore_eos=True)
@@ -305,6 +306,8 @@ def main():
     dtype_desc = {"fp8_block": "fp8-e4m3 weights (128x128 scales) + fp8 KV, bf16 activations",
                   "nvfp4": "nvfp4 weights (e2m1, e4m3 scale per 16, fp32 global)" + (" for experts, bf16 elsewhere" if mcfg.quant.experts_only else "") + " + fp8 KV, bf16 activations",
                   }.get(qm, "bf16 weights + fp8 KV")
+    if args.kv_cache_dtype != "fp8":
+        dtype_desc = dtype_desc.replace("fp8 KV", f"{args.kv_cache_dtype} KV")
     quant_desc = {"fp8_block": " quantized to fp8 block-scaled", "nvfp4": " quantized to nvfp4"}.get(qm, "")
     if rank == 0:
         value = tokens / dev_s if dev_s > 0 else 0.0

@@ -390,6 +390,63 @@ def test_attention_decode_e4m3_tiles(K, D, Hq, Hkv):
         L.atlas_attn_set_decode_f8(0)
 
 
+def test_nvfp4_kv_cache_write_and_attention(K):
+    """NVFP4 KV cache: the fused RoPE + cache-write kernel packs K and V (e2m1 + one e4m3 scale per token and 16 dims),
+    the result dequantises to the written rows within the format's precision, and decode rows, split-K decode and prefill
+    chunks over that cache agree with an fp32 attention over the dequantised contents."""
+    from atlas_b200 import quant as Q
+    from atlas_b200.models.batch import ForwardBatch
+    torch.manual_seed(33)
+    D, Hq, Hkv, bs = 128, 8, 2, 16
+    ctxs, qlens = [0, 0, 0, 0], [700, 33, 16, 130]
+    nblk = [(c + q + 1 + bs - 1) // bs + 1 for c, q in zip(ctxs, qlens)]
+    nb = sum(nblk) + 2
+    perm = torch.randperm(nb).tolist()
+    tables, off = [], 0
+    for n in nblk:
+        tables.append(perm[off:off + n])
+        off += n
+    kc, vc = K.alloc_kv_cache(nb, bs, Hkv, D, K.NVFP4_KV, DEV)
+    kc16, vc16 = K.alloc_kv_cache(nb, bs, Hkv, D, torch.bfloat16, DEV)
+    rope = ref.build_rope_cache(D, 2048, 1e4, None, DEV)
+    ks_g, vs_g = 0.02, 0.03                                    # second-level scales of the two tensors
+    # ---- prefill: write every prompt row, then attend
+    fb = ForwardBatch.build([[0] * q for q in qlens], ctxs, tables, bs, device=DEV)
+    T = sum(qlens)
+    qkv = (torch.randn(T, (Hq + 2 * Hkv) * D, device=DEV) * 0.6).bfloat16()
+    sl = lambda a, n: qkv[:, a * D:(a + n) * D].view(T, n, D)
+    q, k, v = sl(0, Hq), sl(Hq, Hkv), sl(Hq + Hkv, Hkv)
+    q16 = q.clone()
+    qr = K.qk_norm_rope_kv_write(q, k, v, fb.positions, rope, D, kc, vc, fb.slot_mapping, ks_g, vs_g, None, None, 1e-6, False)
+    K.qk_norm_rope_kv_write(q16, k, v, fb.positions, rope, D, kc16, vc16, fb.slot_mapping, 1.0, 1.0, None, None, 1e-6, False)
+    _status_ok(K)
+    Kd, Vd = Q.dequantize_nvfp4_kv(kc, vc, D)
+    slots = fb.slot_mapping.long()
+    got_k = Kd.reshape(nb * bs, Hkv, D)[slots] * ks_g
+    want_k = kc16.reshape(nb * bs, Hkv, D)[slots].float()
+    got_v = Vd.reshape(nb * bs, Hkv, D)[slots] * vs_g
+    want_v = vc16.reshape(nb * bs, Hkv, D)[slots].float()
+    assert _rel_rms(got_k, want_k) < 0.12 and _rel_rms(got_v, want_v) < 0.12        # e2m1: three significant bits at best
+    out = K.paged_attention(qr, kc, vc, fb, D ** -0.5, ks_g, vs_g, None)
+    want = ref.paged_attention(qr, Kd, Vd, fb.block_tables, fb.seq_lens, fb.query_start_loc, D ** -0.5, ks_g, vs_g, None)
+    _status_ok(K)
+    assert _rel_rms(out, want) < 2e-2
+    # ---- one more token per sequence (decode rows; the 700-token sequence takes the split-K path)
+    fb2 = ForwardBatch.build([[0]] * 4, qlens, tables, bs, device=DEV)
+    qkv2 = (torch.randn(4, (Hq + 2 * Hkv) * D, device=DEV) * 0.6).bfloat16()
+    sl2 = lambda a, n: qkv2[:, a * D:(a + n) * D].view(4, n, D)
+    q2 = K.qk_norm_rope_kv_write(sl2(0, Hq), sl2(Hq, Hkv), sl2(Hq + Hkv, Hkv), fb2.positions, rope, D, kc, vc, fb2.slot_mapping,
+                                 ks_g, vs_g, None, None, 1e-6, False)
+    Kd, Vd = Q.dequantize_nvfp4_kv(kc, vc, D)
+    out2 = K.paged_attention(q2, kc, vc, fb2, D ** -0.5, ks_g, vs_g, None)
+    want2 = ref.paged_attention(q2, Kd, Vd, fb2.block_tables, fb2.seq_lens, fb2.query_start_loc, D ** -0.5, ks_g, vs_g, None)
+    _status_ok(K)
+    assert _rel_rms(out2, want2) < 2e-2
+    # the earlier rows were not disturbed by the second write (neighbouring tokens share bytes of V)
+    got_v2 = Vd.reshape(nb * bs, Hkv, D)[slots] * vs_g
+    assert torch.equal(got_v2, got_v)
+
+
 def test_attention_decode_long_splitk(K):
     out, want = _attention_case(K, 128, 8, 1, qlens=[1, 1], ctxs=[5000, 9000])
     assert _rel_rms(out, want) < 2e-2
