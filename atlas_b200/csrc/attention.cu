@@ -710,13 +710,15 @@ attn_decode_kernel(const AttnParams p, int stages, status_t* status) {
 // the 2 KB K and V blocks of a page at ~26 KB/us per SM whatever the ring depth; 16-byte copies issued by all 128 threads
 // stream the same bytes at ~32 KB/us per SM (`microbench --only stream`).
 constexpr int kCpThreads = 128;
-template <int D, int BS, int kCpDepth>       // BS: block size known at compile time (0 = runtime)
+// KV4: NVFP4 pages (layout above paged_attn_kernel): 9/16 of the bytes per page; K is widened and scaled element by
+// element, V's per-token scales are folded into the P operand once per 16-dim tile.
+template <int D, int BS, int kCpDepth, bool KV4 = false>       // BS: block size known at compile time (0 = runtime)
 __global__ void __launch_bounds__(kCpThreads)
 attn_decode_cp_kernel(const AttnParams p) {
   constexpr int KS = D / 16, MT = D / 16, DQ = D / 4;
   extern __shared__ __align__(128) uint8_t dsm[];
   const int bs = BS ? BS : p.block_size;
-  const int stage_bytes = 2 * bs * D;
+  const int stage_bytes = KV4 ? 2 * (bs * D * 9 / 16) : 2 * bs * D;
   int* bt_sm = reinterpret_cast<int*>(dsm);
   uint8_t* ring = dsm + kBtSmemEntries * 4;
 
@@ -772,7 +774,7 @@ attn_decode_cp_kernel(const AttnParams p) {
     // this warp's pages: i = warp + 4 k, slot k % kCpDepth of its private ring
     uint8_t* myring = ring + (size_t)warp * kCpDepth * stage_bytes;
     const int n_w = n_mine > warp ? (n_mine - warp + 3) / 4 : 0;
-    const int half_bytes = bs * D;
+    const int half_bytes = KV4 ? bs * D * 9 / 16 : bs * D;          // one page of K or of V
     auto issue = [&](int k) {
       const int i = warp + 4 * k;
       const int blk = i < kBtSmemEntries ? bt_sm[i] : bt[i];
@@ -797,7 +799,7 @@ attn_decode_cp_kernel(const AttnParams p) {
       __syncwarp();
       const int i = warp + 4 * k;
       const uint8_t* kblk = myring + (size_t)(k % kCpDepth) * stage_bytes;
-      const uint8_t* vblk = kblk + bs * D;
+      const uint8_t* vblk = kblk + half_bytes;
       const int blk_tok0 = (blk_lo + i) * bs;
 #pragma unroll 1
       for (int sub = 0; sub * 16 < bs; ++sub) {
@@ -807,6 +809,27 @@ attn_decode_cp_kernel(const AttnParams p) {
         float s[4] = {0.f, 0.f, 0.f, 0.f};
         const uint4* k0 = reinterpret_cast<const uint4*>(kblk + (sub * 16 + tok_r0) * D + c * DQ);
         const uint4* k1 = reinterpret_cast<const uint4*>(kblk + (sub * 16 + tok_r1) * D + c * DQ);
+        if constexpr (KV4) {
+          const int ta = sub * 16 + tok_r0, tb = sub * 16 + tok_r1;
+          const uint8_t* ka = kblk + ta * (D / 2) + c * (DQ / 2);
+          const uint8_t* kb = kblk + tb * (D / 2) + c * (DQ / 2);
+          const uint8_t* sa = kblk + bs * (D / 2) + ta * (D / 16) + c * (DQ / 16);
+          const uint8_t* sb = kblk + bs * (D / 2) + tb * (D / 16) + c * (DQ / 16);
+#pragma unroll
+          for (int g = 0; g < DQ / 16; ++g) {
+            const uint32_t s2a = fp8x2_to_f16x2((uint16_t)(sa[g] * 0x0101u)), s2b = fp8x2_to_f16x2((uint16_t)(sb[g] * 0x0101u));
+            const uint2 ra = reinterpret_cast<const uint2*>(ka)[g], rb = reinterpret_cast<const uint2*>(kb)[g];
+            const uint32_t wa[2] = {ra.x, ra.y}, wb[2] = {rb.x, rb.y};
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+              const uint32_t ta2 = (wa[wi >> 1] >> (16 * (wi & 1))) & 0xFFFFu, tb2 = (wb[wi >> 1] >> (16 * (wi & 1))) & 0xFFFFu;
+              uint32_t a[4];
+              a[0] = hmul2_u32(e2m1x2_to_f16x2(ta2 & 0xFFu), s2a); a[2] = hmul2_u32(e2m1x2_to_f16x2(ta2 >> 8), s2a);
+              a[1] = hmul2_u32(e2m1x2_to_f16x2(tb2 & 0xFFu), s2b); a[3] = hmul2_u32(e2m1x2_to_f16x2(tb2 >> 8), s2b);
+              mma_f16(s, a, qb[g * 4 + wi][0], qb[g * 4 + wi][1]);
+            }
+          }
+        } else
 #pragma unroll
         for (int v4 = 0; v4 < DQ / 16; ++v4) {
           const uint4 ra = k0[v4], rb = k1[v4];
@@ -865,6 +888,28 @@ attn_decode_cp_kernel(const AttnParams p) {
         const bool rescale = __any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f);
         // ---- O^T += V^T P^T : rows = dims, k = tokens
         const uint8_t* vsub = vblk + sub * 16 + c * 4;
+        if constexpr (KV4) {
+          const uint32_t m0 = ((vmask & 0xFFu) ? 0xFFFFu : 0u) | ((vmask & 0xFF00u) ? 0xFFFF0000u : 0u);
+          const uint32_t m1 = ((vmask & 0xFF0000u) ? 0xFFFFu : 0u) | ((vmask & 0xFF000000u) ? 0xFFFF0000u : 0u);
+          const uint8_t* vd = vblk + ((sub * 16 + c * 4) >> 1);                       // two tokens per byte
+          const uint8_t* vsc = vblk + D * (bs / 2) + sub * 16 + c * 4;                // [D/16][bs] scales
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const uint32_t sw = *reinterpret_cast<const uint32_t*>(vsc + mt * bs) & vmask;
+            const uint32_t pbs0 = hmul2_u32(pb0, fp8x2_to_f16x2((uint16_t)(sw & 0xFFFFu)));
+            const uint32_t pbs1 = hmul2_u32(pb1, fp8x2_to_f16x2((uint16_t)(sw >> 16)));
+            const uint32_t w0 = *reinterpret_cast<const uint16_t*>(vd + (mt * 16 + rq) * (bs / 2));
+            const uint32_t w1 = *reinterpret_cast<const uint16_t*>(vd + (mt * 16 + rq + 8) * (bs / 2));
+            uint32_t a[4];
+            a[0] = e2m1x2_to_f16x2(w0 & 0xFFu) & m0; a[2] = e2m1x2_to_f16x2(w0 >> 8) & m1;
+            a[1] = e2m1x2_to_f16x2(w1 & 0xFFu) & m0; a[3] = e2m1x2_to_f16x2(w1 >> 8) & m1;
+            if (rescale) {
+              o[mt][0] *= alpha[0]; o[mt][1] *= alpha[1];
+              o[mt][2] *= alpha[0]; o[mt][3] *= alpha[1];
+            }
+            mma_f16(o[mt], a, pbs0, pbs1);
+          }
+        } else
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           const uint32_t w0 = *reinterpret_cast<const uint32_t*>(vsub + (mt * 16 + rq) * bs) & vmask;
@@ -1266,15 +1311,15 @@ static int decode_cp_depth() {
   return v;
 }
 
-template <int D, int BS, int kCpDepth>
+template <int D, int BS, int kCpDepth, bool KV4 = false>
 static int launch_decode_cp(const AttnParams& p, int B, cudaStream_t st) {
-  const int stage_bytes = 2 * p.block_size * D;
+  const int stage_bytes = KV4 ? 2 * (p.block_size * D * 9 / 16) : 2 * p.block_size * D;
   const int merge_bytes = (64 + 4 * 8 * D + 8) * (int)sizeof(float);
   const int ring_bytes = 4 * kCpDepth * stage_bytes > merge_bytes ? 4 * kCpDepth * stage_bytes : merge_bytes;
   const int smem = kBtSmemEntries * 4 + ring_bytes;
-  if (ensure_dynamic_smem(reinterpret_cast<const void*>(attn_decode_cp_kernel<D, BS, kCpDepth>), smem) != cudaSuccess) return -20;
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(attn_decode_cp_kernel<D, BS, kCpDepth, KV4>), smem) != cudaSuccess) return -20;
   dim3 grid(p.Hkv, p.num_splits, B);
-  if (launch_chain(attn_decode_cp_kernel<D, BS, kCpDepth>, grid, dim3(kCpThreads), (size_t)smem, st, p) != cudaSuccess) return -21;
+  if (launch_chain(attn_decode_cp_kernel<D, BS, kCpDepth, KV4>, grid, dim3(kCpThreads), (size_t)smem, st, p) != cudaSuccess) return -21;
   if (p.num_splits > 1) {
     dim3 g2(p.Hq, B);
     if (launch_chain(attn_merge_kernel, g2, dim3(D), 0, st, p.part_o, p.part_ml, p.out, p.ldo, p.query_start_loc, p.seq_base,
@@ -1427,6 +1472,11 @@ static int launch_kv4(const AttnParams& p, int B, bool prefill, cudaStream_t st)
     dim3 grid((p.num_tiles + 3) / 4, p.Hq);
     paged_attn_kernel<D, true, false, true><<<grid, 128, 0, st>>>(p);
     return cudaGetLastError() == cudaSuccess ? 0 : -21;
+  }
+  // decode rows: the cp.async pipeline with NVFP4 pages when the warp rings fit, the general kernel otherwise
+  if (4 * 3 * 2 * (p.block_size * D * 9 / 16) <= 96 * 1024 && p.Hq / p.Hkv <= 8) {
+    if (p.block_size == 16) return launch_decode_cp<D, 16, 3, true>(p, B, st);
+    return launch_decode_cp<D, 0, 3, true>(p, B, st);
   }
   const int smem = (128 + 4 * 16 * D) * (int)sizeof(float);
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(paged_attn_kernel<D, false, false, true>), smem) != cudaSuccess) return -20;
