@@ -704,6 +704,30 @@ attn_decode_kernel(const AttnParams p, int stages, status_t* status) {
   decode_merge_store<D>(p, ring, o, m_run, l_run, warp, lane, G, kvh, split, b, q_row0, 1.f);
 }
 
+// ---- e4m3 tensor-core tiles (used by the e4m3 decode variants below)
+ATLAS_DEVICE void mma_e4m3(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// two floats -> two e4m3 bytes (`lo` in bits 7..0, `hi` in bits 15..8) and back
+ATLAS_DEVICE uint32_t pack_e4m3x2(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+ATLAS_DEVICE float2 unpack_e4m3x2(uint32_t v) {
+  const uint32_t h = fp8x2_to_f16x2(static_cast<uint16_t>(v));
+  return __half22float2(*reinterpret_cast<const __half2*>(&h));
+}
+// (x0, x1) as a leading e4m3 pair and the e4m3 pair of what the first one missed
+ATLAS_DEVICE void split_e4m3x2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+  hi = pack_e4m3x2(x0, x1);
+  const float2 back = unpack_e4m3x2(hi);
+  lo = pack_e4m3x2(x0 - back.x, x1 - back.y);
+}
+
 // The same tiles fed by per-thread 16-byte asynchronous copies instead of the bulk-copy engine: every warp streams its own
 // pages (page i of the CTA's range goes to warp i % 4) through a private ring of kCpDepth slots (2 or 3) and waits for them with
 // cp.async.wait_group, so there is no producer warp, no mbarrier and no wait that could run out.  The copy engine moves
@@ -712,10 +736,14 @@ attn_decode_kernel(const AttnParams p, int stages, status_t* status) {
 constexpr int kCpThreads = 128;
 // KV4: NVFP4 pages (layout above paged_attn_kernel): 9/16 of the bytes per page; K is widened and scaled element by
 // element, V's per-token scales are folded into the P operand once per 16-dim tile.
-template <int D, int BS, int kCpDepth, bool KV4 = false>       // BS: block size known at compile time (0 = runtime)
+// F8: FP8 pages go to e4m3 tensor-core tiles as they are (mma.m16n8k32, no widening); Q and P, which are not cached bytes,
+// are fed as two e4m3 terms each (see attn_decode_f8_kernel).  One page per step: the upper half of the 32-wide k
+// dimension of the PV product stays zero, which costs tensor-pipe slots this kernel has to spare.
+template <int D, int BS, int kCpDepth, bool KV4 = false, bool F8 = false>       // BS: block size known at compile time (0 = runtime)
 __global__ void __launch_bounds__(kCpThreads)
 attn_decode_cp_kernel(const AttnParams p) {
   constexpr int KS = D / 16, MT = D / 16, DQ = D / 4;
+  constexpr float kPScale = 256.f;
   extern __shared__ __align__(128) uint8_t dsm[];
   const int bs = BS ? BS : p.block_size;
   const int stage_bytes = KV4 ? 2 * (bs * D * 9 / 16) : 2 * bs * D;
@@ -767,6 +795,45 @@ attn_decode_cp_kernel(const AttnParams p) {
         qb[ks][1] = pack_f16x2(v[2], v[3]);
       }
     }
+    // e4m3 form of Q^T: k index 4c+j of k-step ks8 is dim c*DQ + ks8*8 + j, k index 16+4c+j is dim c*DQ + ks8*8 + 4 + j
+    uint32_t qh[F8 ? D / 32 : 1][2], ql[F8 ? D / 32 : 1][2];
+    float sq[2] = {1.f, 1.f};
+    if constexpr (F8) {
+      float qv[DQ];
+      float amax = 0.f;
+      if (rq < G) {
+        const __nv_bfloat16* qrow = p.q + (long long)q_row0 * p.ldq + (kvh * G + rq) * D + c * DQ;
+#pragma unroll
+        for (int j = 0; j < DQ; j += 4) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(qrow + j);
+          const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+          const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+          qv[j] = __low2float(lo) * p.qk_scale_log2; qv[j + 1] = __high2float(lo) * p.qk_scale_log2;
+          qv[j + 2] = __low2float(hi) * p.qk_scale_log2; qv[j + 3] = __high2float(hi) * p.qk_scale_log2;
+        }
+#pragma unroll
+        for (int j = 0; j < DQ; ++j) amax = fmaxf(amax, fabsf(qv[j]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < DQ; ++j) qv[j] = 0.f;
+      }
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      const float qs = fmaxf(amax, 1e-30f) * (1.f / 448.f);
+      const float qinv = __frcp_rn(qs);
+#pragma unroll
+      for (int k8 = 0; k8 < D / 32; ++k8)
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+          uint32_t h0, l0, h1, l1;
+          split_e4m3x2(qv[k8 * 8 + w * 4 + 0] * qinv, qv[k8 * 8 + w * 4 + 1] * qinv, h0, l0);
+          split_e4m3x2(qv[k8 * 8 + w * 4 + 2] * qinv, qv[k8 * 8 + w * 4 + 3] * qinv, h1, l1);
+          qh[k8][w] = h0 | (h1 << 16);
+          ql[k8][w] = l0 | (l1 << 16);
+        }
+      sq[0] = __shfl_sync(0xffffffffu, qs, (2 * c) * 4);
+      sq[1] = __shfl_sync(0xffffffffu, qs, (2 * c + 1) * 4);
+    }
     const int win_lo = p.window > 0 ? L - 1 - p.window : -1;  // tokens <= win_lo are outside the window
     // this thread's two token rows inside a page
     const int tok_r0 = (rq >> 1) * 4 + (rq & 1);
@@ -809,7 +876,21 @@ attn_decode_cp_kernel(const AttnParams p) {
         float s[4] = {0.f, 0.f, 0.f, 0.f};
         const uint4* k0 = reinterpret_cast<const uint4*>(kblk + (sub * 16 + tok_r0) * D + c * DQ);
         const uint4* k1 = reinterpret_cast<const uint4*>(kblk + (sub * 16 + tok_r1) * D + c * DQ);
-        if constexpr (KV4) {
+        if constexpr (F8) {
+#pragma unroll
+          for (int v4 = 0; v4 < DQ / 16; ++v4) {
+            const uint4 ra = k0[v4], rb = k1[v4];
+            const uint32_t wa[4] = {ra.x, ra.y, ra.z, ra.w};
+            const uint32_t wb[4] = {rb.x, rb.y, rb.z, rb.w};
+#pragma unroll
+            for (int hk = 0; hk < 2; ++hk) {
+              const uint32_t a[4] = {wa[2 * hk], wb[2 * hk], wa[2 * hk + 1], wb[2 * hk + 1]};
+              mma_e4m3(s, a, qh[v4 * 2 + hk][0], qh[v4 * 2 + hk][1]);
+              mma_e4m3(s, a, ql[v4 * 2 + hk][0], ql[v4 * 2 + hk][1]);
+            }
+          }
+          s[0] *= sq[0]; s[1] *= sq[1]; s[2] *= sq[0]; s[3] *= sq[1];
+        } else if constexpr (KV4) {
           const int ta = sub * 16 + tok_r0, tb = sub * 16 + tok_r1;
           const uint8_t* ka = kblk + ta * (D / 2) + c * (DQ / 2);
           const uint8_t* kb = kblk + tb * (D / 2) + c * (DQ / 2);
@@ -888,7 +969,26 @@ attn_decode_cp_kernel(const AttnParams p) {
         const bool rescale = __any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f);
         // ---- O^T += V^T P^T : rows = dims, k = tokens
         const uint8_t* vsub = vblk + sub * 16 + c * 4;
-        if constexpr (KV4) {
+        if constexpr (F8) {
+          // P^T as two e4m3 terms: a b16 unit carries one head's values of this thread's two token rows; the 8x8 transpose
+          // leaves head rq's tokens 4c, 4c+2, 4c+1, 4c+3 in a register, a byte permute puts them in order
+          uint32_t h0, l0, h1, l1;
+          split_e4m3x2(pv[0] * kPScale, pv[2] * kPScale, h0, l0);
+          split_e4m3x2(pv[1] * kPScale, pv[3] * kPScale, h1, l1);
+          const uint32_t pbh = __byte_perm(movmatrix_trans(h0 | (h1 << 16)), 0u, 0x3120);
+          const uint32_t pbl = __byte_perm(movmatrix_trans(l0 | (l1 << 16)), 0u, 0x3120);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const uint32_t a[4] = {*reinterpret_cast<const uint32_t*>(vsub + (mt * 16 + rq) * bs) & vmask,
+                                   *reinterpret_cast<const uint32_t*>(vsub + (mt * 16 + rq + 8) * bs) & vmask, 0u, 0u};
+            if (rescale) {
+              o[mt][0] *= alpha[0]; o[mt][1] *= alpha[1];
+              o[mt][2] *= alpha[0]; o[mt][3] *= alpha[1];
+            }
+            mma_e4m3(o[mt], a, pbh, 0u);
+            mma_e4m3(o[mt], a, pbl, 0u);
+          }
+        } else if constexpr (KV4) {
           const uint32_t m0 = ((vmask & 0xFFu) ? 0xFFFFu : 0u) | ((vmask & 0xFF00u) ? 0xFFFF0000u : 0u);
           const uint32_t m1 = ((vmask & 0xFF0000u) ? 0xFFFFu : 0u) | ((vmask & 0xFF000000u) ? 0xFFFF0000u : 0u);
           const uint8_t* vd = vblk + ((sub * 16 + c * 4) >> 1);                       // two tokens per byte
@@ -936,7 +1036,7 @@ attn_decode_cp_kernel(const AttnParams p) {
     }
   }
 
-  decode_merge_store<D>(p, ring, o, m_run, l_run, warp, lane, G, kvh, split, b, q_row0, 1.f);
+  decode_merge_store<D>(p, ring, o, m_run, l_run, warp, lane, G, kvh, split, b, q_row0, F8 ? 1.f / kPScale : 1.f);
 }
 
 // ----------------------------------------------------------------------------- decode on FP8 tensor-core tiles
@@ -947,29 +1047,6 @@ attn_decode_cp_kernel(const AttnParams p) {
 //   S^T[16 tok x 8 heads] = K[16 x 32 dims] (Qhi^T + Qlo^T)      Q scaled per head to the e4m3 range, scale applied to S
 //   O^T[16 dims x 8 heads] += V^T[16 x 32 tok] (Phi^T + Plo^T)    P scaled by 256 (undone at the end)
 // A warp takes two pages per step so that the PV product's 32-token k dimension is full.
-ATLAS_DEVICE void mma_e4m3(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-// two floats -> two e4m3 bytes (`lo` in bits 7..0, `hi` in bits 15..8) and back
-ATLAS_DEVICE uint32_t pack_e4m3x2(float lo, float hi) {
-  uint16_t r;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(r) : "f"(hi), "f"(lo));
-  return r;
-}
-ATLAS_DEVICE float2 unpack_e4m3x2(uint32_t v) {
-  const uint32_t h = fp8x2_to_f16x2(static_cast<uint16_t>(v));
-  return __half22float2(*reinterpret_cast<const __half2*>(&h));
-}
-// (x0, x1) as a leading e4m3 pair and the e4m3 pair of what the first one missed
-ATLAS_DEVICE void split_e4m3x2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
-  hi = pack_e4m3x2(x0, x1);
-  const float2 back = unpack_e4m3x2(hi);
-  lo = pack_e4m3x2(x0 - back.x, x1 - back.y);
-}
-
 template <int D>
 __global__ void __launch_bounds__(kDecodeThreads)
 attn_decode_f8_kernel(const AttnParams p, int stages, status_t* status) {
@@ -1311,15 +1388,15 @@ static int decode_cp_depth() {
   return v;
 }
 
-template <int D, int BS, int kCpDepth, bool KV4 = false>
+template <int D, int BS, int kCpDepth, bool KV4 = false, bool F8 = false>
 static int launch_decode_cp(const AttnParams& p, int B, cudaStream_t st) {
   const int stage_bytes = KV4 ? 2 * (p.block_size * D * 9 / 16) : 2 * p.block_size * D;
   const int merge_bytes = (64 + 4 * 8 * D + 8) * (int)sizeof(float);
   const int ring_bytes = 4 * kCpDepth * stage_bytes > merge_bytes ? 4 * kCpDepth * stage_bytes : merge_bytes;
   const int smem = kBtSmemEntries * 4 + ring_bytes;
-  if (ensure_dynamic_smem(reinterpret_cast<const void*>(attn_decode_cp_kernel<D, BS, kCpDepth, KV4>), smem) != cudaSuccess) return -20;
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(attn_decode_cp_kernel<D, BS, kCpDepth, KV4, F8>), smem) != cudaSuccess) return -20;
   dim3 grid(p.Hkv, p.num_splits, B);
-  if (launch_chain(attn_decode_cp_kernel<D, BS, kCpDepth, KV4>, grid, dim3(kCpThreads), (size_t)smem, st, p) != cudaSuccess) return -21;
+  if (launch_chain(attn_decode_cp_kernel<D, BS, kCpDepth, KV4, F8>, grid, dim3(kCpThreads), (size_t)smem, st, p) != cudaSuccess) return -21;
   if (p.num_splits > 1) {
     dim3 g2(p.Hq, B);
     if (launch_chain(attn_merge_kernel, g2, dim3(D), 0, st, p.part_o, p.part_ml, p.out, p.ldo, p.query_start_loc, p.seq_base,
@@ -1331,6 +1408,10 @@ static int launch_decode_cp(const AttnParams& p, int B, cudaStream_t st) {
 
 template <int D>
 static int launch_decode(const AttnParams& p, int B, status_t* status, cudaStream_t st) {
+  if (decode_cpasync_enabled() && decode_f8_enabled() && 4 * 3 * 2 * p.block_size * D <= 96 * 1024) {
+    if (p.block_size == 16) return launch_decode_cp<D, 16, 3, false, true>(p, B, st);
+    return launch_decode_cp<D, 0, 3, false, true>(p, B, st);
+  }
   if (p.block_size == 16 && decode_f8_enabled()) return launch_decode_f8<D>(p, B, status, st);
   if (decode_cpasync_enabled() && 4 * 3 * 2 * p.block_size * D <= 96 * 1024) {
     if (decode_cp_depth() == 2) {
