@@ -40,6 +40,10 @@ constexpr int kTcStages = 3;
 
 struct TcAttnParams {
   __nv_bfloat16* out; long long ldo;
+  // q_out != nullptr: write the rows as FP8 with one scale per (row, head) -- a head is one 128-wide quantisation group of
+  // the output projection's A operand -- instead of bf16 `out`; scale of (row, head) at s_out[head * s_ld + row]
+  uint8_t* q_out; long long ldqo;
+  float* s_out; long long s_ld;
   const uint8_t* k_cache; const uint8_t* v_cache;
   const int* block_tables; int bt_ld;
   const int* seq_lens; const int* query_start_loc;
@@ -403,6 +407,43 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const TcAttnP
       if (ok && n_kv > 0 && mbar_wait(pv_done, (n_kv - 1) & 1, abort_flag, p.status, 0x832)) {
         tc_fence_after();
         const float inv = (l > 0.f) ? p.v_scale / l : 0.f;
+        if (p.q_out != nullptr) {
+          // the whole output row in registers (as the score rows were), rounded to bf16 like the unfused path's
+          // output, then one scale for the row's 128 values
+          uint32_t r[4][32];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(tO + t_lane + c * 32, r[c]);
+          tmem_ld_wait();
+          float amax = 0.f;
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float v = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[c][i]) * inv));
+              r[c][i] = __float_as_uint(v);
+              amax = fmaxf(amax, fabsf(v));
+            }
+          if (row_live) {
+            const float sc = fmaxf(amax, 1e-10f) / 448.f;
+            const float qinv = __frcp_rn(sc);
+            uint8_t* qrow = p.q_out + (long long)(q_row0 + tok) * p.ldqo + head * kTcD;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+              for (int q = 0; q < 2; ++q) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int b = q * 16 + j * 4;
+                  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__uint_as_float(r[c][b]) * qinv, __uint_as_float(r[c][b + 1]) * qinv), __NV_SATFINITE, __NV_E4M3);
+                  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__uint_as_float(r[c][b + 2]) * qinv, __uint_as_float(r[c][b + 3]) * qinv), __NV_SATFINITE, __NV_E4M3);
+                  w[j] = lo | (hi << 16);
+                }
+                *reinterpret_cast<uint4*>(qrow + c * 32 + q * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            p.s_out[(long long)head * p.s_ld + q_row0 + tok] = sc;
+          }
+        } else {
         __nv_bfloat16* orow = p.out + (long long)(q_row0 + tok) * p.ldo + head * kTcD;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -420,6 +461,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const TcAttnP
               *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = o;
             }
           }
+        }
         }
       }
     }
@@ -463,12 +505,15 @@ extern "C" int atlas_attn_prefill_tc(const void* q, long long ldq, void* out, lo
                                      const void* v_cache, const int* block_tables, int bt_ld, const int* seq_lens,
                                      const int* query_start_loc, const int* tile_seq, const int* tile_q0, int num_tiles,
                                      int total_tokens, float scale, float k_scale, float v_scale, int Hq, int Hkv, int D,
-                                     int block_size, int window, unsigned long long* status, void* stream) {
+                                     int block_size, int window, unsigned long long* status, void* stream, void* q_out,
+                                     long long ldqo, float* s_out, long long s_ld) {
   if (num_tiles <= 0) return 0;
   if (D != kTcD || block_size != kTcPage || window > 0 || Hq % Hkv) return 1;
+  if (q_out != nullptr && (!s_out || (ldqo % 16) || (reinterpret_cast<uintptr_t>(q_out) & 15))) return 1;
   const int G = Hq / Hkv;
   if (G != 1 && G != 2 && G != 4 && G != 8) return 1;
-  if ((reinterpret_cast<uintptr_t>(q) & 15) || (ldq * 2) % 16 || (ldo % 8) || (reinterpret_cast<uintptr_t>(out) & 15)) return 1;
+  if ((reinterpret_cast<uintptr_t>(q) & 15) || (ldq * 2) % 16) return 1;
+  if (q_out == nullptr && ((ldo % 8) || (reinterpret_cast<uintptr_t>(out) & 15))) return 1;
   EncodeTiledFn enc = tc_encode_fn();
   if (!enc) return -10;
   // Q as [tokens][heads][dims]: box = 64 dims x G heads x 128/G tokens -> 128 rows of 128 bytes, row = token * G + head
@@ -482,6 +527,7 @@ extern "C" int atlas_attn_prefill_tc(const void* q, long long ldq, void* out, lo
     return -11;
   TcAttnParams p;
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ldo = ldo;
+  p.q_out = reinterpret_cast<uint8_t*>(q_out); p.ldqo = ldqo; p.s_out = s_out; p.s_ld = s_ld;
   p.k_cache = reinterpret_cast<const uint8_t*>(k_cache); p.v_cache = reinterpret_cast<const uint8_t*>(v_cache);
   p.block_tables = block_tables; p.bt_ld = bt_ld; p.seq_lens = seq_lens; p.query_start_loc = query_start_loc;
   p.tile_seq = tile_seq; p.tile_q0 = tile_q0;

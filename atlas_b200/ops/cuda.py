@@ -58,7 +58,7 @@ def load() -> None:
     lib.atlas_attn_prefill.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _f, _f, _f, _i,
                                        _i, _i, _i, _i, _vp]
     lib.atlas_attn_prefill_tc.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _f, _f, _f,
-                                          _i, _i, _i, _i, _i, _vp, _vp]
+                                          _i, _i, _i, _i, _i, _vp, _vp, _vp, _ll, _vp, _ll]
     lib.atlas_argmax.argtypes = [_vp, _ll, _i, _i, _i, _vp, _vp, _vp]
     lib.atlas_sample.argtypes = [_vp, _ll, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]
     lib.atlas_spec_accept.argtypes = [_vp, _vp, _i, _i, _vp, _vp]
@@ -556,7 +556,7 @@ def paged_attention(q, k_cache, v_cache, batch, scale, k_scale, v_scale, sliding
                                          v_cache.data_ptr(), bt.data_ptr(), bt.stride(0), batch.seq_lens.data_ptr(),
                                          batch.query_start_loc.data_ptr(), tdev[0].data_ptr(), tdev[1].data_ptr(), n_tiles,
                                          T, float(scale), float(k_scale), float(v_scale), Hq, Hkv, D, bs, window,
-                                         _status_ptr[d], st)
+                                         _status_ptr[d], st, None, 0, None, 0)
         if rc != 1:
             _check(rc, "attn_prefill_tc")
             return out
@@ -581,12 +581,20 @@ def paged_attention(q, k_cache, v_cache, batch, scale, k_scale, v_scale, sliding
 
 
 def paged_attention_q8(q, k_cache, v_cache, batch, scale, k_scale, v_scale, sliding_window):
-    """Decode attention whose kernel writes FP8 rows ``[T, Hq * D]`` and one scale per (row, head), the form the output
-    projection's FP8 GEMM reads, instead of bf16 (``atlas_attn_decode_q8``).  Covers pure decode steps on an FP8 cache
-    with head_dim 128; returns None otherwise (nothing launched)."""
+    """Attention whose kernels write FP8 rows ``[T, Hq * D]`` and one scale per (row, head), the form the output
+    projection's FP8 GEMM reads, instead of bf16: decode rows through ``atlas_attn_decode_q8``, prefill chunks through the
+    tcgen05 chunk kernel's FP8 epilogue, both into the same buffers for a mixed step.  FP8 cache, head_dim 128; returns
+    None when some part of the step is not covered (nothing launched then)."""
     T, Hq, D = q.shape
     nb, bs, Hkv, _ = k_cache.shape
-    if D != 128 or k_cache.dtype != FP8 or batch.num_decodes != batch.num_seqs or batch.num_decodes != T or T == 0:
+    if D != 128 or k_cache.dtype != FP8 or T == 0 or batch.num_seqs == 0:
+        return None
+    nd = batch.num_decodes
+    window = int(sliding_window or 0)
+    has_chunks = batch.num_seqs > nd
+    if has_chunks and (not _tc_prefill_ok(q, Hq, Hkv, D, bs, window, k_cache) or (q.data_ptr() & 15) or (q.stride(0) * 2) % 16):
+        return None
+    if not has_chunks and nd != T:
         return None
     d = _dev(q)
     _kv_layout_ok(k_cache, v_cache)
@@ -599,18 +607,44 @@ def paged_attention_q8(q, k_cache, v_cache, batch, scale, k_scale, v_scale, slid
         L._attn_q8_bound = True
     qo = torch.empty(T, Hq * D, dtype=FP8, device=q.device)
     so = _scale_buf(T, Hq, q.device)
-    splits = decode_splits(T, Hkv, batch.max_seq_len, _num_sms[d])
-    po = pml = None
-    if splits > 1:
-        po = scratch("attn_part_o", T * Hq * splits * D * 4, q.device)
-        pml = scratch("attn_part_ml", T * Hq * splits * 2 * 4, q.device)
     bt = batch.block_tables
-    _check(L.atlas_attn_decode_q8(q.data_ptr(), q.stride(0), qo.data_ptr(), Hq * D, so.data_ptr(), so.stride(1),
-                                  k_cache.data_ptr(), v_cache.data_ptr(), bt.data_ptr(), bt.stride(0),
-                                  batch.seq_lens.data_ptr(), batch.query_start_loc.data_ptr(), 0, T, float(scale),
-                                  float(k_scale), float(v_scale), Hq, Hkv, bs, int(sliding_window or 0), splits, _ptr(po),
-                                  _ptr(pml), _status_ptr[d], _stream()), "attn_decode")
+    if nd > 0:
+        splits = decode_splits(nd, Hkv, batch.max_seq_len, _num_sms[d])
+        po = pml = None
+        if splits > 1:
+            po = scratch("attn_part_o", nd * Hq * splits * D * 4, q.device)
+            pml = scratch("attn_part_ml", nd * Hq * splits * 2 * 4, q.device)
+        _check(L.atlas_attn_decode_q8(q.data_ptr(), q.stride(0), qo.data_ptr(), Hq * D, so.data_ptr(), so.stride(1),
+                                      k_cache.data_ptr(), v_cache.data_ptr(), bt.data_ptr(), bt.stride(0),
+                                      batch.seq_lens.data_ptr(), batch.query_start_loc.data_ptr(), 0, nd, float(scale),
+                                      float(k_scale), float(v_scale), Hq, Hkv, bs, window, splits, _ptr(po),
+                                      _ptr(pml), _status_ptr[d], _stream()), "attn_decode")
+    if has_chunks:
+        tdev, n_tiles, _ = _tc_tiles(q, batch, nd, 128 // (Hq // Hkv))
+        rc = L.atlas_attn_prefill_tc(q.data_ptr(), q.stride(0), None, 0, k_cache.data_ptr(), v_cache.data_ptr(), bt.data_ptr(),
+                                     bt.stride(0), batch.seq_lens.data_ptr(), batch.query_start_loc.data_ptr(),
+                                     tdev[0].data_ptr(), tdev[1].data_ptr(), n_tiles, T, float(scale), float(k_scale),
+                                     float(v_scale), Hq, Hkv, D, bs, window, _status_ptr[d], _stream(), qo.data_ptr(), Hq * D,
+                                     so.data_ptr(), so.stride(1))
+        if rc == 1:
+            raise KernelError("tcgen05 chunk attention refused a shape its eligibility check accepted")
+        _check(rc, "attn_prefill_tc")
     return qo, so
+
+
+def _tc_tiles(q, batch, nd: int, tok: int):
+    """(device tensor [2, n] of (sequence, first chunk token) per query tile of ``tok`` tokens, n, tok), cached on the batch."""
+    tiles = getattr(batch, "_attn_tiles_tc", None)
+    if tiles is None or tiles[2] != tok:
+        ts, tq = [], []
+        for i in range(nd, batch.num_seqs):
+            for q0 in range(0, batch.query_lens_host[i], tok):
+                ts.append(i)
+                tq.append(q0)
+        host = torch.tensor([ts, tq], dtype=torch.int32).pin_memory()
+        tiles = (host.to(q.device, non_blocking=True), len(ts), tok)
+        batch._attn_tiles_tc = tiles
+    return tiles
 
 
 def _paged_attention_kv16(q, out, k_cache, v_cache, batch, scale, window, d, scales=None):

@@ -364,9 +364,18 @@ def test_attention_decode_fp8_output(K, Hq, Hkv, ctxs, window):
     want_q, want_s = K.quant_fp8(out.view(B, Hq * D))
     assert torch.equal(sc, want_s)
     assert torch.equal(q8.view(torch.uint8), want_q.view(torch.uint8))
-    # not covered: a step with a prefill chunk in it
+    # a mixed step (one decode row, one 5-token chunk): decode rows and the chunk meet in the same FP8 buffers
     fb2 = ForwardBatch.build([[0], [0] * 5], [10, 3], [tables[0], tables[1]], bs, device=DEV)
-    assert K.paged_attention_q8(torch.zeros(6, Hq, D, device=DEV).bfloat16(), kc, vc, fb2, D ** -0.5, 1.0, 1.0, None) is None
+    q2 = (torch.randn(6, Hq, D, device=DEV) * 0.5).bfloat16()
+    if window is None and Hq // Hkv in (1, 2, 4, 8):
+        out2 = K.paged_attention(q2, kc, vc, fb2, D ** -0.5, 0.7, 1.3, None)
+        got2 = K.paged_attention_q8(q2, kc, vc, fb2, D ** -0.5, 0.7, 1.3, None)
+        _status_ok(K)
+        wq2, ws2 = K.quant_fp8(out2.view(6, Hq * D))
+        assert got2 is not None and torch.equal(got2[1], ws2) and torch.equal(got2[0].view(torch.uint8), wq2.view(torch.uint8))
+    else:
+        # a sliding window is outside the chunk kernel's coverage: the caller is told before anything is launched
+        assert K.paged_attention_q8(q2, kc, vc, fb2, D ** -0.5, 1.0, 1.0, 64) is None
 
 
 @pytest.mark.parametrize("D,Hq,Hkv", [(128, 8, 2), (64, 4, 4), (128, 32, 8)])
@@ -388,6 +397,35 @@ def test_attention_decode_e4m3_tiles(K, D, Hq, Hkv):
         assert _rel_rms(out, want) < 2e-2
     finally:
         L.atlas_attn_set_decode_f8(0)
+
+
+def test_attention_prefill_fp8_output(K):
+    """The tcgen05 chunk attention kernel with its FP8-output epilogue gives exactly the quantised form of its bf16
+    output (pure prefill steps; chunks that start inside a context and end inside a page)."""
+    from atlas_b200.models.batch import ForwardBatch
+    torch.manual_seed(27)
+    D, Hq, Hkv, bs = 128, 16, 4, 16
+    qlens, ctxs = [300, 37, 513], [0, 1000, 77]
+    nblk = [(c + q + bs - 1) // bs for c, q in zip(ctxs, qlens)]
+    nb = sum(nblk) + 3
+    perm = torch.randperm(nb).tolist()
+    tables, off = [], 0
+    for n in nblk:
+        tables.append(perm[off:off + n])
+        off += n
+    kc, vc = K.alloc_kv_cache(nb, bs, Hkv, D, torch.float8_e4m3fn, DEV)
+    kc.copy_((torch.randn(nb, bs, Hkv, D, device=DEV) * 0.5).to(torch.float8_e4m3fn))
+    vc.copy_((torch.randn(nb, bs, Hkv, D, device=DEV) * 0.5).to(torch.float8_e4m3fn))
+    fb = ForwardBatch.build([[0] * q for q in qlens], ctxs, tables, bs, device=DEV)
+    T = sum(qlens)
+    q = (torch.randn(T, Hq, D, device=DEV) * 0.5).bfloat16()
+    out = K.paged_attention(q, kc, vc, fb, D ** -0.5, 0.7, 1.3, None)
+    got = K.paged_attention_q8(q, kc, vc, fb, D ** -0.5, 0.7, 1.3, None)
+    _status_ok(K)
+    assert got is not None
+    want_q, want_s = K.quant_fp8(out.view(T, Hq * D))
+    assert torch.equal(got[1], want_s)
+    assert torch.equal(got[0].view(torch.uint8), want_q.view(torch.uint8))
 
 
 def test_nvfp4_kv_cache_write_and_attention(K):
