@@ -20,7 +20,7 @@ from collections import defaultdict
 import torch
 
 
-def run(model_name: str, batch: int, ctx: int, prefill: int, steps: int, block_size: int = 16):
+def run(model_name: str, batch: int, ctx: int, prefill: int, steps: int, block_size: int = 16, prefill_seqs: int = 1):
     from atlas_b200.config import PRESETS
     from atlas_b200.models import build_model
     from atlas_b200.models.batch import ForwardBatch
@@ -31,20 +31,28 @@ def run(model_name: str, batch: int, ctx: int, prefill: int, steps: int, block_s
     total = (ctx + 1) if not prefill else prefill
     cfg.max_position_embeddings = max(4096, total + 16)
     model = build_model(cfg, device=dev).init_random(0, max_pos=total + 16)
-    nseq = batch if not prefill else 1
+    nseq = batch if not prefill else max(1, prefill_seqs)
+    if prefill:
+        total = prefill // nseq                      # the chunk is `prefill_seqs` prompts of equal length
     per = (total + block_size - 1) // block_size + 1
     cache = model.alloc_cache(nseq * per + 8, block_size, torch.float8_e4m3fn, state_slots=nseq + 1)
     tables = [list(range(i * per, (i + 1) * per)) for i in range(nseq)]
     g = torch.Generator().manual_seed(0)
     if prefill:
-        toks = [torch.randint(0, cfg.vocab_size, (prefill,), generator=g).tolist()]
-        mk = lambda: ForwardBatch.build(toks, [0], tables, block_size, device=dev, state_slots=[0], has_state=[False])
+        toks = [torch.randint(0, cfg.vocab_size, (total,), generator=g).tolist() for _ in range(nseq)]
+        mk = lambda: ForwardBatch.build(toks, [0] * nseq, tables, block_size, device=dev, state_slots=list(range(nseq)),
+                                        has_state=[False] * nseq)
     else:
         toks = [[int(torch.randint(0, cfg.vocab_size, (1,), generator=g))] for _ in range(batch)]
         mk = lambda: ForwardBatch.build(toks, [ctx] * batch, tables, block_size, device=dev,
                                         state_slots=list(range(batch)), has_state=[True] * batch)
+    def logits(h, fb):
+        # like the engine: only the last row of every sequence goes through the output projection
+        if prefill:
+            return model.compute_logits(h, (fb.query_start_loc[1:] - 1).long())
+        return model.compute_logits(h)
     for _ in range(2):
-        model.compute_logits(model.forward(mk(), cache))
+        logits(model.forward(mk_fb := mk(), cache), mk_fb)
     torch.cuda.synchronize()
     agg = defaultdict(lambda: [0.0, 0])
     step_ms = []
@@ -54,7 +62,7 @@ def run(model_name: str, batch: int, ctx: int, prefill: int, steps: int, block_s
         K.device_marks = []
         t0 = torch.cuda.Event(enable_timing=True)
         t0.record()
-        model.compute_logits(model.forward(fb, cache))
+        logits(model.forward(fb, cache), fb)
         marks, K.device_marks = K.device_marks, None
         torch.cuda.synchronize()
         prev = t0
@@ -79,10 +87,11 @@ def main():
     ap.add_argument("--batch", type=int, default=128)
     ap.add_argument("--ctx", type=int, default=1152)
     ap.add_argument("--prefill", type=int, default=0, help="profile one prefill chunk of this many tokens instead of a decode step")
+    ap.add_argument("--prefill-seqs", type=int, default=1, help="split the prefill chunk into this many equal prompts")
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--out", default=None)
     a = ap.parse_args()
-    res = run(a.model, a.batch, a.ctx, a.prefill, a.steps)
+    res = run(a.model, a.batch, a.ctx, a.prefill, a.steps, prefill_seqs=a.prefill_seqs)
     print(json.dumps({k: v for k, v in res.items() if k != "kernels"}))
     for k in res["kernels"]:
         print(f'{k["name"]:<28} {k["calls"]:>5} x  {k["us"]:>10.1f} us  {100 * k["share"]:5.1f} %')
