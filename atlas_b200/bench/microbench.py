@@ -193,6 +193,26 @@ def run(model: str = "llama3-8b", decode_batch: int = 128, ctx: int = 1152, chun
             note="eager launch")
         return rows
 
+    if only and only.startswith("onefused:"):
+        # one decode-size FP8 GEMM with its fused epilogue (o / down: residual + norm + FP8 quantisation, split-K through a
+        # cluster; gate_up: SwiGLU), few eager launches: the case to put under a profiler.  only = "onefused:<name>:<M>"
+        _, name, m_s = only.split(":")
+        M = int(m_s)
+        N, Kd = {n: (a, b) for n, a, b in gemms}[name]
+        x = torch.randn(M, Kd, device=dev).bfloat16()
+        wq, ws = Q.quantize_fp8_block(torch.randn(N, Kd, device=dev) * 0.02)
+        xq, xs = K.quant_fp8(x)
+        mode = 1 if name == "gate_up" else (2 if name in ("o", "down") else 0)
+        res = torch.randn(M, N, device=dev).bfloat16()
+        nw = torch.ones(N, device=dev).bfloat16()
+        T.use_graph = False
+        ms = T.time(lambda: K.gemm_fp8_fused(xq, xs, wq, ws, mode=mode, residual=res if mode == 2 else None,
+                                             norm_w=nw if mode == 2 else None), iters=3, warmup=2)
+        bn, sp = K.fused_block_n(mode, M, N, Kd, 148) if mode else K.gemm_plan(M, N, Kd, 1, 148)
+        add(f"gemm_fp8 fused mode {mode} {name} M={M} N={N} K={Kd}", ms, bytes_=N * Kd + M * Kd + 2 * M * N, flops=2 * M * N * Kd,
+            note=f"block_n={bn} splits={sp} (eager launch)")
+        return rows
+
     if only and only.startswith("one:"):
         # one FP8 GEMM shape, few launches, no graph: the case to put under a profiler.  only = "one:<name>:<M>"
         _, name, m_s = only.split(":")
