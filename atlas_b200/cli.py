@@ -273,7 +273,7 @@ def cmd_serve(argv: List[str]) -> int:
                          "serve_plan": plan})
     for spec in args.lora_adapter:
         name, _, path = spec.partition("=")
-        state.adapters[name] = {"path": path}
+        state.adapters[name] = {"path": path, "slot": target.load_adapter(name, path)}      # followers get it with the first plan
     app = create_app(state)
     aeng.start()
     try:

@@ -211,6 +211,18 @@ class LLMEngine:
         self._stop_checkers.pop(request_id, None)
         return s is not None
 
+    def load_adapter(self, name: str, path: str) -> int:
+        """Read a PEFT adapter directory and make it resident under ``name``; returns its slot (the value requests pass
+        as ``adapter_slot``).  On a tensor-parallel rank the adapter is cut like the base weights."""
+        from .lora import load_adapter
+        ad = load_adapter(path, self.model)
+        ad.name = name
+        return self.model.register_adapter(ad)
+
+    def unload_adapter(self, name: str) -> None:
+        if getattr(self.model, "lora", None) is not None:
+            self.model.lora.unregister(name)
+
     def has_unfinished(self) -> bool:
         return self.scheduler.has_work()
 

@@ -16,7 +16,7 @@ import torch
 from .. import ops
 from ..config import ModelConfig
 from ..ops import Act, LinearWeight
-from ..lora import add_delta
+from ..lora import GATE_SUFFIX, add_delta
 from .common import ParallelCtx, make_weight, randn_weight, shard_cols, shard_rows
 
 
@@ -85,12 +85,12 @@ class Attention:
     def forward(self, act: Act, batch, kv: Tuple[torch.Tensor, torch.Tensor, float, float],
                 rope_cache: torch.Tensor) -> torch.Tensor:
         out = self.mix(act, batch, kv, rope_cache)
-        y = self.pctx.row_parallel_linear(out, self.o)
         if self.lora is not None and batch.adapter_rows is not None:
-            if y._base is not None:
-                y = y.clone()               # the fused path returns a view of its reduction area
+            # this rank's columns of A give a partial delta: it joins the partial product before the group reduction
+            y = ops.linear(out, self.o)
             add_delta(y, self.lora, f"layers.{self.layer_idx}.self_attn.o_proj", out, batch)
-        return y
+            return self.pctx.all_reduce(y)
+        return self.pctx.row_parallel_linear(out, self.o)
 
     def mix(self, act: Act, batch, kv: Tuple[torch.Tensor, torch.Tensor, float, float],
             rope_cache: torch.Tensor):
@@ -106,6 +106,8 @@ class Attention:
             add_delta(qkv, self.lora, pre + "q_proj", xin, batch, 0, nq)
             add_delta(qkv, self.lora, pre + "k_proj", xin, batch, nq, nkv)
             add_delta(qkv, self.lora, pre + "v_proj", xin, batch, nq + nkv, nkv)
+            if self.gated:
+                add_delta(qkv, self.lora, pre + "q_proj" + GATE_SUFFIX, xin, batch, nq + 2 * nkv, nq)
         q = qkv[:, :nq].view(T, self.hq, self.d)
         k = qkv[:, nq:nq + nkv].view(T, self.hkv, self.d)
         v = qkv[:, nq + nkv:nq + 2 * nkv].view(T, self.hkv, self.d)

@@ -73,13 +73,15 @@ class DenseMLP:
             xin, half = act.plain(), gu.shape[1] // 2
             add_delta(gu, self.lora, self.lora_prefix + "gate_proj", xin, batch, 0, half)
             add_delta(gu, self.lora, self.lora_prefix + "up_proj", xin, batch, half, half)
-        a = ops.silu_mul_act(gu, want_fp8=self.down.kind == "fp8_block" and not use_lora)
-        if self.shard and reduce:
-            y = self.pctx.row_parallel_linear(a, self.down)
+        if self.activation == "gelu_tanh_glu":
+            a = ops.glu_act(gu, False, "gelu_tanh")
         else:
-            y = ops.linear(a, self.down)
+            a = ops.silu_mul_act(gu, want_fp8=self.down.kind == "fp8_block" and not use_lora)
         if use_lora:
-            if y._base is not None:
-                y = y.clone()
+            # with a sharded FFN this rank's columns of A give a partial delta: add it before the group reduction
+            y = ops.linear(a, self.down)
             add_delta(y, self.lora, self.lora_prefix + "down_proj", a.plain(), batch)
-        return y
+            return self.pctx.all_reduce(y) if (self.shard and reduce) else y
+        if self.shard and reduce:
+            return self.pctx.row_parallel_linear(a, self.down)
+        return ops.linear(a, self.down)

@@ -22,6 +22,7 @@ from .. import ops, quant as Q
 from ..config import ModelConfig
 from ..ops import Act, LinearWeight, reference as ref
 from .common import ParallelCtx, make_weight, randn_weight
+from ..lora import add_delta
 from .mlp import DenseMLP
 
 
@@ -44,6 +45,17 @@ class ExpertWeights:
     @property
     def num_local(self) -> int:
         return self.w13.shape[0]
+
+    def dequantized_expert(self, e: int):
+        """``(w13 [2I,H], w2 [H,I])`` of local expert ``e`` in a floating-point dtype, without expanding the others."""
+        if self.kind == "dense":
+            return self.w13[e], self.w2[e]
+        if self._deq is not None:
+            return self._deq[0][e], self._deq[1][e]
+        if self.kind == "fp8_block":
+            return (Q.dequantize_fp8_block(self.w13[e], self.w13_scale[e]), Q.dequantize_fp8_block(self.w2[e], self.w2_scale[e]))
+        return (Q.dequantize_nvfp4(self.w13[e], self.w13_scale[e], self.w13_gscale[e:e + 1]),
+                Q.dequantize_nvfp4(self.w2[e], self.w2_scale[e], self.w2_gscale[e:e + 1]))
 
     def dequantized(self):
         if self.kind == "dense":
@@ -90,6 +102,8 @@ class MoE:
         self.shared_gate: Optional[torch.Tensor] = None
         self.router_bias: Optional[torch.Tensor] = None      # fp32 [E]: selection-only correction (e_score_correction_bias)
         self.hash_table: Optional[torch.Tensor] = None       # int32 [vocab, k]: static token-id -> expert ids
+        self.lora = None                    # lora.LoraSet shared by the model's layers
+        self.lora_prefix = ""               # e.g. "layers.3.mlp."
         if cfg.shared_expert_intermediate_size:
             self.shared = DenseMLP(cfg, pctx, dense_kind, cfg.shared_expert_intermediate_size, shard=False)
 
@@ -124,10 +138,13 @@ class MoE:
             self.shared_gate = randn_weight(gen, 1, h, std, dtype, device)
 
     # ------------------------------------------------------------------ forward
-    def forward(self, act: Act, token_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, act: Act, token_ids: Optional[torch.Tensor] = None, batch=None) -> torch.Tensor:
         x = act.plain()
         cfg = self.cfg
         logits = ops.linear(x, self.router)
+        adapters = self.lora is not None and batch is not None and batch.adapter_rows is not None and bool(self.lora_prefix)
+        if adapters:
+            add_delta(logits, self.lora, self.lora_prefix + "gate", x, batch)
         topk_w, topk_ids = ops.moe_route(logits, self.top_k, cfg.norm_topk_prob, cfg.router_scoring, self.router_bias,
                                          cfg.router_n_group, cfg.router_topk_group, cfg.routed_scaling_factor,
                                          self.hash_table, token_ids if self.hash_table is not None else None)
@@ -135,8 +152,10 @@ class MoE:
             y = ops.cuda_ops().moe_forward(x, topk_w, topk_ids, self.experts, self.e_lo, self.pctx, self.ep_mode)
         else:
             y = self._forward_ref(x, topk_w, topk_ids)
+        if adapters:
+            y = self._adapter_rows_forward(x, y, topk_w, topk_ids, batch.adapter_rows)
         if self.shared is not None:
-            s = self.shared.forward(act, reduce=False)
+            s = self.shared.forward(act, reduce=False, batch=batch)
             if (self.shared_gate is not None and ops.on_gpu(x) and x.dtype == torch.bfloat16 and y.dtype == torch.bfloat16
                     and self.shared_gate.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and y.is_contiguous()):
                 return ops.cuda_ops().shared_expert_blend(y if y._base is None else y.clone(), s, x, self.shared_gate)
@@ -144,6 +163,60 @@ class MoE:
                 g = torch.sigmoid(x.float() @ self.shared_gate.float().t())
                 s = (s.float() * g).to(s.dtype)
             y = y + s
+        return y
+
+    def _adapter_rows_forward(self, x, y, topk_w, topk_ids, adapter_rows) -> torch.Tensor:
+        """Routed-expert output of the rows whose adapter carries per-expert matrices for this layer, recomputed with
+        ``W + scaling * B A`` in every selected local expert and written over those rows of ``y``.  SwiGLU sits between
+        the adapted projections, so the update cannot be added to the base output; the base kernels stay as they are
+        and only adapter rows pay (one dequantised expert at a time, eager: a step with adapter rows is not captured).
+        Every rank sees the same ``adapter_rows``, so the expert-parallel sum below is entered by all or by none.
+        Reference behaviour: ``crates/spark-model/src/layers/moe/lora.rs`` (delta folded around the base grouped GEMM,
+        base rows skipped)."""
+        layer = int(self.lora_prefix.split(".")[1])
+        slots = {s: ad for s, ad in self.lora.slots.items() if layer in ad.expert_layers()}
+        if not slots:
+            return y
+        mask = torch.zeros_like(adapter_rows, dtype=torch.bool)
+        for s in slots:
+            mask |= adapter_rows == s
+        rows = mask.nonzero(as_tuple=True)[0]
+        if rows.numel() == 0:
+            return y
+        xr, ids, wts, slot_r = x[rows].float(), topk_ids[rows].long(), topk_w[rows].float(), adapter_rows[rows]
+        part = torch.zeros(rows.numel(), x.shape[1], dtype=torch.float32, device=x.device)
+        inter = self.cfg.moe_intermediate_size
+
+        def pair(ad, e, leaf):
+            w = ad.weights.get(f"{self.lora_prefix}experts.{e}.{leaf}")
+            return None if w is None else (w[0].float(), w[1].float(), ad.scaling)
+
+        def low_rank(v, w):
+            return 0.0 if w is None else (v @ w[0].t()) @ w[1].t() * w[2]
+
+        for e in ids.unique().tolist():
+            if not (self.e_lo <= e < self.e_hi):
+                continue                                   # its owner rank adds it
+            w13, w2 = self.experts.dequantized_expert(e - self.e_lo)
+            hit = ids == e                                 # [R, k]
+            for s, ad in slots.items():
+                sel = (hit.any(-1) & (slot_r == s)).nonzero(as_tuple=True)[0]
+                if sel.numel() == 0:
+                    continue
+                xe = xr[sel]
+                h = xe @ w13.float().t()
+                g = h[:, :inter] + low_rank(xe, pair(ad, e, "gate_proj"))
+                u = h[:, inter:] + low_rank(xe, pair(ad, e, "up_proj"))
+                a = (torch.nn.functional.silu(g) * u).to(x.dtype).float()
+                o = a @ w2.float().t() + low_rank(a, pair(ad, e, "down_proj"))
+                part.index_add_(0, sel, o * (wts[sel] * hit[sel]).sum(-1, keepdim=True))
+        p = self.pctx
+        comm = p.ep_comm if p.ep_comm is not None else p.comm
+        if p.ep_size > 1 and comm is not None:
+            part = comm.all_reduce(part)
+        if y._base is not None:
+            y = y.clone()                                  # the fused combine returns a view of its reduction area
+        y[rows] = part.to(y.dtype)
         return y
 
     def _forward_ref(self, x, topk_w, topk_ids) -> torch.Tensor:

@@ -1,8 +1,17 @@
 """PEFT LoRA adapters: loading (``adapter_config.json`` + ``adapter_model.safetensors``) and per-request application
 as a batched gather-matrix-vector (shrink then expand) on top of the base projection.
 
+Tensor parallelism: an adapter is cut the way its base projection is (``localize``).  A column-parallel projection
+(q / k / v / gate / up) keeps ``A`` whole and this rank's rows of ``B``; a row-parallel one (o / down) keeps ``B`` whole and
+this rank's columns of ``A``, so its delta is a partial sum that the layer adds BEFORE the group reduction.
+
+Mixture-of-experts layers: the router (``mlp.gate``) delta is added to the routing logits; rows that carry an adapter
+with per-expert matrices (``mlp.experts.<e>.{gate,up,down}_proj``) have their routed-expert output recomputed with the
+adapted expert weights (``layers/moe.py::MoE._adapter_rows_forward``).
+
 Reference parity: ``crates/spark-model/src/layers/lora/*`` (adapter pool, bgmv shrink/expand),
-``kernels/gb10/common/lora_bgmv.cu``, ``spark-runtime/src/weights/adapter.rs``.
+``crates/spark-model/src/layers/moe/lora.rs`` (router + routed-expert deltas), ``kernels/gb10/common/lora_bgmv.cu``,
+``spark-runtime/src/weights/adapter.rs``.
 """
 from __future__ import annotations
 
@@ -26,6 +35,12 @@ class LoraAdapter:
     def scaling(self) -> float:
         return self.alpha / max(1, self.rank)
 
+    def expert_layers(self) -> set:
+        """Indices of the layers for which this adapter carries per-expert matrices."""
+        if getattr(self, "_expert_layers", None) is None:
+            self._expert_layers = {int(k.split(".")[1]) for k in self.weights if ".mlp.experts." in k}
+        return self._expert_layers
+
 
 def load_adapter(path: str, model=None) -> LoraAdapter:
     with open(os.path.join(path, "adapter_config.json")) as f:
@@ -47,6 +62,42 @@ def load_adapter(path: str, model=None) -> LoraAdapter:
     return ad
 
 
+GATE_SUFFIX = "#gate"      # the output-gate half of a gated q_proj (rows [q | gate] per head in the checkpoint)
+
+
+def localize(adapter: LoraAdapter, model) -> LoraAdapter:
+    """This rank's view of ``adapter`` for ``model``: every pair cut like the base projection it updates.  With a
+    tensor parallel size of 1 only the gated q_proj split applies."""
+    from .layers.attention import Attention
+    from .layers.common import shard_cols, shard_rows
+    tp, r = model.pctx.tp_size, model.pctx.tp_rank
+    out = LoraAdapter(adapter.name, adapter.rank, adapter.alpha)
+    for mod, (A, B) in adapter.weights.items():
+        parts = mod.split(".")
+        known = len(parts) >= 4 and parts[0] == "layers" and parts[1].isdigit() and int(parts[1]) < len(model.layers)
+        if known:
+            layer, leaf = model.layers[int(parts[1])], parts[-1]
+            if parts[2] == "self_attn" and isinstance(layer.mixer, Attention):
+                at = layer.mixer
+                if leaf == "q_proj":
+                    if at.gated:
+                        Bv = B.view(model.cfg.num_attention_heads, 2, at.d, B.shape[-1])
+                        out.weights[mod + GATE_SUFFIX] = (A, shard_rows(Bv[:, 1].reshape(-1, B.shape[-1]), r, tp).contiguous())
+                        B = Bv[:, 0].reshape(-1, B.shape[-1])
+                    B = shard_rows(B, r, tp)
+                elif leaf in ("k_proj", "v_proj"):
+                    B = at._kv_slice(B)
+                elif leaf == "o_proj":
+                    A = shard_cols(A, r, tp)
+            elif parts[2] == "mlp" and len(parts) == 4 and not layer.is_moe and getattr(layer.ffn, "shard", False):
+                if leaf in ("gate_proj", "up_proj"):
+                    B = shard_rows(B, r, tp)
+                elif leaf == "down_proj":
+                    A = shard_cols(A, r, tp)
+        out.weights[mod] = (A.contiguous(), B.contiguous())
+    return out
+
+
 def bgmv(x: torch.Tensor, adapters: Dict[int, tuple], slot_of_row: torch.Tensor, scaling: Dict[int, float]) -> torch.Tensor:
     """Per-row LoRA delta: ``delta[t] = scaling * B_s (A_s x[t])`` with ``s = slot_of_row[t]`` (slot 0 = no adapter)."""
     out = None
@@ -65,10 +116,11 @@ class LoraSet:
     """Adapters resident on the device, addressed by slot (0 = base model).  ``delta(module, x, rows)`` gives the
     low-rank update of one projection for a batch whose rows may belong to different adapters (or none).
 
-    Supported targets are the dense projections of attention and the SwiGLU FFN (``q/k/v/o_proj``,
-    ``gate/up/down_proj``) on an unsharded model (tensor parallel size 1)."""
+    Supported targets: the dense projections of attention and the SwiGLU FFN (``q/k/v/o_proj``, ``gate/up/down_proj``),
+    the shared expert, the router and the routed experts of a mixture-of-experts layer.  Adapters are registered in the
+    form ``localize`` gives them, so the set works on a tensor-parallel rank as it does on a whole model."""
 
-    def __init__(self, max_slots: int = 8):
+    def __init__(self, max_slots: int = 7):       # the device kernel takes slots 1..7
         self.max_slots = max_slots
         self.slots: Dict[int, LoraAdapter] = {}
         self.by_name: Dict[str, int] = {}

@@ -194,7 +194,7 @@ class DecoderLayer:
             return self.ffn.pctx.row_parallel_linear(a, self.ffn.down), residual
         if self.is_moe:
             hashed = self.ffn.hash_table is not None and batch.input_ids is not None
-            h = self.ffn.forward(act, batch.input_ids.to(torch.int32) if hashed else None)
+            h = self.ffn.forward(act, batch.input_ids.to(torch.int32) if hashed else None, batch=batch)
         else:
             h = self.ffn.forward(act, batch=batch)
         return h, residual
@@ -296,19 +296,24 @@ class DecoderLM:
         self.finalize(max_pos)
         return self
 
-    def enable_lora(self, max_slots: int = 8):
-        """Attach one adapter set to the attention and dense-FFN projections of every layer (tensor parallel size 1)."""
+    def enable_lora(self, max_slots: int = 7):
+        """Attach one adapter set to the attention, dense-FFN and mixture-of-experts blocks of every layer."""
         from ..lora import LoraSet
-        if self.pctx.tp_size > 1:
-            raise RuntimeError("LoRA adapters are applied on unsharded projections only (tp_size 1)")
         if getattr(self, "lora", None) is None:
             self.lora = LoraSet(max_slots)
             for l in self.layers:
                 if l.kind == "attention":
                     l.mixer.lora = self.lora
-                if not l.is_moe:
-                    l.ffn.lora, l.ffn.lora_prefix = self.lora, f"layers.{l.idx}.mlp."
+                l.ffn.lora, l.ffn.lora_prefix = self.lora, f"layers.{l.idx}.mlp."
+                shared = getattr(l.ffn, "shared", None)
+                if shared is not None:
+                    shared.lora, shared.lora_prefix = self.lora, f"layers.{l.idx}.mlp.shared_expert."
         return self.lora
+
+    def register_adapter(self, adapter) -> int:
+        """Make ``adapter`` (whole, as loaded) resident on this rank, cut like the base weights; returns its slot."""
+        from ..lora import localize
+        return self.enable_lora().register(localize(adapter, self))
 
     def set_lm_head(self, head: torch.Tensor) -> None:
         if self.vocab_parallel:

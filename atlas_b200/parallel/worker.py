@@ -76,6 +76,10 @@ class StepControl:
         with self._lock:
             self._pending.append(("abort", rid, reason))
 
+    def note_adapter(self, op: str, name: str, path: str = "") -> None:
+        with self._lock:
+            self._pending.append((op, name, path))
+
     def _bcast(self, obj):
         try:
             out = self.comm.broadcast_object(obj, src=0)
@@ -132,6 +136,10 @@ class StepControl:
                 reason = FinishReason.TIMEOUT if ev[2] == "timeout" else FinishReason.ABORT
                 engine.scheduler.abort(ev[1], reason)
                 engine._seqs.pop(ev[1], None)
+            elif ev[0] == "lora_load":          # every rank reads the adapter itself and keeps its own slices
+                engine.load_adapter(ev[1], ev[2])
+            elif ev[0] == "lora_unload":
+                engine.unload_adapter(ev[1])
 
 
 class DistributedEngine:
@@ -163,6 +171,17 @@ class DistributedEngine:
         if ok:
             self.control.note_abort(request_id)
         return ok
+
+    def load_adapter(self, name: str, path: str) -> int:
+        """Adapter events travel in order with the request events, so a request that names the slot returned here
+        reaches every follower after the adapter did."""
+        slot = self.engine.load_adapter(name, path)
+        self.control.note_adapter("lora_load", name, path)
+        return slot
+
+    def unload_adapter(self, name: str) -> None:
+        self.engine.unload_adapter(name)
+        self.control.note_adapter("lora_unload", name)
 
     def step(self):
         return self.engine.step()

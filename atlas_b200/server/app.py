@@ -422,11 +422,10 @@ def create_app(state: ServerState) -> FastAPI:
         name, path = b.get("name"), b.get("path")
         if not name:
             raise BadRequest("'name' is required", "name")
-        from ..lora import load_adapter
         try:
-            S.adapters[name] = load_adapter(path, S.engine.engine.model) if path else S.adapters[name]
-            S.adapters[name].name = name
-            S.engine.engine.model.enable_lora().register(S.adapters[name])      # resident from now on, addressed by slot
+            path = path or S.adapters[name]["path"]
+            slot = S.engine.engine.load_adapter(name, path)      # resident on every rank from now on, addressed by slot
+            S.adapters[name] = {"path": path, "slot": slot}
         except KeyError:
             return _err(404, f"adapter '{name}' is not loaded and no path was given", "not_found_error")
         except Exception as e:

@@ -286,3 +286,25 @@ def test_output_sanitizer_rules():
     g = StreamGuards()
     assert not g.on_text("a perfectly ordinary paragraph without any repetition in it at all, just prose.")
     assert g.on_text(" and again the same thirty-something characters" * 4) and g.tripped == "repeated_phrase"
+
+
+def test_lora_control_routes_load_an_adapter_and_requests_use_it(tmp_path):
+    """``/v1/lora/load`` reads a PEFT directory through the engine (every rank would), ``/v1/lora/active`` lists it, a
+    request can name it, and a request without a name runs on the active adapter."""
+    from tests.test_lora_cpu import _write_adapter
+    c, aeng, state = _client()
+    try:
+        path = _write_adapter(str(tmp_path / "ad"), tiny_dense())
+        assert c.post("/v1/lora/load", json={"name": "nope"}).status_code == 404
+        r = c.post("/v1/lora/load", json={"name": "ad", "path": path, "activate": False})
+        assert r.status_code == 200 and r.json() == {"active": None, "loaded": ["ad"]}
+        body = {"model": "tiny", "prompt": "hello there", "max_tokens": 8, "temperature": 0}
+        base = c.post("/v1/completions", json=body).json()["choices"][0]["text"]
+        with_ad = c.post("/v1/completions", json=dict(body, adapter="ad")).json()["choices"][0]["text"]
+        assert with_ad != base
+        assert c.post("/v1/completions", json=dict(body, adapter="missing")).status_code >= 400
+        assert c.post("/v1/lora/load", json={"name": "ad"}).json()["active"] == "ad"      # already resident: activate it
+        assert c.get("/v1/lora/active").json() == {"active": "ad", "loaded": ["ad"]}
+        assert c.post("/v1/completions", json=body).json()["choices"][0]["text"] == with_ad
+    finally:
+        aeng.shutdown(drain=False)
