@@ -31,7 +31,7 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--bind", default="0.0.0.0")
     s.add_argument("--max-seq-len", type=int, default=32768)
     s.add_argument("--block-size", type=int, default=16)
-    s.add_argument("--kv-cache-dtype", default="fp8", choices=["auto", "fp8", "bf16", "nvfp4"])
+    s.add_argument("--kv-cache-dtype", default="fp8", choices=["auto", "fp8", "bf16", "nvfp4", "turbo8"])
     s.add_argument("--sparse-attention-blocks", type=int, default=0,
                    help="long contexts: decode attention reads at most this many KV blocks per sequence, chosen by a "
                         "block predictor (first and most recent blocks always kept); 0 = dense attention")

@@ -45,7 +45,7 @@ class QuantConfig:
     method: str = "none"
     weight_block: Tuple[int, int] = (128, 128)
     group_size: int = 16
-    kv_cache_dtype: str = "auto"  # auto | bf16 | fp8 | nvfp4
+    kv_cache_dtype: str = "auto"  # auto | bf16 | fp8 | turbo8 (Hadamard-rotated fp8) | nvfp4
     # modules kept in high precision (substring match on parameter prefix)
     ignore: List[str] = field(default_factory=lambda: ["lm_head", "embed_tokens", "router", "gate."])
     # when method is nvfp4 for experts only (config 3: attention bf16, experts nvfp4)

@@ -213,6 +213,7 @@ struct RopeKvParams {
   const int* slot_mapping;
   int T, Hq, Hkv, D, rotary_dim, block_size, kv_fp8, plus_one;
   int v_separate;          // V rows are written by v_write_pages_kernel (prefill-size batches), not here
+  int rotate;              // Walsh-Hadamard rotation of every q / k / v head before the write (head_dim-128 kernel only)
   float eps, inv_k_scale, inv_v_scale;
 };
 
@@ -304,6 +305,45 @@ rope_kv_write_kernel(const RopeKvParams p) {
 // Same contract as rope_kv_write_kernel for head_dim = rotary_dim = 128: a lane owns four consecutive dims, the rotation
 // partner (d +- 64) sits in lane ^ 16, so the whole unit stays in registers (one 8-byte load and store per lane, no
 // shared memory).
+// Orthonormal 128-point Walsh-Hadamard transform of one head held four consecutive dims per lane (natural order,
+// H[i][j] = (-1)^popcount(i & j) / sqrt(128)): two butterfly stages inside the lane, five across lanes.  The transform is
+// its own inverse and keeps dot products, so attention over rotated q / k / v gives the rotated output; what it buys is
+// a near-Gaussian coordinate distribution without the outlier channels that cost an FP8 cache its range.
+__device__ __forceinline__ void wht128_lane4(float (&o)[4], int lane) {
+  const float a = o[0] + o[1], b = o[0] - o[1], c = o[2] + o[3], d = o[2] - o[3];
+  o[0] = a + c; o[1] = b + d; o[2] = a - c; o[3] = b - d;
+#pragma unroll
+  for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float pv = __shfl_xor_sync(0xffffffffu, o[i], m);
+      o[i] = (lane & m) ? pv - o[i] : o[i] + pv;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o[i] *= 0.08838834764831845f;
+}
+
+// In-place rotation of bf16 rows [T, H, 128] (the attention output of a rotated cache back to model coordinates).
+__global__ void __launch_bounds__(128)
+wht_d128_kernel(__nv_bfloat16* x, long long ld, long long units, int H) {
+  chain_trigger();
+  chain_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * 4 + warp;
+  if (unit >= units) return;
+  __nv_bfloat16* row = x + (unit / H) * ld + (unit % H) * 128 + lane * 4;
+  const uint2 raw = *reinterpret_cast<const uint2*>(row);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  float o[4] = {a.x, a.y, b.x, b.y};
+  wht128_lane4(o, lane);
+  uint2 pk;
+  pk.x = pack_bf16x2(o[0], o[1]);
+  pk.y = pack_bf16x2(o[2], o[3]);
+  *reinterpret_cast<uint2*>(row) = pk;
+}
+
 __global__ void __launch_bounds__(128)
 rope_kv_write_d128_kernel(const RopeKvParams p) {
   chain_trigger();
@@ -354,6 +394,7 @@ rope_kv_write_d128_kernel(const RopeKvParams p) {
       o[i] = lane < 16 ? v[i] * cc[i] - pv * sn[i] : v[i] * cc[i] + pv * sn[i];
     }
   }
+  if (p.rotate) wht128_lane4(o, lane);
   if (is_q) {
     uint2 pk;
     pk.x = pack_bf16x2(o[0], o[1]);
@@ -667,15 +708,18 @@ extern "C" int atlas_rope_kv_write(void* q, long long ldq, const void* k, long l
   p.k_norm_w = reinterpret_cast<const __nv_bfloat16*>(k_norm_w);
   p.k_cache = k_cache; p.v_cache = v_cache; p.slot_mapping = slot_mapping;
   p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.rotary_dim = rotary_dim; p.block_size = block_size;
+  p.rotate = (kv_fp8 & 8) ? 1 : 0;           // bit 3 of the cache mode asks for the Hadamard rotation
+  kv_fp8 &= 7;
   p.kv_fp8 = kv_fp8; p.plus_one = plus_one; p.eps = eps; p.inv_k_scale = 1.f / k_scale; p.inv_v_scale = 1.f / v_scale;
   // prefill-size batches with 16-token FP8 pages: V goes through the page-row writer (16-byte stores)
-  p.v_separate = (T >= 256 && kv_fp8 == 1 && block_size == 16 && D % 4 == 0 && (ldv % 4) == 0 &&
+  p.v_separate = (T >= 256 && kv_fp8 == 1 && !p.rotate && block_size == 16 && D % 4 == 0 && (ldv % 4) == 0 &&
                   (reinterpret_cast<uintptr_t>(v) & 7) == 0) ? 1 : 0;
   const long long units = (long long)T * (Hq + (p.v_separate ? 1 : 2) * Hkv);
   const int grid = (int)((units + 3) / 4);
   const bool d128 = D == 128 && rotary_dim == 128 && (ldq % 4) == 0 && (ldk % 4) == 0 && (ldv % 4) == 0 &&
                     ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 7) == 0 &&
                     (reinterpret_cast<uintptr_t>(rope) & 15) == 0;
+  if (p.rotate && !d128) return -2;                                   // so is the rotation
   if (kv_fp8 == 2 && (!d128 || block_size % 16)) return -2;          // the NVFP4 cache is written by the head_dim-128 kernel only
   if (d128)
     launch_chain_if(T <= 256, rope_kv_write_d128_kernel, dim3(grid), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream), p);
@@ -686,6 +730,15 @@ extern "C" int atlas_rope_kv_write(void* q, long long ldq, const void* k, long l
     const long long vunits = (long long)((T + 15) / 16) * Hkv;
     launch_chain_if(false, v_write_pages_kernel, dim3((unsigned)((vunits + 3) / 4)), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream), p);
   }
+  return cudaGetLastError() == cudaSuccess ? 0 : -20;
+}
+
+extern "C" int atlas_wht_d128(void* x, long long ld, int T, int H, void* stream) {
+  if (T <= 0 || H <= 0) return 0;
+  if ((ld % 4) || (reinterpret_cast<uintptr_t>(x) & 7)) return -1;
+  const long long units = (long long)T * H;
+  launch_chain_if(T <= 256, wht_d128_kernel, dim3((unsigned)((units + 3) / 4)), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream),
+                  reinterpret_cast<__nv_bfloat16*>(x), ld, units, H);
   return cudaGetLastError() == cudaSuccess ? 0 : -20;
 }
 

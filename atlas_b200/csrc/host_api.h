@@ -53,6 +53,7 @@ int atlas_rope_kv_write(void* q, long long ldq, const void* k, long long ldk, co
                         void* k_cache, void* v_cache, const int* slot_mapping, int T, int Hq, int Hkv, int D,
                         int rotary_dim, int block_size, int kv_fp8, int plus_one, float eps, float k_scale,
                         float v_scale, void* stream);
+int atlas_wht_d128(void* x, long long ld, int T, int H, void* stream);
 int atlas_gated_rmsnorm(const void* x, long long ldx, const void* z, long long ldz, const void* w, void* y,
                         long long ldy, int T, int H, int D, float eps, void* stream);
 

@@ -129,6 +129,11 @@ class LLMEngine:
                 from .models.decoder import KV_NVFP4
                 return KV_NVFP4
             want = "fp8"
+        if want == "turbo8":
+            # Hadamard-rotated heads in an FP8 cache: same bytes and the same attention kernels as "fp8"; a model the
+            # rotation does not cover keeps the plain FP8 cache
+            self.model.set_kv_rotation(True)
+            want = "fp8"
         if want == "bf16":
             return torch.bfloat16           # GPU: the general mma.sync attention kernel on a 16-bit cache
         if want == "fp8" or (want == "auto" and self.model.device.type == "cuda"):

@@ -42,6 +42,7 @@ class Attention:
         self.k_norm: Optional[torch.Tensor] = None
         self.lora = None                    # lora.LoraSet shared by the model's layers
         self.selector = None                # kv.sparse_select.BlockSelector: block-selected decode attention (long contexts)
+        self.kv_rotate = False              # "turbo8" cache: q / k / v heads Hadamard-rotated before the FP8 cache write
 
     # ------------------------------------------------------------------ weights
     def _kv_slice(self, w: torch.Tensor) -> torch.Tensor:
@@ -114,19 +115,21 @@ class Attention:
         rope_pos, rope_cache = batch.rope_inputs(rope_cache, cfg.mrope_section)
         q = ops.qk_norm_rope_kv_write(q, k, v, rope_pos, rope_cache, cfg.rotary_dim, k_cache, v_cache,
                                       batch.slot_mapping, k_scale, v_scale, self.q_norm, self.k_norm,
-                                      cfg.rms_norm_eps, cfg.norm_plus_one)
+                                      cfg.rms_norm_eps, cfg.norm_plus_one, rotate=self.kv_rotate)
         if self.selector is not None:
             from ..kv.sparse_select import attend_selected
             self.selector.on_write(self.layer_idx, k_cache, batch, k_scale)
             out = attend_selected(ops.paged_attention, self.selector, self.layer_idx, q, k_cache, v_cache, batch, self.scale,
                                   k_scale, v_scale, self.window)
         else:
-            if (self.o.kind == "fp8_block" and not self.gated and self.o.bias is None
+            if (self.o.kind == "fp8_block" and not self.gated and self.o.bias is None and not self.kv_rotate
                     and (self.lora is None or batch.adapter_rows is None)):
                 a = ops.paged_attention_fp8_out(q, k_cache, v_cache, batch, self.scale, k_scale, v_scale, self.window)
                 if a is not None:
                     return a                  # decode step: rows already quantised for the output projection
             out = ops.paged_attention(q, k_cache, v_cache, batch, self.scale, k_scale, v_scale, self.window)
+        if self.kv_rotate:
+            out = ops.head_rotate(out)        # sum_j p_j (H v_j) = H o, and H is its own inverse
         out = out.reshape(T, nq)
         if self.gated:
             gate = qkv[:, nq + 2 * nkv:]

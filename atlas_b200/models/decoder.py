@@ -310,6 +310,26 @@ class DecoderLM:
                     shared.lora, shared.lora_prefix = self.lora, f"layers.{l.idx}.mlp.shared_expert."
         return self.lora
 
+    def set_kv_rotation(self, on: bool = True) -> bool:
+        """"turbo8" cache: every plain attention layer (the draft head's included) rotates its q / k / v heads with the
+        orthonormal Walsh-Hadamard transform before the FP8 cache write and rotates the attention output back.  Dot
+        products are unchanged (the transform is orthogonal), rotated coordinates are near-Gaussian, so the FP8 range
+        is not spent on a few outlier channels.  Returns False (nothing changed) when the model has layers the rotation
+        does not cover: latent attention, or a head size other than 128 with full rotary width on the GPU.
+        Reference: ``kernels/gb10/common/reshape_and_cache_turbo.cu`` (turbo8 = WHT + e4m3)."""
+        from ..layers.attention import Attention
+        cfg = self.cfg
+        d = cfg.head_dim
+        if cfg.kv_lora_rank > 0 or d & (d - 1):
+            return False
+        if self.device.type == "cuda" and not (d == 128 and cfg.rotary_dim == 128):
+            return False
+        layers = list(self.layers) + ([self.mtp.layer] if self.mtp is not None else [])
+        for l in layers:
+            if isinstance(getattr(l, "mixer", None), Attention):
+                l.mixer.kv_rotate = bool(on)
+        return True
+
     def register_adapter(self, adapter) -> int:
         """Make ``adapter`` (whole, as loaded) resident on this rank, cut like the base weights; returns its slot."""
         from ..lora import localize

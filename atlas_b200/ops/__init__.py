@@ -256,12 +256,22 @@ def linear_residual_norm(a, w: LinearWeight, residual: torch.Tensor, norm_w: tor
 
 # ----------------------------------------------------------------------------- attention
 def qk_norm_rope_kv_write(q, k, v, positions, rope_cache, rotary_dim, k_cache, v_cache, slot_mapping,
-                          k_scale=1.0, v_scale=1.0, q_norm_w=None, k_norm_w=None, eps=1e-6, norm_plus_one=False):
+                          k_scale=1.0, v_scale=1.0, q_norm_w=None, k_norm_w=None, eps=1e-6, norm_plus_one=False, rotate=False):
+    """``rotate``: every q / k / v head goes through the orthonormal Walsh-Hadamard transform after RoPE, so the cache
+    holds rotated keys and values (the "turbo8" cache: rotation + FP8) and the attention output comes out rotated too
+    (``head_rotate`` takes it back)."""
     if on_gpu(q):
         return cuda_ops().qk_norm_rope_kv_write(q, k, v, positions, rope_cache, rotary_dim, k_cache, v_cache,
-                                                slot_mapping, k_scale, v_scale, q_norm_w, k_norm_w, eps, norm_plus_one)
+                                                slot_mapping, k_scale, v_scale, q_norm_w, k_norm_w, eps, norm_plus_one, rotate)
     return ref.qk_norm_rope_kv_write(q, k, v, positions, rope_cache, rotary_dim, k_cache, v_cache, slot_mapping,
-                                     k_scale, v_scale, q_norm_w, k_norm_w, eps, norm_plus_one)
+                                     k_scale, v_scale, q_norm_w, k_norm_w, eps, norm_plus_one, rotate)
+
+
+def head_rotate(x: torch.Tensor) -> torch.Tensor:
+    """Orthonormal Walsh-Hadamard transform along the last (head) dimension of ``x [T, H, D]``; its own inverse."""
+    if on_gpu(x) and x.shape[-1] == 128 and x.dtype == torch.bfloat16 and x.stride(2) == 1 and x.stride(1) == 128:
+        return cuda_ops().wht_d128(x)
+    return ref.head_rotate(x)
 
 
 def paged_attention(q, k_cache, v_cache, batch, scale, k_scale=1.0, v_scale=1.0, sliding_window=None) -> torch.Tensor:

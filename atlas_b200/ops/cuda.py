@@ -53,6 +53,7 @@ def load() -> None:
     lib.atlas_rope_kv_write.argtypes = [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                                         _i, _i, _i, _i, _f, _f, _f, _vp]
     lib.atlas_gated_rmsnorm.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _ll, _i, _i, _i, _f, _vp]
+    lib.atlas_wht_d128.argtypes = [_vp, _ll, _i, _i, _vp]
     lib.atlas_attn_decode.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _f, _f, _f, _i, _i, _i,
                                       _i, _i, _i, _vp, _vp, _vp, _vp]
     lib.atlas_attn_prefill.argtypes = [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _f, _f, _f, _i,
@@ -476,8 +477,18 @@ def _kv_layout_ok(k_cache: torch.Tensor, v_cache: torch.Tensor) -> None:
         raise KernelError("the GPU attention kernels read an FP8 (e4m3), bf16 or NVFP4 KV cache")
 
 
+def wht_d128(x: torch.Tensor) -> torch.Tensor:
+    """In-place orthonormal Walsh-Hadamard rotation of every 128-wide head of ``x [T, H, 128]`` (bf16)."""
+    T, H, D = x.shape
+    _dev(x)
+    if D != 128 or x.dtype != torch.bfloat16 or x.stride(2) != 1 or x.stride(1) != D:
+        raise KernelError("wht_d128 takes bf16 rows of 128-wide heads")
+    _check(lib().atlas_wht_d128(x.data_ptr(), x.stride(0), T, H, _stream()), "wht_d128")
+    return x
+
+
 def qk_norm_rope_kv_write(q, k, v, positions, rope_cache, rotary_dim, k_cache, v_cache, slot_mapping, k_scale, v_scale,
-                          q_norm_w, k_norm_w, eps, norm_plus_one):
+                          q_norm_w, k_norm_w, eps, norm_plus_one, rotate=False):
     T, Hq, D = q.shape
     Hkv = k.shape[1]
     _dev(q)
@@ -487,7 +498,7 @@ def qk_norm_rope_kv_write(q, k, v, positions, rope_cache, rotary_dim, k_cache, v
     bs = k_cache.shape[1]
     if is_nvfp4_kv(k_cache) and nvfp4_kv_head_dim(k_cache) != D:
         raise KernelError("NVFP4 KV cache was allocated for a different head_dim")
-    kv_mode = 2 if is_nvfp4_kv(k_cache) else (1 if k_cache.dtype == FP8 else 0)
+    kv_mode = (2 if is_nvfp4_kv(k_cache) else (1 if k_cache.dtype == FP8 else 0)) | (8 if rotate else 0)
     if checked.ENABLED:
         checked.kv_write(slot_mapping, positions, k_cache.shape[0], bs, rope_cache.shape[0] if rotary_dim else 0)
     _check(lib().atlas_rope_kv_write(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),

@@ -131,13 +131,32 @@ def head_rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, plus_one: bool) -
     return (xf * torch.rsqrt(var + eps) * wf).to(x.dtype)
 
 
+_HADAMARD: dict = {}
+
+
+def hadamard(d: int, device="cpu") -> torch.Tensor:
+    """Orthonormal Sylvester (natural-order) Hadamard matrix ``[d, d]``, ``H[i][j] = (-1)^popcount(i & j) / sqrt(d)``."""
+    key = (d, str(device))
+    if key not in _HADAMARD:
+        assert d > 0 and d & (d - 1) == 0, "the Walsh-Hadamard rotation needs a power-of-two head_dim"
+        h = torch.ones(1, 1)
+        while h.shape[0] < d:
+            h = torch.cat([torch.cat([h, h], 1), torch.cat([h, -h], 1)], 0)
+        _HADAMARD[key] = (h / d ** 0.5).to(device)
+    return _HADAMARD[key]
+
+
+def head_rotate(x: torch.Tensor) -> torch.Tensor:
+    return (x.float() @ hadamard(x.shape[-1], x.device)).to(x.dtype)
+
+
 def qk_norm_rope_kv_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, positions: torch.Tensor,
                           rope_cache: torch.Tensor, rotary_dim: int,
                           k_cache: torch.Tensor, v_cache: torch.Tensor, slot_mapping: torch.Tensor,
                           k_scale: float = 1.0, v_scale: float = 1.0,
                           q_norm_w: Optional[torch.Tensor] = None, k_norm_w: Optional[torch.Tensor] = None,
-                          eps: float = 1e-6, norm_plus_one: bool = False) -> torch.Tensor:
-    """Fused (q/k head RMSNorm) + RoPE + (FP8 quant) + paged cache write.
+                          eps: float = 1e-6, norm_plus_one: bool = False, rotate: bool = False) -> torch.Tensor:
+    """Fused (q/k head RMSNorm) + RoPE + (head rotation) + (FP8 quant) + paged cache write.
 
     ``q [T,Hq,D]``, ``k,v [T,Hkv,D]``.  Returns the roped ``q``; k/v go to the cache at
     ``slot_mapping`` (rows with slot < 0 are skipped).
@@ -147,6 +166,8 @@ def qk_norm_rope_kv_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos
         k = head_rmsnorm(k, k_norm_w, eps, norm_plus_one)
     q = apply_rope(q, positions, rope_cache, rotary_dim)
     k = apply_rope(k, positions, rope_cache, rotary_dim)
+    if rotate:
+        q, k, v = head_rotate(q), head_rotate(k), head_rotate(v)
     nb, bs, hkv, d = k_cache.shape
     valid = slot_mapping >= 0
     slots = slot_mapping[valid].long()

@@ -149,7 +149,7 @@ def main():
     ap.add_argument("--ep-mode", default="auto", choices=["auto", "allreduce", "alltoall"],
                     help="expert-parallel data path: local experts + fused combine/all-reduce, or peer-memory all-to-all")
     ap.add_argument("--ngram-speculative", action="store_true", help="prompt-lookup drafts (no draft model), --num-drafts deep")
-    ap.add_argument("--kv-cache-dtype", default="fp8", choices=["fp8", "bf16", "nvfp4"], help="paged KV cache dtype (the headline uses fp8)")
+    ap.add_argument("--kv-cache-dtype", default="fp8", choices=["fp8", "bf16", "nvfp4", "turbo8"], help="paged KV cache dtype (the headline uses fp8)")
     ap.add_argument("--self-speculative", action="store_true", help="layer-skipping drafts from the target model itself")
     ap.add_argument("--nvfp4-activations", action="store_true",
                     help="NVFP4 checkpoints: quantise activations to NVFP4 too (block-scaled FP4 x FP4 tensor-core GEMM)")

@@ -146,3 +146,47 @@ def test_ngram_proposer_lookup():
     assert ctl.propose(seq) == [9, 2, 3]            # "4 5 9" -> after its earlier occurrence come 9 2 3
     seq.output_tokens += [7]
     assert ctl.propose(seq) == []                   # nothing ends in "9 7"
+
+
+def test_rotated_kv_cache_keeps_attention_and_spends_fp8_range_better():
+    """The "turbo8" cache: heads rotated by the orthonormal Walsh-Hadamard transform before the cache write.  With a
+    full-precision cache the attention output (rotated back) equals the plain one; with an FP8 cache and an outlier
+    channel in the keys the rotated cache is the more accurate of the two."""
+    from atlas_b200 import ops
+    from atlas_b200.models.batch import ForwardBatch
+    from atlas_b200.ops import reference as ref
+    torch.manual_seed(0)
+    T, Hq, Hkv, D, bs = 40, 4, 2, 64, 16
+    h = ref.hadamard(D)
+    assert torch.allclose(h @ h, torch.eye(D), atol=1e-6)                 # orthonormal and its own inverse
+    q, k, v = torch.randn(T, Hq, D), torch.randn(T, Hkv, D), torch.randn(T, Hkv, D)
+    k[:, :, 7] *= 30.0                                                    # an outlier channel
+    q[:, :, 7] *= 0.05
+    rope = ref.build_rope_cache(D, 64, 1e4, None, "cpu")
+    fb = ForwardBatch.build([[0] * T], [0], [[0, 1, 2]], bs)
+
+    def run(dtype, rotate, k_scale=1.0):
+        kc, vc = torch.zeros(4, bs, Hkv, D, dtype=dtype), torch.zeros(4, bs, Hkv, D, dtype=dtype)
+        qr = ops.qk_norm_rope_kv_write(q.clone(), k, v, fb.positions.int(), rope, D, kc, vc, fb.slot_mapping.int(), k_scale, 1.0,
+                                       rotate=rotate)
+        out = ops.paged_attention(qr, kc, vc, fb, D ** -0.5, k_scale, 1.0)
+        return ops.head_rotate(out) if rotate else out
+    exact = run(torch.float32, False)
+    assert torch.allclose(run(torch.float32, True), exact, atol=2e-4)
+    err_plain = (run(torch.float8_e4m3fn, False, 0.25) - exact).pow(2).mean().sqrt()
+    err_rot = (run(torch.float8_e4m3fn, True, 0.25) - exact).pow(2).mean().sqrt()
+    assert err_rot < err_plain
+
+
+def test_engine_with_rotated_fp8_cache():
+    cfg = tiny_dense()
+    eng = LLMEngine(build_model(cfg).init_random(0), EngineConfig(num_kv_blocks=64, max_num_seqs=4, kv_cache_dtype="turbo8"))
+    assert eng.kv_dtype == torch.float8_e4m3fn and all(l.mixer.kv_rotate for l in eng.model.layers)
+    plain = LLMEngine(build_model(cfg).init_random(0), EngineConfig(num_kv_blocks=64, max_num_seqs=4, kv_cache_dtype="fp8"))
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, 1024, (24,), generator=g).tolist() for _ in range(3)]
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    a = [o.output_tokens for o in eng.generate(prompts, sp)]
+    b = [o.output_tokens for o in plain.generate(prompts, sp)]
+    assert all(len(x) == 6 for x in a)
+    assert sum(x[0] == y[0] for x, y in zip(a, b)) >= 2        # same model, two roundings of the same cache contents

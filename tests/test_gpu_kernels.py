@@ -639,3 +639,33 @@ def test_gemm_fused_residual_norm_quant_and_deferred_factor(K, M, N, Kd, plus_on
     deq = (qa.float().view(M, -1, 128) * sa.contiguous()[..., None]).view(M, 256)
     _status_ok(K)
     assert _rel_rms(deq, want_a) < 6e-2
+
+
+@pytest.mark.parametrize("T", [7, 300])
+def test_rotated_kv_write_and_head_rotation(K, T):
+    """The "turbo8" cache write: q / k / v heads go through the orthonormal 128-point Walsh-Hadamard transform after
+    RoPE (prefill-size batches too, which otherwise send V through the page-row writer), against the matrix form; and
+    the in-place rotation of an attention output, which is its own inverse."""
+    torch.manual_seed(21)
+    D, Hq, Hkv, bs, nb = 128, 8, 2, 16, 24
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=DEV).bfloat16()
+    qkv[:, 5::128] *= 20.0                                 # an outlier channel in every head
+    q = qkv[:, :Hq * D].view(T, Hq, D)
+    k = qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+    pos = torch.arange(T, device=DEV, dtype=torch.int32)
+    slots = torch.randperm(nb * bs, device=DEV)[:T].to(torch.int32)
+    rope = ref.build_rope_cache(D, 512, 1e6, None, DEV)
+    qn = (torch.rand(D, device=DEV) + 0.5).bfloat16()
+    kc, vc = _mk_cache(K, nb, bs, Hkv, D)
+    kc_r, vc_r = torch.zeros_like(kc.contiguous()), torch.zeros_like(vc.contiguous())
+    q_ref = ref.qk_norm_rope_kv_write(q.clone(), k, v, pos, rope, D, kc_r, vc_r, slots, 0.5, 0.25, qn, qn, 1e-6, False, rotate=True)
+    q_out = K.qk_norm_rope_kv_write(q, k, v, pos, rope, D, kc, vc, slots, 0.5, 0.25, qn, qn, 1e-6, False, rotate=True)
+    _status_ok(K)
+    assert _rel_rms(q_out, q_ref) < 1e-2
+    assert _rel_rms(kc.float(), kc_r.float()) < 4e-2 and _rel_rms(vc.float(), vc_r.float()) < 4e-2
+    x = torch.randn(T, Hq, D, device=DEV).bfloat16()
+    y = K.wht_d128(x.clone())
+    _status_ok(K)
+    assert _rel_rms(y, ref.head_rotate(x)) < 5e-3
+    assert _rel_rms(K.wht_d128(y.clone()), x) < 8e-3       # an involution up to bf16 rounding

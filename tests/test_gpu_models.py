@@ -186,8 +186,10 @@ def test_gdn_chunked_matches_recurrence(K, split, monkeypatch):
         assert _rel_rms(st_c["h"][slot], st_r["h"][slot]) < 1e-2, slot
 
 
-def _logits_both_ways(cfg, prompt_len=48, kv_dtype=torch.float8_e4m3fn, high_precision_layers=()):
+def _logits_both_ways(cfg, prompt_len=48, kv_dtype=torch.float8_e4m3fn, high_precision_layers=(), rotate=False):
     model = build_model(cfg, device=DEV).init_random(0)
+    if rotate:
+        assert model.set_kv_rotation(True)
     g = torch.Generator().manual_seed(3)
     toks = torch.randint(0, cfg.vocab_size, (prompt_len,), generator=g).tolist()
     outs = []
@@ -208,7 +210,7 @@ def _logits_both_ways(cfg, prompt_len=48, kv_dtype=torch.float8_e4m3fn, high_pre
 
 
 @pytest.mark.parametrize("name", ["dense_fp8", "dense_bf16", "moe_fp8", "hybrid_bf16", "hybrid_fp8", "nemotron_bf16", "nemotron_fp8",
-                                  "dense_fp8_kvbf16", "dense_fp8_kvmixed", "mla_bf16", "mla_fp8", "gemma_bf16", "gemma_fp8"])
+                                  "dense_fp8_kvbf16", "dense_fp8_kvmixed", "dense_fp8_kvturbo8", "mla_bf16", "mla_fp8", "gemma_bf16", "gemma_fp8"])
 def test_model_logits_kernels_vs_reference(K, name):
     kv_dtype, hi = torch.float8_e4m3fn, ()
     if name.endswith("kvbf16"):
@@ -255,7 +257,7 @@ def test_model_logits_kernels_vs_reference(K, name):
                           max_position_embeddings=4096, quant=QuantConfig(method="fp8_block"))
     else:
         cfg = _hybrid_cfg("fp8_block" if name.endswith("fp8") else "none")
-    got, want = _logits_both_ways(cfg, kv_dtype=kv_dtype, high_precision_layers=hi)
+    got, want = _logits_both_ways(cfg, kv_dtype=kv_dtype, high_precision_layers=hi, rotate=name.endswith("kvturbo8"))
     torch.cuda.synchronize()
     assert K.check_status() == 0
     # fp8 activations feeding a top-2-of-8 router flip a few expert choices between the two paths; that case is
