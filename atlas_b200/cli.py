@@ -31,6 +31,8 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--bind", default="0.0.0.0")
     s.add_argument("--max-seq-len", type=int, default=32768)
     s.add_argument("--block-size", type=int, default=16)
+    s.add_argument("--mtp-vocab", type=int, default=0, help="draft steps score this many rows of the lm_head (0 = all)")
+    s.add_argument("--mtp-vocab-rank", default="id", help="'id' (first rows) or the path of a ranked token-id table")
     s.add_argument("--kv-cache-dtype", default="fp8", choices=["auto", "fp8", "bf16", "nvfp4", "turbo8"])
     s.add_argument("--sparse-attention-blocks", type=int, default=0,
                    help="long contexts: decode attention reads at most this many KV blocks per sequence, chosen by a "
@@ -138,6 +140,7 @@ def _engine_config(args, mcfg):
     prefix = args.enable_prefix_caching if args.enable_prefix_caching is not None else True
     return EngineConfig(max_seq_len=min(args.max_seq_len, max(mcfg.max_position_embeddings, 1)), block_size=args.block_size,
                         kv_cache_dtype=args.kv_cache_dtype, dcut_ratio=args.dcut_ratio,
+                        mtp_draft_vocab=getattr(args, "mtp_vocab", 0), mtp_vocab_rank=getattr(args, "mtp_vocab_rank", "id"),
                         sparse_attention_blocks=args.sparse_attention_blocks,
                         kv_high_precision_layers=tuple(int(v) for v in args.kv_high_precision_layers.split(",") if v.strip()),
                         gpu_memory_utilization=args.gpu_memory_utilization,

@@ -508,6 +508,8 @@ class EngineConfig:
     speculative: bool = False
     num_drafts: int = 0
     mtp_gate: bool = True
+    mtp_draft_vocab: int = 0                  # > 0: draft steps score this many rows of the lm_head (a quantised draft-only head)
+    mtp_vocab_rank: str = "id"                # "id": the first rows; or the path of a ranked-ids table (utils/vocab_rank.py)
     dcut_ratio: float = 0.0                   # > 0: keep this fraction of the batch's draft rows, ranked by drafter confidence
     ngram_speculative: bool = False           # prompt-lookup drafts (no draft model); uses num_drafts
     self_speculative: bool = False            # layer-skipping drafts from the target model itself; uses num_drafts

@@ -90,6 +90,11 @@ class LLMEngine:
         self.runner = ModelRunner(model, self.cache, self.cfg)
         self.spec = SpecController(self, self.cfg) if (self.cfg.speculative and model.mtp is not None
                                                          and self.cfg.num_drafts > 0) else None
+        if self.spec is not None and 0 < self.cfg.mtp_draft_vocab < self.mcfg.vocab_size:
+            from .utils.vocab_rank import load_ranked_ids, select_rows
+            ranked = None if self.cfg.mtp_vocab_rank in ("", "id") else load_ranked_ids(self.cfg.mtp_vocab_rank)
+            model.build_draft_head(select_rows(self.cfg.mtp_draft_vocab, self.mcfg.vocab_size, ranked, self.mcfg.eos_ids()),
+                                   "fp8_block" if model.device.type == "cuda" else "dense")
         if self.spec is None and self.cfg.speculative and getattr(model, "dflash", None) is not None and self.cfg.num_drafts > 0:
             from .sched.spec import DFlashSpecController
             model.dflash.alloc_cache(num_blocks, self.cfg.block_size)

@@ -494,6 +494,58 @@ class DecoderLM:
             logits = torch.tanh(logits.float() / cap).mul_(cap).to(logits.dtype)
         return logits
 
+    def build_draft_head(self, row_ids: List[int], kind: str = "fp8_block") -> None:
+        """A draft-only language-model head over the token ids ``row_ids`` (ascending), quantised to ``kind``: draft
+        steps score these rows instead of the whole vocabulary (``draft_top1``).  On a vocabulary-parallel rank the head
+        holds the chosen rows of this rank's shard.  Reference: ``crates/spark-model/src/layers/mtp_head/ranked_head.rs``
+        (draft-only quantised head built from ranked rows of the full head)."""
+        ids = torch.tensor(sorted(int(t) for t in row_ids), dtype=torch.long)
+        lo = 0
+        if self.vocab_parallel:
+            shard = self.cfg.vocab_size // self.pctx.tp_size
+            lo = self.pctx.tp_rank * shard
+            ids = ids[(ids >= lo) & (ids < lo + shard)]
+        if ids.numel() == 0:
+            ids = torch.tensor([lo], dtype=torch.long)          # a rank never holds an empty head
+        n = int(ids.numel())
+        if self.device.type == "cuda" and n % 128:
+            # the GEMM tiles want a multiple of 128 rows: repeat the last row (same logit, same token id, so the
+            # argmax is unchanged) rather than add zero rows that could win against negative logits
+            ids = torch.cat([ids, ids[-1:].expand(128 - n % 128)])
+        w = self.lm_head.dequantized()[(ids - lo).to(self.lm_head.weight.device)]
+        if kind == "fp8_block" and (w.shape[1] % 128 or not w.is_floating_point()):
+            kind = "dense"
+        self.draft_head = LinearWeight.from_dense(w.contiguous(), kind)
+        self.draft_row_ids = ids.to(self.device)
+        self.draft_rows = n
+
+    @torch.inference_mode()
+    def draft_top1(self, hidden: torch.Tensor, want_logprob: bool = False):
+        """``(token ids [B], ln p(top-1) [B] or None)`` of a draft step: over the draft head's rows when one was built,
+        over the whole vocabulary otherwise.  The probability is taken over the rows that were scored."""
+        if getattr(self, "draft_head", None) is None:
+            lg = self.compute_logits(hidden)
+            tok = ops.argmax(lg)
+            lp = lg.float().log_softmax(-1).gather(-1, tok.view(-1, 1).long())[:, 0] if want_logprob else None
+            return tok, lp
+        lg = ops.linear(hidden, self.draft_head)
+        cap = self.cfg.final_logit_softcapping
+        if cap:
+            lg = torch.tanh(lg.float() / cap).mul_(cap).to(lg.dtype)
+        idx, val = ops.argmax(lg, with_value=True)
+        tok = self.draft_row_ids[idx.long()]
+        lse = torch.logsumexp(lg[:, :self.draft_rows].float(), -1) if want_logprob else None      # not the repeated rows
+        if self.vocab_parallel and self.pctx.comm is not None:
+            cols = [val.double(), tok.double()] + ([lse.double()] if want_logprob else [])
+            allp = self.pctx.comm.all_gather(torch.stack(cols, 1), dim=1).view(val.shape[0], self.pctx.tp_size, len(cols))
+            best = ref.argmax_first(allp[..., 0])
+            tok = allp[..., 1].gather(1, best[:, None])[:, 0].to(torch.int64)
+            val = allp[..., 0].gather(1, best[:, None])[:, 0]
+            if want_logprob:
+                lse = torch.logsumexp(allp[..., 2], -1)
+        lp = (val.float() - lse.float()) if want_logprob else None
+        return tok, lp
+
     @torch.inference_mode()
     def greedy_tokens(self, hidden: torch.Tensor, indices: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Argmax token per row without materialising the full-vocabulary logits on any rank: each rank takes the

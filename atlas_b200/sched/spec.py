@@ -165,12 +165,8 @@ class SpecController:
         conf: List[List[float]] = [[] for _ in want]            # ln of the drafter's top-1 probability per draft
 
         def top1(h):
-            lg = model.compute_logits(h)
-            tok = ops.argmax(lg)
-            if not dcut_on:
-                return tok.tolist(), None
-            lp = lg.float().log_softmax(-1).gather(-1, tok.view(-1, 1).long())[:, 0]
-            return tok.tolist(), lp.tolist()
+            tok, lp = model.draft_top1(h, want_logprob=dcut_on)      # the reduced draft head when the model has one
+            return tok.tolist(), (lp.tolist() if lp is not None else None)
         d, lp0 = top1(cur_h)
         for j, t in enumerate(d):
             drafts[j].append(int(t))

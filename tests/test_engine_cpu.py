@@ -190,3 +190,41 @@ def test_engine_with_rotated_fp8_cache():
     b = [o.output_tokens for o in plain.generate(prompts, sp)]
     assert all(len(x) == 6 for x in a)
     assert sum(x[0] == y[0] for x, y in zip(a, b)) >= 2        # same model, two roundings of the same cache contents
+
+
+def test_reduced_vocabulary_draft_head_is_lossless_and_ranked_rows_cover_more(tmp_path):
+    """A draft head over a subset of the vocabulary changes which drafts are proposed, never what is emitted; rows ranked
+    by a recorded frequency table (forced ids kept) accept more than the first rows by id."""
+    from atlas_b200.utils.vocab_rank import VocabRecorder, coverage, load_ranked_ids, select_rows
+    model = build_model(tiny_hybrid()).init_random(0)
+    prompts = _prompts()
+    sp = SamplingParams(max_tokens=12, ignore_eos=True)
+    base = LLMEngine(model, EngineConfig(num_kv_blocks=64, max_num_seqs=8)).generate(prompts, sp)
+    want = [o.output_tokens for o in base]
+    rec = VocabRecorder()
+    for o in base:
+        rec.add(o.output_tokens)
+    table = str(tmp_path / "rank.json")
+    rec.save(table)
+    ranked = load_ranked_ids(table)
+    assert ranked[0] == rec.counts.most_common(1)[0][0] or rec.counts[ranked[0]] == rec.counts.most_common(1)[0][1]
+    rows = select_rows(64, 1024, ranked, forced=(1023,))
+    assert rows == sorted(rows) and len(rows) == 64 and 1023 in rows
+    emitted = [t for o in want for t in o]
+    assert coverage(rows, emitted) > coverage(select_rows(64, 1024), emitted)
+
+    def run(**kw):
+        eng = LLMEngine(build_model(tiny_hybrid()).init_random(0),
+                        EngineConfig(num_kv_blocks=64, max_num_seqs=8, speculative=True, num_drafts=3, mtp_gate=False, **kw))
+        outs = eng.generate(prompts, sp)
+        assert [o.output_tokens for o in outs] == want
+        return eng
+    full = run()
+    whole = run(mtp_draft_vocab=1023)                       # nearly the whole vocabulary: drafts as good as the full head's
+    by_id = run(mtp_draft_vocab=64)
+    by_freq = run(mtp_draft_vocab=64, mtp_vocab_rank=table)
+    assert by_id.model.draft_rows == 64 and by_freq.model.draft_rows == 64 and getattr(full.model, "draft_head", None) is None
+    assert whole.stats.spec_accepted >= full.stats.spec_accepted - 2
+    assert by_freq.stats.spec_accepted >= by_id.stats.spec_accepted
+    cut = run(mtp_draft_vocab=64, mtp_vocab_rank=table, dcut_ratio=0.5)       # confidence taken over the reduced rows
+    assert cut.spec.dcut_pruned > 0

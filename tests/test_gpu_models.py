@@ -555,3 +555,33 @@ def test_lora_adapters_on_the_gpu_paths(K, kind):
     assert _rel_rms(got, want) < (0.06 if kind == "dense" else 0.12)
     assert _rel_rms(got[:24], plain[:24]) > 0.05                        # the adapter moves its own rows
     assert _rel_rms(got[24:], plain[24:]) < 5e-3                        # and leaves the base sequence alone
+
+
+def test_reduced_vocabulary_draft_head_on_gpu(K):
+    """The quantised draft-only head (rows of the lm_head, FP8 block scales, padded to the GEMM tile by repeating a row):
+    its top-1 over the chosen rows against the full logits restricted to the same rows."""
+    from atlas_b200.utils.vocab_rank import select_rows
+    cfg = ModelConfig(model_type="llama", family="dense", vocab_size=4096, hidden_size=512, intermediate_size=1024,
+                      num_hidden_layers=1, num_attention_heads=8, num_key_value_heads=2, head_dim=128, rope_theta=5e5,
+                      max_position_embeddings=4096, quant=QuantConfig(method="fp8_block"))
+    model = build_model(cfg, device=DEV).init_random(0)
+    g = torch.Generator().manual_seed(2)
+    ranked = torch.randperm(4096, generator=g)[:900].tolist()
+    rows = select_rows(700, 4096, ranked, forced=(4095,))
+    model.build_draft_head(rows)
+    assert model.draft_rows == 700 and model.draft_head.weight.shape[0] == 768 and model.draft_head.kind == "fp8_block"
+    torch.manual_seed(12)
+    h = torch.randn(33, 512, device=DEV).bfloat16()
+    tok, lp = model.draft_top1(h, want_logprob=True)
+    torch.cuda.synchronize()
+    assert K.check_status() == 0
+    full = model.compute_logits(h).float()
+    ids = torch.tensor(rows, device=DEV)
+    sub = full[:, ids]
+    want = ids[sub.argmax(-1)]
+    picked = full.gather(1, tok.view(-1, 1))[:, 0]
+    assert bool(torch.isin(tok, ids).all())
+    assert float((sub.max(-1).values - picked).max()) < 0.05          # the same row up to FP8 rounding of the head
+    assert int((tok == want).sum()) >= 28
+    want_lp = sub.log_softmax(-1).max(-1).values
+    assert float((lp - want_lp).abs().max()) < 0.3 and float((lp - want_lp).abs().mean()) < 0.1
