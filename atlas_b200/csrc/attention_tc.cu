@@ -9,9 +9,11 @@
 //   warps 2..5   converters: FP8 pages -> f16 operand tiles in the 128-byte-swizzled K-major layout the MMA reads
 //                (K: rows = tokens, V: rows = head dims; V pages are stored transposed in the cache, so both are
 //                16-byte-in, two-chunks-out moves)
-//   warps 6..9   softmax: one thread per query row.  The 128 scores of the row are pulled out of TMEM at once, P goes to
-//                shared memory as the A operand of the PV product, and O is rescaled in TMEM lazily (only when a row's
-//                max has grown by more than 2^8 since its reference point was set)
+//   warps 6..13  softmax: two threads per query row, 64 score columns each (warps w and w + 4 share the TMEM lanes of a
+//                row group).  A thread pulls its half row out of TMEM at once, the two halves agree on the row max
+//                through a spare TMEM column and an mbarrier per row group, P goes to shared memory as the A operand of
+//                the PV product, and O is rescaled in TMEM lazily (only when a row's max has grown by more than 2^8
+//                since its reference point was set), each thread its own 64 columns
 //
 // Q is converted to f16 once (softmax scale, K scale and log2(e) folded in), so S is already in the exp2 domain; the V
 // scale is applied with the final 1/l.  QK_{j+1} is issued before PV_j, so the tensor cores work on the next score tile
@@ -32,7 +34,7 @@ constexpr int kTcRows = 128;              // query rows per tile (tokens * G)
 constexpr int kTcKv = 128;                // kv tokens per tile
 constexpr int kTcPage = 16;
 constexpr int kTcPages = kTcKv / kTcPage;
-constexpr int kTcThreads = 320;
+constexpr int kTcThreads = 448;
 constexpr int kSub = 16 * 1024;           // one 128-row x 64-element f16 sub-tile
 constexpr int kPageBytes = kTcPage * kTcD;        // 2 KB (fp8)
 constexpr int kStageBytes = 2 * kTcPages * kPageBytes;   // K pages then V pages: 32 KB
@@ -71,6 +73,12 @@ ATLAS_DEVICE void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
       "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+ATLAS_DEVICE void tmem_st_32x32b_x1(uint32_t taddr, uint32_t v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};\n" ::"r"(taddr), "r"(v) : "memory");
+}
+ATLAS_DEVICE void tmem_ld_32x32b_x1(uint32_t taddr, uint32_t& v) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];\n" : "=r"(v) : "r"(taddr) : "memory");
+}
 ATLAS_DEVICE void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 ATLAS_DEVICE uint32_t fp8x2_to_h2(uint32_t v) {
   uint32_t r;
@@ -92,6 +100,7 @@ ATLAS_DEVICE void widen16(const uint4 v, uint4& lo, uint4& hi) {
   hi.x = fp8x2_to_h2(v.z); hi.y = fp8x2_to_h2(v.z >> 16); hi.z = fp8x2_to_h2(v.w); hi.w = fp8x2_to_h2(v.w >> 16);
 }
 
+// 14 warps are accounted as 16 (warps are allocated four at a time), so 128 registers per thread is the ceiling
 __global__ void __launch_bounds__(kTcThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const TcAttnParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -110,10 +119,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const TcAttnP
   uint64_t* v_ready = k_ready + 2;          // 4 converter warps
   uint64_t* pv_done = k_ready + 3;          // commit after PV: V tile, P tile and O are free / stable
   uint64_t* s_full = k_ready + 4;           // [2] commit after QK
-  uint64_t* s_free = k_ready + 6;           // [2] 4 softmax warps
-  uint64_t* p_ready = k_ready + 8;          // 4 softmax warps
-  uint64_t* q_conv = k_ready + 9;           // 8 warps (converters + softmax) finished the in-place Q conversion
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(k_ready + 10);
+  uint64_t* s_free = k_ready + 6;           // [2] 8 softmax warps
+  uint64_t* p_ready = k_ready + 8;          // 8 softmax warps
+  uint64_t* q_conv = k_ready + 9;           // 12 warps (converters + softmax) finished the in-place Q conversion
+  uint64_t* x_ready = k_ready + 10;         // [2 parities][4 row groups] the two softmax warps of a row group exchanged a value
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(k_ready + 18);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -133,9 +143,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const TcAttnP
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < kTcStages; ++s) { mbar_init(&stg_full[s], 1); mbar_init(&stg_empty[s], 4); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_free[s], 4); }
-    mbar_init(k_ready, 4); mbar_init(k_free, 1); mbar_init(v_ready, 4); mbar_init(pv_done, 1); mbar_init(p_ready, 4);
-    mbar_init(q_conv, 8);
+    for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_free[s], 8); }
+    mbar_init(k_ready, 4); mbar_init(k_free, 1); mbar_init(v_ready, 4); mbar_init(pv_done, 1); mbar_init(p_ready, 8);
+    mbar_init(q_conv, 12);
+    for (int s = 0; s < 8; ++s) mbar_init(&x_ready[s], 2);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -147,6 +158,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const TcAttnP
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS = tmem_base;            // two score buffers: columns [0,128) and [128,256)
   const uint32_t tO = tmem_base + 256;      // output accumulator: columns [256,384)
+  const uint32_t tX = tmem_base + 384;      // four columns through which the two threads of a row exchange a value
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer (whole warp)
@@ -218,16 +230,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const TcAttnP
       if (ok && n_kv > 0) issue_pv(n_kv - 1);
     }
   } else {
-    // ------------------------------------------------------------------ converters (warps 2..5) and softmax (6..9)
+    // ------------------------------------------------------------------ converters (warps 2..5) and softmax (6..13)
     const bool is_conv = warp < 6;
-    const int t128 = threadIdx.x - (is_conv ? 64 : 192);          // 0..127 within the role
+    const int t128 = threadIdx.x - 64;                            // converters: 0..127
     bool ok = true;
     // Q: bf16 -> f16 in place (element-wise, so the swizzled layout is untouched), scaled into the exp2 domain
     if (!mbar_wait(q_full, 0, abort_flag, p.status, 0x820)) ok = false;
     if (ok) {
-      const int t256 = threadIdx.x - 64;                          // 0..255 over both roles
+      const int t384 = threadIdx.x - 64;                          // 0..383 over both roles
       uint4* q4 = reinterpret_cast<uint4*>(sQ);
-      for (int i = t256; i < 2 * kSub / 16; i += 256) {
+      for (int i = t384; i < 2 * kSub / 16; i += 384) {
         uint4 v = q4[i];
         uint32_t* w = reinterpret_cast<uint32_t*>(&v);
 #pragma unroll
@@ -308,17 +320,40 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const TcAttnP
         if (ok) ok = conv_v(j);
       }
     } else {
-      // ---------------------------------------------------------------- softmax, one thread per query row
-      const int lane_group = warp & 3;
+      // ---------------------------------------------------------------- softmax, two threads per query row
+      const int lane_group = warp & 3;                           // the TMEM lanes a warp may touch: 32 * (warp % 4) ..
+      const int half = (warp - 6) >> 2;                          // 0: score / output columns [0, 64), 1: [64, 128)
+      const int col0 = half * 64;
       const int row = lane_group * 32 + lane;
       const uint32_t t_lane = (uint32_t)(lane_group * 32) << 16;
+      // One value per thread to the other thread of the same row: written to a TMEM column of the row's lane, handed
+      // over by a two-warp mbarrier, read back by the partner.  Slots alternate, and a slot is written again only after
+      // the barrier of the exchange in between, which the partner reaches after its read.
+      int xn = 0;
+      auto exchange = [&](float mine, float& other) -> bool {
+        const int par = xn & 1;
+        uint64_t* xb = &x_ready[par * 4 + lane_group];
+        tmem_st_32x32b_x1(tX + t_lane + par * 2 + half, __float_as_uint(mine));
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(xb);
+        if (!mbar_wait(xb, (xn >> 1) & 1, abort_flag, p.status, 0x833)) return false;
+        tc_fence_after();
+        uint32_t o;
+        tmem_ld_32x32b_x1(tX + t_lane + par * 2 + (half ^ 1), o);
+        tmem_ld_wait();
+        other = __uint_as_float(o);
+        ++xn;
+        return true;
+      };
       const int tok = q0 + row / G;                              // chunk-relative query token of this row
       const int head = kvh * G + row % G;
       const bool row_live = tok < q_len;
       const int pos = ctx0 + tok;                                // absolute position: keys [0, pos] are visible
       float m = -INFINITY, l = 0.f;
       const int sw = row & 7;
-      uint8_t* prow0 = sP + (row >> 3) * 1024 + sw * 128;
+      uint8_t* prow0 = sP + half * kSub + (row >> 3) * 1024 + sw * 128;      // this half's 64 columns are one sub-tile
       for (int j = 0; j < n_kv && ok; ++j) {
         const int sb = j & 1;
         const int kv0 = j * kTcKv;
@@ -326,30 +361,32 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const TcAttnP
         tc_fence_after();
         const uint32_t ts = tS + sb * 128 + t_lane;
         const int vis = row_live ? min(pos + 1, L) - kv0 : 0;     // columns [0, vis) of this tile are visible to the row
-        // ---- the whole score row into registers with the four loads in flight together, then release the buffer
-        uint32_t sr[4][32];
+        // ---- this thread's half of the score row into registers, both loads in flight together, then release the buffer
+        uint32_t sr[2][32];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(ts + c * 32, sr[c]);
+        for (int c = 0; c < 2; ++c) tmem_ld_32x32b_x32(ts + col0 + c * 32, sr[c]);
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_free[sb]);
         // tiles below the diagonal need no masking at all (same for every row of the warp)
-        const bool full = __all_sync(0xffffffffu, vis >= kTcKv);
+        const bool full = __all_sync(0xffffffffu, vis >= col0 + 64);
         if (!full) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+          for (int c = 0; c < 2; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-              if (c * 32 + i >= vis) sr[c][i] = 0xff800000u;        // -inf: exp2 gives exactly 0 below
+              if (col0 + c * 32 + i >= vis) sr[c][i] = 0xff800000u;  // -inf: exp2 gives exactly 0 below
         }
         // four independent chains (a single running max would serialise 128 dependent instructions)
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[c][i]));
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        float mx_other;
+        if (!exchange(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])), mx_other)) { ok = false; break; }
+        const float mx = fmaxf(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])), mx_other);    // the same in both halves
         // Lazy rescaling: the reference point m only moves when the row max grew by more than 2^8 (P stays below 256,
         // far inside f16 range), so the O accumulator in TMEM is rarely touched after the first tiles.
         float m_new = m, alpha = 1.f;
@@ -363,13 +400,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const TcAttnP
           tc_fence_after();
           if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
               uint32_t r[32];
-              tmem_ld_32x32b_x32(tO + t_lane + c * 32, r);
+              tmem_ld_32x32b_x32(tO + t_lane + col0 + c * 32, r);
               tmem_ld_wait();
 #pragma unroll
               for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-              tmem_st_32x32b_x32(tO + t_lane + c * 32, r);
+              tmem_st_32x32b_x32(tO + t_lane + col0 + c * 32, r);
             }
             tmem_st_wait();
           }
@@ -379,8 +416,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const TcAttnP
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
         const float mref = (m_new == -INFINITY) ? 0.f : m_new;       // dead rows: -inf - 0 stays -inf, p = 0
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint8_t* rowp = prow0 + (c >> 1) * kSub;
+        for (int c = 0; c < 2; ++c) {
+          uint8_t* rowp = prow0;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             float e[8];
@@ -391,7 +428,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const TcAttnP
             }
             uint4 o;
             o.x = pack_h2(e[0], e[1]); o.y = pack_h2(e[2], e[3]); o.z = pack_h2(e[4], e[5]); o.w = pack_h2(e[6], e[7]);
-            const int ch = (c & 1) * 4 + q;
+            const int ch = c * 4 + q;
             *reinterpret_cast<uint4*>(rowp + ((ch ^ sw) << 4)) = o;
           }
         }
@@ -403,32 +440,38 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const TcAttnP
         __syncwarp();
         if (lane == 0) mbar_arrive(p_ready);
       }
-      // ---- epilogue: O / l * v_scale -> bf16
+      // ---- epilogue: O / l * v_scale -> bf16, each thread its 64 columns; l is the sum of the two halves' row sums
+      float l_other = 0.f;
+      if (ok && n_kv > 0) ok = exchange(l, l_other);
+      l += l_other;
       if (ok && n_kv > 0 && mbar_wait(pv_done, (n_kv - 1) & 1, abort_flag, p.status, 0x832)) {
         tc_fence_after();
         const float inv = (l > 0.f) ? p.v_scale / l : 0.f;
         if (p.q_out != nullptr) {
           // the whole output row in registers (as the score rows were), rounded to bf16 like the unfused path's
           // output, then one scale for the row's 128 values
-          uint32_t r[4][32];
+          uint32_t r[2][32];
 #pragma unroll
-          for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(tO + t_lane + c * 32, r[c]);
+          for (int c = 0; c < 2; ++c) tmem_ld_32x32b_x32(tO + t_lane + col0 + c * 32, r[c]);
           tmem_ld_wait();
           float amax = 0.f;
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+          for (int c = 0; c < 2; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const float v = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[c][i]) * inv));
               r[c][i] = __float_as_uint(v);
               amax = fmaxf(amax, fabsf(v));
             }
-          if (row_live) {
+          float amax_other = 0.f;
+          const bool got = exchange(amax, amax_other);           // every thread takes part, live row or not
+          amax = fmaxf(amax, amax_other);
+          if (row_live && got) {
             const float sc = fmaxf(amax, 1e-10f) / 448.f;
             const float qinv = __frcp_rn(sc);
-            uint8_t* qrow = p.q_out + (long long)(q_row0 + tok) * p.ldqo + head * kTcD;
+            uint8_t* qrow = p.q_out + (long long)(q_row0 + tok) * p.ldqo + head * kTcD + col0;
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+            for (int c = 0; c < 2; ++c)
 #pragma unroll
               for (int q = 0; q < 2; ++q) {
                 uint32_t w[4];
@@ -441,14 +484,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const TcAttnP
                 }
                 *reinterpret_cast<uint4*>(qrow + c * 32 + q * 16) = make_uint4(w[0], w[1], w[2], w[3]);
               }
-            p.s_out[(long long)head * p.s_ld + q_row0 + tok] = sc;
+            if (half == 0) p.s_out[(long long)head * p.s_ld + q_row0 + tok] = sc;
           }
         } else {
-        __nv_bfloat16* orow = p.out + (long long)(q_row0 + tok) * p.ldo + head * kTcD;
+        __nv_bfloat16* orow = p.out + (long long)(q_row0 + tok) * p.ldo + head * kTcD + col0;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t r[32];
-          tmem_ld_32x32b_x32(tO + t_lane + c * 32, r);
+          tmem_ld_32x32b_x32(tO + t_lane + col0 + c * 32, r);
           tmem_ld_wait();
           if (row_live) {
 #pragma unroll

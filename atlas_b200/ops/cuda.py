@@ -551,18 +551,7 @@ def paged_attention(q, k_cache, v_cache, batch, scale, k_scale, v_scale, sliding
                "attn_decode")
     if batch.num_seqs > nd and _tc_prefill_ok(q, Hq, Hkv, D, bs, window, k_cache):
         # tensor-core (tcgen05) chunk attention: tiles of 128 / G query tokens, all G heads of a kv head per tile
-        tok = 128 // (Hq // Hkv)
-        tiles = getattr(batch, "_attn_tiles_tc", None)
-        if tiles is None or tiles[2] != tok:
-            ts, tq = [], []
-            for i in range(nd, batch.num_seqs):
-                for q0 in range(0, batch.query_lens_host[i], tok):
-                    ts.append(i)
-                    tq.append(q0)
-            host = torch.tensor([ts, tq], dtype=torch.int32).pin_memory()
-            tiles = (host.to(q.device, non_blocking=True), len(ts), tok)
-            batch._attn_tiles_tc = tiles
-        tdev, n_tiles, _ = tiles
+        tdev, n_tiles, _ = _tc_tiles(q, batch, nd, 128 // (Hq // Hkv))
         rc = lib().atlas_attn_prefill_tc(q.data_ptr(), q.stride(0), out.data_ptr(), Hq * D, k_cache.data_ptr(),
                                          v_cache.data_ptr(), bt.data_ptr(), bt.stride(0), batch.seq_lens.data_ptr(),
                                          batch.query_start_loc.data_ptr(), tdev[0].data_ptr(), tdev[1].data_ptr(), n_tiles,
@@ -647,11 +636,16 @@ def _tc_tiles(q, batch, nd: int, tok: int):
     """(device tensor [2, n] of (sequence, first chunk token) per query tile of ``tok`` tokens, n, tok), cached on the batch."""
     tiles = getattr(batch, "_attn_tiles_tc", None)
     if tiles is None or tiles[2] != tok:
-        ts, tq = [], []
+        work = []
         for i in range(nd, batch.num_seqs):
-            for q0 in range(0, batch.query_lens_host[i], tok):
-                ts.append(i)
-                tq.append(q0)
+            qlen = batch.query_lens_host[i]
+            ctx = batch.seq_lens_host[i] - qlen
+            for q0 in range(0, qlen, tok):
+                work.append((-(ctx + min(q0 + tok, qlen)), i, q0))        # keys the tile's last row sees
+        # tiles with the most keys first: a causal tile costs up to 8x another, and blocks are handed to SMs in index
+        # order, so the short ones fill the tail of the launch instead of the long ones making it
+        work.sort()
+        ts, tq = [w[1] for w in work], [w[2] for w in work]
         host = torch.tensor([ts, tq], dtype=torch.int32).pin_memory()
         tiles = (host.to(q.device, non_blocking=True), len(ts), tok)
         batch._attn_tiles_tc = tiles
