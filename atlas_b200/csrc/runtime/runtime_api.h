@@ -56,6 +56,13 @@ void atlas_fault_reset_for_tests(void);
 // aligned bounce buffers (falls back to buffered reads where O_DIRECT is refused).  Returns bytes read or -errno.
 long long atlas_read_file(const char* path, long long offset, long long len, void* dst, int threads, long long chunk);
 
+// ---- batched record I/O through io_uring (uring_io.cpp) ----------------------------------------------------------------
+// 1 when this kernel / sandbox lets the process create an io_uring.
+int atlas_uring_available(void);
+// n records of bytes_each at offsets[i] of fd <-> bufs[i] (write != 0: buffers to file), at most depth requests in
+// flight.  Returns n * bytes_each or -errno.
+long long atlas_uring_rw(int fd, int write, int n, const long long* offsets, void* const* bufs, long long bytes_each, int depth);
+
 // ---- grammar-constrained decoding (grammar.cpp) ------------------------------------------------------------------------
 typedef struct atlas_grammar atlas_grammar;
 typedef struct atlas_vocab atlas_vocab;

@@ -44,8 +44,31 @@ def lib():
         L.atlas_fault_reason.argtypes = [C.c_char_p, C.c_int]
         L.atlas_read_file.restype = C.c_longlong
         L.atlas_read_file.argtypes = [C.c_char_p, C.c_longlong, C.c_longlong, vp, C.c_int, C.c_longlong]
+        L.atlas_uring_rw.restype = C.c_longlong
+        L.atlas_uring_rw.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_longlong), C.POINTER(vp), C.c_longlong, C.c_int]
         _LIB = L
     return _LIB
+
+
+def uring_available() -> bool:
+    """True when the native runtime is built and this kernel / sandbox lets the process create an io_uring."""
+    try:
+        return bool(lib().atlas_uring_available())
+    except (OSError, AttributeError):
+        return False
+
+
+def uring_rw(fd: int, write: bool, offsets: Sequence[int], addresses: Sequence[int], bytes_each: int, depth: int = 64) -> int:
+    """``len(offsets)`` records of ``bytes_each`` between file offsets and host addresses, one batched submission."""
+    n = len(offsets)
+    if n == 0:
+        return 0
+    offs = (C.c_longlong * n)(*[int(o) for o in offsets])
+    bufs = (C.c_void_p * n)(*[int(a) for a in addresses])
+    r = lib().atlas_uring_rw(int(fd), 1 if write else 0, n, offs, bufs, int(bytes_each), int(depth))
+    if r < 0:
+        raise OSError(-r, os.strerror(-r))
+    return int(r)
 
 
 def _ints(xs: Sequence[int]):
