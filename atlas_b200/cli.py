@@ -31,6 +31,10 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--bind", default="0.0.0.0")
     s.add_argument("--max-seq-len", type=int, default=32768)
     s.add_argument("--block-size", type=int, default=16)
+    s.add_argument("--no-logit-pipeline", action="store_true",
+                   help="do not attach the think / tool-call logit stages (mid-word close defer, post-close masks, tool-call pin)")
+    s.add_argument("--think-confidence-streak", type=int, default=0,
+                   help="end thinking early after this many consecutive tokens with top-1 probability >= 0.95 (0 = off)")
     s.add_argument("--mtp-vocab", type=int, default=0, help="draft steps score this many rows of the lm_head (0 = all)")
     s.add_argument("--mtp-vocab-rank", default="id", help="'id' (first rows) or the path of a ranked token-id table")
     s.add_argument("--kv-cache-dtype", default="fp8", choices=["auto", "fp8", "bf16", "nvfp4", "turbo8"])
@@ -270,7 +274,8 @@ def cmd_serve(argv: List[str]) -> int:
     keys = list(args.api_key) + [k for k in os.environ.get("ATLAS_API_KEYS", "").split(",") if k]
     state = ServerState(aeng, tokenizer, args.served_model_name or os.path.basename(args.model.rstrip("/")) or args.model,
                         {"api_keys": keys if (keys or args.require_auth) else None, "rate_limit_rpm": args.rate_limit_rpm,
-                         "tool_call_parser": args.tool_call_parser, "disable_thinking": args.disable_thinking,
+                         "tool_call_parser": args.tool_call_parser, "no_logit_pipeline": args.no_logit_pipeline,
+                         "think_confidence_streak": args.think_confidence_streak, "disable_thinking": args.disable_thinking,
                          "max_thinking_budget": args.max_thinking_budget, "dump": args.dump, "profile": args.profile, "loop_guard": args.loop_guard, "no_output_sanitizer": args.no_output_sanitizer, "context_compaction": args.context_compaction,
                          "loop_guard_span": args.loop_guard_span,
                          "serve_plan": plan})

@@ -18,6 +18,7 @@ from typing import Any, AsyncIterator, Dict, List, Optional
 from ..sampling import SamplingParams
 from .grammar import GrammarSpec
 from .reasoning import ReasoningSplitter, ThinkingBudget
+from .logit_processors import ThinkToolPipeline, repeated_tool_call
 from .loop_detector import LoopDetector
 from .compaction import compact_messages
 from .sanitizer import ContentSanitizer, StreamGuards, guarded_stops
@@ -190,6 +191,14 @@ class Generator:
             budget = min(x for x in (req.thinking_budget, s.args.get("max_thinking_budget")) if x)
             close_ids = tk.encode("</think>")
             procs.append(ThinkingBudget(close_ids, int(budget)))
+        loop = bool(tools) and repeated_tool_call(req.messages)
+        if not s.args.get("no_logit_pipeline") and (thinking or (tools and (require_tool or loop))):
+            marker = next((m for m in get_parser(s.tool_parser_name, tools).markers if len(m) > 1), None) if tools else None
+            procs.append(ThinkToolPipeline(
+                think_open=tk.encode("<think>") if thinking else (), think_close=tk.encode("</think>") if thinking else (),
+                tool_open=tk.encode(marker) if marker else (), token_text=lambda t: tk.decode([t]),
+                starts_in_think=bool(thinking) and text.rstrip().endswith("<think>"), require_tool_call=bool(require_tool),
+                suppress_tool_call=loop, streak=int(s.args.get("think_confidence_streak") or 0)))
         ns = s.sessions.namespace(req.cache_key)
         return toks, sp, grammar, procs, ns, thinking, tools, text
 
