@@ -205,7 +205,7 @@ def test_rope_kv_write_prefill_pages(K):
     assert float((vc.float() - vc_r.float()).abs().max()) < 0.6        # no misplaced rows (values are O(1))
 
 
-def _attention_case(K, D, Hq, Hkv, qlens, ctxs, bs=16, window=None, seed=6, kv_dtype=torch.float8_e4m3fn):
+def _attention_case(K, D, Hq, Hkv, qlens, ctxs, bs=16, window=None, seed=6, kv_dtype=torch.float8_e4m3fn, oracle_bug=None):
     from atlas_b200.models.batch import ForwardBatch
     torch.manual_seed(seed)
     B = len(qlens)
@@ -230,7 +230,14 @@ def _attention_case(K, D, Hq, Hkv, qlens, ctxs, bs=16, window=None, seed=6, kv_d
     scale = D ** -0.5
     ks, vs = (0.7, 1.3) if kv_dtype == torch.float8_e4m3fn else (1.0, 1.0)      # a 16-bit cache stores unscaled values
     out = K.paged_attention(q, kc, vc, fb, scale, ks, vs, window)
-    want = ref.paged_attention(q, kc, vc, fb.block_tables, fb.seq_lens, fb.query_start_loc, scale, ks, vs, window)
+    if oracle_bug == "mask":              # every row also sees the key after its own position (one more cached token)
+        want = ref.paged_attention(q, kc, vc, fb.block_tables, fb.seq_lens + 1, fb.query_start_loc, scale, ks, vs, window)
+    elif oracle_bug == "v_scale":
+        want = ref.paged_attention(q, kc, vc, fb.block_tables, fb.seq_lens, fb.query_start_loc, scale, ks, 1.0, window)
+    elif oracle_bug == "scale":
+        want = ref.paged_attention(q, kc, vc, fb.block_tables, fb.seq_lens, fb.query_start_loc, 64 ** -0.5, ks, vs, window)
+    else:
+        want = ref.paged_attention(q, kc, vc, fb.block_tables, fb.seq_lens, fb.query_start_loc, scale, ks, vs, window)
     _status_ok(K)
     return out, want
 
@@ -669,3 +676,29 @@ def test_rotated_kv_write_and_head_rotation(K, T):
     _status_ok(K)
     assert _rel_rms(y, ref.head_rotate(x)) < 5e-3
     assert _rel_rms(K.wht_d128(y.clone()), x) < 8e-3       # an involution up to bf16 rounding
+
+
+def test_oracle_bounds_reject_plausibly_wrong_kernels(K):
+    """The bounds the numerics tests use must be able to fail: each case compares a CORRECT kernel result with an oracle
+    that carries one realistic kernel bug (a weight-scale block skipped, the causal mask off by one key, the value scale
+    dropped, the softmax scale of another head size) and must land outside the bound the real test applies."""
+    torch.manual_seed(3)
+    # FP8 block-scaled GEMM: one 128-wide K block of one 128-row weight block uses a neighbour's scale
+    M, N, K_ = 256, 512, 1024
+    x = torch.randn(M, K_, device=DEV).bfloat16()
+    wq, ws = Q.quantize_fp8_block(torch.randn(N, K_, device=DEV) * 0.05 * (1 + torch.arange(K_, device=DEV) // 128))
+    xq, xs = K.quant_fp8(x)
+    out = K.gemm_fp8_block(xq, xs, wq, ws)
+    _status_ok(K)
+    good = Q.fp8_block_gemm_ref(xq, xs.contiguous(), wq, ws, out_dtype=torch.float32)
+    bad_ws = ws.clone()
+    bad_ws[1, 3] = ws[1, 2]
+    bad = Q.fp8_block_gemm_ref(xq, xs.contiguous(), wq, bad_ws, out_dtype=torch.float32)
+    assert _rel_rms(out, good) < 5e-3 < _rel_rms(out, bad)
+    # paged attention (decode rows and a prefill chunk): mask off by one key / value scale dropped / wrong softmax scale
+    D, Hq, Hkv = 128, 8, 2
+    out, want = _attention_case(K, D, Hq, Hkv, qlens=[1, 1, 40, 130], ctxs=[33, 700, 0, 77])
+    assert _rel_rms(out, want) < 2e-2
+    for mutate in ("mask", "v_scale", "scale"):
+        wrong = _attention_case(K, D, Hq, Hkv, qlens=[1, 1, 40, 130], ctxs=[33, 700, 0, 77], oracle_bug=mutate)[1]
+        assert _rel_rms(out, wrong) > 2e-2, mutate
