@@ -118,6 +118,8 @@ def build_parser() -> argparse.ArgumentParser:
 
     r = sub.add_parser("recipes", help="list built-in recipes or print the argv of one")
     r.add_argument("recipe", nargs="?")
+    r.add_argument("--sync", metavar="INDEX_URL", help="fetch the recipes an index lists (https:// or file://) into the local recipe directory")
+    r.add_argument("--dest", default=None, help="directory for --sync (default: $ATLAS_RECIPES_DIR or ~/.cache/atlas_b200/recipes)")
     return ap
 
 
@@ -372,6 +374,10 @@ def cmd_benchmark(argv: List[str]) -> int:
 def cmd_recipes(argv: List[str]) -> int:
     from . import recipes
     args = build_parser().parse_args(["recipes"] + argv)
+    if args.sync:
+        for rid in recipes.sync(args.sync, args.dest):
+            print(rid)
+        return 0
     if not args.recipe:
         for rid, d in sorted(recipes.BUILTIN.items()):
             print(f"{rid:36s} ranks>={d.get('min_ranks', 1)}  {d.get('description', '')}")

@@ -5,7 +5,8 @@ Precedence when serving: built-in flag defaults < recipe ``defaults`` < explicit
 exported only when the variable is not already set by the operator.
 
 Reference parity: ``crates/spark-server/src/recipe/{mod,schema,yaml}.rs`` (recipe struct, key -> flag mapping,
-``min_nodes`` outside ``defaults``).  Fetching recipes from a remote index is not offered (hermetic deployments only).
+``min_nodes`` outside ``defaults``) and ``recipe/sync.rs`` (``sync``: an index of recipe files with checksums, fetched
+into a local directory that ``resolve`` searches; ``file://`` indexes serve hermetic deployments).
 """
 from __future__ import annotations
 
@@ -28,6 +29,9 @@ SCHEMA: Dict[str, tuple] = {
     "tool_call_parser": ("--tool-call-parser", "value"), "disable_thinking": ("--disable-thinking", "switch"),
     "max_thinking_budget": ("--max-thinking-budget", "value"), "request_timeout": ("--request-timeout", "value"),
     "quantization": ("--quantization", "value"), "comm": ("--comm", "value"), "no_cuda_graphs": ("--no-cuda-graphs", "switch"),
+    "self_speculative": ("--self-speculative", "switch"), "self_spec_keep": ("--self-spec-keep", "value"),
+    "mtp_vocab": ("--mtp-vocab", "value"), "mtp_vocab_rank": ("--mtp-vocab-rank", "value"),
+    "think_confidence_streak": ("--think-confidence-streak", "value"),
 }
 
 ENV_PREFIX = "ATLAS_"
@@ -137,6 +141,60 @@ def builtin(rid: str) -> Recipe:
     return from_dict(BUILTIN[rid], rid)
 
 
+def synced_dir() -> str:
+    return os.environ.get("ATLAS_RECIPES_DIR") or os.path.join(os.path.expanduser("~"), ".cache", "atlas_b200", "recipes")
+
+
 def resolve(spec: str) -> Recipe:
-    """A path to a YAML file or the id of a built-in recipe."""
-    return load(spec) if os.path.exists(spec) else builtin(spec)
+    """A path to a YAML file, the id of a synced recipe (``family/name`` under ``synced_dir()``), or a built-in id."""
+    if os.path.exists(spec):
+        return load(spec)
+    local = os.path.join(synced_dir(), spec + ".yaml")
+    if ".." not in spec.split("/") and os.path.exists(local):
+        return load(local)
+    return builtin(spec)
+
+
+def sync(index_url: str, dest: Optional[str] = None, timeout_s: float = 30.0) -> List[str]:
+    """Fetch a recipe index and the recipes it lists into ``dest`` (default ``synced_dir()``); returns the ids written.
+
+    The index is JSON: ``{"recipes": [{"id": "family/name", "url": "...", "sha256": "..."}]}``; relative urls are taken
+    against the index's own location, ``file://`` works like ``https://``.  A file is written only after its checksum
+    matched and it parsed as a valid recipe, under a temporary name that is renamed into place, so a failed sync leaves
+    the previous copy of every recipe untouched."""
+    import hashlib
+    import json
+    import urllib.parse
+    import urllib.request
+    dest = dest or synced_dir()
+
+    def fetch(url: str) -> bytes:
+        with urllib.request.urlopen(url, timeout=timeout_s) as r:
+            return r.read()
+    index = json.loads(fetch(index_url).decode())
+    entries = index.get("recipes") if isinstance(index, dict) else index
+    if not isinstance(entries, list):
+        raise RecipeError("the recipe index lists no recipes")
+    staged = []
+    for e in entries:
+        rid = str(e.get("id", ""))
+        parts = rid.split("/")
+        if len(parts) != 2 or not all(p and p not in (".", "..") and os.sep not in p for p in parts):
+            raise RecipeError(f"bad recipe id in the index: '{rid}'")
+        data = fetch(urllib.parse.urljoin(index_url, str(e["url"])))
+        digest = hashlib.sha256(data).hexdigest()
+        if e.get("sha256") and digest != str(e["sha256"]).lower():
+            raise RecipeError(f"{rid}: checksum mismatch (index {e['sha256']}, file {digest})")
+        import yaml
+        from_dict(yaml.safe_load(data.decode()), rid)        # raises on an invalid recipe
+        staged.append((rid, data))
+    written = []
+    for rid, data in staged:
+        path = os.path.join(dest, rid + ".yaml")
+        os.makedirs(os.path.dirname(path), exist_ok=True)
+        tmp = path + ".part"
+        with open(tmp, "wb") as f:
+            f.write(data)
+        os.replace(tmp, path)
+        written.append(rid)
+    return written

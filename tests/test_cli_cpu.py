@@ -117,3 +117,37 @@ def test_serve_two_ranks_gloo():
         assert procs[1].poll() is None
     finally:
         _stop(procs)
+
+
+def test_recipe_sync_from_an_index(tmp_path, monkeypatch, capsys):
+    """``recipes --sync``: an index with checksums, fetched over file://; a synced recipe resolves by id; a checksum
+    mismatch or an invalid recipe writes nothing (the earlier copy stays)."""
+    import hashlib
+    import json
+    src, dest = tmp_path / "remote", tmp_path / "local"
+    (src / "fam").mkdir(parents=True)
+    good = b"model: preset:llama3-8b\ndescription: synced\ndefaults:\n  max_num_seqs: 32\n  mtp_vocab: 4096\n"
+    (src / "fam" / "a.yaml").write_bytes(good)
+    index = {"recipes": [{"id": "fam/a", "url": "fam/a.yaml", "sha256": hashlib.sha256(good).hexdigest()}]}
+    (src / "index.json").write_text(json.dumps(index))
+    url = (src / "index.json").as_uri()
+    assert cli.main(["recipes", "--sync", url, "--dest", str(dest)]) == 0
+    assert capsys.readouterr().out.strip() == "fam/a"
+    monkeypatch.setenv("ATLAS_RECIPES_DIR", str(dest))
+    r = recipes.resolve("fam/a")
+    assert r.description == "synced" and "--mtp-vocab" in r.argv() and "32" in r.argv()
+    # a tampered file: nothing is replaced
+    (src / "fam" / "a.yaml").write_bytes(good.replace(b"32", b"64"))
+    with pytest.raises(recipes.RecipeError, match="checksum"):
+        recipes.sync(url, str(dest))
+    assert "32" in recipes.resolve("fam/a").argv()
+    # an invalid recipe (unknown key) and a path-escaping id are refused before anything is written
+    bad = b"model: m\ndefaults:\n  bogus: 1\n"
+    (src / "fam" / "b.yaml").write_bytes(bad)
+    (src / "index.json").write_text(json.dumps({"recipes": [{"id": "fam/b", "url": "fam/b.yaml"}]}))
+    with pytest.raises(recipes.RecipeError):
+        recipes.sync(url, str(dest))
+    assert not (dest / "fam" / "b.yaml").exists()
+    (src / "index.json").write_text(json.dumps({"recipes": [{"id": "../x", "url": "fam/a.yaml"}]}))
+    with pytest.raises(recipes.RecipeError, match="bad recipe id"):
+        recipes.sync(url, str(dest))
