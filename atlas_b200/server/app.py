@@ -174,7 +174,7 @@ def create_app(state: ServerState) -> FastAPI:
                        logprobs=bool(body.get("logprobs")) and not isinstance(body.get("logprobs"), int) or body.get("logprobs") is True,
                        top_logprobs=int(body.get("top_logprobs") or 0), timeout_s=float(to) if to else S.args.get("request_timeout"),
                        cache_key=body.get("prompt_cache_key") or body.get("user"), adapter=body.get("adapter"),
-                       disable_spec=(body.get("atlas_speculative") is False))
+                       disable_spec=(body.get("atlas_speculative") is False), confidence=bool(body.get("atlas_confidence")))
         for k, v in over.items():
             setattr(r, k, v)
         return r
@@ -263,6 +263,10 @@ def create_app(state: ServerState) -> FastAPI:
                   "logprobs": lp_openai(o.logprobs) if r.logprobs else None}
             if want_ids:
                 ch["token_ids"] = o.token_ids
+            if r.confidence:
+                from .confidence import confidence_summary
+                ch["atlas_confidence"] = confidence_summary(o.logprobs)
+                S.metrics.on_confidence(ch["atlas_confidence"])
             choices.append(ch)
             u = o.usage or {}
             usage["prompt_tokens"] = u.get("prompt_tokens", 0)

@@ -43,6 +43,7 @@ class GenRequest:
     echo: bool = False
     logprobs: bool = False
     top_logprobs: int = 0
+    confidence: bool = False             # attach the confidence summary of the first tokens (server/confidence.py)
     timeout_s: Optional[float] = None
     cache_key: Optional[str] = None
     adapter: Optional[str] = None
@@ -157,6 +158,10 @@ class Generator:
         sp = sampling_from_fields(req.sampling, presets, max_default=s.args.get("default_max_tokens", 1024))
         if req.logprobs:
             sp.logprobs, sp.top_logprobs = True, max(sp.top_logprobs, req.top_logprobs)
+        if req.confidence or s.args.get("conf_summary"):
+            from .confidence import INTERNAL_TOP
+            req.confidence = True
+            sp.logprobs, sp.top_logprobs = True, max(sp.top_logprobs, INTERNAL_TOP)     # returned only if the client asked
         room = s.engine.engine.cfg.max_seq_len - len(toks)
         if room <= 0:
             raise BadRequest(f"prompt has {len(toks)} tokens; the context window is {s.engine.engine.cfg.max_seq_len}", "messages",

@@ -36,6 +36,18 @@ class ServerMetrics:
         self.spec_proposed = Gauge("atlas_spec_proposed_tokens_total", "Draft tokens proposed", registry=r)
         self.spec_accepted = Gauge("atlas_spec_accepted_tokens_total", "Draft tokens accepted", registry=r)
         self.gpu_fault = Gauge("atlas_gpu_fault", "1 once the GPU context is lost", registry=r)
+        self.conf_mean_top1 = Histogram("atlas_confidence_mean_top1", "Mean top-1 probability over a request's first tokens",
+                                        registry=r, buckets=(.1, .2, .3, .4, .5, .6, .7, .8, .9, .95, 1.0))
+        self.conf_min_margin = Histogram("atlas_confidence_min_margin", "Smallest top-1 / top-2 probability gap of a request",
+                                         registry=r, buckets=(.01, .02, .05, .1, .2, .3, .5, .7, 1.0))
+        self.conf_low_frac = Histogram("atlas_confidence_low_fraction", "Fraction of a request's first tokens with top-1 < 0.5",
+                                       registry=r, buckets=(0, .05, .1, .2, .3, .5, .7, 1.0))
+
+    def on_confidence(self, summary) -> None:
+        if summary:
+            self.conf_mean_top1.observe(summary["mean_top1"])
+            self.conf_min_margin.observe(summary["min_margin"])
+            self.conf_low_frac.observe(summary["low_frac"])
 
     def on_http(self, path: str, status: int, seconds: float, bytes_in: int) -> None:
         p = path if len(path) < 48 else path[:48]

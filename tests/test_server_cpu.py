@@ -308,3 +308,26 @@ def test_lora_control_routes_load_an_adapter_and_requests_use_it(tmp_path):
         assert c.post("/v1/completions", json=body).json()["choices"][0]["text"] == with_ad
     finally:
         aeng.shutdown(drain=False)
+
+
+def test_confidence_summary_extension(ctx):
+    """``atlas_confidence``: the three figures over the first tokens, computed from internally requested top-2
+    log-probabilities that are not returned unless the client asked for them; the figures feed ``/metrics``."""
+    from atlas_b200.server.confidence import confidence_summary
+    import math
+    ents = [{"logprob": math.log(0.9), "top": [(1, math.log(0.9)), (2, math.log(0.05))]},
+            {"logprob": math.log(0.4), "top": [(3, math.log(0.4)), (4, math.log(0.35))]}]
+    s = confidence_summary(ents)
+    assert s["tokens"] == 2 and abs(s["mean_top1"] - 0.65) < 1e-9 and abs(s["min_margin"] - 0.05) < 1e-9 and s["low_frac"] == 0.5
+    assert confidence_summary(ents, k=1)["low_frac"] == 0.0 and confidence_summary(None) is None
+    c, state = ctx
+    body = {"model": "tiny", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 6, "temperature": 0}
+    plain = c.post("/v1/chat/completions", json=body).json()["choices"][0]
+    assert "atlas_confidence" not in plain
+    r = c.post("/v1/chat/completions", json=dict(body, atlas_confidence=True)).json()["choices"][0]
+    conf = r["atlas_confidence"]
+    assert conf["tokens"] == 6 and 0 < conf["mean_top1"] <= 1 and 0 <= conf["min_margin"] <= 1 and 0 <= conf["low_frac"] <= 1
+    assert r["logprobs"] is None and r["message"]["content"] == plain["message"]["content"]
+    both = c.post("/v1/chat/completions", json=dict(body, atlas_confidence=True, logprobs=True, top_logprobs=3)).json()["choices"][0]
+    assert len(both["logprobs"]["content"]) == 6 and both["atlas_confidence"]["tokens"] == 6
+    assert "atlas_confidence_mean_top1_count 2.0" in c.get("/metrics").text
