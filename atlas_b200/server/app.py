@@ -20,6 +20,7 @@ from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
 from ..utils.fault import FAULT_LATCH
 from .engine_async import AsyncEngine
+from .evidence import ChoiceEvidence, combine
 from .generation import BadRequest, GenDelta, Generator, GenRequest, collect
 from .grammar import GrammarEngine
 from .metrics import ServerMetrics
@@ -213,13 +214,19 @@ def create_app(state: ServerState) -> FastAPI:
                 r.sampling["seed"] = int(body["seed"]) + i
         for r in reqs:
             S.gen.prepare(r)       # validate before any bytes are sent
+        want_evidence = bool(body.get("atlas_evidence"))
+        stop_ids = S.engine.engine.mcfg.eos_ids() if want_evidence else ()
         if body.get("stream"):
             async def sse() -> AsyncIterator[bytes]:
                 base = {"id": cid, "object": "chat.completion.chunk", "created": created, "model": model}
                 usage_tot: Dict[str, Any] = {}
+                ev_tok, ev_out = [], []
                 for idx, r in enumerate(reqs):
                     yield _sse({**base, "choices": [{"index": idx, "delta": {"role": "assistant", "content": ""}, "finish_reason": None}]})
+                    ev, fin = ChoiceEvidence(stop_ids), ""
                     async for d in S.gen.stream(r):
+                        ev.add(d.token_ids, d.content, d.reasoning)
+                        fin = d.finish_reason or fin
                         if d.error:
                             yield _sse({"error": {"message": d.error, "type": "server_error"}})
                             break
@@ -243,7 +250,11 @@ def create_app(state: ServerState) -> FastAPI:
                                     usage_tot[k] = usage_tot.get(k, 0) + v if k != "prompt_tokens" else v
                                 else:
                                     usage_tot[k] = v
-                if include_usage:
+                    ev_tok.append(ev.token_digest(fin))
+                    ev_out.append(ev.output_digest())
+                if want_evidence:
+                    usage_tot["atlas_token_sha"], usage_tot["atlas_output_sha256"] = combine(ev_tok), combine(ev_out)
+                if include_usage or want_evidence:
                     usage_tot["total_tokens"] = usage_tot.get("prompt_tokens", 0) + usage_tot.get("completion_tokens", 0)
                     yield _sse({**base, "choices": [], "usage": usage_tot})
                 yield b"data: [DONE]\n\n"
@@ -251,9 +262,15 @@ def create_app(state: ServerState) -> FastAPI:
         outs = await asyncio.gather(*[collect(S.gen.stream(r)) for r in reqs])
         choices = []
         usage = {"prompt_tokens": 0, "completion_tokens": 0}
+        ev_tok, ev_out = [], []
         for idx, (r, o) in enumerate(zip(reqs, outs)):
             if o.error:
                 return _err(500, o.error, "server_error")
+            if want_evidence:
+                ev = ChoiceEvidence(stop_ids)
+                ev.add(o.token_ids, o.content, o.reasoning)
+                ev_tok.append(ev.token_digest(o.finish_reason or ""))
+                ev_out.append(ev.output_digest())
             msg: Dict[str, Any] = {"role": "assistant", "content": o.content if (o.content or not o.tool_calls) else None}
             if o.reasoning:
                 msg["reasoning_content"] = o.reasoning
@@ -266,6 +283,7 @@ def create_app(state: ServerState) -> FastAPI:
             if r.confidence:
                 from .confidence import confidence_summary
                 ch["atlas_confidence"] = confidence_summary(o.logprobs)
+                usage.setdefault("atlas_confidence", ch["atlas_confidence"])        # the first choice's, as in `usage`
                 S.metrics.on_confidence(ch["atlas_confidence"])
             choices.append(ch)
             u = o.usage or {}
@@ -275,6 +293,8 @@ def create_app(state: ServerState) -> FastAPI:
                 if k in u:
                     usage[k] = u[k]
         usage["total_tokens"] = usage["prompt_tokens"] + usage["completion_tokens"]
+        if want_evidence:
+            usage["atlas_token_sha"], usage["atlas_output_sha256"] = combine(ev_tok), combine(ev_out)
         resp = {"id": cid, "object": "chat.completion", "created": created, "model": model, "choices": choices,
                 "usage": usage, "system_fingerprint": "atlas-b200"}
         if body.get("store"):

@@ -331,3 +331,37 @@ def test_confidence_summary_extension(ctx):
     both = c.post("/v1/chat/completions", json=dict(body, atlas_confidence=True, logprobs=True, top_logprobs=3)).json()["choices"][0]
     assert len(both["logprobs"]["content"]) == 6 and both["atlas_confidence"]["tokens"] == 6
     assert "atlas_confidence_mean_top1_count 2.0" in c.get("/metrics").text
+
+
+def test_evidence_fingerprints_blocking_and_streaming(ctx):
+    """``atlas_evidence``: the token and output fingerprints follow their definition, are equal for two identical greedy
+    requests (blocking and streamed alike, whatever the chunking), differ for another prompt, and combine over choices."""
+    import hashlib
+    import struct
+    from atlas_b200.server.evidence import ChoiceEvidence, combine
+    c, state = ctx
+    body = {"model": "tiny", "messages": [{"role": "user", "content": "fingerprint me"}], "max_tokens": 8, "temperature": 0,
+            "atlas_evidence": True, "return_token_ids": True}
+    a = c.post("/v1/chat/completions", json=body).json()
+    b = c.post("/v1/chat/completions", json=body).json()
+    ua, ub = a["usage"], b["usage"]
+    assert ua["atlas_token_sha"] == ub["atlas_token_sha"] and ua["atlas_output_sha256"] == ub["atlas_output_sha256"]
+    content = a["choices"][0]["message"]["content"] or ""
+    want_out = hashlib.sha256(hashlib.sha256(content.encode()).digest() + hashlib.sha256(b"").digest()).hexdigest()
+    assert ua["atlas_output_sha256"] == want_out
+    other = c.post("/v1/chat/completions", json=dict(body, messages=[{"role": "user", "content": "something else"}])).json()
+    assert other["usage"]["atlas_token_sha"] != ua["atlas_token_sha"]
+    assert "atlas_token_sha" not in c.post("/v1/chat/completions", json={k: v for k, v in body.items() if k != "atlas_evidence"}).json()["usage"]
+    with c.stream("POST", "/v1/chat/completions", json=dict(body, stream=True)) as r:
+        chunks = _sse(r)
+    us = [ch["usage"] for ch in chunks if ch.get("usage")][-1]
+    assert us["atlas_token_sha"] == ua["atlas_token_sha"] and us["atlas_output_sha256"] == ua["atlas_output_sha256"]
+    # the definition itself: stop token dropped only on a "stop" finish, several choices hash their digests
+    ev = ChoiceEvidence(stop_ids=[2])
+    ev.add([5, 6], "ab")
+    ev.add([2], "c", "why")
+    assert ev.token_digest("stop") == hashlib.sha256(struct.pack("<2I", 5, 6)).digest()
+    assert ev.token_digest("length") == hashlib.sha256(struct.pack("<3I", 5, 6, 2)).digest()
+    assert ev.output_digest() == hashlib.sha256(hashlib.sha256(b"abc").digest() + hashlib.sha256(b"why").digest()).digest()
+    d1, d2 = ev.token_digest("stop"), ev.token_digest("length")
+    assert combine([d1]) == d1.hex() and combine([d1, d2]) == hashlib.sha256(d1 + d2).hexdigest()
