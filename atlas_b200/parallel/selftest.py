@@ -360,6 +360,41 @@ def main() -> int:
         # first token of every sequence (straight from the prefill) agrees and most sequences agree in full.
         report("engine tp nccl vs p2p", first == len(prompts) and same >= 3 and K.check_status() == 0, identical=same,
                first_token_identical=first, of=len(prompts), fused_calls=symm.calls["gemm_allreduce"], seq_parallel_gemms=sp_calls)
+        # LoRA on tensor-parallel ranks: every rank cuts the same (seeded) adapter like its shard of the base weights and
+        # adds the row-parallel partial deltas before the reduction; logits of a batch with one adapter sequence and one
+        # base sequence against the same model and adapter unsharded on this rank's GPU.
+        from atlas_b200.lora import LoraAdapter
+        from atlas_b200.models import ForwardBatch
+        lcfg = ModelConfig(model_type="llama", family="dense", vocab_size=2048, hidden_size=1024, intermediate_size=2048,
+                           num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=8, head_dim=128, rope_theta=5e5,
+                           max_position_embeddings=2048, quant=QuantConfig(method="none"))
+        ga = torch.Generator().manual_seed(21)
+        ad = LoraAdapter("ad", 8, 16.0)
+
+        def pair(out, inp):
+            return ((torch.randn(8, inp, generator=ga) * 0.05).bfloat16().to(device), (torch.randn(out, 8, generator=ga) * 0.05).bfloat16().to(device))
+        for l in range(lcfg.num_hidden_layers):
+            for mod, (o_, i_) in {"self_attn.q_proj": (lcfg.q_size, 1024), "self_attn.k_proj": (lcfg.kv_size, 1024),
+                                  "self_attn.o_proj": (1024, lcfg.q_size), "mlp.up_proj": (2048, 1024),
+                                  "mlp.down_proj": (1024, 2048)}.items():
+                ad.weights[f"layers.{l}.{mod}"] = pair(o_, i_)
+        toks = [torch.randint(0, 2048, (24,), generator=ga).tolist() for _ in range(2)]
+        logits = {}
+        for name, pc in (("one", ParallelCtx()), ("tp", ParallelCtx(topo.tp_rank, topo.tp_size, 0, 1, symm, None))):
+            m = build_model(lcfg, pc, device=device).init_random(0)
+            m.register_adapter(ad)
+            cache = m.alloc_cache(8, 16, torch.bfloat16, state_slots=1)
+            fb = ForwardBatch.build(toks, [0, 0], [[0, 1], [2, 3]], 16, device=device, all_logits=True)
+            fb.adapter_rows = torch.tensor([1] * 24 + [0] * 24, device=device)
+            logits[name] = m.compute_logits(m.forward(fb, cache)).float()
+            if name == "one":
+                fb0 = ForwardBatch.build(toks, [0, 0], [[4, 5], [6, 7]], 16, device=device, all_logits=True)
+                fb0.adapter_rows = torch.zeros(48, dtype=torch.long, device=device)
+                logits["base"] = m.compute_logits(m.forward(fb0, cache)).float()
+        torch.cuda.synchronize()
+        rel = float((logits["tp"] - logits["one"]).pow(2).mean().sqrt() / logits["one"].pow(2).mean().sqrt())
+        moved = float((logits["one"][:24] - logits["base"][:24]).pow(2).mean().sqrt() / logits["base"][:24].pow(2).mean().sqrt())
+        report("lora on tensor-parallel ranks", rel < 2e-2 and moved > 5e-2 and K.check_status() == 0, rel=rel, adapter_effect=moved)
     dist.barrier()
     symm.close()
     dist.destroy_process_group()
