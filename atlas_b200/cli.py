@@ -33,6 +33,8 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--block-size", type=int, default=16)
     s.add_argument("--no-logit-pipeline", action="store_true",
                    help="do not attach the think / tool-call logit stages (mid-word close defer, post-close masks, tool-call pin)")
+    s.add_argument("--margin-counter", action="store_true",
+                   help="count decode positions with a small top-1 / top-2 gap (one device read-back per token of the requests it covers)")
     s.add_argument("--think-confidence-streak", type=int, default=0,
                    help="end thinking early after this many consecutive tokens with top-1 probability >= 0.95 (0 = off)")
     s.add_argument("--mtp-vocab", type=int, default=0, help="draft steps score this many rows of the lm_head (0 = all)")
@@ -277,7 +279,7 @@ def cmd_serve(argv: List[str]) -> int:
     state = ServerState(aeng, tokenizer, args.served_model_name or os.path.basename(args.model.rstrip("/")) or args.model,
                         {"api_keys": keys if (keys or args.require_auth) else None, "rate_limit_rpm": args.rate_limit_rpm,
                          "tool_call_parser": args.tool_call_parser, "no_logit_pipeline": args.no_logit_pipeline,
-                         "think_confidence_streak": args.think_confidence_streak, "disable_thinking": args.disable_thinking,
+                         "think_confidence_streak": args.think_confidence_streak, "margin_counter": args.margin_counter, "disable_thinking": args.disable_thinking,
                          "max_thinking_budget": args.max_thinking_budget, "dump": args.dump, "profile": args.profile, "loop_guard": args.loop_guard, "no_output_sanitizer": args.no_output_sanitizer, "context_compaction": args.context_compaction,
                          "loop_guard_span": args.loop_guard_span,
                          "serve_plan": plan})

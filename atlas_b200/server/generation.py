@@ -203,7 +203,8 @@ class Generator:
                 think_open=tk.encode("<think>") if thinking else (), think_close=tk.encode("</think>") if thinking else (),
                 tool_open=tk.encode(marker) if marker else (), token_text=lambda t: tk.decode([t]),
                 starts_in_think=bool(thinking) and text.rstrip().endswith("<think>"), require_tool_call=bool(require_tool),
-                suppress_tool_call=loop, streak=int(s.args.get("think_confidence_streak") or 0)))
+                suppress_tool_call=loop, streak=int(s.args.get("think_confidence_streak") or 0),
+                margin=bool(s.args.get("margin_counter")), guard_pinned=bool(procs)))
         ns = s.sessions.namespace(req.cache_key)
         return toks, sp, grammar, procs, ns, thinking, tools, text
 

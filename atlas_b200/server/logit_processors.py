@@ -15,7 +15,7 @@ order; each is a no-op when the token ids it needs are unknown (fail-open):
                     evidence can still win.
 6. ``pin_tool``     right after the close tag, when the request requires a tool call and none is open yet, the
                     tool-call opener is the only admissible continuation (token by token for multi-token openers).
-7. ``margin``       observability only: counts positions whose top-1 / top-2 log-probability gap is below
+7. ``margin``       (opt-in) observability only: counts positions whose top-1 / top-2 log-probability gap is below
                     ``low_margin`` (the regime where FP8 rounding can flip a greedy pick); never changes the logits.
 
 Masks apply to single-token tags only (the special tokens of real tokenizers); a tag that takes several ordinary
@@ -56,7 +56,8 @@ class ThinkToolPipeline:
     def __init__(self, think_open: Sequence[int] = (), think_close: Sequence[int] = (), tool_open: Sequence[int] = (),
                  token_text: Optional[Callable[[int], str]] = None, starts_in_think: bool = False,
                  require_tool_call: bool = False, suppress_tool_call: bool = False, tool_loop_bias: float = -12.0,
-                 min_think_tokens: int = 400, conf_p: float = 0.95, streak: int = 0, low_margin: float = 1.5):
+                 min_think_tokens: int = 400, conf_p: float = 0.95, streak: int = 0, low_margin: float = 1.5,
+                 margin: bool = False, guard_pinned: bool = False):
         self.open, self.close, self.tool = list(think_open), list(think_close), list(tool_open)
         self.token_text = token_text
         self.in_think = bool(starts_in_think)
@@ -68,6 +69,9 @@ class ThinkToolPipeline:
         self.tool_loop_bias = float(tool_loop_bias)
         self.min_think_tokens, self.conf_p, self.streak = int(min_think_tokens), float(conf_p), int(streak)
         self.low_margin = float(low_margin)
+        # the two stages below read a value back from the row (a device synchronisation per token on a GPU), so they are
+        # on only when asked for: the margin counter, and the check for a position another processor already pinned
+        self.margin, self.guard_pinned = bool(margin), bool(guard_pinned)
         self.stats = PipelineStats()
         self._seen = 0                       # output tokens already folded into the state
         self._think_tokens = 0
@@ -115,7 +119,7 @@ class ThinkToolPipeline:
         # a forced tag in progress owns the position
         if self._forcing:
             return self._force(row, self._forcing.pop(0))
-        if int(torch.isfinite(row).sum()) <= 1:
+        if self.guard_pinned and int(torch.isfinite(row).sum()) <= 1:
             return row                       # an earlier processor already pinned this position (e.g. the think budget)
         single_close = len(self.close) == 1
         # 1. confidence streak (reads only)
@@ -162,7 +166,7 @@ class ThinkToolPipeline:
             return self._force(row, self.tool[0])
         self._pin_pending = self._pin_pending and self.think_just_ended
         # 7. top-1 / top-2 margin (reads only)
-        if row.numel() >= 2:
+        if self.margin and row.numel() >= 2:
             top2 = torch.topk(row.float(), 2).values
             if top2[1] > NEG_INF:
                 gap = float(top2[0] - top2[1])             # a difference of logits is a difference of log-probabilities

@@ -94,7 +94,7 @@ def test_confident_streak_ends_thinking_at_a_word_boundary():
 
 
 def test_margin_counter_reads_only_and_a_pinned_row_is_left_alone():
-    p = _pipe()
+    p = _pipe(margin=True)
     a = _row(t1=3.0, t3=2.5)
     before = a.clone()
     p(a, _Seq([2]))
@@ -103,7 +103,7 @@ def test_margin_counter_reads_only_and_a_pinned_row_is_left_alone():
     assert p.stats.low_margin == 1 and p.stats.positions == 2
     pinned = torch.full((100,), float("-inf"))
     pinned[CLOSE] = 0.0
-    q = _pipe(starts_in_think=True)
+    q = _pipe(starts_in_think=True, guard_pinned=True)
     out = q(pinned.clone(), _Seq([1]))                       # mid-word, but another processor forced the close tag
     assert torch.equal(out, pinned)
 
