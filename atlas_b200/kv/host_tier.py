@@ -77,18 +77,24 @@ class DiskKVTier:
     def write_many(self, recs: List[int], rows: List[torch.Tensor]) -> None:
         """Host rows (one contiguous uint8 tensor of ``record_bytes`` each) -> records, all requests queued at once."""
         if recs and self._uring():
-            self._rt.uring_rw(self.fd, True, [r * self.record_bytes for r in recs], [t.data_ptr() for t in rows], self.record_bytes)
-            self.records_out += len(recs)
-            return
+            try:
+                self._rt.uring_rw(self.fd, True, [r * self.record_bytes for r in recs], [t.data_ptr() for t in rows], self.record_bytes)
+                self.records_out += len(recs)
+                return
+            except OSError:
+                self._uring_ok = False            # e.g. a filesystem that refuses the request type: plain I/O from now on
         for rec, t in zip(recs, rows):
             self.write(rec, t.numpy().tobytes())
 
     def read_many(self, recs: List[int], rows: List[torch.Tensor]) -> None:
         """Records -> host rows, read in place (no intermediate bytes objects on the batched path)."""
         if recs and self._uring():
-            self._rt.uring_rw(self.fd, False, [r * self.record_bytes for r in recs], [t.data_ptr() for t in rows], self.record_bytes)
-            self.records_in += len(recs)
-            return
+            try:
+                self._rt.uring_rw(self.fd, False, [r * self.record_bytes for r in recs], [t.data_ptr() for t in rows], self.record_bytes)
+                self.records_in += len(recs)
+                return
+            except OSError:
+                self._uring_ok = False
         for rec, t in zip(recs, rows):
             t.copy_(torch.frombuffer(bytearray(self.read(rec)), dtype=torch.uint8))
 
